@@ -1,0 +1,58 @@
+// extern "C" surface of libembodiinfer_b200.so: argument checks, then the launchers.
+// Declarations and per-entry documentation live in include/embodiinfer_b200.h.
+#include "common.cuh"
+
+namespace b2 {
+int run_linear(const b2_linear_desc* desc, cudaStream_t stream);
+int launch_geglu(const void* gate, const void* up, void* output, void* scales, void* blocked, const void* scale,
+                 int rows, int columns, int64_t row_stride, int bits, const void* table, int flags,
+                 cudaStream_t stream);
+}  // namespace b2
+
+static bool is_aligned(const void* pointer, uintptr_t bytes) {
+    return (reinterpret_cast<uintptr_t>(pointer) & (bytes - 1)) == 0;
+}
+
+extern "C" {
+
+int b2_abi_version(void) { return B2_ABI_VERSION; }
+
+int b2_tensor_scale(const void* input, int64_t count, float bound, int flags, void* scratch, void* scale,
+                    void* stream) {
+    if (input == nullptr || scratch == nullptr || scale == nullptr || count <= 0 || !(bound > 0.0f)) return B2_E_INVALID;
+    if (!is_aligned(input, 16) || !is_aligned(scratch, 4) || !is_aligned(scale, 4)) return B2_E_INVALID;
+    return b2::launch_tensor_scale(input, count, bound, flags, scratch, scale, static_cast<cudaStream_t>(stream));
+}
+
+int b2_fp8_quantize(const void* input, void* output, const void* scale, int64_t count, int flags, void* stream) {
+    if (input == nullptr || output == nullptr || scale == nullptr || count <= 0) return B2_E_INVALID;
+    if (!is_aligned(input, 16) || !is_aligned(output, 8)) return B2_E_INVALID;
+    return b2::launch_fp8_encode(input, output, scale, count, flags, static_cast<cudaStream_t>(stream));
+}
+
+int b2_nvfp4_quantize(const void* input, void* output, void* scales, void* blocked, const void* global, int rows,
+                      int columns, int flags, void* stream) {
+    if (input == nullptr || output == nullptr || global == nullptr || rows <= 0 || columns <= 0) return B2_E_INVALID;
+    if (columns % 16 != 0) return B2_E_UNSUPPORTED;
+    if (!is_aligned(input, 16) || !is_aligned(output, 4)) return B2_E_INVALID;
+    if ((scales != nullptr && !is_aligned(scales, 4)) || (blocked != nullptr && !is_aligned(blocked, 4)))
+        return B2_E_INVALID;
+    return b2::launch_nvfp4_encode(input, output, scales, blocked, global, rows, columns, flags,
+                                   static_cast<cudaStream_t>(stream));
+}
+
+int b2_geglu(const void* gate, const void* up, void* output, void* scales, void* blocked, const void* scale,
+             int rows, int columns, int64_t row_stride, int bits, const void* table, int flags, void* stream) {
+    if (gate == nullptr || output == nullptr || table == nullptr || rows <= 0 || columns <= 0) return B2_E_INVALID;
+    if (row_stride < columns) return B2_E_INVALID;
+    if (bits != 4 && bits != 8 && bits != 16) return B2_E_UNSUPPORTED;
+    if (bits != 16 && scale == nullptr) return B2_E_INVALID;
+    return b2::launch_geglu(gate, up, output, scales, blocked, scale, rows, columns, row_stride, bits, table, flags,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int b2_linear(const b2_linear_desc* desc, void* stream) {
+    return b2::run_linear(desc, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

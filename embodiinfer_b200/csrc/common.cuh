@@ -1,0 +1,170 @@
+// Shared device helpers: vector loads, bf16 unpacking, the two reference quantiser
+// arithmetics (spec T = torch route, spec C = CUDA route) and the scale-tile offset.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <cfloat>
+#include <cstdint>
+
+#include "../../include/embodiinfer_b200.h"
+
+namespace b2 {
+
+int sm_count();
+
+// ---- loads -----------------------------------------------------------------
+
+__device__ __forceinline__ uint4 ld_nc_u4(const uint4* pointer) {
+    uint4 value;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(value.x), "=r"(value.y), "=r"(value.z), "=r"(value.w)
+                 : "l"(pointer));
+    return value;
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t word) { return __uint_as_float(word << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t word) { return __uint_as_float(word & 0xffff0000u); }
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& packed, float (&v)[8]) {
+    v[0] = bf16_lo(packed.x); v[1] = bf16_hi(packed.x);
+    v[2] = bf16_lo(packed.y); v[3] = bf16_hi(packed.y);
+    v[4] = bf16_lo(packed.z); v[5] = bf16_hi(packed.z);
+    v[6] = bf16_lo(packed.w); v[7] = bf16_hi(packed.w);
+}
+
+__device__ __forceinline__ float abs_max_bf16x8(const uint4& packed) {
+    float v[8];
+    unpack_bf16x8(packed, v);
+    float maximum = fabsf(v[0]);
+#pragma unroll
+    for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, fabsf(v[i]));
+    return maximum;
+}
+
+__device__ __forceinline__ float round_to_bf16(float value) {
+    return __bfloat162float(__float2bfloat16_rn(value));
+}
+
+__device__ __forceinline__ uint16_t bf16_bits(float value) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(value));
+}
+
+// ---- scales ----------------------------------------------------------------
+
+// amax -> per-tensor scale.  `bound` is 448 (FP8) or 448*6 (NVFP4).
+//   B2_SCALAR_RCP  multiply by the rounded fp32 reciprocal (ATen on CUDA, quantize.cu:54)
+//                  instead of dividing (ATen on CPU).
+//   B2_CLAMP_TINY  amax.clamp_min(tiny)/bound (nvfp4.py:38) instead of "1.0 for an all-zero tensor".
+__device__ __forceinline__ float scale_from_amax(float amax, float bound, int flags) {
+    if (flags & B2_CLAMP_TINY) amax = fmaxf(amax, FLT_MIN);
+    else if (!(amax > 0.0f)) return 1.0f;
+    return (flags & B2_SCALAR_RCP) ? __fmul_rn(amax, __fdiv_rn(1.0f, bound)) : __fdiv_rn(amax, bound);
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t code) {
+    return __half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3)));
+}
+
+__device__ __forceinline__ float clamp_keep_nan(float value, float bound) {
+    return value > bound ? bound : (value < -bound ? -bound : value);
+}
+
+// ---- FP8 -------------------------------------------------------------------
+
+// Four values -> four e4m3 bytes (first value in the low byte).
+//   spec C: fp32 quotient (quantize.cu:62-64).
+//   spec T: quotient rounded to bf16, clamped to +-448 (fp8.py:72).
+template <bool SPEC_C>
+__device__ __forceinline__ uint32_t encode_fp8x4(float a, float b, float c, float d, float scale) {
+    float q[4] = {__fdiv_rn(a, scale), __fdiv_rn(b, scale), __fdiv_rn(c, scale), __fdiv_rn(d, scale)};
+    if (!SPEC_C) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = clamp_keep_nan(round_to_bf16(q[i]), 448.0f);
+    }
+    const uint32_t low = __nv_cvt_float2_to_fp8x2(make_float2(q[0], q[1]), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t high = __nv_cvt_float2_to_fp8x2(make_float2(q[2], q[3]), __NV_SATFINITE, __NV_E4M3);
+    return low | (high << 16);
+}
+
+// Same, but the caller supplies already-divided values (used by fused epilogues).
+__device__ __forceinline__ uint32_t pack_fp8x4(float a, float b, float c, float d) {
+    const uint32_t low = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t high = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return low | (high << 16);
+}
+
+// ---- NVFP4 -----------------------------------------------------------------
+
+// e4m3 scale of one 16-element block.
+//   spec C: e4m3(min(448, max/(6*g)))                      quantize.cu:85-86
+//   spec T: e4m3(clamp(max/6/g, tiny, 448))                nvfp4.py:40
+template <bool SPEC_C>
+__device__ __forceinline__ uint8_t nvfp4_block_scale(float block_max, float global, int flags) {
+    float raw;
+    if (SPEC_C) {
+        raw = fminf(448.0f, __fdiv_rn(block_max, __fmul_rn(6.0f, global)));
+    } else {
+        const float sixth = (flags & B2_SCALAR_RCP) ? __fmul_rn(block_max, __fdiv_rn(1.0f, 6.0f))
+                                                    : __fdiv_rn(block_max, 6.0f);
+        raw = __fdiv_rn(sixth, global);
+        raw = raw < FLT_MIN ? FLT_MIN : (raw > 448.0f ? 448.0f : raw);
+    }
+    return uint8_t(__nv_cvt_float_to_fp8(raw, __NV_SATFINITE, __NV_E4M3));
+}
+
+// Torch-route e2m1 code: bucketize(|v|) with ties toward zero, NaN -> 7, sign = v < 0 (nvfp4.py:42-44).
+__device__ __forceinline__ uint32_t e2m1_bucketize(float value) {
+    const float a = fabsf(value);
+    uint32_t magnitude = uint32_t(a > 0.25f) + uint32_t(a > 0.75f) + uint32_t(a > 1.25f) + uint32_t(a > 1.75f) +
+                         uint32_t(a > 2.5f) + uint32_t(a > 3.5f) + uint32_t(a > 5.0f);
+    if (a != a) magnitude = 7u;
+    return magnitude | (value < 0.0f ? 8u : 0u);
+}
+
+// Eight values of one half-block -> eight nibbles, first value in the lowest nibble.
+//   spec C: x/den (0 when den == 0), hardware round-to-nearest-even e2m1   quantize.cu:91-95
+//   spec T: clamp(x/den, +-6) then bucketize                               nvfp4.py:41-44
+template <bool SPEC_C>
+__device__ __forceinline__ uint32_t nvfp4_encode_x8(const float (&v)[8], float denominator) {
+    uint32_t word = 0;
+    if (SPEC_C) {
+        const bool positive = denominator > 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float first = positive ? __fdiv_rn(v[2 * i], denominator) : 0.0f;
+            const float second = positive ? __fdiv_rn(v[2 * i + 1], denominator) : 0.0f;
+            const uint32_t byte = __nv_cvt_float2_to_fp4x2(make_float2(first, second), __NV_E2M1, cudaRoundNearest);
+            word |= (byte & 0xffu) << (8 * i);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float normalized = clamp_keep_nan(__fdiv_rn(v[i], denominator), 6.0f);
+            word |= e2m1_bucketize(normalized) << (4 * i);
+        }
+    }
+    return word;
+}
+
+// Byte offset of the scale of (row, 16-element block) in the 128x4-tile layout
+// (nvfp4.py:14-25, quantize.cu:97-101).  One tile is 512 bytes: 32 rows x 16 bytes,
+// each 16-byte row holding [row, row+32, row+64, row+96] x 4 blocks.
+__host__ __device__ __forceinline__ int64_t scale_tile_offset(int row, int block, int column_tiles) {
+    return (int64_t(row >> 7) * column_tiles + (block >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 +
+           (block & 3);
+}
+
+// ---- launchers shared between translation units ---------------------------------
+
+int launch_tensor_scale(const void* input, int64_t count, float bound, int flags, void* scratch, void* scale,
+                        cudaStream_t stream);
+int launch_fp8_encode(const void* input, void* output, const void* scale, int64_t count, int flags,
+                      cudaStream_t stream);
+int launch_nvfp4_encode(const void* input, void* output, void* scales, void* blocked, const void* global, int rows,
+                        int columns, int flags, cudaStream_t stream);
+
+}  // namespace b2

@@ -1,0 +1,650 @@
+// Quantised Linear on the 5th-generation tensor cores (sm_100a).
+//
+//   out[token, feature] = epilogue( sum_k act[token, k] * weight[feature, k] )
+//
+// Both operands are K-major in global memory.  A tile is 128 tokens (the MMA "A"
+// operand, one token per TMEM lane) by BN features (the "B" operand, one feature per
+// TMEM column).  TMA brings 128-byte-wide K slices of both into 128-byte-swizzled
+// shared-memory stages; one thread issues `tcgen05.mma` (kind::f8f6f4 for e4m3,
+// kind::mxf4nvf4 with a ue4m3 scale per 16 elements for e2m1) into fp32 accumulators
+// in tensor memory.  Because a token's features lie along the columns of its own lane,
+// an epilogue thread owns whole 16-element quantisation blocks of the output row and
+// writes 16-byte vectors: no shuffles, no transposition.
+//
+// One persistent CTA per SM, ten warps:
+//   warp 0      TMA producer (one lane)
+//   warp 1      TMEM owner and MMA issuer (one lane)
+//   warps 2..9  epilogue; warps w and w+4 share a 32-lane TMEM partition and split the columns
+// Accumulators are double-buffered in TMEM whenever two fit, so the epilogue of one
+// tile overlaps the main loop of the next.  Tiles that share a weight slab are
+// consecutive in the schedule, so the slab comes from HBM once and from L2 afterwards.
+//
+// Gated MLP: the gate rows and the up rows of the packed [2F, K] weight land in one
+// shared-memory B tile ([gate BN/2 rows | up BN/2 rows]); one MMA fills columns
+// [0, BN/2) with gate and [BN/2, BN) with up, so an epilogue thread finds gate and up
+// of the same feature in its own lane.
+//
+// Every wait is bounded (ptx.cuh); an expired wait leaves a code in the status word.
+#include "common.cuh"
+#include "ptx.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+
+namespace b2 {
+
+constexpr int GEMM_THREADS = 320;
+constexpr int EPILOGUE_WARPS = 8;
+constexpr int TILE_TOKENS = 128;                   // MMA M
+constexpr int STAGE_K_BYTES = 128;                 // one swizzle row
+constexpr int A_TILE_BYTES = TILE_TOKENS * STAGE_K_BYTES;
+constexpr int SCALE_ATOM_BYTES = 512;              // 128 rows x 4 blocks of 16
+constexpr int SCALE_ATOMS_PER_STAGE = 4;           // 4 x 64 elements = 256 e2m1 = 128 bytes of K
+constexpr int SCALE_STAGE_BYTES = 3 * SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;   // act + two weight row blocks
+constexpr int MAX_STAGES = 8;
+constexpr int TMEM_COLUMNS = 512;
+constexpr int TMEM_SFA = 448;                      // NVFP4: token scales, 4 columns per 64 elements of K
+constexpr int TMEM_SFB = 464;                      // NVFP4: feature scales, 8 columns per 64 elements of K
+constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr int SMEM_MINIMUM = 120 * 1024;           // keeps a second CTA (and its TMEM request) off the SM
+
+enum { EPI_LINEAR = 0, EPI_GEGLU_BF16 = 1, EPI_GEGLU_FP8 = 2, EPI_GEGLU_NVFP4 = 3 };
+
+struct KernelArgs {
+    int tokens, features, k_bytes, num_kb;
+    int tile_n;                  // TMEM columns per tile (GEGLU: gate half + up half)
+    int num_m_tiles, num_n_tiles, total_tiles;
+    int stages, accumulators;
+    int up_row_offset;           // row of the first "up" feature in the packed weight
+    int scale_column_tiles;      // 512-byte scale atoms per 128-row block
+    int act_row_blocks, weight_row_blocks;
+    int flags;
+    const uint8_t* act_scales;
+    const uint8_t* weight_scales;
+    const float* act_scale;
+    const float* weight_scale;
+    const __nv_bfloat16* bias;
+    const __nv_bfloat16* residual;
+    const uint16_t* gelu_table;
+    const float* out_scale;
+    void* out;
+    uint8_t* out_scales;
+    uint8_t* out_blocked;
+    unsigned int* status;
+};
+
+// ---- epilogue helpers ---------------------------------------------------------
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float low, float high) {
+    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+// acc -> the bf16 value the reference's GEMM returns, widened to fp32.
+//   plain:        bf16(acc * s)
+//   round_scale:  bf16(bf16(acc) * s) with s already rounded to bf16 (nvfp4.py:120)
+__device__ __forceinline__ float gemm_value(uint32_t acc_bits, float scale, bool round_scale) {
+    float acc = __uint_as_float(acc_bits);
+    if (round_scale) acc = round_to_bf16(acc);
+    return round_to_bf16(__fmul_rn(acc, scale));
+}
+
+__device__ __forceinline__ void store_u4(void* pointer, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    *reinterpret_cast<uint4*>(pointer) = make_uint4(a, b, c, d);
+}
+
+// 32 accumulator columns of one token -> 32 bf16 outputs (64 contiguous bytes).
+__device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32], const KernelArgs& args, float scale,
+                                                      bool round_scale, int token, int feature0) {
+    float y[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) y[i] = gemm_value(acc[i], scale, round_scale);
+    if (args.bias != nullptr) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (feature0 + 8 * v < args.features) {
+                const uint4 packed = __ldg(reinterpret_cast<const uint4*>(args.bias + feature0 + 8 * v));
+                float b[8];
+                unpack_bf16x8(packed, b);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[8 * v + i] = round_to_bf16(__fadd_rn(y[8 * v + i], b[i]));
+            }
+        }
+    }
+    if (token >= args.tokens) return;
+    const int64_t row = int64_t(token) * args.features;
+    if (args.residual != nullptr) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (feature0 + 8 * v < args.features) {
+                const uint4 packed = ld_nc_u4(reinterpret_cast<const uint4*>(args.residual + row + feature0 + 8 * v));
+                float r[8];
+                unpack_bf16x8(packed, r);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) y[8 * v + i] = round_to_bf16(__fadd_rn(y[8 * v + i], r[i]));
+            }
+        }
+    }
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out) + row + feature0;
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+        if (feature0 + 8 * v < args.features)
+            store_u4(out + 8 * v, pack_bf16x2(y[8 * v], y[8 * v + 1]), pack_bf16x2(y[8 * v + 2], y[8 * v + 3]),
+                     pack_bf16x2(y[8 * v + 4], y[8 * v + 5]), pack_bf16x2(y[8 * v + 6], y[8 * v + 7]));
+}
+
+// 32 gate + 32 up accumulator columns of one token -> 32 hidden values
+// h = bf16(bf16(gelu(gate)) * up), stored as bf16, e4m3 or NVFP4 (fusion.cu:5-10, 31-107).
+template <int EPI>
+__device__ __forceinline__ void epilogue_geglu_chunk(const uint32_t (&gate_acc)[32], const uint32_t (&up_acc)[32],
+                                                     const KernelArgs& args, float scale, bool round_scale,
+                                                     float out_scale, float out_scale_rcp, bool true_div, int token,
+                                                     int feature0) {
+    float h[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const float gate = gemm_value(gate_acc[i], scale, round_scale);
+        const float up = gemm_value(up_acc[i], scale, round_scale);
+        const float gelu = bf16_lo(uint32_t(__ldg(args.gelu_table + (__float_as_uint(gate) >> 16))));
+        h[i] = round_to_bf16(__fmul_rn(gelu, up));
+    }
+    if (token >= args.tokens || feature0 >= args.features) return;
+    const int64_t element = int64_t(token) * args.features + feature0;
+    if (EPI == EPI_GEGLU_BF16) {
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out) + element;
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+            if (feature0 + 8 * v < args.features)
+                store_u4(out + 8 * v, pack_bf16x2(h[8 * v], h[8 * v + 1]), pack_bf16x2(h[8 * v + 2], h[8 * v + 3]),
+                         pack_bf16x2(h[8 * v + 4], h[8 * v + 5]), pack_bf16x2(h[8 * v + 6], h[8 * v + 7]));
+    } else if (EPI == EPI_GEGLU_FP8) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) h[i] = true_div ? __fdiv_rn(h[i], out_scale) : __fmul_rn(h[i], out_scale_rcp);
+        uint8_t* out = static_cast<uint8_t*>(args.out) + element;
+#pragma unroll
+        for (int v = 0; v < 2; ++v)
+            if (feature0 + 16 * v < args.features)
+                store_u4(out + 16 * v, pack_fp8x4(h[16 * v], h[16 * v + 1], h[16 * v + 2], h[16 * v + 3]),
+                         pack_fp8x4(h[16 * v + 4], h[16 * v + 5], h[16 * v + 6], h[16 * v + 7]),
+                         pack_fp8x4(h[16 * v + 8], h[16 * v + 9], h[16 * v + 10], h[16 * v + 11]),
+                         pack_fp8x4(h[16 * v + 12], h[16 * v + 13], h[16 * v + 14], h[16 * v + 15]));
+    } else {
+        // Two whole 16-element blocks of the next layer's input (quantize.cu:85-104 arithmetic).
+        uint32_t words[4];
+        uint32_t scale_codes = 0;
+#pragma unroll
+        for (int block = 0; block < 2; ++block) {
+            float block_max = fabsf(h[16 * block]);
+#pragma unroll
+            for (int i = 1; i < 16; ++i) block_max = fmaxf(block_max, fabsf(h[16 * block + i]));
+            const uint8_t code = nvfp4_block_scale<true>(block_max, out_scale, 0);
+            const float denominator = __fmul_rn(out_scale, e4m3_to_float(code));
+            scale_codes |= uint32_t(code) << (8 * block);
+            float low[8], high[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { low[i] = h[16 * block + i]; high[i] = h[16 * block + 8 + i]; }
+            words[2 * block] = nvfp4_encode_x8<true>(low, denominator);
+            words[2 * block + 1] = nvfp4_encode_x8<true>(high, denominator);
+        }
+        const bool second = feature0 + 16 < args.features;
+        uint8_t* out = static_cast<uint8_t*>(args.out) + (element >> 1);
+        if (second) store_u4(out, words[0], words[1], words[2], words[3]);
+        else *reinterpret_cast<uint2*>(out) = make_uint2(words[0], words[1]);
+        const int block0 = feature0 >> 4;
+        const int blocks_per_row = args.features >> 4;
+        if (args.out_scales != nullptr) {
+            uint8_t* linear = args.out_scales + int64_t(token) * blocks_per_row + block0;
+            if (second) *reinterpret_cast<uint16_t*>(linear) = uint16_t(scale_codes);
+            else *linear = uint8_t(scale_codes);
+        }
+        if (args.out_blocked != nullptr) {
+            uint8_t* tiled = args.out_blocked + scale_tile_offset(token, block0, (blocks_per_row + 3) >> 2);
+            if (second) *reinterpret_cast<uint16_t*>(tiled) = uint16_t(scale_codes);
+            else *tiled = uint8_t(scale_codes);
+        }
+    }
+}
+
+// ---- the kernel ---------------------------------------------------------------
+
+template <int KIND, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
+              const KernelArgs args) {
+    constexpr bool GEGLU = EPI != EPI_LINEAR;
+    extern __shared__ uint8_t shared_raw[];
+    const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
+    const int BN = args.tile_n;
+    const int features_per_tile = GEGLU ? BN / 2 : BN;
+    const uint32_t stage_bytes = A_TILE_BYTES + uint32_t(BN) * STAGE_K_BYTES;
+    const uint32_t scale_stage_bytes = KIND == B2_KIND_NVFP4 ? SCALE_STAGE_BYTES : 0;
+    const uint32_t scale_base = base + uint32_t(args.stages) * stage_bytes;
+    const uint32_t barrier_base = scale_base + uint32_t(args.stages) * scale_stage_bytes;
+    const uint32_t full_bar = barrier_base;                       // [stages]
+    const uint32_t empty_bar = barrier_base + 8 * MAX_STAGES;     // [stages]
+    const uint32_t acc_full_bar = barrier_base + 16 * MAX_STAGES; // [2]
+    const uint32_t acc_empty_bar = acc_full_bar + 16;             // [2]
+    const uint32_t tmem_slot = acc_empty_bar + 16;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&act_map);
+        tma_prefetch_descriptor(&weight_map);
+        for (int s = 0; s < args.stages; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar + 8 * b, 1);
+            mbar_init(acc_empty_bar + 8 * b, EPILOGUE_WARPS);
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLUMNS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    bool failed = false;
+    const int num_kb = args.num_kb;
+    const int last_kb_mmas = ((args.k_bytes - (num_kb - 1) * STAGE_K_BYTES) + 31) / 32;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t filled = 0, fill_parity = 0;     // per stage: ever filled / phase of the last fill
+            for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) {
+                const int n_tile = tile / args.num_m_tiles;
+                const int m_tile = tile - n_tile * args.num_m_tiles;
+                const int m0 = m_tile * TILE_TOKENS;
+                const int f0 = n_tile * features_per_tile;
+                // weight rows whose scales this tile needs: up to two 128-row blocks
+                int scale_row_block[2];
+                int scale_blocks;
+                if (GEGLU) {
+                    scale_row_block[0] = f0 >> 7;
+                    scale_row_block[1] = (args.up_row_offset + f0) >> 7;
+                    scale_blocks = 2;
+                } else {
+                    scale_row_block[0] = f0 >> 7;
+                    scale_row_block[1] = scale_row_block[0] + 1;
+                    scale_blocks = ((f0 + BN - 1) >> 7) - scale_row_block[0] + 1;
+                }
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
+                    const uint32_t bar = full_bar + 8 * stage;
+                    uint32_t bytes = stage_bytes;
+                    int atoms = 0;
+                    if (KIND == B2_KIND_NVFP4) {
+                        atoms = min(SCALE_ATOMS_PER_STAGE, args.scale_column_tiles - kb * SCALE_ATOMS_PER_STAGE);
+                        int live = 1;
+                        for (int i = 0; i < scale_blocks; ++i) live += scale_row_block[i] < args.weight_row_blocks;
+                        bytes += uint32_t(live * atoms) * SCALE_ATOM_BYTES;
+                    }
+                    mbar_expect_tx(bar, bytes);
+                    filled |= 1u << stage;
+                    fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
+                    const uint32_t a_smem = base + uint32_t(stage) * stage_bytes;
+                    const uint32_t b_smem = a_smem + A_TILE_BYTES;
+                    tma_load_2d(a_smem, &act_map, bar, kb * STAGE_K_BYTES, m0);
+                    tma_load_2d(b_smem, &weight_map, bar, kb * STAGE_K_BYTES, f0);
+                    if (GEGLU)
+                        tma_load_2d(b_smem + uint32_t(BN / 2) * STAGE_K_BYTES, &weight_map, bar, kb * STAGE_K_BYTES,
+                                    args.up_row_offset + f0);
+                    if (KIND == B2_KIND_NVFP4) {
+                        const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
+                        const uint32_t copy_bytes = uint32_t(atoms) * SCALE_ATOM_BYTES;
+                        const int64_t atom0 = int64_t(kb) * SCALE_ATOMS_PER_STAGE;
+                        bulk_load(s_smem,
+                                  args.act_scales + (int64_t(m_tile) * args.scale_column_tiles + atom0) * SCALE_ATOM_BYTES,
+                                  copy_bytes, bar);
+                        for (int i = 0; i < scale_blocks; ++i) {
+                            if (scale_row_block[i] >= args.weight_row_blocks) continue;
+                            bulk_load(s_smem + (1 + i) * SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES,
+                                      args.weight_scales +
+                                          (int64_t(scale_row_block[i]) * args.scale_column_tiles + atom0) * SCALE_ATOM_BYTES,
+                                      copy_bytes, bar);
+                        }
+                    }
+                    if (++stage == args.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            // Do not leave while a copy of this CTA is still in flight: wait (bounded) for the
+            // last fill of every stage.  On the normal path these have all completed already.
+            bool drain_failed = false;
+            for (int s = 0; s < args.stages; ++s)
+                if (filled & (1u << s))
+                    mbar_wait(full_bar + 8 * s, (fill_parity >> s) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = KIND == B2_KIND_NVFP4 ? idesc_nvf4(TILE_TOKENS, BN) : idesc_f8(TILE_TOKENS, BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            int local_tile = 0;
+            for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x, ++local_tile) {
+                const int n_tile = tile / args.num_m_tiles;
+                const int f0 = n_tile * features_per_tile;
+                const int scale_offset = (f0 & 127) >> 5;          // column of feature f0 inside its scale block
+                const int scale_blocks = GEGLU ? 2 : ((f0 + BN - 1) >> 7) - (f0 >> 7) + 1;
+                const int buffer = local_tile % args.accumulators;
+                const uint32_t use = uint32_t(local_tile / args.accumulators);
+                mbar_wait(acc_empty_bar + 8 * buffer, (use & 1u) ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + uint32_t(buffer) * 256u;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
+                    tc_fence_after_sync();
+                    const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
+                    const uint32_t a_smem = base + uint32_t(stage) * stage_bytes;
+                    const uint32_t b_smem = a_smem + A_TILE_BYTES;
+                    uint32_t sfb_column[SCALE_ATOMS_PER_STAGE] = {0, 0, 0, 0};
+                    if (KIND == B2_KIND_NVFP4) {
+                        const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
+                        constexpr uint32_t PART = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
+#pragma unroll
+                        for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
+                            if (j >= mmas) break;
+                            const uint32_t atom = uint32_t(j) * SCALE_ATOM_BYTES;
+                            tc_copy_32x128b_x4(tmem_base + TMEM_SFA + j * 4, smem_desc_scale_atom(s_smem + atom));
+                            const uint32_t region = tmem_base + TMEM_SFB + j * 8;
+                            const uint64_t first = smem_desc_scale_atom(s_smem + PART + atom);
+                            const uint64_t second = smem_desc_scale_atom(s_smem + 2 * PART + atom);
+                            if (!GEGLU) {
+                                // one or two consecutive 128-row blocks; the MMA starts reading at the tile's column
+                                tc_copy_32x128b_x4(region, first);
+                                if (scale_blocks == 2) tc_copy_32x128b_x4(region + 4, second);
+                                sfb_column[j] = region + scale_offset;
+                            } else if (BN == 256) {
+                                // 128 gate features then 128 up features: two whole blocks side by side
+                                tc_copy_32x128b_x4(region, first);
+                                tc_copy_32x128b_x4(region + 4, second);
+                                sfb_column[j] = region;
+                            } else {
+                                // 64 gate + 64 up features: two columns of each block must end up adjacent at
+                                // region+2 .. region+5.  The copies move whole 4-column blocks, so the one whose
+                                // unwanted half would cover the other's wanted half goes first.
+                                if (scale_offset == 0) {
+                                    tc_copy_32x128b_x4(region + 2, first);       // gate columns 0,1 -> +2,+3
+                                    tc_copy_32x128b_x4(region + 4, second);      // up columns 0,1   -> +4,+5
+                                } else {
+                                    tc_copy_32x128b_x4(region + 2, second);      // up columns 2,3   -> +4,+5
+                                    tc_copy_32x128b_x4(region, first);           // gate columns 2,3 -> +2,+3
+                                }
+                                sfb_column[j] = region + 2;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
+                        if (j >= mmas) break;
+                        const uint64_t a_desc = smem_desc_sw128(a_smem + j * 32);
+                        const uint64_t b_desc = smem_desc_sw128(b_smem + j * 32);
+                        const uint32_t accumulate = (kb | j) != 0;
+                        if (KIND == B2_KIND_NVFP4)
+                            mma_nvf4(d_tmem, a_desc, b_desc, idesc, tmem_base + TMEM_SFA + j * 4, sfb_column[j], accumulate);
+                        else
+                            mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, accumulate);
+                    }
+                    tc_commit(empty_bar + 8 * stage);
+                    if (++stage == args.stages) { stage = 0; phase ^= 1u; }
+                }
+                tc_commit(acc_full_bar + 8 * buffer);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;                      // the TMEM lane partition this warp may read
+        const int half = (warp - 2) >> 2;                  // which half of the tile's features this warp stores
+        const bool round_scale = (args.flags & B2_LINEAR_ROUND_SCALE_BF16) != 0;
+        float scale = __fmul_rn(__ldg(args.act_scale), __ldg(args.weight_scale));
+        if (round_scale) scale = round_to_bf16(scale);
+        float out_scale = 1.0f, out_scale_rcp = 1.0f;
+        if (EPI == EPI_GEGLU_FP8 || EPI == EPI_GEGLU_NVFP4) {
+            out_scale = __ldg(args.out_scale);
+            out_scale_rcp = __fdiv_rn(1.0f, out_scale);
+        }
+        const bool true_div = (args.flags & B2_GEGLU_TRUE_DIV) != 0;
+        const int chunks = features_per_tile / 32;             // 32-feature chunks in the tile
+        const int chunk_begin = half == 0 ? 0 : (chunks + 1) / 2;
+        const int chunk_end = half == 0 ? (chunks + 1) / 2 : chunks;
+        int local_tile = 0;
+        for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x, ++local_tile) {
+            const int n_tile = tile / args.num_m_tiles;
+            const int m_tile = tile - n_tile * args.num_m_tiles;
+            const int token = m_tile * TILE_TOKENS + quarter * 32 + lane;
+            const int f0 = n_tile * features_per_tile;
+            const int buffer = local_tile % args.accumulators;
+            const uint32_t use = uint32_t(local_tile / args.accumulators);
+            mbar_wait(acc_full_bar + 8 * buffer, use & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
+            tc_fence_after_sync();
+            const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer) * 256u;
+            for (int chunk = chunk_begin; chunk < chunk_end; ++chunk) {
+                uint32_t first[32];
+                tmem_load_32x32(lane_address + chunk * 32, first);
+                if (GEGLU) {
+                    uint32_t second[32];
+                    tmem_load_32x32(lane_address + BN / 2 + chunk * 32, second);
+                    tmem_load_wait();
+                    epilogue_geglu_chunk<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, scale, round_scale, out_scale,
+                                                                      out_scale_rcp, true_div, token, f0 + chunk * 32);
+                } else {
+                    tmem_load_wait();
+                    epilogue_linear_chunk(first, args, scale, round_scale, token, f0 + chunk * 32);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buffer);
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_entry() {
+    static EncodeTiledFn entry = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* pointer = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pointer, cudaEnableDefault, &result) == cudaSuccess &&
+            result == cudaDriverEntryPointSuccess)
+            entry = reinterpret_cast<EncodeTiledFn>(pointer);
+    });
+    return entry;
+}
+
+// Row-major byte matrix [rows, row_bytes] viewed as tiles of box_rows x 128 bytes, 128-byte swizzle.
+// Rows and bytes beyond the matrix read as zero.
+static bool make_operand_map(CUtensorMap* map, const void* pointer, int64_t rows, int64_t row_bytes, int box_rows) {
+    EncodeTiledFn encode = encode_tiled_entry();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {cuuint64_t(row_bytes), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(row_bytes)};
+    const cuuint32_t box[2] = {cuuint32_t(STAGE_K_BYTES), cuuint32_t(box_rows)};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(pointer), dims, strides, box,
+                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int sm_count() {
+    static int counts[64] = {0};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64) device = 0;
+    if (counts[device] == 0) {
+        int value = 0;
+        cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device);
+        counts[device] = value > 0 ? value : 148;
+    }
+    return counts[device];
+}
+
+// Two accumulators (the second at column 256) fit beside the NVFP4 scale columns?
+static bool can_double_buffer(int kind, int tile_n) { return tile_n <= (kind == B2_KIND_NVFP4 ? TMEM_SFA - 256 : 256); }
+
+// LINEAR: 64, 128, 192 or 256 features per tile.  GEGLU: 64 or 128 features (128 or 256 columns).
+static bool tile_allowed(bool geglu, int features_per_tile) {
+    if (geglu) return features_per_tile == 64 || features_per_tile == 128;
+    return features_per_tile == 64 || features_per_tile == 128 || features_per_tile == 192 || features_per_tile == 256;
+}
+
+static int choose_feature_tile(int kind, bool geglu, int features, int m_tiles) {
+    const int sms = sm_count();
+    int best = 0;
+    double best_cost = 0.0;
+    for (int tile = 256; tile >= 64; tile -= 64) {
+        if (!tile_allowed(geglu, tile)) continue;
+        const int columns = geglu ? 2 * tile : tile;
+        const int64_t tiles = int64_t((features + tile - 1) / tile) * m_tiles;
+        const int64_t waves = (tiles + sms - 1) / sms;
+        // main-loop time grows with the columns; the epilogue adds to it unless it overlaps the next tile
+        const double cost = double(waves) * (columns + (can_double_buffer(kind, columns) ? 16.0 : 16.0 + 0.4 * columns));
+        if (best == 0 || cost < best_cost) { best = tile; best_cost = cost; }
+    }
+    return best;
+}
+
+template <int KIND, int EPI>
+static int launch_linear(const CUtensorMap& act_map, const CUtensorMap& weight_map, const KernelArgs& args,
+                         int shared_bytes, cudaStream_t stream) {
+    static bool configured[64] = {false};
+    static std::mutex lock;
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 0 && device < 64) {
+        std::lock_guard<std::mutex> guard(lock);
+        if (!configured[device]) {
+            const cudaError_t error = cudaFuncSetAttribute(linear_kernel<KIND, EPI>,
+                                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+            if (error != cudaSuccess) return int(error);
+            configured[device] = true;
+        }
+    }
+    const int grid = args.total_tiles < sm_count() ? args.total_tiles : sm_count();
+    linear_kernel<KIND, EPI><<<grid, GEMM_THREADS, shared_bytes, stream>>>(act_map, weight_map, args);
+    return int(cudaGetLastError());
+}
+
+static bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
+
+int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
+    if (d == nullptr) return B2_E_INVALID;
+    if (d->kind != B2_KIND_FP8 && d->kind != B2_KIND_NVFP4) return B2_E_UNSUPPORTED;
+    if (d->epilogue != B2_EPI_LINEAR && d->epilogue != B2_EPI_GEGLU) return B2_E_UNSUPPORTED;
+    if (d->tokens <= 0 || d->features <= 0 || d->width <= 0) return B2_E_INVALID;
+    if (d->act == nullptr || d->weight == nullptr || d->act_scale == nullptr || d->weight_scale == nullptr ||
+        d->out == nullptr)
+        return B2_E_INVALID;
+    if (!aligned16(d->act) || !aligned16(d->weight) || !aligned16(d->out)) return B2_E_INVALID;
+    if ((d->bias != nullptr && !aligned16(d->bias)) || (d->residual != nullptr && !aligned16(d->residual)))
+        return B2_E_INVALID;
+    const bool nvfp4 = d->kind == B2_KIND_NVFP4;
+    if (d->width % (nvfp4 ? 64 : 16) != 0) return B2_E_UNSUPPORTED;
+    if (nvfp4 && (d->act_scales == nullptr || d->weight_scales == nullptr || !aligned16(d->act_scales) ||
+                  !aligned16(d->weight_scales)))
+        return B2_E_INVALID;
+    const bool geglu = d->epilogue == B2_EPI_GEGLU;
+    int epilogue = EPI_LINEAR;
+    if (geglu) {
+        if (d->gelu_table == nullptr || d->bias != nullptr || d->residual != nullptr) return B2_E_INVALID;
+        if (d->out_format == B2_OUT_BF16) epilogue = EPI_GEGLU_BF16;
+        else if (d->out_format == B2_OUT_FP8) epilogue = EPI_GEGLU_FP8;
+        else if (d->out_format == B2_OUT_NVFP4) epilogue = EPI_GEGLU_NVFP4;
+        else return B2_E_UNSUPPORTED;
+        if (epilogue != EPI_GEGLU_BF16 && d->out_scale == nullptr) return B2_E_INVALID;
+        if (d->features % 16 != 0) return B2_E_UNSUPPORTED;            // whole output vectors / blocks
+        if (nvfp4 && d->features % 128 != 0) return B2_E_UNSUPPORTED;   // the up rows must start a scale block
+    } else {
+        if (d->out_format != B2_OUT_BF16) return B2_E_UNSUPPORTED;
+        if (d->features % 8 != 0) return B2_E_UNSUPPORTED;             // 16-byte output vectors
+    }
+
+    KernelArgs args{};
+    args.tokens = d->tokens;
+    args.features = d->features;
+    args.k_bytes = nvfp4 ? d->width / 2 : d->width;
+    args.num_kb = (args.k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+    args.num_m_tiles = (d->tokens + TILE_TOKENS - 1) / TILE_TOKENS;
+    const int feature_tile =
+        d->feature_tile > 0 ? d->feature_tile : choose_feature_tile(d->kind, geglu, d->features, args.num_m_tiles);
+    if (!tile_allowed(geglu, feature_tile)) return B2_E_UNSUPPORTED;
+    args.tile_n = geglu ? 2 * feature_tile : feature_tile;
+    args.num_n_tiles = (d->features + feature_tile - 1) / feature_tile;
+    args.total_tiles = args.num_m_tiles * args.num_n_tiles;
+    args.accumulators = can_double_buffer(d->kind, args.tile_n) ? 2 : 1;
+    args.up_row_offset = d->features;
+    args.scale_column_tiles = nvfp4 ? (d->width / 16 + 3) / 4 : 0;
+    args.act_row_blocks = (d->tokens + 127) / 128;
+    const int weight_rows = (geglu ? 2 : 1) * d->features;
+    args.weight_row_blocks = (weight_rows + 127) / 128;
+    args.flags = d->flags;
+    args.act_scales = static_cast<const uint8_t*>(d->act_scales);
+    args.weight_scales = static_cast<const uint8_t*>(d->weight_scales);
+    args.act_scale = static_cast<const float*>(d->act_scale);
+    args.weight_scale = static_cast<const float*>(d->weight_scale);
+    args.bias = static_cast<const __nv_bfloat16*>(d->bias);
+    args.residual = static_cast<const __nv_bfloat16*>(d->residual);
+    args.gelu_table = static_cast<const uint16_t*>(d->gelu_table);
+    args.out_scale = static_cast<const float*>(d->out_scale);
+    args.out = d->out;
+    args.out_scales = static_cast<uint8_t*>(d->out_scales);
+    args.out_blocked = static_cast<uint8_t*>(d->out_blocked);
+    args.status = static_cast<unsigned int*>(d->status);
+
+    const int stage_bytes = A_TILE_BYTES + args.tile_n * STAGE_K_BYTES;
+    const int scale_stage_bytes = nvfp4 ? SCALE_STAGE_BYTES : 0;
+    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 64;
+    int stages = (SMEM_LIMIT - fixed_bytes) / (stage_bytes + scale_stage_bytes);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) return B2_E_UNSUPPORTED;
+    args.stages = stages;
+    int shared_bytes = fixed_bytes + stages * (stage_bytes + scale_stage_bytes);
+    if (shared_bytes < SMEM_MINIMUM) shared_bytes = SMEM_MINIMUM;
+
+    CUtensorMap act_map, weight_map;
+    if (!make_operand_map(&act_map, d->act, d->tokens, args.k_bytes, TILE_TOKENS)) return B2_E_DRIVER;
+    if (!make_operand_map(&weight_map, d->weight, weight_rows, args.k_bytes, feature_tile)) return B2_E_DRIVER;
+
+    if (nvfp4) {
+        switch (epilogue) {
+            case EPI_LINEAR: return launch_linear<B2_KIND_NVFP4, EPI_LINEAR>(act_map, weight_map, args, shared_bytes, stream);
+            case EPI_GEGLU_BF16: return launch_linear<B2_KIND_NVFP4, EPI_GEGLU_BF16>(act_map, weight_map, args, shared_bytes, stream);
+            case EPI_GEGLU_FP8: return launch_linear<B2_KIND_NVFP4, EPI_GEGLU_FP8>(act_map, weight_map, args, shared_bytes, stream);
+            default: return launch_linear<B2_KIND_NVFP4, EPI_GEGLU_NVFP4>(act_map, weight_map, args, shared_bytes, stream);
+        }
+    }
+    switch (epilogue) {
+        case EPI_LINEAR: return launch_linear<B2_KIND_FP8, EPI_LINEAR>(act_map, weight_map, args, shared_bytes, stream);
+        case EPI_GEGLU_BF16: return launch_linear<B2_KIND_FP8, EPI_GEGLU_BF16>(act_map, weight_map, args, shared_bytes, stream);
+        case EPI_GEGLU_FP8: return launch_linear<B2_KIND_FP8, EPI_GEGLU_FP8>(act_map, weight_map, args, shared_bytes, stream);
+        default: return launch_linear<B2_KIND_FP8, EPI_GEGLU_NVFP4>(act_map, weight_map, args, shared_bytes, stream);
+    }
+}
+
+}  // namespace b2

@@ -1,0 +1,201 @@
+// Activation quantisers for sm_100a: bf16 -> FP8 e4m3 (per-tensor scale) and
+// bf16 -> NVFP4 (e2m1 codes, e4m3 scale per 16 elements, fp32 global scale).
+//
+// HBM-bound kernels: every thread moves 16 bytes per load, the tensor amax is
+// reduced with warp shuffles and one atomic per CTA, and the NVFP4 encoder
+// writes the block scales directly in the 128x4 tile order the block-scaled
+// tensor-core instruction consumes.
+//
+// Two arithmetics of the reference are reproduced bit for bit and selected by
+// `flags` (see embodiinfer_b200.h):
+//   spec T  embodiinfer/backend/torch/fp8.py:66-73, backend/torch/nvfp4.py:28-46
+//   spec C  embodiinfer/backend/cuda/csrc/quantize.cu:38-104
+#include "common.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+
+namespace b2 {
+
+constexpr int QUANT_THREADS = 256;
+
+// ---------------------------------------------------------------------------
+// tensor amax -> scale.  scratch[0] accumulates the amax bit pattern (non-negative
+// floats order like unsigned integers), scratch[1] counts finished CTAs.  The last
+// CTA publishes the scale and puts both words back to zero, so the same scratch
+// serves the next call on the stream without a memset.
+
+__global__ void __launch_bounds__(QUANT_THREADS)
+tensor_scale_kernel(const uint4* __restrict__ input, int64_t vectors, const __nv_bfloat16* __restrict__ tail,
+                    int tail_count, float bound, int flags, unsigned int* scratch, float* scale) {
+    float maximum = 0.0f;
+    const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
+    for (int64_t index = int64_t(blockIdx.x) * QUANT_THREADS + threadIdx.x; index < vectors; index += stride) {
+        const uint4 packed = ld_nc_u4(input + index);
+        maximum = fmaxf(maximum, abs_max_bf16x8(packed));
+    }
+    if (blockIdx.x == 0 && int(threadIdx.x) < tail_count)
+        maximum = fmaxf(maximum, fabsf(__bfloat162float(tail[threadIdx.x])));
+#pragma unroll
+    for (int delta = 16; delta; delta >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, delta));
+    __shared__ float warp_max[QUANT_THREADS / 32];
+    __shared__ bool last_block;
+    if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = maximum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int warp = 1; warp < QUANT_THREADS / 32; ++warp) maximum = fmaxf(maximum, warp_max[warp]);
+        atomicMax(scratch, __float_as_uint(maximum));
+        __threadfence();
+        const unsigned int ticket = atomicAdd(scratch + 1, 1u);
+        last_block = ticket == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (last_block && threadIdx.x == 0) {
+        __threadfence();
+        const float total = __uint_as_float(atomicExch(scratch, 0u));
+        scratch[1] = 0u;
+        *scale = scale_from_amax(total, bound, flags);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// FP8 encode: 8 bf16 in (16 bytes), 8 e4m3 out (8 bytes) per thread per step.
+
+template <bool SPEC_C>
+__global__ void __launch_bounds__(QUANT_THREADS)
+fp8_encode_kernel(const uint4* __restrict__ input, uint2* __restrict__ output, int64_t vectors,
+                  const __nv_bfloat16* __restrict__ tail_in, uint8_t* __restrict__ tail_out, int tail_count,
+                  const float* __restrict__ scale_pointer, int flags) {
+    float scale = __ldg(scale_pointer);
+    if (!SPEC_C && (flags & B2_DIVISOR_BF16)) scale = __bfloat162float(__float2bfloat16(scale));
+    const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
+    for (int64_t index = int64_t(blockIdx.x) * QUANT_THREADS + threadIdx.x; index < vectors; index += stride) {
+        const uint4 packed = ld_nc_u4(input + index);
+        float v[8];
+        unpack_bf16x8(packed, v);
+        uint2 out;
+        out.x = encode_fp8x4<SPEC_C>(v[0], v[1], v[2], v[3], scale);
+        out.y = encode_fp8x4<SPEC_C>(v[4], v[5], v[6], v[7], scale);
+        output[index] = out;
+    }
+    if (blockIdx.x == 0 && int(threadIdx.x) < tail_count) {
+        const float value = __bfloat162float(tail_in[threadIdx.x]);
+        tail_out[threadIdx.x] = uint8_t(encode_fp8x4<SPEC_C>(value, 0.0f, 0.0f, 0.0f, scale) & 0xffu);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// NVFP4 encode.  Two adjacent threads own one 16-element block (8 elements, one
+// 16-byte load each); the pair's maximum crosses with a single shuffle.  Eight
+// adjacent threads therefore cover four blocks = one 4-byte word of the tiled
+// scale layout, which the first of them stores whole when the row width allows.
+
+template <bool SPEC_C>
+__global__ void __launch_bounds__(QUANT_THREADS)
+nvfp4_encode_kernel(const uint4* __restrict__ input, uint32_t* __restrict__ output, uint8_t* __restrict__ scales,
+                    uint8_t* __restrict__ blocked, const float* __restrict__ global_pointer, int rows, int columns,
+                    int flags) {
+    const int vectors_per_row = columns >> 3;
+    const int blocks_per_row = columns >> 4;
+    const int column_tiles = (blocks_per_row + 3) >> 2;
+    const int64_t total = int64_t(rows) * vectors_per_row;
+    const float global = __ldg(global_pointer);
+    const bool whole_words = (blocks_per_row & 3) == 0;
+    const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
+    // The loop condition is uniform per warp.  `total` is a multiple of 2 (a row holds whole
+    // blocks), so both threads of a pair are active together; the shuffle mask follows the
+    // active lanes.
+    const int lane = threadIdx.x & 31;
+    for (int64_t warp_base = int64_t(blockIdx.x) * QUANT_THREADS + (threadIdx.x - lane); warp_base < total;
+         warp_base += stride) {
+        const int64_t index = warp_base + lane;
+        const bool active = index < total;
+        const unsigned int mask = __ballot_sync(0xffffffffu, active);
+        if (!active) continue;
+        const uint4 packed = ld_nc_u4(input + index);
+        float v[8];
+        unpack_bf16x8(packed, v);
+        float maximum = abs_max_bf16x8(packed);
+        maximum = fmaxf(maximum, __shfl_xor_sync(mask, maximum, 1));
+        const uint8_t scale_code = nvfp4_block_scale<SPEC_C>(maximum, global, flags);
+        const float denominator = global * e4m3_to_float(scale_code);
+        output[index] = nvfp4_encode_x8<SPEC_C>(v, denominator);
+        const int row = int(index / vectors_per_row);
+        const int vector = int(index - int64_t(row) * vectors_per_row);
+        const int block = vector >> 1;
+        if (whole_words) {
+            // lanes 0,2,4,6 of each group of eight hold the four scale bytes of one word
+            const int base = (threadIdx.x & 31) & ~7;
+            unsigned int word = scale_code;
+            word |= (unsigned int)__shfl_sync(mask, (unsigned int)scale_code, base + 2) << 8;
+            word |= (unsigned int)__shfl_sync(mask, (unsigned int)scale_code, base + 4) << 16;
+            word |= (unsigned int)__shfl_sync(mask, (unsigned int)scale_code, base + 6) << 24;
+            if ((threadIdx.x & 7) == 0) {
+                if (blocked != nullptr)
+                    *reinterpret_cast<uint32_t*>(blocked + scale_tile_offset(row, block, column_tiles)) = word;
+                if (scales != nullptr)
+                    *reinterpret_cast<uint32_t*>(scales + int64_t(row) * blocks_per_row + block) = word;
+            }
+        } else if ((vector & 1) == 0) {
+            if (blocked != nullptr) blocked[scale_tile_offset(row, block, column_tiles)] = scale_code;
+            if (scales != nullptr) scales[int64_t(row) * blocks_per_row + block] = scale_code;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+
+static int grid_for(int64_t work_items, int per_block) {
+    const int64_t wanted = (work_items + per_block - 1) / per_block;
+    const int64_t cap = int64_t(sm_count()) * 8;
+    return int(wanted < 1 ? 1 : (wanted < cap ? wanted : cap));
+}
+
+int launch_tensor_scale(const void* input, int64_t count, float bound, int flags, void* scratch, void* scale,
+                        cudaStream_t stream) {
+    const int64_t vectors = count >> 3;
+    const int tail = int(count & 7);
+    const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(input);
+    tensor_scale_kernel<<<grid_for(vectors, QUANT_THREADS * 4), QUANT_THREADS, 0, stream>>>(
+        static_cast<const uint4*>(input), vectors, base + vectors * 8, tail, bound, flags,
+        static_cast<unsigned int*>(scratch), static_cast<float*>(scale));
+    return int(cudaGetLastError());
+}
+
+int launch_fp8_encode(const void* input, void* output, const void* scale, int64_t count, int flags,
+                      cudaStream_t stream) {
+    const int64_t vectors = count >> 3;
+    const int tail = int(count & 7);
+    const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(input);
+    uint8_t* out_base = static_cast<uint8_t*>(output);
+    const int grid = grid_for(vectors, QUANT_THREADS * 2);
+    if (flags & B2_SPEC_C)
+        fp8_encode_kernel<true><<<grid, QUANT_THREADS, 0, stream>>>(
+            static_cast<const uint4*>(input), static_cast<uint2*>(output), vectors, base + vectors * 8,
+            out_base + vectors * 8, tail, static_cast<const float*>(scale), flags);
+    else
+        fp8_encode_kernel<false><<<grid, QUANT_THREADS, 0, stream>>>(
+            static_cast<const uint4*>(input), static_cast<uint2*>(output), vectors, base + vectors * 8,
+            out_base + vectors * 8, tail, static_cast<const float*>(scale), flags);
+    return int(cudaGetLastError());
+}
+
+int launch_nvfp4_encode(const void* input, void* output, void* scales, void* blocked, const void* global, int rows,
+                        int columns, int flags, cudaStream_t stream) {
+    const int64_t total = int64_t(rows) * (columns >> 3);
+    const int grid = grid_for(total, QUANT_THREADS * 2);
+    if (flags & B2_SPEC_C)
+        nvfp4_encode_kernel<true><<<grid, QUANT_THREADS, 0, stream>>>(
+            static_cast<const uint4*>(input), static_cast<uint32_t*>(output), static_cast<uint8_t*>(scales),
+            static_cast<uint8_t*>(blocked), static_cast<const float*>(global), rows, columns, flags);
+    else
+        nvfp4_encode_kernel<false><<<grid, QUANT_THREADS, 0, stream>>>(
+            static_cast<const uint4*>(input), static_cast<uint32_t*>(output), static_cast<uint8_t*>(scales),
+            static_cast<uint8_t*>(blocked), static_cast<const float*>(global), rows, columns, flags);
+    return int(cudaGetLastError());
+}
+
+}  // namespace b2

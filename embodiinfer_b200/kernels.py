@@ -1,0 +1,191 @@
+"""Tensor-level wrappers over the C ABI: raw pointers, the caller's current stream, no allocation.
+
+These are the calls the plan objects (``embodiinfer_b200.backend``) and the registry kernels
+(``embodiinfer_b200.layers.linear``) are built from.  Every function launches on
+``torch.cuda.current_stream(device)`` like the reference's ctypes wrappers
+(embodiinfer/backend/cuda/quantization.py:139-166) and raises ``RuntimeError`` on a non-zero status.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _native as N
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _require_cuda(*tensors: torch.Tensor | None) -> torch.device:
+    device = None
+    for tensor in tensors:
+        if tensor is None:
+            continue
+        if not tensor.is_cuda:
+            raise ValueError("embodiinfer_b200 kernels require CUDA tensors; there is no CPU fallback")
+        if device is None:
+            device = tensor.device
+        elif tensor.device != device:
+            raise ValueError("all operands must live on one CUDA device")
+    if device is None:
+        raise ValueError("no tensor operands")
+    return device
+
+
+def new_scale_scratch(device: torch.device) -> torch.Tensor:
+    """Zeroed scratch for :func:`tensor_scale`; allocate once per plan, outside graph capture."""
+    return torch.zeros(N.SCALE_SCRATCH_BYTES // 4, device=device, dtype=torch.int32)
+
+
+def tensor_scale(x: torch.Tensor, bound: float, flags: int, scratch: torch.Tensor, scale: torch.Tensor) -> None:
+    """``scale <- amax(|x|) / bound`` (device fp32), see ``b2_tensor_scale``."""
+    device = _require_cuda(x, scratch, scale)
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("tensor_scale requires a contiguous bf16 tensor")
+    with torch.cuda.device(device):
+        status = N.load().b2_tensor_scale(
+            x.data_ptr(), x.numel(), float(bound), int(flags), scratch.data_ptr(), scale.data_ptr(), _stream(device)
+        )
+    N.check(status, "b2_tensor_scale")
+
+
+def fp8_quantize(x: torch.Tensor, out: torch.Tensor, scale: torch.Tensor, flags: int) -> None:
+    """bf16 -> e4m3 at ``*scale``, see ``b2_fp8_quantize``."""
+    device = _require_cuda(x, out, scale)
+    if x.dtype != torch.bfloat16 or not x.is_contiguous() or not out.is_contiguous() or out.numel() != x.numel():
+        raise ValueError("fp8_quantize requires contiguous bf16 input and a same-sized 1-byte output")
+    with torch.cuda.device(device):
+        status = N.load().b2_fp8_quantize(
+            x.data_ptr(), out.data_ptr(), scale.data_ptr(), x.numel(), int(flags), _stream(device)
+        )
+    N.check(status, "b2_fp8_quantize")
+
+
+def nvfp4_quantize(
+    x: torch.Tensor,
+    out: torch.Tensor,
+    scales: torch.Tensor | None,
+    blocked: torch.Tensor | None,
+    global_scale: torch.Tensor,
+    flags: int,
+) -> None:
+    """bf16 [R, K] -> packed e2m1 + e4m3 block scales, see ``b2_nvfp4_quantize``."""
+    device = _require_cuda(x, out, scales, blocked, global_scale)
+    if x.dtype != torch.bfloat16 or x.ndim != 2 or not x.is_contiguous():
+        raise ValueError("nvfp4_quantize requires a contiguous bf16 matrix")
+    rows, columns = x.shape
+    with torch.cuda.device(device):
+        status = N.load().b2_nvfp4_quantize(
+            x.data_ptr(),
+            out.data_ptr(),
+            _ptr(scales),
+            _ptr(blocked),
+            global_scale.data_ptr(),
+            rows,
+            columns,
+            int(flags),
+            _stream(device),
+        )
+    N.check(status, "b2_nvfp4_quantize")
+
+
+def geglu(
+    gate: torch.Tensor,
+    up: torch.Tensor | None,
+    out: torch.Tensor,
+    *,
+    bits: int,
+    table: torch.Tensor,
+    rows: int,
+    columns: int,
+    row_stride: int,
+    scale: torch.Tensor | None = None,
+    scales: torch.Tensor | None = None,
+    blocked: torch.Tensor | None = None,
+    flags: int = 0,
+) -> None:
+    """GELU(gate) * up with the reference's two bf16 roundings, see ``b2_geglu``."""
+    device = _require_cuda(gate, up, out, table, scale, scales, blocked)
+    with torch.cuda.device(device):
+        status = N.load().b2_geglu(
+            gate.data_ptr(),
+            _ptr(up),
+            out.data_ptr(),
+            _ptr(scales),
+            _ptr(blocked),
+            _ptr(scale),
+            rows,
+            columns,
+            row_stride,
+            bits,
+            table.data_ptr(),
+            int(flags),
+            _stream(device),
+        )
+    N.check(status, "b2_geglu")
+
+
+def linear(
+    *,
+    kind: int,
+    epilogue: int,
+    out_format: int,
+    tokens: int,
+    features: int,
+    width: int,
+    act: torch.Tensor,
+    act_scale: torch.Tensor,
+    weight: torch.Tensor,
+    weight_scale: torch.Tensor,
+    out: torch.Tensor,
+    act_scales: torch.Tensor | None = None,
+    weight_scales: torch.Tensor | None = None,
+    bias: torch.Tensor | None = None,
+    residual: torch.Tensor | None = None,
+    gelu_table: torch.Tensor | None = None,
+    out_scale: torch.Tensor | None = None,
+    out_scales: torch.Tensor | None = None,
+    out_blocked: torch.Tensor | None = None,
+    status: torch.Tensor | None = None,
+    flags: int = 0,
+    feature_tile: int = 0,
+) -> None:
+    """One fused tensor-core launch, see ``b2_linear``."""
+    device = _require_cuda(
+        act, act_scale, weight, weight_scale, out, act_scales, weight_scales, bias, residual, gelu_table, out_scale,
+        out_scales, out_blocked, status,
+    )
+    desc = N.LinearDesc(
+        kind=kind,
+        epilogue=epilogue,
+        out_format=out_format,
+        flags=flags,
+        tokens=tokens,
+        features=features,
+        width=width,
+        feature_tile=feature_tile,
+        act=act.data_ptr(),
+        act_scales=_ptr(act_scales),
+        act_scale=act_scale.data_ptr(),
+        weight=weight.data_ptr(),
+        weight_scales=_ptr(weight_scales),
+        weight_scale=weight_scale.data_ptr(),
+        bias=_ptr(bias),
+        residual=_ptr(residual),
+        gelu_table=_ptr(gelu_table),
+        out_scale=_ptr(out_scale),
+        out=out.data_ptr(),
+        out_scales=_ptr(out_scales),
+        out_blocked=_ptr(out_blocked),
+        status=_ptr(status),
+    )
+    with torch.cuda.device(device):
+        code = N.load().b2_linear(ctypes.byref(desc), _stream(device))
+    N.check(code, "b2_linear")

@@ -1,0 +1,135 @@
+/* C ABI of libembodiinfer_b200.so: the quantised-Linear hot path for NVIDIA B200 (sm_100a).
+ *
+ * Conventions (the same ones the reference's ctypes wrappers rely on,
+ * embodiinfer/backend/cuda/quantization.py:33-66, embodiinfer/backend/cuda/native.py:119):
+ *   - every pointer is a raw device pointer unless stated otherwise; `stream` is a cudaStream_t;
+ *   - nothing is allocated, freed or synchronised: outputs and workspaces belong to the caller,
+ *     so every entry point may be recorded into a CUDA graph after one warm-up call;
+ *   - the return value is 0 on success, a negative B2_E_* code for a rejected argument, or a
+ *     positive cudaError_t value reported by the launch;
+ *   - scalars that must stay mutable under graph replay (scales) are read from device memory.
+ *
+ * Matrices are row-major.  bf16 is the 16-bit brain float, e4m3 the FP8 "fn" variant (max 448),
+ * packed e2m1 holds two 4-bit codes per byte with the even column in the low nibble.
+ */
+#ifndef EMBODIINFER_B200_H
+#define EMBODIINFER_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_ABI_VERSION 1
+
+/* ---- status codes ---------------------------------------------------------- */
+#define B2_OK 0
+#define B2_E_INVALID (-1)     /* null pointer, non-positive size, misaligned pointer */
+#define B2_E_UNSUPPORTED (-2) /* shape outside what the kernel implements */
+#define B2_E_DRIVER (-3)      /* tensor-map creation or driver entry point lookup failed */
+#define B2_E_TOO_LARGE (-4)   /* size beyond a documented maximum */
+
+/* ---- quantiser arithmetic flags ----------------------------------------------
+ * The reference has two bit-exact quantiser arithmetics; both are implemented.
+ *   spec T: the torch route   (backend/torch/fp8.py:66-73, backend/torch/nvfp4.py:28-46)
+ *   spec C: the CUDA route    (backend/cuda/csrc/quantize.cu:38-104)
+ */
+#define B2_SPEC_T 0
+#define B2_SPEC_C 1        /* fp32 quotient, hardware round-to-nearest-even e2m1, zero block -> code 0 */
+#define B2_SCALAR_RCP 2    /* tensor / python-scalar evaluated as tensor * fp32(1/scalar), as ATen does on CUDA
+                              and quantize.cu:54 does; without it a true division, as ATen does on CPU */
+#define B2_DIVISOR_BF16 4  /* spec T FP8 only: round the scale to bf16 before dividing */
+#define B2_CLAMP_TINY 8    /* scale = max(amax, FLT_MIN)/bound (nvfp4.py:38) instead of "1.0 when amax == 0" */
+#define B2_GEGLU_TRUE_DIV 16 /* FP8 GELU*up epilogue divides by the scale (fusion.cu:21) instead of
+                                multiplying by 1/scale (fusion.cu:87-92, the path every real shape takes) */
+
+int b2_abi_version(void);
+
+/* Number of bytes of zero-initialised device scratch b2_tensor_scale needs (it leaves them zero). */
+#define B2_SCALE_SCRATCH_BYTES 8
+
+/* Tensor amax -> scale = amax / bound, written to `scale` (device fp32).
+ * Replaces cc_scale (backend/cuda/csrc/quantize.cu:116-125) and the amax lines of
+ * fp8.py:70-71 / nvfp4.py:38.  `input` is bf16[count], 16-byte aligned.  `scratch` is
+ * B2_SCALE_SCRATCH_BYTES of device memory that is zero before the first call; the kernel
+ * restores it to zero, so calls on one stream may share it.  flags: B2_SCALAR_RCP, B2_CLAMP_TINY. */
+int b2_tensor_scale(const void* input, int64_t count, float bound, int flags, void* scratch, void* scale,
+                    void* stream);
+
+/* bf16[count] -> e4m3[count] with the per-tensor scale read from device memory.
+ * Replaces cc_fp8 (quantize.cu:127-133); spec T reproduces fp8.py:72.  flags: B2_SPEC_*, B2_DIVISOR_BF16. */
+int b2_fp8_quantize(const void* input, void* output, const void* scale, int64_t count, int flags, void* stream);
+
+/* bf16[rows, columns] -> packed e2m1 [rows, columns/2], e4m3 block scales in row-major order
+ * (`scales`, [rows, columns/16], may be NULL) and in the 128x4-tile order the tensor core reads
+ * (`blocked`, ceil(rows/128)*128 * ceil(columns/64)*4 bytes whose padding the caller zeroed once; may be
+ * NULL).  `global` is the device fp32 global scale.  columns % 16 == 0.
+ * Replaces cc_fp4 (quantize.cu:135-142) and nvfp4.quantize_weight + blocked_scales (nvfp4.py:14-46). */
+int b2_nvfp4_quantize(const void* input, void* output, void* scales, void* blocked, const void* global, int rows,
+                      int columns, int flags, void* stream);
+
+/* h = bf16(bf16(gelu(gate)) * up) with GELU read from `table` (uint16[65536], indexed by the bf16 bit
+ * pattern of gate), then stored as bf16 (bits 16), e4m3 (bits 8) or NVFP4 (bits 4).
+ * gate/up are bf16 [rows, columns] with row stride `row_stride` elements (row_stride == columns for two
+ * separate matrices; 2*columns with up == gate + columns for one packed [rows, 2*columns] matrix).
+ * Replaces cc_geglu, cc_geglu_fp4, cc_geglu_packed and cc_geglu_bf16_strided
+ * (backend/cuda/csrc/fusion.cu:109-200).  `scale` is the device fp32 calibrated scale (unused for 16 bits);
+ * `scales`/`blocked` as in b2_nvfp4_quantize (4 bits only).  flags: B2_GEGLU_TRUE_DIV. */
+int b2_geglu(const void* gate, const void* up, void* output, void* scales, void* blocked, const void* scale,
+             int rows, int columns, int64_t row_stride, int bits, const void* table, int flags, void* stream);
+
+/* ---- the tensor-core Linear ------------------------------------------------- */
+
+#define B2_KIND_FP8 0   /* e4m3 x e4m3, per-tensor fp32 scales            (fp8.py:118-141, projection.py:155-163) */
+#define B2_KIND_NVFP4 1 /* e2m1 x e2m1, ue4m3 scale per 16, fp32 globals  (nvfp4.py:96-123, projection.py:224-234) */
+
+#define B2_EPI_LINEAR 0 /* out = act * weight^T (+bias)(+residual) */
+#define B2_EPI_GEGLU 1  /* weight holds [gate; up] (2*features rows): out = GELU(act*gate^T) * (act*up^T) */
+
+#define B2_OUT_BF16 0
+#define B2_OUT_FP8 1    /* GEGLU only: e4m3 at *out_scale                   (fusion.cu:64-107) */
+#define B2_OUT_NVFP4 2  /* GEGLU only: packed e2m1 + block scales at *out_scale (fusion.cu:31-62) */
+
+#define B2_LINEAR_ROUND_SCALE_BF16 1 /* NVFP4 registry route: y = bf16(bf16(acc) * bf16(g_a*g_w))
+                                        (nvfp4.py:120, quantize.cu:106-114) instead of bf16(acc*g_a*g_w) */
+
+typedef struct b2_linear_desc {
+    int32_t kind;        /* B2_KIND_* */
+    int32_t epilogue;    /* B2_EPI_* */
+    int32_t out_format;  /* B2_OUT_* */
+    int32_t flags;       /* B2_LINEAR_* | B2_GEGLU_TRUE_DIV */
+    int32_t tokens;      /* M: rows of the activation matrix */
+    int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
+    int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */
+    int32_t feature_tile; /* output features per tile: 0 = choose; LINEAR 64/128/192/256, GEGLU 64/128 */
+    const void* act;           /* e4m3 [M, K] or packed e2m1 [M, K/2] */
+    const void* act_scales;    /* NVFP4: block scales of act in 128x4-tile order */
+    const void* act_scale;     /* device fp32: per-tensor scale (FP8) or global scale (NVFP4) */
+    const void* weight;        /* e4m3 [rows, K] or packed e2m1 [rows, K/2] */
+    const void* weight_scales; /* NVFP4: block scales of weight in 128x4-tile order */
+    const void* weight_scale;  /* device fp32 */
+    const void* bias;          /* bf16 [N] or NULL (LINEAR only) */
+    const void* residual;      /* bf16 [M, N] or NULL (LINEAR only): out = bf16(y + residual) */
+    const void* gelu_table;    /* uint16[65536] (GEGLU only) */
+    const void* out_scale;     /* device fp32 the epilogue quantises at (B2_OUT_FP8 / B2_OUT_NVFP4) */
+    void* out;                 /* bf16 [M, N] | e4m3 [M, N] | packed e2m1 [M, N/2] */
+    void* out_scales;          /* B2_OUT_NVFP4: row-major block scales [M, N/16] or NULL */
+    void* out_blocked;         /* B2_OUT_NVFP4: block scales in 128x4-tile order (padding zeroed by caller) */
+    void* status;              /* device uint32 or NULL: set nonzero if a bounded device-side wait expired */
+} b2_linear_desc;
+
+/* One launch: TMA-staged operands, tcgen05 MMA into TMEM, fused epilogue.
+ * LINEAR needs N % 8 == 0; GEGLU needs N % 16 == 0 (N % 128 == 0 for NVFP4 operands).
+ * bias, residual and out must be 16-byte aligned.
+ * Replaces the library GEMM + separate elementwise launches behind fp8.native_linear (fp8.py:118-141),
+ * nvfp4._native_linear (nvfp4.py:96-123), Projection.apply (projection.py:108-235) and, for GEGLU,
+ * the two GEMMs + cc_geglu/cc_geglu_fp4 of MlpPlan (policies/pi05/inference/mlp.py:481-501).
+ * `desc` is host memory and is read before the call returns. */
+int b2_linear(const b2_linear_desc* desc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* EMBODIINFER_B200_H */
