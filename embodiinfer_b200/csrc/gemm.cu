@@ -330,6 +330,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         // ------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             const uint32_t idesc = KIND == B2_KIND_NVFP4 ? idesc_nvf4(TILE_TOKENS, BN) : idesc_f8(TILE_TOKENS, BN);
+            const uint32_t idesc_half = idesc_nvf4(TILE_TOKENS, 64);
             int stage = 0;
             uint32_t phase = 0;
             int local_tile = 0;
@@ -372,17 +373,12 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                                 tc_copy_32x128b_x4(region + 4, second);
                                 sfb_column[j] = region;
                             } else {
-                                // 64 gate + 64 up features: two columns of each block must end up adjacent at
-                                // region+2 .. region+5.  The copies move whole 4-column blocks, so the one whose
-                                // unwanted half would cover the other's wanted half goes first.
-                                if (scale_offset == 0) {
-                                    tc_copy_32x128b_x4(region + 2, first);       // gate columns 0,1 -> +2,+3
-                                    tc_copy_32x128b_x4(region + 4, second);      // up columns 0,1   -> +4,+5
-                                } else {
-                                    tc_copy_32x128b_x4(region + 2, second);      // up columns 2,3   -> +4,+5
-                                    tc_copy_32x128b_x4(region, first);           // gate columns 2,3 -> +2,+3
-                                }
-                                sfb_column[j] = region + 2;
+                                // 64 gate + 64 up features sit in the same two columns of two different
+                                // blocks, and a copy can only land on a multiple of four columns: keep the
+                                // blocks apart and issue one MMA per half, each with its own scale column.
+                                tc_copy_32x128b_x4(region, first);
+                                tc_copy_32x128b_x4(region + 4, second);
+                                sfb_column[j] = region + scale_offset;
                             }
                         }
                     }
@@ -392,7 +388,12 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         const uint64_t a_desc = smem_desc_sw128(a_smem + j * 32);
                         const uint64_t b_desc = smem_desc_sw128(b_smem + j * 32);
                         const uint32_t accumulate = (kb | j) != 0;
-                        if (KIND == B2_KIND_NVFP4)
+                        if (KIND == B2_KIND_NVFP4 && GEGLU && BN == 128) {
+                            // gate half -> columns [0, 64), up half -> columns [64, 128)
+                            mma_nvf4(d_tmem, a_desc, b_desc, idesc_half, tmem_base + TMEM_SFA + j * 4, sfb_column[j], accumulate);
+                            mma_nvf4(d_tmem + 64, a_desc, smem_desc_sw128(b_smem + 64 * STAGE_K_BYTES + j * 32), idesc_half,
+                                     tmem_base + TMEM_SFA + j * 4, sfb_column[j] + 4, accumulate);
+                        } else if (KIND == B2_KIND_NVFP4)
                             mma_nvf4(d_tmem, a_desc, b_desc, idesc, tmem_base + TMEM_SFA + j * 4, sfb_column[j], accumulate);
                         else
                             mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, accumulate);
