@@ -48,6 +48,7 @@ class LinearDesc(ctypes.Structure):
         ("weight", ctypes.c_void_p),
         ("weight_scales", ctypes.c_void_p),
         ("weight_scale", ctypes.c_void_p),
+        ("weight_scale_up", ctypes.c_void_p),
         ("bias", ctypes.c_void_p),
         ("residual", ctypes.c_void_p),
         ("gelu_table", ctypes.c_void_p),

@@ -1,0 +1,83 @@
+"""Gated MLP as three launches: encode(x), [gate;up] GEMM + GELU + re-encode, down GEMM.
+
+Replaces the chain of ``MlpPlan._project`` (embodiinfer/policies/pi05/inference/mlp.py:481-501):
+encode once, ``gate.apply`` + ``up.apply`` (two library GEMMs writing bf16), ``fusion.encode``
+(re-reads both), ``down.apply``.  Here gate and up are one fused tensor-core launch whose epilogue
+emits the down projection's encoded input directly, so the [M, F] bf16 intermediates never reach HBM.
+Arithmetic (rounding points, encoders, scales) is that of the separate steps.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Callable
+from typing import Literal
+
+import torch
+
+from ..layers.plans import ActivationQuantizer, EncodedActivation, Precision, WorkspaceKey
+from .activation import gelu_table
+from .projection import B200Projection
+
+_BITS = {"bf16": 16, "fp8": 8, "nvfp4": 4}
+
+
+class FusedMlpPlan:
+    """``down(gelu(gate(x)) * up(x))`` with calibrated activation ranges.
+
+    ``gate_up_max`` / ``down_max`` are the calibrated absolute maxima of the MLP input and of the
+    hidden activation (the reference's per-layer ``gate_up_max`` / ``down_max``); they fix the
+    activation scales, so every launch is graph-capturable.
+    """
+
+    def __init__(
+        self,
+        gate_weight: torch.Tensor,
+        up_weight: torch.Tensor,
+        down_weight: torch.Tensor,
+        *,
+        gate_up_max: float,
+        down_max: float,
+        gate_up: Precision,
+        down: Precision,
+        quantizer: ActivationQuantizer,
+        approximate: Literal["none", "tanh"] = "tanh",
+        workspace_key: Callable[[torch.device], WorkspaceKey] | None = None,
+        table: torch.Tensor | None = None,
+    ) -> None:
+        if gate_up == "bf16":
+            raise ValueError("the fused MLP needs fp8 or nvfp4 gate/up projections")
+        if gate_weight.shape != up_weight.shape or down_weight.shape != tuple(reversed(gate_weight.shape)):
+            raise ValueError("Optimized MLP projection dimensions do not match")
+        self.inter_size, self.hidden_size = gate_weight.shape
+        self.gate_up = B200Projection.gated_pair(gate_weight, up_weight, gate_up_max, gate_up, quantizer, workspace_key)
+        self.down = B200Projection(down_weight, down_max, down, quantizer if down != "bf16" else None, workspace_key)
+        self.table = gelu_table(gate_weight.device, approximate) if table is None else table
+        self.approximate = approximate
+
+    def encode(self, inputs: torch.Tensor) -> EncodedActivation:
+        return self.gate_up.encode(inputs)
+
+    def project(self, inputs: torch.Tensor, encoded: EncodedActivation, *, residual: torch.Tensor | None = None):
+        """``encoded`` is ``inputs`` at the gate/up scale (shared by both halves, mlp.py:222)."""
+        bits = _BITS[self.down.precision]
+        scale = None if bits == 16 else self.down.maximum / (448 * (6 if bits == 4 else 1))
+        hidden = self.gate_up.apply_gated(inputs, encoded, table=self.table, bits=bits, scale=scale)
+        shape = (*inputs.shape[:-1], self.inter_size)
+        if bits == 16:
+            return self.down.apply(hidden.output.reshape(shape), None)
+        # The encoded hidden activation is complete; `apply` only reads shape/dtype/device of its first argument.
+        return self.down.apply(_ShapeOnly(shape, inputs), hidden, residual=residual)
+
+    def __call__(self, inputs: torch.Tensor, *, residual: torch.Tensor | None = None) -> torch.Tensor:
+        return self.project(inputs, self.encode(inputs), residual=residual)
+
+    def release_scope(self, scope: WorkspaceKey) -> None:
+        self.gate_up.release_scope(scope)
+        self.down.release_scope(scope)
+
+
+class _ShapeOnly:
+    """Stands in for the bf16 hidden activation that the fused epilogue never materialises."""
+
+    def __init__(self, shape: tuple[int, ...], like: torch.Tensor) -> None:
+        self.shape, self.device, self.dtype = torch.Size(shape), like.device, like.dtype

@@ -64,6 +64,7 @@ struct KernelArgs {
     const uint8_t* weight_scales;
     const float* act_scale;
     const float* weight_scale;
+    const float* weight_scale_up;   // GEGLU: scale of the up rows (nullptr = same as the gate rows)
     const __nv_bfloat16* bias;
     const __nv_bfloat16* residual;
     const uint16_t* gelu_table;
@@ -138,14 +139,14 @@ __device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32],
 // h = bf16(bf16(gelu(gate)) * up), stored as bf16, e4m3 or NVFP4 (fusion.cu:5-10, 31-107).
 template <int EPI>
 __device__ __forceinline__ void epilogue_geglu_chunk(const uint32_t (&gate_acc)[32], const uint32_t (&up_acc)[32],
-                                                     const KernelArgs& args, float scale, bool round_scale,
-                                                     float out_scale, float out_scale_rcp, bool true_div, int token,
+                                                     const KernelArgs& args, float scale, float scale_up,
+                                                     bool round_scale, float out_scale, float out_scale_rcp, bool true_div, int token,
                                                      int feature0) {
     float h[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
         const float gate = gemm_value(gate_acc[i], scale, round_scale);
-        const float up = gemm_value(up_acc[i], scale, round_scale);
+        const float up = gemm_value(up_acc[i], scale_up, round_scale);
         const float gelu = bf16_lo(uint32_t(__ldg(args.gelu_table + (__float_as_uint(gate) >> 16))));
         h[i] = round_to_bf16(__fmul_rn(gelu, up));
     }
@@ -411,6 +412,11 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         const bool round_scale = (args.flags & B2_LINEAR_ROUND_SCALE_BF16) != 0;
         float scale = __fmul_rn(__ldg(args.act_scale), __ldg(args.weight_scale));
         if (round_scale) scale = round_to_bf16(scale);
+        float scale_up = scale;
+        if (GEGLU && args.weight_scale_up != nullptr) {
+            scale_up = __fmul_rn(__ldg(args.act_scale), __ldg(args.weight_scale_up));
+            if (round_scale) scale_up = round_to_bf16(scale_up);
+        }
         float out_scale = 1.0f, out_scale_rcp = 1.0f;
         if (EPI == EPI_GEGLU_FP8 || EPI == EPI_GEGLU_NVFP4) {
             out_scale = __ldg(args.out_scale);
@@ -438,7 +444,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     uint32_t second[32];
                     tmem_load_32x32(lane_address + BN / 2 + chunk * 32, second);
                     tmem_load_wait();
-                    epilogue_geglu_chunk<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, scale, round_scale, out_scale,
+                    epilogue_geglu_chunk<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, scale, scale_up, round_scale, out_scale,
                                                                       out_scale_rcp, true_div, token, f0 + chunk * 32);
                 } else {
                     tmem_load_wait();
@@ -609,6 +615,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
     args.weight_scales = static_cast<const uint8_t*>(d->weight_scales);
     args.act_scale = static_cast<const float*>(d->act_scale);
     args.weight_scale = static_cast<const float*>(d->weight_scale);
+    args.weight_scale_up = geglu ? static_cast<const float*>(d->weight_scale_up) : nullptr;
     args.bias = static_cast<const __nv_bfloat16*>(d->bias);
     args.residual = static_cast<const __nv_bfloat16*>(d->residual);
     args.gelu_table = static_cast<const uint16_t*>(d->gelu_table);

@@ -147,6 +147,7 @@ def linear(
     out: torch.Tensor,
     act_scales: torch.Tensor | None = None,
     weight_scales: torch.Tensor | None = None,
+    weight_scale_up: torch.Tensor | None = None,
     bias: torch.Tensor | None = None,
     residual: torch.Tensor | None = None,
     gelu_table: torch.Tensor | None = None,
@@ -159,7 +160,7 @@ def linear(
 ) -> None:
     """One fused tensor-core launch, see ``b2_linear``."""
     device = _require_cuda(
-        act, act_scale, weight, weight_scale, out, act_scales, weight_scales, bias, residual, gelu_table, out_scale,
+        act, act_scale, weight, weight_scale, out, act_scales, weight_scales, weight_scale_up, bias, residual, gelu_table, out_scale,
         out_scales, out_blocked, status,
     )
     desc = N.LinearDesc(
@@ -177,6 +178,7 @@ def linear(
         weight=weight.data_ptr(),
         weight_scales=_ptr(weight_scales),
         weight_scale=weight_scale.data_ptr(),
+        weight_scale_up=_ptr(weight_scale_up),
         bias=_ptr(bias),
         residual=_ptr(residual),
         gelu_table=_ptr(gelu_table),

@@ -109,6 +109,8 @@ typedef struct b2_linear_desc {
     const void* weight;        /* e4m3 [rows, K] or packed e2m1 [rows, K/2] */
     const void* weight_scales; /* NVFP4: block scales of weight in 128x4-tile order */
     const void* weight_scale;  /* device fp32 */
+    const void* weight_scale_up; /* GEGLU: device fp32 scale of the up rows when gate and up were quantised
+                                    separately; NULL = weight_scale covers both */
     const void* bias;          /* bf16 [N] or NULL (LINEAR only) */
     const void* residual;      /* bf16 [M, N] or NULL (LINEAR only): out = bf16(y + residual) */
     const void* gelu_table;    /* uint16[65536] (GEGLU only) */

@@ -1,0 +1,74 @@
+"""The C-ABI shared object: loads, exports every symbol the header declares, rejects bad
+arguments with its documented codes.  No kernel is launched here."""
+
+from __future__ import annotations
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from embodiinfer_b200 import _native as N
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "embodiinfer_b200.h"
+
+
+def declared_functions() -> list[str]:
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return re.findall(r"^\s*int\s+(b2_\w+)\s*\(", text, flags=re.M)
+
+
+def test_library_exports_every_declared_symbol():
+    library = N.load()
+    names = declared_functions()
+    assert {"b2_abi_version", "b2_tensor_scale", "b2_fp8_quantize", "b2_nvfp4_quantize", "b2_geglu", "b2_linear"} <= set(names)
+    for name in names:
+        assert hasattr(library, name), f"{name} is declared in the header but not exported"
+        assert name in N.SIGNATURES, f"{name} has no ctypes signature"
+    assert library.b2_abi_version() == N.ABI_VERSION
+
+
+def test_header_constants_match_python_mirror():
+    text = HEADER.read_text()
+    values = {m.group(1): int(m.group(2), 0) for m in re.finditer(r"#define\s+(B2_\w+)\s+\(?(-?\w+)\)?\s", text) if re.fullmatch(r"-?(0x)?[0-9a-fA-F]+", m.group(2))}
+    for name in ("SPEC_T", "SPEC_C", "SCALAR_RCP", "DIVISOR_BF16", "CLAMP_TINY", "GEGLU_TRUE_DIV", "KIND_FP8", "KIND_NVFP4",
+                 "EPI_LINEAR", "EPI_GEGLU", "OUT_BF16", "OUT_FP8", "OUT_NVFP4", "LINEAR_ROUND_SCALE_BF16",
+                 "SCALE_SCRATCH_BYTES", "ABI_VERSION", "E_INVALID", "E_UNSUPPORTED", "E_DRIVER", "E_TOO_LARGE"):
+        assert values[f"B2_{name}"] == getattr(N, name), name
+
+
+def test_linear_desc_layout_matches_header():
+    text = HEADER.read_text()
+    body = re.search(r"typedef struct b2_linear_desc \{(.*?)\} b2_linear_desc;", text, flags=re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = re.findall(r"(?:const\s+)?(?:int32_t|void\*)\s+(\w+);", body)
+    assert fields == [name for name, _ in N.LinearDesc._fields_]
+
+
+def test_argument_rejection_without_a_gpu():
+    library = N.load()
+    assert library.b2_fp8_quantize(None, None, None, 0, 0, None) == N.E_INVALID
+    assert library.b2_tensor_scale(None, 16, 448.0, 0, None, None, None) == N.E_INVALID
+    assert library.b2_nvfp4_quantize(None, None, None, None, None, 4, 64, 0, None) == N.E_INVALID
+    assert library.b2_geglu(None, None, None, None, None, None, 4, 64, 64, 8, None, 0, None) == N.E_INVALID
+    assert library.b2_linear(None, None) == N.E_INVALID
+    fake = ctypes.c_void_p(4096)   # aligned, never dereferenced: checks happen before any launch
+    assert library.b2_nvfp4_quantize(fake, fake, None, None, fake, 4, 24, 0, None) == N.E_UNSUPPORTED
+    assert library.b2_geglu(fake, fake, fake, None, None, fake, 4, 64, 32, 8, fake, 0, None) == N.E_INVALID
+    assert library.b2_geglu(fake, fake, fake, None, None, fake, 4, 64, 64, 5, fake, 0, None) == N.E_UNSUPPORTED
+    desc = N.LinearDesc(kind=7, tokens=1, features=8, width=16)
+    assert library.b2_linear(ctypes.byref(desc), None) == N.E_UNSUPPORTED
+    desc = N.LinearDesc(kind=N.KIND_FP8, tokens=4, features=8, width=24, act=4096, weight=4096, act_scale=4096,
+                        weight_scale=4096, out=4096)
+    assert library.b2_linear(ctypes.byref(desc), None) == N.E_UNSUPPORTED      # K % 16
+    desc.width, desc.act = 32, 4100
+    assert library.b2_linear(ctypes.byref(desc), None) == N.E_INVALID          # misaligned operand
+
+
+def test_check_raises_like_the_reference_wrappers():
+    N.check(0, "x")
+    with pytest.raises(RuntimeError, match="failed with error -2"):
+        N.check(-2, "b2_linear")
+    with pytest.raises(RuntimeError, match="failed with error 700"):
+        N.check(700, "b2_linear")

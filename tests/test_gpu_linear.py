@@ -1,0 +1,193 @@
+"""The fused tensor-core Linear through the C ABI against the oracle on identical quantised operands.
+
+Tolerance: relative Frobenius <= 1e-3 and max-abs <= 2e-2 in bf16 (tests/util.py explains the one-ulp
+allowance for large magnitudes).  Encoded outputs of the fused epilogues (e4m3 / e2m1 codes and block
+scales) are compared bit for bit against the stand-alone epilogue run on the kernel's own bf16 gate/up.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from embodiinfer_b200 import _native as N
+from embodiinfer_b200 import kernels as K
+from embodiinfer_b200.backend.quantization import blocked_scale_bytes
+from oracle import quant_oracle as O
+from tests.util import assert_gemm_close, bits, gelu_table_cpu, make_input, make_weight, u8
+
+pytestmark = pytest.mark.gpu
+
+
+def operands(kind, tokens, rows, width, seed, device):
+    x = bits(make_input((tokens, width), seed))
+    w = bits(make_weight((rows, width), seed).to(torch.bfloat16))
+    if kind == "fp8":
+        aq, a_s = O.fp8_quantize_C(x)
+        wq, w_s = O.fp8_quantize_C(w)
+        host = dict(a=aq, a_s=a_s, w=wq, w_s=w_s)
+        dev = dict(kind=N.KIND_FP8, act=torch.from_numpy(aq).to(device), weight=torch.from_numpy(wq).to(device))
+    else:
+        ap, asl, abl, a_s = O.nvfp4_quantize_C(x)
+        wp, wsl, wbl, w_s = O.nvfp4_quantize_C(w)
+        host = dict(a=ap, a_sl=asl, a_s=a_s, w=wp, w_sl=wsl, w_s=w_s)
+        dev = dict(kind=N.KIND_NVFP4, act=torch.from_numpy(ap).to(device), weight=torch.from_numpy(wp).to(device),
+                   act_scales=torch.from_numpy(abl).to(device), weight_scales=torch.from_numpy(wbl).to(device))
+    dev["act_scale"] = torch.tensor(float(host["a_s"]), device=device)
+    dev["weight_scale"] = torch.tensor(float(host["w_s"]), device=device)
+    return host, dev
+
+
+def accumulate(kind, host):
+    if kind == "fp8":
+        return O.e4m3_decode(host["a"]).astype(np.float64) @ O.e4m3_decode(host["w"]).astype(np.float64).T
+    return O.nvfp4_block_acc(host["a"], host["a_sl"], host["w"], host["w_sl"])
+
+
+LINEAR_CASES = [
+    # tokens, features, width, tile
+    (32, 128, 128, 64), (200, 256, 1024, 64), (10, 2560, 1024, 0), (80, 1024, 2048, 0), (640, 4096, 1024, 0),
+    (560, 2048, 2048, 0), (560, 2048, 2048, 64), (560, 2048, 2048, 128), (560, 2048, 2048, 192), (560, 2048, 2048, 256),
+    (1, 64, 64, 0), (17, 72, 192, 0), (129, 200, 320, 0), (559, 1152, 1152, 0), (561, 1024, 2048, 0),
+]
+
+
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+@pytest.mark.parametrize("tokens,features,width,tile", LINEAR_CASES)
+def test_linear_matches_oracle(device, kind, tokens, features, width, tile):
+    host, dev = operands(kind, tokens, features, width, tokens + features, device)
+    status = torch.zeros(1, device=device, dtype=torch.int32)
+    out = torch.full((tokens + 1, features), float("nan"), device=device, dtype=torch.bfloat16)
+    K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out[:tokens],
+             status=status, feature_tile=tile, **dev)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert torch.isnan(out[tokens]).all(), "wrote past the last token row"
+    if kind == "fp8":
+        want = O.fp8_linear(host["a"], host["a_s"], host["w"], host["w_s"])
+    else:
+        want = O.nvfp4_linear_plan(host["a"], host["a_sl"], host["a_s"], host["w"], host["w_sl"], host["w_s"])
+    assert_gemm_close(bits(out[:tokens]), want)
+
+
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+def test_siglip_shapes_with_bias(device, kind):
+    """K = 4304 is not a multiple of 128 (ragged last K slice); N = 4304 is not a multiple of any tile."""
+    for tokens, features, width in ((512, 1152, 4304 if kind == "fp8" else 4288), (512, 4304, 1152), (256, 3456, 1152)):
+        host, dev = operands(kind, tokens, features, width, 7 + features, device)
+        bias = make_weight((1, features), 9, std=0.1).to(torch.bfloat16).reshape(-1)
+        out = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+        K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out,
+                 bias=bias.to(device), **dev)
+        if kind == "fp8":
+            want = O.fp8_linear(host["a"], host["a_s"], host["w"], host["w_s"], bits(bias))
+        else:
+            want = O.nvfp4_linear_plan(host["a"], host["a_sl"], host["a_s"], host["w"], host["w_sl"], host["w_s"])
+            want = O.f32_to_bf16(O.bf16_to_f32(want) + O.bf16_to_f32(bits(bias))[None, :])
+        assert_gemm_close(bits(out), want)
+
+
+def test_registry_rounding_bias_and_residual(device):
+    """NVFP4 registry route: bf16(bf16(acc) * bf16(g_a*g_w)), then bias and residual as separate bf16 adds."""
+    tokens, features, width = 80, 1024, 2048
+    host, dev = operands("nvfp4", tokens, features, width, 5, device)
+    bias = make_weight((1, features), 3, std=0.1).to(torch.bfloat16).reshape(-1)
+    residual = make_input((tokens, features), 4, outliers=False)
+    out = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+    K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out,
+             bias=bias.to(device), residual=residual.to(device), flags=N.LINEAR_ROUND_SCALE_BF16, **dev)
+    want = O.nvfp4_linear_registry(host["a"], host["a_sl"], host["a_s"], host["w"], host["w_sl"], host["w_s"], bits(bias))
+    want = O.f32_to_bf16(O.bf16_to_f32(want) + O.bf16_to_f32(bits(residual)))
+    assert_gemm_close(bits(out), want)
+
+
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+@pytest.mark.parametrize("tokens,features,width,tile", [(64, 256, 512, 64), (200, 256, 512, 128), (560, 2048, 2048, 0), (130, 384, 1024, 0)])
+def test_gated_epilogues(device, kind, tokens, features, width, tile):
+    host, dev = operands(kind, tokens, 2 * features, width, 21 + tokens, device)
+    table_host = gelu_table_cpu("tanh")
+    table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+    common = dict(epilogue=N.EPI_GEGLU, tokens=tokens, features=features, width=width, gelu_table=table, feature_tile=tile, **dev)
+    # bf16 hidden against the oracle (two GEMM outputs, GELU table, product rounding)
+    hidden = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+    K.linear(out_format=N.OUT_BF16, out=hidden, **common)
+    y = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+    want_hidden = O.gelu_mul(y[:, :features], y[:, features:], table_host)
+    assert_gemm_close(bits(hidden), want_hidden)
+    got_hidden = bits(hidden)
+    peak = float(np.abs(O.bf16_to_f32(got_hidden)).max())
+    # e4m3 output: identical to encoding the kernel's own bf16 hidden with the reciprocal scale (fusion.cu:87-92)
+    scale8 = np.float32(peak / 448.0)
+    out8 = torch.empty((tokens, features), device=device, dtype=torch.uint8)
+    K.linear(out_format=N.OUT_FP8, out=out8, out_scale=torch.tensor(float(scale8), device=device), **common)
+    want8 = O.e4m3_encode_satfinite((O.bf16_to_f32(got_hidden) * (np.float32(1.0) / scale8)).astype(np.float32))
+    assert np.array_equal(u8(out8), want8)
+    K.linear(out_format=N.OUT_FP8, out=out8, out_scale=torch.tensor(float(scale8), device=device), flags=N.GEGLU_TRUE_DIV, **common)
+    assert np.array_equal(u8(out8), O.fp8_quantize_C(got_hidden, scale8)[0])
+    # NVFP4 output: codes, row-major scales and tiled scales of the CUDA-route encoder on the same hidden
+    scale4 = np.float32(peak / (448.0 * 6.0))
+    out4 = torch.empty((tokens, features // 2), device=device, dtype=torch.uint8)
+    linear = torch.empty((tokens, features // 16), device=device, dtype=torch.uint8)
+    blocked = torch.zeros(blocked_scale_bytes(tokens, features), device=device, dtype=torch.uint8)
+    K.linear(out_format=N.OUT_NVFP4, out=out4, out_scales=linear, out_blocked=blocked,
+             out_scale=torch.tensor(float(scale4), device=device), **common)
+    want4 = O.nvfp4_quantize_C(got_hidden, scale4)
+    assert np.array_equal(u8(out4), want4[0]) and np.array_equal(u8(linear), want4[1]) and np.array_equal(u8(blocked), want4[2])
+
+
+def test_gated_with_separate_up_scale(device):
+    """gate and up quantised separately (two per-tensor scales) give the same result as two Linears."""
+    tokens, features, width = 96, 128, 256
+    x = bits(make_input((tokens, width), 1))
+    wg = bits(make_weight((features, width), 2).to(torch.bfloat16))
+    wu = bits(make_weight((features, width), 3, std=0.05).to(torch.bfloat16))
+    aq, a_s = O.fp8_quantize_C(x)
+    gq, g_s = O.fp8_quantize_C(wg)
+    uq, u_s = O.fp8_quantize_C(wu)
+    table_host = gelu_table_cpu("tanh")
+    table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+    hidden = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+    scalar = lambda v: torch.tensor(float(v), device=device)
+    K.linear(kind=N.KIND_FP8, epilogue=N.EPI_GEGLU, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width,
+             act=torch.from_numpy(aq).to(device), act_scale=scalar(a_s), weight=torch.from_numpy(np.concatenate([gq, uq])).to(device),
+             weight_scale=scalar(g_s), weight_scale_up=scalar(u_s), gelu_table=table, out=hidden)
+    want = O.gelu_mul(O.fp8_linear(aq, a_s, gq, g_s), O.fp8_linear(aq, a_s, uq, u_s), table_host)
+    assert_gemm_close(bits(hidden), want)
+
+
+def test_full_size_properties(device):
+    """Config-2 sizes: zero activations give zero; doubling the activation scale doubles the output."""
+    tokens, features, width = 560, 16384, 2048
+    host, dev = operands("nvfp4", tokens, features, width, 1002, device)
+    out = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+    common = dict(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width)
+    K.linear(out=out, **common, **dev)
+    doubled = torch.empty_like(out)
+    K.linear(out=doubled, **common, **{**dev, "act_scale": dev["act_scale"] * 2})
+    assert torch.equal(out.float() * 2, doubled.float())
+    zero = {**dev, "act": torch.zeros_like(dev["act"])}
+    K.linear(out=doubled, **common, **zero)
+    assert not doubled.any()
+    rows = slice(300, 316)
+    want = O.nvfp4_linear_plan(host["a"][rows], host["a_sl"][rows], host["a_s"], host["w"], host["w_sl"], host["w_s"])
+    assert_gemm_close(bits(out[rows]), want)
+
+
+def test_rejections(device):
+    x = torch.zeros((8, 64), device=device, dtype=torch.uint8)
+    w = torch.zeros((16, 64), device=device, dtype=torch.uint8)
+    one = torch.ones((), device=device)
+    out = torch.zeros((8, 16), device=device, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="error -2"):
+        K.linear(kind=N.KIND_FP8, epilogue=N.EPI_LINEAR, out_format=N.OUT_FP8, tokens=8, features=16, width=64, act=x,
+                 act_scale=one, weight=w, weight_scale=one, out=out)
+    with pytest.raises(RuntimeError, match="error -2"):
+        K.linear(kind=N.KIND_FP8, epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=8, features=16, width=64, act=x,
+                 act_scale=one, weight=w, weight_scale=one, out=out, feature_tile=48)
+    with pytest.raises(RuntimeError, match="error -1"):
+        K.linear(kind=N.KIND_NVFP4, epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=8, features=16, width=128, act=x,
+                 act_scale=one, weight=w, weight_scale=one, out=out)      # NVFP4 without block scales
+    with pytest.raises(ValueError, match="no CPU fallback"):
+        K.linear(kind=N.KIND_FP8, epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=8, features=16, width=64, act=x.cpu(),
+                 act_scale=one, weight=w, weight_scale=one, out=out)

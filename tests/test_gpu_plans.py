@@ -1,0 +1,183 @@
+"""The reference-facing API on the GPU: registry Linear (bundles), plan registries, fused MLP.
+Mirrors the reference's own GPU tests for this path (tests/test_fused_operators.py:125-298,
+tests/pi05/test_graphs.py:238-313): fused == separate bit for bit, graph replay == eager."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from embodiinfer_b200 import layers as L
+from embodiinfer_b200.backend.mlp import FusedMlpPlan
+from embodiinfer_b200.bundles import pack_quantized_linears, quantize_linear
+from embodiinfer_b200.layers.registry import OperatorRequest
+from oracle import quant_oracle as O
+from tests.util import assert_gemm_close, bits, gelu_table_cpu, make_input, make_weight, u8
+
+pytestmark = pytest.mark.gpu
+
+
+def request(device, shape=None, bits_=None):
+    return OperatorRequest(device, torch.bfloat16, shape=shape, bits=bits_, cuda_graph=True)
+
+
+def module(n, k, seed, device, bias=False):
+    layer = nn.Linear(k, n, bias=bias)
+    layer.weight.data = make_weight((n, k), seed)
+    if bias:
+        layer.bias.data = make_weight((1, n), seed + 1, std=0.1).reshape(-1)
+    return layer.to(device=device, dtype=torch.bfloat16)
+
+
+def test_fp8_registry_linear_matches_reference_route(device):
+    """FP8Linear.forward -> fp8_native: oracle spec T with CUDA ATen semantics + W8A8 GEMM + bias."""
+    layer = module(1024, 2048, 3, device, bias=True)
+    bundle = quantize_linear(layer, L.FP8Config(backend="native"))
+    assert bundle.weight_scale.ndim == 0          # tensorwise on Blackwell (fp8.py:80-85)
+    x = make_input((2, 40, 2048), 5).to(device)
+    y = bundle(x)
+    assert y.shape == (2, 40, 1024) and y.dtype == torch.bfloat16
+    xb = bits(x).reshape(80, 2048)
+    aq, a_s = O.fp8_quantize_T(xb, scalar_div="rcp", divisor_bf16=True)
+    want = O.fp8_linear(aq, a_s, u8(bundle.weight), np.float32(bundle.weight_scale.item()), bits(layer.bias))
+    assert_gemm_close(bits(y).reshape(80, 1024), want)
+    # weight codes equal the oracle's weight quantiser under CUDA ATen semantics
+    codes, scale = O.fp8_quantize_weight_tensorwise(O.bf16_to_f32(bits(layer.weight)), "rcp")
+    assert np.array_equal(u8(bundle.weight), codes) and np.float32(bundle.weight_scale.item()) == scale
+
+
+def test_nvfp4_registry_linear_and_pack(device):
+    q, k, v = (module(n, 2048, 10 + i, device) for i, n in enumerate((2048, 256, 256)))
+    members = tuple(quantize_linear(layer, L.NVFP4Config(backend="auto")) for layer in (q, k, v))
+    packed = pack_quantized_linears(members)
+    x = make_input((560, 2048), 6).to(device)
+    y = packed(x)
+    assert y.shape == (560, 2560)
+    ap, asl, a_g = O.nvfp4_quantize_T(bits(x), "rcp")
+    want = O.nvfp4_linear_registry(ap, asl, a_g, u8(packed.weight), u8(packed.weight_scale),
+                                   np.float32(packed.weight_global_scale.item()))
+    assert_gemm_close(bits(y), want)
+    # a member views the packed storage, so it gives the matching slice
+    assert torch.equal(members[1](x), y[:, 2048:2304])
+
+
+def test_explicit_backend_errors(device):
+    layer = module(64, 72, 1, device)       # K = 72 is not a multiple of 16
+    with pytest.raises(RuntimeError, match="K divisible by 16"):
+        quantize_linear(layer, L.FP8Config(backend="native", scaling_scheme="tensorwise"))(torch.zeros((4, 72), device=device, dtype=torch.bfloat16))
+    channel = quantize_linear(module(64, 64, 1, device), L.FP8Config(backend="native", scaling_scheme="channelwise"))
+    with pytest.raises(RuntimeError, match="requires tensorwise weights"):
+        channel(torch.zeros((4, 64), device=device, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="no CPU or weight-only fallback"):
+        quantize_linear(module(64, 64, 1, device), L.FP8Config(backend="torch"))(torch.zeros((4, 64), device=device, dtype=torch.bfloat16))
+
+
+def test_quantizer_plans(device):
+    quantizer = L.quantization_backends.get("cuda", request(device, (560, 2048), 8))
+    x = make_input((560, 2048), 8).to(device)
+    plan = quantizer.plan(x, 8)
+    assert plan.dynamic and plan.quantize(x) is plan
+    codes, scale = O.fp8_quantize_C(bits(x))
+    assert np.float32(plan.scale.item()) == scale and np.array_equal(u8(plan.output), codes)
+    static = quantizer.plan(x, 4, 0.0123).quantize(x)
+    want = O.nvfp4_quantize_C(bits(x), np.float32(0.0123))
+    assert np.array_equal(u8(static.output), want[0]) and np.array_equal(u8(static.scales), want[1])
+    assert np.array_equal(u8(static.blocked), want[2]) and static.output.shape == (560, 1024)
+    with pytest.raises(ValueError, match="K divisible by 64"):
+        quantizer.plan(torch.zeros((4, 48), device=device, dtype=torch.bfloat16), 8)
+    with pytest.raises(ValueError, match="finite and positive"):
+        quantizer.plan(x, 8, float("nan"))
+    with pytest.raises(ValueError, match="contiguous CUDA BF16"):
+        quantizer.plan(x.float(), 8)
+    with pytest.raises(ValueError, match="shape or layout changed"):
+        plan.quantize(x[:100])
+    with pytest.raises(ValueError, match="3-bit"):
+        L.quantization_backends.get("cuda", request(device, (8, 64), 3))
+
+
+@pytest.mark.parametrize("bits_", (16, 8, 4))
+def test_standalone_gelu_mul_equals_separate_steps(device, bits_):
+    quantizer = L.quantization_backends.get("cuda", request(device))
+    fusion = L.gelu_mul_backends.get("cuda", request(device), backend=quantizer, approximate="tanh")
+    gate, up = make_input((130, 256), 1).to(device), make_input((130, 256), 2, outliers=False).to(device)
+    hidden = O.gelu_mul(bits(gate), bits(up), gelu_table_cpu("tanh"))
+    assert np.array_equal(u8(fusion.table).view(np.uint16), gelu_table_cpu("tanh")), "device-built GELU table differs from the CPU one"
+    scale = None if bits_ == 16 else 0.05
+    plan = fusion.plan(gate, bits_, scale).encode(gate, up)
+    if bits_ == 16:
+        assert np.array_equal(bits(plan.output), hidden)
+        packed = fusion.plan(gate, 16).encode_packed(torch.cat((gate, up), dim=1).contiguous())
+        assert np.array_equal(bits(packed.output), hidden)
+    elif bits_ == 8:
+        want = O.e4m3_encode_satfinite((O.bf16_to_f32(hidden) * (np.float32(1.0) / np.float32(0.05))).astype(np.float32))
+        assert np.array_equal(u8(plan.output), want)
+    else:
+        want = O.nvfp4_quantize_C(hidden, np.float32(0.05))
+        assert np.array_equal(u8(plan.output), want[0]) and np.array_equal(u8(plan.scales), want[1])
+        assert np.array_equal(u8(plan.blocked), want[2])
+
+
+@pytest.mark.parametrize("precision", ("fp8", "nvfp4"))
+def test_projection_plan_and_fused_mlp(device, precision):
+    """Fused MLP (3 launches) == encode, gate GEMM, up GEMM, stand-alone GELU*up encode, down GEMM."""
+    hidden_size, inter = 1024, 4096
+    quantizer = L.quantization_backends.get("cuda", request(device))
+    projections = L.projection_backends.get("cuda", request(device))
+    fusion = L.gelu_mul_backends.get("cuda", request(device), backend=quantizer, approximate="tanh")
+    gate_w, up_w = (make_weight((inter, hidden_size), s).to(device, torch.bfloat16) for s in (1, 2))
+    down_w = make_weight((hidden_size, inter), 3).to(device, torch.bfloat16)
+    x = make_input((1, 560, hidden_size), 4).to(device)
+    key = lambda dev: ("stream", torch.cuda.current_stream(dev).cuda_stream)
+    gate = projections.plan(gate_w, 40.0, precision, quantizer, key)
+    up = projections.plan(up_w, 40.0, precision, quantizer, key)
+    down = projections.plan(down_w, 8.0, precision, quantizer, key)
+    encoded = gate.encode(x)
+    g, u = gate.apply(x, encoded), up.apply(x, encoded)
+    assert g.shape == (1, 560, inter)
+    # oracle check of one projection
+    xb = bits(x).reshape(560, hidden_size)
+    if precision == "fp8":
+        aq, a_s = O.fp8_quantize_C(xb, np.float32(40.0 / 448))
+        want = O.fp8_linear(aq, a_s, u8(gate.weight), np.float32(gate.weight_scale.item()))
+    else:
+        ap, asl, _, a_s = O.nvfp4_quantize_C(xb, np.float32(40.0 / 2688))
+        wp, wsl, _, w_s = O.nvfp4_quantize_C(bits(gate_w))
+        assert np.array_equal(u8(gate.weight), wp) and np.float32(gate.weight_scale.item()) == w_s
+        want = O.nvfp4_linear_plan(ap, asl, a_s, wp, wsl, w_s)
+    assert_gemm_close(bits(g).reshape(560, inter), want)
+    bits_ = 8 if precision == "fp8" else 4
+    separate = fusion.plan(g.reshape(560, inter), bits_, 8.0 / (448 * (6 if bits_ == 4 else 1)))
+    separate.encode(g.reshape(560, inter), u.reshape(560, inter).contiguous())
+    y_separate = down.apply(g, separate).clone()
+    mlp = FusedMlpPlan(gate_w, up_w, down_w, gate_up_max=40.0, down_max=8.0, gate_up=precision, down=precision,
+                       quantizer=quantizer, approximate="tanh", workspace_key=key)
+    y_fused = mlp(x)
+    assert torch.equal(y_fused, y_separate), "fused MLP differs from the separate steps"
+    residual = make_input((1, 560, hidden_size), 9, outliers=False).to(device)
+    assert torch.equal(mlp(x, residual=residual), y_separate + residual)
+    # graph replay == eager (after the warm-up above)
+    static_x = x.clone()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        mlp(static_x)                              # warm this stream's workspaces
+        with torch.cuda.graph(graph, stream=side):
+            y_graph = mlp(static_x)
+    static_x.copy_(make_input((1, 560, hidden_size), 44).to(device))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y_graph, mlp(static_x))
+    mlp.release_scope(key(device))
+    assert not mlp.gate_up.plans and not mlp.down.outputs
+
+
+def test_backend_construction_refused_during_capture(device):
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with pytest.raises(RuntimeError, match="before CUDA Graph capture"):
+            with torch.cuda.graph(graph, stream=side):
+                L.quantization_backends.get("cuda", request(device))
