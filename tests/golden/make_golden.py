@@ -49,7 +49,7 @@ def make_input(shape, seed, multiplier):
     generator = torch.Generator().manual_seed(seed)
     x = torch.randn(shape, generator=generator) * multiplier
     x = torch.where(torch.rand(shape, generator=generator) < 0.01, x * 20, x).to(torch.bfloat16)
-    if shape[0] > 1 and shape[1] >= 32:
+    if len(shape) == 2 and shape[0] > 1 and shape[1] >= 32:
         x[0, :16] = 0
         x[1, 16:32] = torch.tensor([0.0, -0.0] * 8).to(torch.bfloat16)
     return x

@@ -102,8 +102,17 @@ def test_standalone_gelu_mul_equals_separate_steps(device, bits_):
     quantizer = L.quantization_backends.get("cuda", request(device))
     fusion = L.gelu_mul_backends.get("cuda", request(device), backend=quantizer, approximate="tanh")
     gate, up = make_input((130, 256), 1).to(device), make_input((130, 256), 2, outliers=False).to(device)
-    hidden = O.gelu_mul(bits(gate), bits(up), gelu_table_cpu("tanh"))
-    assert np.array_equal(u8(fusion.table).view(np.uint16), gelu_table_cpu("tanh")), "device-built GELU table differs from the CPU one"
+    # The table is the framework's GELU evaluated on the device (activation.py:34-37); NaN inputs aside
+    # it must agree with the CPU evaluation that the golden vectors were made with.
+    table = u8(fusion.table).view(np.uint16)
+    finite = np.isfinite(O.bf16_to_f32(np.arange(65536, dtype=np.uint32).astype(np.uint16)))
+    cpu_table = gelu_table_cpu("tanh")
+    differing = np.nonzero(finite & (table != cpu_table))[0]
+    # The device's tanh and the host's differ in the last bit for a handful of inputs (4 of 65,280 on a
+    # B200 with torch 2.11); the kernels take the table as an operand, so either one is reproduced exactly.
+    assert len(differing) <= 16
+    assert np.abs(table[differing].astype(np.int32) - cpu_table[differing].astype(np.int32)).max(initial=0) <= 1
+    hidden = O.gelu_mul(bits(gate), bits(up), table)
     scale = None if bits_ == 16 else 0.05
     plan = fusion.plan(gate, bits_, scale).encode(gate, up)
     if bits_ == 16:
@@ -170,8 +179,9 @@ def test_projection_plan_and_fused_mlp(device, precision):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(y_graph, mlp(static_x))
-    mlp.release_scope(key(device))
-    assert not mlp.gate_up.plans and not mlp.down.outputs
+    scope = key(device)
+    mlp.release_scope(scope)
+    assert all(k[-1] != scope for k in (*mlp.gate_up.plans, *mlp.gate_up.outputs, *mlp.down.outputs))
 
 
 def test_backend_construction_refused_during_capture(device):

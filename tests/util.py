@@ -23,7 +23,7 @@ def make_input(shape, seed, multiplier=1.0, outliers=True):
     else:
         torch.rand(shape, generator=generator)
     x = x.to(torch.bfloat16)
-    if shape[0] > 1 and shape[1] >= 32:
+    if len(shape) == 2 and shape[0] > 1 and shape[1] >= 32:
         x[0, :16] = 0
         x[1, 16:32] = torch.tensor([0.0, -0.0] * 8).to(torch.bfloat16)
     return x
