@@ -1,0 +1,345 @@
+"""Benchmark of the quantised-Linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (BASELINE config 2): the NVFP4 W4A4 linear pair of a Gemma-2B-shaped MLP at M = 560 tokens:
+encode x (bf16 -> NVFP4, calibrated scale) -> [gate;up] 2048 -> 2x16384 with the gated GELU-tanh
+epilogue that re-encodes the hidden activation to NVFP4 -> down 16384 -> 2048 (bf16 out).
+Inputs are seeded synthetic tensors with the config's shapes and distributions (x ~ N(0,1) with 1 %
+outliers x20, weights ~ N(0, 0.02)).  One "step" is one pass of that chain over one batch.
+
+Metric: quant GEMM TFLOP/s = 2*M*K*N summed over the two GEMMs / time, whole job over all ranks.
+  value  device time only: operands resident in HBM, CUDA events around every step on the launching
+         stream, L2 flushed between steps, max over ranks.
+  e2e    the same chain through the public API with host buffers: pinned-host x -> device, the three
+         launches, bf16 result -> pinned host, all inside the timed region.
+With N > 1 every rank runs the same chain on its own batch (weights replicated, no collective on the
+data path): weak scaling.
+
+`--impl reference` times the CPU restatement of the reference's route (oracle/, numpy + BLAS on all
+host threads) on the same workload and prints the same line with "impl": "reference".
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+TOKENS, HIDDEN, INTER = 560, 2048, 16384
+SEED = 1002
+FLOPS_GATE_UP = 2.0 * TOKENS * HIDDEN * 2 * INTER
+FLOPS_DOWN = 2.0 * TOKENS * INTER * HIDDEN
+FLOPS_STEP = FLOPS_GATE_UP + FLOPS_DOWN
+METRIC = "quant_gemm_tflops"
+UNIT = "TFLOP/s"
+WORKLOAD = "cfg2: NVFP4 W4A4 MLP pair, M=560, gate_up 2048->2x16384 (+GELU-tanh, NVFP4 re-encode), down 16384->2048"
+NOMINAL_NVFP4_TFLOPS = 9000.0
+
+
+def synthetic_inputs(seed: int):
+    """Seeded tensors with BASELINE config 2's shapes and value distributions."""
+    generator = torch.Generator().manual_seed(seed)
+    x = torch.randn((TOKENS, HIDDEN), generator=generator)
+    x = torch.where(torch.rand((TOKENS, HIDDEN), generator=generator) < 0.01, x * 20, x).to(torch.bfloat16)
+    gate = (0.02 * torch.randn((INTER, HIDDEN), generator=generator)).to(torch.bfloat16)
+    up = (0.02 * torch.randn((INTER, HIDDEN), generator=generator)).to(torch.bfloat16)
+    down = (0.02 * torch.randn((HIDDEN, INTER), generator=generator)).to(torch.bfloat16)
+    return x, gate, up, down
+
+
+def measured_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text())
+    return {}
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU leg: the oracle port of the reference's route
+
+
+def bits(tensor: torch.Tensor) -> np.ndarray:
+    return tensor.contiguous().view(torch.uint16).numpy()
+
+
+def cpu_port_step(x, gate, up, down, gate_up_max: float, down_max: float, table: np.ndarray):
+    """One pass of the chain with the numpy oracle; returns (bf16 bits of y, seconds)."""
+    from oracle import quant_oracle as O
+
+    if not hasattr(cpu_port_step, "weights"):
+        cpu_port_step.weights = [O.nvfp4_quantize_C(bits(w)) for w in (gate, up, down)]   # one-time, not timed
+    (gp, gsl, _, g_s), (up_, usl, _, u_s), (dp, dsl, _, d_s) = cpu_port_step.weights
+    start = time.perf_counter()
+    ap, asl, _, a_s = O.nvfp4_quantize_C(bits(x), np.float32(gate_up_max / 2688.0))
+    g = O.nvfp4_linear_plan(ap, asl, a_s, gp, gsl, g_s)
+    u = O.nvfp4_linear_plan(ap, asl, a_s, up_, usl, u_s)
+    hidden = O.gelu_mul(g, u, table)
+    hp, hsl, _, h_s = O.nvfp4_quantize_C(hidden, np.float32(down_max / 2688.0))
+    y = O.nvfp4_linear_plan(hp, hsl, h_s, dp, dsl, d_s)
+    return y, time.perf_counter() - start
+
+
+def cpu_table() -> np.ndarray:
+    codes = torch.arange(65536, dtype=torch.int32).to(torch.uint16).view(torch.bfloat16)
+    return torch.nn.functional.gelu(codes, approximate="tanh").view(torch.uint16).numpy()
+
+
+def calibrate_on_cpu(x, gate, up):
+    """Calibrated maxima the way a calibration pass would record them: amax of the MLP input and of
+    the hidden activation (bf16 reference math on a 64-token sample)."""
+    gate_up_max = float(x.float().abs().max())
+    sample = x[:64].float()
+    hidden = torch.nn.functional.gelu(sample @ gate.float().t(), approximate="tanh") * (sample @ up.float().t())
+    return gate_up_max, float(hidden.abs().max()) * 2.0
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    x, gate, up, down = synthetic_inputs(SEED)
+    gate_up_max, down_max = calibrate_on_cpu(x, gate, up)
+    table = cpu_table()
+    threads = torch.get_num_threads()
+    # A full step is ~10 s of host work: bound the run to a few minutes whatever K says.
+    steps = max(1, min(args.steps, 3))
+    warmup = max(0, min(args.warmup, 1))
+    for _ in range(warmup):
+        cpu_port_step(x, gate, up, down, gate_up_max, down_max, table)
+    seconds = [cpu_port_step(x, gate, up, down, gate_up_max, down_max, table)[1] for _ in range(steps)]
+    mean = float(np.mean(seconds))
+    value = FLOPS_STEP / mean / 1e12
+    sample = f"{steps} full step(s) of the workload (bounded from --steps {args.steps}); weights quantised once, untimed"
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+        "ms_per_step": mean * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "host": "numpy/BLAS port of the reference's route (oracle/quant_oracle.py)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU leg
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+        0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index: int) -> None:
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._halt = threading.Event()
+        self.error = None
+
+    def run(self) -> None:
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = int(visible.split(",")[self.index]) if visible and visible.split(",")[self.index].isdigit() else self.index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(physical)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            while not self._halt.is_set():
+                self.samples.append(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.reasons.update(name for bit, name in self.REASONS.items() if mask & bit and bit != 0x1)
+                time.sleep(0.002)
+        except Exception as error:   # NVML missing: report it instead of failing the benchmark
+            self.error = repr(error)
+
+    def stop(self) -> dict:
+        self._halt.set()
+        self.join(timeout=2.0)
+        out = {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+               "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        if self.error:
+            out["error"] = self.error
+        return out
+
+
+def run_ours(args) -> None:
+    import torch.distributed as dist
+
+    from embodiinfer_b200 import _native as N
+    from embodiinfer_b200 import kernels as K
+    from embodiinfer_b200 import layers as L
+    from embodiinfer_b200.backend.mlp import FusedMlpPlan, _ShapeOnly
+    from embodiinfer_b200.layers.registry import OperatorRequest
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU leg)")
+    if world != args.gpus:
+        raise RuntimeError(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    x, gate, up, down = synthetic_inputs(SEED + rank)       # every rank its own batch; same weights' distribution
+    gate_up_max, down_max = calibrate_on_cpu(x, gate, up)
+    quantizer = L.quantization_backends.get("cuda", OperatorRequest(device, torch.bfloat16, shape=(TOKENS, HIDDEN), bits=4))
+    mlp = FusedMlpPlan(gate.to(device), up.to(device), down.to(device), gate_up_max=gate_up_max, down_max=down_max,
+                       gate_up="nvfp4", down="nvfp4", quantizer=quantizer, approximate="tanh")
+    x_device = x.to(device)
+    x_host = x.pin_memory()
+    y_host = torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    flush = torch.empty(256 * 1024 * 1024, device=device, dtype=torch.uint8)     # 2x the 126 MB L2
+    stream = torch.cuda.current_stream(device)
+
+    def step_device(events=None):
+        encoded = mlp.encode(x_device)
+        if events is not None:
+            events[0].record(stream)
+        hidden = mlp.gate_up.apply_gated(x_device, encoded, table=mlp.table, bits=4, scale=mlp.down.maximum / 2688.0)
+        if events is not None:
+            events[1].record(stream)
+        return mlp.down.apply(mlp_shape, hidden)
+
+    mlp_shape = _ShapeOnly((TOKENS, INTER), x_device)
+
+    def step_e2e():
+        staged = x_device_staging.copy_(x_host, non_blocking=True)
+        y = mlp(staged)
+        y_host.copy_(y, non_blocking=True)
+
+    x_device_staging = torch.empty_like(x_device)
+
+    y_first = step_device().clone()
+    torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step_device()
+        step_e2e()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    new_event = lambda: torch.cuda.Event(enable_timing=True)
+    starts, mids0, mids1, ends = ([new_event() for _ in range(args.steps)] for _ in range(4))
+    sampler = ClockSampler(local)
+    sampler.start()
+    # keep the clocks under load for the sampler and out of their idle state before timing
+    spin_until = time.time() + 0.5
+    while time.time() < spin_until:
+        step_device()
+    barrier()
+    for i in range(args.steps):
+        flush.zero_()
+        starts[i].record(stream)
+        step_device((mids0[i], mids1[i]))
+        ends[i].record(stream)
+    barrier()
+    device_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+    gate_up_ms = sum(a.elapsed_time(b) for a, b in zip(mids0, mids1)) / args.steps
+
+    e2e_starts, e2e_ends = ([new_event() for _ in range(args.steps)] for _ in range(2))
+    barrier()
+    for i in range(args.steps):
+        flush.zero_()
+        e2e_starts[i].record(stream)
+        step_e2e()
+        e2e_ends[i].record(stream)
+    barrier()
+    e2e_ms = sum(s.elapsed_time(e) for s, e in zip(e2e_starts, e2e_ends))
+    clocks = sampler.stop()
+
+    if world > 1:
+        times = torch.tensor([device_ms, e2e_ms, gate_up_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        device_ms, e2e_ms, gate_up_ms = times.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    value = world * args.steps * FLOPS_STEP / (device_ms * 1e-3) / 1e12
+    e2e_value = world * args.steps * FLOPS_STEP / (e2e_ms * 1e-3) / 1e12
+    peaks = measured_peaks()
+    achieved = FLOPS_GATE_UP / (gate_up_ms * 1e-3) / 1e12
+    if "bf16_tflops" in peaks:
+        peak = 4.0 * float(peaks["bf16_tflops"])
+        peak_source = "4 x measured cuBLAS bf16 burst (MEASURED_PEAKS.json has no NVFP4 figure; 4x is the nominal NVFP4:bf16 ratio)"
+    else:
+        peak = 4.0 * 1590.0
+        peak_source = "4 x fallback bf16 burst 1590 TFLOP/s (MEASURED_PEAKS.json absent)"
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": device_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "nvfp4", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "flushed between steps (256 MiB write)", "launches_per_step": 3,
+                   "calibrated_max": {"gate_up": gate_up_max, "down": down_max}},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": 3 * args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "linear_kernel<NVFP4, GEGLU->NVFP4> (gate_up)", "achieved": achieved, "peak": peak,
+                     "unit": "TFLOP/s", "frac": achieved / peak, "frac_of_nominal_9000": achieved / NOMINAL_NVFP4_TFLOPS,
+                     "peak_source": peak_source, "us_per_launch": gate_up_ms * 1e3, "traffic": TRAFFIC_BYTES_GATE_UP},
+    }
+    if world == 1:
+        table = cpu_table()
+        x0, gate0, up0, down0 = synthetic_inputs(SEED)
+        y_cpu, seconds = cpu_port_step(x0, gate0, up0, down0, gate_up_max, down_max, table)
+        from oracle import quant_oracle as O
+        y_gpu = y_first.cpu().view(torch.uint16).numpy()
+        line["parity"] = {"rel_frobenius": O.rel_frobenius(y_gpu, y_cpu), "max_abs": O.max_abs(y_gpu, y_cpu),
+                          "against": "CPU oracle, whole output of this workload"}
+        line["cpu_baseline"] = {"value": FLOPS_STEP / seconds / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": "one full step of the same workload with the numpy/BLAS oracle (weights quantised once, untimed)"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up launch, from the ncu capture summarised in
+# profiles/ (None until that capture exists).
+TRAFFIC_BYTES_GATE_UP = None
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=20)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
