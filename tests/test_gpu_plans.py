@@ -108,10 +108,13 @@ def test_standalone_gelu_mul_equals_separate_steps(device, bits_):
     finite = np.isfinite(O.bf16_to_f32(np.arange(65536, dtype=np.uint32).astype(np.uint16)))
     cpu_table = gelu_table_cpu("tanh")
     differing = np.nonzero(finite & (table != cpu_table))[0]
-    # The device's tanh and the host's differ in the last bit for a handful of inputs (4 of 65,280 on a
-    # B200 with torch 2.11); the kernels take the table as an operand, so either one is reproduced exactly.
+    # The device's tanh and the host's differ for a handful of inputs (on a B200 with torch 2.11: the four
+    # codes 0xc0a2..0xc0a5, x ~ -5.1, where the host saturates tanh to -1 and returns -0.0 while the device
+    # returns -1.5e-7); the kernels take the table as an operand, so either one is reproduced exactly.
     assert len(differing) <= 16
-    assert np.abs(table[differing].astype(np.int32) - cpu_table[differing].astype(np.int32)).max(initial=0) <= 1
+    on_device, on_host = O.bf16_to_f32(table[differing]), O.bf16_to_f32(cpu_table[differing])
+    close = np.abs(on_device - on_host) <= 1e-6 + 2.0**-7 * np.maximum(np.abs(on_device), np.abs(on_host))
+    assert close.all(), [(hex(int(c)), float(a), float(b)) for c, a, b in zip(differing, on_device, on_host)]
     hidden = O.gelu_mul(bits(gate), bits(up), table)
     scale = None if bits_ == 16 else 0.05
     plan = fusion.plan(gate, bits_, scale).encode(gate, up)
