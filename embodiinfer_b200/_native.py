@@ -20,6 +20,8 @@ EPI_LINEAR, EPI_GEGLU = 0, 1
 OUT_BF16, OUT_FP8, OUT_NVFP4 = 0, 1, 2
 LINEAR_ROUND_SCALE_BF16 = 1
 SCALE_SCRATCH_BYTES = 8
+STATIC_SCRATCH_BYTES = 16640
+STATIC_SCALE_MAX_COUNT = 67108864
 ABI_VERSION = 1
 
 _ERRORS = {
@@ -66,6 +68,7 @@ _P, _I, _I64, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 SIGNATURES: dict[str, list] = {
     "b2_abi_version": [],
     "b2_tensor_scale": [_P, _I64, _F, _I, _P, _P, _P],
+    "b2_tensor_scale_static": [_P, _I64, _F, _I, _P, _P],
     "b2_fp8_quantize": [_P, _P, _P, _I64, _I, _P],
     "b2_nvfp4_quantize": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "b2_geglu": [_P, _P, _P, _P, _P, _P, _I, _I, _I64, _I, _P, _I, _P],

@@ -7,6 +7,8 @@ int run_linear(const b2_linear_desc* desc, cudaStream_t stream);
 int launch_geglu(const void* gate, const void* up, void* output, void* scales, void* blocked, const void* scale,
                  int rows, int columns, int64_t row_stride, int bits, const void* table, int flags,
                  cudaStream_t stream);
+int launch_tensor_scale_static(const void* input, int64_t count, float bound, int flags, void* scale,
+                               cudaStream_t stream);
 }  // namespace b2
 
 static bool is_aligned(const void* pointer, uintptr_t bytes) {
@@ -22,6 +24,12 @@ int b2_tensor_scale(const void* input, int64_t count, float bound, int flags, vo
     if (input == nullptr || scratch == nullptr || scale == nullptr || count <= 0 || !(bound > 0.0f)) return B2_E_INVALID;
     if (!is_aligned(input, 16) || !is_aligned(scratch, 4) || !is_aligned(scale, 4)) return B2_E_INVALID;
     return b2::launch_tensor_scale(input, count, bound, flags, scratch, scale, static_cast<cudaStream_t>(stream));
+}
+
+int b2_tensor_scale_static(const void* input, int64_t count, float bound, int flags, void* scale, void* stream) {
+    if (input == nullptr || scale == nullptr || count <= 0 || !(bound > 0.0f)) return B2_E_INVALID;
+    if (!is_aligned(input, 16) || !is_aligned(scale, 4)) return B2_E_INVALID;
+    return b2::launch_tensor_scale_static(input, count, bound, flags, scale, static_cast<cudaStream_t>(stream));
 }
 
 int b2_fp8_quantize(const void* input, void* output, const void* scale, int64_t count, int flags, void* stream) {

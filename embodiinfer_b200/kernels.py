@@ -56,6 +56,21 @@ def tensor_scale(x: torch.Tensor, bound: float, flags: int, scratch: torch.Tenso
     N.check(status, "b2_tensor_scale")
 
 
+def tensor_scale_static(x: torch.Tensor, bound: float, flags: int, scale: torch.Tensor) -> None:
+    """``tensor_scale`` for callers that may not allocate or pass scratch memory: the scratch is a static
+    array inside the library (``b2_tensor_scale_static``).  At most ``STATIC_SCALE_MAX_COUNT`` elements;
+    calls that overlap on one GPU race on the shared array; make the first call on a device outside
+    any stream capture."""
+    device = _require_cuda(x, scale)
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("tensor_scale_static requires a contiguous bf16 tensor")
+    with torch.cuda.device(device):
+        status = N.load().b2_tensor_scale_static(
+            x.data_ptr(), x.numel(), float(bound), int(flags), scale.data_ptr(), _stream(device)
+        )
+    N.check(status, "b2_tensor_scale_static")
+
+
 def fp8_quantize(x: torch.Tensor, out: torch.Tensor, scale: torch.Tensor, flags: int) -> None:
     """bf16 -> e4m3 at ``*scale``, see ``b2_fp8_quantize``."""
     device = _require_cuda(x, out, scale)

@@ -57,6 +57,21 @@ int b2_abi_version(void);
 int b2_tensor_scale(const void* input, int64_t count, float bound, int flags, void* scratch, void* scale,
                     void* stream);
 
+/* Same result as b2_tensor_scale, for callers that cannot provide scratch memory and must not allocate:
+ * a control loop working inside a fixed arena of device pointers owned by another runtime, or a server
+ * that bans cudaMalloc once it is running because the call synchronises the device.  It has no
+ * counterpart in the reference.  The scratch is a static device array of B2_STATIC_SCRATCH_BYTES inside
+ * the library (held by every GPU that loads it, until the process exits).  Limits and rules:
+ *   - count <= B2_STATIC_SCALE_MAX_COUNT elements, otherwise B2_E_TOO_LARGE;
+ *   - the first call on each device looks up the array's device address (that device must be current);
+ *     make that first call before starting any stream capture;
+ *   - all calls on a GPU share the one array: calls that overlap on that GPU (two streams, two threads)
+ *     race; calls ordered on one stream do not.  Nothing needs zeroing by the caller.
+ * It allocates and frees nothing. */
+#define B2_STATIC_SCRATCH_BYTES 16640
+#define B2_STATIC_SCALE_MAX_COUNT 67108864
+int b2_tensor_scale_static(const void* input, int64_t count, float bound, int flags, void* scale, void* stream);
+
 /* bf16[count] -> e4m3[count] with the per-tensor scale read from device memory.
  * Replaces cc_fp8 (quantize.cu:127-133); spec T reproduces fp8.py:72.  flags: B2_SPEC_*, B2_DIVISOR_BF16. */
 int b2_fp8_quantize(const void* input, void* output, const void* scale, int64_t count, int flags, void* stream);
