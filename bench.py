@@ -218,7 +218,8 @@ def run_ours(args) -> None:
         encoded = mlp.encode(x_device)
         if events is not None:
             events[0].record(stream)
-        hidden = mlp.gate_up.apply_gated(x_device, encoded, table=mlp.table, bits=4, scale=mlp.down.maximum / 2688.0)
+        hidden = mlp.gate_up.apply_gated(x_device, encoded, table=mlp.table, bits=4, scale=mlp.down.maximum / 2688.0,
+                                         table_range=mlp.table_range)
         if events is not None:
             events[1].record(stream)
         return mlp.down.apply(mlp_shape, hidden)

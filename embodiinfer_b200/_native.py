@@ -44,6 +44,8 @@ class LinearDesc(ctypes.Structure):
         ("features", ctypes.c_int32),
         ("width", ctypes.c_int32),
         ("feature_tile", ctypes.c_int32),
+        ("gelu_lo", ctypes.c_int32),
+        ("gelu_hi", ctypes.c_int32),
         ("act", ctypes.c_void_p),
         ("act_scales", ctypes.c_void_p),
         ("act_scale", ctypes.c_void_p),
@@ -73,6 +75,7 @@ SIGNATURES: dict[str, list] = {
     "b2_nvfp4_quantize": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "b2_geglu": [_P, _P, _P, _P, _P, _P, _I, _I, _I64, _I, _P, _I, _P],
     "b2_linear": [ctypes.POINTER(LinearDesc), _P],
+    "b2_gelu_table_range": [_P, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)],
 }
 
 _lock = threading.Lock()

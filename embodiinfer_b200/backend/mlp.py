@@ -14,6 +14,7 @@ from typing import Literal
 
 import torch
 
+from .. import kernels as K
 from ..layers.plans import ActivationQuantizer, EncodedActivation, Precision, WorkspaceKey
 from .activation import gelu_table
 from .projection import B200Projection
@@ -53,6 +54,7 @@ class FusedMlpPlan:
         self.down = B200Projection(down_weight, down_max, down, quantizer if down != "bf16" else None, workspace_key)
         self.table = gelu_table(gate_weight.device, approximate) if table is None else table
         self.approximate = approximate
+        self.table_range = K.gelu_table_range(self.table)
 
     def encode(self, inputs: torch.Tensor) -> EncodedActivation:
         return self.gate_up.encode(inputs)
@@ -61,7 +63,9 @@ class FusedMlpPlan:
         """``encoded`` is ``inputs`` at the gate/up scale (shared by both halves, mlp.py:222)."""
         bits = _BITS[self.down.precision]
         scale = None if bits == 16 else self.down.maximum / (448 * (6 if bits == 4 else 1))
-        hidden = self.gate_up.apply_gated(inputs, encoded, table=self.table, bits=bits, scale=scale)
+        hidden = self.gate_up.apply_gated(
+            inputs, encoded, table=self.table, bits=bits, scale=scale, table_range=self.table_range
+        )
         shape = (*inputs.shape[:-1], self.inter_size)
         if bits == 16:
             return self.down.apply(hidden.output.reshape(shape), None)

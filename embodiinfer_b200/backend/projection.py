@@ -159,6 +159,7 @@ class B200Projection:
         table: torch.Tensor,
         bits: int,
         scale: float | None = None,
+        table_range: tuple[int, int] = (0, 0),
     ):
         """This weight is a packed ``[gate; up]`` (2F rows): one launch computes both projections,
         ``h = bf16(bf16(gelu(gate)) * up)`` and stores ``h`` as bf16 (``bits=16``), e4m3 (8) or
@@ -193,7 +194,8 @@ class B200Projection:
         K.linear(
             epilogue=N.EPI_GEGLU, out_format=out_format, tokens=rows, features=features, width=self.input_dim,
             out=result.output, gelu_table=table, out_scale=result.scale, out_scales=result.scales,
-            out_blocked=result.blocked, weight_scale_up=self.weight_scale_up, **self._operands(encoded),
+            out_blocked=result.blocked, weight_scale_up=self.weight_scale_up, gelu_range=table_range,
+            **self._operands(encoded),
         )
         return result
 

@@ -2,6 +2,8 @@
 // Declarations and per-entry documentation live in include/embodiinfer_b200.h.
 #include "common.cuh"
 
+#include <cstring>
+
 namespace b2 {
 int run_linear(const b2_linear_desc* desc, cudaStream_t stream);
 int launch_geglu(const void* gate, const void* up, void* output, void* scales, void* blocked, const void* scale,
@@ -57,6 +59,35 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
     if (bits != 16 && scale == nullptr) return B2_E_INVALID;
     return b2::launch_geglu(gate, up, output, scales, blocked, scale, rows, columns, row_stride, bits, table, flags,
                             static_cast<cudaStream_t>(stream));
+}
+
+static uint16_t host_bf16(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    if ((bits & 0x7fffffffu) > 0x7f800000u) return 0x7fc0;
+    return uint16_t((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
+}
+
+int b2_gelu_table_range(const void* host_table, int32_t* lo, int32_t* hi) {
+    if (host_table == nullptr || lo == nullptr || hi == nullptr) return B2_E_INVALID;
+    const uint16_t* table = static_cast<const uint16_t*>(host_table);
+    *lo = *hi = 0;
+    const int first = 0x80, last = 0x7f80;        // normal finite magnitudes
+    int low = first;
+    for (; low < last; ++low) {
+        const uint32_t word = uint32_t(low) << 16;
+        float x;
+        memcpy(&x, &word, 4);
+        if (table[low] != host_bf16(0.5f * x) || table[0x8000 + low] != host_bf16(-0.5f * x)) break;
+    }
+    int high = last;
+    for (; high > low; --high)
+        if (table[high - 1] != high - 1 || table[0x8000 + high - 1] != 0x8000) break;
+    if (high - low > 4096) return B2_E_UNSUPPORTED;
+    if (high == low) high = low + 1 <= last ? low + 1 : low;   // keep a non-empty range so the closed forms stay enabled
+    *lo = low;
+    *hi = high;
+    return B2_OK;
 }
 
 int b2_linear(const b2_linear_desc* desc, void* stream) {

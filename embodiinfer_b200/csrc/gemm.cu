@@ -47,6 +47,7 @@ constexpr int TMEM_COLUMNS = 512;
 constexpr int TMEM_SFA = 448;                      // NVFP4: token scales, 4 columns per 64 elements of K
 constexpr int TMEM_SFB = 464;                      // NVFP4: feature scales, 8 columns per 64 elements of K
 constexpr int SMEM_LIMIT = 227 * 1024;
+constexpr int MAX_COMPACT_GELU = 4096;             // magnitude codes of the GELU table kept in shared memory
 constexpr int SMEM_MINIMUM = 120 * 1024;           // keeps a second CTA (and its TMEM request) off the SM
 
 enum { EPI_LINEAR = 0, EPI_GEGLU_BF16 = 1, EPI_GEGLU_FP8 = 2, EPI_GEGLU_NVFP4 = 3 };
@@ -60,6 +61,7 @@ struct KernelArgs {
     int scale_column_tiles;      // 512-byte scale atoms per 128-row block
     int act_row_blocks, weight_row_blocks;
     int flags;
+    int gelu_lo, gelu_hi;        // bf16 magnitude codes [lo, hi) whose GELU is kept in shared memory (0,0 = none)
     const uint8_t* act_scales;
     const uint8_t* weight_scales;
     const float* act_scale;
@@ -135,19 +137,40 @@ __device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32],
                      pack_bf16x2(y[8 * v + 4], y[8 * v + 5]), pack_bf16x2(y[8 * v + 6], y[8 * v + 7]));
 }
 
+// GELU of a bf16 value held in a float.  Magnitude codes [lo, hi) come from the shared-memory copy of
+// the table ([positive | negative] halves); below lo the table equals bf16(x/2), from hi up to the
+// largest finite value it equals x (positive) or -0 (negative) — the host verified both against the
+// table before choosing lo and hi.  Subnormals, infinities and NaNs read the full table in global memory.
+__device__ __forceinline__ float gelu_lookup(float gate, const KernelArgs& args, uint32_t compact_table) {
+    const uint32_t bits = __float_as_uint(gate) >> 16;
+    const uint32_t magnitude = bits & 0x7fffu;
+    const uint32_t span = uint32_t(args.gelu_hi - args.gelu_lo);
+    const uint32_t offset = magnitude - uint32_t(args.gelu_lo);
+    if (offset < span) {
+        uint32_t value;
+        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(value) : "r"(compact_table + 2u * (offset + (bits >> 15) * span)));
+        return __uint_as_float(value << 16);
+    }
+    if (span != 0 && magnitude >= 0x80u && magnitude < 0x7f80u) {
+        if (magnitude < uint32_t(args.gelu_lo)) return round_to_bf16(__fmul_rn(0.5f, gate));
+        return (bits >> 15) ? -0.0f : gate;
+    }
+    return bf16_lo(uint32_t(__ldg(args.gelu_table + bits)));
+}
+
 // 32 gate + 32 up accumulator columns of one token -> 32 hidden values
 // h = bf16(bf16(gelu(gate)) * up), stored as bf16, e4m3 or NVFP4 (fusion.cu:5-10, 31-107).
 template <int EPI>
 __device__ __forceinline__ void epilogue_geglu_chunk(const uint32_t (&gate_acc)[32], const uint32_t (&up_acc)[32],
-                                                     const KernelArgs& args, float scale, float scale_up,
-                                                     bool round_scale, float out_scale, float out_scale_rcp, bool true_div, int token,
+                                                     const KernelArgs& args, uint32_t compact_table, float scale,
+                                                     float scale_up, bool round_scale, float out_scale, float out_scale_rcp, bool true_div, int token,
                                                      int feature0) {
     float h[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
         const float gate = gemm_value(gate_acc[i], scale, round_scale);
         const float up = gemm_value(up_acc[i], scale_up, round_scale);
-        const float gelu = bf16_lo(uint32_t(__ldg(args.gelu_table + (__float_as_uint(gate) >> 16))));
+        const float gelu = gelu_lookup(gate, args, compact_table);
         h[i] = round_to_bf16(__fmul_rn(gelu, up));
     }
     if (token >= args.tokens || feature0 >= args.features) return;
@@ -227,6 +250,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     const uint32_t acc_full_bar = barrier_base + 16 * MAX_STAGES; // [2]
     const uint32_t acc_empty_bar = acc_full_bar + 16;             // [2]
     const uint32_t tmem_slot = acc_empty_bar + 16;
+    const uint32_t compact_table = tmem_slot + 16;                // 2 * (gelu_hi - gelu_lo) bf16 entries
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -247,6 +271,13 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLUMNS);
         tmem_relinquish();
+    }
+    if (GEGLU) {
+        const int span = args.gelu_hi - args.gelu_lo;
+        for (int i = threadIdx.x; i < 2 * span; i += GEMM_THREADS) {
+            const int code = i < span ? args.gelu_lo + i : 0x8000 + args.gelu_lo + (i - span);
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(compact_table + 2u * uint32_t(i)), "h"(__ldg(args.gelu_table + code)) : "memory");
+        }
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -444,7 +475,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     uint32_t second[32];
                     tmem_load_32x32(lane_address + BN / 2 + chunk * 32, second);
                     tmem_load_wait();
-                    epilogue_geglu_chunk<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, scale, scale_up, round_scale, out_scale,
+                    epilogue_geglu_chunk<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, compact_table, scale, scale_up, round_scale, out_scale,
                                                                       out_scale_rcp, true_div, token, f0 + chunk * 32);
                 } else {
                     tmem_load_wait();
@@ -627,7 +658,13 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
 
     const int stage_bytes = A_TILE_BYTES + args.tile_n * STAGE_K_BYTES;
     const int scale_stage_bytes = nvfp4 ? SCALE_STAGE_BYTES : 0;
-    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 64;
+    args.gelu_lo = args.gelu_hi = 0;
+    if (geglu && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
+        d->gelu_hi - d->gelu_lo <= MAX_COMPACT_GELU) {
+        args.gelu_lo = d->gelu_lo;
+        args.gelu_hi = d->gelu_hi;
+    }
+    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 64 + 4 * (args.gelu_hi - args.gelu_lo);
     int stages = (SMEM_LIMIT - fixed_bytes) / (stage_bytes + scale_stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) return B2_E_UNSUPPORTED;

@@ -39,6 +39,21 @@ def _require_cuda(*tensors: torch.Tensor | None) -> torch.device:
     return device
 
 
+def gelu_table_range(table: torch.Tensor) -> tuple[int, int]:
+    """Magnitude-code range of a GELU table that the fused epilogue must keep in shared memory
+    (``b2_gelu_table_range``); ``(0, 0)`` when the table has no closed-form tails.  Copies the table
+    to the host: call it once per table, outside graph capture."""
+    host = table.detach().to("cpu").contiguous().view(torch.uint16)
+    if host.numel() != 65536:
+        raise ValueError("a GELU table has 65536 entries")
+    lo, hi = ctypes.c_int32(0), ctypes.c_int32(0)
+    status = N.load().b2_gelu_table_range(host.data_ptr(), ctypes.byref(lo), ctypes.byref(hi))
+    if status == N.E_UNSUPPORTED:
+        return (0, 0)
+    N.check(status, "b2_gelu_table_range")
+    return (lo.value, hi.value)
+
+
 def new_scale_scratch(device: torch.device) -> torch.Tensor:
     """Zeroed scratch for :func:`tensor_scale`; allocate once per plan, outside graph capture."""
     return torch.zeros(N.SCALE_SCRATCH_BYTES // 4, device=device, dtype=torch.int32)
@@ -172,6 +187,7 @@ def linear(
     status: torch.Tensor | None = None,
     flags: int = 0,
     feature_tile: int = 0,
+    gelu_range: tuple[int, int] = (0, 0),
 ) -> None:
     """One fused tensor-core launch, see ``b2_linear``."""
     device = _require_cuda(
@@ -187,6 +203,8 @@ def linear(
         features=features,
         width=width,
         feature_tile=feature_tile,
+        gelu_lo=gelu_range[0],
+        gelu_hi=gelu_range[1],
         act=act.data_ptr(),
         act_scales=_ptr(act_scales),
         act_scale=act_scale.data_ptr(),

@@ -118,6 +118,8 @@ typedef struct b2_linear_desc {
     int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
     int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */
     int32_t feature_tile; /* output features per tile: 0 = choose; LINEAR 64/128/192/256, GEGLU 64/128 */
+    int32_t gelu_lo;      /* GEGLU: range of bf16 magnitude codes from b2_gelu_table_range, or 0, 0 */
+    int32_t gelu_hi;
     const void* act;           /* e4m3 [M, K] or packed e2m1 [M, K/2] */
     const void* act_scales;    /* NVFP4: block scales of act in 128x4-tile order */
     const void* act_scale;     /* device fp32: per-tensor scale (FP8) or global scale (NVFP4) */
@@ -135,6 +137,17 @@ typedef struct b2_linear_desc {
     void* out_blocked;         /* B2_OUT_NVFP4: block scales in 128x4-tile order (padding zeroed by caller) */
     void* status;              /* device uint32 or NULL: set nonzero if a bounded device-side wait expired */
 } b2_linear_desc;
+
+/* Which part of a GELU table needs to be looked up.  `host_table` is a HOST copy of the uint16[65536]
+ * table.  On success *lo and *hi bound the bf16 magnitude codes [lo, hi) outside which the table
+ * provably equals a closed form for every finite normal input: bf16(x/2) below lo; x (positive) or -0
+ * (negative) from hi upward.  b2_linear then keeps only [lo, hi) of the table, for both signs, in shared
+ * memory and evaluates the closed forms elsewhere, which is bit-identical to indexing the full table.
+ * Returns B2_E_UNSUPPORTED (and 0, 0) when the table has no such structure or the range is wider than
+ * 4096 codes; b2_linear then reads the full table from global memory.  The tanh-approximated GELU has
+ * lo = 0x3b4b, hi = 0x40a2 (|x| in [3.1e-3, 5.06)).  Host-only; no reference counterpart (the reference
+ * always gathers from the 128 KiB table, fusion.cu:5-10). */
+int b2_gelu_table_range(const void* host_table, int32_t* lo, int32_t* hi);
 
 /* One launch: TMA-staged operands, tcgen05 MMA into TMEM, fused epilogue.
  * LINEAR needs N % 8 == 0; GEGLU needs N % 16 == 0 (N % 128 == 0 for NVFP4 operands).

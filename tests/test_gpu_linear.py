@@ -191,3 +191,39 @@ def test_rejections(device):
     with pytest.raises(ValueError, match="no CPU fallback"):
         K.linear(kind=N.KIND_FP8, epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=8, features=16, width=64, act=x.cpu(),
                  act_scale=one, weight=w, weight_scale=one, out=out)
+
+
+@pytest.mark.parametrize("std", (1e-4, 0.02, 0.5))
+def test_compact_gelu_table_matches_full_table(device, std):
+    """Keeping only the non-trivial part of the GELU table in shared memory (b2_gelu_table_range)
+    gives the same bits as gathering from the full table, for tiny, ordinary and huge gate values."""
+    tokens, features, width = 200, 256, 512
+    x = bits(make_input((tokens, width), 3))
+    w = bits(make_weight((2 * features, width), 4, std=std).to(torch.bfloat16))
+    aq, a_s = O.fp8_quantize_C(x)
+    wq, w_s = O.fp8_quantize_C(w)
+    table_host = gelu_table_cpu("tanh")
+    table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+    table_range = K.gelu_table_range(table)
+    assert table_range == (0x3B4B, 0x40A2)
+    scalar = lambda v: torch.tensor(float(v), device=device)
+    common = dict(kind=N.KIND_FP8, epilogue=N.EPI_GEGLU, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width,
+                  act=torch.from_numpy(aq).to(device), act_scale=scalar(a_s), weight=torch.from_numpy(wq).to(device),
+                  weight_scale=scalar(w_s), gelu_table=table)
+    full = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+    compact = torch.empty_like(full)
+    K.linear(out=full, **common)
+    K.linear(out=compact, gelu_range=table_range, **common)
+    assert torch.equal(full.view(torch.int16), compact.view(torch.int16))
+    gate = O.bf16_to_f32(O.fp8_linear(aq, a_s, wq[:features], w_s))
+    magnitudes = (O.f32_to_bf16(gate) & 0x7FFF)
+    if std == 1e-4:
+        assert (magnitudes < 0x3B4B).mean() > 0.5       # the x/2 tail is exercised
+    if std == 0.5:
+        assert (magnitudes >= 0x40A2).mean() > 0.2      # the identity / -0 tail is exercised
+
+
+def test_gelu_table_range_rejects_unstructured_tables(device):
+    generator = torch.Generator().manual_seed(0)
+    noise = torch.randint(0, 65535, (65536,), generator=generator, dtype=torch.int32).to(torch.uint16)
+    assert K.gelu_table_range(noise) == (0, 0)
