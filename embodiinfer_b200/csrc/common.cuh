@@ -73,14 +73,40 @@ __device__ __forceinline__ float clamp_keep_nan(float value, float bound) {
     return value > bound ? bound : (value < -bound ? -bound : value);
 }
 
+// ---- exact division by a repeated divisor --------------------------------------
+// The reference divides in fp32 (x / scale, x / (g * s_block)); bit-exact codes need the correctly
+// rounded quotient.  For a divisor used many times the quotient is rebuilt from the correctly rounded
+// reciprocal y = RN(1/b) with one residual step (Markstein): q = RN(a*y), r = a - b*q (exact in an FMA),
+// RN(q + r*y) = RN(a/b).  The step is not guaranteed when b's significand is all ones or when the
+// residual can underflow/overflow, so those divisors (and non-finite or huge dividends) take the IEEE
+// division instead; a zero product keeps its sign, as a true division would.
+struct ExactDivider {
+    float divisor, reciprocal;
+    bool fast;
+    __device__ __forceinline__ explicit ExactDivider(float b) : divisor(b) {
+        const uint32_t bits = __float_as_uint(b);
+        const uint32_t exponent = (bits >> 23) & 0xffu;
+        fast = (bits >> 31) == 0 && exponent >= 67u && exponent <= 187u && (bits & 0x7fffffu) != 0x7fffffu;
+        reciprocal = fast ? __frcp_rn(b) : 0.0f;
+    }
+    __device__ __forceinline__ float operator()(float a) const {
+        if (fast && fabsf(a) < 1.0e30f) {
+            const float q = __fmul_rn(a, reciprocal);
+            if (q == 0.0f) return q;
+            return __fmaf_rn(__fmaf_rn(-q, divisor, a), reciprocal, q);
+        }
+        return __fdiv_rn(a, divisor);
+    }
+};
+
 // ---- FP8 -------------------------------------------------------------------
 
 // Four values -> four e4m3 bytes (first value in the low byte).
 //   spec C: fp32 quotient (quantize.cu:62-64).
 //   spec T: quotient rounded to bf16, clamped to +-448 (fp8.py:72).
 template <bool SPEC_C>
-__device__ __forceinline__ uint32_t encode_fp8x4(float a, float b, float c, float d, float scale) {
-    float q[4] = {__fdiv_rn(a, scale), __fdiv_rn(b, scale), __fdiv_rn(c, scale), __fdiv_rn(d, scale)};
+__device__ __forceinline__ uint32_t encode_fp8x4(float a, float b, float c, float d, const ExactDivider& scale) {
+    float q[4] = {scale(a), scale(b), scale(c), scale(d)};
     if (!SPEC_C) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) q[i] = clamp_keep_nan(round_to_bf16(q[i]), 448.0f);
@@ -102,15 +128,16 @@ __device__ __forceinline__ uint32_t pack_fp8x4(float a, float b, float c, float 
 // e4m3 scale of one 16-element block.
 //   spec C: e4m3(min(448, max/(6*g)))                      quantize.cu:85-86
 //   spec T: e4m3(clamp(max/6/g, tiny, 448))                nvfp4.py:40
+//   `by_global` divides by 6*g (spec C) or by g (spec T).
 template <bool SPEC_C>
-__device__ __forceinline__ uint8_t nvfp4_block_scale(float block_max, float global, int flags) {
+__device__ __forceinline__ uint8_t nvfp4_block_scale(float block_max, const ExactDivider& by_global, int flags) {
     float raw;
     if (SPEC_C) {
-        raw = fminf(448.0f, __fdiv_rn(block_max, __fmul_rn(6.0f, global)));
+        raw = fminf(448.0f, by_global(block_max));
     } else {
         const float sixth = (flags & B2_SCALAR_RCP) ? __fmul_rn(block_max, __fdiv_rn(1.0f, 6.0f))
                                                     : __fdiv_rn(block_max, 6.0f);
-        raw = __fdiv_rn(sixth, global);
+        raw = by_global(sixth);
         raw = raw < FLT_MIN ? FLT_MIN : (raw > 448.0f ? 448.0f : raw);
     }
     return uint8_t(__nv_cvt_float_to_fp8(raw, __NV_SATFINITE, __NV_E4M3));
@@ -129,21 +156,21 @@ __device__ __forceinline__ uint32_t e2m1_bucketize(float value) {
 //   spec C: x/den (0 when den == 0), hardware round-to-nearest-even e2m1   quantize.cu:91-95
 //   spec T: clamp(x/den, +-6) then bucketize                               nvfp4.py:41-44
 template <bool SPEC_C>
-__device__ __forceinline__ uint32_t nvfp4_encode_x8(const float (&v)[8], float denominator) {
+__device__ __forceinline__ uint32_t nvfp4_encode_x8(const float (&v)[8], const ExactDivider& denominator) {
     uint32_t word = 0;
     if (SPEC_C) {
-        const bool positive = denominator > 0.0f;
+        const bool positive = denominator.divisor > 0.0f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float first = positive ? __fdiv_rn(v[2 * i], denominator) : 0.0f;
-            const float second = positive ? __fdiv_rn(v[2 * i + 1], denominator) : 0.0f;
+            const float first = positive ? denominator(v[2 * i]) : 0.0f;
+            const float second = positive ? denominator(v[2 * i + 1]) : 0.0f;
             const uint32_t byte = __nv_cvt_float2_to_fp4x2(make_float2(first, second), __NV_E2M1, cudaRoundNearest);
             word |= (byte & 0xffu) << (8 * i);
         }
     } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float normalized = clamp_keep_nan(__fdiv_rn(v[i], denominator), 6.0f);
+            const float normalized = clamp_keep_nan(denominator(v[i]), 6.0f);
             word |= e2m1_bucketize(normalized) << (4 * i);
         }
     }

@@ -42,6 +42,7 @@ geglu_vector_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16*
         reciprocal = __fdiv_rn(1.0f, scale);
     }
     const bool true_div = (flags & B2_GEGLU_TRUE_DIV) != 0;
+    const ExactDivider divide(scale);
     const bool has_up = up != nullptr;
     const int64_t stride = int64_t(gridDim.x) * GEGLU_THREADS;
     for (int64_t index = int64_t(blockIdx.x) * GEGLU_THREADS + threadIdx.x; index < total; index += stride) {
@@ -61,7 +62,7 @@ geglu_vector_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16*
             static_cast<uint4*>(output)[index] = out;
         } else {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) h[i] = true_div ? __fdiv_rn(h[i], scale) : __fmul_rn(h[i], reciprocal);
+            for (int i = 0; i < 8; ++i) h[i] = true_div ? divide(h[i]) : __fmul_rn(h[i], reciprocal);
             uint2 out;
             out.x = pack_fp8x4(h[0], h[1], h[2], h[3]);
             out.y = pack_fp8x4(h[4], h[5], h[6], h[7]);
@@ -105,6 +106,7 @@ geglu_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* 
     const int column_tiles = (blocks_per_row + 3) >> 2;
     const int64_t total = int64_t(rows) * vectors_per_row;
     const float global = __ldg(global_pointer);
+    const ExactDivider by_global(__fmul_rn(6.0f, global));
     const bool has_up = up != nullptr;
     const int lane = threadIdx.x & 31;
     const int64_t stride = int64_t(gridDim.x) * GEGLU_THREADS;
@@ -125,8 +127,8 @@ geglu_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* 
 #pragma unroll
         for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, fabsf(h[i]));
         maximum = fmaxf(maximum, __shfl_xor_sync(mask, maximum, 1));
-        const uint8_t scale_code = nvfp4_block_scale<true>(maximum, global, 0);
-        const float denominator = __fmul_rn(global, e4m3_to_float(scale_code));
+        const uint8_t scale_code = nvfp4_block_scale<true>(maximum, by_global, 0);
+        const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
         output[index] = nvfp4_encode_x8<true>(h, denominator);
         if ((vector & 1) == 0) {
             const int block = vector >> 1;

@@ -163,7 +163,8 @@ __device__ __forceinline__ float gelu_lookup(float gate, const KernelArgs& args,
 template <int EPI>
 __device__ __forceinline__ void epilogue_geglu_chunk(const uint32_t (&gate_acc)[32], const uint32_t (&up_acc)[32],
                                                      const KernelArgs& args, uint32_t compact_table, float scale,
-                                                     float scale_up, bool round_scale, float out_scale, float out_scale_rcp, bool true_div, int token,
+                                                     float scale_up, bool round_scale, const ExactDivider& out_scale,
+                                                     const ExactDivider& by_global, float out_scale_rcp, bool true_div, int token,
                                                      int feature0) {
     float h[32];
 #pragma unroll
@@ -184,7 +185,7 @@ __device__ __forceinline__ void epilogue_geglu_chunk(const uint32_t (&gate_acc)[
                          pack_bf16x2(h[8 * v + 4], h[8 * v + 5]), pack_bf16x2(h[8 * v + 6], h[8 * v + 7]));
     } else if (EPI == EPI_GEGLU_FP8) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) h[i] = true_div ? __fdiv_rn(h[i], out_scale) : __fmul_rn(h[i], out_scale_rcp);
+        for (int i = 0; i < 32; ++i) h[i] = true_div ? out_scale(h[i]) : __fmul_rn(h[i], out_scale_rcp);
         uint8_t* out = static_cast<uint8_t*>(args.out) + element;
 #pragma unroll
         for (int v = 0; v < 2; ++v)
@@ -202,8 +203,8 @@ __device__ __forceinline__ void epilogue_geglu_chunk(const uint32_t (&gate_acc)[
             float block_max = fabsf(h[16 * block]);
 #pragma unroll
             for (int i = 1; i < 16; ++i) block_max = fmaxf(block_max, fabsf(h[16 * block + i]));
-            const uint8_t code = nvfp4_block_scale<true>(block_max, out_scale, 0);
-            const float denominator = __fmul_rn(out_scale, e4m3_to_float(code));
+            const uint8_t code = nvfp4_block_scale<true>(block_max, by_global, 0);
+            const ExactDivider denominator(__fmul_rn(out_scale.divisor, e4m3_to_float(code)));
             scale_codes |= uint32_t(code) << (8 * block);
             float low[8], high[8];
 #pragma unroll
@@ -448,11 +449,13 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             scale_up = __fmul_rn(__ldg(args.act_scale), __ldg(args.weight_scale_up));
             if (round_scale) scale_up = round_to_bf16(scale_up);
         }
-        float out_scale = 1.0f, out_scale_rcp = 1.0f;
+        float out_scale_value = 1.0f, out_scale_rcp = 1.0f;
         if (EPI == EPI_GEGLU_FP8 || EPI == EPI_GEGLU_NVFP4) {
-            out_scale = __ldg(args.out_scale);
-            out_scale_rcp = __fdiv_rn(1.0f, out_scale);
+            out_scale_value = __ldg(args.out_scale);
+            out_scale_rcp = __fdiv_rn(1.0f, out_scale_value);
         }
+        const ExactDivider out_scale(out_scale_value);
+        const ExactDivider by_global(__fmul_rn(6.0f, out_scale_value));
         const bool true_div = (args.flags & B2_GEGLU_TRUE_DIV) != 0;
         const int chunks = features_per_tile / 32;             // 32-feature chunks in the tile
         const int chunk_begin = half == 0 ? 0 : (chunks + 1) / 2;
@@ -468,7 +471,8 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             mbar_wait(acc_full_bar + 8 * buffer, use & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
             tc_fence_after_sync();
             const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer) * 256u;
-            for (int chunk = chunk_begin; chunk < chunk_end; ++chunk) {
+            const bool warp_has_tokens = m_tile * TILE_TOKENS + quarter * 32 < args.tokens;   // else: padding rows only
+            for (int chunk = chunk_begin; chunk < chunk_end && warp_has_tokens; ++chunk) {
                 uint32_t first[32];
                 tmem_load_32x32(lane_address + chunk * 32, first);
                 if (GEGLU) {
@@ -476,7 +480,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     tmem_load_32x32(lane_address + BN / 2 + chunk * 32, second);
                     tmem_load_wait();
                     epilogue_geglu_chunk<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, compact_table, scale, scale_up, round_scale, out_scale,
-                                                                      out_scale_rcp, true_div, token, f0 + chunk * 32);
+                                                                      by_global, out_scale_rcp, true_div, token, f0 + chunk * 32);
                 } else {
                     tmem_load_wait();
                     epilogue_linear_chunk(first, args, scale, round_scale, token, f0 + chunk * 32);

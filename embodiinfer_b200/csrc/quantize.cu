@@ -68,8 +68,9 @@ __global__ void __launch_bounds__(QUANT_THREADS)
 fp8_encode_kernel(const uint4* __restrict__ input, uint2* __restrict__ output, int64_t vectors,
                   const __nv_bfloat16* __restrict__ tail_in, uint8_t* __restrict__ tail_out, int tail_count,
                   const float* __restrict__ scale_pointer, int flags) {
-    float scale = __ldg(scale_pointer);
-    if (!SPEC_C && (flags & B2_DIVISOR_BF16)) scale = __bfloat162float(__float2bfloat16(scale));
+    float scale_value = __ldg(scale_pointer);
+    if (!SPEC_C && (flags & B2_DIVISOR_BF16)) scale_value = __bfloat162float(__float2bfloat16(scale_value));
+    const ExactDivider scale(scale_value);
     const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
     for (int64_t index = int64_t(blockIdx.x) * QUANT_THREADS + threadIdx.x; index < vectors; index += stride) {
         const uint4 packed = ld_nc_u4(input + index);
@@ -102,6 +103,7 @@ nvfp4_encode_kernel(const uint4* __restrict__ input, uint32_t* __restrict__ outp
     const int column_tiles = (blocks_per_row + 3) >> 2;
     const int64_t total = int64_t(rows) * vectors_per_row;
     const float global = __ldg(global_pointer);
+    const ExactDivider by_global(SPEC_C ? __fmul_rn(6.0f, global) : global);
     const bool whole_words = (blocks_per_row & 3) == 0;
     const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
     // The loop condition is uniform per warp.  `total` is a multiple of 2 (a row holds whole
@@ -119,8 +121,8 @@ nvfp4_encode_kernel(const uint4* __restrict__ input, uint32_t* __restrict__ outp
         unpack_bf16x8(packed, v);
         float maximum = abs_max_bf16x8(packed);
         maximum = fmaxf(maximum, __shfl_xor_sync(mask, maximum, 1));
-        const uint8_t scale_code = nvfp4_block_scale<SPEC_C>(maximum, global, flags);
-        const float denominator = global * e4m3_to_float(scale_code);
+        const uint8_t scale_code = nvfp4_block_scale<SPEC_C>(maximum, by_global, flags);
+        const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
         output[index] = nvfp4_encode_x8<SPEC_C>(v, denominator);
         const int row = int(index / vectors_per_row);
         const int vector = int(index - int64_t(row) * vectors_per_row);

@@ -186,3 +186,33 @@ def test_large_tensor_properties(device):
     assert torch.equal(slab, full[1120:1680])
     want = O.fp8_quantize_C(bits(x[:64]), np.float32(scale.item()))[0]
     assert np.array_equal(u8(full[:64]), want)
+
+
+def test_division_by_repeated_divisor_is_correctly_rounded(device):
+    """The encoders divide by a per-tensor / per-block constant through a reciprocal + one residual step;
+    the codes must equal those of a true fp32 division for every bf16 dividend and for ordinary,
+    extreme and all-ones-significand divisors."""
+    rng = np.random.default_rng(5)
+    codes = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    finite = np.isfinite(O.bf16_to_f32(codes))
+    xb = codes[finite][: (finite.sum() // 64) * 64].reshape(-1, 64)
+    xd = torch.from_numpy(xb.copy()).view(torch.bfloat16).to(device)
+    mantissas = rng.integers(0, 1 << 23, size=160, dtype=np.uint32)
+    exponents = rng.integers(100, 150, size=160, dtype=np.uint32)
+    scales = ((exponents << 23) | mantissas).view(np.float32).tolist()
+    scales += [np.uint32(0x3F7FFFFF).view(np.float32).item(), np.uint32(0x3EFFFFFF).view(np.float32).item(),   # all ones
+               1e-30, 1e30, 3.0e-39, 1.0, 0.5, 3.0, 7.0 / 448.0, float(np.float32(1.0) / np.float32(3.0))]
+    out = torch.empty(xb.shape, device=device, dtype=torch.uint8)
+    for value in scales:
+        scale_value = np.float32(value)
+        K.fp8_quantize(xd, out, torch.tensor(float(scale_value), device=device), N.SPEC_C)
+        want = O.fp8_quantize_C(xb, scale_value)[0]
+        assert np.array_equal(u8(out), want), f"scale {float(scale_value)!r}"
+    rows, columns = xb.shape
+    packed = torch.empty((rows, columns // 2), device=device, dtype=torch.uint8)
+    linear = torch.empty((rows, columns // 16), device=device, dtype=torch.uint8)
+    for value in scales[:24] + scales[-10:-5]:
+        g_value = np.float32(value)
+        K.nvfp4_quantize(xd, packed, linear, None, torch.tensor(float(g_value), device=device), N.SPEC_C)
+        want = O.nvfp4_quantize_C(xb, g_value)
+        assert np.array_equal(u8(linear), want[1]) and np.array_equal(u8(packed), want[0]), f"global {float(g_value)!r}"
