@@ -1,0 +1,232 @@
+"""A random-init policy with the shapes of the reference's pi0.5 stack, for rollout measurements.
+
+Not a port of ``Pi05Policy``: no checkpoint, tokenizer or processor.  It strings together the layer
+equations the reference runs (embodiinfer/policies/pi05/modeling_pi05.py:924-1168: pre-norm Gemma
+blocks with a packed QKV projection, RoPE, grouped-query attention, gated GELU-tanh MLP; a SigLIP
+vision tower; a 10-step flow-matching action expert that attends to the prefix keys/values and is
+advanced by ``x += dt * v``, embodiinfer/models/schedulers/flow.py:21-23) at the widths the reference
+guards for (operators.py:99-107, vision.py:276-601), with every q/k/v/o/gate/up/down/fc projection a
+quantised ``FP8Linear`` / ``NVFP4Linear`` bundle dispatched through the registry to the sm_100a
+kernels.  Norms, RoPE, softmax attention and the tiny action in/out projections are plain bf16 tensor
+operations: they are not the quantised Linear this package is about.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .bundles import pack_quantized_linears, quantize_linear
+from .layers.linear import parse_quantization_config
+
+
+@dataclass(frozen=True)
+class TowerShape:
+    width: int
+    mlp: int
+    layers: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+
+
+GEMMA_2B = TowerShape(2048, 16384, 18, 8, 1, 256)
+GEMMA_300M = TowerShape(1024, 4096, 18, 8, 1, 256)
+SIGLIP_SO400M = TowerShape(1152, 4304, 27, 16, 16, 72)
+IMAGE_SIZE, PATCH, CAMERAS, TEXT_TOKENS, VOCAB = 224, 14, 2, 48, 257152
+ACTION_HORIZON, ACTION_DIM, DENOISE_STEPS = 10, 32, 10
+
+
+def _random_linear(out_features: int, in_features: int, generator: torch.Generator, device, bias: bool = False) -> nn.Linear:
+    layer = nn.Linear(in_features, out_features, bias=bias, device=device, dtype=torch.bfloat16)
+    with torch.no_grad():
+        layer.weight.copy_(0.02 * torch.randn((out_features, in_features), generator=generator, device=device))
+        if bias:
+            layer.bias.zero_()
+    return layer
+
+
+def _quantized(layers: tuple[nn.Linear, ...], config):
+    members = tuple(quantize_linear(layer, config) for layer in layers)
+    return members[0] if len(members) == 1 else pack_quantized_linears(members)
+
+
+def _rms_norm(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    values = x.float()
+    values = values * torch.rsqrt(values.pow(2).mean(-1, keepdim=True) + 1e-6)
+    return (values * (1.0 + weight.float())).to(x.dtype)
+
+
+def _rope(x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    """x [B, H, T, D]; rotary embedding with theta 1e4 over the last dimension."""
+    half = x.shape[-1] // 2
+    frequency = torch.exp(-math.log(10000.0) * torch.arange(half, device=x.device, dtype=torch.float32) / half)
+    angles = positions.float()[:, None] * frequency[None, :]
+    cos, sin = angles.cos()[None, None], angles.sin()[None, None]
+    first, second = x.float()[..., :half], x.float()[..., half:]
+    return torch.cat((first * cos - second * sin, second * cos + first * sin), dim=-1).to(x.dtype)
+
+
+class GemmaBlock(nn.Module):
+    """Pre-norm block; ``prefix_kv`` lets the action expert attend to the prefix tower's keys/values."""
+
+    def __init__(self, shape: TowerShape, attention_width: int, config, generator, device) -> None:
+        super().__init__()
+        self.shape = shape
+        q_dim, kv_dim = shape.heads * shape.head_dim, shape.kv_heads * shape.head_dim
+        make = lambda n, k: _random_linear(n, k, generator, device)
+        self.qkv = _quantized((make(q_dim, shape.width), make(kv_dim, shape.width), make(kv_dim, shape.width)), config)
+        self.o_proj = _quantized((make(shape.width, attention_width),), config)
+        self.gate_up = _quantized((make(shape.mlp, shape.width), make(shape.mlp, shape.width)), config)
+        self.down = _quantized((make(shape.width, shape.mlp),), config)
+        self.input_norm = nn.Parameter(torch.zeros(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.post_norm = nn.Parameter(torch.zeros(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
+
+    def forward(self, x, positions, prefix_kv=None):
+        shape = self.shape
+        batch, tokens, _ = x.shape
+        qkv = self.qkv(_rms_norm(x, self.input_norm))
+        q_dim, kv_dim = shape.heads * shape.head_dim, shape.kv_heads * shape.head_dim
+        q, k, v = qkv.split((q_dim, kv_dim, kv_dim), dim=-1)
+        q = _rope(q.view(batch, tokens, shape.heads, shape.head_dim).transpose(1, 2), positions)
+        k = _rope(k.view(batch, tokens, shape.kv_heads, shape.head_dim).transpose(1, 2), positions)
+        v = v.view(batch, tokens, shape.kv_heads, shape.head_dim).transpose(1, 2)
+        own_kv = (k, v)
+        if prefix_kv is not None:
+            k, v = torch.cat((prefix_kv[0], k), dim=2), torch.cat((prefix_kv[1], v), dim=2)
+        attended = F.scaled_dot_product_attention(q, k, v, enable_gqa=shape.heads != shape.kv_heads)
+        x = x + self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim))
+        gate, up = self.gate_up(_rms_norm(x, self.post_norm)).chunk(2, dim=-1)
+        return x + self.down(F.gelu(gate, approximate="tanh") * up), own_kv
+
+
+class SiglipBlock(nn.Module):
+    def __init__(self, shape: TowerShape, config, generator, device) -> None:
+        super().__init__()
+        self.shape = shape
+        make = lambda n, k: _random_linear(n, k, generator, device, bias=True)
+        width = shape.width
+        self.qkv = _quantized((make(3 * width, width),), config)
+        self.out = _quantized((make(width, width),), config)
+        self.fc1 = _quantized((make(shape.mlp, width),), config)
+        self.fc2 = _quantized((make(width, shape.mlp),), config)
+        self.norm1 = nn.LayerNorm(width, eps=1e-6, device=device, dtype=torch.bfloat16)
+        self.norm2 = nn.LayerNorm(width, eps=1e-6, device=device, dtype=torch.bfloat16)
+
+    def forward(self, x):
+        batch, tokens, width = x.shape
+        heads, head_dim = self.shape.heads, self.shape.head_dim
+        q, k, v = self.qkv(self.norm1(x)).view(batch, tokens, 3, heads, head_dim).permute(2, 0, 3, 1, 4)
+        x = x + self.out(F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(batch, tokens, width))
+        return x + self.fc2(F.gelu(self.fc1(self.norm2(x)), approximate="tanh"))
+
+
+class Pi05ShapedPolicy(nn.Module):
+    """uint8 camera frames + text tokens -> [B, 10, 32] action chunk.
+
+    ``layer_scale`` < 1 shortens every tower (tests use 2 layers); widths never change, so every
+    quantised projection runs at its real shape.
+    """
+
+    def __init__(self, quantization="fp8", *, device="cuda", seed: int = 1005, layer_scale: float = 1.0,
+                 vocabulary: int = VOCAB) -> None:
+        super().__init__()
+        device = torch.device(device)
+        config = parse_quantization_config(quantization)
+        generator = torch.Generator(device=device).manual_seed(seed)
+        depth = lambda shape: max(1, round(shape.layers * layer_scale))
+        self.vision = nn.ModuleList(SiglipBlock(SIGLIP_SO400M, config, generator, device) for _ in range(depth(SIGLIP_SO400M)))
+        self.prefix = nn.ModuleList(
+            GemmaBlock(GEMMA_2B, GEMMA_2B.heads * GEMMA_2B.head_dim, config, generator, device) for _ in range(depth(GEMMA_2B))
+        )
+        self.expert = nn.ModuleList(
+            GemmaBlock(GEMMA_300M, GEMMA_300M.heads * GEMMA_300M.head_dim, config, generator, device)
+            for _ in range(min(depth(GEMMA_300M), len(self.prefix)))
+        )
+        patches = (IMAGE_SIZE // PATCH) ** 2
+        rand = lambda *shape: nn.Parameter(0.02 * torch.randn(shape, generator=generator, device=device).to(torch.bfloat16), requires_grad=False)
+        self.patch_weight, self.patch_bias = rand(SIGLIP_SO400M.width, 3 * PATCH * PATCH), rand(SIGLIP_SO400M.width)
+        self.position = rand(patches, SIGLIP_SO400M.width)
+        self.vision_norm = nn.LayerNorm(SIGLIP_SO400M.width, eps=1e-6, device=device, dtype=torch.bfloat16)
+        self.projector = _quantized((_random_linear(GEMMA_2B.width, SIGLIP_SO400M.width, generator, device, bias=True),), config)
+        self.token_embedding = rand(vocabulary, GEMMA_2B.width)
+        self.action_in, self.action_out = rand(GEMMA_300M.width, ACTION_DIM), rand(ACTION_DIM, GEMMA_300M.width)
+        self.time_mlp = rand(GEMMA_300M.width, GEMMA_300M.width)
+        self.final_norm = nn.Parameter(torch.zeros(GEMMA_300M.width, device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.device_ = device
+        self.noise_seed = seed
+
+    # -- stages ----------------------------------------------------------------------------------
+    def embed_images(self, images: torch.Tensor) -> torch.Tensor:
+        """uint8 [B, cameras, H, W, 3] -> [B, cameras*256, 2048]; frames are scaled as (x/255)*2-1."""
+        batch, cameras = images.shape[:2]
+        frames = (images.to(self.device_, non_blocking=True).float() / 255.0) * 2.0 - 1.0
+        grid = IMAGE_SIZE // PATCH
+        tiles = frames.view(batch * cameras, grid, PATCH, grid, PATCH, 3).permute(0, 1, 3, 5, 2, 4)
+        tiles = tiles.reshape(batch * cameras, grid * grid, 3 * PATCH * PATCH).to(torch.bfloat16)
+        x = F.linear(tiles, self.patch_weight, self.patch_bias) + self.position
+        for block in self.vision:
+            x = block(x)
+        return self.projector(self.vision_norm(x)).view(batch, cameras * grid * grid, GEMMA_2B.width)
+
+    def encode_prefix(self, images: torch.Tensor, tokens: torch.Tensor):
+        text = self.token_embedding[tokens.to(self.device_)] * math.sqrt(GEMMA_2B.width)
+        x = torch.cat((self.embed_images(images), text.to(torch.bfloat16)), dim=1)
+        positions = torch.arange(x.shape[1], device=self.device_)
+        cache = []
+        for block in self.prefix:
+            x, kv = block(x, positions)
+            cache.append(kv)
+        return cache, x.shape[1]
+
+    def denoise(self, cache, prefix_length: int, batch: int, generator: torch.Generator | None = None) -> torch.Tensor:
+        actions = torch.randn((batch, ACTION_HORIZON, ACTION_DIM), device=self.device_, generator=generator)
+        positions = prefix_length + torch.arange(ACTION_HORIZON, device=self.device_)
+        dt = -1.0 / DENOISE_STEPS
+        half = GEMMA_300M.width // 2
+        frequency = torch.exp(-math.log(10000.0) * torch.arange(half, device=self.device_) / half)
+        for step in range(DENOISE_STEPS):
+            time = 1.0 + step * dt
+            angles = time * frequency
+            time_embedding = F.linear(torch.cat((angles.sin(), angles.cos())).to(torch.bfloat16), self.time_mlp)
+            x = F.linear(actions.to(torch.bfloat16), self.action_in) + time_embedding
+            for block, kv in zip(self.expert, cache):
+                x, _ = block(x, positions, prefix_kv=kv)
+            velocity = F.linear(_rms_norm(x, self.final_norm), self.action_out).float()
+            actions = actions + dt * velocity              # Euler step of the flow (flow.py:21-23)
+        return actions
+
+    @torch.no_grad()
+    def forward(self, observations: dict) -> torch.Tensor:
+        images, tokens = observations["images"], observations["tokens"]
+        cache, prefix_length = self.encode_prefix(images, tokens)
+        generator = torch.Generator(device=self.device_).manual_seed(self.noise_seed)
+        return self.denoise(cache, prefix_length, images.shape[0], generator)
+
+    def flops_per_observation(self) -> float:
+        """2*M*N*K over the quantised projections of one observation (attention and norms excluded)."""
+        def block(shape, tokens, attention_width):
+            q_dim, kv_dim = shape.heads * shape.head_dim, shape.kv_heads * shape.head_dim
+            per_token = shape.width * (q_dim + 2 * kv_dim) + attention_width * shape.width + 3 * shape.width * shape.mlp
+            return 2.0 * tokens * per_token
+        vision_tokens = CAMERAS * (IMAGE_SIZE // PATCH) ** 2
+        siglip = SIGLIP_SO400M
+        vision = len(self.vision) * 2.0 * vision_tokens * (4 * siglip.width * siglip.width + 2 * siglip.width * siglip.mlp)
+        vision += 2.0 * vision_tokens * siglip.width * GEMMA_2B.width
+        prefix = len(self.prefix) * block(GEMMA_2B, vision_tokens + TEXT_TOKENS, GEMMA_2B.heads * GEMMA_2B.head_dim)
+        expert = DENOISE_STEPS * len(self.expert) * block(GEMMA_300M, ACTION_HORIZON, GEMMA_300M.heads * GEMMA_300M.head_dim)
+        return vision + prefix + expert
+
+
+def synthetic_observations(count: int, seed: int = 1005, vocabulary: int = VOCAB) -> dict:
+    """Seeded stand-ins with the reference's observation shapes: two 224x224 uint8 RGB cameras ~U[0,255]
+    and 48 text tokens per observation (host tensors; the policy moves them to its device)."""
+    generator = torch.Generator().manual_seed(seed)
+    return {
+        "images": torch.randint(0, 256, (count, CAMERAS, IMAGE_SIZE, IMAGE_SIZE, 3), dtype=torch.uint8, generator=generator),
+        "tokens": torch.randint(0, vocabulary, (count, TEXT_TOKENS), generator=generator),
+    }

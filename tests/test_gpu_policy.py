@@ -1,0 +1,49 @@
+"""The pi0.5-shaped random-init stack on the GPU: every quantised projection at its real width, towers
+shortened to one layer.  Checker: the same stack with the registry kernels swapped for a composed
+"dequantised" route (the reference's torch-route expressions evaluated by torch on the device, fp32 GEMM),
+i.e. the W8A8 oracle composition applied layer by layer."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from embodiinfer_b200.layers import linear as registry
+from embodiinfer_b200.pi05_shaped import ACTION_DIM, ACTION_HORIZON, Pi05ShapedPolicy, synthetic_observations
+from embodiinfer_b200.rollout import DataParallelRollout
+
+pytestmark = pytest.mark.gpu
+
+
+def composed_fp8_linear(inputs, weight, weight_scale, bias=None):
+    """fp8.py:66-73 + 118-141 with torch ops: quantise, dequantise both operands, fp32 matmul, bf16, + bias."""
+    rows = inputs.reshape(-1, inputs.shape[-1])
+    peak = rows.float().abs().amax()
+    scale = torch.where(peak > 0, peak / 448.0, torch.ones_like(peak))
+    codes = (rows / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    product = (codes.float() @ weight.float().t()) * (scale * weight_scale)
+    output = product.to(torch.bfloat16)
+    if bias is not None:
+        output = output + bias
+    return output.reshape(*inputs.shape[:-1], weight.shape[0])
+
+
+def test_one_layer_policy_matches_composed_route(device, monkeypatch):
+    policy = Pi05ShapedPolicy("fp8", device=device, layer_scale=0.01, vocabulary=4096)
+    assert len(policy.vision) == len(policy.prefix) == len(policy.expert) == 1
+    observations = synthetic_observations(3, vocabulary=4096)
+    actions = policy(observations)
+    assert actions.shape == (3, ACTION_HORIZON, ACTION_DIM) and actions.dtype == torch.float32
+    assert torch.isfinite(actions).all()
+    assert torch.equal(actions, policy(observations)), "the rollout step must be deterministic"
+    native = registry._resolve("fp8_native")
+    monkeypatch.setitem(registry._REGISTRY, "fp8_native", (composed_fp8_linear, native[1]))
+    expected = policy(observations)
+    monkeypatch.setitem(registry._REGISTRY, "fp8_native", native)
+    # Ten Euler steps through requantising layers amplify single-ulp differences of the bf16 GEMM outputs;
+    # the per-Linear tolerance (1e-3) is checked in test_gpu_linear / test_gpu_plans.
+    error = (actions - expected).norm() / expected.norm()
+    assert error < 2e-2, float(error)
+    result = DataParallelRollout(policy, device=device).run(observations)
+    assert torch.equal(result.actions, actions) and result.owner_rank == [0, 0, 0]
+    assert policy.flops_per_observation() > 1e11
