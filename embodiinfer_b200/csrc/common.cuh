@@ -89,6 +89,12 @@ struct ExactDivider {
         fast = (bits >> 31) == 0 && exponent >= 67u && exponent <= 187u && (bits & 0x7fffffu) != 0x7fffffu;
         reciprocal = fast ? __frcp_rn(b) : 0.0f;
     }
+    // The residual step alone, for callers that have already established: `fast`, |a * reciprocal| finite.
+    // copysign restores the sign of a zero quotient (and changes nothing else: the divisor is positive).
+    __device__ __forceinline__ float unchecked(float a) const {
+        const float q = __fmul_rn(a, reciprocal);
+        return copysignf(__fmaf_rn(__fmaf_rn(-q, divisor, a), reciprocal, q), a);
+    }
     __device__ __forceinline__ float operator()(float a) const {
         if (fast && fabsf(a) < 1.0e30f) {
             const float q = __fmul_rn(a, reciprocal);
@@ -106,7 +112,17 @@ struct ExactDivider {
 //   spec T: quotient rounded to bf16, clamped to +-448 (fp8.py:72).
 template <bool SPEC_C>
 __device__ __forceinline__ uint32_t encode_fp8x4(float a, float b, float c, float d, const ExactDivider& scale) {
-    float q[4] = {scale(a), scale(b), scale(c), scale(d)};
+    float q[4];
+    if (scale.fast) {
+        // |x| >= 1024*scale saturates to +-448 whatever x is: clamping there keeps the product finite
+        // without changing a code (NaN fails the comparison and stays NaN).
+        const float bound = __fmul_rn(1024.0f, scale.divisor);
+        const float in[4] = {a, b, c, d};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = scale.unchecked(fabsf(in[i]) > bound ? copysignf(bound, in[i]) : in[i]);
+    } else {
+        q[0] = scale(a); q[1] = scale(b); q[2] = scale(c); q[3] = scale(d);
+    }
     if (!SPEC_C) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) q[i] = clamp_keep_nan(round_to_bf16(q[i]), 448.0f);
@@ -155,10 +171,20 @@ __device__ __forceinline__ uint32_t e2m1_bucketize(float value) {
 // Eight values of one half-block -> eight nibbles, first value in the lowest nibble.
 //   spec C: x/den (0 when den == 0), hardware round-to-nearest-even e2m1   quantize.cu:91-95
 //   spec T: clamp(x/den, +-6) then bucketize                               nvfp4.py:41-44
+//   `block_max` is the largest magnitude of the block the eight values belong to; when the divisor is
+//   in the divider's safe range and block_max/den is finite, all eight quotients take the short path.
 template <bool SPEC_C>
-__device__ __forceinline__ uint32_t nvfp4_encode_x8(const float (&v)[8], const ExactDivider& denominator) {
+__device__ __forceinline__ uint32_t nvfp4_encode_x8(const float (&v)[8], const ExactDivider& denominator, float block_max) {
     uint32_t word = 0;
-    if (SPEC_C) {
+    const bool short_path = denominator.fast && __fmul_rn(block_max, denominator.reciprocal) < 1.0e30f;
+    if (SPEC_C && short_path) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t byte = __nv_cvt_float2_to_fp4x2(
+                make_float2(denominator.unchecked(v[2 * i]), denominator.unchecked(v[2 * i + 1])), __NV_E2M1, cudaRoundNearest);
+            word |= (byte & 0xffu) << (8 * i);
+        }
+    } else if (SPEC_C) {
         const bool positive = denominator.divisor > 0.0f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -170,7 +196,7 @@ __device__ __forceinline__ uint32_t nvfp4_encode_x8(const float (&v)[8], const E
     } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float normalized = clamp_keep_nan(denominator(v[i]), 6.0f);
+            const float normalized = clamp_keep_nan(short_path ? denominator.unchecked(v[i]) : denominator(v[i]), 6.0f);
             word |= e2m1_bucketize(normalized) << (4 * i);
         }
     }

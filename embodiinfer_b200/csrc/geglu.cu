@@ -116,7 +116,7 @@ geglu_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* 
         const bool active = index < total;
         const unsigned int mask = __ballot_sync(0xffffffffu, active);
         if (!active) continue;
-        const int row = int(index / vectors_per_row);
+        const int row = total <= 0x7fffffff ? int(uint32_t(index) / uint32_t(vectors_per_row)) : int(index / vectors_per_row);
         const int vector = int(index - int64_t(row) * vectors_per_row);
         const int64_t offset = int64_t(row) * row_stride + int64_t(vector) * 8;
         const uint4 g = ld_nc_u4(reinterpret_cast<const uint4*>(gate + offset));
@@ -129,7 +129,7 @@ geglu_nvfp4_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* 
         maximum = fmaxf(maximum, __shfl_xor_sync(mask, maximum, 1));
         const uint8_t scale_code = nvfp4_block_scale<true>(maximum, by_global, 0);
         const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
-        output[index] = nvfp4_encode_x8<true>(h, denominator);
+        output[index] = nvfp4_encode_x8<true>(h, denominator, maximum);
         if ((vector & 1) == 0) {
             const int block = vector >> 1;
             if (blocked != nullptr) blocked[scale_tile_offset(row, block, column_tiles)] = scale_code;

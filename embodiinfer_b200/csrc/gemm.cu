@@ -34,8 +34,12 @@
 
 namespace b2 {
 
-constexpr int GEMM_THREADS = 320;
-constexpr int EPILOGUE_WARPS = 8;
+// Two service warps (TMA, MMA) plus the epilogue warps.  The plain Linear epilogue is a handful of
+// instructions per element and runs on 8 warps; the gated epilogue (GELU lookup, two roundings, block
+// scale, exact division, e2m1 packing) is latency-bound, so it gets 16 warps: four per TMEM lane
+// partition, each owning 16-feature units of the tile.
+__host__ __device__ constexpr int epilogue_warps(int epi) { return epi == 0 ? 8 : 16; }
+__host__ __device__ constexpr int gemm_threads(int epi) { return 64 + 32 * epilogue_warps(epi); }
 constexpr int TILE_TOKENS = 128;                   // MMA M
 constexpr int STAGE_K_BYTES = 128;                 // one swizzle row
 constexpr int A_TILE_BYTES = TILE_TOKENS * STAGE_K_BYTES;
@@ -44,8 +48,12 @@ constexpr int SCALE_ATOMS_PER_STAGE = 4;           // 4 x 64 elements = 256 e2m1
 constexpr int SCALE_STAGE_BYTES = 3 * SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;   // act + two weight row blocks
 constexpr int MAX_STAGES = 8;
 constexpr int TMEM_COLUMNS = 512;
-constexpr int TMEM_SFA = 448;                      // NVFP4: token scales, 4 columns per 64 elements of K
-constexpr int TMEM_SFB = 464;                      // NVFP4: feature scales, 8 columns per 64 elements of K
+// NVFP4 scale factors live in TMEM columns 384..479: two sets (alternating by K slice, so the copies for
+// one slice never overwrite columns an MMA of the previous slice may still be reading), each 16 columns
+// of token scales (4 per 64 elements of K) followed by 32 columns of feature scales (8 per 64 elements).
+constexpr int TMEM_SCALES = 384;
+constexpr int TMEM_SCALE_SET = 48;
+constexpr int TMEM_SFB_OFFSET = 16;
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int MAX_COMPACT_GELU = 4096;             // magnitude codes of the GELU table kept in shared memory
 constexpr int SMEM_MINIMUM = 120 * 1024;           // keeps a second CTA (and its TMEM request) off the SM
@@ -56,7 +64,7 @@ struct KernelArgs {
     int tokens, features, k_bytes, num_kb;
     int tile_n;                  // TMEM columns per tile (GEGLU: gate half + up half)
     int num_m_tiles, num_n_tiles, total_tiles;
-    int stages, accumulators;
+    int stages, accumulators, accumulator_stride;
     int up_row_offset;           // row of the first "up" feature in the packed weight
     int scale_column_tiles;      // 512-byte scale atoms per 128-row block
     int act_row_blocks, weight_row_blocks;
@@ -137,104 +145,97 @@ __device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32],
                      pack_bf16x2(y[8 * v + 4], y[8 * v + 5]), pack_bf16x2(y[8 * v + 6], y[8 * v + 7]));
 }
 
-// GELU of a bf16 value held in a float.  Magnitude codes [lo, hi) come from the shared-memory copy of
-// the table ([positive | negative] halves); below lo the table equals bf16(x/2), from hi up to the
-// largest finite value it equals x (positive) or -0 (negative) — the host verified both against the
-// table before choosing lo and hi.  Subnormals, infinities and NaNs read the full table in global memory.
-__device__ __forceinline__ float gelu_lookup(float gate, const KernelArgs& args, uint32_t compact_table) {
-    const uint32_t bits = __float_as_uint(gate) >> 16;
-    const uint32_t magnitude = bits & 0x7fffu;
-    const uint32_t span = uint32_t(args.gelu_hi - args.gelu_lo);
-    const uint32_t offset = magnitude - uint32_t(args.gelu_lo);
-    if (offset < span) {
-        uint32_t value;
-        asm volatile("ld.shared.u16 %0, [%1];" : "=r"(value) : "r"(compact_table + 2u * (offset + (bits >> 15) * span)));
-        return __uint_as_float(value << 16);
-    }
-    if (span != 0 && magnitude >= 0x80u && magnitude < 0x7f80u) {
-        if (magnitude < uint32_t(args.gelu_lo)) return round_to_bf16(__fmul_rn(0.5f, gate));
-        return (bits >> 15) ? -0.0f : gate;
-    }
-    return bf16_lo(uint32_t(__ldg(args.gelu_table + bits)));
+// bf16 pair from two floats in one conversion: low half = `low`, high half = `high`.
+__device__ __forceinline__ uint32_t cvt_bf16x2(float high, float low) {
+    uint32_t packed;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(high), "f"(low));
+    return packed;
 }
 
-// 32 gate + 32 up accumulator columns of one token -> 32 hidden values
-// h = bf16(bf16(gelu(gate)) * up), stored as bf16, e4m3 or NVFP4 (fusion.cu:5-10, 31-107).
+// GELU of a bf16 bit pattern (low 16 bits of `gate_bits`), as a float.  Magnitude codes [lo, hi) come
+// from the shared-memory copy of the table ([positive | negative] halves).  Below lo the table equals
+// bf16(x/2); from hi up to the largest finite value it equals x (positive) or -0 (negative): the host
+// verified both against the table before choosing lo and hi.  Subnormals, infinities, NaNs (and every
+// value when no range was supplied) read the full table in global memory.
+__device__ __forceinline__ float gelu_lookup(uint32_t gate_bits, const KernelArgs& args, uint32_t compact_table,
+                                             uint32_t lo, uint32_t span) {
+    const uint32_t magnitude = gate_bits & 0x7fffu;
+    const uint32_t offset = magnitude - lo;
+    const uint32_t negative = (gate_bits >> 15) & 1u;
+    uint32_t value;
+    // unconditional shared-memory read at a clamped index keeps the common case free of branches
+    const uint32_t slot = min(offset, span - 1u) + negative * span;
+    asm("ld.shared.u16 %0, [%1];" : "=r"(value) : "r"(compact_table + 2u * slot));
+    if (offset >= span) {                                   // rare: outside the stored range
+        if (span > 1u && magnitude >= 0x80u && magnitude < 0x7f80u) {
+            const float x = __uint_as_float(gate_bits << 16);
+            value = magnitude < lo ? uint32_t(bf16_bits(__fmul_rn(0.5f, x))) : (negative ? 0x8000u : (gate_bits & 0xffffu));
+        } else {
+            value = uint32_t(__ldg(args.gelu_table + (gate_bits & 0xffffu)));
+        }
+    }
+    return __uint_as_float(value << 16);
+}
+
+// One 16-feature unit of a token's row: 16 gate + 16 up accumulator columns -> 16 hidden values
+// h = bf16(bf16(gelu(gate)) * up), stored as bf16, e4m3 or NVFP4 (fusion.cu:5-10, 31-107).  For NVFP4
+// the unit is exactly one quantisation block of the next layer's input.
 template <int EPI>
-__device__ __forceinline__ void epilogue_geglu_chunk(const uint32_t (&gate_acc)[32], const uint32_t (&up_acc)[32],
-                                                     const KernelArgs& args, uint32_t compact_table, float scale,
-                                                     float scale_up, bool round_scale, const ExactDivider& out_scale,
-                                                     const ExactDivider& by_global, float out_scale_rcp, bool true_div, int token,
-                                                     int feature0) {
-    float h[32];
+__device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[16], const uint32_t (&up_acc)[16],
+                                                    const KernelArgs& args, uint32_t compact_table, float scale,
+                                                    float scale_up, bool round_scale, const ExactDivider& out_scale,
+                                                    const ExactDivider& by_global, float out_scale_rcp, bool true_div,
+                                                    int token, int feature0) {
+    const uint32_t lo = uint32_t(args.gelu_lo);
+    const uint32_t span = max(1u, uint32_t(args.gelu_hi - args.gelu_lo));
+    float h[16];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const float gate = gemm_value(gate_acc[i], scale, round_scale);
-        const float up = gemm_value(up_acc[i], scale_up, round_scale);
-        const float gelu = gelu_lookup(gate, args, compact_table);
-        h[i] = round_to_bf16(__fmul_rn(gelu, up));
+    for (int i = 0; i < 16; ++i) {
+        float gate = __uint_as_float(gate_acc[i]), up = __uint_as_float(up_acc[i]);
+        if (round_scale) { gate = round_to_bf16(gate); up = round_to_bf16(up); }
+        const uint32_t pair = cvt_bf16x2(__fmul_rn(up, scale_up), __fmul_rn(gate, scale));   // low = gate, high = up
+        const float gelu = gelu_lookup(pair, args, compact_table, lo, span);
+        h[i] = round_to_bf16(__fmul_rn(gelu, __uint_as_float(pair & 0xffff0000u)));
     }
     if (token >= args.tokens || feature0 >= args.features) return;
     const int64_t element = int64_t(token) * args.features + feature0;
     if (EPI == EPI_GEGLU_BF16) {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out) + element;
 #pragma unroll
-        for (int v = 0; v < 4; ++v)
-            if (feature0 + 8 * v < args.features)
-                store_u4(out + 8 * v, pack_bf16x2(h[8 * v], h[8 * v + 1]), pack_bf16x2(h[8 * v + 2], h[8 * v + 3]),
-                         pack_bf16x2(h[8 * v + 4], h[8 * v + 5]), pack_bf16x2(h[8 * v + 6], h[8 * v + 7]));
+        for (int v = 0; v < 2; ++v)
+            store_u4(out + 8 * v, cvt_bf16x2(h[8 * v + 1], h[8 * v]), cvt_bf16x2(h[8 * v + 3], h[8 * v + 2]),
+                     cvt_bf16x2(h[8 * v + 5], h[8 * v + 4]), cvt_bf16x2(h[8 * v + 7], h[8 * v + 6]));
     } else if (EPI == EPI_GEGLU_FP8) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) h[i] = true_div ? out_scale(h[i]) : __fmul_rn(h[i], out_scale_rcp);
-        uint8_t* out = static_cast<uint8_t*>(args.out) + element;
-#pragma unroll
-        for (int v = 0; v < 2; ++v)
-            if (feature0 + 16 * v < args.features)
-                store_u4(out + 16 * v, pack_fp8x4(h[16 * v], h[16 * v + 1], h[16 * v + 2], h[16 * v + 3]),
-                         pack_fp8x4(h[16 * v + 4], h[16 * v + 5], h[16 * v + 6], h[16 * v + 7]),
-                         pack_fp8x4(h[16 * v + 8], h[16 * v + 9], h[16 * v + 10], h[16 * v + 11]),
-                         pack_fp8x4(h[16 * v + 12], h[16 * v + 13], h[16 * v + 14], h[16 * v + 15]));
+        for (int i = 0; i < 16; ++i) h[i] = true_div ? out_scale(h[i]) : __fmul_rn(h[i], out_scale_rcp);
+        store_u4(static_cast<uint8_t*>(args.out) + element, pack_fp8x4(h[0], h[1], h[2], h[3]),
+                 pack_fp8x4(h[4], h[5], h[6], h[7]), pack_fp8x4(h[8], h[9], h[10], h[11]),
+                 pack_fp8x4(h[12], h[13], h[14], h[15]));
     } else {
-        // Two whole 16-element blocks of the next layer's input (quantize.cu:85-104 arithmetic).
-        uint32_t words[4];
-        uint32_t scale_codes = 0;
+        // quantize.cu:85-104 arithmetic on this block
+        float block_max = fabsf(h[0]);
 #pragma unroll
-        for (int block = 0; block < 2; ++block) {
-            float block_max = fabsf(h[16 * block]);
+        for (int i = 1; i < 16; ++i) block_max = fmaxf(block_max, fabsf(h[i]));
+        const uint8_t code = nvfp4_block_scale<true>(block_max, by_global, 0);
+        const ExactDivider denominator(__fmul_rn(out_scale.divisor, e4m3_to_float(code)));
+        float low[8], high[8];
 #pragma unroll
-            for (int i = 1; i < 16; ++i) block_max = fmaxf(block_max, fabsf(h[16 * block + i]));
-            const uint8_t code = nvfp4_block_scale<true>(block_max, by_global, 0);
-            const ExactDivider denominator(__fmul_rn(out_scale.divisor, e4m3_to_float(code)));
-            scale_codes |= uint32_t(code) << (8 * block);
-            float low[8], high[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { low[i] = h[16 * block + i]; high[i] = h[16 * block + 8 + i]; }
-            words[2 * block] = nvfp4_encode_x8<true>(low, denominator);
-            words[2 * block + 1] = nvfp4_encode_x8<true>(high, denominator);
-        }
-        const bool second = feature0 + 16 < args.features;
-        uint8_t* out = static_cast<uint8_t*>(args.out) + (element >> 1);
-        if (second) store_u4(out, words[0], words[1], words[2], words[3]);
-        else *reinterpret_cast<uint2*>(out) = make_uint2(words[0], words[1]);
-        const int block0 = feature0 >> 4;
+        for (int i = 0; i < 8; ++i) { low[i] = h[i]; high[i] = h[8 + i]; }
+        const uint32_t word0 = nvfp4_encode_x8<true>(low, denominator, block_max);
+        const uint32_t word1 = nvfp4_encode_x8<true>(high, denominator, block_max);
+        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(args.out) + (element >> 1)) = make_uint2(word0, word1);
+        const int block = feature0 >> 4;
         const int blocks_per_row = args.features >> 4;
-        if (args.out_scales != nullptr) {
-            uint8_t* linear = args.out_scales + int64_t(token) * blocks_per_row + block0;
-            if (second) *reinterpret_cast<uint16_t*>(linear) = uint16_t(scale_codes);
-            else *linear = uint8_t(scale_codes);
-        }
-        if (args.out_blocked != nullptr) {
-            uint8_t* tiled = args.out_blocked + scale_tile_offset(token, block0, (blocks_per_row + 3) >> 2);
-            if (second) *reinterpret_cast<uint16_t*>(tiled) = uint16_t(scale_codes);
-            else *tiled = uint8_t(scale_codes);
-        }
+        if (args.out_scales != nullptr) args.out_scales[int64_t(token) * blocks_per_row + block] = code;
+        if (args.out_blocked != nullptr)
+            args.out_blocked[scale_tile_offset(token, block, (blocks_per_row + 3) >> 2)] = code;
     }
 }
 
 // ---- the kernel ---------------------------------------------------------------
 
 template <int KIND, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(gemm_threads(EPI), 1)
 linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
               const KernelArgs args) {
     constexpr bool GEGLU = EPI != EPI_LINEAR;
@@ -265,7 +266,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar + 8 * b, 1);
-            mbar_init(acc_empty_bar + 8 * b, EPILOGUE_WARPS);
+            mbar_init(acc_empty_bar + 8 * b, epilogue_warps(EPI));
         }
         fence_barrier_init();
     }
@@ -275,7 +276,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     }
     if (GEGLU) {
         const int span = args.gelu_hi - args.gelu_lo;
-        for (int i = threadIdx.x; i < 2 * span; i += GEMM_THREADS) {
+        for (int i = threadIdx.x; i < 2 * span; i += gemm_threads(EPI)) {
             const int code = i < span ? args.gelu_lo + i : 0x8000 + args.gelu_lo + (i - span);
             asm volatile("st.shared.u16 [%0], %1;" ::"r"(compact_table + 2u * uint32_t(i)), "h"(__ldg(args.gelu_table + code)) : "memory");
         }
@@ -362,74 +363,80 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
         if (lane == 0) {
+            // One thread feeds the tensor pipe, so its instruction stream is kept to a few integer adds
+            // per tcgen05 operation: descriptors are a constant high word plus (address >> 4), and
+            // everything that depends only on the tile is computed once per tile.
             const uint32_t idesc = KIND == B2_KIND_NVFP4 ? idesc_nvf4(TILE_TOKENS, BN) : idesc_f8(TILE_TOKENS, BN);
             const uint32_t idesc_half = idesc_nvf4(TILE_TOKENS, 64);
+            const uint64_t operand_desc = smem_desc_sw128(0);        // + (address >> 4)
+            const uint64_t scale_desc = smem_desc_scale_atom(0);     // + (address >> 4)
+            const bool split_halves = KIND == B2_KIND_NVFP4 && GEGLU && BN == 128;
             int stage = 0;
             uint32_t phase = 0;
             int local_tile = 0;
+            // The scale copies of K slice i reuse the TMEM columns of slice i-2.  Copies are ordered before
+            // later MMAs but not after earlier ones, so before overwriting a set the thread makes sure the
+            // MMAs of slice i-2 have completed (their commit on that stage's `empty` barrier); by then this
+            // is almost always already true, so the check costs one barrier poll.
+            uint32_t older_bar = 0, older_parity = 0, newer_bar = 0, newer_parity = 0;
             for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x, ++local_tile) {
                 const int n_tile = tile / args.num_m_tiles;
                 const int f0 = n_tile * features_per_tile;
-                const int scale_offset = (f0 & 127) >> 5;          // column of feature f0 inside its scale block
-                const int scale_blocks = GEGLU ? 2 : ((f0 + BN - 1) >> 7) - (f0 >> 7) + 1;
+                // feature scales: one or two 4-column blocks per 64 elements of K, and the column the MMA
+                // starts reading at (a tile that starts 64 features into a 128-row block starts at column 2)
+                const bool second_block = GEGLU || ((f0 + BN - 1) >> 7) != (f0 >> 7);
+                const uint32_t scale_column = (GEGLU && BN == 256) ? 0u : uint32_t((f0 & 127) >> 5);
                 const int buffer = local_tile % args.accumulators;
                 const uint32_t use = uint32_t(local_tile / args.accumulators);
                 mbar_wait(acc_empty_bar + 8 * buffer, (use & 1u) ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + uint32_t(buffer) * 256u;
+                const uint32_t d_tmem = tmem_base + uint32_t(buffer * args.accumulator_stride);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
                     tc_fence_after_sync();
                     const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
                     const uint32_t a_smem = base + uint32_t(stage) * stage_bytes;
-                    const uint32_t b_smem = a_smem + A_TILE_BYTES;
-                    uint32_t sfb_column[SCALE_ATOMS_PER_STAGE] = {0, 0, 0, 0};
+                    const uint64_t a_desc = operand_desc + (a_smem >> 4);
+                    const uint64_t b_desc = a_desc + (A_TILE_BYTES >> 4);
+                    const uint32_t sfa_tmem = tmem_base + TMEM_SCALES + uint32_t(kb & 1) * TMEM_SCALE_SET;
+                    const uint32_t sfb_tmem = sfa_tmem + TMEM_SFB_OFFSET;
                     if (KIND == B2_KIND_NVFP4) {
-                        const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
-                        constexpr uint32_t PART = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
+                        if (older_bar != 0) mbar_wait(older_bar, older_parity, failed, args.status, STATUS_WAIT_MMA_TMEM);
+                        older_bar = newer_bar;
+                        older_parity = newer_parity;
+                        newer_bar = empty_bar + 8 * stage;
+                        newer_parity = phase;
+                        // shared memory: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
+                        const uint64_t atom_desc = scale_desc + ((scale_base + uint32_t(stage) * scale_stage_bytes) >> 4);
+                        constexpr uint64_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
 #pragma unroll
                         for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
-                            if (j >= mmas) break;
-                            const uint32_t atom = uint32_t(j) * SCALE_ATOM_BYTES;
-                            tc_copy_32x128b_x4(tmem_base + TMEM_SFA + j * 4, smem_desc_scale_atom(s_smem + atom));
-                            const uint32_t region = tmem_base + TMEM_SFB + j * 8;
-                            const uint64_t first = smem_desc_scale_atom(s_smem + PART + atom);
-                            const uint64_t second = smem_desc_scale_atom(s_smem + 2 * PART + atom);
-                            if (!GEGLU) {
-                                // one or two consecutive 128-row blocks; the MMA starts reading at the tile's column
-                                tc_copy_32x128b_x4(region, first);
-                                if (scale_blocks == 2) tc_copy_32x128b_x4(region + 4, second);
-                                sfb_column[j] = region + scale_offset;
-                            } else if (BN == 256) {
-                                // 128 gate features then 128 up features: two whole blocks side by side
-                                tc_copy_32x128b_x4(region, first);
-                                tc_copy_32x128b_x4(region + 4, second);
-                                sfb_column[j] = region;
-                            } else {
-                                // 64 gate + 64 up features sit in the same two columns of two different
-                                // blocks, and a copy can only land on a multiple of four columns: keep the
-                                // blocks apart and issue one MMA per half, each with its own scale column.
-                                tc_copy_32x128b_x4(region, first);
-                                tc_copy_32x128b_x4(region + 4, second);
-                                sfb_column[j] = region + scale_offset;
+                            if (j < mmas) {
+                                tc_copy_32x128b_x4(sfa_tmem + j * 4, atom_desc + j * ATOM);
+                                tc_copy_32x128b_x4(sfb_tmem + j * 8, atom_desc + PART + j * ATOM);
+                                if (second_block) tc_copy_32x128b_x4(sfb_tmem + j * 8 + 4, atom_desc + 2 * PART + j * ATOM);
                             }
                         }
                     }
 #pragma unroll
                     for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
-                        if (j >= mmas) break;
-                        const uint64_t a_desc = smem_desc_sw128(a_smem + j * 32);
-                        const uint64_t b_desc = smem_desc_sw128(b_smem + j * 32);
-                        const uint32_t accumulate = (kb | j) != 0;
-                        if (KIND == B2_KIND_NVFP4 && GEGLU && BN == 128) {
-                            // gate half -> columns [0, 64), up half -> columns [64, 128)
-                            mma_nvf4(d_tmem, a_desc, b_desc, idesc_half, tmem_base + TMEM_SFA + j * 4, sfb_column[j], accumulate);
-                            mma_nvf4(d_tmem + 64, a_desc, smem_desc_sw128(b_smem + 64 * STAGE_K_BYTES + j * 32), idesc_half,
-                                     tmem_base + TMEM_SFA + j * 4, sfb_column[j] + 4, accumulate);
-                        } else if (KIND == B2_KIND_NVFP4)
-                            mma_nvf4(d_tmem, a_desc, b_desc, idesc, tmem_base + TMEM_SFA + j * 4, sfb_column[j], accumulate);
-                        else
-                            mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, accumulate);
+                        if (j < mmas) {
+                            const uint32_t accumulate = (kb | j) != 0;
+                            if (KIND != B2_KIND_NVFP4) {
+                                mma_f8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, accumulate);
+                            } else if (split_halves) {
+                                // 64 gate + 64 up features sit in the same two columns of two different scale
+                                // blocks, and a copy can only land on a multiple of four columns: the blocks stay
+                                // apart and each half gets its own MMA (gate -> columns [0,64), up -> [64,128)).
+                                mma_nvf4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc_half, sfa_tmem + j * 4,
+                                         sfb_tmem + j * 8 + scale_column, accumulate);
+                                mma_nvf4(d_tmem + 64, a_desc + 2 * j, b_desc + ((64 * STAGE_K_BYTES) >> 4) + 2 * j, idesc_half,
+                                         sfa_tmem + j * 4, sfb_tmem + j * 8 + 4 + scale_column, accumulate);
+                            } else {
+                                mma_nvf4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, sfa_tmem + j * 4,
+                                         sfb_tmem + j * 8 + scale_column, accumulate);
+                            }
+                        }
                     }
                     tc_commit(empty_bar + 8 * stage);
                     if (++stage == args.stages) { stage = 0; phase ^= 1u; }
@@ -440,7 +447,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     } else {
         // ------------------------------------------------------------- epilogue
         const int quarter = warp & 3;                      // the TMEM lane partition this warp may read
-        const int half = (warp - 2) >> 2;                  // which half of the tile's features this warp stores
         const bool round_scale = (args.flags & B2_LINEAR_ROUND_SCALE_BF16) != 0;
         float scale = __fmul_rn(__ldg(args.act_scale), __ldg(args.weight_scale));
         if (round_scale) scale = round_to_bf16(scale);
@@ -457,9 +463,8 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         const ExactDivider out_scale(out_scale_value);
         const ExactDivider by_global(__fmul_rn(6.0f, out_scale_value));
         const bool true_div = (args.flags & B2_GEGLU_TRUE_DIV) != 0;
-        const int chunks = features_per_tile / 32;             // 32-feature chunks in the tile
-        const int chunk_begin = half == 0 ? 0 : (chunks + 1) / 2;
-        const int chunk_end = half == 0 ? (chunks + 1) / 2 : chunks;
+        constexpr int WARPS_PER_QUARTER = epilogue_warps(EPI) / 4;
+        const int part = (warp - 2) >> 2;                       // 0 .. WARPS_PER_QUARTER-1
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x, ++local_tile) {
             const int n_tile = tile / args.num_m_tiles;
@@ -470,18 +475,24 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             const uint32_t use = uint32_t(local_tile / args.accumulators);
             mbar_wait(acc_full_bar + 8 * buffer, use & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
             tc_fence_after_sync();
-            const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer) * 256u;
+            const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer * args.accumulator_stride);
             const bool warp_has_tokens = m_tile * TILE_TOKENS + quarter * 32 < args.tokens;   // else: padding rows only
-            for (int chunk = chunk_begin; chunk < chunk_end && warp_has_tokens; ++chunk) {
-                uint32_t first[32];
-                tmem_load_32x32(lane_address + chunk * 32, first);
-                if (GEGLU) {
-                    uint32_t second[32];
-                    tmem_load_32x32(lane_address + BN / 2 + chunk * 32, second);
+            if (GEGLU) {
+                const int units = features_per_tile / 16;
+                for (int unit = part; unit < units && warp_has_tokens; unit += WARPS_PER_QUARTER) {
+                    uint32_t first[16], second[16];
+                    tmem_load_32x16(lane_address + unit * 16, first);
+                    tmem_load_32x16(lane_address + BN / 2 + unit * 16, second);
                     tmem_load_wait();
-                    epilogue_geglu_chunk<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, compact_table, scale, scale_up, round_scale, out_scale,
-                                                                      by_global, out_scale_rcp, true_div, token, f0 + chunk * 32);
-                } else {
+                    epilogue_geglu_unit<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, compact_table, scale, scale_up,
+                                                                     round_scale, out_scale, by_global, out_scale_rcp,
+                                                                     true_div, token, f0 + unit * 16);
+                }
+            } else {
+                const int chunks = features_per_tile / 32;
+                for (int chunk = part; chunk < chunks && warp_has_tokens; chunk += WARPS_PER_QUARTER) {
+                    uint32_t first[32];
+                    tmem_load_32x32(lane_address + chunk * 32, first);
                     tmem_load_wait();
                     epilogue_linear_chunk(first, args, scale, round_scale, token, f0 + chunk * 32);
                 }
@@ -547,8 +558,8 @@ int sm_count() {
     return counts[device];
 }
 
-// Two accumulators (the second at column 256) fit beside the NVFP4 scale columns?
-static bool can_double_buffer(int kind, int tile_n) { return tile_n <= (kind == B2_KIND_NVFP4 ? TMEM_SFA - 256 : 256); }
+// Two accumulators fit (beside the NVFP4 scale columns)?
+static bool can_double_buffer(int kind, int tile_n) { return 2 * tile_n <= (kind == B2_KIND_NVFP4 ? TMEM_SCALES : TMEM_COLUMNS); }
 
 // LINEAR: 64, 128, 192 or 256 features per tile.  GEGLU: 64 or 128 features (128 or 256 columns).
 static bool tile_allowed(bool geglu, int features_per_tile) {
@@ -589,7 +600,7 @@ static int launch_linear(const CUtensorMap& act_map, const CUtensorMap& weight_m
         }
     }
     const int grid = args.total_tiles < sm_count() ? args.total_tiles : sm_count();
-    linear_kernel<KIND, EPI><<<grid, GEMM_THREADS, shared_bytes, stream>>>(act_map, weight_map, args);
+    linear_kernel<KIND, EPI><<<grid, gemm_threads(EPI), shared_bytes, stream>>>(act_map, weight_map, args);
     return int(cudaGetLastError());
 }
 
@@ -640,6 +651,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
     args.num_n_tiles = (d->features + feature_tile - 1) / feature_tile;
     args.total_tiles = args.num_m_tiles * args.num_n_tiles;
     args.accumulators = can_double_buffer(d->kind, args.tile_n) ? 2 : 1;
+    args.accumulator_stride = nvfp4 ? args.tile_n : 256;     // the second accumulator starts on a multiple of the tile width
     args.up_row_offset = d->features;
     args.scale_column_tiles = nvfp4 ? (d->width / 16 + 3) / 4 : 0;
     args.act_row_blocks = (d->tokens + 127) / 128;

@@ -123,8 +123,9 @@ nvfp4_encode_kernel(const uint4* __restrict__ input, uint32_t* __restrict__ outp
         maximum = fmaxf(maximum, __shfl_xor_sync(mask, maximum, 1));
         const uint8_t scale_code = nvfp4_block_scale<SPEC_C>(maximum, by_global, flags);
         const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
-        output[index] = nvfp4_encode_x8<SPEC_C>(v, denominator);
-        const int row = int(index / vectors_per_row);
+        output[index] = nvfp4_encode_x8<SPEC_C>(v, denominator, maximum);
+        // 32-bit index arithmetic whenever the matrix allows it (a 64-bit division costs dozens of instructions)
+        const int row = total <= 0x7fffffff ? int(uint32_t(index) / uint32_t(vectors_per_row)) : int(index / vectors_per_row);
         const int vector = int(index - int64_t(row) * vectors_per_row);
         const int block = vector >> 1;
         if (whole_words) {
