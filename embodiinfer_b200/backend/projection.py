@@ -19,6 +19,7 @@ from .. import _native as N
 from .. import kernels as K
 from ..layers.plans import ActivationQuantizer, EncodedActivation, Precision, WorkspaceKey
 from ..layers.registry import OperatorCapabilities
+from ..weights import blocked_scales
 from .quantization import blocked_scale_bytes
 
 
@@ -50,6 +51,7 @@ class B200Projection:
         self.plans: dict = {}
         self.outputs: dict = {}
         self.weight_scale_up: torch.Tensor | None = None   # set by `gated_pair`
+        self.gated_flags = 0
         if precision == "bf16":
             self.bf16_weight = weight.detach()
         elif precision == "fp8":
@@ -65,6 +67,7 @@ class B200Projection:
             source = weight.detach().contiguous()
             plan = backend.plan(source, 4).quantize(source)
             self.weight, self.weight_scale, self.weight_blocks = plan.output, plan.scale, plan.blocked
+            self.weight_rowmajor_scales = plan.scales
 
     # -- activations ---------------------------------------------------------------------------
     def encode(self, inputs: torch.Tensor) -> EncodedActivation | None:
@@ -195,6 +198,7 @@ class B200Projection:
             epilogue=N.EPI_GEGLU, out_format=out_format, tokens=rows, features=features, width=self.input_dim,
             out=result.output, gelu_table=table, out_scale=result.scale, out_scales=result.scales,
             out_blocked=result.blocked, weight_scale_up=self.weight_scale_up, gelu_range=table_range,
+            flags=self.gated_flags,
             **self._operands(encoded),
         )
         return result
@@ -233,9 +237,15 @@ class B200Projection:
         else:
             if gate.output_dim % 128:
                 raise ValueError("NVFP4 gated pairs need an intermediate width divisible by 128")
-            pair.weight_blocks = torch.cat(
-                (gate.weight_blocks.view(torch.uint8), up.weight_blocks.view(torch.uint8))
-            ).contiguous()
+            # Block scales in the paired row order the fused kernel reads fastest: 64 gate rows, then the
+            # 64 up rows of the same features, and so on (B2_LINEAR_PAIRED_GATE_UP_SCALES).
+            rows, blocks = gate.weight_rowmajor_scales.shape
+            paired = torch.stack(
+                (gate.weight_rowmajor_scales.view(torch.uint8).view(rows // 64, 64, blocks),
+                 up.weight_rowmajor_scales.view(torch.uint8).view(rows // 64, 64, blocks)), dim=1,
+            ).reshape(2 * rows, blocks)
+            pair.weight_blocks = blocked_scales(paired)
+            pair.gated_flags = N.LINEAR_PAIRED_GATE_UP_SCALES
         return pair
 
 

@@ -34,12 +34,14 @@
 
 namespace b2 {
 
-// Two service warps (TMA, MMA) plus the epilogue warps.  The plain Linear epilogue is a handful of
+// Three service warps (TMA, MMA, scale-factor copies) plus the epilogue warps.  The plain Linear epilogue is a handful of
 // instructions per element and runs on 8 warps; the gated epilogue (GELU lookup, two roundings, block
 // scale, exact division, e2m1 packing) is latency-bound, so it gets 16 warps: four per TMEM lane
 // partition, each owning 16-feature units of the tile.
 __host__ __device__ constexpr int epilogue_warps(int epi) { return epi == 0 ? 8 : 16; }
-__host__ __device__ constexpr int gemm_threads(int epi) { return 64 + 32 * epilogue_warps(epi); }
+constexpr int COPY_WARPS = 1;
+constexpr int FIRST_EPILOGUE_WARP = 2 + COPY_WARPS;
+__host__ __device__ constexpr int gemm_threads(int epi) { return 32 * (FIRST_EPILOGUE_WARP + epilogue_warps(epi)); }
 constexpr int TILE_TOKENS = 128;                   // MMA M
 constexpr int STAGE_K_BYTES = 128;                 // one swizzle row
 constexpr int A_TILE_BYTES = TILE_TOKENS * STAGE_K_BYTES;
@@ -51,8 +53,7 @@ constexpr int TMEM_COLUMNS = 512;
 // NVFP4 scale factors live in TMEM columns 384..479: two sets (alternating by K slice, so the copies for
 // one slice never overwrite columns an MMA of the previous slice may still be reading), each 16 columns
 // of token scales (4 per 64 elements of K) followed by 32 columns of feature scales (8 per 64 elements).
-constexpr int TMEM_SCALES = 384;
-constexpr int TMEM_SCALE_SET = 48;
+constexpr int TMEM_SCALE_SET = 48;                 // columns per set; sets are stacked downwards from column 512
 constexpr int TMEM_SFB_OFFSET = 16;
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int MAX_COMPACT_GELU = 4096;             // magnitude codes of the GELU table kept in shared memory
@@ -64,7 +65,7 @@ struct KernelArgs {
     int tokens, features, k_bytes, num_kb;
     int tile_n;                  // TMEM columns per tile (GEGLU: gate half + up half)
     int num_m_tiles, num_n_tiles, total_tiles;
-    int stages, accumulators, accumulator_stride;
+    int stages, accumulators, accumulator_stride, scale_sets;
     int up_row_offset;           // row of the first "up" feature in the packed weight
     int scale_column_tiles;      // 512-byte scale atoms per 128-row block
     int act_row_blocks, weight_row_blocks;
@@ -251,7 +252,9 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     const uint32_t empty_bar = barrier_base + 8 * MAX_STAGES;     // [stages]
     const uint32_t acc_full_bar = barrier_base + 16 * MAX_STAGES; // [2]
     const uint32_t acc_empty_bar = acc_full_bar + 16;             // [2]
-    const uint32_t tmem_slot = acc_empty_bar + 16;
+    const uint32_t sf_full_bar = acc_empty_bar + 16;              // [3] scale set filled (commit of the copy warp)
+    const uint32_t sf_empty_bar = sf_full_bar + 24;               // [3] scale set read (commit of the MMA warp)
+    const uint32_t tmem_slot = sf_empty_bar + 24;
     const uint32_t compact_table = tmem_slot + 16;                // 2 * (gelu_hi - gelu_lo) bf16 entries
 
     const int warp = threadIdx.x >> 5;
@@ -267,6 +270,10 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar + 8 * b, 1);
             mbar_init(acc_empty_bar + 8 * b, epilogue_warps(EPI));
+        }
+        for (int b = 0; b < 3; ++b) {
+            mbar_init(sf_full_bar + 8 * b, COPY_WARPS);
+            mbar_init(sf_empty_bar + 8 * b, 1);
         }
         fence_barrier_init();
     }
@@ -305,7 +312,11 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 // weight rows whose scales this tile needs: up to two 128-row blocks
                 int scale_row_block[2];
                 int scale_blocks;
-                if (GEGLU) {
+                if (GEGLU && (args.flags & B2_LINEAR_PAIRED_GATE_UP_SCALES)) {
+                    scale_row_block[0] = n_tile;            // 64 gate rows + 64 up rows of this tile form one block
+                    scale_row_block[1] = n_tile;
+                    scale_blocks = 1;
+                } else if (GEGLU) {
                     scale_row_block[0] = f0 >> 7;
                     scale_row_block[1] = (args.up_row_offset + f0) >> 7;
                     scale_blocks = 2;
@@ -360,6 +371,44 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 if (filled & (1u << s))
                     mbar_wait(full_bar + 8 * s, (fill_parity >> s) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
         }
+    } else if (warp >= 2 && warp < FIRST_EPILOGUE_WARP) {
+        // ------------------------------------------------------------- scale-factor copies (NVFP4)
+        // tcgen05.cp holds its issuing thread for ~150 cycles per 512-byte atom, longer than the MMAs of a
+        // K stage take (spreading the copies over several warps does not shorten them: the pipe runs them
+        // one after another).  A warp of its own issues them one or two stages ahead into alternating TMEM
+        // column sets, so the MMA thread only ever waits on a barrier and its MMAs overlap the next copies.
+        if (KIND == B2_KIND_NVFP4 && lane == 0) {
+            const uint64_t scale_desc = smem_desc_scale_atom(0);
+            const bool paired_scales = GEGLU && (args.flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
+            int stage = 0, set = 0;
+            uint32_t phase = 0, set_phase = 0;
+            for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) {
+                const int f0 = (tile / args.num_m_tiles) * features_per_tile;
+                const bool second_block = paired_scales ? false : (GEGLU || ((f0 + BN - 1) >> 7) != (f0 >> 7));
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
+                    mbar_wait(sf_empty_bar + 8 * set, set_phase ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
+                    tc_fence_after_sync();
+                    const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
+                    const uint32_t sfa_tmem = tmem_base + uint32_t(TMEM_COLUMNS - TMEM_SCALE_SET * (set + 1));
+                    const uint32_t sfb_tmem = sfa_tmem + TMEM_SFB_OFFSET;
+                    // shared memory: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
+                    const uint64_t atom_desc = scale_desc + ((scale_base + uint32_t(stage) * scale_stage_bytes) >> 4);
+                    constexpr uint64_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
+#pragma unroll
+                    for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
+                        if (j < mmas) {
+                            tc_copy_32x128b_x4(sfa_tmem + j * 4, atom_desc + j * ATOM);
+                            tc_copy_32x128b_x4(sfb_tmem + j * 8, atom_desc + PART + j * ATOM);
+                            if (second_block) tc_copy_32x128b_x4(sfb_tmem + j * 8 + 4, atom_desc + 2 * PART + j * ATOM);
+                        }
+                    }
+                    tc_commit(sf_full_bar + 8 * set);
+                    if (++stage == args.stages) { stage = 0; phase ^= 1u; }
+                    if (++set == args.scale_sets) { set = 0; set_phase ^= 1u; }
+                }
+            }
+        }
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
         if (lane == 0) {
@@ -369,23 +418,19 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             const uint32_t idesc = KIND == B2_KIND_NVFP4 ? idesc_nvf4(TILE_TOKENS, BN) : idesc_f8(TILE_TOKENS, BN);
             const uint32_t idesc_half = idesc_nvf4(TILE_TOKENS, 64);
             const uint64_t operand_desc = smem_desc_sw128(0);        // + (address >> 4)
-            const uint64_t scale_desc = smem_desc_scale_atom(0);     // + (address >> 4)
-            const bool split_halves = KIND == B2_KIND_NVFP4 && GEGLU && BN == 128;
+            const bool paired_scales = GEGLU && (args.flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
+            const bool split_halves = KIND == B2_KIND_NVFP4 && GEGLU && BN == 128 && !paired_scales;
             int stage = 0;
             uint32_t phase = 0;
             int local_tile = 0;
-            // The scale copies of K slice i reuse the TMEM columns of slice i-2.  Copies are ordered before
-            // later MMAs but not after earlier ones, so before overwriting a set the thread makes sure the
-            // MMAs of slice i-2 have completed (their commit on that stage's `empty` barrier); by then this
-            // is almost always already true, so the check costs one barrier poll.
-            uint32_t older_bar = 0, older_parity = 0, newer_bar = 0, newer_parity = 0;
+            int set = 0;
+            uint32_t set_phase = 0;
             for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x, ++local_tile) {
                 const int n_tile = tile / args.num_m_tiles;
                 const int f0 = n_tile * features_per_tile;
-                // feature scales: one or two 4-column blocks per 64 elements of K, and the column the MMA
-                // starts reading at (a tile that starts 64 features into a 128-row block starts at column 2)
-                const bool second_block = GEGLU || ((f0 + BN - 1) >> 7) != (f0 >> 7);
-                const uint32_t scale_column = (GEGLU && BN == 256) ? 0u : uint32_t((f0 & 127) >> 5);
+                // column of the feature-scale block the MMA starts reading at (a tile that starts 64 features
+                // into a 128-row block starts at column 2)
+                const uint32_t scale_column = (paired_scales || (GEGLU && BN == 256)) ? 0u : uint32_t((f0 & 127) >> 5);
                 const int buffer = local_tile % args.accumulators;
                 const uint32_t use = uint32_t(local_tile / args.accumulators);
                 mbar_wait(acc_empty_bar + 8 * buffer, (use & 1u) ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
@@ -398,25 +443,11 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     const uint32_t a_smem = base + uint32_t(stage) * stage_bytes;
                     const uint64_t a_desc = operand_desc + (a_smem >> 4);
                     const uint64_t b_desc = a_desc + (A_TILE_BYTES >> 4);
-                    const uint32_t sfa_tmem = tmem_base + TMEM_SCALES + uint32_t(kb & 1) * TMEM_SCALE_SET;
+                    const uint32_t sfa_tmem = tmem_base + uint32_t(TMEM_COLUMNS - TMEM_SCALE_SET * (set + 1));
                     const uint32_t sfb_tmem = sfa_tmem + TMEM_SFB_OFFSET;
                     if (KIND == B2_KIND_NVFP4) {
-                        if (older_bar != 0) mbar_wait(older_bar, older_parity, failed, args.status, STATUS_WAIT_MMA_TMEM);
-                        older_bar = newer_bar;
-                        older_parity = newer_parity;
-                        newer_bar = empty_bar + 8 * stage;
-                        newer_parity = phase;
-                        // shared memory: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
-                        const uint64_t atom_desc = scale_desc + ((scale_base + uint32_t(stage) * scale_stage_bytes) >> 4);
-                        constexpr uint64_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
-#pragma unroll
-                        for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
-                            if (j < mmas) {
-                                tc_copy_32x128b_x4(sfa_tmem + j * 4, atom_desc + j * ATOM);
-                                tc_copy_32x128b_x4(sfb_tmem + j * 8, atom_desc + PART + j * ATOM);
-                                if (second_block) tc_copy_32x128b_x4(sfb_tmem + j * 8 + 4, atom_desc + 2 * PART + j * ATOM);
-                            }
-                        }
+                        mbar_wait(sf_full_bar + 8 * set, set_phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
+                        tc_fence_after_sync();
                     }
 #pragma unroll
                     for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
@@ -439,6 +470,10 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         }
                     }
                     tc_commit(empty_bar + 8 * stage);
+                    if (KIND == B2_KIND_NVFP4) {
+                        tc_commit(sf_empty_bar + 8 * set);
+                        if (++set == args.scale_sets) { set = 0; set_phase ^= 1u; }
+                    }
                     if (++stage == args.stages) { stage = 0; phase ^= 1u; }
                 }
                 tc_commit(acc_full_bar + 8 * buffer);
@@ -464,7 +499,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         const ExactDivider by_global(__fmul_rn(6.0f, out_scale_value));
         const bool true_div = (args.flags & B2_GEGLU_TRUE_DIV) != 0;
         constexpr int WARPS_PER_QUARTER = epilogue_warps(EPI) / 4;
-        const int part = (warp - 2) >> 2;                       // 0 .. WARPS_PER_QUARTER-1
+        const int part = (warp - FIRST_EPILOGUE_WARP) >> 2;     // 0 .. WARPS_PER_QUARTER-1
         int local_tile = 0;
         for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x, ++local_tile) {
             const int n_tile = tile / args.num_m_tiles;
@@ -559,7 +594,9 @@ int sm_count() {
 }
 
 // Two accumulators fit (beside the NVFP4 scale columns)?
-static bool can_double_buffer(int kind, int tile_n) { return 2 * tile_n <= (kind == B2_KIND_NVFP4 ? TMEM_SCALES : TMEM_COLUMNS); }
+static bool can_double_buffer(int kind, int tile_n) {
+    return 2 * tile_n <= (kind == B2_KIND_NVFP4 ? TMEM_COLUMNS - 2 * TMEM_SCALE_SET : TMEM_COLUMNS);
+}
 
 // LINEAR: 64, 128, 192 or 256 features per tile.  GEGLU: 64 or 128 features (128 or 256 columns).
 static bool tile_allowed(bool geglu, int features_per_tile) {
@@ -644,14 +681,18 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
     args.k_bytes = nvfp4 ? d->width / 2 : d->width;
     args.num_kb = (args.k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
     args.num_m_tiles = (d->tokens + TILE_TOKENS - 1) / TILE_TOKENS;
-    const int feature_tile =
-        d->feature_tile > 0 ? d->feature_tile : choose_feature_tile(d->kind, geglu, d->features, args.num_m_tiles);
+    const bool paired = (d->flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
+    if (paired && !(geglu && nvfp4)) return B2_E_INVALID;
+    if (paired && d->feature_tile != 0 && d->feature_tile != 64) return B2_E_UNSUPPORTED;
+    const int feature_tile = paired ? 64
+        : d->feature_tile > 0 ? d->feature_tile : choose_feature_tile(d->kind, geglu, d->features, args.num_m_tiles);
     if (!tile_allowed(geglu, feature_tile)) return B2_E_UNSUPPORTED;
     args.tile_n = geglu ? 2 * feature_tile : feature_tile;
     args.num_n_tiles = (d->features + feature_tile - 1) / feature_tile;
     args.total_tiles = args.num_m_tiles * args.num_n_tiles;
     args.accumulators = can_double_buffer(d->kind, args.tile_n) ? 2 : 1;
     args.accumulator_stride = nvfp4 ? args.tile_n : 256;     // the second accumulator starts on a multiple of the tile width
+    args.scale_sets = !nvfp4 ? 1 : (args.accumulators * args.tile_n + 3 * TMEM_SCALE_SET <= TMEM_COLUMNS ? 3 : 2);
     args.up_row_offset = d->features;
     args.scale_column_tiles = nvfp4 ? (d->width / 16 + 3) / 4 : 0;
     args.act_row_blocks = (d->tokens + 127) / 128;
@@ -680,7 +721,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
         args.gelu_lo = d->gelu_lo;
         args.gelu_hi = d->gelu_hi;
     }
-    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 64 + 4 * (args.gelu_hi - args.gelu_lo);
+    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 128 + 4 * (args.gelu_hi - args.gelu_lo);
     int stages = (SMEM_LIMIT - fixed_bytes) / (stage_bytes + scale_stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) return B2_E_UNSUPPORTED;

@@ -109,11 +109,17 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
 #define B2_LINEAR_ROUND_SCALE_BF16 1 /* NVFP4 registry route: y = bf16(bf16(acc) * bf16(g_a*g_w))
                                         (nvfp4.py:120, quantize.cu:106-114) instead of bf16(acc*g_a*g_w) */
 
+#define B2_LINEAR_PAIRED_GATE_UP_SCALES 4 /* GEGLU with NVFP4 operands: `weight_scales` is the 128x4-tile layout of the
+                                            block scales with their ROWS reordered so that rows [128t, 128t+64) are gate
+                                            features [64t, 64t+64) and rows [128t+64, 128t+128) the up features of the same
+                                            range.  Each 64-feature tile then needs one scale block and one MMA per K step
+                                            instead of two of each.  The weight codes keep the bundle order (gate, then up). */
+
 typedef struct b2_linear_desc {
     int32_t kind;        /* B2_KIND_* */
     int32_t epilogue;    /* B2_EPI_* */
     int32_t out_format;  /* B2_OUT_* */
-    int32_t flags;       /* B2_LINEAR_* | B2_GEGLU_TRUE_DIV */
+    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_GEGLU_TRUE_DIV */
     int32_t tokens;      /* M: rows of the activation matrix */
     int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
     int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */

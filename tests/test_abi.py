@@ -33,7 +33,7 @@ def test_header_constants_match_python_mirror():
     text = HEADER.read_text()
     values = {m.group(1): int(m.group(2), 0) for m in re.finditer(r"#define\s+(B2_\w+)\s+\(?(-?\w+)\)?\s", text) if re.fullmatch(r"-?(0x)?[0-9a-fA-F]+", m.group(2))}
     for name in ("SPEC_T", "SPEC_C", "SCALAR_RCP", "DIVISOR_BF16", "CLAMP_TINY", "GEGLU_TRUE_DIV", "KIND_FP8", "KIND_NVFP4",
-                 "EPI_LINEAR", "EPI_GEGLU", "OUT_BF16", "OUT_FP8", "OUT_NVFP4", "LINEAR_ROUND_SCALE_BF16",
+                 "EPI_LINEAR", "EPI_GEGLU", "OUT_BF16", "OUT_FP8", "OUT_NVFP4", "LINEAR_ROUND_SCALE_BF16", "LINEAR_PAIRED_GATE_UP_SCALES",
                  "SCALE_SCRATCH_BYTES", "ABI_VERSION", "E_INVALID", "E_UNSUPPORTED", "E_DRIVER", "E_TOO_LARGE"):
         assert values[f"B2_{name}"] == getattr(N, name), name
 

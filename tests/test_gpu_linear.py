@@ -227,3 +227,27 @@ def test_gelu_table_range_rejects_unstructured_tables(device):
     generator = torch.Generator().manual_seed(0)
     noise = torch.randint(0, 65535, (65536,), generator=generator, dtype=torch.int32).to(torch.uint16)
     assert K.gelu_table_range(noise) == (0, 0)
+
+
+def test_paired_gate_up_scale_layout(device):
+    """B2_LINEAR_PAIRED_GATE_UP_SCALES: same bits as the bundle-order scale layout, fewer tensor-core operations."""
+    tokens, features, width = 200, 256, 512
+    host, dev = operands("nvfp4", tokens, 2 * features, width, 77, device)
+    scales = host["w_sl"]                                    # row-major [2F, K/16]: gate rows, then up rows
+    blocks = scales.shape[1]
+    paired = np.stack((scales[:features].reshape(features // 64, 64, blocks),
+                       scales[features:].reshape(features // 64, 64, blocks)), axis=1).reshape(2 * features, blocks)
+    table_host = gelu_table_cpu("tanh")
+    table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+    common = dict(epilogue=N.EPI_GEGLU, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, gelu_table=table)
+    plain = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+    K.linear(out=plain, feature_tile=64, **common, **dev)
+    fast = torch.empty_like(plain)
+    paired_dev = {**dev, "weight_scales": torch.from_numpy(O.swizzle_scales(paired)).to(device)}
+    K.linear(out=fast, flags=N.LINEAR_PAIRED_GATE_UP_SCALES, **common, **paired_dev)
+    assert torch.equal(plain.view(torch.int16), fast.view(torch.int16))
+    with pytest.raises(RuntimeError, match="error -2"):
+        K.linear(out=fast, flags=N.LINEAR_PAIRED_GATE_UP_SCALES, feature_tile=128, **common, **paired_dev)
+    fp8_host, fp8_dev = operands("fp8", tokens, 2 * features, width, 77, device)
+    with pytest.raises(RuntimeError, match="error -1"):
+        K.linear(out=fast, flags=N.LINEAR_PAIRED_GATE_UP_SCALES, **common, **fp8_dev)
