@@ -39,8 +39,7 @@ namespace b2 {
 // scale, exact division, e2m1 packing) is latency-bound, so it gets 16 warps: four per TMEM lane
 // partition, each owning 16-feature units of the tile.
 __host__ __device__ constexpr int epilogue_warps(int epi) { return epi == 0 ? 8 : 16; }
-constexpr int COPY_WARPS = 1;
-constexpr int FIRST_EPILOGUE_WARP = 2 + COPY_WARPS;
+constexpr int FIRST_EPILOGUE_WARP = 2;
 __host__ __device__ constexpr int gemm_threads(int epi) { return 32 * (FIRST_EPILOGUE_WARP + epilogue_warps(epi)); }
 constexpr int TILE_TOKENS = 128;                   // MMA M
 constexpr int STAGE_K_BYTES = 128;                 // one swizzle row
@@ -53,8 +52,10 @@ constexpr int TMEM_COLUMNS = 512;
 // NVFP4 scale factors live in TMEM columns 384..479: two sets (alternating by K slice, so the copies for
 // one slice never overwrite columns an MMA of the previous slice may still be reading), each 16 columns
 // of token scales (4 per 64 elements of K) followed by 32 columns of feature scales (8 per 64 elements).
-constexpr int TMEM_SCALE_SET = 48;                 // columns per set; sets are stacked downwards from column 512
-constexpr int TMEM_SFB_OFFSET = 16;
+constexpr int PREFETCH_DISTANCE = 12;              // K stages between an L2 prefetch and its load
+constexpr int TMEM_SFA_COLUMNS = 16;               // 4 atoms x 4 columns of token scales per K stage
+// A set of scale columns = 16 token-scale columns + 16 per 128-row block of feature scales; sets are
+// stacked downwards from column 512 and rotate with the K stages.
 constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int MAX_COMPACT_GELU = 4096;             // magnitude codes of the GELU table kept in shared memory
 constexpr int SMEM_MINIMUM = 120 * 1024;           // keeps a second CTA (and its TMEM request) off the SM
@@ -65,7 +66,7 @@ struct KernelArgs {
     int tokens, features, k_bytes, num_kb;
     int tile_n;                  // TMEM columns per tile (GEGLU: gate half + up half)
     int num_m_tiles, num_n_tiles, total_tiles;
-    int stages, accumulators, accumulator_stride, scale_sets;
+    int stages, accumulators, accumulator_stride, scale_sets, scale_blocks;
     int up_row_offset;           // row of the first "up" feature in the packed weight
     int scale_column_tiles;      // 512-byte scale atoms per 128-row block
     int act_row_blocks, weight_row_blocks;
@@ -165,10 +166,11 @@ __device__ __forceinline__ float gelu_lookup(uint32_t gate_bits, const KernelArg
     const uint32_t negative = (gate_bits >> 15) & 1u;
     uint32_t value;
     // unconditional shared-memory read at a clamped index keeps the common case free of branches
-    const uint32_t slot = min(offset, span - 1u) + negative * span;
+    // (span == 0: no range was supplied; the read is harmless and its value is never used)
+    const uint32_t slot = min(offset, span == 0u ? 0u : span - 1u) + negative * span;
     asm("ld.shared.u16 %0, [%1];" : "=r"(value) : "r"(compact_table + 2u * slot));
     if (offset >= span) {                                   // rare: outside the stored range
-        if (span > 1u && magnitude >= 0x80u && magnitude < 0x7f80u) {
+        if (span != 0u && magnitude >= 0x80u && magnitude < 0x7f80u) {
             const float x = __uint_as_float(gate_bits << 16);
             value = magnitude < lo ? uint32_t(bf16_bits(__fmul_rn(0.5f, x))) : (negative ? 0x8000u : (gate_bits & 0xffffu));
         } else {
@@ -188,7 +190,7 @@ __device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[1
                                                     const ExactDivider& by_global, float out_scale_rcp, bool true_div,
                                                     int token, int feature0) {
     const uint32_t lo = uint32_t(args.gelu_lo);
-    const uint32_t span = max(1u, uint32_t(args.gelu_hi - args.gelu_lo));
+    const uint32_t span = uint32_t(args.gelu_hi - args.gelu_lo);     // 0: every lookup reads the full table
     float h[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -233,6 +235,11 @@ __device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[1
     }
 }
 
+#ifdef B2_TRACE
+#define TRACE(slot, index) do { if (blockIdx.x == 0 && (args.flags & 0x1000) && lane == 0 && (index) < 400) reinterpret_cast<long long*>(args.status)[(slot) * 400 + (index)] = clock64(); } while (0)
+#else
+#define TRACE(slot, index)
+#endif
 // ---- the kernel ---------------------------------------------------------------
 
 template <int KIND, int EPI>
@@ -252,9 +259,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     const uint32_t empty_bar = barrier_base + 8 * MAX_STAGES;     // [stages]
     const uint32_t acc_full_bar = barrier_base + 16 * MAX_STAGES; // [2]
     const uint32_t acc_empty_bar = acc_full_bar + 16;             // [2]
-    const uint32_t sf_full_bar = acc_empty_bar + 16;              // [3] scale set filled (commit of the copy warp)
-    const uint32_t sf_empty_bar = sf_full_bar + 24;               // [3] scale set read (commit of the MMA warp)
-    const uint32_t tmem_slot = sf_empty_bar + 24;
+    const uint32_t tmem_slot = acc_empty_bar + 16;
     const uint32_t compact_table = tmem_slot + 16;                // 2 * (gelu_hi - gelu_lo) bf16 entries
 
     const int warp = threadIdx.x >> 5;
@@ -270,10 +275,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar + 8 * b, 1);
             mbar_init(acc_empty_bar + 8 * b, epilogue_warps(EPI));
-        }
-        for (int b = 0; b < 3; ++b) {
-            mbar_init(sf_full_bar + 8 * b, COPY_WARPS);
-            mbar_init(sf_empty_bar + 8 * b, 1);
         }
         fence_barrier_init();
     }
@@ -300,10 +301,21 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
 
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer
-        if (lane == 0) {
+        // (all lanes run the loop; one elected lane issues the copies)
+        {
             int stage = 0;
             uint32_t phase = 0;
+            int trace_index = 0; (void)trace_index;
             uint32_t filled = 0, fill_parity = 0;     // per stage: ever filled / phase of the last fill
+            // L2 prefetch cursor, PREFETCH_DISTANCE K stages ahead of the loads.  Shared memory holds about
+            // 2500 cycles' worth of loads at the tensor pipe's rate while a first touch of HBM takes about as
+            // long to arrive, so loads that miss the L2 leave the pipe waiting; weights prefetched into the L2
+            // a few thousand cycles earlier arrive in a third of that.  The token tiles sharing a weight slab
+            // run side by side, so they take turns issuing its prefetches.
+            int pf_tile = blockIdx.x, pf_kb = 0;
+            for (int i = 0; i < PREFETCH_DISTANCE; ++i)
+                if (++pf_kb == num_kb) { pf_kb = 0; pf_tile += gridDim.x; }
+            int pf_f0 = 0, pf_turn = 0, pf_seen = -1;      // feature row of the cursor's tile; stages until this CTA's turn
             for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) {
                 const int n_tile = tile / args.num_m_tiles;
                 const int m_tile = tile - n_tile * args.num_m_tiles;
@@ -325,42 +337,71 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     scale_row_block[1] = scale_row_block[0] + 1;
                     scale_blocks = ((f0 + BN - 1) >> 7) - scale_row_block[0] + 1;
                 }
+                // Everything a K stage needs is fixed per tile except the K offset: source pointers of the
+                // scale atoms, which of the two feature-scale blocks exist, and the byte count of a full stage.
+                const uint8_t* token_scales = nullptr;
+                const uint8_t* feature_scales[2] = {nullptr, nullptr};
+                int live = 0;
+                if (KIND == B2_KIND_NVFP4) {
+                    token_scales = args.act_scales + int64_t(m_tile) * args.scale_column_tiles * SCALE_ATOM_BYTES;
+                    live = 1;
+                    for (int i = 0; i < scale_blocks; ++i)
+                        if (scale_row_block[i] < args.weight_row_blocks) {
+                            feature_scales[i] = args.weight_scales + int64_t(scale_row_block[i]) * args.scale_column_tiles * SCALE_ATOM_BYTES;
+                            ++live;
+                        }
+                }
+                const int tail_atoms = args.scale_column_tiles - (num_kb - 1) * SCALE_ATOMS_PER_STAGE;
+                const uint32_t up_smem_offset = uint32_t(BN / 2) * STAGE_K_BYTES;
+                const int up_row = args.up_row_offset + f0;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
-                    const uint32_t bar = full_bar + 8 * stage;
-                    uint32_t bytes = stage_bytes;
-                    int atoms = 0;
-                    if (KIND == B2_KIND_NVFP4) {
-                        atoms = min(SCALE_ATOMS_PER_STAGE, args.scale_column_tiles - kb * SCALE_ATOMS_PER_STAGE);
-                        int live = 1;
-                        for (int i = 0; i < scale_blocks; ++i) live += scale_row_block[i] < args.weight_row_blocks;
-                        bytes += uint32_t(live * atoms) * SCALE_ATOM_BYTES;
-                    }
-                    mbar_expect_tx(bar, bytes);
+                    __syncwarp();
+                    TRACE(0, trace_index);
                     filled |= 1u << stage;
                     fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
-                    const uint32_t a_smem = base + uint32_t(stage) * stage_bytes;
-                    const uint32_t b_smem = a_smem + A_TILE_BYTES;
-                    tma_load_2d(a_smem, &act_map, bar, kb * STAGE_K_BYTES, m0);
-                    tma_load_2d(b_smem, &weight_map, bar, kb * STAGE_K_BYTES, f0);
-                    if (GEGLU)
-                        tma_load_2d(b_smem + uint32_t(BN / 2) * STAGE_K_BYTES, &weight_map, bar, kb * STAGE_K_BYTES,
-                                    args.up_row_offset + f0);
-                    if (KIND == B2_KIND_NVFP4) {
-                        const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
-                        const uint32_t copy_bytes = uint32_t(atoms) * SCALE_ATOM_BYTES;
-                        const int64_t atom0 = int64_t(kb) * SCALE_ATOMS_PER_STAGE;
-                        bulk_load(s_smem,
-                                  args.act_scales + (int64_t(m_tile) * args.scale_column_tiles + atom0) * SCALE_ATOM_BYTES,
-                                  copy_bytes, bar);
-                        for (int i = 0; i < scale_blocks; ++i) {
-                            if (scale_row_block[i] >= args.weight_row_blocks) continue;
-                            bulk_load(s_smem + (1 + i) * SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES,
-                                      args.weight_scales +
-                                          (int64_t(scale_row_block[i]) * args.scale_column_tiles + atom0) * SCALE_ATOM_BYTES,
-                                      copy_bytes, bar);
+                    if (elect_one()) {
+                        const uint32_t bar = full_bar + 8 * stage;
+                        const uint32_t a_smem = base + uint32_t(stage) * stage_bytes;
+                        const uint32_t b_smem = a_smem + A_TILE_BYTES;
+                        const int k0 = kb * STAGE_K_BYTES;
+                        const uint32_t copy_bytes = uint32_t(kb == num_kb - 1 ? tail_atoms : SCALE_ATOMS_PER_STAGE) * SCALE_ATOM_BYTES;
+                        mbar_expect_tx(bar, stage_bytes + (KIND == B2_KIND_NVFP4 ? uint32_t(live) * copy_bytes : 0u));
+                        tma_load_2d(a_smem, &act_map, bar, k0, m0);
+                        tma_load_2d(b_smem, &weight_map, bar, k0, f0);
+                        if (GEGLU) tma_load_2d(b_smem + up_smem_offset, &weight_map, bar, k0, up_row);
+                        if (KIND == B2_KIND_NVFP4) {
+                            const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
+                            const int64_t offset = int64_t(kb) * (SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES);
+                            bulk_load(s_smem, token_scales + offset, copy_bytes, bar);
+                            if (feature_scales[0] != nullptr)
+                                bulk_load(s_smem + SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES, feature_scales[0] + offset, copy_bytes, bar);
+                            if (feature_scales[1] != nullptr)
+                                bulk_load(s_smem + 2 * SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES, feature_scales[1] + offset, copy_bytes, bar);
                         }
                     }
+#ifdef B2_TRACE
+                    if (args.flags & 0x2000) pf_tile = args.total_tiles;
+#endif
+                    if (pf_tile < args.total_tiles) {
+                        if (pf_tile != pf_seen) {
+                            const int pf_n_tile = pf_tile / args.num_m_tiles;
+                            pf_f0 = pf_n_tile * features_per_tile;
+                            pf_turn = (pf_tile - pf_n_tile * args.num_m_tiles + args.num_m_tiles - pf_kb % args.num_m_tiles) % args.num_m_tiles;
+                            pf_seen = pf_tile;
+                        }
+                        if (pf_turn == 0) {
+                            if (elect_one()) {
+                                tma_prefetch_l2_2d(&weight_map, pf_kb * STAGE_K_BYTES, pf_f0);
+                                if (GEGLU) tma_prefetch_l2_2d(&weight_map, pf_kb * STAGE_K_BYTES, args.up_row_offset + pf_f0);
+                            }
+                            pf_turn = args.num_m_tiles;
+                        }
+                        --pf_turn;
+                        if (++pf_kb == num_kb) { pf_kb = 0; pf_tile += gridDim.x; }
+                    }
+                    __syncwarp();
+                    TRACE(1, trace_index); ++trace_index;
                     if (++stage == args.stages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -371,50 +412,12 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 if (filled & (1u << s))
                     mbar_wait(full_bar + 8 * s, (fill_parity >> s) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
         }
-    } else if (warp >= 2 && warp < FIRST_EPILOGUE_WARP) {
-        // ------------------------------------------------------------- scale-factor copies (NVFP4)
-        // tcgen05.cp holds its issuing thread for ~150 cycles per 512-byte atom, longer than the MMAs of a
-        // K stage take (spreading the copies over several warps does not shorten them: the pipe runs them
-        // one after another).  A warp of its own issues them one or two stages ahead into alternating TMEM
-        // column sets, so the MMA thread only ever waits on a barrier and its MMAs overlap the next copies.
-        if (KIND == B2_KIND_NVFP4 && lane == 0) {
-            const uint64_t scale_desc = smem_desc_scale_atom(0);
-            const bool paired_scales = GEGLU && (args.flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
-            int stage = 0, set = 0;
-            uint32_t phase = 0, set_phase = 0;
-            for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) {
-                const int f0 = (tile / args.num_m_tiles) * features_per_tile;
-                const bool second_block = paired_scales ? false : (GEGLU || ((f0 + BN - 1) >> 7) != (f0 >> 7));
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
-                    mbar_wait(sf_empty_bar + 8 * set, set_phase ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
-                    tc_fence_after_sync();
-                    const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
-                    const uint32_t sfa_tmem = tmem_base + uint32_t(TMEM_COLUMNS - TMEM_SCALE_SET * (set + 1));
-                    const uint32_t sfb_tmem = sfa_tmem + TMEM_SFB_OFFSET;
-                    // shared memory: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
-                    const uint64_t atom_desc = scale_desc + ((scale_base + uint32_t(stage) * scale_stage_bytes) >> 4);
-                    constexpr uint64_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
-#pragma unroll
-                    for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
-                        if (j < mmas) {
-                            tc_copy_32x128b_x4(sfa_tmem + j * 4, atom_desc + j * ATOM);
-                            tc_copy_32x128b_x4(sfb_tmem + j * 8, atom_desc + PART + j * ATOM);
-                            if (second_block) tc_copy_32x128b_x4(sfb_tmem + j * 8 + 4, atom_desc + 2 * PART + j * ATOM);
-                        }
-                    }
-                    tc_commit(sf_full_bar + 8 * set);
-                    if (++stage == args.stages) { stage = 0; phase ^= 1u; }
-                    if (++set == args.scale_sets) { set = 0; set_phase ^= 1u; }
-                }
-            }
-        }
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            // One thread feeds the tensor pipe, so its instruction stream is kept to a few integer adds
-            // per tcgen05 operation: descriptors are a constant high word plus (address >> 4), and
-            // everything that depends only on the tile is computed once per tile.
+        // (all lanes run the loop; one elected lane issues the tcgen05 instructions)
+        {
+            // Descriptors are a constant high word plus (address >> 4), and everything that depends only
+            // on the tile is computed once per tile.
             const uint32_t idesc = KIND == B2_KIND_NVFP4 ? idesc_nvf4(TILE_TOKENS, BN) : idesc_f8(TILE_TOKENS, BN);
             const uint32_t idesc_half = idesc_nvf4(TILE_TOKENS, 64);
             const uint64_t operand_desc = smem_desc_sw128(0);        // + (address >> 4)
@@ -423,8 +426,17 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             int local_tile = 0;
-            int set = 0;
-            uint32_t set_phase = 0;
+            // Scale factors: tcgen05.cp (shared memory -> TMEM) is ordered before a later tcgen05.mma of the
+            // same thread, so this thread issues the copies of a K stage right before its MMAs (about 50
+            // cycles per 512-byte atom, overlapping the MMAs already queued).  The reverse order is not
+            // guaranteed: before a set of columns is overwritten, the MMAs that last read it (scale_sets
+            // stages ago) must have completed, which their commit to that stage's `empty` barrier reports.
+            int trace_index = 0; (void)trace_index;
+            int set = 0, lag_stage = 0, issued = 0;
+            uint32_t lag_phase = 0;
+            const uint32_t set_columns = uint32_t(TMEM_SFA_COLUMNS + 16 * args.scale_blocks);
+            const uint32_t sfb_stride = 4u * uint32_t(args.scale_blocks);
+            const uint64_t scale_desc = smem_desc_scale_atom(0);
             for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x, ++local_tile) {
                 const int n_tile = tile / args.num_m_tiles;
                 const int f0 = n_tile * features_per_tile;
@@ -443,40 +455,76 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     const uint32_t a_smem = base + uint32_t(stage) * stage_bytes;
                     const uint64_t a_desc = operand_desc + (a_smem >> 4);
                     const uint64_t b_desc = a_desc + (A_TILE_BYTES >> 4);
-                    const uint32_t sfa_tmem = tmem_base + uint32_t(TMEM_COLUMNS - TMEM_SCALE_SET * (set + 1));
-                    const uint32_t sfb_tmem = sfa_tmem + TMEM_SFB_OFFSET;
+                    const uint32_t sfa_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t(set + 1);
+                    const uint32_t sfb_tmem = sfa_tmem + TMEM_SFA_COLUMNS;
                     if (KIND == B2_KIND_NVFP4) {
-                        mbar_wait(sf_full_bar + 8 * set, set_phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
-                        tc_fence_after_sync();
-                    }
-#pragma unroll
-                    for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
-                        if (j < mmas) {
-                            const uint32_t accumulate = (kb | j) != 0;
-                            if (KIND != B2_KIND_NVFP4) {
-                                mma_f8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, accumulate);
-                            } else if (split_halves) {
-                                // 64 gate + 64 up features sit in the same two columns of two different scale
-                                // blocks, and a copy can only land on a multiple of four columns: the blocks stay
-                                // apart and each half gets its own MMA (gate -> columns [0,64), up -> [64,128)).
-                                mma_nvf4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc_half, sfa_tmem + j * 4,
-                                         sfb_tmem + j * 8 + scale_column, accumulate);
-                                mma_nvf4(d_tmem + 64, a_desc + 2 * j, b_desc + ((64 * STAGE_K_BYTES) >> 4) + 2 * j, idesc_half,
-                                         sfa_tmem + j * 4, sfb_tmem + j * 8 + 4 + scale_column, accumulate);
-                            } else {
-                                mma_nvf4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, sfa_tmem + j * 4,
-                                         sfb_tmem + j * 8 + scale_column, accumulate);
-                            }
+                        if (issued >= args.scale_sets) {
+                            mbar_wait(empty_bar + 8 * lag_stage, lag_phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
+                            tc_fence_after_sync();
+                            if (++lag_stage == args.stages) { lag_stage = 0; lag_phase ^= 1u; }
                         }
+                        ++issued;
+#ifdef B2_TRACE
+                        if ((args.flags & 0x4000) && issued > 1) {      // debug: previous stage's MMAs complete before these copies
+                            const int previous = stage == 0 ? args.stages - 1 : stage - 1;
+                            mbar_wait(empty_bar + 8 * previous, stage == 0 ? phase ^ 1u : phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
+                            tc_fence_after_sync();
+                        }
+#endif
                     }
+                    __syncwarp();
+                    TRACE(2, trace_index);
+                    if (elect_one()) {
+                        // shared memory: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
+                        const uint64_t atom_desc = scale_desc + ((scale_base + uint32_t(stage) * scale_stage_bytes) >> 4);
+                        constexpr uint64_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
+                        const bool two_blocks = args.scale_blocks == 2;
+                        const uint32_t first_accumulate = kb != 0;
+                        // `count` is a literal on the full-stage path, so its loop carries no per-step conditions.
+                        auto issue = [&](const int count) {
+                            if (KIND == B2_KIND_NVFP4) {
+#pragma unroll
+                                for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
+                                    if (j < count) {
+                                        tc_copy_32x128b_x4(sfa_tmem + j * 4, atom_desc + j * ATOM);
+                                        tc_copy_32x128b_x4(sfb_tmem + j * sfb_stride, atom_desc + PART + j * ATOM);
+                                        if (two_blocks)
+                                            tc_copy_32x128b_x4(sfb_tmem + j * sfb_stride + 4, atom_desc + 2 * PART + j * ATOM);
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
+                                if (j < count) {
+                                    const uint32_t accumulate = j == 0 ? first_accumulate : 1u;
+                                    if (KIND != B2_KIND_NVFP4) {
+                                        mma_f8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, accumulate);
+                                    } else if (split_halves) {
+                                        // 64 gate + 64 up features sit in the same two columns of two different scale
+                                        // blocks, and a copy can only land on a multiple of four columns: the blocks stay
+                                        // apart and each half gets its own MMA (gate -> columns [0,64), up -> [64,128)).
+                                        mma_nvf4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc_half, sfa_tmem + j * 4,
+                                                 sfb_tmem + j * sfb_stride + scale_column, accumulate);
+                                        mma_nvf4(d_tmem + 64, a_desc + 2 * j, b_desc + ((64 * STAGE_K_BYTES) >> 4) + 2 * j, idesc_half,
+                                                 sfa_tmem + j * 4, sfb_tmem + j * sfb_stride + 4 + scale_column, accumulate);
+                                    } else {
+                                        mma_nvf4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, sfa_tmem + j * 4,
+                                                 sfb_tmem + j * sfb_stride + scale_column, accumulate);
+                                    }
+                                }
+                            }
+                        };
+                        if (mmas == SCALE_ATOMS_PER_STAGE) issue(SCALE_ATOMS_PER_STAGE);
+                        else issue(mmas);
                     tc_commit(empty_bar + 8 * stage);
-                    if (KIND == B2_KIND_NVFP4) {
-                        tc_commit(sf_empty_bar + 8 * set);
-                        if (++set == args.scale_sets) { set = 0; set_phase ^= 1u; }
                     }
+                    __syncwarp();
+                    TRACE(3, trace_index); ++trace_index;
+                    if (KIND == B2_KIND_NVFP4 && ++set == args.scale_sets) set = 0;
                     if (++stage == args.stages) { stage = 0; phase ^= 1u; }
                 }
-                tc_commit(acc_full_bar + 8 * buffer);
+                if (elect_one()) tc_commit(acc_full_bar + 8 * buffer);
+                __syncwarp();
             }
         }
     } else {
@@ -510,6 +558,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             const uint32_t use = uint32_t(local_tile / args.accumulators);
             mbar_wait(acc_full_bar + 8 * buffer, use & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
             tc_fence_after_sync();
+            if (warp == FIRST_EPILOGUE_WARP) TRACE(4, local_tile);
             const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer * args.accumulator_stride);
             const bool warp_has_tokens = m_tile * TILE_TOKENS + quarter * 32 < args.tokens;   // else: padding rows only
             if (GEGLU) {
@@ -535,6 +584,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buffer);
+            if (warp == FIRST_EPILOGUE_WARP) TRACE(5, local_tile);
         }
     }
 
@@ -594,8 +644,8 @@ int sm_count() {
 }
 
 // Two accumulators fit (beside the NVFP4 scale columns)?
-static bool can_double_buffer(int kind, int tile_n) {
-    return 2 * tile_n <= (kind == B2_KIND_NVFP4 ? TMEM_COLUMNS - 2 * TMEM_SCALE_SET : TMEM_COLUMNS);
+static bool can_double_buffer(int kind, int tile_n, int scale_blocks = 2) {
+    return 2 * tile_n <= (kind == B2_KIND_NVFP4 ? TMEM_COLUMNS - 2 * (TMEM_SFA_COLUMNS + 16 * scale_blocks) : TMEM_COLUMNS);
 }
 
 // LINEAR: 64, 128, 192 or 256 features per tile.  GEGLU: 64 or 128 features (128 or 256 columns).
@@ -690,9 +740,9 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
     args.tile_n = geglu ? 2 * feature_tile : feature_tile;
     args.num_n_tiles = (d->features + feature_tile - 1) / feature_tile;
     args.total_tiles = args.num_m_tiles * args.num_n_tiles;
-    args.accumulators = can_double_buffer(d->kind, args.tile_n) ? 2 : 1;
+    args.scale_blocks = paired ? 1 : (geglu || args.tile_n > 128) ? 2 : 1;   // 128-row blocks of feature scales per tile
+    args.accumulators = can_double_buffer(d->kind, args.tile_n, args.scale_blocks) ? 2 : 1;
     args.accumulator_stride = nvfp4 ? args.tile_n : 256;     // the second accumulator starts on a multiple of the tile width
-    args.scale_sets = !nvfp4 ? 1 : (args.accumulators * args.tile_n + 3 * TMEM_SCALE_SET <= TMEM_COLUMNS ? 3 : 2);
     args.up_row_offset = d->features;
     args.scale_column_tiles = nvfp4 ? (d->width / 16 + 3) / 4 : 0;
     args.act_row_blocks = (d->tokens + 127) / 128;
@@ -726,6 +776,13 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) return B2_E_UNSUPPORTED;
     args.stages = stages;
+    args.scale_sets = 1;
+    if (nvfp4) {
+        const int free_columns = TMEM_COLUMNS - args.accumulators * args.accumulator_stride;
+        args.scale_sets = free_columns / (TMEM_SFA_COLUMNS + 16 * args.scale_blocks);
+        if (args.scale_sets > stages) args.scale_sets = stages;
+        if (args.scale_sets < 2) return B2_E_UNSUPPORTED;
+    }
     int shared_bytes = fixed_bytes + stages * (stage_bytes + scale_stage_bytes);
     if (shared_bytes < SMEM_MINIMUM) shared_bytes = SMEM_MINIMUM;
 

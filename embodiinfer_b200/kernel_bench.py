@@ -1,0 +1,250 @@
+"""Per-kernel timings on one B200: the quantisers, the stand-alone gated epilogue and the tensor-core
+Linear at the shapes of the pi0.5-style towers.  One JSON line per case.
+
+    python -m embodiinfer_b200.kernel_bench                       # every case
+    python -m embodiinfer_b200.kernel_bench --case 'linear/fp8'   # cases whose name matches the regex
+    python -m embodiinfer_b200.kernel_bench --case cfg1 --library # also time torch's scaled_mm on the same shape
+
+Method: each case is launched ``--launches`` times inside one CUDA graph, rotating over as many
+operand sets as it takes to exceed the L2 capacity (capped at 16 sets; ``"l2": "warm"`` marks the
+cases whose rotation stays below it), the graph is replayed for 0.5 s to settle the clocks and then
+timed with CUDA events.  ``gbs`` counts each operand and result once (algorithmic bytes), ``tflops``
+is 2*M*N*K.  Operands are random codes: the timings do not depend on values.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import re
+import time
+
+import torch
+
+from . import _native as N
+from . import kernels as K
+from .backend.activation import gelu_table
+
+L2_BYTES = 126 * 2**20
+MAX_SETS = 16
+
+
+def _codes(shape, device):
+    return torch.randint(0, 255, shape, device=device, dtype=torch.uint8) & 0x77      # no NaN codes
+
+
+def _scale_codes(shape, device):
+    return torch.randint(40, 72, shape, device=device, dtype=torch.uint8)              # e4m3 around 1
+
+
+def _blocked_bytes(rows: int, blocks: int) -> int:
+    return -(-rows // 128) * 128 * (-(-blocks // 4) * 4)
+
+
+def time_graph(make, set_bytes: int, launches: int, settle: float = 0.5) -> tuple[float, int]:
+    """Average microseconds per launch; ``make(i)`` returns the launch closure of operand set ``i``."""
+    sets = max(1, min(MAX_SETS, -(-2 * L2_BYTES // max(set_bytes, 1))))
+    closures = [make(index) for index in range(sets)]
+    for closure in closures[:2]:
+        closure()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+        for index in range(launches):
+            closures[index % sets]()
+    torch.cuda.synchronize()
+    begin = time.time()
+    while time.time() - begin < settle:
+        graph.replay()
+        torch.cuda.synchronize()
+    replays = 20
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e3 / (replays * launches), sets
+
+
+# ---- cases -----------------------------------------------------------------------------------
+
+def quantiser_cases(device):
+    for rows in (560, 17920):
+        columns = 2048
+        count = rows * columns
+
+        def amax(_i, rows=rows):
+            x = torch.randn((rows, columns), device=device).to(torch.bfloat16)
+            scratch, scale = K.new_scale_scratch(device), torch.ones((), device=device)
+            return lambda: K.tensor_scale(x, 448.0, N.SCALAR_RCP, scratch, scale)
+
+        def fp8(flags):
+            def make(_i, rows=rows):
+                x = torch.randn((rows, columns), device=device).to(torch.bfloat16)
+                out, scale = torch.empty((rows, columns), device=device, dtype=torch.uint8), torch.full((), 0.01, device=device)
+                return lambda: K.fp8_quantize(x, out, scale, flags)
+            return make
+
+        def nvfp4(flags):
+            def make(_i, rows=rows):
+                x = torch.randn((rows, columns), device=device).to(torch.bfloat16)
+                out = torch.empty((rows, columns // 2), device=device, dtype=torch.uint8)
+                blocked = torch.zeros(_blocked_bytes(rows, columns // 16), device=device, dtype=torch.uint8)
+                scale = torch.full((), 0.002, device=device)
+                return lambda: K.nvfp4_quantize(x, out, None, blocked, scale, flags)
+            return make
+
+        yield f"quant/tensor_scale/{rows}x{columns}", amax, 2 * count, 2 * count, 0
+        yield f"quant/fp8_C/{rows}x{columns}", fp8(N.SPEC_C), 3 * count, 3 * count, 0
+        yield f"quant/fp8_T/{rows}x{columns}", fp8(N.SPEC_T | N.DIVISOR_BF16), 3 * count, 3 * count, 0
+        nv = 2 * count + count // 2 + count // 16
+        yield f"quant/nvfp4_C/{rows}x{columns}", nvfp4(N.SPEC_C), nv, nv, 0
+        yield f"quant/nvfp4_T/{rows}x{columns}", nvfp4(N.SPEC_T | N.SCALAR_RCP), nv, nv, 0
+
+
+def geglu_cases(device):
+    rows, features = 560, 16384
+    table = gelu_table(device, "tanh")
+    for bits, out_bytes in ((16, 2.0), (8, 1.0), (4, 0.5 + 1 / 16)):
+        def make(_i, bits=bits):
+            packed = torch.randn((rows, 2 * features), device=device).to(torch.bfloat16)
+            gate, up = packed[:, :features], packed[:, features:]
+            out = torch.empty((rows, features * (2 if bits == 16 else 1) // (2 if bits == 4 else 1)), device=device, dtype=torch.uint8)
+            scale = torch.full((), 0.01, device=device)
+            blocked = torch.zeros(_blocked_bytes(rows, features // 16), device=device, dtype=torch.uint8) if bits == 4 else None
+            return lambda: K.geglu(gate, up, out, bits=bits, table=table, rows=rows, columns=features, row_stride=2 * features,
+                                   scale=scale, blocked=blocked)
+        total = int(rows * features * (4 + out_bytes))
+        yield f"geglu/standalone_bits{bits}/{rows}x{features}", make, total, total, 0
+
+
+LINEAR_SHAPES = [
+    # name, kind, M, N (features; GEGLU: gate features), K, epilogue
+    ("cfg1_fp8_560x16384x2048", "fp8", 560, 16384, 2048, "linear"),
+    ("cfg2_nvfp4_gate_up_geglu_560x2x16384x2048", "nvfp4", 560, 16384, 2048, "geglu"),
+    ("cfg2_nvfp4_down_560x2048x16384", "nvfp4", 560, 2048, 16384, "linear"),
+    ("nvfp4_gate_up_plain_560x32768x2048", "nvfp4", 560, 32768, 2048, "linear"),
+    ("fp8_gate_up_geglu_560x2x16384x2048", "fp8", 560, 16384, 2048, "geglu"),
+    ("fp8_down_560x2048x16384", "fp8", 560, 2048, 16384, "linear"),
+    ("prefix_qkv_fp8_560x2560x2048", "fp8", 560, 2560, 2048, "linear"),
+    ("prefix_o_fp8_560x2048x2048", "fp8", 560, 2048, 2048, "linear"),
+    ("prefix_qkv_nvfp4_560x2560x2048", "nvfp4", 560, 2560, 2048, "linear"),
+    ("siglip_qkv_fp8_8192x3456x1152", "fp8", 8192, 3456, 1152, "linear"),
+    ("siglip_fc1_fp8_8192x4304x1152", "fp8", 8192, 4304, 1152, "linear"),
+    ("siglip_fc2_fp8_8192x1152x4304", "fp8", 8192, 1152, 4304, "linear"),
+    ("prefix_mb16_gate_up_fp8_geglu_8960x2x16384x2048", "fp8", 8960, 16384, 2048, "geglu"),
+    ("prefix_mb16_down_fp8_8960x2048x16384", "fp8", 8960, 2048, 16384, "linear"),
+] + [
+    (f"expert_B{batch}_{name}_{kind}_{10 * batch}x{n}x{k}", kind, 10 * batch, n, k, epilogue)
+    for batch in (1, 8, 64) for kind in ("fp8", "nvfp4")
+    for name, n, k, epilogue in (("qkv", 2560, 1024, "linear"), ("o", 1024, 2048, "linear"),
+                                 ("gate_up_geglu", 4096, 1024, "geglu"), ("down", 1024, 4096, "linear"))
+]
+
+
+def linear_cases(device):
+    table = gelu_table(device, "tanh")
+    table_range = K.gelu_table_range(table)
+    for name, kind, tokens, features, width, epilogue in LINEAR_SHAPES:
+        gated = epilogue == "geglu"
+        rows = 2 * features if gated else features
+        operand = 1.0 if kind == "fp8" else 0.5 + 1 / 16
+        out_bytes = (1.0 if kind == "fp8" else 0.5 + 1 / 16) if gated else 2.0
+        total = int(tokens * width * operand + rows * width * operand + tokens * features * out_bytes)
+
+        def make(_i, kind=kind, tokens=tokens, features=features, width=width, gated=gated, rows=rows):
+            one = torch.ones((), device=device)
+            status = torch.zeros(4, device=device, dtype=torch.int32)
+            arguments = dict(tokens=tokens, features=features, width=width, act_scale=one, weight_scale=one, status=status)
+            if kind == "fp8":
+                arguments.update(kind=N.KIND_FP8, act=_codes((tokens, width), device), weight=_codes((rows, width), device))
+            else:
+                arguments.update(
+                    kind=N.KIND_NVFP4, act=_codes((tokens, width // 2), device), weight=_codes((rows, width // 2), device),
+                    act_scales=_scale_codes((_blocked_bytes(tokens, width // 16),), device),
+                    weight_scales=_scale_codes((_blocked_bytes(rows, width // 16),), device))
+            if gated:
+                out_format = N.OUT_FP8 if kind == "fp8" else N.OUT_NVFP4
+                out = torch.empty((tokens, features if kind == "fp8" else features // 2), device=device, dtype=torch.uint8)
+                arguments.update(epilogue=N.EPI_GEGLU, out_format=out_format, out=out, gelu_table=table, gelu_range=table_range,
+                                 out_scale=torch.full((), 0.01, device=device))
+                if kind == "nvfp4":
+                    arguments.update(flags=N.LINEAR_PAIRED_GATE_UP_SCALES)
+                    arguments.update(out_blocked=torch.zeros(_blocked_bytes(tokens, features // 16), device=device, dtype=torch.uint8))
+            else:
+                arguments.update(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16,
+                                 out=torch.empty((tokens, features), device=device, dtype=torch.bfloat16))
+            return lambda: K.linear(**arguments)
+
+        yield f"linear/{name}", make, total, total, 2.0 * tokens * rows * width
+
+
+def library_time(kind: str, tokens: int, rows: int, width: int, device, launches: int) -> float | None:
+    """torch's scaled_mm (the GEMM the reference calls on this GPU) at the same shape; None when this
+    torch build has no such kernel for the operand type."""
+    try:
+        if kind == "fp8":
+            def make(_i):
+                a = _codes((tokens, width), device).view(torch.float8_e4m3fn)
+                w = _codes((rows, width), device).view(torch.float8_e4m3fn)
+                one = torch.ones((), device=device)
+                return lambda: torch._scaled_mm(a, w.t(), one, one, out_dtype=torch.bfloat16)
+            set_bytes = tokens * width + rows * width + 2 * tokens * rows
+        else:
+            def make(_i):
+                a = _codes((tokens, width // 2), device).view(torch.float4_e2m1fn_x2)
+                w = _codes((rows, width // 2), device).view(torch.float4_e2m1fn_x2)
+                sa = _scale_codes((_blocked_bytes(tokens, width // 16),), device).view(torch.float8_e4m3fn)
+                sw = _scale_codes((_blocked_bytes(rows, width // 16),), device).view(torch.float8_e4m3fn)
+                return lambda: torch._scaled_mm(a, w.t(), sa, sw, out_dtype=torch.bfloat16)
+            set_bytes = (tokens + rows) * width // 2 + 2 * tokens * rows
+        return time_graph(make, set_bytes, launches)[0]
+    except Exception as error:                      # no kernel for this type/shape in this torch build
+        print(json.dumps({"library_unavailable": f"{kind}: {type(error).__name__}: {str(error)[:120]}"}))
+        return None
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--case", default=".", help="regex over case names")
+    parser.add_argument("--launches", type=int, default=32)
+    parser.add_argument("--library", action="store_true", help="also time torch's scaled_mm at each linear shape")
+    parser.add_argument("--list", action="store_true")
+    args = parser.parse_args()
+    pattern = re.compile(args.case)
+    if args.list:
+        for name, *_ in LINEAR_SHAPES:
+            print("linear/" + name)
+        return
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    peaks = {"hbm_gbs": 6541.5, "fp8_tflops": 4500.0, "nvfp4_tflops": 9000.0}
+    for source in (quantiser_cases, geglu_cases, linear_cases):
+        for name, make, set_bytes, algorithmic_bytes, flops in source(device):
+            if not pattern.search(name):
+                continue
+            microseconds, sets = time_graph(make, set_bytes, args.launches)
+            line = {"case": name, "us": round(microseconds, 2), "gbs": round(algorithmic_bytes / microseconds / 1e3, 1),
+                    "sets": sets, "l2": "cold" if sets * set_bytes >= L2_BYTES else "warm"}
+            if flops:
+                line["tflops"] = round(flops / microseconds / 1e6, 1)
+                nominal = peaks["fp8_tflops"] if "fp8" in name else peaks["nvfp4_tflops"]
+                line["frac_of_nominal_tensor_peak"] = round(line["tflops"] / nominal, 3)
+                if args.library:
+                    _, kind, tokens, features, width, epilogue = next(s for s in LINEAR_SHAPES if "linear/" + s[0] == name)
+                    rows = 2 * features if epilogue == "geglu" else features
+                    library = library_time(kind, tokens, rows, width, device, args.launches)
+                    if library is not None:
+                        line["torch_scaled_mm_us"] = round(library, 2)
+                        line["torch_scaled_mm_tflops"] = round(flops / library / 1e6, 1)
+            else:
+                line["frac_of_measured_hbm"] = round(line["gbs"] / peaks["hbm_gbs"], 3)
+            print(json.dumps(line), flush=True)
+            torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

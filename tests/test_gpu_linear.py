@@ -136,6 +136,24 @@ def test_gated_epilogues(device, kind, tokens, features, width, tile):
     assert np.array_equal(u8(out4), want4[0]) and np.array_equal(u8(linear), want4[1]) and np.array_equal(u8(blocked), want4[2])
 
 
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+def test_gated_zero_gate_reads_the_full_table(device, kind):
+    """A gate of exactly zero lies below every compact range and, with no range at all, must still come
+    from the table: zero activations give gelu(0) * 0 = 0 everywhere."""
+    tokens, features, width = 200, 256, 512
+    host, dev = operands(kind, tokens, 2 * features, width, 5, device)
+    dev["act"] = torch.zeros_like(dev["act"])
+    table = torch.from_numpy(gelu_table_cpu("tanh").view(np.int16).copy()).view(torch.uint16).to(device)
+    # dirty the shared memory of every SM first: 200 KB of non-zero bytes per CTA
+    K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=2 * features, width=width,
+             out=torch.empty((tokens, 2 * features), device=device, dtype=torch.bfloat16), **operands(kind, tokens, 2 * features, width, 6, device)[1])
+    for table_range in ((0, 0), K.gelu_table_range(table)):
+        hidden = torch.full((tokens, features), 7.0, device=device, dtype=torch.bfloat16)
+        K.linear(epilogue=N.EPI_GEGLU, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=hidden,
+                 gelu_table=table, gelu_range=table_range, **dev)
+        assert not (bits(hidden) & 0x7fff).any()
+
+
 def test_gated_with_separate_up_scale(device):
     """gate and up quantised separately (two per-tensor scales) give the same result as two Linears."""
     tokens, features, width = 96, 128, 256
