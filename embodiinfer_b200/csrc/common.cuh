@@ -26,6 +26,22 @@ __device__ __forceinline__ uint4 ld_nc_u4(const uint4* pointer) {
     return value;
 }
 
+// 32-byte vector access (sm_100): one full DRAM/L2 sector per lane and instruction.  The address must be
+// 32-byte aligned.
+__device__ __forceinline__ void ld_nc_u8(const void* pointer, uint32_t (&v)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "l"(pointer));
+}
+
+__device__ __forceinline__ void st_u8(void* pointer, const uint32_t (&v)[8]) {
+    asm volatile("st.global.v8.u32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(pointer), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+
+__device__ __forceinline__ bool aligned32(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 31u) == 0; }
+
 __device__ __forceinline__ float bf16_lo(uint32_t word) { return __uint_as_float(word << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t word) { return __uint_as_float(word & 0xffff0000u); }
 
@@ -43,6 +59,32 @@ __device__ __forceinline__ float abs_max_bf16x8(const uint4& packed) {
 #pragma unroll
     for (int i = 1; i < 8; ++i) maximum = fmaxf(maximum, fabsf(v[i]));
     return maximum;
+}
+
+// Two bf16 values in one word <-> two floats (low half first).
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t word) { return make_float2(bf16_lo(word), bf16_hi(word)); }
+
+__device__ __forceinline__ uint32_t float2_to_bf16x2(float2 value) {
+    uint32_t packed;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(value.y), "f"(value.x));
+    return packed;
+}
+
+// max(|a|, |b|) per 16-bit half, NaN-ignoring like fmaxf.
+__device__ __forceinline__ uint32_t abs_max_bf16x2(uint32_t a, uint32_t b) {
+    const uint32_t x = a & 0x7fff7fffu, y = b & 0x7fff7fffu;
+    uint32_t result;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(result) : "r"(x), "r"(y));
+    return result;
+}
+
+// Largest magnitude among the 2*WORDS bf16 values of `words`.
+template <int WORDS>
+__device__ __forceinline__ float abs_max_bf16_words(const uint32_t (&words)[WORDS]) {
+    uint32_t m = abs_max_bf16x2(words[0], WORDS > 1 ? words[1] : words[0]);
+#pragma unroll
+    for (int i = 2; i < WORDS; ++i) m = abs_max_bf16x2(m, words[i]);
+    return fmaxf(bf16_lo(m), bf16_hi(m));
 }
 
 __device__ __forceinline__ float round_to_bf16(float value) {
@@ -95,6 +137,13 @@ struct ExactDivider {
         const float q = __fmul_rn(a, reciprocal);
         return copysignf(__fmaf_rn(__fmaf_rn(-q, divisor, a), reciprocal, q), a);
     }
+    // Two quotients at once on the packed fp32 pipe (same arithmetic per lane as `unchecked`).
+    __device__ __forceinline__ float2 unchecked2(float2 a) const {
+        const float2 r = make_float2(reciprocal, reciprocal), negative = make_float2(-divisor, -divisor);
+        const float2 q = __fmul2_rn(a, r);
+        const float2 o = __ffma2_rn(__ffma2_rn(q, negative, a), r, q);
+        return make_float2(copysignf(o.x, a.x), copysignf(o.y, a.y));
+    }
     __device__ __forceinline__ float operator()(float a) const {
         if (fast && fabsf(a) < 1.0e30f) {
             const float q = __fmul_rn(a, reciprocal);
@@ -132,6 +181,32 @@ __device__ __forceinline__ uint32_t encode_fp8x4(float a, float b, float c, floa
     return low | (high << 16);
 }
 
+// Two bf16 values (one word) -> two e4m3 bytes on the divider's short path (caller checked: `scale.fast`
+// and |x| <= 1024*scale for both, or x is NaN).  Dropping the reference's clamp to +-448 of spec T changes
+// nothing: the saturating conversion maps every finite value beyond 448 and both infinities to +-448 too.
+template <bool SPEC_C>
+__device__ __forceinline__ uint32_t encode_fp8x2_short(uint32_t word, const ExactDivider& scale) {
+    float2 q = scale.unchecked2(bf16x2_to_float2(word));
+    if (!SPEC_C) q = bf16x2_to_float2(float2_to_bf16x2(q));
+    return uint32_t(__nv_cvt_float2_to_fp8x2(q, __NV_SATFINITE, __NV_E4M3));
+}
+
+// 2*WORDS bf16 values -> e4m3 bytes, WORDS/2 output words.  One magnitude test per vector picks the short
+// path; vectors holding a value beyond 1024*scale (which saturates whatever it is) take the general one.
+template <bool SPEC_C, int WORDS>
+__device__ __forceinline__ void encode_fp8_words(const uint32_t (&in)[WORDS], uint32_t (&out)[WORDS / 2],
+                                                 const ExactDivider& scale, float short_path_bound) {
+    if (scale.fast && abs_max_bf16_words(in) <= short_path_bound) {
+#pragma unroll
+        for (int i = 0; i < WORDS / 2; ++i)
+            out[i] = encode_fp8x2_short<SPEC_C>(in[2 * i], scale) | (encode_fp8x2_short<SPEC_C>(in[2 * i + 1], scale) << 16);
+    } else {
+#pragma unroll
+        for (int i = 0; i < WORDS / 2; ++i)
+            out[i] = encode_fp8x4<SPEC_C>(bf16_lo(in[2 * i]), bf16_hi(in[2 * i]), bf16_lo(in[2 * i + 1]), bf16_hi(in[2 * i + 1]), scale);
+    }
+}
+
 // Same, but the caller supplies already-divided values (used by fused epilogues).
 __device__ __forceinline__ uint32_t pack_fp8x4(float a, float b, float c, float d) {
     const uint32_t low = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
@@ -166,6 +241,37 @@ __device__ __forceinline__ uint32_t e2m1_bucketize(float value) {
                          uint32_t(a > 2.5f) + uint32_t(a > 3.5f) + uint32_t(a > 5.0f);
     if (a != a) magnitude = 7u;
     return magnitude | (value < 0.0f ? 8u : 0u);
+}
+
+// Same code as e2m1_bucketize without the seven comparisons.  Below 2 the e2m1 grid is uniform (step 0.5)
+// and "ties toward zero" is ceil(2a - 0.5), exact in fp32 for a >= 0.25 and of the right sign below; from
+// 2 up the code is the float's exponent and top mantissa bit after a round-half-down of the bits beneath
+// (adding 0x1fffff, one less than half a step, so exact ties do not carry).  Values beyond 6, infinities
+// and NaN (whose bit pattern exceeds every number's) end at 7.
+__device__ __forceinline__ uint32_t e2m1_bucketize_fast(float value) {
+    const float a = fabsf(value);
+    const uint32_t low = uint32_t(__float2int_ru(__fmaf_rn(a, 2.0f, -0.5f)));
+    const uint32_t high = ((__float_as_uint(a) + 0x1fffffu) >> 22) - 252u;
+    const uint32_t magnitude = min(a < 2.0f ? low : high, 7u);
+    return magnitude | (value < 0.0f ? 8u : 0u);
+}
+
+// Eight bf16 values in four words -> eight nibbles, on the divider's short path (caller checked
+// `denominator.fast` and that block_max / denominator is finite).
+template <bool SPEC_C>
+__device__ __forceinline__ uint32_t nvfp4_encode_words_short(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3,
+                                                            const ExactDivider& denominator) {
+    const uint32_t words[4] = {w0, w1, w2, w3};
+    uint32_t codes = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 q = denominator.unchecked2(bf16x2_to_float2(words[i]));
+        uint32_t byte;
+        if (SPEC_C) byte = uint32_t(__nv_cvt_float2_to_fp4x2(q, __NV_E2M1, cudaRoundNearest)) & 0xffu;
+        else byte = e2m1_bucketize_fast(q.x) | (e2m1_bucketize_fast(q.y) << 4);
+        codes |= byte << (8 * i);
+    }
+    return codes;
 }
 
 // Eight values of one half-block -> eight nibbles, first value in the lowest nibble.

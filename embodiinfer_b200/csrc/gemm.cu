@@ -107,21 +107,27 @@ __device__ __forceinline__ void store_u4(void* pointer, uint32_t a, uint32_t b, 
     *reinterpret_cast<uint4*>(pointer) = make_uint4(a, b, c, d);
 }
 
-// 32 accumulator columns of one token -> 32 bf16 outputs (64 contiguous bytes).
+// 32 accumulator columns of one token -> 32 bf16 outputs (64 contiguous bytes): one packed multiply and
+// one two-value conversion per pair, 32-byte stores where the row allows them.
 __device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32], const KernelArgs& args, float scale,
                                                       bool round_scale, int token, int feature0) {
-    float y[32];
+    uint32_t y[16];                                   // bf16 pairs
+    const float2 scale2 = make_float2(scale, scale);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) y[i] = gemm_value(acc[i], scale, round_scale);
+    for (int p = 0; p < 16; ++p) {
+        float2 value = make_float2(__uint_as_float(acc[2 * p]), __uint_as_float(acc[2 * p + 1]));
+        if (round_scale) value = bf16x2_to_float2(float2_to_bf16x2(value));     // nvfp4.py:120: the GEMM's own bf16 output
+        y[p] = float2_to_bf16x2(__fmul2_rn(value, scale2));
+    }
     if (args.bias != nullptr) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
             if (feature0 + 8 * v < args.features) {
                 const uint4 packed = __ldg(reinterpret_cast<const uint4*>(args.bias + feature0 + 8 * v));
-                float b[8];
-                unpack_bf16x8(packed, b);
+                const uint32_t b[4] = {packed.x, packed.y, packed.z, packed.w};
 #pragma unroll
-                for (int i = 0; i < 8; ++i) y[8 * v + i] = round_to_bf16(__fadd_rn(y[8 * v + i], b[i]));
+                for (int i = 0; i < 4; ++i)
+                    y[4 * v + i] = float2_to_bf16x2(__fadd2_rn(bf16x2_to_float2(y[4 * v + i]), bf16x2_to_float2(b[i])));
             }
         }
     }
@@ -132,19 +138,24 @@ __device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32],
         for (int v = 0; v < 4; ++v) {
             if (feature0 + 8 * v < args.features) {
                 const uint4 packed = ld_nc_u4(reinterpret_cast<const uint4*>(args.residual + row + feature0 + 8 * v));
-                float r[8];
-                unpack_bf16x8(packed, r);
+                const uint32_t r[4] = {packed.x, packed.y, packed.z, packed.w};
 #pragma unroll
-                for (int i = 0; i < 8; ++i) y[8 * v + i] = round_to_bf16(__fadd_rn(y[8 * v + i], r[i]));
+                for (int i = 0; i < 4; ++i)
+                    y[4 * v + i] = float2_to_bf16x2(__fadd2_rn(bf16x2_to_float2(y[4 * v + i]), bf16x2_to_float2(r[i])));
             }
         }
     }
     __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out) + row + feature0;
+    if (feature0 + 32 <= args.features && aligned32(out)) {
+        const uint32_t first[8] = {y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]};
+        const uint32_t second[8] = {y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]};
+        st_u8(out, first);
+        st_u8(out + 16, second);
+        return;
+    }
 #pragma unroll
     for (int v = 0; v < 4; ++v)
-        if (feature0 + 8 * v < args.features)
-            store_u4(out + 8 * v, pack_bf16x2(y[8 * v], y[8 * v + 1]), pack_bf16x2(y[8 * v + 2], y[8 * v + 3]),
-                     pack_bf16x2(y[8 * v + 4], y[8 * v + 5]), pack_bf16x2(y[8 * v + 6], y[8 * v + 7]));
+        if (feature0 + 8 * v < args.features) store_u4(out + 8 * v, y[4 * v], y[4 * v + 1], y[4 * v + 2], y[4 * v + 3]);
 }
 
 // bf16 pair from two floats in one conversion: low half = `low`, high half = `high`.
@@ -154,35 +165,66 @@ __device__ __forceinline__ uint32_t cvt_bf16x2(float high, float low) {
     return packed;
 }
 
-// GELU of a bf16 bit pattern (low 16 bits of `gate_bits`), as a float.  Magnitude codes [lo, hi) come
-// from the shared-memory copy of the table ([positive | negative] halves).  Below lo the table equals
-// bf16(x/2); from hi up to the largest finite value it equals x (positive) or -0 (negative): the host
-// verified both against the table before choosing lo and hi.  Subnormals, infinities, NaNs (and every
-// value when no range was supplied) read the full table in global memory.
-__device__ __forceinline__ float gelu_lookup(uint32_t gate_bits, const KernelArgs& args, uint32_t compact_table,
-                                             uint32_t lo, uint32_t span) {
-    const uint32_t magnitude = gate_bits & 0x7fffu;
+// GELU of one bf16 bit pattern (16 bits), as bf16 bits.  Magnitude codes [lo, lo + span) come from the
+// shared-memory copy of the table ([positive | negative] halves).  Below lo the table equals bf16(x/2);
+// from lo + span up to the largest finite value it equals x (positive) or -0 (negative): the host verified
+// both against the table before choosing the range.  Subnormals, infinities, NaNs (and every value when
+// no range was supplied, span == 0) read the full table in global memory.
+__device__ __forceinline__ uint32_t gelu_lookup_general(uint32_t code, const KernelArgs& args, uint32_t compact_table,
+                                                        uint32_t lo, uint32_t span) {
+    const uint32_t magnitude = code & 0x7fffu;
     const uint32_t offset = magnitude - lo;
-    const uint32_t negative = (gate_bits >> 15) & 1u;
-    uint32_t value;
-    // unconditional shared-memory read at a clamped index keeps the common case free of branches
-    // (span == 0: no range was supplied; the read is harmless and its value is never used)
-    const uint32_t slot = min(offset, span == 0u ? 0u : span - 1u) + negative * span;
-    asm("ld.shared.u16 %0, [%1];" : "=r"(value) : "r"(compact_table + 2u * slot));
-    if (offset >= span) {                                   // rare: outside the stored range
-        if (span != 0u && magnitude >= 0x80u && magnitude < 0x7f80u) {
-            const float x = __uint_as_float(gate_bits << 16);
-            value = magnitude < lo ? uint32_t(bf16_bits(__fmul_rn(0.5f, x))) : (negative ? 0x8000u : (gate_bits & 0xffffu));
-        } else {
-            value = uint32_t(__ldg(args.gelu_table + (gate_bits & 0xffffu)));
-        }
+    const uint32_t negative = code >> 15;
+    if (offset < span) {
+        uint32_t value;
+        asm("ld.shared.u16 %0, [%1];" : "=r"(value) : "r"(compact_table + 2u * (offset + negative * span)));
+        return value;
     }
-    return __uint_as_float(value << 16);
+    if (span != 0u && magnitude >= 0x80u && magnitude < 0x7f80u) {
+        const float x = __uint_as_float(code << 16);
+        return magnitude < lo ? uint32_t(bf16_bits(__fmul_rn(0.5f, x))) : (negative ? 0x8000u : code);
+    }
+    return uint32_t(__ldg(args.gelu_table + code));
+}
+
+// The sixteen gates of one unit as eight bf16x2 words -> their GELUs as eight bf16x2 words.  One test per
+// unit (two adds per word: a magnitude m is >= lo iff m + (0x8000 - lo) carries into bit 15, and < hi iff
+// m + (0x8000 - hi) does not) picks between straight-line shared-memory lookups and the general path.
+__device__ __forceinline__ void gelu_lookup_unit(const uint32_t (&gate)[8], uint32_t (&gelu)[8], const KernelArgs& args,
+                                                 uint32_t compact_table, uint32_t lo, uint32_t span) {
+    const uint32_t above_lo = (0x8000u - lo) * 0x10001u, above_hi = (0x8000u - (lo + span)) * 0x10001u;
+    uint32_t reach_lo = 0xffffffffu, reach_hi = 0u;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        const uint32_t magnitudes = gate[p] & 0x7fff7fffu;
+        reach_lo &= magnitudes + above_lo;
+        reach_hi |= magnitudes + above_hi;
+    }
+    if (span != 0u && ((~reach_lo | reach_hi) & 0x80008000u) == 0u) {
+        // address of code c: table + 2*(c - lo) for positive c, table + 2*(c - 0x8000 - lo + span) for negative
+        const uint32_t origin = compact_table - 2u * lo;
+        const uint32_t fold = 0x10000u - 2u * span;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) {
+            const uint32_t first = gate[p] & 0xffffu, second = gate[p] >> 16;
+            uint32_t low, high;
+            asm("ld.shared.u16 %0, [%1];" : "=r"(low) : "r"(origin + 2u * first - (first >> 15) * fold));
+            asm("ld.shared.u16 %0, [%1];" : "=r"(high) : "r"(origin + 2u * second - (second >> 15) * fold));
+            gelu[p] = low | (high << 16);
+        }
+    } else {
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+            gelu[p] = gelu_lookup_general(gate[p] & 0xffffu, args, compact_table, lo, span) |
+                      (gelu_lookup_general(gate[p] >> 16, args, compact_table, lo, span) << 16);
+    }
 }
 
 // One 16-feature unit of a token's row: 16 gate + 16 up accumulator columns -> 16 hidden values
 // h = bf16(bf16(gelu(gate)) * up), stored as bf16, e4m3 or NVFP4 (fusion.cu:5-10, 31-107).  For NVFP4
-// the unit is exactly one quantisation block of the next layer's input.
+// the unit is exactly one quantisation block of the next layer's input.  Values travel as bf16 pairs:
+// the product of two bf16 numbers is exact in fp32, so the packed bf16 multiply rounds once, like the
+// reference's float multiply followed by the bf16 store.
 template <int EPI>
 __device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[16], const uint32_t (&up_acc)[16],
                                                     const KernelArgs& args, uint32_t compact_table, float scale,
@@ -191,41 +233,65 @@ __device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[1
                                                     int token, int feature0) {
     const uint32_t lo = uint32_t(args.gelu_lo);
     const uint32_t span = uint32_t(args.gelu_hi - args.gelu_lo);     // 0: every lookup reads the full table
-    float h[16];
+    const float2 scale2 = make_float2(scale, scale), scale_up2 = make_float2(scale_up, scale_up);
+    uint32_t gate[8], up[8], gelu[8], h[8];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        float gate = __uint_as_float(gate_acc[i]), up = __uint_as_float(up_acc[i]);
-        if (round_scale) { gate = round_to_bf16(gate); up = round_to_bf16(up); }
-        const uint32_t pair = cvt_bf16x2(__fmul_rn(up, scale_up), __fmul_rn(gate, scale));   // low = gate, high = up
-        const float gelu = gelu_lookup(pair, args, compact_table, lo, span);
-        h[i] = round_to_bf16(__fmul_rn(gelu, __uint_as_float(pair & 0xffff0000u)));
+    for (int p = 0; p < 8; ++p) {
+        float2 g = make_float2(__uint_as_float(gate_acc[2 * p]), __uint_as_float(gate_acc[2 * p + 1]));
+        float2 u = make_float2(__uint_as_float(up_acc[2 * p]), __uint_as_float(up_acc[2 * p + 1]));
+        if (round_scale) {
+            g = bf16x2_to_float2(float2_to_bf16x2(g));
+            u = bf16x2_to_float2(float2_to_bf16x2(u));
+        }
+        gate[p] = float2_to_bf16x2(__fmul2_rn(g, scale2));
+        up[p] = float2_to_bf16x2(__fmul2_rn(u, scale_up2));
     }
+    gelu_lookup_unit(gate, gelu, args, compact_table, lo, span);
+#pragma unroll
+    for (int p = 0; p < 8; ++p) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(h[p]) : "r"(gelu[p]), "r"(up[p]));
     if (token >= args.tokens || feature0 >= args.features) return;
     const int64_t element = int64_t(token) * args.features + feature0;
     if (EPI == EPI_GEGLU_BF16) {
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out) + element;
-#pragma unroll
-        for (int v = 0; v < 2; ++v)
-            store_u4(out + 8 * v, cvt_bf16x2(h[8 * v + 1], h[8 * v]), cvt_bf16x2(h[8 * v + 3], h[8 * v + 2]),
-                     cvt_bf16x2(h[8 * v + 5], h[8 * v + 4]), cvt_bf16x2(h[8 * v + 7], h[8 * v + 6]));
+        if (aligned32(out)) {
+            st_u8(out, h);
+        } else {
+            store_u4(out, h[0], h[1], h[2], h[3]);
+            store_u4(out + 8, h[4], h[5], h[6], h[7]);
+        }
     } else if (EPI == EPI_GEGLU_FP8) {
+        uint32_t codes[4];
+        if (true_div) {
+            encode_fp8_words<true, 8>(h, codes, out_scale, __fmul_rn(1024.0f, out_scale.divisor));
+        } else {
+            const float2 rcp2 = make_float2(out_scale_rcp, out_scale_rcp);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) h[i] = true_div ? out_scale(h[i]) : __fmul_rn(h[i], out_scale_rcp);
-        store_u4(static_cast<uint8_t*>(args.out) + element, pack_fp8x4(h[0], h[1], h[2], h[3]),
-                 pack_fp8x4(h[4], h[5], h[6], h[7]), pack_fp8x4(h[8], h[9], h[10], h[11]),
-                 pack_fp8x4(h[12], h[13], h[14], h[15]));
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t low = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(h[2 * i]), rcp2), __NV_SATFINITE, __NV_E4M3);
+                const uint32_t high = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(h[2 * i + 1]), rcp2), __NV_SATFINITE, __NV_E4M3);
+                codes[i] = low | (high << 16);
+            }
+        }
+        store_u4(static_cast<uint8_t*>(args.out) + element, codes[0], codes[1], codes[2], codes[3]);
     } else {
         // quantize.cu:85-104 arithmetic on this block
-        float block_max = fabsf(h[0]);
-#pragma unroll
-        for (int i = 1; i < 16; ++i) block_max = fmaxf(block_max, fabsf(h[i]));
+        const float block_max = abs_max_bf16_words(h);
         const uint8_t code = nvfp4_block_scale<true>(block_max, by_global, 0);
         const ExactDivider denominator(__fmul_rn(out_scale.divisor, e4m3_to_float(code)));
-        float low[8], high[8];
+        uint32_t word0, word1;
+        if (denominator.fast && __fmul_rn(block_max, denominator.reciprocal) < 1.0e30f) {
+            word0 = nvfp4_encode_words_short<true>(h[0], h[1], h[2], h[3], denominator);
+            word1 = nvfp4_encode_words_short<true>(h[4], h[5], h[6], h[7], denominator);
+        } else {
+            float low[8], high[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { low[i] = h[i]; high[i] = h[8 + i]; }
-        const uint32_t word0 = nvfp4_encode_x8<true>(low, denominator, block_max);
-        const uint32_t word1 = nvfp4_encode_x8<true>(high, denominator, block_max);
+            for (int i = 0; i < 4; ++i) {
+                low[2 * i] = bf16_lo(h[i]); low[2 * i + 1] = bf16_hi(h[i]);
+                high[2 * i] = bf16_lo(h[4 + i]); high[2 * i + 1] = bf16_hi(h[4 + i]);
+            }
+            word0 = nvfp4_encode_x8<true>(low, denominator, block_max);
+            word1 = nvfp4_encode_x8<true>(high, denominator, block_max);
+        }
         *reinterpret_cast<uint2*>(static_cast<uint8_t*>(args.out) + (element >> 1)) = make_uint2(word0, word1);
         const int block = feature0 >> 4;
         const int blocks_per_row = args.features >> 4;

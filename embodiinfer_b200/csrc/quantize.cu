@@ -87,6 +87,33 @@ fp8_encode_kernel(const uint4* __restrict__ input, uint2* __restrict__ output, i
     }
 }
 
+// Wide variant for 32-byte aligned tensors: 16 bf16 in (one 32-byte load), 16 e4m3 out (one 16-byte store)
+// per thread and step, two steps in flight per thread, packed fp32 arithmetic.
+template <bool SPEC_C>
+__global__ void __launch_bounds__(QUANT_THREADS)
+fp8_encode_wide_kernel(const uint8_t* __restrict__ input, uint4* __restrict__ output, int64_t vectors,
+                       const float* __restrict__ scale_pointer, int flags) {
+    float scale_value = __ldg(scale_pointer);
+    if (!SPEC_C && (flags & B2_DIVISOR_BF16)) scale_value = __bfloat162float(__float2bfloat16(scale_value));
+    const ExactDivider scale(scale_value);
+    const float bound = __fmul_rn(1024.0f, scale_value);
+    const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
+    for (int64_t index = int64_t(blockIdx.x) * QUANT_THREADS + threadIdx.x; index < vectors; index += 2 * stride) {
+        const int64_t second = index + stride;
+        const bool has_second = second < vectors;
+        uint32_t a[8], b[8];
+        ld_nc_u8(input + index * 32, a);
+        if (has_second) ld_nc_u8(input + second * 32, b);
+        uint32_t out[4];
+        encode_fp8_words<SPEC_C, 8>(a, out, scale, bound);
+        output[index] = make_uint4(out[0], out[1], out[2], out[3]);
+        if (has_second) {
+            encode_fp8_words<SPEC_C, 8>(b, out, scale, bound);
+            output[second] = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // NVFP4 encode.  Two adjacent threads own one 16-element block (8 elements, one
 // 16-byte load each); the pair's maximum crosses with a single shuffle.  Eight
@@ -148,6 +175,71 @@ nvfp4_encode_kernel(const uint4* __restrict__ input, uint32_t* __restrict__ outp
     }
 }
 
+// Wide variant for 32-byte aligned matrices: one thread owns a whole 16-element block (one 32-byte load,
+// one 8-byte store of codes), so the block maximum needs no shuffle and the scale arithmetic runs once per
+// block; four adjacent threads assemble one 4-byte word of scale bytes.
+template <bool SPEC_C>
+__global__ void __launch_bounds__(QUANT_THREADS)
+nvfp4_encode_wide_kernel(const uint8_t* __restrict__ input, uint2* __restrict__ output, uint8_t* __restrict__ scales,
+                         uint8_t* __restrict__ blocked, const float* __restrict__ global_pointer, int rows, int columns,
+                         int flags) {
+    const int blocks_per_row = columns >> 4;
+    const int column_tiles = (blocks_per_row + 3) >> 2;
+    const int64_t total = int64_t(rows) * blocks_per_row;
+    const float global = __ldg(global_pointer);
+    const ExactDivider by_global(SPEC_C ? __fmul_rn(6.0f, global) : global);
+    const bool whole_words = (blocks_per_row & 3) == 0;
+    const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
+    const int lane = threadIdx.x & 31;
+    // warp-uniform loop: `total` is a multiple of 4 whenever whole words are stored, so the four lanes of
+    // a scale word are active together
+    for (int64_t warp_base = int64_t(blockIdx.x) * QUANT_THREADS + (threadIdx.x - lane); warp_base < total;
+         warp_base += stride) {
+        const int64_t index = warp_base + lane;
+        const bool active = index < total;
+        const unsigned int mask = __ballot_sync(0xffffffffu, active);
+        if (!active) continue;
+        uint32_t w[8];
+        ld_nc_u8(input + index * 32, w);
+        const float maximum = abs_max_bf16_words(w);
+        const uint8_t scale_code = nvfp4_block_scale<SPEC_C>(maximum, by_global, flags);
+        const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
+        uint2 codes;
+        if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f) {
+            codes.x = nvfp4_encode_words_short<SPEC_C>(w[0], w[1], w[2], w[3], denominator);
+            codes.y = nvfp4_encode_words_short<SPEC_C>(w[4], w[5], w[6], w[7], denominator);
+        } else {
+            float low[8], high[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                low[2 * i] = bf16_lo(w[i]); low[2 * i + 1] = bf16_hi(w[i]);
+                high[2 * i] = bf16_lo(w[4 + i]); high[2 * i + 1] = bf16_hi(w[4 + i]);
+            }
+            codes.x = nvfp4_encode_x8<SPEC_C>(low, denominator, maximum);
+            codes.y = nvfp4_encode_x8<SPEC_C>(high, denominator, maximum);
+        }
+        output[index] = codes;
+        const int row = total <= 0x7fffffff ? int(uint32_t(index) / uint32_t(blocks_per_row)) : int(index / blocks_per_row);
+        const int block = int(index - int64_t(row) * blocks_per_row);
+        if (whole_words) {
+            const int base = lane & ~3;
+            unsigned int word = scale_code;
+            word |= (unsigned int)__shfl_sync(mask, (unsigned int)scale_code, base + 1) << 8;
+            word |= (unsigned int)__shfl_sync(mask, (unsigned int)scale_code, base + 2) << 16;
+            word |= (unsigned int)__shfl_sync(mask, (unsigned int)scale_code, base + 3) << 24;
+            if ((lane & 3) == 0) {
+                if (blocked != nullptr)
+                    *reinterpret_cast<uint32_t*>(blocked + scale_tile_offset(row, block, column_tiles)) = word;
+                if (scales != nullptr)
+                    *reinterpret_cast<uint32_t*>(scales + int64_t(row) * blocks_per_row + block) = word;
+            }
+        } else {
+            if (blocked != nullptr) blocked[scale_tile_offset(row, block, column_tiles)] = scale_code;
+            if (scales != nullptr) scales[int64_t(row) * blocks_per_row + block] = scale_code;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 
@@ -170,10 +262,28 @@ int launch_tensor_scale(const void* input, int64_t count, float bound, int flags
 
 int launch_fp8_encode(const void* input, void* output, const void* scale, int64_t count, int flags,
                       cudaStream_t stream) {
-    const int64_t vectors = count >> 3;
-    const int tail = int(count & 7);
     const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(input);
     uint8_t* out_base = static_cast<uint8_t*>(output);
+    if ((reinterpret_cast<uintptr_t>(input) & 31u) == 0 && (reinterpret_cast<uintptr_t>(output) & 15u) == 0 && count >= 16) {
+        // whole 16-element vectors on the wide kernel, the rest (< 16 elements) on the narrow one below
+        const int64_t wide = count >> 4;
+        const int grid = grid_for(wide, QUANT_THREADS * 2);
+        if (flags & B2_SPEC_C)
+            fp8_encode_wide_kernel<true><<<grid, QUANT_THREADS, 0, stream>>>(
+                static_cast<const uint8_t*>(input), static_cast<uint4*>(output), wide, static_cast<const float*>(scale), flags);
+        else
+            fp8_encode_wide_kernel<false><<<grid, QUANT_THREADS, 0, stream>>>(
+                static_cast<const uint8_t*>(input), static_cast<uint4*>(output), wide, static_cast<const float*>(scale), flags);
+        const cudaError_t error = cudaGetLastError();
+        if (error != cudaSuccess || (count & 15) == 0) return int(error);
+        base += wide * 16;
+        out_base += wide * 16;
+        count &= 15;
+        input = base;
+        output = out_base;
+    }
+    const int64_t vectors = count >> 3;
+    const int tail = int(count & 7);
     const int grid = grid_for(vectors, QUANT_THREADS * 2);
     if (flags & B2_SPEC_C)
         fp8_encode_kernel<true><<<grid, QUANT_THREADS, 0, stream>>>(
@@ -188,6 +298,18 @@ int launch_fp8_encode(const void* input, void* output, const void* scale, int64_
 
 int launch_nvfp4_encode(const void* input, void* output, void* scales, void* blocked, const void* global, int rows,
                         int columns, int flags, cudaStream_t stream) {
+    if ((reinterpret_cast<uintptr_t>(input) & 31u) == 0 && (reinterpret_cast<uintptr_t>(output) & 7u) == 0) {
+        const int grid = grid_for(int64_t(rows) * (columns >> 4), QUANT_THREADS);
+        if (flags & B2_SPEC_C)
+            nvfp4_encode_wide_kernel<true><<<grid, QUANT_THREADS, 0, stream>>>(
+                static_cast<const uint8_t*>(input), static_cast<uint2*>(output), static_cast<uint8_t*>(scales),
+                static_cast<uint8_t*>(blocked), static_cast<const float*>(global), rows, columns, flags);
+        else
+            nvfp4_encode_wide_kernel<false><<<grid, QUANT_THREADS, 0, stream>>>(
+                static_cast<const uint8_t*>(input), static_cast<uint2*>(output), static_cast<uint8_t*>(scales),
+                static_cast<uint8_t*>(blocked), static_cast<const float*>(global), rows, columns, flags);
+        return int(cudaGetLastError());
+    }
     const int64_t total = int64_t(rows) * (columns >> 3);
     const int grid = grid_for(total, QUANT_THREADS * 2);
     if (flags & B2_SPEC_C)
