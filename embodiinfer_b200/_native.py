@@ -20,6 +20,7 @@ EPI_LINEAR, EPI_GEGLU = 0, 1
 OUT_BF16, OUT_FP8, OUT_NVFP4 = 0, 1, 2
 LINEAR_ROUND_SCALE_BF16 = 1
 LINEAR_PAIRED_GATE_UP_SCALES = 4
+LINEAR_STREAM_TOKENS = 8
 SCALE_SCRATCH_BYTES = 8
 STATIC_SCRATCH_BYTES = 16640
 STATIC_SCALE_MAX_COUNT = 67108864

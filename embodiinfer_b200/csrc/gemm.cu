@@ -38,7 +38,10 @@ namespace b2 {
 // instructions per element and runs on 8 warps; the gated epilogue (GELU lookup, two roundings, block
 // scale, exact division, e2m1 packing) is latency-bound, so it gets 16 warps: four per TMEM lane
 // partition, each owning 16-feature units of the tile.
-__host__ __device__ constexpr int epilogue_warps(int epi) { return epi == 0 ? 8 : 16; }
+#ifndef B2_GEGLU_EPILOGUE_WARPS
+#define B2_GEGLU_EPILOGUE_WARPS 16
+#endif
+__host__ __device__ constexpr int epilogue_warps(int epi) { return epi == 0 ? 8 : B2_GEGLU_EPILOGUE_WARPS; }
 constexpr int FIRST_EPILOGUE_WARP = 2;
 __host__ __device__ constexpr int gemm_threads(int epi) { return 32 * (FIRST_EPILOGUE_WARP + epilogue_warps(epi)); }
 constexpr int TILE_TOKENS = 128;                   // MMA M
@@ -46,12 +49,13 @@ constexpr int STAGE_K_BYTES = 128;                 // one swizzle row
 constexpr int A_TILE_BYTES = TILE_TOKENS * STAGE_K_BYTES;
 constexpr int SCALE_ATOM_BYTES = 512;              // 128 rows x 4 blocks of 16
 constexpr int SCALE_ATOMS_PER_STAGE = 4;           // 4 x 64 elements = 256 e2m1 = 128 bytes of K
-constexpr int SCALE_STAGE_BYTES = 3 * SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;   // act + two weight row blocks
+
 constexpr int MAX_STAGES = 8;
 constexpr int TMEM_COLUMNS = 512;
 // NVFP4 scale factors live in TMEM columns 384..479: two sets (alternating by K slice, so the copies for
 // one slice never overwrite columns an MMA of the previous slice may still be reading), each 16 columns
 // of token scales (4 per 64 elements of K) followed by 32 columns of feature scales (8 per 64 elements).
+constexpr int MAX_RESIDENT_KB = 8;                 // K stages of a token tile kept in shared memory (8 x 16 KB)
 constexpr int PREFETCH_DISTANCE = 12;              // K stages between an L2 prefetch and its load
 constexpr int TMEM_SFA_COLUMNS = 16;               // 4 atoms x 4 columns of token scales per K stage
 // A set of scale columns = 16 token-scale columns + 16 per 128-row block of feature scales; sets are
@@ -67,6 +71,7 @@ struct KernelArgs {
     int tile_n;                  // TMEM columns per tile (GEGLU: gate half + up half)
     int num_m_tiles, num_n_tiles, total_tiles;
     int stages, accumulators, accumulator_stride, scale_sets, scale_blocks;
+    int resident;                // 1: the CTA keeps its token tile (all of K) and its token scales on chip, see TileWalk
     int up_row_offset;           // row of the first "up" feature in the packed weight
     int scale_column_tiles;      // 512-byte scale atoms per 128-row block
     int act_row_blocks, weight_row_blocks;
@@ -306,6 +311,44 @@ __device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[1
 #else
 #define TRACE(slot, index)
 #endif
+// Which tiles a CTA computes, in which order.
+//   streaming (default): tile = blockIdx.x + i * gridDim.x over the n-major tile list (token tile inner), so
+//       the CTAs running side by side share a weight slab and every K stage loads a token tile and a
+//       weight tile.
+//   resident: the CTA stays on one token tile (blockIdx.x % num_m_tiles) and walks the feature tiles
+//       r, r + G, r + 2G ... (r = blockIdx.x / num_m_tiles, G = CTAs on that token tile).  The token tile
+//       and its scales are loaded once for all of K (shared memory / TMEM), and a K stage loads weights
+//       only: less than half the bytes per MMA, which is what bounds the streaming order at 128 tokens.
+struct TileWalk {
+    int m_tile, n_tile, step, linear;
+    bool resident;
+    __device__ __forceinline__ explicit TileWalk(const KernelArgs& args) : resident(args.resident != 0) {
+        if (resident) {
+            m_tile = int(blockIdx.x) % args.num_m_tiles;
+            n_tile = int(blockIdx.x) / args.num_m_tiles;
+            step = (int(gridDim.x) - m_tile + args.num_m_tiles - 1) / args.num_m_tiles;
+            linear = 0;
+        } else {
+            linear = blockIdx.x;
+            step = gridDim.x;
+            n_tile = linear / args.num_m_tiles;
+            m_tile = linear - n_tile * args.num_m_tiles;
+        }
+    }
+    __device__ __forceinline__ bool valid(const KernelArgs& args) const {
+        return resident ? n_tile < args.num_n_tiles : linear < args.total_tiles;
+    }
+    __device__ __forceinline__ void next(const KernelArgs& args) {
+        if (resident) {
+            n_tile += step;
+        } else {
+            linear += step;
+            n_tile = linear / args.num_m_tiles;
+            m_tile = linear - n_tile * args.num_m_tiles;
+        }
+    }
+};
+
 // ---- the kernel ---------------------------------------------------------------
 
 template <int KIND, int EPI>
@@ -317,15 +360,25 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
     const int BN = args.tile_n;
     const int features_per_tile = GEGLU ? BN / 2 : BN;
-    const uint32_t stage_bytes = A_TILE_BYTES + uint32_t(BN) * STAGE_K_BYTES;
-    const uint32_t scale_stage_bytes = KIND == B2_KIND_NVFP4 ? SCALE_STAGE_BYTES : 0;
-    const uint32_t scale_base = base + uint32_t(args.stages) * stage_bytes;
+    // shared memory: [resident token tile: num_kb x 16 KB][resident token scales: num_kb x 2 KB]
+    //                [stages x (token tile unless resident | weight tile)][stages x scale atoms][barriers][GELU table]
+    const bool resident = args.resident != 0;
+    const uint32_t a_stage_bytes = resident ? 0u : uint32_t(A_TILE_BYTES);
+    const uint32_t stage_bytes = a_stage_bytes + uint32_t(BN) * STAGE_K_BYTES;
+    constexpr uint32_t SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;     // one operand's atoms of a K stage
+    const uint32_t token_part_bytes = resident ? 0u : SCALE_PART_BYTES;                 // offset of the feature atoms in a scale stage
+    const uint32_t scale_stage_bytes = KIND == B2_KIND_NVFP4 ? token_part_bytes + uint32_t(args.scale_blocks) * SCALE_PART_BYTES : 0;
+    const uint32_t panel_base = base;
+    const uint32_t panel_scale_base = panel_base + (resident ? uint32_t(args.num_kb) * A_TILE_BYTES : 0u);
+    const uint32_t stage_base = panel_scale_base + (resident && KIND == B2_KIND_NVFP4 ? uint32_t(args.num_kb) * SCALE_PART_BYTES : 0u);
+    const uint32_t scale_base = stage_base + uint32_t(args.stages) * stage_bytes;
     const uint32_t barrier_base = scale_base + uint32_t(args.stages) * scale_stage_bytes;
     const uint32_t full_bar = barrier_base;                       // [stages]
     const uint32_t empty_bar = barrier_base + 8 * MAX_STAGES;     // [stages]
     const uint32_t acc_full_bar = barrier_base + 16 * MAX_STAGES; // [2]
     const uint32_t acc_empty_bar = acc_full_bar + 16;             // [2]
-    const uint32_t tmem_slot = acc_empty_bar + 16;
+    const uint32_t panel_bar = acc_empty_bar + 16;                // [MAX_RESIDENT_KB] token tile + scales of K stage kb landed
+    const uint32_t tmem_slot = panel_bar + 8 * MAX_RESIDENT_KB;
     const uint32_t compact_table = tmem_slot + 16;                // 2 * (gelu_hi - gelu_lo) bf16 entries
 
     const int warp = threadIdx.x >> 5;
@@ -342,6 +395,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             mbar_init(acc_full_bar + 8 * b, 1);
             mbar_init(acc_empty_bar + 8 * b, epilogue_warps(EPI));
         }
+        for (int kb = 0; kb < MAX_RESIDENT_KB; ++kb) mbar_init(panel_bar + 8 * kb, 1);
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -378,13 +432,33 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             // long to arrive, so loads that miss the L2 leave the pipe waiting; weights prefetched into the L2
             // a few thousand cycles earlier arrive in a third of that.  The token tiles sharing a weight slab
             // run side by side, so they take turns issuing its prefetches.
-            int pf_tile = blockIdx.x, pf_kb = 0;
+            TileWalk pf(args);
+            int pf_kb = 0;
             for (int i = 0; i < PREFETCH_DISTANCE; ++i)
-                if (++pf_kb == num_kb) { pf_kb = 0; pf_tile += gridDim.x; }
+                if (++pf_kb == num_kb) { pf_kb = 0; pf.next(args); }
             int pf_f0 = 0, pf_turn = 0, pf_seen = -1;      // feature row of the cursor's tile; stages until this CTA's turn
-            for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x) {
-                const int n_tile = tile / args.num_m_tiles;
-                const int m_tile = tile - n_tile * args.num_m_tiles;
+            TileWalk walk(args);
+            const bool panel_loaded = resident && walk.valid(args);
+            if (panel_loaded) {
+                // the token tile for all of K, and its scale atoms, once
+                if (elect_one()) {
+                    const uint8_t* token_scales = KIND == B2_KIND_NVFP4
+                        ? args.act_scales + int64_t(walk.m_tile) * args.scale_column_tiles * SCALE_ATOM_BYTES : nullptr;
+                    for (int kb = 0; kb < num_kb; ++kb) {
+                        const uint32_t bar = panel_bar + 8 * kb;
+                        const int atoms = min(SCALE_ATOMS_PER_STAGE, args.scale_column_tiles - kb * SCALE_ATOMS_PER_STAGE);
+                        mbar_expect_tx(bar, A_TILE_BYTES + (KIND == B2_KIND_NVFP4 ? uint32_t(atoms) * SCALE_ATOM_BYTES : 0u));
+                        tma_load_2d(panel_base + uint32_t(kb) * A_TILE_BYTES, &act_map, bar, kb * STAGE_K_BYTES, walk.m_tile * TILE_TOKENS);
+                        if (KIND == B2_KIND_NVFP4)
+                            bulk_load(panel_scale_base + uint32_t(kb) * SCALE_PART_BYTES,
+                                      token_scales + int64_t(kb) * SCALE_PART_BYTES, uint32_t(atoms) * SCALE_ATOM_BYTES, bar);
+                    }
+                }
+                __syncwarp();
+            }
+            for (; walk.valid(args); walk.next(args)) {
+                const int n_tile = walk.n_tile;
+                const int m_tile = walk.m_tile;
                 const int m0 = m_tile * TILE_TOKENS;
                 const int f0 = n_tile * features_per_tile;
                 // weight rows whose scales this tile needs: up to two 128-row blocks
@@ -410,7 +484,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 int live = 0;
                 if (KIND == B2_KIND_NVFP4) {
                     token_scales = args.act_scales + int64_t(m_tile) * args.scale_column_tiles * SCALE_ATOM_BYTES;
-                    live = 1;
+                    live = resident ? 0 : 1;
                     for (int i = 0; i < scale_blocks; ++i)
                         if (scale_row_block[i] < args.weight_row_blocks) {
                             feature_scales[i] = args.weight_scales + int64_t(scale_row_block[i]) * args.scale_column_tiles * SCALE_ATOM_BYTES;
@@ -428,33 +502,29 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
                     if (elect_one()) {
                         const uint32_t bar = full_bar + 8 * stage;
-                        const uint32_t a_smem = base + uint32_t(stage) * stage_bytes;
-                        const uint32_t b_smem = a_smem + A_TILE_BYTES;
+                        const uint32_t a_smem = stage_base + uint32_t(stage) * stage_bytes;
+                        const uint32_t b_smem = a_smem + a_stage_bytes;
                         const int k0 = kb * STAGE_K_BYTES;
                         const uint32_t copy_bytes = uint32_t(kb == num_kb - 1 ? tail_atoms : SCALE_ATOMS_PER_STAGE) * SCALE_ATOM_BYTES;
                         mbar_expect_tx(bar, stage_bytes + (KIND == B2_KIND_NVFP4 ? uint32_t(live) * copy_bytes : 0u));
-                        tma_load_2d(a_smem, &act_map, bar, k0, m0);
+                        if (!resident) tma_load_2d(a_smem, &act_map, bar, k0, m0);
                         tma_load_2d(b_smem, &weight_map, bar, k0, f0);
                         if (GEGLU) tma_load_2d(b_smem + up_smem_offset, &weight_map, bar, k0, up_row);
                         if (KIND == B2_KIND_NVFP4) {
                             const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
                             const int64_t offset = int64_t(kb) * (SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES);
-                            bulk_load(s_smem, token_scales + offset, copy_bytes, bar);
+                            if (!resident) bulk_load(s_smem, token_scales + offset, copy_bytes, bar);
                             if (feature_scales[0] != nullptr)
-                                bulk_load(s_smem + SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES, feature_scales[0] + offset, copy_bytes, bar);
+                                bulk_load(s_smem + token_part_bytes, feature_scales[0] + offset, copy_bytes, bar);
                             if (feature_scales[1] != nullptr)
-                                bulk_load(s_smem + 2 * SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES, feature_scales[1] + offset, copy_bytes, bar);
+                                bulk_load(s_smem + token_part_bytes + SCALE_PART_BYTES, feature_scales[1] + offset, copy_bytes, bar);
                         }
                     }
-#ifdef B2_TRACE
-                    if (args.flags & 0x2000) pf_tile = args.total_tiles;
-#endif
-                    if (pf_tile < args.total_tiles) {
-                        if (pf_tile != pf_seen) {
-                            const int pf_n_tile = pf_tile / args.num_m_tiles;
-                            pf_f0 = pf_n_tile * features_per_tile;
-                            pf_turn = (pf_tile - pf_n_tile * args.num_m_tiles + args.num_m_tiles - pf_kb % args.num_m_tiles) % args.num_m_tiles;
-                            pf_seen = pf_tile;
+                    if (pf.valid(args)) {
+                        if (pf.n_tile != pf_seen) {
+                            pf_f0 = pf.n_tile * features_per_tile;
+                            pf_turn = (pf.m_tile + args.num_m_tiles - pf_kb % args.num_m_tiles) % args.num_m_tiles;
+                            pf_seen = pf.n_tile;
                         }
                         if (pf_turn == 0) {
                             if (elect_one()) {
@@ -464,7 +534,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                             pf_turn = args.num_m_tiles;
                         }
                         --pf_turn;
-                        if (++pf_kb == num_kb) { pf_kb = 0; pf_tile += gridDim.x; }
+                        if (++pf_kb == num_kb) { pf_kb = 0; pf.next(args); }
                     }
                     __syncwarp();
                     TRACE(1, trace_index); ++trace_index;
@@ -477,6 +547,8 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             for (int s = 0; s < args.stages; ++s)
                 if (filled & (1u << s))
                     mbar_wait(full_bar + 8 * s, (fill_parity >> s) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
+            if (panel_loaded)
+                for (int kb = 0; kb < num_kb; ++kb) mbar_wait(panel_bar + 8 * kb, 0u, drain_failed, args.status, STATUS_WAIT_DRAIN);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
@@ -487,6 +559,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             const uint32_t idesc = KIND == B2_KIND_NVFP4 ? idesc_nvf4(TILE_TOKENS, BN) : idesc_f8(TILE_TOKENS, BN);
             const uint32_t idesc_half = idesc_nvf4(TILE_TOKENS, 64);
             const uint64_t operand_desc = smem_desc_sw128(0);        // + (address >> 4)
+            const uint32_t operand_low = uint32_t(operand_desc), operand_high = uint32_t(operand_desc >> 32);
             const bool paired_scales = GEGLU && (args.flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
             const bool split_halves = KIND == B2_KIND_NVFP4 && GEGLU && BN == 128 && !paired_scales;
             int stage = 0;
@@ -500,11 +573,30 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             int trace_index = 0; (void)trace_index;
             int set = 0, lag_stage = 0, issued = 0;
             uint32_t lag_phase = 0;
-            const uint32_t set_columns = uint32_t(TMEM_SFA_COLUMNS + 16 * args.scale_blocks);
+            const uint32_t set_columns = uint32_t((resident ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
             const uint32_t sfb_stride = 4u * uint32_t(args.scale_blocks);
             const uint64_t scale_desc = smem_desc_scale_atom(0);
-            for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x, ++local_tile) {
-                const int n_tile = tile / args.num_m_tiles;
+            const uint32_t scale_desc_high = uint32_t(scale_desc >> 32);
+            // resident order: the token scales of all K stages sit in TMEM right after the accumulators
+            const uint32_t resident_sfa = tmem_base + uint32_t(args.accumulators * args.accumulator_stride);
+            TileWalk walk(args);
+            if (resident && KIND == B2_KIND_NVFP4 && walk.valid(args)) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    mbar_wait(panel_bar + 8 * kb, 0u, failed, args.status, STATUS_WAIT_MMA_FULL);
+                    tc_fence_after_sync();
+                    __syncwarp();
+                    if (elect_one()) {
+                        const uint32_t atom_low = (panel_scale_base + uint32_t(kb) * SCALE_PART_BYTES) >> 4;
+                        const int atoms = min(SCALE_ATOMS_PER_STAGE, args.scale_column_tiles - kb * SCALE_ATOMS_PER_STAGE);
+                        for (int j = 0; j < atoms; ++j)
+                            tc_copy_32x128b_x4(resident_sfa + uint32_t(kb * TMEM_SFA_COLUMNS + j * 4),
+                                               desc_from_words(atom_low + uint32_t(j) * (SCALE_ATOM_BYTES >> 4), scale_desc_high));
+                    }
+                    __syncwarp();
+                }
+            }
+            for (; walk.valid(args); walk.next(args), ++local_tile) {
+                const int n_tile = walk.n_tile;
                 const int f0 = n_tile * features_per_tile;
                 // column of the feature-scale block the MMA starts reading at (a tile that starts 64 features
                 // into a 128-row block starts at column 2)
@@ -518,11 +610,16 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
                     tc_fence_after_sync();
                     const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
-                    const uint32_t a_smem = base + uint32_t(stage) * stage_bytes;
-                    const uint64_t a_desc = operand_desc + (a_smem >> 4);
-                    const uint64_t b_desc = a_desc + (A_TILE_BYTES >> 4);
-                    const uint32_t sfa_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t(set + 1);
-                    const uint32_t sfb_tmem = sfa_tmem + TMEM_SFA_COLUMNS;
+                    if (resident && local_tile == 0) {       // first pass over K: the token tile may still be landing
+                        mbar_wait(panel_bar + 8 * kb, 0u, failed, args.status, STATUS_WAIT_MMA_FULL);
+                        tc_fence_after_sync();
+                    }
+                    const uint32_t stage_smem = stage_base + uint32_t(stage) * stage_bytes;
+                    const uint32_t a_low = operand_low + ((resident ? panel_base + uint32_t(kb) * A_TILE_BYTES : stage_smem) >> 4);
+                    const uint32_t b_low = operand_low + ((stage_smem + a_stage_bytes) >> 4);
+                    const uint32_t set_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t(set + 1);
+                    const uint32_t sfa_tmem = resident ? resident_sfa + uint32_t(kb * TMEM_SFA_COLUMNS) : set_tmem;
+                    const uint32_t sfb_tmem = resident ? set_tmem : set_tmem + TMEM_SFA_COLUMNS;
                     if (KIND == B2_KIND_NVFP4) {
                         if (issued >= args.scale_sets) {
                             mbar_wait(empty_bar + 8 * lag_stage, lag_phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
@@ -530,20 +627,14 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                             if (++lag_stage == args.stages) { lag_stage = 0; lag_phase ^= 1u; }
                         }
                         ++issued;
-#ifdef B2_TRACE
-                        if ((args.flags & 0x4000) && issued > 1) {      // debug: previous stage's MMAs complete before these copies
-                            const int previous = stage == 0 ? args.stages - 1 : stage - 1;
-                            mbar_wait(empty_bar + 8 * previous, stage == 0 ? phase ^ 1u : phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
-                            tc_fence_after_sync();
-                        }
-#endif
                     }
                     __syncwarp();
                     TRACE(2, trace_index);
                     if (elect_one()) {
                         // shared memory: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
-                        const uint64_t atom_desc = scale_desc + ((scale_base + uint32_t(stage) * scale_stage_bytes) >> 4);
-                        constexpr uint64_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
+                        const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes) >> 4;
+                        constexpr uint32_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
+                        const uint32_t feature_low = atom_low + (resident ? 0u : PART);   // the stage holds no token atoms when they are resident
                         const bool two_blocks = args.scale_blocks == 2;
                         const uint32_t first_accumulate = kb != 0;
                         // `count` is a literal on the full-stage path, so its loop carries no per-step conditions.
@@ -552,10 +643,10 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
 #pragma unroll
                                 for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
                                     if (j < count) {
-                                        tc_copy_32x128b_x4(sfa_tmem + j * 4, atom_desc + j * ATOM);
-                                        tc_copy_32x128b_x4(sfb_tmem + j * sfb_stride, atom_desc + PART + j * ATOM);
+                                        if (!resident) tc_copy_32x128b_x4(sfa_tmem + j * 4, desc_from_words(atom_low + j * ATOM, scale_desc_high));
+                                        tc_copy_32x128b_x4(sfb_tmem + j * sfb_stride, desc_from_words(feature_low + j * ATOM, scale_desc_high));
                                         if (two_blocks)
-                                            tc_copy_32x128b_x4(sfb_tmem + j * sfb_stride + 4, atom_desc + 2 * PART + j * ATOM);
+                                            tc_copy_32x128b_x4(sfb_tmem + j * sfb_stride + 4, desc_from_words(feature_low + PART + j * ATOM, scale_desc_high));
                                     }
                                 }
                             }
@@ -563,18 +654,20 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                             for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
                                 if (j < count) {
                                     const uint32_t accumulate = j == 0 ? first_accumulate : 1u;
+                                    const uint64_t a_desc = desc_from_words(a_low + 2 * j, operand_high);
+                                    const uint64_t b_desc = desc_from_words(b_low + 2 * j, operand_high);
                                     if (KIND != B2_KIND_NVFP4) {
-                                        mma_f8f6f4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, accumulate);
+                                        mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, accumulate);
                                     } else if (split_halves) {
                                         // 64 gate + 64 up features sit in the same two columns of two different scale
                                         // blocks, and a copy can only land on a multiple of four columns: the blocks stay
                                         // apart and each half gets its own MMA (gate -> columns [0,64), up -> [64,128)).
-                                        mma_nvf4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc_half, sfa_tmem + j * 4,
+                                        mma_nvf4(d_tmem, a_desc, b_desc, idesc_half, sfa_tmem + j * 4,
                                                  sfb_tmem + j * sfb_stride + scale_column, accumulate);
-                                        mma_nvf4(d_tmem + 64, a_desc + 2 * j, b_desc + ((64 * STAGE_K_BYTES) >> 4) + 2 * j, idesc_half,
+                                        mma_nvf4(d_tmem + 64, a_desc, desc_from_words(b_low + ((64 * STAGE_K_BYTES) >> 4) + 2 * j, operand_high), idesc_half,
                                                  sfa_tmem + j * 4, sfb_tmem + j * sfb_stride + 4 + scale_column, accumulate);
                                     } else {
-                                        mma_nvf4(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, sfa_tmem + j * 4,
+                                        mma_nvf4(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4,
                                                  sfb_tmem + j * sfb_stride + scale_column, accumulate);
                                     }
                                 }
@@ -615,9 +708,9 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         constexpr int WARPS_PER_QUARTER = epilogue_warps(EPI) / 4;
         const int part = (warp - FIRST_EPILOGUE_WARP) >> 2;     // 0 .. WARPS_PER_QUARTER-1
         int local_tile = 0;
-        for (int tile = blockIdx.x; tile < args.total_tiles; tile += gridDim.x, ++local_tile) {
-            const int n_tile = tile / args.num_m_tiles;
-            const int m_tile = tile - n_tile * args.num_m_tiles;
+        for (TileWalk walk(args); walk.valid(args); walk.next(args), ++local_tile) {
+            const int n_tile = walk.n_tile;
+            const int m_tile = walk.m_tile;
             const int token = m_tile * TILE_TOKENS + quarter * 32 + lane;
             const int f0 = n_tile * features_per_tile;
             const int buffer = local_tile % args.accumulators;
@@ -729,8 +822,9 @@ static int choose_feature_tile(int kind, bool geglu, int features, int m_tiles) 
         const int columns = geglu ? 2 * tile : tile;
         const int64_t tiles = int64_t((features + tile - 1) / tile) * m_tiles;
         const int64_t waves = (tiles + sms - 1) / sms;
-        // main-loop time grows with the columns; the epilogue adds to it unless it overlaps the next tile
-        const double cost = double(waves) * (columns + (can_double_buffer(kind, columns) ? 16.0 : 16.0 + 0.4 * columns));
+        // a K stage moves 128 token rows + `columns` weight rows through shared memory, which is what its time
+        // follows; the epilogue adds to it unless it overlaps the next tile
+        const double cost = double(waves) * (128.0 + columns + (can_double_buffer(kind, columns) ? 16.0 : 16.0 + 0.4 * columns));
         if (best == 0 || cost < best_cost) { best = tile; best_cost = cost; }
     }
     return best;
@@ -829,27 +923,47 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
     args.out_blocked = static_cast<uint8_t*>(d->out_blocked);
     args.status = static_cast<unsigned int*>(d->status);
 
-    const int stage_bytes = A_TILE_BYTES + args.tile_n * STAGE_K_BYTES;
-    const int scale_stage_bytes = nvfp4 ? SCALE_STAGE_BYTES : 0;
+    constexpr int SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
+    int stage_bytes = A_TILE_BYTES + args.tile_n * STAGE_K_BYTES;
+    int scale_stage_bytes = nvfp4 ? (1 + args.scale_blocks) * SCALE_PART_BYTES : 0;
     args.gelu_lo = args.gelu_hi = 0;
     if (geglu && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
         d->gelu_hi - d->gelu_lo <= MAX_COMPACT_GELU) {
         args.gelu_lo = d->gelu_lo;
         args.gelu_hi = d->gelu_hi;
     }
-    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 128 + 4 * (args.gelu_hi - args.gelu_lo);
-    int stages = (SMEM_LIMIT - fixed_bytes) / (stage_bytes + scale_stage_bytes);
+    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 8 * MAX_RESIDENT_KB + 128 + 4 * (args.gelu_hi - args.gelu_lo);
+    // Resident order (TileWalk): worth it when a CTA computes several feature tiles of its token tile and the
+    // token tile of all K, the weight stages and (NVFP4) the token scales in TMEM all fit.
+    int panel_bytes = 0;
+    args.resident = 0;
+    {
+        const int grid = args.total_tiles < sm_count() ? args.total_tiles : sm_count();
+        const int resident_panel = args.num_kb * (A_TILE_BYTES + (nvfp4 ? SCALE_PART_BYTES : 0));
+        const int resident_stage = args.tile_n * STAGE_K_BYTES + (nvfp4 ? args.scale_blocks * SCALE_PART_BYTES : 0);
+        const int resident_stages = (SMEM_LIMIT - fixed_bytes - resident_panel) / resident_stage;
+        const int free_columns = TMEM_COLUMNS - args.accumulators * args.accumulator_stride - (nvfp4 ? args.num_kb * TMEM_SFA_COLUMNS : 0);
+        const bool columns_fit = !nvfp4 || free_columns >= 2 * 16 * args.scale_blocks;
+        if (!(d->flags & B2_LINEAR_STREAM_TOKENS) && args.num_kb <= MAX_RESIDENT_KB && args.num_m_tiles <= grid &&
+            int64_t(args.num_n_tiles) * args.num_m_tiles >= 2 * int64_t(grid) && resident_stages >= 3 && columns_fit) {
+            args.resident = 1;
+            panel_bytes = resident_panel;
+            stage_bytes = args.tile_n * STAGE_K_BYTES;
+            scale_stage_bytes = nvfp4 ? args.scale_blocks * SCALE_PART_BYTES : 0;
+        }
+    }
+    int stages = (SMEM_LIMIT - fixed_bytes - panel_bytes) / (stage_bytes + scale_stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) return B2_E_UNSUPPORTED;
     args.stages = stages;
     args.scale_sets = 1;
     if (nvfp4) {
-        const int free_columns = TMEM_COLUMNS - args.accumulators * args.accumulator_stride;
-        args.scale_sets = free_columns / (TMEM_SFA_COLUMNS + 16 * args.scale_blocks);
+        const int free_columns = TMEM_COLUMNS - args.accumulators * args.accumulator_stride - (args.resident ? args.num_kb * TMEM_SFA_COLUMNS : 0);
+        args.scale_sets = free_columns / ((args.resident ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
         if (args.scale_sets > stages) args.scale_sets = stages;
         if (args.scale_sets < 2) return B2_E_UNSUPPORTED;
     }
-    int shared_bytes = fixed_bytes + stages * (stage_bytes + scale_stage_bytes);
+    int shared_bytes = fixed_bytes + panel_bytes + stages * (stage_bytes + scale_stage_bytes);
     if (shared_bytes < SMEM_MINIMUM) shared_bytes = SMEM_MINIMUM;
 
     CUtensorMap act_map, weight_map;

@@ -235,6 +235,15 @@ __device__ __forceinline__ uint64_t smem_desc_scale_atom(uint32_t smem_address) 
     return desc;
 }
 
+// A descriptor whose address field alone varies: the low word is (address >> 4) plus the constant low bits,
+// so stepping through a tile is one 32-bit add (the 14-bit address field never carries: shared memory ends
+// below 2^18).
+__device__ __forceinline__ uint64_t desc_from_words(uint32_t low, uint32_t high) {
+    uint64_t desc;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(desc) : "r"(low), "r"(high));
+    return desc;
+}
+
 // Instruction descriptor, kind::f8f6f4, e4m3 x e4m3 -> fp32, both operands K-major.
 __device__ __forceinline__ uint32_t idesc_f8(uint32_t m, uint32_t n) {
     return (1u << 4)            // D format fp32

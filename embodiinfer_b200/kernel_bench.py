@@ -9,7 +9,8 @@ Method: each case is launched ``--launches`` times inside one CUDA graph, rotati
 operand sets as it takes to exceed the L2 capacity (capped at 16 sets; ``"l2": "warm"`` marks the
 cases whose rotation stays below it), the graph is replayed for 0.5 s to settle the clocks and then
 timed with CUDA events.  ``gbs`` counts each operand and result once (algorithmic bytes), ``tflops``
-is 2*M*N*K.  Operands are random codes: the timings do not depend on values.
+is 2*M*N*K.  Operands are Gaussian matrices (activations ~N(0,1), weights ~N(0,0.02)) quantised by the
+package's own kernels, so the gated epilogue sees realistic gate values.
 """
 
 from __future__ import annotations
@@ -145,7 +146,24 @@ LINEAR_SHAPES = [
 ]
 
 
-def linear_cases(device):
+def quantised_operand(kind: str, rows: int, width: int, std: float, device):
+    """Codes, tiled block scales and the global scale of a Gaussian matrix, through the package's own
+    quantiser (random codes where the width is not a multiple of 64, which the quantiser plans require)."""
+    if width % 64 != 0:
+        codes = _codes((rows, width if kind == "fp8" else width // 2), device)
+        scales = _scale_codes((_blocked_bytes(rows, width // 16),), device) if kind == "nvfp4" else None
+        return codes, scales, torch.full((), 1e-3 if kind == "fp8" else 3e-2, device=device)
+    from .backend.quantization import B200Quantizer
+    matrix = (std * torch.randn((rows, width), device=device)).to(torch.bfloat16)
+    plan = B200Quantizer().plan(matrix, 8 if kind == "fp8" else 4)
+    plan.quantize(matrix)
+    torch.cuda.synchronize()
+    scales = plan.blocked.view(torch.uint8).clone() if kind == "nvfp4" else None
+    return plan.output.view(torch.uint8).clone(), scales, plan.scale.reshape(()).clone()
+
+
+def linear_cases(device, options=None):
+    options = options or {}
     table = gelu_table(device, "tanh")
     table_range = K.gelu_table_range(table)
     for name, kind, tokens, features, width, epilogue in LINEAR_SHAPES:
@@ -156,27 +174,27 @@ def linear_cases(device):
         total = int(tokens * width * operand + rows * width * operand + tokens * features * out_bytes)
 
         def make(_i, kind=kind, tokens=tokens, features=features, width=width, gated=gated, rows=rows):
-            one = torch.ones((), device=device)
             status = torch.zeros(4, device=device, dtype=torch.int32)
-            arguments = dict(tokens=tokens, features=features, width=width, act_scale=one, weight_scale=one, status=status)
-            if kind == "fp8":
-                arguments.update(kind=N.KIND_FP8, act=_codes((tokens, width), device), weight=_codes((rows, width), device))
-            else:
-                arguments.update(
-                    kind=N.KIND_NVFP4, act=_codes((tokens, width // 2), device), weight=_codes((rows, width // 2), device),
-                    act_scales=_scale_codes((_blocked_bytes(tokens, width // 16),), device),
-                    weight_scales=_scale_codes((_blocked_bytes(rows, width // 16),), device))
+            act, act_scales, act_scale = quantised_operand(kind, tokens, width, 1.0, device)
+            weight, weight_scales, weight_scale = quantised_operand(kind, rows, width, 0.02, device)
+            arguments = dict(tokens=tokens, features=features, width=width, act=act, weight=weight, act_scale=act_scale,
+                             weight_scale=weight_scale, status=status, kind=N.KIND_FP8 if kind == "fp8" else N.KIND_NVFP4)
+            if kind == "nvfp4":
+                arguments.update(act_scales=act_scales, weight_scales=weight_scales)
             if gated:
                 out_format = N.OUT_FP8 if kind == "fp8" else N.OUT_NVFP4
                 out = torch.empty((tokens, features if kind == "fp8" else features // 2), device=device, dtype=torch.uint8)
                 arguments.update(epilogue=N.EPI_GEGLU, out_format=out_format, out=out, gelu_table=table, gelu_range=table_range,
-                                 out_scale=torch.full((), 0.01, device=device))
+                                 out_scale=torch.full((), 0.02 if kind == "fp8" else 0.003, device=device))
                 if kind == "nvfp4":
-                    arguments.update(flags=N.LINEAR_PAIRED_GATE_UP_SCALES)
+                    if not options.get("unpaired"):
+                        arguments.update(flags=N.LINEAR_PAIRED_GATE_UP_SCALES)
                     arguments.update(out_blocked=torch.zeros(_blocked_bytes(tokens, features // 16), device=device, dtype=torch.uint8))
             else:
                 arguments.update(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16,
                                  out=torch.empty((tokens, features), device=device, dtype=torch.bfloat16))
+            arguments["flags"] = arguments.get("flags", 0) | options.get("flags", 0)
+            arguments["feature_tile"] = options.get("feature_tile", 0)
             return lambda: K.linear(**arguments)
 
         yield f"linear/{name}", make, total, total, 2.0 * tokens * rows * width
@@ -213,6 +231,9 @@ def main() -> None:
     parser.add_argument("--launches", type=int, default=32)
     parser.add_argument("--library", action="store_true", help="also time torch's scaled_mm at each linear shape")
     parser.add_argument("--list", action="store_true")
+    parser.add_argument("--flags", type=int, default=0, help="OR-ed into the b2_linear flags (8 = stream the token tile)")
+    parser.add_argument("--feature-tile", type=int, default=0, help="features per tile (0 = the library's choice)")
+    parser.add_argument("--unpaired", action="store_true", help="gated NVFP4 cases without the paired gate/up scale layout")
     args = parser.parse_args()
     pattern = re.compile(args.case)
     if args.list:
@@ -222,7 +243,9 @@ def main() -> None:
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     peaks = {"hbm_gbs": 6541.5, "fp8_tflops": 4500.0, "nvfp4_tflops": 9000.0}
-    for source in (quantiser_cases, geglu_cases, linear_cases):
+    options = {"flags": args.flags, "feature_tile": args.feature_tile, "unpaired": args.unpaired}
+    sources = (quantiser_cases, geglu_cases, lambda dev: linear_cases(dev, options))
+    for source in sources:
         for name, make, set_bytes, algorithmic_bytes, flops in source(device):
             if not pattern.search(name):
                 continue

@@ -115,11 +115,15 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
                                             range.  Each 64-feature tile then needs one scale block and one MMA per K step
                                             instead of two of each.  The weight codes keep the bundle order (gate, then up). */
 
+#define B2_LINEAR_STREAM_TOKENS 8 /* tuning aid: always load the token tile with every K stage.  By default a CTA keeps its
+                                     128-token tile (all of K) and the token scales on chip whenever they fit and it computes
+                                     several feature tiles of that token tile; results are identical either way. */
+
 typedef struct b2_linear_desc {
     int32_t kind;        /* B2_KIND_* */
     int32_t epilogue;    /* B2_EPI_* */
     int32_t out_format;  /* B2_OUT_* */
-    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_GEGLU_TRUE_DIV */
+    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_GEGLU_TRUE_DIV */
     int32_t tokens;      /* M: rows of the activation matrix */
     int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
     int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */

@@ -154,6 +154,33 @@ def test_gated_zero_gate_reads_the_full_table(device, kind):
         assert not (bits(hidden) & 0x7fff).any()
 
 
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+@pytest.mark.parametrize("epilogue,tokens,features,width", [("linear", 560, 8192, 1024), ("linear", 300, 12288, 768), ("geglu", 300, 8192, 512)])
+def test_token_resident_order_matches_streaming_and_oracle(device, kind, epilogue, tokens, features, width):
+    """Enough feature tiles per CTA for the kernel to keep its token tile on chip (the default there);
+    B2_LINEAR_STREAM_TOKENS forces the streaming order: both must give the same bits, and match the oracle."""
+    gated = epilogue == "geglu"
+    host, dev = operands(kind, tokens, (2 if gated else 1) * features, width, 77 + tokens, device)
+    outputs = []
+    for flags in (0, N.LINEAR_STREAM_TOKENS):
+        out = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+        status = torch.zeros(1, device=device, dtype=torch.int32)
+        if gated:
+            table_host = gelu_table_cpu("tanh")
+            table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+            K.linear(epilogue=N.EPI_GEGLU, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out,
+                     gelu_table=table, gelu_range=K.gelu_table_range(table), flags=flags, status=status, **dev)
+        else:
+            K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out,
+                     flags=flags, status=status, **dev)
+        assert int(status.item()) == 0
+        outputs.append(bits(out))
+    assert np.array_equal(outputs[0], outputs[1])
+    y = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+    want = O.gelu_mul(y[:, :features], y[:, features:], gelu_table_cpu("tanh")) if gated else y
+    assert_gemm_close(outputs[0], want)
+
+
 def test_gated_with_separate_up_scale(device):
     """gate and up quantised separately (two per-tensor scales) give the same result as two Linears."""
     tokens, features, width = 96, 128, 256
