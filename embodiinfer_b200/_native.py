@@ -24,7 +24,7 @@ LINEAR_STREAM_TOKENS = 8
 SCALE_SCRATCH_BYTES = 8
 STATIC_SCRATCH_BYTES = 16640
 STATIC_SCALE_MAX_COUNT = 67108864
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _ERRORS = {
     E_INVALID: "invalid argument (null, non-positive size or misaligned pointer)",
@@ -63,6 +63,8 @@ class LinearDesc(ctypes.Structure):
         ("out_scales", ctypes.c_void_p),
         ("out_blocked", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_int64),
     ]
 
 
@@ -78,7 +80,9 @@ SIGNATURES: dict[str, list] = {
     "b2_geglu": [_P, _P, _P, _P, _P, _P, _I, _I, _I64, _I, _P, _I, _P],
     "b2_linear": [ctypes.POINTER(LinearDesc), _P],
     "b2_gelu_table_range": [_P, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)],
+    "b2_linear_workspace_bytes": [ctypes.POINTER(LinearDesc)],
 }
+RESULT_TYPES = {"b2_linear_workspace_bytes": ctypes.c_int64}
 
 _lock = threading.Lock()
 _library: ctypes.CDLL | None = None
@@ -100,7 +104,7 @@ def load() -> ctypes.CDLL:
                 if function is None:
                     raise RuntimeError(f"{LIBRARY_PATH} does not export {name}")
                 function.argtypes = argtypes
-                function.restype = ctypes.c_int
+                function.restype = RESULT_TYPES.get(name, ctypes.c_int)
             if library.b2_abi_version() != ABI_VERSION:
                 raise RuntimeError("libembodiinfer_b200.so ABI version mismatch; rebuild it")
             _library = library

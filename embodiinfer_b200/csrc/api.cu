@@ -5,7 +5,7 @@
 #include <cstring>
 
 namespace b2 {
-int run_linear(const b2_linear_desc* desc, cudaStream_t stream);
+int run_linear(const b2_linear_desc* desc, cudaStream_t stream, int64_t* workspace_need = nullptr);
 int launch_geglu(const void* gate, const void* up, void* output, void* scales, void* blocked, const void* scale,
                  int rows, int columns, int64_t row_stride, int bits, const void* table, int flags,
                  cudaStream_t stream);
@@ -92,6 +92,12 @@ int b2_gelu_table_range(const void* host_table, int32_t* lo, int32_t* hi) {
 
 int b2_linear(const b2_linear_desc* desc, void* stream) {
     return b2::run_linear(desc, static_cast<cudaStream_t>(stream));
+}
+
+int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc) {
+    int64_t need = 0;
+    if (b2::run_linear(desc, nullptr, &need) != B2_OK) return 0;
+    return need;
 }
 
 }  // extern "C"

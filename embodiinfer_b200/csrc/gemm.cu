@@ -71,6 +71,7 @@ struct KernelArgs {
     int tile_n;                  // TMEM columns per tile (GEGLU: gate half + up half)
     int num_m_tiles, num_n_tiles, total_tiles;
     int stages, accumulators, accumulator_stride, scale_sets, scale_blocks;
+    int splits;                  // > 1: K is cut into `splits` ranges computed by different CTAs, see the epilogue
     int resident;                // 1: the CTA keeps its token tile (all of K) and its token scales on chip, see TileWalk
     int up_row_offset;           // row of the first "up" feature in the packed weight
     int scale_column_tiles;      // 512-byte scale atoms per 128-row block
@@ -90,6 +91,8 @@ struct KernelArgs {
     uint8_t* out_scales;
     uint8_t* out_blocked;
     unsigned int* status;
+    unsigned int* tickets;       // split-K: one arrival counter per tile (zero between launches)
+    float* partials;             // split-K: [tile][split][128][tile_n] fp32
 };
 
 // ---- epilogue helpers ---------------------------------------------------------
@@ -321,8 +324,25 @@ __device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[1
 //       only: less than half the bytes per MMA, which is what bounds the streaming order at 128 tokens.
 struct TileWalk {
     int m_tile, n_tile, step, linear;
+    int tile, split, kb_begin, kb_end;       // streaming order only: tile index, K range [kb_begin, kb_end) of this work item
     bool resident;
+    __device__ __forceinline__ void decompose(const KernelArgs& args) {
+        tile = linear;
+        split = 0;
+        kb_begin = 0;
+        kb_end = args.num_kb;
+        if (args.splits > 1) {
+            tile = linear / args.splits;
+            split = linear - tile * args.splits;
+            kb_begin = split * args.num_kb / args.splits;
+            kb_end = (split + 1) * args.num_kb / args.splits;
+        }
+        n_tile = tile / args.num_m_tiles;
+        m_tile = tile - n_tile * args.num_m_tiles;
+    }
     __device__ __forceinline__ explicit TileWalk(const KernelArgs& args) : resident(args.resident != 0) {
+        tile = split = kb_begin = 0;
+        kb_end = args.num_kb;
         if (resident) {
             m_tile = int(blockIdx.x) % args.num_m_tiles;
             n_tile = int(blockIdx.x) / args.num_m_tiles;
@@ -331,20 +351,18 @@ struct TileWalk {
         } else {
             linear = blockIdx.x;
             step = gridDim.x;
-            n_tile = linear / args.num_m_tiles;
-            m_tile = linear - n_tile * args.num_m_tiles;
+            decompose(args);
         }
     }
     __device__ __forceinline__ bool valid(const KernelArgs& args) const {
-        return resident ? n_tile < args.num_n_tiles : linear < args.total_tiles;
+        return resident ? n_tile < args.num_n_tiles : linear < args.total_tiles * args.splits;
     }
     __device__ __forceinline__ void next(const KernelArgs& args) {
         if (resident) {
             n_tile += step;
         } else {
             linear += step;
-            n_tile = linear / args.num_m_tiles;
-            m_tile = linear - n_tile * args.num_m_tiles;
+            decompose(args);
         }
     }
 };
@@ -379,6 +397,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     const uint32_t acc_empty_bar = acc_full_bar + 16;             // [2]
     const uint32_t panel_bar = acc_empty_bar + 16;                // [MAX_RESIDENT_KB] token tile + scales of K stage kb landed
     const uint32_t tmem_slot = panel_bar + 8 * MAX_RESIDENT_KB;
+    const uint32_t split_flag = tmem_slot + 8;                    // split-K: "this CTA drew the last ticket"
     const uint32_t compact_table = tmem_slot + 16;                // 2 * (gelu_hi - gelu_lo) bf16 entries
 
     const int warp = threadIdx.x >> 5;
@@ -436,6 +455,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             int pf_kb = 0;
             for (int i = 0; i < PREFETCH_DISTANCE; ++i)
                 if (++pf_kb == num_kb) { pf_kb = 0; pf.next(args); }
+            const bool prefetching = args.splits == 1;      // split K ranges are a few stages long: nothing to run ahead of
             int pf_f0 = 0, pf_turn = 0, pf_seen = -1;      // feature row of the cursor's tile; stages until this CTA's turn
             TileWalk walk(args);
             const bool panel_loaded = resident && walk.valid(args);
@@ -494,7 +514,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 const int tail_atoms = args.scale_column_tiles - (num_kb - 1) * SCALE_ATOMS_PER_STAGE;
                 const uint32_t up_smem_offset = uint32_t(BN / 2) * STAGE_K_BYTES;
                 const int up_row = args.up_row_offset + f0;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
                     mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
                     __syncwarp();
                     TRACE(0, trace_index);
@@ -520,7 +540,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                                 bulk_load(s_smem + token_part_bytes + SCALE_PART_BYTES, feature_scales[1] + offset, copy_bytes, bar);
                         }
                     }
-                    if (pf.valid(args)) {
+                    if (prefetching && pf.valid(args)) {
                         if (pf.n_tile != pf_seen) {
                             pf_f0 = pf.n_tile * features_per_tile;
                             pf_turn = (pf.m_tile + args.num_m_tiles - pf_kb % args.num_m_tiles) % args.num_m_tiles;
@@ -606,7 +626,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 mbar_wait(acc_empty_bar + 8 * buffer, (use & 1u) ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + uint32_t(buffer * args.accumulator_stride);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
                     mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
                     tc_fence_after_sync();
                     const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
@@ -636,7 +656,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         constexpr uint32_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
                         const uint32_t feature_low = atom_low + (resident ? 0u : PART);   // the stage holds no token atoms when they are resident
                         const bool two_blocks = args.scale_blocks == 2;
-                        const uint32_t first_accumulate = kb != 0;
+                        const uint32_t first_accumulate = kb != walk.kb_begin;
                         // `count` is a literal on the full-stage path, so its loop carries no per-step conditions.
                         auto issue = [&](const int count) {
                             if (KIND == B2_KIND_NVFP4) {
@@ -720,13 +740,75 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             if (warp == FIRST_EPILOGUE_WARP) TRACE(4, local_tile);
             const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer * args.accumulator_stride);
             const bool warp_has_tokens = m_tile * TILE_TOKENS + quarter * 32 < args.tokens;   // else: padding rows only
+            // Split K: every CTA of a tile leaves its partial sums (fp32, valid token rows only) in its slot of
+            // the workspace and takes a ticket; the CTA that draws the last ticket adds the slots in split order
+            // (so the result does not depend on which CTA that is) and runs the epilogue on the sums.  No CTA
+            // waits for another.
+            const float* sums = nullptr;
+            if (args.splits > 1) {
+                const int64_t slot_floats = int64_t(TILE_TOKENS) * BN;
+                float* slot = args.partials + (int64_t(walk.tile) * args.splits + walk.split) * slot_floats +
+                              int64_t(quarter * 32 + lane) * BN;
+                for (int chunk = part; chunk < BN / 32 && warp_has_tokens; chunk += WARPS_PER_QUARTER) {
+                    uint32_t v[32];
+                    tmem_load_32x32(lane_address + chunk * 32, v);
+                    tmem_load_wait();
+                    if (token < args.tokens) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            __stcg(reinterpret_cast<uint4*>(slot + chunk * 32) + i, make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buffer);
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"r"(32 * epilogue_warps(EPI)) : "memory");
+                if (threadIdx.x == 32 * FIRST_EPILOGUE_WARP) {
+                    const unsigned int ticket = atomicAdd(args.tickets + walk.tile, 1u);
+                    const unsigned int last = ticket == unsigned(args.splits - 1);
+                    if (last) args.tickets[walk.tile] = 0u;              // ready for the next launch
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(split_flag), "r"(last) : "memory");
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(32 * epilogue_warps(EPI)) : "memory");
+                unsigned int last;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(last) : "r"(split_flag) : "memory");
+                if (!last) continue;
+                __threadfence();
+                sums = args.partials + int64_t(walk.tile) * args.splits * slot_floats + int64_t(quarter * 32 + lane) * BN;
+            }
+            // 16 (or 32) accumulator columns of this lane's token, from TMEM or from the split-K slots
+            auto load_columns = [&](int column, uint32_t* values, int count) {
+                const int64_t slot_floats = int64_t(TILE_TOKENS) * BN;
+                for (int i = 0; i < count; i += 4) {
+                    float4 total = __ldcg(reinterpret_cast<const float4*>(sums + column + i));
+                    for (int s = 1; s < args.splits; ++s) {
+                        const float4 next = __ldcg(reinterpret_cast<const float4*>(sums + s * slot_floats + column + i));
+                        total.x = __fadd_rn(total.x, next.x); total.y = __fadd_rn(total.y, next.y);
+                        total.z = __fadd_rn(total.z, next.z); total.w = __fadd_rn(total.w, next.w);
+                    }
+                    values[i] = __float_as_uint(total.x); values[i + 1] = __float_as_uint(total.y);
+                    values[i + 2] = __float_as_uint(total.z); values[i + 3] = __float_as_uint(total.w);
+                }
+            };
+            const bool lane_has_token = token < args.tokens;
             if (GEGLU) {
                 const int units = features_per_tile / 16;
                 for (int unit = part; unit < units && warp_has_tokens; unit += WARPS_PER_QUARTER) {
                     uint32_t first[16], second[16];
-                    tmem_load_32x16(lane_address + unit * 16, first);
-                    tmem_load_32x16(lane_address + BN / 2 + unit * 16, second);
-                    tmem_load_wait();
+                    if (sums != nullptr) {
+                        if (lane_has_token) {
+                            load_columns(unit * 16, first, 16);
+                            load_columns(BN / 2 + unit * 16, second, 16);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) first[i] = second[i] = 0u;
+                        }
+                    } else {
+                        tmem_load_32x16(lane_address + unit * 16, first);
+                        tmem_load_32x16(lane_address + BN / 2 + unit * 16, second);
+                        tmem_load_wait();
+                    }
                     epilogue_geglu_unit<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, compact_table, scale, scale_up,
                                                                      round_scale, out_scale, by_global, out_scale_rcp,
                                                                      true_div, token, f0 + unit * 16);
@@ -735,14 +817,25 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 const int chunks = features_per_tile / 32;
                 for (int chunk = part; chunk < chunks && warp_has_tokens; chunk += WARPS_PER_QUARTER) {
                     uint32_t first[32];
-                    tmem_load_32x32(lane_address + chunk * 32, first);
-                    tmem_load_wait();
+                    if (sums != nullptr) {
+                        if (lane_has_token) {
+                            load_columns(chunk * 32, first, 32);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) first[i] = 0u;
+                        }
+                    } else {
+                        tmem_load_32x32(lane_address + chunk * 32, first);
+                        tmem_load_wait();
+                    }
                     epilogue_linear_chunk(first, args, scale, round_scale, token, f0 + chunk * 32);
                 }
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buffer);
+            if (sums == nullptr) {                 // (split K released the accumulator right after the dump)
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buffer);
+            }
             if (warp == FIRST_EPILOGUE_WARP) TRACE(5, local_tile);
         }
     }
@@ -846,38 +939,44 @@ static int launch_linear(const CUtensorMap& act_map, const CUtensorMap& weight_m
             configured[device] = true;
         }
     }
-    const int grid = args.total_tiles < sm_count() ? args.total_tiles : sm_count();
+    const int items = args.total_tiles * args.splits;
+    const int grid = items < sm_count() ? items : sm_count();
     linear_kernel<KIND, EPI><<<grid, gemm_threads(EPI), shared_bytes, stream>>>(act_map, weight_map, args);
     return int(cudaGetLastError());
 }
 
 static bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
 
-int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
+// `workspace_need` != nullptr: report the split-K scratch this launch could use and return without launching
+// (pointer fields are then not required).
+int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_need) {
     if (d == nullptr) return B2_E_INVALID;
+    const bool planning = workspace_need != nullptr;
     if (d->kind != B2_KIND_FP8 && d->kind != B2_KIND_NVFP4) return B2_E_UNSUPPORTED;
     if (d->epilogue != B2_EPI_LINEAR && d->epilogue != B2_EPI_GEGLU) return B2_E_UNSUPPORTED;
     if (d->tokens <= 0 || d->features <= 0 || d->width <= 0) return B2_E_INVALID;
-    if (d->act == nullptr || d->weight == nullptr || d->act_scale == nullptr || d->weight_scale == nullptr ||
-        d->out == nullptr)
-        return B2_E_INVALID;
-    if (!aligned16(d->act) || !aligned16(d->weight) || !aligned16(d->out)) return B2_E_INVALID;
+    if (!planning) {
+        if (d->act == nullptr || d->weight == nullptr || d->act_scale == nullptr || d->weight_scale == nullptr ||
+            d->out == nullptr)
+            return B2_E_INVALID;
+        if (!aligned16(d->act) || !aligned16(d->weight) || !aligned16(d->out)) return B2_E_INVALID;
+    }
     if ((d->bias != nullptr && !aligned16(d->bias)) || (d->residual != nullptr && !aligned16(d->residual)))
         return B2_E_INVALID;
     const bool nvfp4 = d->kind == B2_KIND_NVFP4;
     if (d->width % (nvfp4 ? 64 : 16) != 0) return B2_E_UNSUPPORTED;
-    if (nvfp4 && (d->act_scales == nullptr || d->weight_scales == nullptr || !aligned16(d->act_scales) ||
-                  !aligned16(d->weight_scales)))
+    if (!planning && nvfp4 && (d->act_scales == nullptr || d->weight_scales == nullptr || !aligned16(d->act_scales) ||
+                               !aligned16(d->weight_scales)))
         return B2_E_INVALID;
     const bool geglu = d->epilogue == B2_EPI_GEGLU;
     int epilogue = EPI_LINEAR;
     if (geglu) {
-        if (d->gelu_table == nullptr || d->bias != nullptr || d->residual != nullptr) return B2_E_INVALID;
+        if ((!planning && d->gelu_table == nullptr) || d->bias != nullptr || d->residual != nullptr) return B2_E_INVALID;
         if (d->out_format == B2_OUT_BF16) epilogue = EPI_GEGLU_BF16;
         else if (d->out_format == B2_OUT_FP8) epilogue = EPI_GEGLU_FP8;
         else if (d->out_format == B2_OUT_NVFP4) epilogue = EPI_GEGLU_NVFP4;
         else return B2_E_UNSUPPORTED;
-        if (epilogue != EPI_GEGLU_BF16 && d->out_scale == nullptr) return B2_E_INVALID;
+        if (!planning && epilogue != EPI_GEGLU_BF16 && d->out_scale == nullptr) return B2_E_INVALID;
         if (d->features % 16 != 0) return B2_E_UNSUPPORTED;            // whole output vectors / blocks
         if (nvfp4 && d->features % 128 != 0) return B2_E_UNSUPPORTED;   // the up rows must start a scale block
     } else {
@@ -965,6 +1064,32 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream) {
     }
     int shared_bytes = fixed_bytes + panel_bytes + stages * (stage_bytes + scale_stage_bytes);
     if (shared_bytes < SMEM_MINIMUM) shared_bytes = SMEM_MINIMUM;
+
+    // Split K when the tiles leave more than half of the SMs idle and K is long enough to cut.
+    args.splits = 1;
+    args.tickets = nullptr;
+    args.partials = nullptr;
+    {
+        const int sms = sm_count();
+        int splits = args.total_tiles * 2 <= sms ? sms / args.total_tiles : 1;
+        if (splits > args.num_kb / 2) splits = args.num_kb / 2;
+        if (splits > 16) splits = 16;
+        if (args.resident || splits < 2) splits = 1;
+        // the ticket words sit in a region of fixed size, so that launches of different shapes sharing a workspace
+        // find them zero (a split launch has at most sms/2 tiles)
+        constexpr int64_t ticket_bytes = 1024;
+        if (args.total_tiles * 4 > ticket_bytes) splits = 1;
+        const int64_t need = splits > 1 ? ticket_bytes + int64_t(args.total_tiles) * splits * TILE_TOKENS * args.tile_n * 4 : 0;
+        if (planning) {
+            *workspace_need = need;
+            return B2_OK;
+        }
+        if (splits > 1 && d->workspace != nullptr && d->workspace_bytes >= need && aligned16(d->workspace)) {
+            args.splits = splits;
+            args.tickets = static_cast<unsigned int*>(d->workspace);
+            args.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(d->workspace) + ticket_bytes);
+        }
+    }
 
     CUtensorMap act_map, weight_map;
     if (!make_operand_map(&act_map, d->act, d->tokens, args.k_bytes, TILE_TOKENS)) return B2_E_DRIVER;

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 1
+#define B2_ABI_VERSION 2
 
 /* ---- status codes ---------------------------------------------------------- */
 #define B2_OK 0
@@ -146,7 +146,19 @@ typedef struct b2_linear_desc {
     void* out_scales;          /* B2_OUT_NVFP4: row-major block scales [M, N/16] or NULL */
     void* out_blocked;         /* B2_OUT_NVFP4: block scales in 128x4-tile order (padding zeroed by caller) */
     void* status;              /* device uint32 or NULL: set nonzero if a bounded device-side wait expired */
+    void* workspace;           /* NULL, or device scratch for split K (16-byte aligned, ZERO before its first use; every
+                                  launch leaves its first 1024 bytes (the ticket words) zero again, so
+                                  launches that follow one another on a stream may share it) */
+    int64_t workspace_bytes;   /* size of `workspace`; split K is used only when b2_linear_workspace_bytes(desc) fits */
 } b2_linear_desc;
+
+/* Device scratch a launch described by `desc` could use, in bytes (0: it would not split K).  With few
+ * tiles (M = 10*B tokens against 148 SMs) the library cuts K into up to 16 ranges computed by different CTAs;
+ * the CTA that finishes a tile last adds the fp32 partial sums in a fixed order (results do not depend on
+ * timing) and runs the epilogue.  Without a workspace the same launch runs unsplit.  Pointer fields of
+ * `desc` are not dereferenced.  No reference counterpart (cuBLASLt manages its own workspace behind
+ * F.scaled_mm). */
+int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc);
 
 /* Which part of a GELU table needs to be looked up.  `host_table` is a HOST copy of the uint16[65536]
  * table.  On success *lo and *hi bound the bf16 magnitude codes [lo, hi) outside which the table

@@ -16,7 +16,7 @@ HEADER = Path(__file__).resolve().parent.parent / "include" / "embodiinfer_b200.
 
 def declared_functions() -> list[str]:
     text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return re.findall(r"^\s*int\s+(b2_\w+)\s*\(", text, flags=re.M)
+    return re.findall(r"^\s*(?:int|int64_t)\s+(b2_\w+)\s*\(", text, flags=re.M)
 
 
 def test_library_exports_every_declared_symbol():
@@ -34,6 +34,7 @@ def test_header_constants_match_python_mirror():
     values = {m.group(1): int(m.group(2), 0) for m in re.finditer(r"#define\s+(B2_\w+)\s+\(?(-?\w+)\)?\s", text) if re.fullmatch(r"-?(0x)?[0-9a-fA-F]+", m.group(2))}
     for name in ("SPEC_T", "SPEC_C", "SCALAR_RCP", "DIVISOR_BF16", "CLAMP_TINY", "GEGLU_TRUE_DIV", "KIND_FP8", "KIND_NVFP4",
                  "EPI_LINEAR", "EPI_GEGLU", "OUT_BF16", "OUT_FP8", "OUT_NVFP4", "LINEAR_ROUND_SCALE_BF16", "LINEAR_PAIRED_GATE_UP_SCALES",
+                 "LINEAR_STREAM_TOKENS",
                  "SCALE_SCRATCH_BYTES", "ABI_VERSION", "E_INVALID", "E_UNSUPPORTED", "E_DRIVER", "E_TOO_LARGE"):
         assert values[f"B2_{name}"] == getattr(N, name), name
 
@@ -42,7 +43,7 @@ def test_linear_desc_layout_matches_header():
     text = HEADER.read_text()
     body = re.search(r"typedef struct b2_linear_desc \{(.*?)\} b2_linear_desc;", text, flags=re.S).group(1)
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
-    fields = re.findall(r"(?:const\s+)?(?:int32_t|void\*)\s+(\w+);", body)
+    fields = re.findall(r"(?:const\s+)?(?:int32_t|int64_t|void\*)\s+(\w+);", body)
     assert fields == [name for name, _ in N.LinearDesc._fields_]
 
 
@@ -62,6 +63,10 @@ def test_argument_rejection_without_a_gpu():
     desc = N.LinearDesc(kind=N.KIND_FP8, tokens=4, features=8, width=24, act=4096, weight=4096, act_scale=4096,
                         weight_scale=4096, out=4096)
     assert library.b2_linear(ctypes.byref(desc), None) == N.E_UNSUPPORTED      # K % 16
+    plan = N.LinearDesc(kind=N.KIND_FP8, epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=10, features=1024, width=4096)
+    assert library.b2_linear_workspace_bytes(ctypes.byref(plan)) > 0          # 16 tiles on 148 SMs: K would be split
+    plan.tokens, plan.features = 8960, 16384
+    assert library.b2_linear_workspace_bytes(ctypes.byref(plan)) == 0
     desc.width, desc.act = 32, 4100
     assert library.b2_linear(ctypes.byref(desc), None) == N.E_INVALID          # misaligned operand
 

@@ -181,6 +181,34 @@ def test_token_resident_order_matches_streaming_and_oracle(device, kind, epilogu
     assert_gemm_close(outputs[0], want)
 
 
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+@pytest.mark.parametrize("epilogue,tokens,features,width", [("linear", 10, 1024, 4096), ("linear", 80, 1024, 2048), ("linear", 10, 2560, 1024),
+                                                            ("geglu", 10, 4096, 1024), ("geglu", 130, 512, 2048)])
+def test_split_k_is_deterministic_and_matches_oracle(device, kind, epilogue, tokens, features, width):
+    """Few tiles: K is cut across CTAs when a workspace is given.  Same bits on every run (the partial sums
+    are added in split order), tickets back at zero, within tolerance of the oracle like the unsplit launch."""
+    gated = epilogue == "geglu"
+    host, dev = operands(kind, tokens, (2 if gated else 1) * features, width, 11 + tokens, device)
+    table_host = gelu_table_cpu("tanh")
+    table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+    workspace = torch.zeros(16 << 20, device=device, dtype=torch.uint8)
+    outputs = []
+    for ws in (workspace, workspace, False):
+        out = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+        status = torch.zeros(1, device=device, dtype=torch.int32)
+        extra = dict(epilogue=N.EPI_GEGLU, gelu_table=table, gelu_range=K.gelu_table_range(table)) if gated else dict(epilogue=N.EPI_LINEAR)
+        K.linear(out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out, status=status, workspace=ws, **extra, **dev)
+        assert int(status.item()) == 0
+        outputs.append(bits(out))
+    assert np.array_equal(outputs[0], outputs[1])
+    assert not workspace[:1024].any()                       # ticket words
+    assert workspace.any()                                  # partial sums were written: K was split
+    y = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+    want = O.gelu_mul(y[:, :features], y[:, features:], table_host) if gated else y
+    assert_gemm_close(outputs[0], want)
+    assert_gemm_close(outputs[2], want)
+
+
 def test_gated_with_separate_up_scale(device):
     """gate and up quantised separately (two per-tensor scales) give the same result as two Linears."""
     tokens, features, width = 96, 128, 256
