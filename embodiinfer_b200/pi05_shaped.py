@@ -9,6 +9,12 @@ guards for (operators.py:99-107, vision.py:276-601), with every q/k/v/o/gate/up/
 quantised ``FP8Linear`` / ``NVFP4Linear`` bundle dispatched through the registry to the sm_100a
 kernels.  Norms, RoPE, softmax attention and the tiny action in/out projections are plain bf16 tensor
 operations: they are not the quantised Linear this package is about.
+
+Two MLP routes: the registry route (dynamic activation scales; gate_up Linear, GELU*up, down Linear as
+separate steps, what ``QuantizedLinear.forward`` does in the reference) and, after
+``calibrate_fused_mlp``, the calibrated plan route (``FusedMlpPlan``: encode, one fused gate_up + GELU*up
++ re-encode launch, down with the residual add in its epilogue), the counterpart of the reference's
+``quantized_residual_mlp`` (policies/pi05/inference/operators.py:999-1037).
 """
 
 from __future__ import annotations
@@ -20,8 +26,10 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from .backend.mlp import FusedMlpPlan
+from .backend.quantization import B200Quantizer
 from .bundles import pack_quantized_linears, quantize_linear
-from .layers.linear import parse_quantization_config
+from .layers.linear import FP8Config, NVFP4Config, parse_quantization_config
 
 
 @dataclass(frozen=True)
@@ -55,20 +63,26 @@ def _quantized(layers: tuple[nn.Linear, ...], config):
     return members[0] if len(members) == 1 else pack_quantized_linears(members)
 
 
-def _rms_norm(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    values = x.float()
-    values = values * torch.rsqrt(values.pow(2).mean(-1, keepdim=True) + 1e-6)
-    return (values * (1.0 + weight.float())).to(x.dtype)
+def _rms_norm(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """Gemma RMSNorm, ``scale`` = 1 + weight (one fused kernel)."""
+    return F.rms_norm(x, (x.shape[-1],), scale, 1e-6)
 
 
-def _rope(x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
-    """x [B, H, T, D]; rotary embedding with theta 1e4 over the last dimension."""
-    half = x.shape[-1] // 2
-    frequency = torch.exp(-math.log(10000.0) * torch.arange(half, device=x.device, dtype=torch.float32) / half)
+def rope_tables(positions: torch.Tensor, head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos / sin [T, head_dim] (both halves) for theta 1e4; computed once per forward, shared by all layers."""
+    half = head_dim // 2
+    frequency = torch.exp(-math.log(10000.0) * torch.arange(half, device=positions.device, dtype=torch.float32) / half)
     angles = positions.float()[:, None] * frequency[None, :]
-    cos, sin = angles.cos()[None, None], angles.sin()[None, None]
-    first, second = x.float()[..., :half], x.float()[..., half:]
-    return torch.cat((first * cos - second * sin, second * cos + first * sin), dim=-1).to(x.dtype)
+    angles = torch.cat((angles, angles), dim=-1)
+    return angles.cos().to(torch.bfloat16), angles.sin().to(torch.bfloat16)
+
+
+def _rope(x: torch.Tensor, tables: tuple[torch.Tensor, torch.Tensor]) -> torch.Tensor:
+    """x [B, H, T, D]: x * cos + rotate_half(x) * sin."""
+    cos, sin = tables
+    half = x.shape[-1] // 2
+    rotated = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+    return x * cos + rotated * sin
 
 
 class GemmaBlock(nn.Module):
@@ -81,27 +95,58 @@ class GemmaBlock(nn.Module):
         make = lambda n, k: _random_linear(n, k, generator, device)
         self.qkv = _quantized((make(q_dim, shape.width), make(kv_dim, shape.width), make(kv_dim, shape.width)), config)
         self.o_proj = _quantized((make(shape.width, attention_width),), config)
-        self.gate_up = _quantized((make(shape.mlp, shape.width), make(shape.mlp, shape.width)), config)
-        self.down = _quantized((make(shape.width, shape.mlp),), config)
-        self.input_norm = nn.Parameter(torch.zeros(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
-        self.post_norm = nn.Parameter(torch.zeros(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
+        gate, up, down = make(shape.mlp, shape.width), make(shape.mlp, shape.width), make(shape.width, shape.mlp)
+        self.gate_up = _quantized((gate, up), config)
+        self.down = _quantized((down,), config)
+        # bf16 originals, kept until `calibrate_fused_mlp` has built the calibrated plan (or dropped it)
+        self.dense_mlp = (gate.weight.detach(), up.weight.detach(), down.weight.detach())
+        self.method = "fp8" if isinstance(config, FP8Config) else "nvfp4" if isinstance(config, NVFP4Config) else None
+        self.fused_mlp: FusedMlpPlan | None = None
+        self.mlp_ranges = [0.0, 0.0]          # calibration: max |MLP input|, max |hidden|
+        self.recording = False
+        # scale = 1 + weight with zero-initialised weights (SURVEY config 3: "RMSNorm weights 0")
+        self.input_scale = nn.Parameter(torch.ones(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.post_scale = nn.Parameter(torch.ones(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
 
-    def forward(self, x, positions, prefix_kv=None):
+    def mlp(self, x: torch.Tensor) -> torch.Tensor:
+        """x + down(gelu_tanh(gate(n)) * up(n)), n = RMSNorm(x)."""
+        normed = _rms_norm(x, self.post_scale)
+        if self.fused_mlp is not None:
+            rows = normed.reshape(-1, normed.shape[-1])
+            return self.fused_mlp(rows, residual=x.reshape(rows.shape)).reshape(x.shape)
+        gate, up = self.gate_up(normed).chunk(2, dim=-1)
+        hidden = F.gelu(gate, approximate="tanh") * up
+        if self.recording:
+            self.mlp_ranges[0] = max(self.mlp_ranges[0], float(normed.abs().max()))
+            self.mlp_ranges[1] = max(self.mlp_ranges[1], float(hidden.abs().max()))
+        return x + self.down(hidden)
+
+    def build_fused_mlp(self, quantizer: B200Quantizer, margin: float = 1.0) -> None:
+        gate, up, down = self.dense_mlp
+        self.fused_mlp = FusedMlpPlan(gate, up, down, gate_up_max=margin * self.mlp_ranges[0], down_max=margin * self.mlp_ranges[1],
+                                      gate_up=self.method, down=self.method, quantizer=quantizer)
+        self.dense_mlp = None
+
+    def forward(self, x, rope, kv_buffers=None):
+        """``kv_buffers`` (action expert): per-layer [B, 1, prefix + T, D] key/value buffers whose first
+        ``prefix`` rows hold the prefix tower's keys/values; this block writes its own rows behind them."""
         shape = self.shape
         batch, tokens, _ = x.shape
-        qkv = self.qkv(_rms_norm(x, self.input_norm))
+        qkv = self.qkv(_rms_norm(x, self.input_scale))
         q_dim, kv_dim = shape.heads * shape.head_dim, shape.kv_heads * shape.head_dim
         q, k, v = qkv.split((q_dim, kv_dim, kv_dim), dim=-1)
-        q = _rope(q.view(batch, tokens, shape.heads, shape.head_dim).transpose(1, 2), positions)
-        k = _rope(k.view(batch, tokens, shape.kv_heads, shape.head_dim).transpose(1, 2), positions)
+        q = _rope(q.view(batch, tokens, shape.heads, shape.head_dim).transpose(1, 2), rope)
+        k = _rope(k.view(batch, tokens, shape.kv_heads, shape.head_dim).transpose(1, 2), rope)
         v = v.view(batch, tokens, shape.kv_heads, shape.head_dim).transpose(1, 2)
         own_kv = (k, v)
-        if prefix_kv is not None:
-            k, v = torch.cat((prefix_kv[0], k), dim=2), torch.cat((prefix_kv[1], v), dim=2)
+        if kv_buffers is not None:
+            keys, values = kv_buffers
+            keys[:, :, -tokens:].copy_(k)
+            values[:, :, -tokens:].copy_(v)
+            k, v = keys, values
         attended = F.scaled_dot_product_attention(q, k, v, enable_gqa=shape.heads != shape.kv_heads)
         x = x + self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim))
-        gate, up = self.gate_up(_rms_norm(x, self.post_norm)).chunk(2, dim=-1)
-        return x + self.down(F.gelu(gate, approximate="tanh") * up), own_kv
+        return self.mlp(x), own_kv
 
 
 class SiglipBlock(nn.Module):
@@ -137,9 +182,13 @@ class Pi05ShapedPolicy(nn.Module):
         super().__init__()
         device = torch.device(device)
         config = parse_quantization_config(quantization)
+        # SigLIP's fc2 has K = 4304: its packed e2m1 rows (2152 bytes) are not a multiple of the 16 bytes a
+        # TMA row pitch needs, so an NVFP4 policy keeps the vision tower in FP8 (as the reference's
+        # nvfp4 presets do).
+        vision_config = parse_quantization_config("fp8") if isinstance(config, NVFP4Config) else config
         generator = torch.Generator(device=device).manual_seed(seed)
         depth = lambda shape: max(1, round(shape.layers * layer_scale))
-        self.vision = nn.ModuleList(SiglipBlock(SIGLIP_SO400M, config, generator, device) for _ in range(depth(SIGLIP_SO400M)))
+        self.vision = nn.ModuleList(SiglipBlock(SIGLIP_SO400M, vision_config, generator, device) for _ in range(depth(SIGLIP_SO400M)))
         self.prefix = nn.ModuleList(
             GemmaBlock(GEMMA_2B, GEMMA_2B.heads * GEMMA_2B.head_dim, config, generator, device) for _ in range(depth(GEMMA_2B))
         )
@@ -152,11 +201,12 @@ class Pi05ShapedPolicy(nn.Module):
         self.patch_weight, self.patch_bias = rand(SIGLIP_SO400M.width, 3 * PATCH * PATCH), rand(SIGLIP_SO400M.width)
         self.position = rand(patches, SIGLIP_SO400M.width)
         self.vision_norm = nn.LayerNorm(SIGLIP_SO400M.width, eps=1e-6, device=device, dtype=torch.bfloat16)
-        self.projector = _quantized((_random_linear(GEMMA_2B.width, SIGLIP_SO400M.width, generator, device, bias=True),), config)
+        self.projector = _quantized((_random_linear(GEMMA_2B.width, SIGLIP_SO400M.width, generator, device, bias=True),), vision_config)
         self.token_embedding = rand(vocabulary, GEMMA_2B.width)
         self.action_in, self.action_out = rand(GEMMA_300M.width, ACTION_DIM), rand(ACTION_DIM, GEMMA_300M.width)
         self.time_mlp = rand(GEMMA_300M.width, GEMMA_300M.width)
-        self.final_norm = nn.Parameter(torch.zeros(GEMMA_300M.width, device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.final_scale = nn.Parameter(torch.ones(GEMMA_300M.width, device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.quantizer = B200Quantizer() if isinstance(config, (FP8Config, NVFP4Config)) and device.type == "cuda" else None
         self.device_ = device
         self.noise_seed = seed
 
@@ -176,36 +226,57 @@ class Pi05ShapedPolicy(nn.Module):
     def encode_prefix(self, images: torch.Tensor, tokens: torch.Tensor):
         text = self.token_embedding[tokens.to(self.device_)] * math.sqrt(GEMMA_2B.width)
         x = torch.cat((self.embed_images(images), text.to(torch.bfloat16)), dim=1)
-        positions = torch.arange(x.shape[1], device=self.device_)
+        rope = rope_tables(torch.arange(x.shape[1], device=self.device_), GEMMA_2B.head_dim)
         cache = []
         for block in self.prefix:
-            x, kv = block(x, positions)
+            x, kv = block(x, rope)
             cache.append(kv)
         return cache, x.shape[1]
 
-    def denoise(self, cache, prefix_length: int, batch: int, generator: torch.Generator | None = None) -> torch.Tensor:
-        actions = torch.randn((batch, ACTION_HORIZON, ACTION_DIM), device=self.device_, generator=generator)
-        positions = prefix_length + torch.arange(ACTION_HORIZON, device=self.device_)
+    def denoise(self, cache, prefix_length: int, noise: torch.Tensor) -> torch.Tensor:
+        """``noise`` [B, 10, 32] fp32 ~ N(0, 1): ten Euler steps of the flow from t = 1 to t = 0."""
+        actions = noise
+        rope = rope_tables(prefix_length + torch.arange(ACTION_HORIZON, device=self.device_), GEMMA_300M.head_dim)
         dt = -1.0 / DENOISE_STEPS
         half = GEMMA_300M.width // 2
         frequency = torch.exp(-math.log(10000.0) * torch.arange(half, device=self.device_) / half)
+        # one key/value buffer per layer: the prefix rows are written once, the action rows every step
+        buffers = []
+        for keys, values in cache[: len(self.expert)]:
+            pad = keys.new_zeros((*keys.shape[:2], ACTION_HORIZON, keys.shape[-1]))
+            buffers.append((torch.cat((keys, pad), dim=2), torch.cat((values, pad), dim=2)))
         for step in range(DENOISE_STEPS):
             time = 1.0 + step * dt
             angles = time * frequency
             time_embedding = F.linear(torch.cat((angles.sin(), angles.cos())).to(torch.bfloat16), self.time_mlp)
             x = F.linear(actions.to(torch.bfloat16), self.action_in) + time_embedding
-            for block, kv in zip(self.expert, cache):
-                x, _ = block(x, positions, prefix_kv=kv)
-            velocity = F.linear(_rms_norm(x, self.final_norm), self.action_out).float()
+            for block, kv in zip(self.expert, buffers):
+                x, _ = block(x, rope, kv_buffers=kv)
+            velocity = F.linear(_rms_norm(x, self.final_scale), self.action_out).float()
             actions = actions + dt * velocity              # Euler step of the flow (flow.py:21-23)
         return actions
 
+    def noise(self, batch: int) -> torch.Tensor:
+        generator = torch.Generator(device=self.device_).manual_seed(self.noise_seed)
+        return torch.randn((batch, ACTION_HORIZON, ACTION_DIM), device=self.device_, generator=generator)
+
     @torch.no_grad()
-    def forward(self, observations: dict) -> torch.Tensor:
+    def forward(self, observations: dict, noise: torch.Tensor | None = None) -> torch.Tensor:
         images, tokens = observations["images"], observations["tokens"]
         cache, prefix_length = self.encode_prefix(images, tokens)
-        generator = torch.Generator(device=self.device_).manual_seed(self.noise_seed)
-        return self.denoise(cache, prefix_length, images.shape[0], generator)
+        return self.denoise(cache, prefix_length, self.noise(images.shape[0]) if noise is None else noise)
+
+    @torch.no_grad()
+    def calibrate_fused_mlp(self, observations: dict, margin: float = 1.0) -> None:
+        """Run ``observations`` through the registry route, record every Gemma MLP's input and hidden
+        ranges, and switch those MLPs to the calibrated fused plan (three launches, static scales)."""
+        blocks = [*self.prefix, *self.expert]
+        for block in blocks:
+            block.recording = True
+        self.forward(observations)
+        for block in blocks:
+            block.recording = False
+            block.build_fused_mlp(self.quantizer, margin)
 
     def flops_per_observation(self) -> float:
         """2*M*N*K over the quantised projections of one observation (attention and norms excluded)."""

@@ -47,3 +47,31 @@ def test_one_layer_policy_matches_composed_route(device, monkeypatch):
     result = DataParallelRollout(policy, device=device).run(observations)
     assert torch.equal(result.actions, actions) and result.owner_rank == [0, 0, 0]
     assert policy.flops_per_observation() > 1e11
+
+
+@pytest.mark.parametrize("quantization", ("fp8", "nvfp4"))
+def test_calibrated_fused_mlp_route_stays_close_to_the_registry_route(device, quantization):
+    """After calibration on the same observations the Gemma MLPs run as encode + fused gate_up/GELU/re-encode
+    + down(+residual).  Static scales and the CUDA-route weight encoder change roundings, not the result:
+    the action chunks stay within a few percent of the registry route's, and the step is deterministic."""
+    policy = Pi05ShapedPolicy(quantization, device=device, layer_scale=0.01, vocabulary=4096)
+    observations = synthetic_observations(3, vocabulary=4096)
+    reference = policy(observations)
+    policy.calibrate_fused_mlp(observations)
+    assert all(block.fused_mlp is not None for block in [*policy.prefix, *policy.expert])
+    fused = policy(observations)
+    assert torch.isfinite(fused).all() and torch.equal(fused, policy(observations))
+    error = (fused - reference).norm() / reference.norm()
+    assert error < 0.1, float(error)
+
+
+def test_graph_replay_of_the_policy_step_equals_eager(device):
+    from embodiinfer_b200.rollout_bench import GraphedReplica
+    policy = Pi05ShapedPolicy("fp8", device=device, layer_scale=0.01, vocabulary=4096)
+    observations = {key: value.pin_memory() for key, value in synthetic_observations(4, vocabulary=4096).items()}
+    policy.calibrate_fused_mlp(observations)
+    eager = policy(observations)
+    graphed = GraphedReplica(policy, observations, 4)
+    assert torch.equal(graphed(observations), eager)
+    half = {key: value[:2] for key, value in observations.items()}
+    assert torch.equal(graphed(half), eager[:2])
