@@ -16,7 +16,7 @@ OK = 0
 E_INVALID, E_UNSUPPORTED, E_DRIVER, E_TOO_LARGE = -1, -2, -3, -4
 SPEC_T, SPEC_C, SCALAR_RCP, DIVISOR_BF16, CLAMP_TINY, GEGLU_TRUE_DIV = 0, 1, 2, 4, 8, 16
 KIND_FP8, KIND_NVFP4 = 0, 1
-EPI_LINEAR, EPI_GEGLU = 0, 1
+EPI_LINEAR, EPI_GEGLU, EPI_GELU = 0, 1, 2
 OUT_BF16, OUT_FP8, OUT_NVFP4 = 0, 1, 2
 LINEAR_ROUND_SCALE_BF16 = 1
 LINEAR_PAIRED_GATE_UP_SCALES = 4

@@ -80,6 +80,46 @@ class FusedMlpPlan:
         self.down.release_scope(scope)
 
 
+class FusedGeluMlpPlan:
+    """``fc2(gelu(fc1(x) + b1)) + b2`` with calibrated FP8 ranges in three launches: encode(x), fc1 + bias +
+    GELU + e4m3 re-encode, fc2 + bias (+ residual).  The SigLIP block MLP of the reference's fast FP8 path
+    (policies/pi05/inference/vision.py:441-576: fc1 GEMM + bias + tanh GELU + quant, fc2 GEMM + bias)."""
+
+    def __init__(
+        self,
+        fc1_weight: torch.Tensor,
+        fc1_bias: torch.Tensor | None,
+        fc2_weight: torch.Tensor,
+        fc2_bias: torch.Tensor | None,
+        *,
+        fc1_max: float,
+        fc2_max: float,
+        quantizer: ActivationQuantizer,
+        approximate: Literal["none", "tanh"] = "tanh",
+        workspace_key: Callable[[torch.device], WorkspaceKey] | None = None,
+    ) -> None:
+        if fc2_weight.shape != tuple(reversed(fc1_weight.shape)):
+            raise ValueError("Optimized MLP projection dimensions do not match")
+        self.inter_size = fc1_weight.shape[0]
+        self.fc1 = B200Projection(fc1_weight, fc1_max, "fp8", quantizer, workspace_key)
+        self.fc2 = B200Projection(fc2_weight, fc2_max, "fp8", quantizer, workspace_key)
+        self.fc1_bias = None if fc1_bias is None else fc1_bias.detach().to(torch.bfloat16).contiguous()
+        self.fc2_bias = None if fc2_bias is None else fc2_bias.detach().to(torch.bfloat16).contiguous()
+        self.table = gelu_table(fc1_weight.device, approximate)
+        self.table_range = K.gelu_table_range(self.table)
+
+    def __call__(self, inputs: torch.Tensor, *, residual: torch.Tensor | None = None) -> torch.Tensor:
+        encoded = self.fc1.encode(inputs)
+        hidden = self.fc1.apply_gelu(inputs, encoded, table=self.table, bias=self.fc1_bias, bits=8,
+                                     scale=self.fc2.maximum / 448, table_range=self.table_range)
+        shape = (*inputs.shape[:-1], self.inter_size)
+        return self.fc2.apply(_ShapeOnly(shape, inputs), hidden, bias=self.fc2_bias, residual=residual)
+
+    def release_scope(self, scope: WorkspaceKey) -> None:
+        self.fc1.release_scope(scope)
+        self.fc2.release_scope(scope)
+
+
 class _ShapeOnly:
     """Stands in for the bf16 hidden activation that the fused epilogue never materialises."""
 

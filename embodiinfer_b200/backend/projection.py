@@ -203,6 +203,40 @@ class B200Projection:
         )
         return result
 
+    def apply_gelu(
+        self,
+        inputs: torch.Tensor,
+        encoded: EncodedActivation | None,
+        *,
+        table: torch.Tensor,
+        bias: torch.Tensor | None = None,
+        bits: int = 16,
+        scale: float | None = None,
+        table_range: tuple[int, int] = (0, 0),
+    ):
+        """``h = gelu(x W^T + bias)`` in one launch (bias add and GELU with their bf16 roundings, GELU from the
+        table), stored as bf16 (``bits=16``) or as e4m3 at the calibrated ``scale`` (``bits=8``): the fc1 of a
+        SigLIP block together with the encoder of fc2's input (vision.py:441-576).  Returns an object with
+        ``output`` and ``scale`` like a quantisation plan."""
+        if self.precision == "bf16":
+            raise ValueError("apply_gelu needs an fp8 or nvfp4 projection")
+        if bits not in (8, 16) or (bits == 8 and (scale is None or not math.isfinite(scale) or scale <= 0)):
+            raise ValueError("GELU encoding requires bits 8/16 and a finite positive calibrated scale")
+        self._check(inputs, encoded)
+        rows = encoded.output.shape[0]
+        result = _GatedOutput()
+        if bits == 16:
+            result.output = self._buffer("gelu16", (rows, self.output_dim), torch.bfloat16)
+        else:
+            result.scale = self._scale_buffer(float(scale))
+            result.output = self._buffer("gelu8", (rows, self.output_dim), torch.float8_e4m3fn)
+        K.linear(
+            epilogue=N.EPI_GELU, out_format=N.OUT_BF16 if bits == 16 else N.OUT_FP8, tokens=rows, features=self.output_dim,
+            width=self.input_dim, out=result.output, bias=bias, gelu_table=table, out_scale=result.scale,
+            gelu_range=table_range, **self._operands(encoded),
+        )
+        return result
+
     @classmethod
     def gated_pair(
         cls,

@@ -11,10 +11,10 @@
 // an epilogue thread owns whole 16-element quantisation blocks of the output row and
 // writes 16-byte vectors: no shuffles, no transposition.
 //
-// One persistent CTA per SM, ten warps:
-//   warp 0      TMA producer (one lane)
-//   warp 1      TMEM owner and MMA issuer (one lane)
-//   warps 2..9  epilogue; warps w and w+4 share a 32-lane TMEM partition and split the columns
+// One persistent CTA per SM, ten or eighteen warps:
+//   warp 0      TMA producer (all lanes run the loop, an elected lane issues)
+//   warp 1      TMEM owner and tcgen05 issuer (scale-factor copies and MMAs; same scheme)
+//   warps 2..   epilogue; warps w, w+4, ... share a 32-lane TMEM partition and split the columns
 // Accumulators are double-buffered in TMEM whenever two fit, so the epilogue of one
 // tile overlaps the main loop of the next.  Tiles that share a weight slab are
 // consecutive in the schedule, so the slab comes from HBM once and from L2 afterwards.
@@ -34,14 +34,14 @@
 
 namespace b2 {
 
-// Three service warps (TMA, MMA, scale-factor copies) plus the epilogue warps.  The plain Linear epilogue is a handful of
-// instructions per element and runs on 8 warps; the gated epilogue (GELU lookup, two roundings, block
-// scale, exact division, e2m1 packing) is latency-bound, so it gets 16 warps: four per TMEM lane
-// partition, each owning 16-feature units of the tile.
+// Two service warps (TMA, MMA) plus the epilogue warps.  The plain Linear epilogue is a handful of
+// instructions per element and runs on 8 warps; the epilogues that go through the GELU table (lookups, two
+// roundings, block scale, exact division, packing) are latency-bound, so they get 16 warps: four per TMEM
+// lane partition, each owning 16-feature units (or 32-column chunks) of the tile.
 #ifndef B2_GEGLU_EPILOGUE_WARPS
 #define B2_GEGLU_EPILOGUE_WARPS 16
 #endif
-__host__ __device__ constexpr int epilogue_warps(int epi) { return epi == 0 ? 8 : B2_GEGLU_EPILOGUE_WARPS; }
+__host__ __device__ constexpr int epilogue_warps(int epi) { return epi != 0 ? B2_GEGLU_EPILOGUE_WARPS : 8; }
 constexpr int FIRST_EPILOGUE_WARP = 2;
 __host__ __device__ constexpr int gemm_threads(int epi) { return 32 * (FIRST_EPILOGUE_WARP + epilogue_warps(epi)); }
 constexpr int TILE_TOKENS = 128;                   // MMA M
@@ -64,7 +64,8 @@ constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int MAX_COMPACT_GELU = 4096;             // magnitude codes of the GELU table kept in shared memory
 constexpr int SMEM_MINIMUM = 120 * 1024;           // keeps a second CTA (and its TMEM request) off the SM
 
-enum { EPI_LINEAR = 0, EPI_GEGLU_BF16 = 1, EPI_GEGLU_FP8 = 2, EPI_GEGLU_NVFP4 = 3 };
+enum { EPI_LINEAR = 0, EPI_GEGLU_BF16 = 1, EPI_GEGLU_FP8 = 2, EPI_GEGLU_NVFP4 = 3, EPI_GELU_BF16 = 4, EPI_GELU_FP8 = 5 };
+__host__ __device__ constexpr bool is_gated(int epi) { return epi >= EPI_GEGLU_BF16 && epi <= EPI_GEGLU_NVFP4; }
 
 struct KernelArgs {
     int tokens, features, k_bytes, num_kb;
@@ -113,57 +114,6 @@ __device__ __forceinline__ float gemm_value(uint32_t acc_bits, float scale, bool
 
 __device__ __forceinline__ void store_u4(void* pointer, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     *reinterpret_cast<uint4*>(pointer) = make_uint4(a, b, c, d);
-}
-
-// 32 accumulator columns of one token -> 32 bf16 outputs (64 contiguous bytes): one packed multiply and
-// one two-value conversion per pair, 32-byte stores where the row allows them.
-__device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32], const KernelArgs& args, float scale,
-                                                      bool round_scale, int token, int feature0) {
-    uint32_t y[16];                                   // bf16 pairs
-    const float2 scale2 = make_float2(scale, scale);
-#pragma unroll
-    for (int p = 0; p < 16; ++p) {
-        float2 value = make_float2(__uint_as_float(acc[2 * p]), __uint_as_float(acc[2 * p + 1]));
-        if (round_scale) value = bf16x2_to_float2(float2_to_bf16x2(value));     // nvfp4.py:120: the GEMM's own bf16 output
-        y[p] = float2_to_bf16x2(__fmul2_rn(value, scale2));
-    }
-    if (args.bias != nullptr) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            if (feature0 + 8 * v < args.features) {
-                const uint4 packed = __ldg(reinterpret_cast<const uint4*>(args.bias + feature0 + 8 * v));
-                const uint32_t b[4] = {packed.x, packed.y, packed.z, packed.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    y[4 * v + i] = float2_to_bf16x2(__fadd2_rn(bf16x2_to_float2(y[4 * v + i]), bf16x2_to_float2(b[i])));
-            }
-        }
-    }
-    if (token >= args.tokens) return;
-    const int64_t row = int64_t(token) * args.features;
-    if (args.residual != nullptr) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            if (feature0 + 8 * v < args.features) {
-                const uint4 packed = ld_nc_u4(reinterpret_cast<const uint4*>(args.residual + row + feature0 + 8 * v));
-                const uint32_t r[4] = {packed.x, packed.y, packed.z, packed.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    y[4 * v + i] = float2_to_bf16x2(__fadd2_rn(bf16x2_to_float2(y[4 * v + i]), bf16x2_to_float2(r[i])));
-            }
-        }
-    }
-    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out) + row + feature0;
-    if (feature0 + 32 <= args.features && aligned32(out)) {
-        const uint32_t first[8] = {y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]};
-        const uint32_t second[8] = {y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]};
-        st_u8(out, first);
-        st_u8(out + 16, second);
-        return;
-    }
-#pragma unroll
-    for (int v = 0; v < 4; ++v)
-        if (feature0 + 8 * v < args.features) store_u4(out + 8 * v, y[4 * v], y[4 * v + 1], y[4 * v + 2], y[4 * v + 3]);
 }
 
 // bf16 pair from two floats in one conversion: low half = `low`, high half = `high`.
@@ -226,6 +176,105 @@ __device__ __forceinline__ void gelu_lookup_unit(const uint32_t (&gate)[8], uint
             gelu[p] = gelu_lookup_general(gate[p] & 0xffffu, args, compact_table, lo, span) |
                       (gelu_lookup_general(gate[p] >> 16, args, compact_table, lo, span) << 16);
     }
+}
+
+// 32 accumulator columns of one token -> 32 bf16 outputs (64 contiguous bytes): one packed multiply and
+// one two-value conversion per pair, 32-byte stores where the row allows them.
+// EPI_GELU_*: the bf16 result goes through the GELU table and is stored as bf16 or, divided by *out_scale,
+// as e4m3 (32 contiguous bytes) -- SigLIP's fc1 (bias + tanh GELU + the encoder of fc2's input in one launch).
+template <int EPI>
+__device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32], const KernelArgs& args, float scale,
+                                                      bool round_scale, int token, int feature0, uint32_t compact_table,
+                                                      const ExactDivider& out_scale, float out_scale_rcp, bool true_div) {
+    uint32_t y[16];                                   // bf16 pairs
+    const float2 scale2 = make_float2(scale, scale);
+#pragma unroll
+    for (int p = 0; p < 16; ++p) {
+        float2 value = make_float2(__uint_as_float(acc[2 * p]), __uint_as_float(acc[2 * p + 1]));
+        if (round_scale) value = bf16x2_to_float2(float2_to_bf16x2(value));     // nvfp4.py:120: the GEMM's own bf16 output
+        y[p] = float2_to_bf16x2(__fmul2_rn(value, scale2));
+    }
+    if (args.bias != nullptr) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (feature0 + 8 * v < args.features) {
+                const uint4 packed = __ldg(reinterpret_cast<const uint4*>(args.bias + feature0 + 8 * v));
+                const uint32_t b[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    y[4 * v + i] = float2_to_bf16x2(__fadd2_rn(bf16x2_to_float2(y[4 * v + i]), bf16x2_to_float2(b[i])));
+            }
+        }
+    }
+    if (EPI != EPI_LINEAR) {
+        const uint32_t lo = uint32_t(args.gelu_lo), span = uint32_t(args.gelu_hi - args.gelu_lo);
+        uint32_t in[8], out[8];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) in[i] = y[8 * half + i];
+            gelu_lookup_unit(in, out, args, compact_table, lo, span);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) y[8 * half + i] = out[i];
+        }
+    }
+    if (token >= args.tokens) return;
+    const int64_t row = int64_t(token) * args.features;
+    if (EPI == EPI_GELU_FP8) {
+        uint32_t codes[8];
+        if (true_div) {
+            const float bound = __fmul_rn(1024.0f, out_scale.divisor);
+            uint32_t in[8], part[4];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) in[i] = y[8 * half + i];
+                encode_fp8_words<true, 8>(in, part, out_scale, bound);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) codes[4 * half + i] = part[i];
+            }
+        } else {
+            const float2 rcp2 = make_float2(out_scale_rcp, out_scale_rcp);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t low = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(y[2 * i]), rcp2), __NV_SATFINITE, __NV_E4M3);
+                const uint32_t high = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(y[2 * i + 1]), rcp2), __NV_SATFINITE, __NV_E4M3);
+                codes[i] = low | (high << 16);
+            }
+        }
+        uint8_t* out8 = static_cast<uint8_t*>(args.out) + row + feature0;
+        if (feature0 + 32 <= args.features && aligned32(out8)) {
+            st_u8(out8, codes);
+        } else {
+#pragma unroll
+            for (int v = 0; v < 4; ++v)        // 8 features = 8 bytes per step
+                if (feature0 + 8 * v < args.features) *reinterpret_cast<uint2*>(out8 + 8 * v) = make_uint2(codes[2 * v], codes[2 * v + 1]);
+        }
+        return;
+    }
+    if (args.residual != nullptr) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (feature0 + 8 * v < args.features) {
+                const uint4 packed = ld_nc_u4(reinterpret_cast<const uint4*>(args.residual + row + feature0 + 8 * v));
+                const uint32_t r[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    y[4 * v + i] = float2_to_bf16x2(__fadd2_rn(bf16x2_to_float2(y[4 * v + i]), bf16x2_to_float2(r[i])));
+            }
+        }
+    }
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out) + row + feature0;
+    if (feature0 + 32 <= args.features && aligned32(out)) {
+        const uint32_t first[8] = {y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]};
+        const uint32_t second[8] = {y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]};
+        st_u8(out, first);
+        st_u8(out + 16, second);
+        return;
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+        if (feature0 + 8 * v < args.features) store_u4(out + 8 * v, y[4 * v], y[4 * v + 1], y[4 * v + 2], y[4 * v + 3]);
 }
 
 // One 16-feature unit of a token's row: 16 gate + 16 up accumulator columns -> 16 hidden values
@@ -373,7 +422,8 @@ template <int KIND, int EPI>
 __global__ void __launch_bounds__(gemm_threads(EPI), 1)
 linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
               const KernelArgs args) {
-    constexpr bool GEGLU = EPI != EPI_LINEAR;
+    constexpr bool GEGLU = is_gated(EPI);
+    constexpr bool USES_TABLE = EPI != EPI_LINEAR;
     extern __shared__ uint8_t shared_raw[];
     const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
     const int BN = args.tile_n;
@@ -421,7 +471,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         tmem_alloc(tmem_slot, TMEM_COLUMNS);
         tmem_relinquish();
     }
-    if (GEGLU) {
+    if (USES_TABLE) {
         const int span = args.gelu_hi - args.gelu_lo;
         for (int i = threadIdx.x; i < 2 * span; i += gemm_threads(EPI)) {
             const int code = i < span ? args.gelu_lo + i : 0x8000 + args.gelu_lo + (i - span);
@@ -718,7 +768,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             if (round_scale) scale_up = round_to_bf16(scale_up);
         }
         float out_scale_value = 1.0f, out_scale_rcp = 1.0f;
-        if (EPI == EPI_GEGLU_FP8 || EPI == EPI_GEGLU_NVFP4) {
+        if (EPI == EPI_GEGLU_FP8 || EPI == EPI_GEGLU_NVFP4 || EPI == EPI_GELU_FP8) {
             out_scale_value = __ldg(args.out_scale);
             out_scale_rcp = __fdiv_rn(1.0f, out_scale_value);
         }
@@ -828,7 +878,8 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         tmem_load_32x32(lane_address + chunk * 32, first);
                         tmem_load_wait();
                     }
-                    epilogue_linear_chunk(first, args, scale, round_scale, token, f0 + chunk * 32);
+                    epilogue_linear_chunk<GEGLU ? EPI_LINEAR : EPI>(first, args, scale, round_scale, token, f0 + chunk * 32, compact_table,
+                                                                    out_scale, out_scale_rcp, true_div);
                 }
             }
             if (sums == nullptr) {                 // (split K released the accumulator right after the dump)
@@ -953,7 +1004,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     if (d == nullptr) return B2_E_INVALID;
     const bool planning = workspace_need != nullptr;
     if (d->kind != B2_KIND_FP8 && d->kind != B2_KIND_NVFP4) return B2_E_UNSUPPORTED;
-    if (d->epilogue != B2_EPI_LINEAR && d->epilogue != B2_EPI_GEGLU) return B2_E_UNSUPPORTED;
+    if (d->epilogue != B2_EPI_LINEAR && d->epilogue != B2_EPI_GEGLU && d->epilogue != B2_EPI_GELU) return B2_E_UNSUPPORTED;
     if (d->tokens <= 0 || d->features <= 0 || d->width <= 0) return B2_E_INVALID;
     if (!planning) {
         if (d->act == nullptr || d->weight == nullptr || d->act_scale == nullptr || d->weight_scale == nullptr ||
@@ -979,6 +1030,13 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         if (!planning && epilogue != EPI_GEGLU_BF16 && d->out_scale == nullptr) return B2_E_INVALID;
         if (d->features % 16 != 0) return B2_E_UNSUPPORTED;            // whole output vectors / blocks
         if (nvfp4 && d->features % 128 != 0) return B2_E_UNSUPPORTED;   // the up rows must start a scale block
+    } else if (d->epilogue == B2_EPI_GELU) {
+        if ((!planning && d->gelu_table == nullptr) || d->residual != nullptr) return B2_E_INVALID;
+        if (d->out_format == B2_OUT_BF16) epilogue = EPI_GELU_BF16;
+        else if (d->out_format == B2_OUT_FP8) epilogue = EPI_GELU_FP8;
+        else return B2_E_UNSUPPORTED;
+        if (!planning && epilogue == EPI_GELU_FP8 && d->out_scale == nullptr) return B2_E_INVALID;
+        if (d->features % 8 != 0) return B2_E_UNSUPPORTED;
     } else {
         if (d->out_format != B2_OUT_BF16) return B2_E_UNSUPPORTED;
         if (d->features % 8 != 0) return B2_E_UNSUPPORTED;             // 16-byte output vectors
@@ -1026,7 +1084,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     int stage_bytes = A_TILE_BYTES + args.tile_n * STAGE_K_BYTES;
     int scale_stage_bytes = nvfp4 ? (1 + args.scale_blocks) * SCALE_PART_BYTES : 0;
     args.gelu_lo = args.gelu_hi = 0;
-    if (geglu && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
+    if (epilogue != EPI_LINEAR && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
         d->gelu_hi - d->gelu_lo <= MAX_COMPACT_GELU) {
         args.gelu_lo = d->gelu_lo;
         args.gelu_hi = d->gelu_hi;
@@ -1100,6 +1158,8 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
             case EPI_LINEAR: return launch_linear<B2_KIND_NVFP4, EPI_LINEAR>(act_map, weight_map, args, shared_bytes, stream);
             case EPI_GEGLU_BF16: return launch_linear<B2_KIND_NVFP4, EPI_GEGLU_BF16>(act_map, weight_map, args, shared_bytes, stream);
             case EPI_GEGLU_FP8: return launch_linear<B2_KIND_NVFP4, EPI_GEGLU_FP8>(act_map, weight_map, args, shared_bytes, stream);
+            case EPI_GELU_BF16: return launch_linear<B2_KIND_NVFP4, EPI_GELU_BF16>(act_map, weight_map, args, shared_bytes, stream);
+            case EPI_GELU_FP8: return launch_linear<B2_KIND_NVFP4, EPI_GELU_FP8>(act_map, weight_map, args, shared_bytes, stream);
             default: return launch_linear<B2_KIND_NVFP4, EPI_GEGLU_NVFP4>(act_map, weight_map, args, shared_bytes, stream);
         }
     }
@@ -1107,6 +1167,8 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         case EPI_LINEAR: return launch_linear<B2_KIND_FP8, EPI_LINEAR>(act_map, weight_map, args, shared_bytes, stream);
         case EPI_GEGLU_BF16: return launch_linear<B2_KIND_FP8, EPI_GEGLU_BF16>(act_map, weight_map, args, shared_bytes, stream);
         case EPI_GEGLU_FP8: return launch_linear<B2_KIND_FP8, EPI_GEGLU_FP8>(act_map, weight_map, args, shared_bytes, stream);
+        case EPI_GELU_BF16: return launch_linear<B2_KIND_FP8, EPI_GELU_BF16>(act_map, weight_map, args, shared_bytes, stream);
+        case EPI_GELU_FP8: return launch_linear<B2_KIND_FP8, EPI_GELU_FP8>(act_map, weight_map, args, shared_bytes, stream);
         default: return launch_linear<B2_KIND_FP8, EPI_GEGLU_NVFP4>(act_map, weight_map, args, shared_bytes, stream);
     }
 }

@@ -26,7 +26,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from .backend.mlp import FusedMlpPlan
+from .backend.mlp import FusedGeluMlpPlan, FusedMlpPlan
 from .backend.quantization import B200Quantizer
 from .bundles import pack_quantized_linears, quantize_linear
 from .layers.linear import FP8Config, NVFP4Config, parse_quantization_config
@@ -157,8 +157,13 @@ class SiglipBlock(nn.Module):
         width = shape.width
         self.qkv = _quantized((make(3 * width, width),), config)
         self.out = _quantized((make(width, width),), config)
-        self.fc1 = _quantized((make(shape.mlp, width),), config)
-        self.fc2 = _quantized((make(width, shape.mlp),), config)
+        fc1, fc2 = make(shape.mlp, width), make(width, shape.mlp)
+        self.fc1 = _quantized((fc1,), config)
+        self.fc2 = _quantized((fc2,), config)
+        self.dense_mlp = (fc1.weight.detach(), fc1.bias.detach(), fc2.weight.detach(), fc2.bias.detach())
+        self.fused_mlp: FusedGeluMlpPlan | None = None
+        self.mlp_ranges = [0.0, 0.0]
+        self.recording = False
         self.norm1 = nn.LayerNorm(width, eps=1e-6, device=device, dtype=torch.bfloat16)
         self.norm2 = nn.LayerNorm(width, eps=1e-6, device=device, dtype=torch.bfloat16)
 
@@ -167,7 +172,21 @@ class SiglipBlock(nn.Module):
         heads, head_dim = self.shape.heads, self.shape.head_dim
         q, k, v = self.qkv(self.norm1(x)).view(batch, tokens, 3, heads, head_dim).permute(2, 0, 3, 1, 4)
         x = x + self.out(F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(batch, tokens, width))
-        return x + self.fc2(F.gelu(self.fc1(self.norm2(x)), approximate="tanh"))
+        normed = self.norm2(x)
+        if self.fused_mlp is not None:
+            rows = normed.reshape(-1, width)
+            return self.fused_mlp(rows, residual=x.reshape(rows.shape)).reshape(x.shape)
+        hidden = F.gelu(self.fc1(normed), approximate="tanh")
+        if self.recording:
+            self.mlp_ranges[0] = max(self.mlp_ranges[0], float(normed.abs().max()))
+            self.mlp_ranges[1] = max(self.mlp_ranges[1], float(hidden.abs().max()))
+        return x + self.fc2(hidden)
+
+    def build_fused_mlp(self, quantizer: B200Quantizer, margin: float = 1.0) -> None:
+        fc1_weight, fc1_bias, fc2_weight, fc2_bias = self.dense_mlp
+        self.fused_mlp = FusedGeluMlpPlan(fc1_weight, fc1_bias, fc2_weight, fc2_bias, fc1_max=margin * self.mlp_ranges[0],
+                                          fc2_max=margin * self.mlp_ranges[1], quantizer=quantizer)
+        self.dense_mlp = None
 
 
 class Pi05ShapedPolicy(nn.Module):
@@ -268,9 +287,10 @@ class Pi05ShapedPolicy(nn.Module):
 
     @torch.no_grad()
     def calibrate_fused_mlp(self, observations: dict, margin: float = 1.0) -> None:
-        """Run ``observations`` through the registry route, record every Gemma MLP's input and hidden
-        ranges, and switch those MLPs to the calibrated fused plan (three launches, static scales)."""
-        blocks = [*self.prefix, *self.expert]
+        """Run ``observations`` through the registry route, record every MLP's input and hidden ranges, and
+        switch the MLPs (Gemma: gated; SigLIP: bias + GELU, FP8) to the calibrated fused plans (three launches
+        each, static scales)."""
+        blocks = [*self.vision, *self.prefix, *self.expert]
         for block in blocks:
             block.recording = True
         self.forward(observations)

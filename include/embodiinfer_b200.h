@@ -101,9 +101,11 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
 
 #define B2_EPI_LINEAR 0 /* out = act * weight^T (+bias)(+residual) */
 #define B2_EPI_GEGLU 1  /* weight holds [gate; up] (2*features rows): out = GELU(act*gate^T) * (act*up^T) */
+#define B2_EPI_GELU 2   /* out = GELU(act*weight^T + bias) through the table; bf16, or e4m3 at *out_scale (B2_OUT_FP8):
+                           SigLIP fc1 + bias + tanh-GELU + the encoder of fc2's input (policies/pi05/inference/vision.py:441-576) */
 
 #define B2_OUT_BF16 0
-#define B2_OUT_FP8 1    /* GEGLU only: e4m3 at *out_scale                   (fusion.cu:64-107) */
+#define B2_OUT_FP8 1    /* GEGLU, GELU: e4m3 at *out_scale                   (fusion.cu:64-107) */
 #define B2_OUT_NVFP4 2  /* GEGLU only: packed e2m1 + block scales at *out_scale (fusion.cu:31-62) */
 
 #define B2_LINEAR_ROUND_SCALE_BF16 1 /* NVFP4 registry route: y = bf16(bf16(acc) * bf16(g_a*g_w))

@@ -209,6 +209,33 @@ def test_split_k_is_deterministic_and_matches_oracle(device, kind, epilogue, tok
     assert_gemm_close(outputs[2], want)
 
 
+@pytest.mark.parametrize("kind,tokens,features,width", [("fp8", 256, 4304, 1152), ("fp8", 130, 384, 1024), ("nvfp4", 130, 384, 1024)])
+def test_bias_gelu_epilogue(device, kind, tokens, features, width):
+    """out = gelu(x W^T + bias): bf16 against the oracle; e4m3 output identical to encoding the kernel's own
+    bf16 result (reciprocal multiply, and true division with B2_GEGLU_TRUE_DIV), with and without a table range."""
+    host, dev = operands(kind, tokens, features, width, 31 + features, device)
+    bias = make_weight((1, features), 9, std=0.5).to(torch.bfloat16).reshape(-1)
+    table_host = gelu_table_cpu("tanh")
+    table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+    common = dict(epilogue=N.EPI_GELU, tokens=tokens, features=features, width=width, bias=bias.to(device), gelu_table=table, **dev)
+    hidden = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+    K.linear(out_format=N.OUT_BF16, out=hidden, **common)
+    y = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+    y = O.f32_to_bf16(O.bf16_to_f32(y) + O.bf16_to_f32(bits(bias))[None, :])
+    assert_gemm_close(bits(hidden), table_host[y])
+    got = bits(hidden)
+    ranged = torch.empty_like(hidden)
+    K.linear(out_format=N.OUT_BF16, out=ranged, gelu_range=K.gelu_table_range(table), **common)
+    assert np.array_equal(bits(ranged), got)
+    scale = np.float32(float(np.abs(O.bf16_to_f32(got)).max()) / 448.0)
+    out8 = torch.empty((tokens, features), device=device, dtype=torch.uint8)
+    K.linear(out_format=N.OUT_FP8, out=out8, out_scale=torch.tensor(float(scale), device=device), **common)
+    assert np.array_equal(u8(out8), O.e4m3_encode_satfinite((O.bf16_to_f32(got) * (np.float32(1.0) / scale)).astype(np.float32)))
+    K.linear(out_format=N.OUT_FP8, out=out8, out_scale=torch.tensor(float(scale), device=device), flags=N.GEGLU_TRUE_DIV,
+             gelu_range=K.gelu_table_range(table), **common)
+    assert np.array_equal(u8(out8), O.fp8_quantize_C(got, scale)[0])
+
+
 def test_gated_with_separate_up_scale(device):
     """gate and up quantised separately (two per-tensor scales) give the same result as two Linears."""
     tokens, features, width = 96, 128, 256

@@ -58,7 +58,7 @@ def test_calibrated_fused_mlp_route_stays_close_to_the_registry_route(device, qu
     observations = synthetic_observations(3, vocabulary=4096)
     reference = policy(observations)
     policy.calibrate_fused_mlp(observations)
-    assert all(block.fused_mlp is not None for block in [*policy.prefix, *policy.expert])
+    assert all(block.fused_mlp is not None for block in [*policy.vision, *policy.prefix, *policy.expert])
     fused = policy(observations)
     assert torch.isfinite(fused).all() and torch.equal(fused, policy(observations))
     error = (fused - reference).norm() / reference.norm()
