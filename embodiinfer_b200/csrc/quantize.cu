@@ -175,67 +175,87 @@ nvfp4_encode_kernel(const uint4* __restrict__ input, uint32_t* __restrict__ outp
     }
 }
 
-// Wide variant for 32-byte aligned matrices: one thread owns a whole 16-element block (one 32-byte load,
-// one 8-byte store of codes), so the block maximum needs no shuffle and the scale arithmetic runs once per
-// block; four adjacent threads assemble one 4-byte word of scale bytes.
+// Wide variant for 32-byte aligned matrices: one thread owns whole 16-element blocks (one 32-byte load and
+// one 8-byte store of codes each), so the block maximum needs no shuffle and the scale arithmetic runs once
+// per block.  BLOCKS = 2 (rows of a multiple of 32 elements): two adjacent blocks per thread, both loads in
+// flight before any arithmetic, 16-byte code stores, and two adjacent threads assemble a 4-byte word of
+// scale bytes; BLOCKS = 1: four adjacent threads do.
 template <bool SPEC_C>
+__device__ __forceinline__ uint2 nvfp4_encode_block(const uint32_t (&w)[8], float global, const ExactDivider& by_global,
+                                                    int flags, uint8_t& scale_code) {
+    const float maximum = abs_max_bf16_words(w);
+    scale_code = nvfp4_block_scale<SPEC_C>(maximum, by_global, flags);
+    const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
+    uint2 codes;
+    if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f) {
+        codes.x = nvfp4_encode_words_short<SPEC_C>(w[0], w[1], w[2], w[3], denominator);
+        codes.y = nvfp4_encode_words_short<SPEC_C>(w[4], w[5], w[6], w[7], denominator);
+    } else {
+        float low[8], high[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            low[2 * i] = bf16_lo(w[i]); low[2 * i + 1] = bf16_hi(w[i]);
+            high[2 * i] = bf16_lo(w[4 + i]); high[2 * i + 1] = bf16_hi(w[4 + i]);
+        }
+        codes.x = nvfp4_encode_x8<SPEC_C>(low, denominator, maximum);
+        codes.y = nvfp4_encode_x8<SPEC_C>(high, denominator, maximum);
+    }
+    return codes;
+}
+
+template <bool SPEC_C, int BLOCKS>
 __global__ void __launch_bounds__(QUANT_THREADS)
-nvfp4_encode_wide_kernel(const uint8_t* __restrict__ input, uint2* __restrict__ output, uint8_t* __restrict__ scales,
+nvfp4_encode_wide_kernel(const uint8_t* __restrict__ input, uint8_t* __restrict__ output, uint8_t* __restrict__ scales,
                          uint8_t* __restrict__ blocked, const float* __restrict__ global_pointer, int rows, int columns,
                          int flags) {
     const int blocks_per_row = columns >> 4;
     const int column_tiles = (blocks_per_row + 3) >> 2;
-    const int64_t total = int64_t(rows) * blocks_per_row;
+    const int items_per_row = blocks_per_row / BLOCKS;                 // one item = BLOCKS adjacent blocks of one row
+    const int64_t total = int64_t(rows) * items_per_row;
     const float global = __ldg(global_pointer);
     const ExactDivider by_global(SPEC_C ? __fmul_rn(6.0f, global) : global);
     const bool whole_words = (blocks_per_row & 3) == 0;
+    constexpr int LANES_PER_WORD = 4 / BLOCKS;
     const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
     const int lane = threadIdx.x & 31;
-    // warp-uniform loop: `total` is a multiple of 4 whenever whole words are stored, so the four lanes of
-    // a scale word are active together
+    // warp-uniform loop: `total` is a multiple of LANES_PER_WORD whenever whole words are stored, so the
+    // lanes of a scale word are active together
     for (int64_t warp_base = int64_t(blockIdx.x) * QUANT_THREADS + (threadIdx.x - lane); warp_base < total;
          warp_base += stride) {
         const int64_t index = warp_base + lane;
         const bool active = index < total;
         const unsigned int mask = __ballot_sync(0xffffffffu, active);
         if (!active) continue;
-        uint32_t w[8];
-        ld_nc_u8(input + index * 32, w);
-        const float maximum = abs_max_bf16_words(w);
-        const uint8_t scale_code = nvfp4_block_scale<SPEC_C>(maximum, by_global, flags);
-        const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
-        uint2 codes;
-        if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f) {
-            codes.x = nvfp4_encode_words_short<SPEC_C>(w[0], w[1], w[2], w[3], denominator);
-            codes.y = nvfp4_encode_words_short<SPEC_C>(w[4], w[5], w[6], w[7], denominator);
-        } else {
-            float low[8], high[8];
+        uint32_t w[BLOCKS][8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                low[2 * i] = bf16_lo(w[i]); low[2 * i + 1] = bf16_hi(w[i]);
-                high[2 * i] = bf16_lo(w[4 + i]); high[2 * i + 1] = bf16_hi(w[4 + i]);
-            }
-            codes.x = nvfp4_encode_x8<SPEC_C>(low, denominator, maximum);
-            codes.y = nvfp4_encode_x8<SPEC_C>(high, denominator, maximum);
-        }
-        output[index] = codes;
-        const int row = total <= 0x7fffffff ? int(uint32_t(index) / uint32_t(blocks_per_row)) : int(index / blocks_per_row);
-        const int block = int(index - int64_t(row) * blocks_per_row);
+        for (int b = 0; b < BLOCKS; ++b) ld_nc_u8(input + (index * BLOCKS + b) * 32, w[b]);
+        uint8_t code[BLOCKS];
+        uint2 codes[BLOCKS];
+#pragma unroll
+        for (int b = 0; b < BLOCKS; ++b) codes[b] = nvfp4_encode_block<SPEC_C>(w[b], global, by_global, flags, code[b]);
+        if (BLOCKS == 2) *reinterpret_cast<uint4*>(output + index * 16) = make_uint4(codes[0].x, codes[0].y, codes[BLOCKS - 1].x, codes[BLOCKS - 1].y);
+        else *reinterpret_cast<uint2*>(output + index * 8) = codes[0];
+        const int row = total <= 0x7fffffff ? int(uint32_t(index) / uint32_t(items_per_row)) : int(index / items_per_row);
+        const int block = int(index - int64_t(row) * items_per_row) * BLOCKS;
         if (whole_words) {
-            const int base = lane & ~3;
-            unsigned int word = scale_code;
-            word |= (unsigned int)__shfl_sync(mask, (unsigned int)scale_code, base + 1) << 8;
-            word |= (unsigned int)__shfl_sync(mask, (unsigned int)scale_code, base + 2) << 16;
-            word |= (unsigned int)__shfl_sync(mask, (unsigned int)scale_code, base + 3) << 24;
-            if ((lane & 3) == 0) {
+            const int base = lane & ~(LANES_PER_WORD - 1);
+            unsigned int mine = code[0];
+            if (BLOCKS == 2) mine |= (unsigned int)code[BLOCKS - 1] << 8;
+            unsigned int word = 0;
+#pragma unroll
+            for (int i = 0; i < LANES_PER_WORD; ++i) word |= __shfl_sync(mask, mine, base + i) << (8 * BLOCKS * i);
+            if ((lane & (LANES_PER_WORD - 1)) == 0) {
                 if (blocked != nullptr)
                     *reinterpret_cast<uint32_t*>(blocked + scale_tile_offset(row, block, column_tiles)) = word;
                 if (scales != nullptr)
                     *reinterpret_cast<uint32_t*>(scales + int64_t(row) * blocks_per_row + block) = word;
             }
         } else {
-            if (blocked != nullptr) blocked[scale_tile_offset(row, block, column_tiles)] = scale_code;
-            if (scales != nullptr) scales[int64_t(row) * blocks_per_row + block] = scale_code;
+#pragma unroll
+            for (int b = 0; b < BLOCKS; ++b) {
+                if (blocked != nullptr) blocked[scale_tile_offset(row, block + b, column_tiles)] = code[b];
+                if (scales != nullptr) scales[int64_t(row) * blocks_per_row + block + b] = code[b];
+            }
         }
     }
 }
@@ -298,16 +318,21 @@ int launch_fp8_encode(const void* input, void* output, const void* scale, int64_
 
 int launch_nvfp4_encode(const void* input, void* output, void* scales, void* blocked, const void* global, int rows,
                         int columns, int flags, cudaStream_t stream) {
-    if ((reinterpret_cast<uintptr_t>(input) & 31u) == 0 && (reinterpret_cast<uintptr_t>(output) & 7u) == 0) {
-        const int grid = grid_for(int64_t(rows) * (columns >> 4), QUANT_THREADS);
-        if (flags & B2_SPEC_C)
-            nvfp4_encode_wide_kernel<true><<<grid, QUANT_THREADS, 0, stream>>>(
-                static_cast<const uint8_t*>(input), static_cast<uint2*>(output), static_cast<uint8_t*>(scales),
-                static_cast<uint8_t*>(blocked), static_cast<const float*>(global), rows, columns, flags);
-        else
-            nvfp4_encode_wide_kernel<false><<<grid, QUANT_THREADS, 0, stream>>>(
-                static_cast<const uint8_t*>(input), static_cast<uint2*>(output), static_cast<uint8_t*>(scales),
-                static_cast<uint8_t*>(blocked), static_cast<const float*>(global), rows, columns, flags);
+    if ((reinterpret_cast<uintptr_t>(input) & 31u) == 0 && (reinterpret_cast<uintptr_t>(output) & 15u) == 0) {
+        const bool pairs = (columns & 31) == 0;
+        const int grid = grid_for(int64_t(rows) * (columns >> (pairs ? 5 : 4)), QUANT_THREADS);
+        const uint8_t* in = static_cast<const uint8_t*>(input);
+        uint8_t* out = static_cast<uint8_t*>(output);
+        uint8_t* row_major = static_cast<uint8_t*>(scales);
+        uint8_t* tiled = static_cast<uint8_t*>(blocked);
+        const float* g = static_cast<const float*>(global);
+        if (flags & B2_SPEC_C) {
+            if (pairs) nvfp4_encode_wide_kernel<true, 2><<<grid, QUANT_THREADS, 0, stream>>>(in, out, row_major, tiled, g, rows, columns, flags);
+            else nvfp4_encode_wide_kernel<true, 1><<<grid, QUANT_THREADS, 0, stream>>>(in, out, row_major, tiled, g, rows, columns, flags);
+        } else {
+            if (pairs) nvfp4_encode_wide_kernel<false, 2><<<grid, QUANT_THREADS, 0, stream>>>(in, out, row_major, tiled, g, rows, columns, flags);
+            else nvfp4_encode_wide_kernel<false, 1><<<grid, QUANT_THREADS, 0, stream>>>(in, out, row_major, tiled, g, rows, columns, flags);
+        }
         return int(cudaGetLastError());
     }
     const int64_t total = int64_t(rows) * (columns >> 3);
