@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include <mutex>
+#include <type_traits>
 
 namespace b2 {
 
@@ -644,7 +645,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             int set = 0, lag_stage = 0, issued = 0;
             uint32_t lag_phase = 0;
             const uint32_t set_columns = uint32_t((resident ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
-            const uint32_t sfb_stride = 4u * uint32_t(args.scale_blocks);
             const uint64_t scale_desc = smem_desc_scale_atom(0);
             const uint32_t scale_desc_high = uint32_t(scale_desc >> 32);
             // resident order: the token scales of all K stages sit in TMEM right after the accumulators
@@ -707,16 +707,20 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         const uint32_t feature_low = atom_low + (resident ? 0u : PART);   // the stage holds no token atoms when they are resident
                         const bool two_blocks = args.scale_blocks == 2;
                         const uint32_t first_accumulate = kb != walk.kb_begin;
-                        // `count` is a literal on the full-stage path, so its loop carries no per-step conditions.
-                        auto issue = [&](const int count) {
+                        // The launch-wide choices (resident token tile, one or two feature-scale blocks, split halves) are
+                        // turned into compile-time tags once per stage, so the unrolled copies and MMAs below carry no
+                        // branches; only a ragged last K stage takes the generic count.
+                        auto issue = [&](const int count, auto resident_tag, auto two_blocks_tag, auto split_tag) {
+                            constexpr bool RESIDENT = decltype(resident_tag)::value, TWO = decltype(two_blocks_tag)::value;
+                            constexpr bool SPLIT = decltype(split_tag)::value;
                             if (KIND == B2_KIND_NVFP4) {
 #pragma unroll
                                 for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
                                     if (j < count) {
-                                        if (!resident) tc_copy_32x128b_x4(sfa_tmem + j * 4, desc_from_words(atom_low + j * ATOM, scale_desc_high));
-                                        tc_copy_32x128b_x4(sfb_tmem + j * sfb_stride, desc_from_words(feature_low + j * ATOM, scale_desc_high));
-                                        if (two_blocks)
-                                            tc_copy_32x128b_x4(sfb_tmem + j * sfb_stride + 4, desc_from_words(feature_low + PART + j * ATOM, scale_desc_high));
+                                        if (!RESIDENT) tc_copy_32x128b_x4(sfa_tmem + j * 4, desc_from_words(atom_low + j * ATOM, scale_desc_high));
+                                        tc_copy_32x128b_x4(sfb_tmem + j * (TWO ? 8 : 4), desc_from_words(feature_low + j * ATOM, scale_desc_high));
+                                        if (TWO)
+                                            tc_copy_32x128b_x4(sfb_tmem + j * 8 + 4, desc_from_words(feature_low + PART + j * ATOM, scale_desc_high));
                                     }
                                 }
                             }
@@ -728,23 +732,31 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                                     const uint64_t b_desc = desc_from_words(b_low + 2 * j, operand_high);
                                     if (KIND != B2_KIND_NVFP4) {
                                         mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, accumulate);
-                                    } else if (split_halves) {
+                                    } else if (SPLIT) {
                                         // 64 gate + 64 up features sit in the same two columns of two different scale
                                         // blocks, and a copy can only land on a multiple of four columns: the blocks stay
                                         // apart and each half gets its own MMA (gate -> columns [0,64), up -> [64,128)).
                                         mma_nvf4(d_tmem, a_desc, b_desc, idesc_half, sfa_tmem + j * 4,
-                                                 sfb_tmem + j * sfb_stride + scale_column, accumulate);
+                                                 sfb_tmem + j * 8 + scale_column, accumulate);
                                         mma_nvf4(d_tmem + 64, a_desc, desc_from_words(b_low + ((64 * STAGE_K_BYTES) >> 4) + 2 * j, operand_high), idesc_half,
-                                                 sfa_tmem + j * 4, sfb_tmem + j * sfb_stride + 4 + scale_column, accumulate);
+                                                 sfa_tmem + j * 4, sfb_tmem + j * 8 + 4 + scale_column, accumulate);
                                     } else {
                                         mma_nvf4(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4,
-                                                 sfb_tmem + j * sfb_stride + scale_column, accumulate);
+                                                 sfb_tmem + j * (TWO ? 8 : 4) + scale_column, accumulate);
                                     }
                                 }
                             }
                         };
-                        if (mmas == SCALE_ATOMS_PER_STAGE) issue(SCALE_ATOMS_PER_STAGE);
-                        else issue(mmas);
+                        using Yes = std::true_type;
+                        using No = std::false_type;
+                        auto with_count = [&](const int count) {
+                            if (KIND != B2_KIND_NVFP4) issue(count, No{}, No{}, No{});
+                            else if (split_halves) { if (resident) issue(count, Yes{}, Yes{}, Yes{}); else issue(count, No{}, Yes{}, Yes{}); }
+                            else if (two_blocks) { if (resident) issue(count, Yes{}, Yes{}, No{}); else issue(count, No{}, Yes{}, No{}); }
+                            else { if (resident) issue(count, Yes{}, No{}, No{}); else issue(count, No{}, No{}, No{}); }
+                        };
+                        if (mmas == SCALE_ATOMS_PER_STAGE) with_count(SCALE_ATOMS_PER_STAGE);
+                        else with_count(mmas);
                     tc_commit(empty_bar + 8 * stage);
                     }
                     __syncwarp();
@@ -855,13 +867,23 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                             for (int i = 0; i < 16; ++i) first[i] = second[i] = 0u;
                         }
                     } else {
+#ifdef B2_TRACE
+                        if (args.flags & 0x20000) continue;                    // debug: no TMEM loads, no math, no stores
+#endif
                         tmem_load_32x16(lane_address + unit * 16, first);
                         tmem_load_32x16(lane_address + BN / 2 + unit * 16, second);
                         tmem_load_wait();
+#ifdef B2_TRACE
+                        if (args.flags & 0x10000) continue;                    // debug: TMEM loads only
+#endif
                     }
+                    int store_token = token;
+#ifdef B2_TRACE
+                    if (args.flags & 0x40000) store_token = args.tokens + (first[0] == 0x12345678u);   // debug: math, no stores
+#endif
                     epilogue_geglu_unit<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, compact_table, scale, scale_up,
                                                                      round_scale, out_scale, by_global, out_scale_rcp,
-                                                                     true_div, token, f0 + unit * 16);
+                                                                     true_div, store_token, f0 + unit * 16);
                 }
             } else {
                 const int chunks = features_per_tile / 32;
