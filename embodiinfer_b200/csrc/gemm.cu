@@ -491,8 +491,10 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
 
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer
-        // (all lanes run the loop; one elected lane issues the copies)
-        {
+        // (all lanes run the loop; one elected lane issues the copies; like the MMA role it is specialised
+        // on the launch-wide choices and entered once)
+        auto producer_role = [&](auto resident_tag, auto prefetch_tag) {
+            constexpr bool RESIDENT = decltype(resident_tag)::value, PREFETCH = decltype(prefetch_tag)::value;
             int stage = 0;
             uint32_t phase = 0;
             int trace_index = 0; (void)trace_index;
@@ -506,10 +508,9 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             int pf_kb = 0;
             for (int i = 0; i < PREFETCH_DISTANCE; ++i)
                 if (++pf_kb == num_kb) { pf_kb = 0; pf.next(args); }
-            const bool prefetching = args.splits == 1;      // split K ranges are a few stages long: nothing to run ahead of
             int pf_f0 = 0, pf_turn = 0, pf_seen = -1;      // feature row of the cursor's tile; stages until this CTA's turn
             TileWalk walk(args);
-            const bool panel_loaded = resident && walk.valid(args);
+            const bool panel_loaded = RESIDENT && walk.valid(args);
             if (panel_loaded) {
                 // the token tile for all of K, and its scale atoms, once
                 if (elect_one()) {
@@ -555,7 +556,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 int live = 0;
                 if (KIND == B2_KIND_NVFP4) {
                     token_scales = args.act_scales + int64_t(m_tile) * args.scale_column_tiles * SCALE_ATOM_BYTES;
-                    live = resident ? 0 : 1;
+                    live = RESIDENT ? 0 : 1;
                     for (int i = 0; i < scale_blocks; ++i)
                         if (scale_row_block[i] < args.weight_row_blocks) {
                             feature_scales[i] = args.weight_scales + int64_t(scale_row_block[i]) * args.scale_column_tiles * SCALE_ATOM_BYTES;
@@ -578,20 +579,20 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         const int k0 = kb * STAGE_K_BYTES;
                         const uint32_t copy_bytes = uint32_t(kb == num_kb - 1 ? tail_atoms : SCALE_ATOMS_PER_STAGE) * SCALE_ATOM_BYTES;
                         mbar_expect_tx(bar, stage_bytes + (KIND == B2_KIND_NVFP4 ? uint32_t(live) * copy_bytes : 0u));
-                        if (!resident) tma_load_2d(a_smem, &act_map, bar, k0, m0);
+                        if (!RESIDENT) tma_load_2d(a_smem, &act_map, bar, k0, m0);
                         tma_load_2d(b_smem, &weight_map, bar, k0, f0);
                         if (GEGLU) tma_load_2d(b_smem + up_smem_offset, &weight_map, bar, k0, up_row);
                         if (KIND == B2_KIND_NVFP4) {
                             const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
                             const int64_t offset = int64_t(kb) * (SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES);
-                            if (!resident) bulk_load(s_smem, token_scales + offset, copy_bytes, bar);
+                            if (!RESIDENT) bulk_load(s_smem, token_scales + offset, copy_bytes, bar);
                             if (feature_scales[0] != nullptr)
                                 bulk_load(s_smem + token_part_bytes, feature_scales[0] + offset, copy_bytes, bar);
                             if (feature_scales[1] != nullptr)
                                 bulk_load(s_smem + token_part_bytes + SCALE_PART_BYTES, feature_scales[1] + offset, copy_bytes, bar);
                         }
                     }
-                    if (prefetching && pf.valid(args)) {
+                    if (PREFETCH && pf.valid(args)) {
                         if (pf.n_tile != pf_seen) {
                             pf_f0 = pf.n_tile * features_per_tile;
                             pf_turn = (pf.m_tile + args.num_m_tiles - pf_kb % args.num_m_tiles) % args.num_m_tiles;
@@ -620,11 +621,21 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     mbar_wait(full_bar + 8 * s, (fill_parity >> s) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
             if (panel_loaded)
                 for (int kb = 0; kb < num_kb; ++kb) mbar_wait(panel_bar + 8 * kb, 0u, drain_failed, args.status, STATUS_WAIT_DRAIN);
-        }
+        };
+        using Yes = std::true_type;
+        using No = std::false_type;
+        // (split K ranges are a few stages long: nothing to prefetch ahead of)
+        if (resident) { if (args.splits == 1) producer_role(Yes{}, Yes{}); else producer_role(Yes{}, No{}); }
+        else { if (args.splits == 1) producer_role(No{}, Yes{}); else producer_role(No{}, No{}); }
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
         // (all lanes run the loop; one elected lane issues the tcgen05 instructions)
-        {
+        // The launch-wide choices (resident token tile, one or two feature-scale blocks, split halves) are
+        // compile-time tags of the role: it is entered once through the dispatch below, and the unrolled
+        // copies and MMAs of its stage loop carry no branches.
+        auto mma_role = [&](auto resident_tag, auto two_blocks_tag, auto split_tag) {
+            constexpr bool RESIDENT = decltype(resident_tag)::value, TWO = decltype(two_blocks_tag)::value;
+            constexpr bool SPLIT = decltype(split_tag)::value;
             // Descriptors are a constant high word plus (address >> 4), and everything that depends only
             // on the tile is computed once per tile.
             const uint32_t idesc = KIND == B2_KIND_NVFP4 ? idesc_nvf4(TILE_TOKENS, BN) : idesc_f8(TILE_TOKENS, BN);
@@ -632,7 +643,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             const uint64_t operand_desc = smem_desc_sw128(0);        // + (address >> 4)
             const uint32_t operand_low = uint32_t(operand_desc), operand_high = uint32_t(operand_desc >> 32);
             const bool paired_scales = GEGLU && (args.flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
-            const bool split_halves = KIND == B2_KIND_NVFP4 && GEGLU && BN == 128 && !paired_scales;
             int stage = 0;
             uint32_t phase = 0;
             int local_tile = 0;
@@ -644,13 +654,13 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             int trace_index = 0; (void)trace_index;
             int set = 0, lag_stage = 0, issued = 0;
             uint32_t lag_phase = 0;
-            const uint32_t set_columns = uint32_t((resident ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
+            const uint32_t set_columns = uint32_t((RESIDENT ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
             const uint64_t scale_desc = smem_desc_scale_atom(0);
             const uint32_t scale_desc_high = uint32_t(scale_desc >> 32);
             // resident order: the token scales of all K stages sit in TMEM right after the accumulators
             const uint32_t resident_sfa = tmem_base + uint32_t(args.accumulators * args.accumulator_stride);
             TileWalk walk(args);
-            if (resident && KIND == B2_KIND_NVFP4 && walk.valid(args)) {
+            if (RESIDENT && KIND == B2_KIND_NVFP4 && walk.valid(args)) {
                 for (int kb = 0; kb < num_kb; ++kb) {
                     mbar_wait(panel_bar + 8 * kb, 0u, failed, args.status, STATUS_WAIT_MMA_FULL);
                     tc_fence_after_sync();
@@ -680,16 +690,16 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
                     tc_fence_after_sync();
                     const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
-                    if (resident && local_tile == 0) {       // first pass over K: the token tile may still be landing
+                    if (RESIDENT && local_tile == 0) {       // first pass over K: the token tile may still be landing
                         mbar_wait(panel_bar + 8 * kb, 0u, failed, args.status, STATUS_WAIT_MMA_FULL);
                         tc_fence_after_sync();
                     }
                     const uint32_t stage_smem = stage_base + uint32_t(stage) * stage_bytes;
-                    const uint32_t a_low = operand_low + ((resident ? panel_base + uint32_t(kb) * A_TILE_BYTES : stage_smem) >> 4);
+                    const uint32_t a_low = operand_low + ((RESIDENT ? panel_base + uint32_t(kb) * A_TILE_BYTES : stage_smem) >> 4);
                     const uint32_t b_low = operand_low + ((stage_smem + a_stage_bytes) >> 4);
                     const uint32_t set_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t(set + 1);
-                    const uint32_t sfa_tmem = resident ? resident_sfa + uint32_t(kb * TMEM_SFA_COLUMNS) : set_tmem;
-                    const uint32_t sfb_tmem = resident ? set_tmem : set_tmem + TMEM_SFA_COLUMNS;
+                    const uint32_t sfa_tmem = RESIDENT ? resident_sfa + uint32_t(kb * TMEM_SFA_COLUMNS) : set_tmem;
+                    const uint32_t sfb_tmem = RESIDENT ? set_tmem : set_tmem + TMEM_SFA_COLUMNS;
                     if (KIND == B2_KIND_NVFP4) {
                         if (issued >= args.scale_sets) {
                             mbar_wait(empty_bar + 8 * lag_stage, lag_phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
@@ -704,15 +714,10 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         // shared memory: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
                         const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes) >> 4;
                         constexpr uint32_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
-                        const uint32_t feature_low = atom_low + (resident ? 0u : PART);   // the stage holds no token atoms when they are resident
-                        const bool two_blocks = args.scale_blocks == 2;
+                        const uint32_t feature_low = atom_low + (RESIDENT ? 0u : PART);   // the stage holds no token atoms when they are resident
                         const uint32_t first_accumulate = kb != walk.kb_begin;
-                        // The launch-wide choices (resident token tile, one or two feature-scale blocks, split halves) are
-                        // turned into compile-time tags once per stage, so the unrolled copies and MMAs below carry no
-                        // branches; only a ragged last K stage takes the generic count.
-                        auto issue = [&](const int count, auto resident_tag, auto two_blocks_tag, auto split_tag) {
-                            constexpr bool RESIDENT = decltype(resident_tag)::value, TWO = decltype(two_blocks_tag)::value;
-                            constexpr bool SPLIT = decltype(split_tag)::value;
+                        // `count` is a literal on the full-stage path; only a ragged last K stage takes the generic one.
+                        auto issue = [&](const int count) {
                             if (KIND == B2_KIND_NVFP4) {
 #pragma unroll
                                 for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
@@ -747,16 +752,8 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                                 }
                             }
                         };
-                        using Yes = std::true_type;
-                        using No = std::false_type;
-                        auto with_count = [&](const int count) {
-                            if (KIND != B2_KIND_NVFP4) issue(count, No{}, No{}, No{});
-                            else if (split_halves) { if (resident) issue(count, Yes{}, Yes{}, Yes{}); else issue(count, No{}, Yes{}, Yes{}); }
-                            else if (two_blocks) { if (resident) issue(count, Yes{}, Yes{}, No{}); else issue(count, No{}, Yes{}, No{}); }
-                            else { if (resident) issue(count, Yes{}, No{}, No{}); else issue(count, No{}, No{}, No{}); }
-                        };
-                        if (mmas == SCALE_ATOMS_PER_STAGE) with_count(SCALE_ATOMS_PER_STAGE);
-                        else with_count(mmas);
+                        if (mmas == SCALE_ATOMS_PER_STAGE) issue(SCALE_ATOMS_PER_STAGE);
+                        else issue(mmas);
                     tc_commit(empty_bar + 8 * stage);
                     }
                     __syncwarp();
@@ -767,7 +764,15 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 if (elect_one()) tc_commit(acc_full_bar + 8 * buffer);
                 __syncwarp();
             }
-        }
+        };
+        using Yes = std::true_type;
+        using No = std::false_type;
+        const bool two_blocks = args.scale_blocks == 2;
+        const bool split_halves = KIND == B2_KIND_NVFP4 && GEGLU && BN == 128 && !(args.flags & B2_LINEAR_PAIRED_GATE_UP_SCALES);
+        if (KIND != B2_KIND_NVFP4) { if (resident) mma_role(Yes{}, No{}, No{}); else mma_role(No{}, No{}, No{}); }
+        else if (split_halves) { if (resident) mma_role(Yes{}, Yes{}, Yes{}); else mma_role(No{}, Yes{}, Yes{}); }
+        else if (two_blocks) { if (resident) mma_role(Yes{}, Yes{}, No{}); else mma_role(No{}, Yes{}, No{}); }
+        else { if (resident) mma_role(Yes{}, No{}, No{}); else mma_role(No{}, No{}, No{}); }
     } else {
         // ------------------------------------------------------------- epilogue
         const int quarter = warp & 3;                      // the TMEM lane partition this warp may read
