@@ -564,8 +564,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         }
                 }
                 const int tail_atoms = args.scale_column_tiles - (num_kb - 1) * SCALE_ATOMS_PER_STAGE;
-                const uint32_t up_smem_offset = uint32_t(BN / 2) * STAGE_K_BYTES;
-                const int up_row = args.up_row_offset + f0;
                 for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
                     mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
                     __syncwarp();
@@ -580,8 +578,10 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         const uint32_t copy_bytes = uint32_t(kb == num_kb - 1 ? tail_atoms : SCALE_ATOMS_PER_STAGE) * SCALE_ATOM_BYTES;
                         mbar_expect_tx(bar, stage_bytes + (KIND == B2_KIND_NVFP4 ? uint32_t(live) * copy_bytes : 0u));
                         if (!RESIDENT) tma_load_2d(a_smem, &act_map, bar, k0, m0);
-                        tma_load_2d(b_smem, &weight_map, bar, k0, f0);
-                        if (GEGLU) tma_load_2d(b_smem + up_smem_offset, &weight_map, bar, k0, up_row);
+                        // gated: the map is three-dimensional (plane 0 = gate rows, plane 1 = up rows), one instruction
+                        // brings both halves of the tile ([gate | up] in shared memory)
+                        if (GEGLU) tma_load_3d(b_smem, &weight_map, bar, k0, f0, 0);
+                        else tma_load_2d(b_smem, &weight_map, bar, k0, f0);
                         if (KIND == B2_KIND_NVFP4) {
                             const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
                             const int64_t offset = int64_t(kb) * (SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES);
@@ -600,8 +600,8 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         }
                         if (pf_turn == 0) {
                             if (elect_one()) {
-                                tma_prefetch_l2_2d(&weight_map, pf_kb * STAGE_K_BYTES, pf_f0);
-                                if (GEGLU) tma_prefetch_l2_2d(&weight_map, pf_kb * STAGE_K_BYTES, args.up_row_offset + pf_f0);
+                                if (GEGLU) tma_prefetch_l2_3d(&weight_map, pf_kb * STAGE_K_BYTES, pf_f0, 0);
+                                else tma_prefetch_l2_2d(&weight_map, pf_kb * STAGE_K_BYTES, pf_f0);
                             }
                             pf_turn = args.num_m_tiles;
                         }
@@ -960,6 +960,20 @@ static bool make_operand_map(CUtensorMap* map, const void* pointer, int64_t rows
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The packed [gate; up] weight ([2 * features, row_bytes]) as [2 planes][features][row_bytes]: one box of
+// box_rows x 128 bytes x 2 planes lands as [gate rows | up rows].
+static bool make_gated_map(CUtensorMap* map, const void* pointer, int64_t features, int64_t row_bytes, int box_rows) {
+    EncodeTiledFn encode = encode_tiled_entry();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[3] = {cuuint64_t(row_bytes), cuuint64_t(features), 2};
+    const cuuint64_t strides[2] = {cuuint64_t(row_bytes), cuuint64_t(row_bytes) * cuuint64_t(features)};
+    const cuuint32_t box[3] = {cuuint32_t(STAGE_K_BYTES), cuuint32_t(box_rows), 2};
+    const cuuint32_t element_strides[3] = {1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(pointer), dims, strides, box,
+                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int sm_count() {
     static int counts[64] = {0};
     int device = 0;
@@ -1178,7 +1192,9 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
 
     CUtensorMap act_map, weight_map;
     if (!make_operand_map(&act_map, d->act, d->tokens, args.k_bytes, TILE_TOKENS)) return B2_E_DRIVER;
-    if (!make_operand_map(&weight_map, d->weight, weight_rows, args.k_bytes, feature_tile)) return B2_E_DRIVER;
+    if (geglu ? !make_gated_map(&weight_map, d->weight, d->features, args.k_bytes, feature_tile)
+              : !make_operand_map(&weight_map, d->weight, weight_rows, args.k_bytes, feature_tile))
+        return B2_E_DRIVER;
 
     if (nvfp4) {
         switch (epilogue) {

@@ -106,6 +106,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tensor_map
         : "memory");
 }
 
+// Three-dimensional box (x innermost): used for the packed [gate; up] weight, whose two row ranges of a tile
+// arrive with one instruction as planes z = 0 (gate) and z = 1 (up), one behind the other in shared memory.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tensor_map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_l2_3d(const void* tensor_map, int x, int y, int z) {
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+                 ::"l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+
 // Hints the L2 to fetch one box of a tensor map / a byte range ahead of the loads that will need it.
 __device__ __forceinline__ void tma_prefetch_l2_2d(const void* tensor_map, int x, int y) {
     asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
