@@ -104,7 +104,7 @@ class GemmaBlock(nn.Module):
         self.fused_mlp: FusedMlpPlan | None = None
         self.mlp_ranges = [0.0, 0.0]          # calibration: max |MLP input|, max |hidden|
         self.recording = False
-        # scale = 1 + weight with zero-initialised weights (SURVEY config 3: "RMSNorm weights 0")
+        # scale = 1 + weight with zero-initialised weights (the random-init stacks use RMSNorm weights of 0)
         self.input_scale = nn.Parameter(torch.ones(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
         self.post_scale = nn.Parameter(torch.ones(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
 
