@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload (BASELINE config 2): the NVFP4 W4A4 linear pair of a Gemma-2B-shaped MLP at M = 560 tokens:
+Workload (benchmark configuration 2): the NVFP4 W4A4 linear pair of a Gemma-2B-shaped MLP at M = 560 tokens:
 encode x (bf16 -> NVFP4, calibrated scale) -> [gate;up] 2048 -> 2x16384 with the gated GELU-tanh
 epilogue that re-encodes the hidden activation to NVFP4 -> down 16384 -> 2048 (bf16 out).
 Inputs are seeded synthetic tensors with the config's shapes and distributions (x ~ N(0,1) with 1 %
@@ -52,7 +52,7 @@ NOMINAL_NVFP4_TFLOPS = 9000.0
 
 
 def synthetic_inputs(seed: int):
-    """Seeded tensors with BASELINE config 2's shapes and value distributions."""
+    """Seeded tensors with the shapes and value distributions of benchmark configuration 2."""
     generator = torch.Generator().manual_seed(seed)
     x = torch.randn((TOKENS, HIDDEN), generator=generator)
     x = torch.where(torch.rand((TOKENS, HIDDEN), generator=generator) < 0.01, x * 20, x).to(torch.bfloat16)

@@ -1,4 +1,4 @@
-"""Observations per second of the data-parallel rollout (BASELINE config 5 shapes, synthetic inputs).
+"""Observations per second of the data-parallel rollout (the rollout benchmark configuration: 256 observations, synthetic inputs).
 
     python -m embodiinfer_b200.rollout_bench --observations 256 [--layer-scale 1.0] [--quantization fp8]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \

@@ -1,4 +1,4 @@
-"""Milliseconds of the pi0.5-shaped stacks on one B200 (BASELINE configs 3 and 4, synthetic inputs).
+"""Milliseconds of the pi0.5-shaped stacks on one B200 (the prefix-stack and action-expert benchmark configurations, synthetic inputs).
 
     python -m embodiinfer_b200.stack_bench [--quantization fp8|nvfp4] [--batches 1 8 64] [--registry-route]
 

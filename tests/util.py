@@ -8,7 +8,7 @@ import torch
 
 from oracle import quant_oracle as O
 
-# BASELINE tolerances for GEMM / layer outputs in bf16 against the reference's result on identical
+# Tolerances for GEMM / layer outputs in bf16 against the reference's result on identical
 # quantised operands.
 REL_FROBENIUS = 1e-3
 MAX_ABS = 2e-2
