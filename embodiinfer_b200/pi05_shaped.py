@@ -27,6 +27,7 @@ import torch.nn.functional as F
 from torch import nn
 
 from .backend.mlp import FusedGeluMlpPlan, FusedMlpPlan
+from .backend.projection import B200Projection
 from .backend.quantization import B200Quantizer
 from .bundles import pack_quantized_linears, quantize_linear
 from .layers.linear import FP8Config, NVFP4Config, parse_quantization_config
@@ -63,6 +64,39 @@ def _quantized(layers: tuple[nn.Linear, ...], config):
     return members[0] if len(members) == 1 else pack_quantized_linears(members)
 
 
+class Projection(nn.Module):
+    """One quantised Linear of the stack.  Registry route (the bundle, dynamic activation scale) until
+    ``calibrate`` has seen its input range; afterwards the calibrated plan: static activation scale (no amax
+    pass), bias and residual added in the GEMM's epilogue."""
+
+    def __init__(self, layers: tuple[nn.Linear, ...], config) -> None:
+        super().__init__()
+        self.bundle = _quantized(layers, config)
+        self.dense_weight = torch.cat([layer.weight.detach() for layer in layers]) if len(layers) > 1 else layers[0].weight.detach()
+        self.dense_bias = None if layers[0].bias is None else torch.cat([layer.bias.detach() for layer in layers])
+        self.method = "fp8" if isinstance(config, FP8Config) else "nvfp4" if isinstance(config, NVFP4Config) else None
+        self.plan: B200Projection | None = None
+        self.maximum, self.recording = 0.0, False
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        if self.plan is not None:
+            rows = x.reshape(-1, x.shape[-1])
+            extra = None if residual is None else residual.reshape(-1, residual.shape[-1])
+            output = self.plan.apply(rows, self.plan.encode(rows), bias=self.dense_bias, residual=extra)
+            return output.reshape(*x.shape[:-1], output.shape[-1])
+        if self.recording:
+            self.maximum = max(self.maximum, float(x.abs().max()))
+        output = self.bundle(x)
+        return output if residual is None else output + residual
+
+    def calibrate(self, quantizer: B200Quantizer, margin: float) -> None:
+        if self.method is None or self.maximum <= 0.0:
+            return
+        self.plan = B200Projection(self.dense_weight.contiguous(), margin * self.maximum, self.method, quantizer)
+        self.dense_bias = None if self.dense_bias is None else self.dense_bias.to(torch.bfloat16).contiguous()
+        self.dense_weight = None
+
+
 def _rms_norm(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """Gemma RMSNorm, ``scale`` = 1 + weight (one fused kernel)."""
     return F.rms_norm(x, (x.shape[-1],), scale, 1e-6)
@@ -93,8 +127,8 @@ class GemmaBlock(nn.Module):
         self.shape = shape
         q_dim, kv_dim = shape.heads * shape.head_dim, shape.kv_heads * shape.head_dim
         make = lambda n, k: _random_linear(n, k, generator, device)
-        self.qkv = _quantized((make(q_dim, shape.width), make(kv_dim, shape.width), make(kv_dim, shape.width)), config)
-        self.o_proj = _quantized((make(shape.width, attention_width),), config)
+        self.qkv = Projection((make(q_dim, shape.width), make(kv_dim, shape.width), make(kv_dim, shape.width)), config)
+        self.o_proj = Projection((make(shape.width, attention_width),), config)
         gate, up, down = make(shape.mlp, shape.width), make(shape.mlp, shape.width), make(shape.width, shape.mlp)
         self.gate_up = _quantized((gate, up), config)
         self.down = _quantized((down,), config)
@@ -145,7 +179,7 @@ class GemmaBlock(nn.Module):
             values[:, :, -tokens:].copy_(v)
             k, v = keys, values
         attended = F.scaled_dot_product_attention(q, k, v, enable_gqa=shape.heads != shape.kv_heads)
-        x = x + self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim))
+        x = self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim), residual=x)
         return self.mlp(x), own_kv
 
 
@@ -155,8 +189,8 @@ class SiglipBlock(nn.Module):
         self.shape = shape
         make = lambda n, k: _random_linear(n, k, generator, device, bias=True)
         width = shape.width
-        self.qkv = _quantized((make(3 * width, width),), config)
-        self.out = _quantized((make(width, width),), config)
+        self.qkv = Projection((make(3 * width, width),), config)
+        self.out = Projection((make(width, width),), config)
         fc1, fc2 = make(shape.mlp, width), make(width, shape.mlp)
         self.fc1 = _quantized((fc1,), config)
         self.fc2 = _quantized((fc2,), config)
@@ -171,7 +205,7 @@ class SiglipBlock(nn.Module):
         batch, tokens, width = x.shape
         heads, head_dim = self.shape.heads, self.shape.head_dim
         q, k, v = self.qkv(self.norm1(x)).view(batch, tokens, 3, heads, head_dim).permute(2, 0, 3, 1, 4)
-        x = x + self.out(F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(batch, tokens, width))
+        x = self.out(F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(batch, tokens, width), residual=x)
         normed = self.norm2(x)
         if self.fused_mlp is not None:
             rows = normed.reshape(-1, width)
@@ -220,7 +254,7 @@ class Pi05ShapedPolicy(nn.Module):
         self.patch_weight, self.patch_bias = rand(SIGLIP_SO400M.width, 3 * PATCH * PATCH), rand(SIGLIP_SO400M.width)
         self.position = rand(patches, SIGLIP_SO400M.width)
         self.vision_norm = nn.LayerNorm(SIGLIP_SO400M.width, eps=1e-6, device=device, dtype=torch.bfloat16)
-        self.projector = _quantized((_random_linear(GEMMA_2B.width, SIGLIP_SO400M.width, generator, device, bias=True),), vision_config)
+        self.projector = Projection((_random_linear(GEMMA_2B.width, SIGLIP_SO400M.width, generator, device, bias=True),), vision_config)
         self.token_embedding = rand(vocabulary, GEMMA_2B.width)
         self.action_in, self.action_out = rand(GEMMA_300M.width, ACTION_DIM), rand(ACTION_DIM, GEMMA_300M.width)
         self.time_mlp = rand(GEMMA_300M.width, GEMMA_300M.width)
@@ -289,14 +323,19 @@ class Pi05ShapedPolicy(nn.Module):
     def calibrate_fused_mlp(self, observations: dict, margin: float = 1.0) -> None:
         """Run ``observations`` through the registry route, record every MLP's input and hidden ranges, and
         switch the MLPs (Gemma: gated; SigLIP: bias + GELU, FP8) to the calibrated fused plans (three launches
-        each, static scales)."""
+        each, static scales) and the attention projections to calibrated plans (two launches each, bias and
+        residual in the epilogue)."""
         blocks = [*self.vision, *self.prefix, *self.expert]
-        for block in blocks:
-            block.recording = True
+        projections = [module for module in self.modules() if isinstance(module, Projection)]
+        for module in (*blocks, *projections):
+            module.recording = True
         self.forward(observations)
         for block in blocks:
             block.recording = False
             block.build_fused_mlp(self.quantizer, margin)
+        for projection in projections:
+            projection.recording = False
+            projection.calibrate(self.quantizer, margin)
 
     def flops_per_observation(self) -> float:
         """2*M*N*K over the quantised projections of one observation (attention and norms excluded)."""
