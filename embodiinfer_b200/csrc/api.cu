@@ -6,6 +6,9 @@
 
 namespace b2 {
 int run_linear(const b2_linear_desc* desc, cudaStream_t stream, int64_t* workspace_need = nullptr);
+int launch_rope_split(const void* qkv, const void* sine, const void* cosine, void* q_out, void* k_out, void* v_out, int batch,
+                      int tokens, int heads, int kv_heads, int head_dim, int64_t factor_batch_stride, int kv_capacity,
+                      int kv_offset, cudaStream_t stream);
 int launch_geglu(const void* gate, const void* up, void* output, void* scales, void* blocked, const void* scale,
                  int rows, int columns, int64_t row_stride, int bits, const void* table, int flags,
                  cudaStream_t stream);
@@ -92,6 +95,22 @@ int b2_gelu_table_range(const void* host_table, int32_t* lo, int32_t* hi) {
 
 int b2_linear(const b2_linear_desc* desc, void* stream) {
     return b2::run_linear(desc, static_cast<cudaStream_t>(stream));
+}
+
+int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q_out, void* k_out, void* v_out,
+                  int32_t batch, int32_t tokens, int32_t heads, int32_t kv_heads, int32_t head_dim,
+                  int64_t factor_batch_stride, int32_t kv_capacity, int32_t kv_offset, void* stream) {
+    if (qkv == nullptr || sine == nullptr || cosine == nullptr || q_out == nullptr || k_out == nullptr || v_out == nullptr)
+        return B2_E_INVALID;
+    if (batch <= 0 || tokens <= 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || kv_offset < 0 ||
+        kv_offset + tokens > kv_capacity || factor_batch_stride < 0)
+        return B2_E_INVALID;
+    if (head_dim % 16 != 0) return B2_E_UNSUPPORTED;
+    const uintptr_t alignment = reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                                reinterpret_cast<uintptr_t>(k_out) | reinterpret_cast<uintptr_t>(v_out);
+    if (alignment & 15u) return B2_E_INVALID;
+    return b2::launch_rope_split(qkv, sine, cosine, q_out, k_out, v_out, batch, tokens, heads, kv_heads, head_dim,
+                                 factor_batch_stride, kv_capacity, kv_offset, static_cast<cudaStream_t>(stream));
 }
 
 int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc) {

@@ -162,6 +162,32 @@ def geglu(
     N.check(status, "b2_geglu")
 
 
+def rope_split(qkv: torch.Tensor, sine: torch.Tensor, cosine: torch.Tensor, q_out: torch.Tensor, k_out: torch.Tensor,
+               v_out: torch.Tensor, *, batch: int, tokens: int, heads: int, kv_heads: int, head_dim: int, kv_offset: int = 0) -> None:
+    """Split a packed QKV projection, rotate queries and keys, write ``q_out`` [B, heads, T, D] and the
+    keys / values into ``k_out`` / ``v_out`` [B, kv_heads, S, D] at ``kv_offset``; see ``b2_rope_split``.
+    ``sine`` / ``cosine``: fp32 [T, D/2] or [B, T, D/2]."""
+    device = _require_cuda(qkv, sine, cosine, q_out, k_out, v_out)
+    width = (heads + 2 * kv_heads) * head_dim
+    if qkv.dtype != torch.bfloat16 or not qkv.is_contiguous() or qkv.numel() != batch * tokens * width:
+        raise ValueError("rope_split requires a contiguous bf16 [batch*tokens, (heads + 2*kv_heads)*head_dim] projection")
+    for factor in (sine, cosine):
+        if factor.dtype != torch.float32 or not factor.is_contiguous() or factor.shape[-2:] != (tokens, head_dim // 2):
+            raise ValueError("rope_split requires contiguous fp32 factors [tokens, head_dim/2] (optionally with a batch dimension)")
+    if q_out.shape != (batch, heads, tokens, head_dim) or not q_out.is_contiguous() or q_out.dtype != torch.bfloat16:
+        raise ValueError("q_out must be a contiguous bf16 [batch, heads, tokens, head_dim] tensor")
+    for cache in (k_out, v_out):
+        if cache.ndim != 4 or cache.shape[0] != batch or cache.shape[1] != kv_heads or cache.shape[3] != head_dim or \
+                not cache.is_contiguous() or cache.dtype != torch.bfloat16:
+            raise ValueError("key/value buffers must be contiguous bf16 [batch, kv_heads, capacity, head_dim] tensors")
+    stride = tokens * (head_dim // 2) if sine.ndim == 3 else 0
+    with torch.cuda.device(device):
+        status = N.load().b2_rope_split(qkv.data_ptr(), sine.data_ptr(), cosine.data_ptr(), q_out.data_ptr(), k_out.data_ptr(),
+                                        v_out.data_ptr(), batch, tokens, heads, kv_heads, head_dim, stride, k_out.shape[2],
+                                        kv_offset, _stream(device))
+    N.check(status, "b2_rope_split")
+
+
 _WORKSPACE_BYTES = 32 << 20
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 

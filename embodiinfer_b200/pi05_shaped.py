@@ -26,6 +26,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from . import kernels as K
 from .backend.mlp import FusedGeluMlpPlan, FusedMlpPlan
 from .backend.projection import B200Projection
 from .backend.quantization import B200Quantizer
@@ -103,20 +104,19 @@ def _rms_norm(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
 
 
 def rope_tables(positions: torch.Tensor, head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
-    """cos / sin [T, head_dim] (both halves) for theta 1e4; computed once per forward, shared by all layers."""
+    """(sine, cosine), fp32 [T, head_dim/2] for theta 1e4; computed once per forward, shared by all layers."""
     half = head_dim // 2
     frequency = torch.exp(-math.log(10000.0) * torch.arange(half, device=positions.device, dtype=torch.float32) / half)
     angles = positions.float()[:, None] * frequency[None, :]
-    angles = torch.cat((angles, angles), dim=-1)
-    return angles.cos().to(torch.bfloat16), angles.sin().to(torch.bfloat16)
+    return angles.sin().contiguous(), angles.cos().contiguous()
 
 
-def _rope(x: torch.Tensor, tables: tuple[torch.Tensor, torch.Tensor]) -> torch.Tensor:
-    """x [B, H, T, D]: x * cos + rotate_half(x) * sin."""
-    cos, sin = tables
-    half = x.shape[-1] // 2
-    rotated = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
-    return x * cos + rotated * sin
+def rope_reference(x: torch.Tensor, tables: tuple[torch.Tensor, torch.Tensor]) -> torch.Tensor:
+    """x [..., T, D] bf16: the reference's rotation (backend/torch/rotary.py:24-27) as tensor operations:
+    fp32 factors, separate multiplies and add/subtract, one rounding to bf16."""
+    sine, cosine = tables
+    first, second = x.chunk(2, dim=-1)
+    return torch.cat((first * cosine - second * sine, second * cosine + first * sine), dim=-1).to(x.dtype)
 
 
 class GemmaBlock(nn.Module):
@@ -167,17 +167,17 @@ class GemmaBlock(nn.Module):
         shape = self.shape
         batch, tokens, _ = x.shape
         qkv = self.qkv(_rms_norm(x, self.input_scale))
-        q_dim, kv_dim = shape.heads * shape.head_dim, shape.kv_heads * shape.head_dim
-        q, k, v = qkv.split((q_dim, kv_dim, kv_dim), dim=-1)
-        q = _rope(q.view(batch, tokens, shape.heads, shape.head_dim).transpose(1, 2), rope)
-        k = _rope(k.view(batch, tokens, shape.kv_heads, shape.head_dim).transpose(1, 2), rope)
-        v = v.view(batch, tokens, shape.kv_heads, shape.head_dim).transpose(1, 2)
+        q_dim = shape.heads * shape.head_dim
+        # one launch: split, rotate q and k, [B, heads, T, D] queries, keys / values written into the buffers
+        q = torch.empty((batch, shape.heads, tokens, shape.head_dim), device=x.device, dtype=x.dtype)
+        if kv_buffers is None:
+            k = torch.empty((batch, shape.kv_heads, tokens, shape.head_dim), device=x.device, dtype=x.dtype)
+            v = torch.empty_like(k)
+        else:
+            k, v = kv_buffers
+        K.rope_split(qkv.reshape(batch * tokens, -1), rope[0], rope[1], q, k, v, batch=batch, tokens=tokens, heads=shape.heads,
+                     kv_heads=shape.kv_heads, head_dim=shape.head_dim, kv_offset=k.shape[2] - tokens)
         own_kv = (k, v)
-        if kv_buffers is not None:
-            keys, values = kv_buffers
-            keys[:, :, -tokens:].copy_(k)
-            values[:, :, -tokens:].copy_(v)
-            k, v = keys, values
         attended = F.scaled_dot_product_attention(q, k, v, enable_gqa=shape.heads != shape.kv_heads)
         x = self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim), residual=x)
         return self.mlp(x), own_kv

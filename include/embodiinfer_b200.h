@@ -154,6 +154,20 @@ typedef struct b2_linear_desc {
     int64_t workspace_bytes;   /* size of `workspace`; split K is used only when b2_linear_workspace_bytes(desc) fits */
 } b2_linear_desc;
 
+/* Attention preparation after a packed QKV projection (the steps between the projection and the attention in
+ * embodiinfer/policies/pi05/modeling_pi05.py:924-1010: split, rotary embedding, layout change, key/value cache
+ * write; rotation arithmetic of embodiinfer/backend/torch/rotary.py:24-27, contract "fp32_rope_bf16_output").
+ *   qkv     bf16 [batch*tokens, (heads + 2*kv_heads) * head_dim]: per token q heads, then k heads, then v heads
+ *   sine, cosine  fp32 [tokens, head_dim/2] (factor_batch_stride = 0) or [batch, tokens, head_dim/2]
+ *                 (factor_batch_stride = tokens*head_dim/2)
+ *   q_out   bf16 [batch, heads, tokens, head_dim]              rotated queries
+ *   k_out, v_out  bf16 [batch, kv_heads, kv_capacity, head_dim]: rotated keys and plain values are written at
+ *                 token positions [kv_offset, kv_offset + tokens); other positions are left untouched
+ * head_dim must be a multiple of 16; all pointers 16-byte aligned. */
+int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q_out, void* k_out, void* v_out,
+                  int32_t batch, int32_t tokens, int32_t heads, int32_t kv_heads, int32_t head_dim,
+                  int64_t factor_batch_stride, int32_t kv_capacity, int32_t kv_offset, void* stream);
+
 /* Device scratch a launch described by `desc` could use, in bytes (0: it would not split K).  With few
  * tiles (M = 10*B tokens against 148 SMs) the library cuts K into up to 16 ranges computed by different CTAs;
  * the CTA that finishes a tile last adds the fp32 partial sums in a fixed order (results do not depend on

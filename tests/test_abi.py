@@ -58,6 +58,9 @@ def test_argument_rejection_without_a_gpu():
     assert library.b2_nvfp4_quantize(fake, fake, None, None, fake, 4, 24, 0, None) == N.E_UNSUPPORTED
     assert library.b2_geglu(fake, fake, fake, None, None, fake, 4, 64, 32, 8, fake, 0, None) == N.E_INVALID
     assert library.b2_geglu(fake, fake, fake, None, None, fake, 4, 64, 64, 5, fake, 0, None) == N.E_UNSUPPORTED
+    assert library.b2_rope_split(None, None, None, None, None, None, 1, 4, 8, 1, 256, 0, 4, 0, None) == N.E_INVALID
+    assert library.b2_rope_split(fake, fake, fake, fake, fake, fake, 1, 4, 8, 1, 24, 0, 4, 0, None) == N.E_UNSUPPORTED   # head_dim % 16
+    assert library.b2_rope_split(fake, fake, fake, fake, fake, fake, 1, 4, 8, 1, 256, 0, 3, 0, None) == N.E_INVALID      # capacity < tokens
     desc = N.LinearDesc(kind=7, tokens=1, features=8, width=16)
     assert library.b2_linear(ctypes.byref(desc), None) == N.E_UNSUPPORTED
     desc = N.LinearDesc(kind=N.KIND_FP8, tokens=4, features=8, width=24, act=4096, weight=4096, act_scale=4096,
