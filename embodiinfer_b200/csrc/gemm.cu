@@ -419,7 +419,9 @@ struct TileWalk {
 
 // ---- the kernel ---------------------------------------------------------------
 
-template <int KIND, int EPI>
+// SPLIT_K: the variant whose epilogue goes through the split-K fix-up (its extra registers stay out of the
+// unsplit kernels).
+template <int KIND, int EPI, bool SPLIT_K>
 __global__ void __launch_bounds__(gemm_threads(EPI), 1)
 linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
               const KernelArgs args) {
@@ -812,7 +814,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             // (so the result does not depend on which CTA that is) and runs the epilogue on the sums.  No CTA
             // waits for another.
             const float* sums = nullptr;
-            if (args.splits > 1) {
+            if (SPLIT_K) {
                 const int64_t slot_floats = int64_t(TILE_TOKENS) * BN;
                 float* slot = args.partials + (int64_t(walk.tile) * args.splits + walk.split) * slot_floats +
                               int64_t(quarter * 32 + lane) * BN;
@@ -844,18 +846,40 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 __threadfence();
                 sums = args.partials + int64_t(walk.tile) * args.splits * slot_floats + int64_t(quarter * 32 + lane) * BN;
             }
-            // 16 (or 32) accumulator columns of this lane's token, from TMEM or from the split-K slots
+            // 16 (or 32) accumulator columns of this lane's token from the split-K slots: the loads of up to four
+            // splits of a 16-column group are issued together (one L2 round trip), then added in split order
             auto load_columns = [&](int column, uint32_t* values, int count) {
                 const int64_t slot_floats = int64_t(TILE_TOKENS) * BN;
-                for (int i = 0; i < count; i += 4) {
-                    float4 total = __ldcg(reinterpret_cast<const float4*>(sums + column + i));
-                    for (int s = 1; s < args.splits; ++s) {
-                        const float4 next = __ldcg(reinterpret_cast<const float4*>(sums + s * slot_floats + column + i));
-                        total.x = __fadd_rn(total.x, next.x); total.y = __fadd_rn(total.y, next.y);
-                        total.z = __fadd_rn(total.z, next.z); total.w = __fadd_rn(total.w, next.w);
+                for (int base = 0; base < count; base += 16) {
+                    float4 total[4];
+                    for (int first_split = 0; first_split < args.splits; first_split += 4) {
+                        float4 part[4][4];
+#pragma unroll
+                        for (int s = 0; s < 4; ++s)
+                            if (first_split + s < args.splits) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    part[s][j] = __ldcg(reinterpret_cast<const float4*>(sums + (first_split + s) * slot_floats + column + base) + j);
+                            }
+#pragma unroll
+                        for (int s = 0; s < 4; ++s)
+                            if (first_split + s < args.splits) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    if (first_split + s == 0) {
+                                        total[j] = part[s][j];
+                                    } else {
+                                        total[j].x = __fadd_rn(total[j].x, part[s][j].x); total[j].y = __fadd_rn(total[j].y, part[s][j].y);
+                                        total[j].z = __fadd_rn(total[j].z, part[s][j].z); total[j].w = __fadd_rn(total[j].w, part[s][j].w);
+                                    }
+                                }
+                            }
                     }
-                    values[i] = __float_as_uint(total.x); values[i + 1] = __float_as_uint(total.y);
-                    values[i + 2] = __float_as_uint(total.z); values[i + 3] = __float_as_uint(total.w);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        values[base + 4 * j] = __float_as_uint(total[j].x); values[base + 4 * j + 1] = __float_as_uint(total[j].y);
+                        values[base + 4 * j + 2] = __float_as_uint(total[j].z); values[base + 4 * j + 3] = __float_as_uint(total[j].w);
+                    }
                 }
             };
             const bool lane_has_token = token < args.tokens;
@@ -863,7 +887,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 const int units = features_per_tile / 16;
                 for (int unit = part; unit < units && warp_has_tokens; unit += WARPS_PER_QUARTER) {
                     uint32_t first[16], second[16];
-                    if (sums != nullptr) {
+                    if (SPLIT_K) {
                         if (lane_has_token) {
                             load_columns(unit * 16, first, 16);
                             load_columns(BN / 2 + unit * 16, second, 16);
@@ -894,7 +918,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 const int chunks = features_per_tile / 32;
                 for (int chunk = part; chunk < chunks && warp_has_tokens; chunk += WARPS_PER_QUARTER) {
                     uint32_t first[32];
-                    if (sums != nullptr) {
+                    if (SPLIT_K) {
                         if (lane_has_token) {
                             load_columns(chunk * 32, first, 32);
                         } else {
@@ -909,7 +933,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                                                                     out_scale, out_scale_rcp, true_div);
                 }
             }
-            if (sums == nullptr) {                 // (split K released the accumulator right after the dump)
+            if (!SPLIT_K) {                        // (split K released the accumulator right after the dump)
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buffer);
@@ -998,25 +1022,39 @@ static bool tile_allowed(bool geglu, int features_per_tile) {
     return features_per_tile == 64 || features_per_tile == 128 || features_per_tile == 192 || features_per_tile == 256;
 }
 
-static int choose_feature_tile(int kind, bool geglu, int features, int m_tiles) {
+constexpr int64_t TICKET_BYTES = 1024;     // fixed, so that launches of different shapes sharing a workspace find it zero
+constexpr int MAX_SPLITS = 8;
+
+// Features per tile and K splits, chosen together from a cycle estimate:
+//   a K stage moves 128 token rows + `columns` weight rows through shared memory, which is what its time follows
+//   (~2.9 cycles per row, measured); a work item (tile x split) adds ~2,500 cycles of pipeline fill and epilogue,
+//   more when the accumulator is not double-buffered; a split launch adds the fix-up (partial sums through the
+//   L2, ticket, fixed-order sum).  Splits are considered only when the launch stays within one wave.
+static void choose_tile_and_splits(int kind, bool geglu, int forced_tile, int features, int m_tiles, int num_kb,
+                                   bool allow_split, int* tile_out, int* splits_out) {
     const int sms = sm_count();
-    int best = 0;
     double best_cost = 0.0;
+    *tile_out = 0;
+    *splits_out = 1;
     for (int tile = 256; tile >= 64; tile -= 64) {
-        if (!tile_allowed(geglu, tile)) continue;
+        if (!tile_allowed(geglu, tile) || (forced_tile > 0 && tile != forced_tile)) continue;
         const int columns = geglu ? 2 * tile : tile;
         const int64_t tiles = int64_t((features + tile - 1) / tile) * m_tiles;
-        const int64_t waves = (tiles + sms - 1) / sms;
-        // a K stage moves 128 token rows + `columns` weight rows through shared memory, which is what its time
-        // follows; the epilogue adds to it unless it overlaps the next tile
-        const double cost = double(waves) * (128.0 + columns + (can_double_buffer(kind, columns) ? 16.0 : 16.0 + 0.4 * columns));
-        if (best == 0 || cost < best_cost) { best = tile; best_cost = cost; }
+        const double stage = 2.9 * (128.0 + columns);
+        const double fixed = 2500.0 + (can_double_buffer(kind, columns) ? 0.0 : 10.0 * columns);
+        for (int splits = 1; splits <= MAX_SPLITS; ++splits) {
+            if (splits > 1 && (!allow_split || tiles * splits > sms || num_kb / splits < 4 || tiles * 4 > TICKET_BYTES)) break;
+            const int64_t waves = (tiles * splits + sms - 1) / sms;
+            const int kb_item = (num_kb + splits - 1) / splits;
+            // fix-up as measured (560x2048x16384 in 2-3 splits of 192-256 columns: ~35 k cycles): it pays only for very long K
+            const double cost = double(waves) * (kb_item * stage + fixed) + (splits > 1 ? 12000.0 + 45.0 * columns * splits : 0.0);
+            if (*tile_out == 0 || cost < best_cost) { *tile_out = tile; *splits_out = splits; best_cost = cost; }
+        }
     }
-    return best;
 }
 
-template <int KIND, int EPI>
-static int launch_linear(const CUtensorMap& act_map, const CUtensorMap& weight_map, const KernelArgs& args,
+template <int KIND, int EPI, bool SPLIT_K>
+static int launch_linear_variant(const CUtensorMap& act_map, const CUtensorMap& weight_map, const KernelArgs& args,
                          int shared_bytes, cudaStream_t stream) {
     static bool configured[64] = {false};
     static std::mutex lock;
@@ -1025,7 +1063,7 @@ static int launch_linear(const CUtensorMap& act_map, const CUtensorMap& weight_m
     if (device >= 0 && device < 64) {
         std::lock_guard<std::mutex> guard(lock);
         if (!configured[device]) {
-            const cudaError_t error = cudaFuncSetAttribute(linear_kernel<KIND, EPI>,
+            const cudaError_t error = cudaFuncSetAttribute(linear_kernel<KIND, EPI, SPLIT_K>,
                                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
             if (error != cudaSuccess) return int(error);
             configured[device] = true;
@@ -1033,8 +1071,19 @@ static int launch_linear(const CUtensorMap& act_map, const CUtensorMap& weight_m
     }
     const int items = args.total_tiles * args.splits;
     const int grid = items < sm_count() ? items : sm_count();
-    linear_kernel<KIND, EPI><<<grid, gemm_threads(EPI), shared_bytes, stream>>>(act_map, weight_map, args);
+    linear_kernel<KIND, EPI, SPLIT_K><<<grid, gemm_threads(EPI), shared_bytes, stream>>>(act_map, weight_map, args);
     return int(cudaGetLastError());
+}
+
+template <int KIND, int EPI>
+static int launch_linear(const CUtensorMap& act_map, const CUtensorMap& weight_map, const KernelArgs& args,
+                         int shared_bytes, cudaStream_t stream) {
+    // only the plain epilogue has a split-K variant (the table epilogues would spill registers in the fix-up,
+    // and `run_linear` never asks them to split)
+    if constexpr (EPI == EPI_LINEAR) {
+        if (args.splits > 1) return launch_linear_variant<KIND, EPI, true>(act_map, weight_map, args, shared_bytes, stream);
+    }
+    return launch_linear_variant<KIND, EPI, false>(act_map, weight_map, args, shared_bytes, stream);
 }
 
 static bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
@@ -1092,9 +1141,24 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     const bool paired = (d->flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
     if (paired && !(geglu && nvfp4)) return B2_E_INVALID;
     if (paired && d->feature_tile != 0 && d->feature_tile != 64) return B2_E_UNSUPPORTED;
-    const int feature_tile = paired ? 64
-        : d->feature_tile > 0 ? d->feature_tile : choose_feature_tile(d->kind, geglu, d->features, args.num_m_tiles);
-    if (!tile_allowed(geglu, feature_tile)) return B2_E_UNSUPPORTED;
+    if (d->feature_tile > 0 && !tile_allowed(geglu, d->feature_tile)) return B2_E_UNSUPPORTED;
+    // K is split only into a caller-provided workspace; when the one given is too small the choice is repeated
+    // without splitting
+    bool allow_split = d->epilogue == B2_EPI_LINEAR && (planning || (d->workspace != nullptr && aligned16(d->workspace)));
+    int feature_tile = 0, splits = 1;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        choose_tile_and_splits(d->kind, geglu, paired ? 64 : d->feature_tile, d->features, args.num_m_tiles, args.num_kb,
+                               allow_split, &feature_tile, &splits);
+        if (feature_tile == 0) return B2_E_UNSUPPORTED;
+        const int64_t tiles = int64_t((d->features + feature_tile - 1) / feature_tile) * args.num_m_tiles;
+        const int64_t need = splits > 1 ? TICKET_BYTES + tiles * splits * TILE_TOKENS * (geglu ? 2 : 1) * feature_tile * 4 : 0;
+        if (planning) {
+            *workspace_need = need;
+            return B2_OK;
+        }
+        if (splits == 1 || d->workspace_bytes >= need) break;
+        allow_split = false;
+    }
     args.tile_n = geglu ? 2 * feature_tile : feature_tile;
     args.num_n_tiles = (d->features + feature_tile - 1) / feature_tile;
     args.total_tiles = args.num_m_tiles * args.num_n_tiles;
@@ -1142,7 +1206,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         const int resident_stages = (SMEM_LIMIT - fixed_bytes - resident_panel) / resident_stage;
         const int free_columns = TMEM_COLUMNS - args.accumulators * args.accumulator_stride - (nvfp4 ? args.num_kb * TMEM_SFA_COLUMNS : 0);
         const bool columns_fit = !nvfp4 || free_columns >= 2 * 16 * args.scale_blocks;
-        if (!(d->flags & B2_LINEAR_STREAM_TOKENS) && args.num_kb <= MAX_RESIDENT_KB && args.num_m_tiles <= grid &&
+        if (splits == 1 && !(d->flags & B2_LINEAR_STREAM_TOKENS) && args.num_kb <= MAX_RESIDENT_KB && args.num_m_tiles <= grid &&
             int64_t(args.num_n_tiles) * args.num_m_tiles >= 2 * int64_t(grid) && resident_stages >= 3 && columns_fit) {
             args.resident = 1;
             panel_bytes = resident_panel;
@@ -1164,30 +1228,12 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     int shared_bytes = fixed_bytes + panel_bytes + stages * (stage_bytes + scale_stage_bytes);
     if (shared_bytes < SMEM_MINIMUM) shared_bytes = SMEM_MINIMUM;
 
-    // Split K when the tiles leave more than half of the SMs idle and K is long enough to cut.
-    args.splits = 1;
+    args.splits = splits;
     args.tickets = nullptr;
     args.partials = nullptr;
-    {
-        const int sms = sm_count();
-        int splits = args.total_tiles * 2 <= sms ? sms / args.total_tiles : 1;
-        if (splits > args.num_kb / 2) splits = args.num_kb / 2;
-        if (splits > 16) splits = 16;
-        if (args.resident || splits < 2) splits = 1;
-        // the ticket words sit in a region of fixed size, so that launches of different shapes sharing a workspace
-        // find them zero (a split launch has at most sms/2 tiles)
-        constexpr int64_t ticket_bytes = 1024;
-        if (args.total_tiles * 4 > ticket_bytes) splits = 1;
-        const int64_t need = splits > 1 ? ticket_bytes + int64_t(args.total_tiles) * splits * TILE_TOKENS * args.tile_n * 4 : 0;
-        if (planning) {
-            *workspace_need = need;
-            return B2_OK;
-        }
-        if (splits > 1 && d->workspace != nullptr && d->workspace_bytes >= need && aligned16(d->workspace)) {
-            args.splits = splits;
-            args.tickets = static_cast<unsigned int*>(d->workspace);
-            args.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(d->workspace) + ticket_bytes);
-        }
+    if (splits > 1) {
+        args.tickets = static_cast<unsigned int*>(d->workspace);
+        args.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(d->workspace) + TICKET_BYTES);
     }
 
     CUtensorMap act_map, weight_map;

@@ -232,8 +232,9 @@ def linear(
     workspace: torch.Tensor | None | bool = None,
 ) -> None:
     """One fused tensor-core launch, see ``b2_linear``.  ``workspace``: zeroed split-K scratch, e.g.
-    :func:`linear_workspace`; without one (the default) K is never split.  Today the split costs more in
-    fences and global round trips than it saves at the M = 10*B shapes (12.5 vs 5.6 us at 10x2560x1024)."""
+    :func:`linear_workspace`; without one (the default) K is never split.  The fix-up through the L2 costs
+    more than the shorter K loop saves at every shape of the pi0.5 stacks measured so far (560x2048x16384:
+    35 vs 28 us; 10x2560x1024: 12.5 vs 5.6 us), so the plans do not pass one."""
     device = _require_cuda(
         act, act_scale, weight, weight_scale, out, act_scales, weight_scales, weight_scale_up, bias, residual, gelu_table, out_scale,
         out_scales, out_blocked, status,

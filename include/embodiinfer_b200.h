@@ -168,7 +168,8 @@ int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q
                   int32_t batch, int32_t tokens, int32_t heads, int32_t kv_heads, int32_t head_dim,
                   int64_t factor_batch_stride, int32_t kv_capacity, int32_t kv_offset, void* stream);
 
-/* Device scratch a launch described by `desc` could use, in bytes (0: it would not split K).  With few
+/* Device scratch a launch described by `desc` could use, in bytes (0: it would not split K; only B2_EPI_LINEAR
+ * launches split).  With few
  * tiles (M = 10*B tokens against 148 SMs) the library cuts K into up to 16 ranges computed by different CTAs;
  * the CTA that finishes a tile last adds the fp32 partial sums in a fixed order (results do not depend on
  * timing) and runs the epilogue.  Without a workspace the same launch runs unsplit.  Pointer fields of

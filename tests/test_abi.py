@@ -66,8 +66,8 @@ def test_argument_rejection_without_a_gpu():
     desc = N.LinearDesc(kind=N.KIND_FP8, tokens=4, features=8, width=24, act=4096, weight=4096, act_scale=4096,
                         weight_scale=4096, out=4096)
     assert library.b2_linear(ctypes.byref(desc), None) == N.E_UNSUPPORTED      # K % 16
-    plan = N.LinearDesc(kind=N.KIND_FP8, epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=10, features=1024, width=4096)
-    assert library.b2_linear_workspace_bytes(ctypes.byref(plan)) > 0          # 16 tiles on 148 SMs: K would be split
+    plan = N.LinearDesc(kind=N.KIND_FP8, epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=10, features=128, width=32768)
+    assert library.b2_linear_workspace_bytes(ctypes.byref(plan)) > 0          # 2 tiles, 256 K stages: K would be split
     plan.tokens, plan.features = 8960, 16384
     assert library.b2_linear_workspace_bytes(ctypes.byref(plan)) == 0
     desc.width, desc.act = 32, 4100

@@ -7,6 +7,8 @@ scales) are compared bit for bit against the stand-alone epilogue run on the ker
 
 from __future__ import annotations
 
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -183,10 +185,12 @@ def test_token_resident_order_matches_streaming_and_oracle(device, kind, epilogu
 
 @pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
 @pytest.mark.parametrize("epilogue,tokens,features,width", [("linear", 10, 1024, 4096), ("linear", 80, 1024, 2048), ("linear", 10, 2560, 1024),
-                                                            ("geglu", 10, 4096, 1024), ("geglu", 130, 512, 2048)])
+                                                            ("linear", 560, 2048, 16384), ("linear", 10, 128, 32768), ("linear", 80, 256, 16384),
+                                                            ("geglu", 10, 4096, 1024)])
 def test_split_k_is_deterministic_and_matches_oracle(device, kind, epilogue, tokens, features, width):
-    """Few tiles: K is cut across CTAs when a workspace is given.  Same bits on every run (the partial sums
-    are added in split order), tickets back at zero, within tolerance of the oracle like the unsplit launch."""
+    """Few tiles and a long K: K is cut across CTAs when a workspace is given and the library's estimate says it
+    pays (the two long-K cases; the others run unsplit).  Same bits on every run (the partial sums are added in
+    split order), tickets back at zero, within tolerance of the oracle like the unsplit launch."""
     gated = epilogue == "geglu"
     host, dev = operands(kind, tokens, (2 if gated else 1) * features, width, 11 + tokens, device)
     table_host = gelu_table_cpu("tanh")
@@ -202,7 +206,10 @@ def test_split_k_is_deterministic_and_matches_oracle(device, kind, epilogue, tok
         outputs.append(bits(out))
     assert np.array_equal(outputs[0], outputs[1])
     assert not workspace[:1024].any()                       # ticket words
-    assert workspace.any()                                  # partial sums were written: K was split
+    plan = N.LinearDesc(kind=dev["kind"], epilogue=N.EPI_GEGLU if gated else N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens,
+                        features=features, width=width)
+    planned = N.load().b2_linear_workspace_bytes(ctypes.byref(plan))
+    assert bool(workspace.any()) == (planned > 0)           # partial sums were written exactly when the library plans a split
     y = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
     want = O.gelu_mul(y[:, :features], y[:, features:], table_host) if gated else y
     assert_gemm_close(outputs[0], want)
