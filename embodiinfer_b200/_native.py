@@ -21,6 +21,7 @@ OUT_BF16, OUT_FP8, OUT_NVFP4 = 0, 1, 2
 LINEAR_ROUND_SCALE_BF16 = 1
 LINEAR_PAIRED_GATE_UP_SCALES = 4
 LINEAR_STREAM_TOKENS = 8
+NORM_RESIDUAL_EVICT_LAST = 1
 SCALE_SCRATCH_BYTES = 8
 STATIC_SCRATCH_BYTES = 16640
 STATIC_SCALE_MAX_COUNT = 67108864
@@ -68,6 +69,14 @@ class LinearDesc(ctypes.Structure):
     ]
 
 
+class NormDesc(ctypes.Structure):
+    """``b2_norm_desc``."""
+
+    _fields_ = [(name, ctypes.c_void_p) for name in (
+        "input", "update", "update_gate", "scale", "modulation", "mean", "global_scale", "residual", "output", "scales",
+        "blocked", "gate", "inverse")] + [(name, ctypes.c_int32) for name in ("rows", "columns", "tokens", "bits", "flags")]
+
+
 _P, _I, _I64, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
 # name -> argtypes; every entry returns int.
@@ -81,6 +90,7 @@ SIGNATURES: dict[str, list] = {
     "b2_linear": [ctypes.POINTER(LinearDesc), _P],
     "b2_gelu_table_range": [_P, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)],
     "b2_linear_workspace_bytes": [ctypes.POINTER(LinearDesc)],
+    "b2_norm_quant": [ctypes.POINTER(NormDesc), _P],
     "b2_rope_split": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I64, _I, _I, _P],
 }
 RESULT_TYPES = {"b2_linear_workspace_bytes": ctypes.c_int64}

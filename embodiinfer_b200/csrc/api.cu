@@ -12,6 +12,7 @@ int launch_rope_split(const void* qkv, const void* sine, const void* cosine, voi
 int launch_geglu(const void* gate, const void* up, void* output, void* scales, void* blocked, const void* scale,
                  int rows, int columns, int64_t row_stride, int bits, const void* table, int flags,
                  cudaStream_t stream);
+int launch_norm_quant(const b2_norm_desc* desc, cudaStream_t stream);
 int launch_tensor_scale_static(const void* input, int64_t count, float bound, int flags, void* scale,
                                cudaStream_t stream);
 }  // namespace b2
@@ -111,6 +112,27 @@ int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q
     if (alignment & 15u) return B2_E_INVALID;
     return b2::launch_rope_split(qkv, sine, cosine, q_out, k_out, v_out, batch, tokens, heads, kv_heads, head_dim,
                                  factor_batch_stride, kv_capacity, kv_offset, static_cast<cudaStream_t>(stream));
+}
+
+int b2_norm_quant(const b2_norm_desc* desc, void* stream) {
+    if (desc == nullptr || desc->input == nullptr || desc->output == nullptr) return B2_E_INVALID;
+    if (desc->rows <= 0 || desc->columns <= 0 || desc->tokens <= 0 || desc->rows % desc->tokens != 0) return B2_E_INVALID;
+    if (desc->bits != 4 && desc->bits != 8 && desc->bits != 16) return B2_E_UNSUPPORTED;
+    if (desc->columns % 64 != 0) return B2_E_UNSUPPORTED;
+    if (desc->columns > 8192) return B2_E_TOO_LARGE;
+    if (desc->flags & ~B2_NORM_RESIDUAL_EVICT_LAST) return B2_E_INVALID;
+    if (desc->modulation == nullptr && desc->scale == nullptr) return B2_E_INVALID;
+    if (desc->modulation == nullptr && desc->gate != nullptr) return B2_E_INVALID;
+    if (desc->update == nullptr && desc->update_gate != nullptr) return B2_E_INVALID;
+    if (desc->mean != nullptr && desc->update != nullptr) return B2_E_INVALID;
+    if (desc->bits != 16 && desc->global == nullptr) return B2_E_INVALID;
+    if (desc->bits == 4 && desc->blocked == nullptr) return B2_E_INVALID;
+    const void* vectors[] = {desc->input, desc->update, desc->update_gate, desc->scale, desc->modulation,
+                             desc->residual, desc->output, desc->gate};
+    for (const void* pointer : vectors)
+        if (!is_aligned(pointer, 16)) return B2_E_INVALID;
+    if (!is_aligned(desc->mean, 4) || !is_aligned(desc->global, 4) || !is_aligned(desc->inverse, 4)) return B2_E_INVALID;
+    return b2::launch_norm_quant(desc, static_cast<cudaStream_t>(stream));
 }
 
 int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc) {

@@ -309,6 +309,30 @@ __device__ __forceinline__ uint32_t nvfp4_encode_x8(const float (&v)[8], const E
     return word;
 }
 
+// One 16-element block held as eight bf16x2 words -> 16 nibbles (two words) and the block's e4m3 scale.
+template <bool SPEC_C>
+__device__ __forceinline__ uint2 nvfp4_encode_block(const uint32_t (&w)[8], float global, const ExactDivider& by_global,
+                                                    int flags, uint8_t& scale_code) {
+    const float maximum = abs_max_bf16_words(w);
+    scale_code = nvfp4_block_scale<SPEC_C>(maximum, by_global, flags);
+    const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
+    uint2 codes;
+    if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f) {
+        codes.x = nvfp4_encode_words_short<SPEC_C>(w[0], w[1], w[2], w[3], denominator);
+        codes.y = nvfp4_encode_words_short<SPEC_C>(w[4], w[5], w[6], w[7], denominator);
+    } else {
+        float low[8], high[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            low[2 * i] = bf16_lo(w[i]); low[2 * i + 1] = bf16_hi(w[i]);
+            high[2 * i] = bf16_lo(w[4 + i]); high[2 * i + 1] = bf16_hi(w[4 + i]);
+        }
+        codes.x = nvfp4_encode_x8<SPEC_C>(low, denominator, maximum);
+        codes.y = nvfp4_encode_x8<SPEC_C>(high, denominator, maximum);
+    }
+    return codes;
+}
+
 // Byte offset of the scale of (row, 16-element block) in the 128x4-tile layout
 // (nvfp4.py:14-25, quantize.cu:97-101).  One tile is 512 bytes: 32 rows x 16 bytes,
 // each 16-byte row holding [row, row+32, row+64, row+96] x 4 blocks.

@@ -180,29 +180,6 @@ nvfp4_encode_kernel(const uint4* __restrict__ input, uint32_t* __restrict__ outp
 // per block.  BLOCKS = 2 (rows of a multiple of 32 elements): two adjacent blocks per thread, both loads in
 // flight before any arithmetic, 16-byte code stores, and two adjacent threads assemble a 4-byte word of
 // scale bytes; BLOCKS = 1: four adjacent threads do.
-template <bool SPEC_C>
-__device__ __forceinline__ uint2 nvfp4_encode_block(const uint32_t (&w)[8], float global, const ExactDivider& by_global,
-                                                    int flags, uint8_t& scale_code) {
-    const float maximum = abs_max_bf16_words(w);
-    scale_code = nvfp4_block_scale<SPEC_C>(maximum, by_global, flags);
-    const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
-    uint2 codes;
-    if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f) {
-        codes.x = nvfp4_encode_words_short<SPEC_C>(w[0], w[1], w[2], w[3], denominator);
-        codes.y = nvfp4_encode_words_short<SPEC_C>(w[4], w[5], w[6], w[7], denominator);
-    } else {
-        float low[8], high[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            low[2 * i] = bf16_lo(w[i]); low[2 * i + 1] = bf16_hi(w[i]);
-            high[2 * i] = bf16_lo(w[4 + i]); high[2 * i + 1] = bf16_hi(w[4 + i]);
-        }
-        codes.x = nvfp4_encode_x8<SPEC_C>(low, denominator, maximum);
-        codes.y = nvfp4_encode_x8<SPEC_C>(high, denominator, maximum);
-    }
-    return codes;
-}
-
 template <bool SPEC_C, int BLOCKS>
 __global__ void __launch_bounds__(QUANT_THREADS)
 nvfp4_encode_wide_kernel(const uint8_t* __restrict__ input, uint8_t* __restrict__ output, uint8_t* __restrict__ scales,

@@ -1,4 +1,4 @@
-"""Per-kernel timings on one B200: the quantisers, the stand-alone gated epilogue and the tensor-core
+"""Per-kernel timings on one B200: the quantisers, the stand-alone gated epilogue, the norm producer and the tensor-core
 Linear at the shapes of the pi0.5-style towers.  One JSON line per case.
 
     python -m embodiinfer_b200.kernel_bench                       # every case
@@ -120,6 +120,26 @@ def geglu_cases(device):
                                    scale=scale, blocked=blocked)
         total = int(rows * features * (4 + out_bytes))
         yield f"geglu/standalone_bits{bits}/{rows}x{features}", make, total, total, 0
+
+
+def norm_cases(device):
+    """Residual update + RMSNorm + encoder in one launch (bytes: input, update, residual out, codes out)."""
+    columns = 2048
+    for rows in (560, 17920):
+        for bits, out_bytes in ((8, 1.0), (4, 0.5 + 1 / 16), (16, 2.0)):
+            def make(_i, rows=rows, bits=bits):
+                x = torch.randn((rows, columns), device=device).to(torch.bfloat16)
+                update = torch.randn((rows, columns), device=device).to(torch.bfloat16)
+                residual = torch.empty_like(x)
+                weight = torch.randn(columns, device=device) * 0.1
+                width = {16: 2 * columns, 8: columns, 4: columns // 2}[bits]
+                out = torch.empty((rows, width), device=device, dtype=torch.uint8)
+                blocked = torch.zeros(_blocked_bytes(rows, columns // 16), device=device, dtype=torch.uint8) if bits == 4 else None
+                scale = torch.full((), 0.01, device=device)
+                return lambda: K.norm_quant(x, out, bits=bits, tokens=560, scale=weight, update=update, residual=residual,
+                                            global_scale=None if bits == 16 else scale, blocked=blocked)
+            total = int(rows * columns * (6 + out_bytes))
+            yield f"norm/residual_rms_bits{bits}/{rows}x{columns}", make, total, total, 0
 
 
 LINEAR_SHAPES = [
@@ -244,7 +264,7 @@ def main() -> None:
     torch.cuda.set_device(device)
     peaks = {"hbm_gbs": 6541.5, "fp8_tflops": 4500.0, "nvfp4_tflops": 9000.0}
     options = {"flags": args.flags, "feature_tile": args.feature_tile, "unpaired": args.unpaired}
-    sources = (quantiser_cases, geglu_cases, lambda dev: linear_cases(dev, options))
+    sources = (quantiser_cases, geglu_cases, norm_cases, lambda dev: linear_cases(dev, options))
     for source in sources:
         for name, make, set_bytes, algorithmic_bytes, flops in source(device):
             if not pattern.search(name):

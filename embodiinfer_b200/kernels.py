@@ -188,6 +188,37 @@ def rope_split(qkv: torch.Tensor, sine: torch.Tensor, cosine: torch.Tensor, q_ou
     N.check(status, "b2_rope_split")
 
 
+def norm_quant(inputs: torch.Tensor, output: torch.Tensor, *, bits: int, tokens: int, scale: torch.Tensor | None = None,
+               modulation: torch.Tensor | None = None, update: torch.Tensor | None = None,
+               update_gate: torch.Tensor | None = None, mean: torch.Tensor | None = None,
+               global_scale: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+               scales: torch.Tensor | None = None, blocked: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+               inverse: torch.Tensor | None = None, flags: int = 0) -> None:
+    """Residual update + RMSNorm (offset scale or adaptive modulation) + bf16 rounding + encoder over the
+    contiguous bf16 rows of ``inputs`` [..., columns]; see ``b2_norm_quant`` for every argument."""
+    present = [t for t in (inputs, output, scale, modulation, update, update_gate, mean, global_scale, residual, scales,
+                           blocked, gate, inverse) if t is not None]
+    device = _require_cuda(*present)
+    if inputs.dtype != torch.bfloat16 or not inputs.is_contiguous():
+        raise ValueError("norm_quant requires contiguous bf16 rows")
+    for other in (update, residual):
+        if other is not None and (other.shape != inputs.shape or other.dtype != torch.bfloat16 or not other.is_contiguous()):
+            raise ValueError("update and residual must match the input's shape, dtype and layout")
+    for affine in (scale, modulation, mean, inverse):
+        if affine is not None and (affine.dtype != torch.float32 or not affine.is_contiguous()):
+            raise ValueError("scale, modulation, mean and inverse must be contiguous fp32 tensors")
+    columns = inputs.shape[-1]
+    rows = inputs.numel() // columns
+    desc = N.NormDesc(
+        input=inputs.data_ptr(), update=_ptr(update), update_gate=_ptr(update_gate), scale=_ptr(scale),
+        modulation=_ptr(modulation), mean=_ptr(mean), global_scale=_ptr(global_scale), residual=_ptr(residual),
+        output=output.data_ptr(), scales=_ptr(scales), blocked=_ptr(blocked), gate=_ptr(gate), inverse=_ptr(inverse),
+        rows=rows, columns=columns, tokens=tokens, bits=bits, flags=int(flags))
+    with torch.cuda.device(device):
+        status = N.load().b2_norm_quant(ctypes.byref(desc), _stream(device))
+    N.check(status, "b2_norm_quant")
+
+
 _WORKSPACE_BYTES = 32 << 20
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 

@@ -28,6 +28,7 @@ from torch import nn
 
 from . import kernels as K
 from .backend.mlp import FusedGeluMlpPlan, FusedMlpPlan
+from .backend.norm_quant import B200NormQuant
 from .backend.projection import B200Projection
 from .backend.quantization import B200Quantizer
 from .bundles import pack_quantized_linears, quantize_linear
@@ -65,6 +66,27 @@ def _quantized(layers: tuple[nn.Linear, ...], config):
     return members[0] if len(members) == 1 else pack_quantized_linears(members)
 
 
+class FusedNorm:
+    """RMSNorm + bf16 rounding + activation encoding at a calibrated projection's static scale in one launch
+    (``NormQuantPlan.normalize``); one plan per activation shape and stream, created on first use."""
+
+    def __init__(self, quantizer: B200Quantizer, projection: B200Projection) -> None:
+        self.backend = B200NormQuant(quantizer)
+        self.bits = 8 if projection.precision == "fp8" else 4
+        self.scale = projection.maximum / (448 * (6 if self.bits == 4 else 1))
+        self.plans: dict = {}
+
+    def __call__(self, x: torch.Tensor, weight: torch.Tensor):
+        """``x``: contiguous bf16 [B, T, D]; ``weight``: fp32 [D] RMSNorm weight (the scale is 1 + weight)."""
+        key = (tuple(x.shape), torch.cuda.current_stream(x.device).cuda_stream)
+        plan = self.plans.get(key)
+        if plan is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("Warm the fused norm before graph capture")
+            plan = self.plans[key] = self.backend.plan(x, bits=self.bits, calibrated_scale=self.scale, adaptive=False)
+        return plan.normalize(x, scale=weight)
+
+
 class Projection(nn.Module):
     """One quantised Linear of the stack.  Registry route (the bundle, dynamic activation scale) until
     ``calibrate`` has seen its input range; afterwards the calibrated plan: static activation scale (no amax
@@ -77,7 +99,13 @@ class Projection(nn.Module):
         self.dense_bias = None if layers[0].bias is None else torch.cat([layer.bias.detach() for layer in layers])
         self.method = "fp8" if isinstance(config, FP8Config) else "nvfp4" if isinstance(config, NVFP4Config) else None
         self.plan: B200Projection | None = None
+        self.norm: FusedNorm | None = None
         self.maximum, self.recording = 0.0, False
+
+    def normed(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """``self(RMSNorm(x))`` with the norm and the activation encoding in one launch (calibrated plans only)."""
+        output = self.plan.apply(x.reshape(-1, x.shape[-1]), self.norm(x.contiguous(), weight), bias=self.dense_bias)
+        return output.reshape(*x.shape[:-1], output.shape[-1])
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         if self.plan is not None:
@@ -94,6 +122,7 @@ class Projection(nn.Module):
         if self.method is None or self.maximum <= 0.0:
             return
         self.plan = B200Projection(self.dense_weight.contiguous(), margin * self.maximum, self.method, quantizer)
+        self.norm = FusedNorm(quantizer, self.plan)
         self.dense_bias = None if self.dense_bias is None else self.dense_bias.to(torch.bfloat16).contiguous()
         self.dense_weight = None
 
@@ -141,9 +170,17 @@ class GemmaBlock(nn.Module):
         # scale = 1 + weight with zero-initialised weights (the random-init stacks use RMSNorm weights of 0)
         self.input_scale = nn.Parameter(torch.ones(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
         self.post_scale = nn.Parameter(torch.ones(shape.width, device=device, dtype=torch.bfloat16), requires_grad=False)
+        # the same norms as fp32 weights (scale - 1) for the fused norm + encoder launch of the calibrated plans
+        self.input_weight = torch.zeros(shape.width, device=device)
+        self.post_weight = torch.zeros(shape.width, device=device)
+        self.mlp_norm: FusedNorm | None = None
+        self.fused_norm = True
 
     def mlp(self, x: torch.Tensor) -> torch.Tensor:
         """x + down(gelu_tanh(gate(n)) * up(n)), n = RMSNorm(x)."""
+        if self.fused_mlp is not None and self.mlp_norm is not None and self.fused_norm:
+            rows = x.reshape(-1, x.shape[-1])
+            return self.fused_mlp.project(rows, self.mlp_norm(x.contiguous(), self.post_weight), residual=rows).reshape(x.shape)
         normed = _rms_norm(x, self.post_scale)
         if self.fused_mlp is not None:
             rows = normed.reshape(-1, normed.shape[-1])
@@ -159,6 +196,7 @@ class GemmaBlock(nn.Module):
         gate, up, down = self.dense_mlp
         self.fused_mlp = FusedMlpPlan(gate, up, down, gate_up_max=margin * self.mlp_ranges[0], down_max=margin * self.mlp_ranges[1],
                                       gate_up=self.method, down=self.method, quantizer=quantizer)
+        self.mlp_norm = FusedNorm(quantizer, self.fused_mlp.gate_up) if self.method is not None else None
         self.dense_mlp = None
 
     def forward(self, x, rope, kv_buffers=None):
@@ -166,7 +204,10 @@ class GemmaBlock(nn.Module):
         ``prefix`` rows hold the prefix tower's keys/values; this block writes its own rows behind them."""
         shape = self.shape
         batch, tokens, _ = x.shape
-        qkv = self.qkv(_rms_norm(x, self.input_scale))
+        if self.qkv.norm is not None and self.fused_norm:
+            qkv = self.qkv.normed(x, self.input_weight)
+        else:
+            qkv = self.qkv(_rms_norm(x, self.input_scale))
         q_dim = shape.heads * shape.head_dim
         # one launch: split, rotate q and k, [B, heads, T, D] queries, keys / values written into the buffers
         q = torch.empty((batch, shape.heads, tokens, shape.head_dim), device=x.device, dtype=x.dtype)

@@ -168,6 +168,46 @@ int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q
                   int32_t batch, int32_t tokens, int32_t heads, int32_t kv_heads, int32_t head_dim,
                   int64_t factor_batch_stride, int32_t kv_capacity, int32_t kv_offset, void* stream);
 
+/* RMSNorm (+ residual update, + adaptive modulation) fused with the activation encoder: the step in front of
+ * every quantised projection.  Replaces cc_norm_quant and cc_norm_quant_reduce
+ * (embodiinfer/backend/cuda/csrc/norm_quant.cu:91-112, 517-562; bound by NormQuantPlan.normalize /
+ * residual_normalize, embodiinfer/backend/cuda/norm_quant.py:139-303) and the bf16 result of the strict
+ * normalisation (contract "torch_rmsnorm_bf16_rounding", embodiinfer/backend/torch/normalization.py:49-103).
+ *
+ * Per row (token), in the reference's fp32 arithmetic and rounding points:
+ *   r   = update == NULL ? input : bf16(input + (update_gate ? bf16(update * update_gate[batch]) : update))
+ *   inv = rsqrtf(mean + 1e-6), mean = mean[row] when given, else sum(r*r) * fp32(1/columns), the sum taken
+ *         in the reference kernels' order (columns 1024 and 2048: 8 consecutive columns per lane, then a
+ *         butterfly over 32 lanes and over the warps; other widths: 256 strided lanes, then a halving tree)
+ *   y   = bf16(modulation ? (r*inv) * (1 + m_scale) + m_shift : (r*inv) * (1 + scale))
+ *   bits 16: output = y (bf16)
+ *   bits 8 : output = e4m3(y * fp32(1 / *global))  (mean == NULL)  or  e4m3(y / *global)  (mean given)
+ *   bits 4 : NVFP4 spec C of y at *global: packed e2m1, row-major block scales (`scales`, may be NULL) and
+ *            the 128x4-tile layout (`blocked`; padding bytes are the caller's to zero)
+ * `residual` (may be NULL) receives r; `gate` (may be NULL) receives bf16(modulation[:, 2*columns:]) per batch
+ * entry; `inverse` (may be NULL) receives inv per row (test hook: rsqrtf is the one step a CPU cannot
+ * restate bit-exactly).  `modulation` is fp32 [rows/tokens, 3*columns] = scale | shift | gate.
+ * columns % 64 == 0, columns <= 8192, rows % tokens == 0; bf16 pointers 16-byte aligned.
+ * flags: B2_NORM_RESIDUAL_EVICT_LAST stores `residual` with an L2 evict-last policy (norm_quant.cu:370-379). */
+#define B2_NORM_RESIDUAL_EVICT_LAST 1
+typedef struct b2_norm_desc {
+    const void* input;       /* bf16 [rows, columns] */
+    const void* update;      /* bf16 [rows, columns] or NULL */
+    const void* update_gate; /* bf16 [rows/tokens, columns] or NULL */
+    const void* scale;       /* fp32 [columns], RMSNorm weight without the +1; ignored when modulation != NULL */
+    const void* modulation;  /* fp32 [rows/tokens, 3*columns] or NULL */
+    const void* mean;        /* fp32 [rows] mean of squares, or NULL: reduce in the kernel */
+    const void* global;      /* device fp32: per-tensor scale (bits 8) or NVFP4 global scale (bits 4); NULL for bits 16 */
+    void* residual;          /* bf16 [rows, columns] or NULL */
+    void* output;            /* bf16 [rows, columns] | e4m3 [rows, columns] | packed e2m1 [rows, columns/2] */
+    void* scales;            /* bits 4: e4m3 [rows, columns/16] or NULL */
+    void* blocked;           /* bits 4: block scales in 128x4-tile order */
+    void* gate;              /* bf16 [rows/tokens, columns] or NULL (modulation only) */
+    void* inverse;           /* fp32 [rows] or NULL */
+    int32_t rows, columns, tokens, bits, flags;
+} b2_norm_desc;
+int b2_norm_quant(const b2_norm_desc* desc, void* stream);
+
 /* Device scratch a launch described by `desc` could use, in bytes (0: it would not split K; only B2_EPI_LINEAR
  * launches split).  With few
  * tiles (M = 10*B tokens against 148 SMs) the library cuts K into up to 16 ranges computed by different CTAs;

@@ -61,6 +61,18 @@ def test_argument_rejection_without_a_gpu():
     assert library.b2_rope_split(None, None, None, None, None, None, 1, 4, 8, 1, 256, 0, 4, 0, None) == N.E_INVALID
     assert library.b2_rope_split(fake, fake, fake, fake, fake, fake, 1, 4, 8, 1, 24, 0, 4, 0, None) == N.E_UNSUPPORTED   # head_dim % 16
     assert library.b2_rope_split(fake, fake, fake, fake, fake, fake, 1, 4, 8, 1, 256, 0, 3, 0, None) == N.E_INVALID      # capacity < tokens
+    assert library.b2_norm_quant(None, None) == N.E_INVALID
+    norm = N.NormDesc(input=4096, output=4096, scale=4096, global_scale=4096, rows=6, columns=64, tokens=3, bits=8)
+    norm.columns = 48
+    assert library.b2_norm_quant(ctypes.byref(norm), None) == N.E_UNSUPPORTED  # width % 64
+    norm.columns = 16384
+    assert library.b2_norm_quant(ctypes.byref(norm), None) == N.E_TOO_LARGE
+    norm.columns, norm.tokens = 64, 4
+    assert library.b2_norm_quant(ctypes.byref(norm), None) == N.E_INVALID      # rows % tokens
+    norm.tokens, norm.bits = 3, 4
+    assert library.b2_norm_quant(ctypes.byref(norm), None) == N.E_INVALID      # NVFP4 without the tiled scale buffer
+    norm.bits, norm.scale = 8, None
+    assert library.b2_norm_quant(ctypes.byref(norm), None) == N.E_INVALID      # neither scale nor modulation
     desc = N.LinearDesc(kind=7, tokens=1, features=8, width=16)
     assert library.b2_linear(ctypes.byref(desc), None) == N.E_UNSUPPORTED
     desc = N.LinearDesc(kind=N.KIND_FP8, tokens=4, features=8, width=24, act=4096, weight=4096, act_scale=4096,

@@ -1,0 +1,122 @@
+"""The fused residual + RMSNorm + encoder kernel against the CPU oracle (oracle/norm_oracle.py), through the
+C ABI.  The kernel's own reciprocal-root factor is read back, required to lie within 2 units in the last
+place of the exactly rounded value of the oracle's kernel-order mean, and every other output must then be
+bit-exact given that factor."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from embodiinfer_b200 import _native as N
+from embodiinfer_b200 import kernels as K
+from oracle import norm_oracle as NO
+from tests.util import bits, u8
+
+pytestmark = pytest.mark.gpu
+
+
+def blocked_bytes(rows, blocks):
+    return -(-rows // 128) * 128 * (-(-blocks // 4) * 4)
+
+
+def run_case(device, *, batch, tokens, columns, bits_, adaptive, with_update, with_gate, given_mean=False, seed=0, flags=0):
+    generator = torch.Generator().manual_seed(seed + columns + tokens)
+    rows = batch * tokens
+    inputs = (torch.randn((rows, columns), generator=generator) * 3).to(torch.bfloat16)
+    inputs[0, :16] = 0
+    update = torch.randn((rows, columns), generator=generator).to(torch.bfloat16) if with_update else None
+    gate = torch.randn((batch, columns), generator=generator).to(torch.bfloat16) if with_gate else None
+    scale = None if adaptive else torch.randn((columns,), generator=generator) * 0.2
+    modulation = torch.randn((batch, 3 * columns), generator=generator) * 0.3 if adaptive else None
+    mean = inputs.float().square().mean(dim=-1).contiguous() if given_mean else None
+    global_scale = torch.tensor({8: 0.011, 4: 0.0023, 16: 1.0}[bits_])
+    to = lambda t: None if t is None else t.to(device)
+    width = {16: 2 * columns, 8: columns, 4: columns // 2}[bits_]
+    output = torch.zeros((rows, width), device=device, dtype=torch.uint8)
+    residual = torch.zeros((rows, columns), device=device, dtype=torch.bfloat16)
+    scales = torch.zeros((rows, columns // 16), device=device, dtype=torch.uint8) if bits_ == 4 else None
+    blocked = torch.zeros(blocked_bytes(rows, columns // 16), device=device, dtype=torch.uint8) if bits_ == 4 else None
+    next_gate = torch.zeros((batch, columns), device=device, dtype=torch.bfloat16) if adaptive else None
+    inverse = torch.zeros(rows, device=device)
+    K.norm_quant(to(inputs), output, bits=bits_, tokens=tokens, scale=to(scale), modulation=to(modulation), update=to(update),
+                 update_gate=to(gate), mean=to(mean), global_scale=None if bits_ == 16 else to(global_scale),
+                 residual=residual, scales=scales, blocked=blocked, gate=next_gate, inverse=inverse, flags=flags)
+    torch.cuda.synchronize()
+    np_or_none = lambda t: None if t is None else t.numpy()
+    expected = NO.norm_quant(bits(inputs), bits=bits_, tokens=tokens, scale=np_or_none(scale), modulation=np_or_none(modulation),
+                             update=None if update is None else bits(update), update_gate=None if gate is None else bits(gate),
+                             mean=np_or_none(mean), global_scale=np.float32(global_scale.item()), inverse=inverse.cpu().numpy())
+    assert np.all(NO.ulp_distance(inverse.cpu().numpy(), NO.inverse_exact(expected["term"])) <= 2)
+    assert np.array_equal(bits(residual), expected["residual"])
+    got = u8(output)
+    want = expected["output"].view(np.uint8).reshape(rows, -1)
+    assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} output bytes differ"
+    if bits_ == 4:
+        assert np.array_equal(u8(scales), expected["scales"])
+        assert np.array_equal(u8(blocked), expected["blocked"].reshape(-1))
+    if adaptive:
+        assert np.array_equal(bits(next_gate), expected["gate"])
+
+
+@pytest.mark.parametrize("bits_", [8, 4, 16])
+@pytest.mark.parametrize("columns", [2048, 1024])
+def test_rms_norm_encode_lane_order(device, bits_, columns):
+    run_case(device, batch=2, tokens=35, columns=columns, bits_=bits_, adaptive=False, with_update=False, with_gate=False)
+    run_case(device, batch=2, tokens=35, columns=columns, bits_=bits_, adaptive=False, with_update=True, with_gate=False, seed=1)
+
+
+@pytest.mark.parametrize("bits_", [8, 4, 16])
+def test_adaptive_modulation_and_gated_update(device, bits_):
+    run_case(device, batch=3, tokens=10, columns=1024, bits_=bits_, adaptive=True, with_update=True, with_gate=True, seed=2)
+    run_case(device, batch=3, tokens=10, columns=1024, bits_=bits_, adaptive=True, with_update=False, with_gate=False, seed=3)
+
+
+@pytest.mark.parametrize("bits_", [8, 4, 16])
+@pytest.mark.parametrize("columns", [64, 1152, 4096, 8192])
+def test_strided_order_widths(device, bits_, columns):
+    run_case(device, batch=2, tokens=9, columns=columns, bits_=bits_, adaptive=False, with_update=True, with_gate=False, seed=4)
+    run_case(device, batch=2, tokens=3, columns=columns, bits_=bits_, adaptive=True, with_update=True, with_gate=True, seed=5)
+
+
+@pytest.mark.parametrize("bits_", [8, 4])
+def test_given_mean_divides_by_the_scale(device, bits_):
+    run_case(device, batch=2, tokens=17, columns=2048, bits_=bits_, adaptive=False, with_update=False, with_gate=False,
+             given_mean=True, seed=6)
+    run_case(device, batch=2, tokens=5, columns=320, bits_=bits_, adaptive=True, with_update=False, with_gate=False,
+             given_mean=True, seed=7)
+
+
+def test_full_prefix_micro_batch_and_evict_last(device):
+    """The rollout's shape (32 observations x 560 tokens x 2048), with the residual stored evict-last."""
+    run_case(device, batch=32, tokens=560, columns=2048, bits_=8, adaptive=False, with_update=True, with_gate=False, seed=8,
+             flags=N.NORM_RESIDUAL_EVICT_LAST)
+
+
+@pytest.mark.parametrize("bits_", [8, 4, 16])
+def test_row_per_warp_variants(device, bits_):
+    """4096 rows and more run one warp per row; same results as the oracle in every mode."""
+    run_case(device, batch=5, tokens=840, columns=1024, bits_=bits_, adaptive=True, with_update=True, with_gate=True, seed=9)
+    run_case(device, batch=2, tokens=2100, columns=2048, bits_=bits_, adaptive=False, with_update=False, with_gate=False, seed=10)
+    if bits_ != 16:
+        run_case(device, batch=1, tokens=4099, columns=1024, bits_=bits_, adaptive=False, with_update=False, with_gate=False,
+                 given_mean=True, seed=11)
+
+
+def test_rejects_bad_arguments(device):
+    x = torch.zeros((4, 64), device=device, dtype=torch.bfloat16)
+    out = torch.zeros((4, 64), device=device, dtype=torch.uint8)
+    scale = torch.zeros(64, device=device)
+    g = torch.ones((), device=device)
+    with pytest.raises(RuntimeError):      # neither scale nor modulation
+        K.norm_quant(x, out, bits=8, tokens=4, global_scale=g)
+    with pytest.raises(RuntimeError):      # rows not a multiple of tokens
+        K.norm_quant(x, out, bits=8, tokens=3, scale=scale, global_scale=g)
+    with pytest.raises(RuntimeError):      # unsupported bit width
+        K.norm_quant(x, out, bits=6, tokens=4, scale=scale, global_scale=g)
+    with pytest.raises(RuntimeError):      # NVFP4 needs the tiled scale buffer
+        K.norm_quant(x, out, bits=4, tokens=4, scale=scale, global_scale=g)
+    narrow = torch.zeros((4, 48), device=device, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):      # width must be a multiple of 64
+        K.norm_quant(narrow, out, bits=8, tokens=4, scale=scale, global_scale=g)

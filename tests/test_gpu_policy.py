@@ -63,6 +63,14 @@ def test_calibrated_fused_mlp_route_stays_close_to_the_registry_route(device, qu
     assert torch.isfinite(fused).all() and torch.equal(fused, policy(observations))
     error = (fused - reference).norm() / reference.norm()
     assert error < 0.1, float(error)
+    # the norm + encoder launch in front of the calibrated plans against torch's rms_norm + the separate encoder
+    gemma = [*policy.prefix, *policy.expert]
+    assert all(block.mlp_norm is not None and block.qkv.norm is not None for block in gemma)
+    for block in gemma:
+        block.fused_norm = False
+    separate = policy(observations)
+    error = (fused - separate).norm() / separate.norm()
+    assert error < 0.05, float(error)
 
 
 def test_graph_replay_of_the_policy_step_equals_eager(device):
