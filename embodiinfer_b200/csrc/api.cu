@@ -13,6 +13,9 @@ int launch_geglu(const void* gate, const void* up, void* output, void* scales, v
                  int rows, int columns, int64_t row_stride, int bits, const void* table, int flags,
                  cudaStream_t stream);
 int launch_norm_quant(const b2_norm_desc* desc, cudaStream_t stream);
+int launch_layer_norm_quant(const void* input, const void* update, const void* weight, const void* bias, void* residual,
+                            void* output, void* scales, void* blocked, void* statistics, float scale_value, int rows,
+                            int columns, int bits, cudaStream_t stream);
 int launch_tensor_scale_static(const void* input, int64_t count, float bound, int flags, void* scale,
                                cudaStream_t stream);
 }  // namespace b2
@@ -133,6 +136,24 @@ int b2_norm_quant(const b2_norm_desc* desc, void* stream) {
         if (!is_aligned(pointer, 16)) return B2_E_INVALID;
     if (!is_aligned(desc->mean, 4) || !is_aligned(desc->global, 4) || !is_aligned(desc->inverse, 4)) return B2_E_INVALID;
     return b2::launch_norm_quant(desc, static_cast<cudaStream_t>(stream));
+}
+
+int b2_layer_norm_quant(const void* input, const void* update, const void* weight, const void* bias, void* residual,
+                        void* output, void* scales, void* blocked, void* statistics, float scale_value, int32_t rows,
+                        int32_t columns, int32_t bits, void* stream) {
+    if (input == nullptr || weight == nullptr || bias == nullptr || output == nullptr || rows <= 0 || columns <= 0)
+        return B2_E_INVALID;
+    if (bits != 4 && bits != 8 && bits != 16) return B2_E_UNSUPPORTED;
+    if (columns % 16 != 0) return B2_E_UNSUPPORTED;
+    if (columns > 2048) return B2_E_TOO_LARGE;
+    if (bits == 4 && blocked == nullptr) return B2_E_INVALID;
+    if (bits != 16 && !(scale_value > 0.0f)) return B2_E_INVALID;
+    const void* vectors[] = {input, update, weight, bias, residual, output};
+    for (const void* pointer : vectors)
+        if (!is_aligned(pointer, 16)) return B2_E_INVALID;
+    if (!is_aligned(statistics, 4)) return B2_E_INVALID;
+    return b2::launch_layer_norm_quant(input, update, weight, bias, residual, output, scales, blocked, statistics, scale_value,
+                                       rows, columns, bits, static_cast<cudaStream_t>(stream));
 }
 
 int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc) {

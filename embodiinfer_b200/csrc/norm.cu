@@ -117,10 +117,14 @@ struct Encoder {
     __device__ __forceinline__ explicit Encoder(const NormArgs& a)
         : global(BITS == 16 ? 1.0f : *a.global), reciprocal(rounded_reciprocal(global)), divide(a.mean != nullptr),
           by_global(rounded_product(6.0f, global)) {}
+    // Scale (and, for e4m3, the multiplier) given by value, as the layer-norm entry points of the reference take them.
+    __device__ __forceinline__ Encoder(float global_scale, float multiplier)
+        : global(global_scale), reciprocal(multiplier), divide(false), by_global(rounded_product(6.0f, global_scale)) {}
 
     // Every lane of the warp calls this (the NVFP4 block maximum is exchanged with the neighbouring lane);
     // lanes without a vector pass valid = false.
-    __device__ __forceinline__ void store(const NormArgs& a, int row, int64_t base, int column, bool valid, const float (&y)[8]) const {
+    template <class Args>
+    __device__ __forceinline__ void store(const Args& a, int row, int64_t base, int column, bool valid, const float (&y)[8]) const {
         if (BITS == 16) {
             if (valid) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.output) + base + column) = pack_bf16x8(y);
         } else if (BITS == 8) {
@@ -361,6 +365,155 @@ int launch_norm_quant(const b2_norm_desc* d, cudaStream_t stream) {
     if (d->bits == 16) return launch_norm_bits<16>(a, stream);
     if (d->bits == 8) return launch_norm_bits<8>(a, stream);
     return launch_norm_bits<4>(a, stream);
+}
+
+// ---- LayerNorm producer (the SigLIP tower) ------------------------------------------------------------
+// embodiinfer/backend/cuda/csrc/norm_quant.cu:564-687 (e4m3 / bf16) and 797-931 (NVFP4), compiled by the
+// reference without fused multiply-add, so every operation below is a separate fp32 rounding:
+//   r = update ? bf16(input + update) : input
+//   per thread (8 columns, pairs (x, y)):  sum = sum + (x + y);  sq = sq + (x*x + y*y)
+//   32-lane butterflies, then butterflies over the warp totals of a 160-thread (columns <= 1152) or
+//   256-thread block; mean = sum / columns;  var = max(0, sq / columns - mean*mean);  inv = rsqrtf(var + 1e-6)
+//   y = bf16((((r - mean) * inv) * weight) + bias), then e4m3(y * multiplier), NVFP4 spec C at the global
+//   scale, or y itself.
+// WARP_ROW = true: one warp per row holding WARPS vectors per lane (the reference's thread t = lane + 32*i);
+// false: one block of 32*WARPS threads per row, one vector per thread (few rows).
+struct LayerNormArgs {
+    const __nv_bfloat16* input;
+    const __nv_bfloat16* update;
+    const __nv_bfloat16* weight;
+    const __nv_bfloat16* bias;
+    __nv_bfloat16* residual;
+    uint8_t* output;
+    uint8_t* scales;
+    uint8_t* blocked;
+    float* statistics;      // optional [rows, 2]: mean, inverse deviation
+    float scale_value;      // bits 8: multiplier; bits 4: global scale
+    int rows, columns;
+};
+
+__device__ __forceinline__ void layer_sums_of_vector(const uint4& packed, float& sum, float& squares) {
+    float v[8];
+    unpack_bf16x8(packed, v);
+    sum = 0.0f;
+    squares = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        sum = __fadd_rn(sum, __fadd_rn(v[2 * j], v[2 * j + 1]));
+        squares = __fadd_rn(squares, __fadd_rn(__fmul_rn(v[2 * j], v[2 * j]), __fmul_rn(v[2 * j + 1], v[2 * j + 1])));
+    }
+}
+
+template <int BITS, int WARPS, bool WARP_ROW>
+__global__ void __launch_bounds__(WARP_ROW ? NORM_ROWS_PER_BLOCK * 32 : WARPS * 32)
+layer_norm_encode_kernel(const LayerNormArgs a) {
+    constexpr int VECTORS = WARP_ROW ? WARPS : 1;
+    __shared__ float block_totals[2][8];
+    const int lane = threadIdx.x & 31;
+    const int row = WARP_ROW ? blockIdx.x * NORM_ROWS_PER_BLOCK + (threadIdx.x >> 5) : blockIdx.x;
+    if (row >= a.rows) return;                                   // WARP_ROW only: the whole warp leaves together
+    const int64_t base = int64_t(row) * a.columns;
+    uint4 packed[VECTORS], update[VECTORS];
+    bool valid[VECTORS];
+#pragma unroll
+    for (int i = 0; i < VECTORS; ++i) {
+        const int column = (WARP_ROW ? lane + 32 * i : int(threadIdx.x)) * 8;
+        valid[i] = column < a.columns;
+        packed[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (valid[i]) packed[i] = ld_nc_u4(reinterpret_cast<const uint4*>(a.input + base + column));
+        if (valid[i] && a.update != nullptr) update[i] = ld_nc_u4(reinterpret_cast<const uint4*>(a.update + base + column));
+    }
+    float sums[8], squares[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sums[i] = squares[i] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VECTORS; ++i) {
+        const int column = (WARP_ROW ? lane + 32 * i : int(threadIdx.x)) * 8;
+        if (valid[i] && a.update != nullptr) {
+            float v[8], delta[8];
+            unpack_bf16x8(packed[i], v);
+            unpack_bf16x8(update[i], delta);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __fadd_rn(v[j], delta[j]);
+            packed[i] = pack_bf16x8(v);
+        }
+        if (valid[i] && a.residual != nullptr) *reinterpret_cast<uint4*>(a.residual + base + column) = packed[i];
+        float sum, square;
+        layer_sums_of_vector(packed[i], sum, square);            // an absent vector is all zeros: both sums 0.0
+        sums[i] = warp_butterfly_sum(sum);
+        squares[i] = warp_butterfly_sum(square);
+    }
+    if (!WARP_ROW) {
+        if (lane == 0) {
+            block_totals[0][threadIdx.x >> 5] = sums[0];
+            block_totals[1][threadIdx.x >> 5] = squares[0];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            sums[i] = i < WARPS ? block_totals[0][i] : 0.0f;
+            squares[i] = i < WARPS ? block_totals[1][i] : 0.0f;
+        }
+    }
+    const float width = float(a.columns);
+    const float mean = __fdiv_rn(combine_warp_totals(sums), width);
+    const float variance = fmaxf(0.0f, __fsub_rn(__fdiv_rn(combine_warp_totals(squares), width), __fmul_rn(mean, mean)));
+    const float deviation = rsqrtf(__fadd_rn(variance, 1.0e-6f));
+    if (a.statistics != nullptr && (WARP_ROW ? lane == 0 : threadIdx.x == 0)) {
+        a.statistics[2 * row] = mean;
+        a.statistics[2 * row + 1] = deviation;
+    }
+    const Encoder<BITS> encoder(BITS == 4 ? a.scale_value : 1.0f, a.scale_value);
+#pragma unroll
+    for (int i = 0; i < VECTORS; ++i) {
+        const int column = (WARP_ROW ? lane + 32 * i : int(threadIdx.x)) * 8;
+        float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        if (valid[i]) {
+            float weight[8], bias[8];
+            unpack_bf16x8(packed[i], y);
+            unpack_bf16x8(*reinterpret_cast<const uint4*>(a.weight + column), weight);
+            unpack_bf16x8(*reinterpret_cast<const uint4*>(a.bias + column), bias);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                y[j] = round_to_bf16(__fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(y[j], mean), deviation), weight[j]), bias[j]));
+        }
+        encoder.store(a, row, base, column, valid[i], y);
+    }
+}
+
+template <int BITS>
+static int launch_layer_norm_bits(const LayerNormArgs& a, cudaStream_t stream) {
+    const int blocks = (a.rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK;
+    const bool narrow = a.columns <= 1152;                       // the reference's 160-thread block (norm_quant.cu:681)
+    if (a.rows >= NORM_WARP_ROWS_THRESHOLD) {
+        if (narrow) layer_norm_encode_kernel<BITS, 5, true><<<blocks, NORM_ROWS_PER_BLOCK * 32, 0, stream>>>(a);
+        else layer_norm_encode_kernel<BITS, 8, true><<<blocks, NORM_ROWS_PER_BLOCK * 32, 0, stream>>>(a);
+    } else {
+        if (narrow) layer_norm_encode_kernel<BITS, 5, false><<<a.rows, 160, 0, stream>>>(a);
+        else layer_norm_encode_kernel<BITS, 8, false><<<a.rows, 256, 0, stream>>>(a);
+    }
+    return cudaGetLastError() == cudaSuccess ? B2_OK : B2_E_DRIVER;
+}
+
+int launch_layer_norm_quant(const void* input, const void* update, const void* weight, const void* bias, void* residual,
+                            void* output, void* scales, void* blocked, void* statistics, float scale_value, int rows,
+                            int columns, int bits, cudaStream_t stream) {
+    LayerNormArgs a;
+    a.input = static_cast<const __nv_bfloat16*>(input);
+    a.update = static_cast<const __nv_bfloat16*>(update);
+    a.weight = static_cast<const __nv_bfloat16*>(weight);
+    a.bias = static_cast<const __nv_bfloat16*>(bias);
+    a.residual = static_cast<__nv_bfloat16*>(residual);
+    a.output = static_cast<uint8_t*>(output);
+    a.scales = static_cast<uint8_t*>(scales);
+    a.blocked = static_cast<uint8_t*>(blocked);
+    a.statistics = static_cast<float*>(statistics);
+    a.scale_value = scale_value;
+    a.rows = rows;
+    a.columns = columns;
+    if (bits == 16) return launch_layer_norm_bits<16>(a, stream);
+    if (bits == 8) return launch_layer_norm_bits<8>(a, stream);
+    return launch_layer_norm_bits<4>(a, stream);
 }
 
 }  // namespace b2

@@ -140,6 +140,21 @@ def norm_cases(device):
                                             global_scale=None if bits == 16 else scale, blocked=blocked)
             total = int(rows * columns * (6 + out_bytes))
             yield f"norm/residual_rms_bits{bits}/{rows}x{columns}", make, total, total, 0
+    columns = 1152
+    for rows in (768, 24576):
+        for bits, out_bytes in ((8, 1.0), (4, 0.5 + 1 / 16)):
+            def make(_i, rows=rows, bits=bits):
+                x = torch.randn((rows, columns), device=device).to(torch.bfloat16)
+                update = torch.randn((rows, columns), device=device).to(torch.bfloat16)
+                residual = torch.empty_like(x)
+                weight = torch.randn(columns, device=device).to(torch.bfloat16)
+                bias = torch.randn(columns, device=device).to(torch.bfloat16)
+                out = torch.empty((rows, columns if bits == 8 else columns // 2), device=device, dtype=torch.uint8)
+                blocked = torch.zeros(_blocked_bytes(rows, columns // 16), device=device, dtype=torch.uint8) if bits == 4 else None
+                return lambda: K.layer_norm_quant(x, weight, bias, out, bits=bits, scale_value=40.0 if bits == 8 else 0.004,
+                                                  update=update, residual=residual, blocked=blocked)
+            total = int(rows * columns * (6 + out_bytes))
+            yield f"norm/residual_layer_norm_bits{bits}/{rows}x{columns}", make, total, total, 0
 
 
 LINEAR_SHAPES = [

@@ -219,6 +219,30 @@ def norm_quant(inputs: torch.Tensor, output: torch.Tensor, *, bits: int, tokens:
     N.check(status, "b2_norm_quant")
 
 
+def layer_norm_quant(inputs: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, output: torch.Tensor, *, bits: int,
+                     scale_value: float = 1.0, update: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+                     scales: torch.Tensor | None = None, blocked: torch.Tensor | None = None,
+                     statistics: torch.Tensor | None = None) -> None:
+    """Residual update + LayerNorm + bf16 rounding + encoder over the contiguous bf16 rows of ``inputs``
+    [..., columns]; ``scale_value`` is the e4m3 multiplier (bits 8) or the NVFP4 global scale (bits 4); see
+    ``b2_layer_norm_quant``."""
+    device = _require_cuda(inputs, weight, bias, output, update, residual, scales, blocked, statistics)
+    if inputs.dtype != torch.bfloat16 or not inputs.is_contiguous():
+        raise ValueError("layer_norm_quant requires contiguous bf16 rows")
+    columns = inputs.shape[-1]
+    for affine in (weight, bias):
+        if affine.dtype != torch.bfloat16 or affine.shape != (columns,) or not affine.is_contiguous():
+            raise ValueError("weight and bias must be contiguous bf16 [columns] tensors")
+    for other in (update, residual):
+        if other is not None and (other.shape != inputs.shape or other.dtype != torch.bfloat16 or not other.is_contiguous()):
+            raise ValueError("update and residual must match the input's shape, dtype and layout")
+    with torch.cuda.device(device):
+        status = N.load().b2_layer_norm_quant(inputs.data_ptr(), _ptr(update), weight.data_ptr(), bias.data_ptr(), _ptr(residual),
+                                              output.data_ptr(), _ptr(scales), _ptr(blocked), _ptr(statistics), float(scale_value),
+                                              inputs.numel() // columns, columns, bits, _stream(device))
+    N.check(status, "b2_layer_norm_quant")
+
+
 _WORKSPACE_BYTES = 32 << 20
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 

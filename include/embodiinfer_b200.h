@@ -208,6 +208,24 @@ typedef struct b2_norm_desc {
 } b2_norm_desc;
 int b2_norm_quant(const b2_norm_desc* desc, void* stream);
 
+/* LayerNorm (+ residual update) fused with the activation encoder, for the SigLIP tower.  Replaces
+ * cc_layer_norm_fp8 and cc_layer_norm_fp4 (embodiinfer/backend/cuda/csrc/norm_quant.cu:678-687, 922-931; called
+ * from embodiinfer/policies/pi05/inference/vision.py:303-546).  Per row, every step a separate fp32 rounding
+ * (the reference compiles these kernels without fused multiply-add):
+ *   r    = update == NULL ? input : bf16(input + update)                     (`residual`, may be NULL, receives r)
+ *   mean = sum(r) / columns, var = max(0, sum(r*r) / columns - mean*mean), inv = rsqrtf(var + 1e-6), sums in the
+ *          reference kernels' order (8 columns per lane in pairs, 32-lane butterfly, butterfly over the warps
+ *          of a 160-thread block when columns <= 1152, else of a 256-thread block)
+ *   y    = bf16((((r - mean) * inv) * weight) + bias)                        weight, bias: bf16 [columns]
+ *   bits 16: output = y;  bits 8: output = e4m3(y * scale_value) (scale_value = 448 / calibrated maximum, the
+ *   reciprocal of the activation scale, as the reference passes it);  bits 4: NVFP4 spec C of y at the global
+ *   scale `scale_value`: packed e2m1, `blocked` scales in 128x4-tile order, `scales` (may be NULL) row-major.
+ * `statistics` (may be NULL) receives fp32 [rows, 2] = mean, inv (test hook, see b2_norm_quant).
+ * columns % 16 == 0, columns <= 2048; bf16 pointers 16-byte aligned. */
+int b2_layer_norm_quant(const void* input, const void* update, const void* weight, const void* bias, void* residual,
+                        void* output, void* scales, void* blocked, void* statistics, float scale_value, int32_t rows,
+                        int32_t columns, int32_t bits, void* stream);
+
 /* Device scratch a launch described by `desc` could use, in bytes (0: it would not split K; only B2_EPI_LINEAR
  * launches split).  With few
  * tiles (M = 10*B tokens against 148 SMs) the library cuts K into up to 16 ranges computed by different CTAs;

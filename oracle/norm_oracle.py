@@ -168,3 +168,59 @@ def norm_quant(inputs: np.ndarray, *, bits: int, tokens: int = 1, scale=None, mo
     if modulation is not None:
         result["gate"] = modulation_gate(modulation, values.shape[1])
     return result
+
+
+# --------------------------------------------------------------------------
+# LayerNorm producer (SigLIP).  Restated from the kernel source only (norm_quant.cu:564-687, 797-931, built
+# by the reference with --fmad=false): the reference has no CPU route with this arithmetic (its torch route
+# calls F.layer_norm), so this part is "parity unpinned"; GPU tests feed the device's rsqrtf result back.
+
+
+def layer_norm_sums(rows: np.ndarray, warps: int) -> tuple[np.ndarray, np.ndarray]:
+    """Per-row sum and sum of squares in the kernels' order: thread t owns columns 8t..8t+7 and adds the pairs
+    ``sum = sum + (x + y)``, ``sq = sq + (x*x + y*y)``; 32-lane xor-butterfly; xor-butterfly over the totals of
+    ``warps`` warps (threads beyond the row contribute 0.0)."""
+    rows = np.asarray(rows, dtype=F32)
+    count, columns = rows.shape
+    padded = np.zeros((count, warps * 256), dtype=F32)
+    padded[:, :columns] = rows
+    pairs = padded.reshape(count, warps * 32, 4, 2)
+    total = np.zeros((count, warps * 32), dtype=F32)
+    squares = np.zeros((count, warps * 32), dtype=F32)
+    for j in range(4):
+        x, y = pairs[:, :, j, 0], pairs[:, :, j, 1]
+        total = (total + (x + y).astype(F32)).astype(F32)
+        squares = (squares + ((x * x).astype(F32) + (y * y).astype(F32)).astype(F32)).astype(F32)
+    results = []
+    for values in (total, squares):
+        per_warp = _butterfly(values.reshape(count, warps, 32), (16, 8, 4, 2, 1))[..., 0]
+        eight = np.zeros((count, 8), dtype=F32)
+        eight[:, :warps] = per_warp
+        results.append(_butterfly(eight, (4, 2, 1))[:, 0])
+    return results[0], results[1]
+
+
+def layer_norm_quant(inputs: np.ndarray, weight: np.ndarray, bias: np.ndarray, *, bits: int, scale_value=1.0,
+                     update: np.ndarray | None = None, deviation: np.ndarray | None = None) -> dict:
+    """The whole LayerNorm producer on bf16 bit patterns.  ``deviation`` overrides ``1/sqrt(var + 1e-6)`` (tests
+    pass the device's own rsqrtf result).  bits 8: ``e4m3(y * scale_value)``; bits 4: NVFP4 spec C at
+    ``scale_value``; bits 16: y."""
+    residual = residual_rows(inputs, update)
+    values = Q.bf16_to_f32(residual)
+    columns = values.shape[1]
+    total, squares = layer_norm_sums(values, 5 if columns <= 1152 else 8)
+    width = F32(columns)
+    mean = (total / width).astype(F32)
+    variance = np.maximum(F32(0.0), ((squares / width).astype(F32) - (mean * mean).astype(F32)).astype(F32))
+    term = (variance + EPS).astype(F32)
+    factor = inverse_exact(term) if deviation is None else np.asarray(deviation, dtype=F32).reshape(-1)
+    centred = (values - mean[:, None]).astype(F32)
+    scaled = ((centred * factor[:, None]).astype(F32) * Q.bf16_to_f32(weight)[None, :]).astype(F32)
+    normalized = Q.f32_to_bf16((scaled + Q.bf16_to_f32(bias)[None, :]).astype(F32))
+    if bits == 8:
+        with np.errstate(over="ignore", invalid="ignore"):
+            result = {"output": Q.e4m3_encode_satfinite((Q.bf16_to_f32(normalized) * F32(scale_value)).astype(F32))}
+    else:
+        result = encode(normalized, bits, scale_value)
+    result.update(residual=residual, normalized=normalized, mean=mean, term=term, deviation=factor)
+    return result

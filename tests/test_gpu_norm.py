@@ -120,3 +120,61 @@ def test_rejects_bad_arguments(device):
     narrow = torch.zeros((4, 48), device=device, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):      # width must be a multiple of 64
         K.norm_quant(narrow, out, bits=8, tokens=4, scale=scale, global_scale=g)
+
+
+def run_layer_norm(device, *, rows, columns, bits_, with_update, seed):
+    generator = torch.Generator().manual_seed(seed + columns)
+    inputs = (torch.randn((rows, columns), generator=generator) * 2 + 0.3).to(torch.bfloat16)
+    inputs[0, :16] = 0
+    update = torch.randn((rows, columns), generator=generator).to(torch.bfloat16) if with_update else None
+    weight = torch.randn((columns,), generator=generator).to(torch.bfloat16)
+    bias = torch.randn((columns,), generator=generator).to(torch.bfloat16)
+    scale_value = {8: 448.0 / 11.0, 4: 11.0 / 2688.0, 16: 1.0}[bits_]
+    width = {16: 2 * columns, 8: columns, 4: columns // 2}[bits_]
+    output = torch.zeros((rows, width), device=device, dtype=torch.uint8)
+    residual = torch.zeros((rows, columns), device=device, dtype=torch.bfloat16)
+    scales = torch.zeros((rows, columns // 16), device=device, dtype=torch.uint8) if bits_ == 4 else None
+    blocked = torch.zeros(blocked_bytes(rows, columns // 16), device=device, dtype=torch.uint8) if bits_ == 4 else None
+    statistics = torch.zeros((rows, 2), device=device)
+    K.layer_norm_quant(inputs.to(device), weight.to(device), bias.to(device), output, bits=bits_, scale_value=scale_value,
+                       update=None if update is None else update.to(device), residual=residual, scales=scales, blocked=blocked,
+                       statistics=statistics)
+    torch.cuda.synchronize()
+    measured = statistics.cpu().numpy()
+    expected = NO.layer_norm_quant(bits(inputs), bits(weight), bits(bias), bits=bits_, scale_value=np.float32(scale_value),
+                                   update=None if update is None else bits(update), deviation=measured[:, 1])
+    assert np.array_equal(measured[:, 0], expected["mean"])
+    assert np.all(NO.ulp_distance(measured[:, 1], NO.inverse_exact(expected["term"])) <= 2)
+    assert np.array_equal(bits(residual), expected["residual"])
+    got, want = u8(output), expected["output"].view(np.uint8).reshape(rows, -1)
+    assert np.array_equal(got, want), f"{(got != want).sum()} of {got.size} output bytes differ"
+    if bits_ == 4:
+        assert np.array_equal(u8(scales), expected["scales"])
+        assert np.array_equal(u8(blocked), expected["blocked"].reshape(-1))
+
+
+@pytest.mark.parametrize("bits_", [8, 4, 16])
+@pytest.mark.parametrize("columns", [1152, 2048, 64, 1024, 1168])
+def test_layer_norm_encode(device, bits_, columns):
+    run_layer_norm(device, rows=37, columns=columns, bits_=bits_, with_update=True, seed=20)
+    run_layer_norm(device, rows=130, columns=columns, bits_=bits_, with_update=False, seed=21)
+
+
+@pytest.mark.parametrize("bits_", [8, 4, 16])
+def test_layer_norm_row_per_warp(device, bits_):
+    run_layer_norm(device, rows=4100, columns=1152, bits_=bits_, with_update=True, seed=22)
+    run_layer_norm(device, rows=4096, columns=2048, bits_=bits_, with_update=False, seed=23)
+
+
+def test_layer_norm_rejects_bad_arguments(device):
+    x = torch.zeros((4, 64), device=device, dtype=torch.bfloat16)
+    w = torch.zeros(64, device=device, dtype=torch.bfloat16)
+    out = torch.zeros((4, 64), device=device, dtype=torch.uint8)
+    with pytest.raises(RuntimeError):      # NVFP4 needs the tiled scale buffer
+        K.layer_norm_quant(x, w, w, out, bits=4, scale_value=0.01)
+    with pytest.raises(RuntimeError):      # the e4m3 multiplier must be positive
+        K.layer_norm_quant(x, w, w, out, bits=8, scale_value=0.0)
+    wide = torch.zeros((2, 4096), device=device, dtype=torch.bfloat16)
+    wide_w = torch.zeros(4096, device=device, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):      # beyond the 256-thread block of the reference
+        K.layer_norm_quant(wide, wide_w, wide_w, torch.zeros((2, 4096), device=device, dtype=torch.uint8), bits=8, scale_value=1.0)

@@ -85,3 +85,47 @@ def test_encode_and_whole_producer():
     assert np.all(NO.ulp_distance(out8["inverse"], NO.inverse_exact(out8["term"])) == 0)
     out16 = NO.norm_quant(inputs, bits=16, tokens=3, scale=scale)
     assert np.array_equal(out16["output"], out8["normalized"])
+
+
+def test_layer_norm_restatement_tracks_torch_layer_norm():
+    """The kernel-order LayerNorm stays within one bf16 unit in the last place of torch's fp32 layer_norm."""
+    import torch
+    rng = np.random.default_rng(13)
+    for columns in (1152, 2048, 64):
+        x = Q.f32_to_bf16(rng.standard_normal((9, columns)).astype(np.float32) * 2 + 0.3)
+        update = Q.f32_to_bf16(rng.standard_normal((9, columns)).astype(np.float32))
+        weight = Q.f32_to_bf16(rng.standard_normal(columns).astype(np.float32))
+        bias = Q.f32_to_bf16(rng.standard_normal(columns).astype(np.float32))
+        result = NO.layer_norm_quant(x, weight, bias, bits=16, update=update)
+        residual = torch.from_numpy(Q.bf16_to_f32(result["residual"]))
+        assert np.array_equal(result["residual"], Q.f32_to_bf16((Q.bf16_to_f32(x) + Q.bf16_to_f32(update)).astype(np.float32)))
+        want = torch.nn.functional.layer_norm(residual, (columns,), torch.from_numpy(Q.bf16_to_f32(weight)),
+                                              torch.from_numpy(Q.bf16_to_f32(bias)), 1e-6).numpy()
+        got = Q.bf16_to_f32(result["output"])
+        ulp = np.exp2(np.floor(np.log2(np.maximum(np.abs(want), 1e-30))) - 7)
+        assert np.all(np.abs(got - want) <= np.maximum(ulp, 1e-2))
+        assert np.allclose(result["mean"], residual.numpy().astype(np.float64).mean(axis=1), atol=1e-5)
+    encoded = NO.layer_norm_quant(x, weight, bias, bits=8, scale_value=448.0 / 9.0)
+    y = Q.bf16_to_f32(encoded["normalized"])
+    assert np.array_equal(encoded["output"], Q.e4m3_encode_satfinite((y * np.float32(448.0 / 9.0)).astype(np.float32)))
+    packed = NO.layer_norm_quant(x, weight, bias, bits=4, scale_value=9.0 / 2688.0)
+    assert np.array_equal(packed["output"], Q.nvfp4_quantize_C(packed["normalized"], np.float32(9.0 / 2688.0))[0])
+
+
+def test_layer_norm_sums_by_hand():
+    """One thread's pair order and the two butterflies on a row that fits two warps."""
+    row = (np.arange(1, 513, dtype=np.float32) / np.float32(7)).reshape(1, 512)
+    total, squares = NO.layer_norm_sums(row, 5)
+    lanes = row.reshape(64, 4, 2)
+    per_thread = np.zeros(64, np.float32)
+    for j in range(4):
+        per_thread = (per_thread + (lanes[:, j, 0] + lanes[:, j, 1]).astype(np.float32)).astype(np.float32)
+    warps = []
+    for w in range(2):
+        v = per_thread[32 * w:32 * w + 32].copy()
+        for offset in (16, 8, 4, 2, 1):
+            v = (v + v[np.arange(32) ^ offset]).astype(np.float32)
+        warps.append(v[0])
+    w0, w1, z = warps[0], warps[1], np.float32(0)
+    expected = np.float32(np.float32(np.float32(w0 + z) + np.float32(z + z)) + np.float32(np.float32(w1 + z) + np.float32(z + z)))
+    assert total[0] == expected and squares[0] > 0
