@@ -109,7 +109,11 @@ class FusedGeluMlpPlan:
         self.table_range = K.gelu_table_range(self.table)
 
     def __call__(self, inputs: torch.Tensor, *, residual: torch.Tensor | None = None) -> torch.Tensor:
-        encoded = self.fc1.encode(inputs)
+        return self.project(inputs, self.fc1.encode(inputs), residual=residual)
+
+    def project(self, inputs: torch.Tensor, encoded: EncodedActivation, *, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``encoded`` is the MLP input at fc1's calibrated scale (e.g. written by the fused norm + encoder);
+        ``inputs`` is only consulted for shape, dtype and device."""
         hidden = self.fc1.apply_gelu(inputs, encoded, table=self.table, bias=self.fc1_bias, bits=8,
                                      scale=self.fc2.maximum / 448, table_range=self.table_range)
         shape = (*inputs.shape[:-1], self.inter_size)

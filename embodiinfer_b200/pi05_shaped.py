@@ -87,6 +87,30 @@ class FusedNorm:
         return plan.normalize(x, scale=weight)
 
 
+class FusedLayerNorm:
+    """LayerNorm + bf16 rounding + e4m3 / NVFP4 encoding at a calibrated projection's static scale in one launch
+    (``b2_layer_norm_quant``); one encoding workspace per activation shape and stream, created on first use."""
+
+    def __init__(self, quantizer: B200Quantizer, projection: B200Projection) -> None:
+        self.quantizer = quantizer
+        self.bits = 8 if projection.precision == "fp8" else 4
+        self.scale = projection.maximum / (448 * (6 if self.bits == 4 else 1))
+        self.scale_value = 448.0 / projection.maximum if self.bits == 8 else self.scale
+        self.plans: dict = {}
+
+    def __call__(self, x: torch.Tensor, norm: nn.LayerNorm):
+        rows = x.reshape(-1, x.shape[-1])
+        key = (tuple(rows.shape), torch.cuda.current_stream(x.device).cuda_stream)
+        plan = self.plans.get(key)
+        if plan is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("Warm the fused norm before graph capture")
+            plan = self.plans[key] = self.quantizer.plan(rows, self.bits, self.scale)
+        K.layer_norm_quant(rows, norm.weight, norm.bias, plan.output, bits=self.bits, scale_value=self.scale_value,
+                           scales=plan.scales if self.bits == 4 else None, blocked=plan.blocked if self.bits == 4 else None)
+        return plan
+
+
 class Projection(nn.Module):
     """One quantised Linear of the stack.  Registry route (the bundle, dynamic activation scale) until
     ``calibrate`` has seen its input range; afterwards the calibrated plan: static activation scale (no amax
@@ -100,7 +124,13 @@ class Projection(nn.Module):
         self.method = "fp8" if isinstance(config, FP8Config) else "nvfp4" if isinstance(config, NVFP4Config) else None
         self.plan: B200Projection | None = None
         self.norm: FusedNorm | None = None
+        self.layer_norm: FusedLayerNorm | None = None
         self.maximum, self.recording = 0.0, False
+
+    def layer_normed(self, x: torch.Tensor, norm: nn.LayerNorm) -> torch.Tensor:
+        """``self(norm(x))`` with the LayerNorm and the activation encoding in one launch (calibrated plans only)."""
+        output = self.plan.apply(x.reshape(-1, x.shape[-1]), self.layer_norm(x.contiguous(), norm), bias=self.dense_bias)
+        return output.reshape(*x.shape[:-1], output.shape[-1])
 
     def normed(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         """``self(RMSNorm(x))`` with the norm and the activation encoding in one launch (calibrated plans only)."""
@@ -123,6 +153,7 @@ class Projection(nn.Module):
             return
         self.plan = B200Projection(self.dense_weight.contiguous(), margin * self.maximum, self.method, quantizer)
         self.norm = FusedNorm(quantizer, self.plan)
+        self.layer_norm = FusedLayerNorm(quantizer, self.plan)
         self.dense_bias = None if self.dense_bias is None else self.dense_bias.to(torch.bfloat16).contiguous()
         self.dense_weight = None
 
@@ -241,12 +272,19 @@ class SiglipBlock(nn.Module):
         self.recording = False
         self.norm1 = nn.LayerNorm(width, eps=1e-6, device=device, dtype=torch.bfloat16)
         self.norm2 = nn.LayerNorm(width, eps=1e-6, device=device, dtype=torch.bfloat16)
+        self.mlp_norm: FusedLayerNorm | None = None
+        self.fused_norm = True
 
     def forward(self, x):
         batch, tokens, width = x.shape
         heads, head_dim = self.shape.heads, self.shape.head_dim
-        q, k, v = self.qkv(self.norm1(x)).view(batch, tokens, 3, heads, head_dim).permute(2, 0, 3, 1, 4)
+        fused_norm = self.fused_norm and self.qkv.layer_norm is not None
+        qkv = self.qkv.layer_normed(x, self.norm1) if fused_norm else self.qkv(self.norm1(x))
+        q, k, v = qkv.view(batch, tokens, 3, heads, head_dim).permute(2, 0, 3, 1, 4)
         x = self.out(F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(batch, tokens, width), residual=x)
+        if self.fused_mlp is not None and self.mlp_norm is not None and self.fused_norm:
+            rows = x.reshape(-1, width)
+            return self.fused_mlp.project(rows, self.mlp_norm(x.contiguous(), self.norm2), residual=rows).reshape(x.shape)
         normed = self.norm2(x)
         if self.fused_mlp is not None:
             rows = normed.reshape(-1, width)
@@ -261,6 +299,7 @@ class SiglipBlock(nn.Module):
         fc1_weight, fc1_bias, fc2_weight, fc2_bias = self.dense_mlp
         self.fused_mlp = FusedGeluMlpPlan(fc1_weight, fc1_bias, fc2_weight, fc2_bias, fc1_max=margin * self.mlp_ranges[0],
                                           fc2_max=margin * self.mlp_ranges[1], quantizer=quantizer)
+        self.mlp_norm = FusedLayerNorm(quantizer, self.fused_mlp.fc1)
         self.dense_mlp = None
 
 

@@ -66,7 +66,8 @@ def test_calibrated_fused_mlp_route_stays_close_to_the_registry_route(device, qu
     # the norm + encoder launch in front of the calibrated plans against torch's rms_norm + the separate encoder
     gemma = [*policy.prefix, *policy.expert]
     assert all(block.mlp_norm is not None and block.qkv.norm is not None for block in gemma)
-    for block in gemma:
+    assert all(block.mlp_norm is not None and block.qkv.layer_norm is not None for block in policy.vision)
+    for block in [*gemma, *policy.vision]:
         block.fused_norm = False
     separate = policy(observations)
     error = (fused - separate).norm() / separate.norm()
