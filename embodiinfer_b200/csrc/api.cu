@@ -13,6 +13,9 @@ int launch_geglu(const void* gate, const void* up, void* output, void* scales, v
                  int rows, int columns, int64_t row_stride, int bits, const void* table, int flags,
                  cudaStream_t stream);
 int launch_norm_quant(const b2_norm_desc* desc, cudaStream_t stream);
+int launch_bhsd_quant(const void* input, void* output, void* scales, void* blocked, float scale_value, int64_t stride_b,
+                      int64_t stride_h, int64_t stride_s, int batch, int heads, int tokens, int head_dim, int bits,
+                      cudaStream_t stream);
 int launch_layer_norm_quant(const void* input, const void* update, const void* weight, const void* bias, void* residual,
                             void* output, void* scales, void* blocked, void* statistics, float scale_value, int rows,
                             int columns, int bits, cudaStream_t stream);
@@ -154,6 +157,21 @@ int b2_layer_norm_quant(const void* input, const void* update, const void* weigh
     if (!is_aligned(statistics, 4)) return B2_E_INVALID;
     return b2::launch_layer_norm_quant(input, update, weight, bias, residual, output, scales, blocked, statistics, scale_value,
                                        rows, columns, bits, static_cast<cudaStream_t>(stream));
+}
+
+int b2_bhsd_quant(const void* input, void* output, void* scales, void* blocked, float scale_value, int64_t stride_b,
+                  int64_t stride_h, int64_t stride_s, int32_t batch, int32_t heads, int32_t tokens, int32_t head_dim,
+                  int32_t bits, void* stream) {
+    if (input == nullptr || output == nullptr || batch <= 0 || heads <= 0 || tokens <= 0 || head_dim <= 0) return B2_E_INVALID;
+    if (bits != 4 && bits != 8 && bits != 16) return B2_E_UNSUPPORTED;
+    if (head_dim % (bits == 4 ? 16 : 8) != 0) return B2_E_UNSUPPORTED;
+    if (bits == 4 && blocked == nullptr) return B2_E_INVALID;
+    if (bits != 16 && !(scale_value > 0.0f)) return B2_E_INVALID;
+    if (stride_b < 0 || stride_h < 0 || stride_s < 0 || ((stride_b | stride_h | stride_s) & 7)) return B2_E_INVALID;
+    if (!is_aligned(input, 16) || !is_aligned(output, 16)) return B2_E_INVALID;
+    if (int64_t(batch) * tokens > 2147483647LL || int64_t(heads) * head_dim > 2147483647LL) return B2_E_TOO_LARGE;
+    return b2::launch_bhsd_quant(input, output, scales, blocked, scale_value, stride_b, stride_h, stride_s, batch, heads, tokens,
+                                 head_dim, bits, static_cast<cudaStream_t>(stream));
 }
 
 int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc) {

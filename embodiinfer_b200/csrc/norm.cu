@@ -516,4 +516,69 @@ int launch_layer_norm_quant(const void* input, const void* update, const void* w
     return launch_layer_norm_bits<4>(a, stream);
 }
 
+// ---- attention output [B, H, S, D] -> encoded rows [B*S, H*D] ---------------------------------------------
+// embodiinfer/backend/cuda/csrc/norm_quant.cu:689-795 (cc_bhsd_fp8 / cc_bhsd_fp4): the transpose in front of the
+// output projection fused with its activation encoder.  e4m3: x * multiplier (the reference passes the
+// reciprocal of the activation scale by value); NVFP4: spec C at the global scale; bits 16: the plain
+// transposing copy.  One 8-element vector per thread, grid-stride; a head's D elements are contiguous in the
+// source, a row's H*D elements in the destination, so both sides move whole 16-byte vectors.
+struct BhsdArgs {
+    const __nv_bfloat16* input;
+    uint8_t* output;
+    uint8_t* scales;
+    uint8_t* blocked;
+    float scale_value;
+    int64_t stride_b, stride_h, stride_s;
+    int batch, heads, tokens, head_dim, columns;
+};
+
+constexpr int BHSD_THREADS = 256;
+
+template <int BITS>
+__global__ void __launch_bounds__(BHSD_THREADS)
+bhsd_encode_kernel(const BhsdArgs a) {
+    const int vectors_per_row = a.columns >> 3;
+    const int64_t total = int64_t(a.batch) * a.tokens * vectors_per_row;
+    const int64_t rounded = (total + 31) & ~int64_t(31);        // whole warps enter the loop: NVFP4 pairs exchange maxima
+    const Encoder<BITS> encoder(BITS == 4 ? a.scale_value : 1.0f, a.scale_value);
+    for (int64_t index = int64_t(blockIdx.x) * BHSD_THREADS + threadIdx.x; index < rounded; index += int64_t(gridDim.x) * BHSD_THREADS) {
+        const bool valid = index < total;
+        const int row = int(index / vectors_per_row);           // b * tokens + s
+        const int column = int(index - int64_t(row) * vectors_per_row) * 8;
+        float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        if (valid) {
+            const int b = row / a.tokens, s = row - b * a.tokens;
+            const int h = column / a.head_dim, d = column - h * a.head_dim;
+            unpack_bf16x8(ld_nc_u4(reinterpret_cast<const uint4*>(a.input + b * a.stride_b + h * a.stride_h + s * a.stride_s + d)), y);
+        }
+        encoder.store(a, row, int64_t(row) * a.columns, column, valid, y);
+    }
+}
+
+int launch_bhsd_quant(const void* input, void* output, void* scales, void* blocked, float scale_value, int64_t stride_b,
+                      int64_t stride_h, int64_t stride_s, int batch, int heads, int tokens, int head_dim, int bits,
+                      cudaStream_t stream) {
+    BhsdArgs a;
+    a.input = static_cast<const __nv_bfloat16*>(input);
+    a.output = static_cast<uint8_t*>(output);
+    a.scales = static_cast<uint8_t*>(scales);
+    a.blocked = static_cast<uint8_t*>(blocked);
+    a.scale_value = scale_value;
+    a.stride_b = stride_b;
+    a.stride_h = stride_h;
+    a.stride_s = stride_s;
+    a.batch = batch;
+    a.heads = heads;
+    a.tokens = tokens;
+    a.head_dim = head_dim;
+    a.columns = heads * head_dim;
+    const int64_t total = int64_t(batch) * tokens * (a.columns >> 3);
+    const int64_t wanted = (total + BHSD_THREADS - 1) / BHSD_THREADS;
+    const int blocks = int(wanted < int64_t(sm_count()) * 16 ? wanted : int64_t(sm_count()) * 16);
+    if (bits == 16) bhsd_encode_kernel<16><<<blocks, BHSD_THREADS, 0, stream>>>(a);
+    else if (bits == 8) bhsd_encode_kernel<8><<<blocks, BHSD_THREADS, 0, stream>>>(a);
+    else bhsd_encode_kernel<4><<<blocks, BHSD_THREADS, 0, stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? B2_OK : B2_E_DRIVER;
+}
+
 }  // namespace b2

@@ -243,6 +243,21 @@ def layer_norm_quant(inputs: torch.Tensor, weight: torch.Tensor, bias: torch.Ten
     N.check(status, "b2_layer_norm_quant")
 
 
+def bhsd_quant(attended: torch.Tensor, output: torch.Tensor, *, bits: int, scale_value: float = 1.0,
+               scales: torch.Tensor | None = None, blocked: torch.Tensor | None = None) -> None:
+    """Attention output [B, H, S, D] (any strides with D contiguous) -> encoded rows [B*S, H*D]; ``scale_value`` is
+    the e4m3 multiplier (bits 8) or the NVFP4 global scale (bits 4); see ``b2_bhsd_quant``."""
+    device = _require_cuda(attended, output, scales, blocked)
+    if attended.dtype != torch.bfloat16 or attended.ndim != 4 or attended.stride(3) != 1:
+        raise ValueError("bhsd_quant requires a bf16 [B, H, S, D] tensor whose last dimension is contiguous")
+    batch, heads, tokens, head_dim = attended.shape
+    with torch.cuda.device(device):
+        status = N.load().b2_bhsd_quant(attended.data_ptr(), output.data_ptr(), _ptr(scales), _ptr(blocked), float(scale_value),
+                                        attended.stride(0), attended.stride(1), attended.stride(2), batch, heads, tokens,
+                                        head_dim, bits, _stream(device))
+    N.check(status, "b2_bhsd_quant")
+
+
 _WORKSPACE_BYTES = 32 << 20
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 

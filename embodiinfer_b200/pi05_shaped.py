@@ -66,6 +66,13 @@ def _quantized(layers: tuple[nn.Linear, ...], config):
     return members[0] if len(members) == 1 else pack_quantized_linears(members)
 
 
+class _Shape:
+    """Shape, dtype and device of an activation that only exists encoded."""
+
+    def __init__(self, shape: tuple[int, ...], like: torch.Tensor) -> None:
+        self.shape, self.device, self.dtype = torch.Size(shape), like.device, like.dtype
+
+
 class FusedNorm:
     """RMSNorm + bf16 rounding + activation encoding at a calibrated projection's static scale in one launch
     (``NormQuantPlan.normalize``); one plan per activation shape and stream, created on first use."""
@@ -111,6 +118,31 @@ class FusedLayerNorm:
         return plan
 
 
+class FusedAttentionOutput:
+    """Attention output [B, H, T, D] -> activations of the output projection [B*T, H*D], transposed and encoded at
+    the projection's static scale in one launch (``b2_bhsd_quant``)."""
+
+    def __init__(self, quantizer: B200Quantizer, projection: B200Projection) -> None:
+        self.quantizer = quantizer
+        self.bits = 8 if projection.precision == "fp8" else 4
+        self.scale = projection.maximum / (448 * (6 if self.bits == 4 else 1))
+        self.scale_value = 448.0 / projection.maximum if self.bits == 8 else self.scale
+        self.plans: dict = {}
+
+    def __call__(self, attended: torch.Tensor):
+        batch, heads, tokens, head_dim = attended.shape
+        key = (batch * tokens, heads * head_dim, torch.cuda.current_stream(attended.device).cuda_stream)
+        plan = self.plans.get(key)
+        if plan is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("Warm the attention-output encoder before graph capture")
+            like = torch.empty((batch * tokens, heads * head_dim), device=attended.device, dtype=torch.bfloat16)
+            plan = self.plans[key] = self.quantizer.plan(like, self.bits, self.scale)
+        K.bhsd_quant(attended, plan.output, bits=self.bits, scale_value=self.scale_value,
+                     scales=plan.scales if self.bits == 4 else None, blocked=plan.blocked if self.bits == 4 else None)
+        return plan
+
+
 class Projection(nn.Module):
     """One quantised Linear of the stack.  Registry route (the bundle, dynamic activation scale) until
     ``calibrate`` has seen its input range; afterwards the calibrated plan: static activation scale (no amax
@@ -125,7 +157,16 @@ class Projection(nn.Module):
         self.plan: B200Projection | None = None
         self.norm: FusedNorm | None = None
         self.layer_norm: FusedLayerNorm | None = None
+        self.attention_output: FusedAttentionOutput | None = None
         self.maximum, self.recording = 0.0, False
+
+    def attended(self, attended: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """``self(attended.transpose(1, 2).flatten(2), residual)`` for an attention output [B, H, T, D], the transpose
+        and the activation encoding in one launch (calibrated plans only)."""
+        rows = residual.reshape(-1, residual.shape[-1])
+        like = _Shape((rows.shape[0], attended.shape[1] * attended.shape[3]), rows)
+        output = self.plan.apply(like, self.attention_output(attended), bias=self.dense_bias, residual=rows)
+        return output.reshape(residual.shape)
 
     def layer_normed(self, x: torch.Tensor, norm: nn.LayerNorm) -> torch.Tensor:
         """``self(norm(x))`` with the LayerNorm and the activation encoding in one launch (calibrated plans only)."""
@@ -154,6 +195,7 @@ class Projection(nn.Module):
         self.plan = B200Projection(self.dense_weight.contiguous(), margin * self.maximum, self.method, quantizer)
         self.norm = FusedNorm(quantizer, self.plan)
         self.layer_norm = FusedLayerNorm(quantizer, self.plan)
+        self.attention_output = FusedAttentionOutput(quantizer, self.plan)
         self.dense_bias = None if self.dense_bias is None else self.dense_bias.to(torch.bfloat16).contiguous()
         self.dense_weight = None
 
@@ -251,7 +293,10 @@ class GemmaBlock(nn.Module):
                      kv_heads=shape.kv_heads, head_dim=shape.head_dim, kv_offset=k.shape[2] - tokens)
         own_kv = (k, v)
         attended = F.scaled_dot_product_attention(q, k, v, enable_gqa=shape.heads != shape.kv_heads)
-        x = self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim), residual=x)
+        if self.o_proj.attention_output is not None and self.fused_norm:
+            x = self.o_proj.attended(attended, x)
+        else:
+            x = self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim), residual=x)
         return self.mlp(x), own_kv
 
 
@@ -281,7 +326,11 @@ class SiglipBlock(nn.Module):
         fused_norm = self.fused_norm and self.qkv.layer_norm is not None
         qkv = self.qkv.layer_normed(x, self.norm1) if fused_norm else self.qkv(self.norm1(x))
         q, k, v = qkv.view(batch, tokens, 3, heads, head_dim).permute(2, 0, 3, 1, 4)
-        x = self.out(F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(batch, tokens, width), residual=x)
+        attended = F.scaled_dot_product_attention(q, k, v)
+        if fused_norm:
+            x = self.out.attended(attended, x)
+        else:
+            x = self.out(attended.transpose(1, 2).reshape(batch, tokens, width), residual=x)
         if self.fused_mlp is not None and self.mlp_norm is not None and self.fused_norm:
             rows = x.reshape(-1, width)
             return self.fused_mlp.project(rows, self.mlp_norm(x.contiguous(), self.norm2), residual=rows).reshape(x.shape)

@@ -226,6 +226,21 @@ int b2_layer_norm_quant(const void* input, const void* update, const void* weigh
                         void* output, void* scales, void* blocked, void* statistics, float scale_value, int32_t rows,
                         int32_t columns, int32_t bits, void* stream);
 
+/* Attention output [batch, heads, tokens, head_dim] (any batch / head / token strides, head_dim contiguous) ->
+ * encoded rows [batch*tokens, heads*head_dim] for the output projection: the transpose fused with the activation
+ * encoder.  Replaces cc_bhsd_fp8 and cc_bhsd_fp4 (embodiinfer/backend/cuda/csrc/norm_quant.cu:720-731, 785-795;
+ * bound in embodiinfer/backend/cuda/norm_quant.py:49-78).
+ *   bits 8 : e4m3(x * scale_value), scale_value = the reciprocal of the activation scale (by value, as the
+ *            reference passes it)
+ *   bits 4 : NVFP4 spec C at the global scale `scale_value`: packed e2m1, `blocked` scales in 128x4-tile order
+ *            (padding is the caller's to zero), `scales` (may be NULL) row-major
+ *   bits 16: bf16 copy in the new layout
+ * Strides are in elements.  head_dim % 8 == 0 (16 for bits 4); input and output 16-byte aligned, strides
+ * multiples of 8 elements. */
+int b2_bhsd_quant(const void* input, void* output, void* scales, void* blocked, float scale_value, int64_t stride_b,
+                  int64_t stride_h, int64_t stride_s, int32_t batch, int32_t heads, int32_t tokens, int32_t head_dim,
+                  int32_t bits, void* stream);
+
 /* Device scratch a launch described by `desc` could use, in bytes (0: it would not split K; only B2_EPI_LINEAR
  * launches split).  With few
  * tiles (M = 10*B tokens against 148 SMs) the library cuts K into up to 16 ranges computed by different CTAs;

@@ -224,3 +224,19 @@ def layer_norm_quant(inputs: np.ndarray, weight: np.ndarray, bias: np.ndarray, *
         result = encode(normalized, bits, scale_value)
     result.update(residual=residual, normalized=normalized, mean=mean, term=term, deviation=factor)
     return result
+
+
+# --------------------------------------------------------------------------
+# Attention output [B, H, S, D] -> encoded rows [B*S, H*D] (norm_quant.cu:689-795)
+
+
+def bhsd_quant(attended: np.ndarray, bits: int, scale_value=1.0) -> dict:
+    """``attended``: bf16 bits [B, H, S, D].  bits 8: ``e4m3(x * scale_value)`` (norm_quant.cu:705-712);
+    bits 4: NVFP4 spec C at the global scale ``scale_value`` (norm_quant.cu:750-779); bits 16: the rows."""
+    batch, heads, tokens, head_dim = attended.shape
+    rows = np.ascontiguousarray(np.transpose(np.asarray(attended, dtype=np.uint16), (0, 2, 1, 3))).reshape(
+        batch * tokens, heads * head_dim)
+    if bits == 8:
+        with np.errstate(over="ignore", invalid="ignore"):
+            return {"output": Q.e4m3_encode_satfinite((Q.bf16_to_f32(rows) * F32(scale_value)).astype(F32))}
+    return encode(rows, bits, scale_value)

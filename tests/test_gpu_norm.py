@@ -178,3 +178,28 @@ def test_layer_norm_rejects_bad_arguments(device):
     wide_w = torch.zeros(4096, device=device, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError):      # beyond the 256-thread block of the reference
         K.layer_norm_quant(wide, wide_w, wide_w, torch.zeros((2, 4096), device=device, dtype=torch.uint8), bits=8, scale_value=1.0)
+
+
+@pytest.mark.parametrize("bits_", [8, 4, 16])
+@pytest.mark.parametrize("batch,heads,tokens,head_dim", [(1, 8, 560, 256), (3, 8, 10, 256), (2, 16, 256, 72), (2, 3, 5, 16)])
+def test_attention_output_transposing_encoder(device, bits_, batch, heads, tokens, head_dim):
+    if bits_ == 4 and head_dim % 16:
+        pytest.skip("NVFP4 blocks need head_dim % 16 == 0")
+    generator = torch.Generator().manual_seed(head_dim + tokens)
+    attended = (torch.randn((batch, heads, tokens, head_dim), generator=generator) * 2).to(torch.bfloat16)
+    attended[0, 0, 0, :16] = 0
+    rows, columns = batch * tokens, heads * head_dim
+    scale_value = {8: 448.0 / 9.0, 4: 9.0 / 2688.0, 16: 1.0}[bits_]
+    width = {16: 2 * columns, 8: columns, 4: columns // 2}[bits_]
+    expected = NO.bhsd_quant(bits(attended), bits_, np.float32(scale_value))
+    # contiguous [B, H, S, D], and the same values held as a transposed view of [B, S, H, D]
+    for source in (attended.to(device), attended.to(device).transpose(1, 2).contiguous().transpose(1, 2)):
+        output = torch.zeros((rows, width), device=device, dtype=torch.uint8)
+        scales = torch.zeros((rows, columns // 16), device=device, dtype=torch.uint8) if bits_ == 4 else None
+        blocked = torch.zeros(blocked_bytes(rows, columns // 16), device=device, dtype=torch.uint8) if bits_ == 4 else None
+        K.bhsd_quant(source, output, bits=bits_, scale_value=scale_value, scales=scales, blocked=blocked)
+        torch.cuda.synchronize()
+        assert np.array_equal(u8(output), expected["output"].view(np.uint8).reshape(rows, -1))
+        if bits_ == 4:
+            assert np.array_equal(u8(scales), expected["scales"])
+            assert np.array_equal(u8(blocked), expected["blocked"].reshape(-1))

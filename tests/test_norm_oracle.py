@@ -129,3 +129,15 @@ def test_layer_norm_sums_by_hand():
     w0, w1, z = warps[0], warps[1], np.float32(0)
     expected = np.float32(np.float32(np.float32(w0 + z) + np.float32(z + z)) + np.float32(np.float32(w1 + z) + np.float32(z + z)))
     assert total[0] == expected and squares[0] > 0
+
+
+def test_transposing_encoder_restatement():
+    rng = np.random.default_rng(17)
+    attended = Q.f32_to_bf16(rng.standard_normal((2, 3, 5, 16)).astype(np.float32))
+    rows = NO.bhsd_quant(attended, 16)["output"]
+    assert rows.shape == (10, 48)
+    assert np.array_equal(rows[1 * 5 + 2, 16:32], attended[1, 1, 2])       # row b*S+s, columns h*D..h*D+D
+    codes = NO.bhsd_quant(attended, 8, np.float32(100.0))["output"]
+    assert np.array_equal(codes, Q.e4m3_encode_satfinite((Q.bf16_to_f32(rows) * np.float32(100.0)).astype(np.float32)))
+    packed = NO.bhsd_quant(attended, 4, np.float32(0.003))
+    assert np.array_equal(packed["output"], Q.nvfp4_quantize_C(rows, np.float32(0.003))[0])
