@@ -13,6 +13,9 @@ int launch_geglu(const void* gate, const void* up, void* output, void* scales, v
                  int rows, int columns, int64_t row_stride, int bits, const void* table, int flags,
                  cudaStream_t stream);
 int launch_norm_quant(const b2_norm_desc* desc, cudaStream_t stream);
+int launch_normalize_frames(const void* frames, void* images, int cameras, int pixels, cudaStream_t stream);
+int launch_frames_to_patches(const void* frames, void* patches, int cameras, int height, int width, int patch,
+                             cudaStream_t stream);
 int launch_bhsd_quant(const void* input, void* output, void* scales, void* blocked, float scale_value, int64_t stride_b,
                       int64_t stride_h, int64_t stride_s, int batch, int heads, int tokens, int head_dim, int bits,
                       cudaStream_t stream);
@@ -172,6 +175,20 @@ int b2_bhsd_quant(const void* input, void* output, void* scales, void* blocked, 
     if (int64_t(batch) * tokens > 2147483647LL || int64_t(heads) * head_dim > 2147483647LL) return B2_E_TOO_LARGE;
     return b2::launch_bhsd_quant(input, output, scales, blocked, scale_value, stride_b, stride_h, stride_s, batch, heads, tokens,
                                  head_dim, bits, static_cast<cudaStream_t>(stream));
+}
+
+int b2_normalize_frames(const void* frames, void* images, int32_t cameras, int32_t pixels, void* stream) {
+    if (frames == nullptr || images == nullptr || cameras <= 0 || pixels <= 0) return B2_E_INVALID;
+    if (!is_aligned(images, 4)) return B2_E_INVALID;
+    return b2::launch_normalize_frames(frames, images, cameras, pixels, static_cast<cudaStream_t>(stream));
+}
+
+int b2_frames_to_patches(const void* frames, void* patches, int32_t cameras, int32_t height, int32_t width, int32_t patch,
+                         void* stream) {
+    if (frames == nullptr || patches == nullptr || cameras <= 0 || height <= 0 || width <= 0 || patch <= 0) return B2_E_INVALID;
+    if (height % patch != 0 || width % patch != 0 || (3 * patch * patch) % 4 != 0) return B2_E_UNSUPPORTED;
+    if (!is_aligned(patches, 8)) return B2_E_INVALID;
+    return b2::launch_frames_to_patches(frames, patches, cameras, height, width, patch, static_cast<cudaStream_t>(stream));
 }
 
 int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc) {

@@ -258,6 +258,40 @@ def bhsd_quant(attended: torch.Tensor, output: torch.Tensor, *, bits: int, scale
     N.check(status, "b2_bhsd_quant")
 
 
+def normalize_frames(frames: torch.Tensor, images: torch.Tensor) -> None:
+    """``(frames / 255) * 2 - 1`` into fp32 ``images`` [cameras, 3, H, W]; ``frames`` is contiguous uint8
+    [cameras, H, W, 3] (same checks and errors as the reference's ``normalize_frames``)."""
+    if frames.dtype != torch.uint8 or frames.ndim != 4 or frames.shape[3] != 3 or not frames.is_contiguous():
+        raise ValueError("frames must be contiguous uint8 [cameras, height, width, 3]")
+    if images.dtype != torch.float32 or images.ndim != 4 or tuple(images.shape[:2]) != (frames.shape[0], 3) or \
+            not images.is_contiguous():
+        raise ValueError("images must be contiguous float32 [cameras, 3, height, width]")
+    if frames.device.type != "cuda" or images.device != frames.device:
+        raise ValueError("frames and images must share a CUDA device")
+    if tuple(images.shape[2:]) != tuple(frames.shape[1:3]):
+        raise ValueError("images must have the frame height and width")
+    with torch.cuda.device(frames.device):
+        status = N.load().b2_normalize_frames(frames.data_ptr(), images.data_ptr(), frames.shape[0],
+                                              frames.shape[1] * frames.shape[2], _stream(frames.device))
+    N.check(status, "b2_normalize_frames")
+
+
+def frames_to_patches(frames: torch.Tensor, patches: torch.Tensor, patch: int) -> None:
+    """uint8 frames [cameras, H, W, 3] -> bf16 patch rows [cameras * (H/patch) * (W/patch), 3*patch*patch] holding
+    ``bf16((x / 255) * 2 - 1)`` in (channel, y, x) order; see ``b2_frames_to_patches``."""
+    device = _require_cuda(frames, patches)
+    if frames.dtype != torch.uint8 or frames.ndim != 4 or frames.shape[3] != 3 or not frames.is_contiguous():
+        raise ValueError("frames must be contiguous uint8 [cameras, height, width, 3]")
+    cameras, height, width, _ = frames.shape
+    expected = (cameras * (height // patch) * (width // patch), 3 * patch * patch)
+    if patches.dtype != torch.bfloat16 or tuple(patches.shape) != expected or not patches.is_contiguous():
+        raise ValueError("patches must be contiguous bf16 [cameras * grid_h * grid_w, 3 * patch * patch]")
+    with torch.cuda.device(device):
+        status = N.load().b2_frames_to_patches(frames.data_ptr(), patches.data_ptr(), cameras, height, width, patch,
+                                               _stream(device))
+    N.check(status, "b2_frames_to_patches")
+
+
 _WORKSPACE_BYTES = 32 << 20
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 

@@ -396,10 +396,12 @@ class Pi05ShapedPolicy(nn.Module):
     def embed_images(self, images: torch.Tensor) -> torch.Tensor:
         """uint8 [B, cameras, H, W, 3] -> [B, cameras*256, 2048]; frames are scaled as (x/255)*2-1."""
         batch, cameras = images.shape[:2]
-        frames = (images.to(self.device_, non_blocking=True).float() / 255.0) * 2.0 - 1.0
         grid = IMAGE_SIZE // PATCH
-        tiles = frames.view(batch * cameras, grid, PATCH, grid, PATCH, 3).permute(0, 1, 3, 5, 2, 4)
-        tiles = tiles.reshape(batch * cameras, grid * grid, 3 * PATCH * PATCH).to(torch.bfloat16)
+        frames = images.to(self.device_, non_blocking=True).reshape(batch * cameras, IMAGE_SIZE, IMAGE_SIZE, 3)
+        # one launch: (x/255)*2-1 in fp32, bf16, and the (channel, y, x) patch gather of the patch embedding
+        tiles = torch.empty((batch * cameras * grid * grid, 3 * PATCH * PATCH), device=self.device_, dtype=torch.bfloat16)
+        K.frames_to_patches(frames.contiguous(), tiles, PATCH)
+        tiles = tiles.view(batch * cameras, grid * grid, 3 * PATCH * PATCH)
         x = F.linear(tiles, self.patch_weight, self.patch_bias) + self.position
         for block in self.vision:
             x = block(x)

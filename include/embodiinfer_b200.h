@@ -241,6 +241,19 @@ int b2_bhsd_quant(const void* input, void* output, void* scales, void* blocked, 
                   int64_t stride_h, int64_t stride_s, int32_t batch, int32_t heads, int32_t tokens, int32_t head_dim,
                   int32_t bits, void* stream);
 
+/* Camera frames uint8 [cameras, height*width, 3] -> fp32 planes [cameras, 3, height*width] holding
+ * (x / 255) * 2 - 1, each step rounded separately in fp32.  Replaces cc_normalize_frames
+ * (embodiinfer/backend/cuda/csrc/camera_frames.cu:107-115; bound in embodiinfer/backend/cuda/camera_frames.py:45-61). */
+int b2_normalize_frames(const void* frames, void* images, int32_t cameras, int32_t pixels, void* stream);
+
+/* Camera frames uint8 [cameras, height, width, 3] -> bf16 patch rows [cameras * (height/patch) * (width/patch),
+ * 3*patch*patch], row = (camera, patch row, patch column), column = (channel, y in patch, x in patch), value =
+ * bf16((x / 255) * 2 - 1): the normalisation above followed by the cast and the patch gather of the SigLIP patch
+ * embedding (embodiinfer/policies/pi05/inference/vision.py:593-602) in one launch, bit-identical to those steps.
+ * height % patch == 0, width % patch == 0, (3*patch*patch) % 4 == 0; `patches` 8-byte aligned. */
+int b2_frames_to_patches(const void* frames, void* patches, int32_t cameras, int32_t height, int32_t width, int32_t patch,
+                         void* stream);
+
 /* Device scratch a launch described by `desc` could use, in bytes (0: it would not split K; only B2_EPI_LINEAR
  * launches split).  With few
  * tiles (M = 10*B tokens against 148 SMs) the library cuts K into up to 16 ranges computed by different CTAs;

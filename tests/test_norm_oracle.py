@@ -141,3 +141,15 @@ def test_transposing_encoder_restatement():
     assert np.array_equal(codes, Q.e4m3_encode_satfinite((Q.bf16_to_f32(rows) * np.float32(100.0)).astype(np.float32)))
     packed = NO.bhsd_quant(attended, 4, np.float32(0.003))
     assert np.array_equal(packed["output"], Q.nvfp4_quantize_C(rows, np.float32(0.003))[0])
+
+
+def test_frames_oracle():
+    from oracle import frames_oracle as FO
+    frames = np.arange(2 * 4 * 6 * 3, dtype=np.uint8).reshape(2, 4, 6, 3)
+    images = FO.normalize_frames(frames)
+    assert images.shape == (2, 3, 4, 6) and images.dtype == np.float32
+    assert images[0, 0, 0, 0] == np.float32(-1) and images[1, 2, 3, 5] == np.float32(np.float32(np.float32(143) / np.float32(255)) * np.float32(2)) - np.float32(1)
+    patches = FO.frames_to_patches(frames, 2)
+    assert patches.shape == (2 * 2 * 3, 12)
+    # row (camera 1, patch row 1, patch column 2), column (channel 1, y 1, x 0) = pixel (y 3, x 4) of camera 1
+    assert patches[1 * 6 + 1 * 3 + 2, 1 * 4 + 1 * 2 + 0] == Q.f32_to_bf16(images[1, 1, 3, 4].reshape(1))[0]
