@@ -194,3 +194,34 @@ def test_backend_construction_refused_during_capture(device):
         with pytest.raises(RuntimeError, match="before CUDA Graph capture"):
             with torch.cuda.graph(graph, stream=side):
                 L.quantization_backends.get("cuda", request(device))
+
+
+@pytest.mark.parametrize("precision", ["fp8", "nvfp4"])
+def test_calibrated_layer_record_with_smoothquant_scales(device, precision):
+    """A layer record with SmoothQuant scales: gate/up are packed as W*s and the caller feeds x/s (the folded norm),
+    so the fused MLP's result stays that of the unsmoothed plan up to quantisation noise; the fused norm + encoder
+    launch with the folded norm scale produces the x/s encoding directly."""
+    from embodiinfer_b200 import calibration as C
+    from embodiinfer_b200.backend.norm_quant import B200NormQuant
+    from embodiinfer_b200.backend.quantization import B200Quantizer
+    hidden_size, inter = 256, 512
+    quantizer = B200Quantizer()
+    gate_w, up_w = make_weight((inter, hidden_size), 61).bfloat16().to(device), make_weight((inter, hidden_size), 62).bfloat16().to(device)
+    down_w = make_weight((hidden_size, inter), 63).bfloat16().to(device)
+    generator = torch.Generator().manual_seed(64)
+    smooth = (torch.rand(hidden_size, generator=generator) * 1.5 + 0.5)
+    residual = make_input((1, 70, hidden_size), 65, outliers=False).to(device)
+    norm_weight = (torch.randn(hidden_size, generator=generator) * 0.1).to(device)
+    inverse = torch.rsqrt(residual.float().square().mean(-1, keepdim=True) + 1e-6)
+    normed = (residual.float() * inverse * (1 + norm_weight)).to(torch.bfloat16)
+    plain = C.fused_mlp_from_layer(gate_w, up_w, down_w, C.MlpLayerPrecision(precision, precision, 8.0, 2.0), quantizer)
+    expected = plain(normed.reshape(70, hidden_size))
+    layer = C.MlpLayerPrecision(precision, precision, 16.0, 2.0, smooth=[float(v) for v in smooth])
+    smoothed = C.fused_mlp_from_layer(gate_w, up_w, down_w, layer, quantizer)
+    folded_scale = C.smoothed_norm_scale(norm_weight, smooth.to(device))
+    bits_ = 8 if precision == "fp8" else 4
+    plan = B200NormQuant(quantizer).plan(residual, bits=bits_, calibrated_scale=16.0 / (448 * (6 if bits_ == 4 else 1)), adaptive=False)
+    encoded = plan.normalize(residual, scale=folded_scale)
+    got = smoothed.project(residual.reshape(70, hidden_size), encoded)
+    error = (got.float() - expected.float()).norm() / expected.float().norm()
+    assert error < (0.06 if precision == "fp8" else 0.2), float(error)
