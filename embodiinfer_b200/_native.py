@@ -95,6 +95,7 @@ SIGNATURES: dict[str, list] = {
     "b2_bhsd_quant": [_P, _P, _P, _P, _F, _I64, _I64, _I64, _I, _I, _I, _I, _I, _P],
     "b2_normalize_frames": [_P, _P, _I, _I, _P],
     "b2_frames_to_patches": [_P, _P, _I, _I, _I, _I, _P],
+    "b2_resize_frames": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "b2_rope_split": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I64, _I, _I, _P],
 }
 RESULT_TYPES = {"b2_linear_workspace_bytes": ctypes.c_int64}

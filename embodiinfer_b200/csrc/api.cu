@@ -13,6 +13,10 @@ int launch_geglu(const void* gate, const void* up, void* output, void* scales, v
                  int rows, int columns, int64_t row_stride, int bits, const void* table, int flags,
                  cudaStream_t stream);
 int launch_norm_quant(const b2_norm_desc* desc, cudaStream_t stream);
+int launch_resize_frames(const void* frames, void* images, const void* row_bounds, const void* row_weights, int row_taps,
+                         const void* column_bounds, const void* column_weights, int column_taps, int cameras, int height,
+                         int width, int out_height, int out_width, int canvas_height, int canvas_width, int top, int left,
+                         cudaStream_t stream);
 int launch_normalize_frames(const void* frames, void* images, int cameras, int pixels, cudaStream_t stream);
 int launch_frames_to_patches(const void* frames, void* patches, int cameras, int height, int width, int patch,
                              cudaStream_t stream);
@@ -189,6 +193,24 @@ int b2_frames_to_patches(const void* frames, void* patches, int32_t cameras, int
     if (height % patch != 0 || width % patch != 0 || (3 * patch * patch) % 4 != 0) return B2_E_UNSUPPORTED;
     if (!is_aligned(patches, 8)) return B2_E_INVALID;
     return b2::launch_frames_to_patches(frames, patches, cameras, height, width, patch, static_cast<cudaStream_t>(stream));
+}
+
+int b2_resize_frames(const void* frames, void* images, const void* row_bounds, const void* row_weights, int32_t row_taps,
+                     const void* column_bounds, const void* column_weights, int32_t column_taps, int32_t cameras,
+                     int32_t height, int32_t width, int32_t out_height, int32_t out_width, int32_t canvas_height,
+                     int32_t canvas_width, int32_t top, int32_t left, void* stream) {
+    if (frames == nullptr || images == nullptr || row_bounds == nullptr || row_weights == nullptr || column_bounds == nullptr ||
+        column_weights == nullptr)
+        return B2_E_INVALID;
+    if (cameras <= 0 || height <= 0 || width <= 0 || out_height <= 0 || out_width <= 0 || row_taps <= 0 || column_taps <= 0)
+        return B2_E_INVALID;
+    if (top < 0 || left < 0 || top + out_height > canvas_height || left + out_width > canvas_width) return B2_E_INVALID;
+    if (!is_aligned(images, 4) || !is_aligned(row_bounds, 4) || !is_aligned(row_weights, 4) || !is_aligned(column_bounds, 4) ||
+        !is_aligned(column_weights, 4))
+        return B2_E_INVALID;
+    return b2::launch_resize_frames(frames, images, row_bounds, row_weights, row_taps, column_bounds, column_weights, column_taps,
+                                    cameras, height, width, out_height, out_width, canvas_height, canvas_width, top, left,
+                                    static_cast<cudaStream_t>(stream));
 }
 
 int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc) {

@@ -246,6 +246,20 @@ int b2_bhsd_quant(const void* input, void* output, void* scales, void* blocked, 
  * (embodiinfer/backend/cuda/csrc/camera_frames.cu:107-115; bound in embodiinfer/backend/cuda/camera_frames.py:45-61). */
 int b2_normalize_frames(const void* frames, void* images, int32_t cameras, int32_t pixels, void* stream);
 
+/* OpenPI's resize_with_pad on the device: uint8 frames [cameras, height, width, 3] are resampled to
+ * [out_height, out_width] with Pillow's two-pass 8-bit bilinear filter (22-bit fixed-point taps, a byte clamp after
+ * each pass), placed at (top, left) on a black [canvas_height, canvas_width] canvas and written as fp32 planes
+ * [cameras, 3, canvas_height, canvas_width] of (x / 255) * 2 - 1.  Replaces cc_resize_frames
+ * (embodiinfer/backend/cuda/csrc/camera_frames.cu:90-105; bound by FrameResize,
+ * embodiinfer/backend/cuda/camera_frames.py:93-160) in one launch and without its `rows` scratch.
+ * Device int32 tables, as the reference's host code builds them: `*_bounds` [out, 2] = first source index and tap
+ * count per output index, `*_weights` [out, *_taps] fixed-point taps (row_* for the horizontal axis, column_* for
+ * the vertical one). */
+int b2_resize_frames(const void* frames, void* images, const void* row_bounds, const void* row_weights, int32_t row_taps,
+                     const void* column_bounds, const void* column_weights, int32_t column_taps, int32_t cameras,
+                     int32_t height, int32_t width, int32_t out_height, int32_t out_width, int32_t canvas_height,
+                     int32_t canvas_width, int32_t top, int32_t left, void* stream);
+
 /* Camera frames uint8 [cameras, height, width, 3] -> bf16 patch rows [cameras * (height/patch) * (width/patch),
  * 3*patch*patch], row = (camera, patch row, patch column), column = (channel, y in patch, x in patch), value =
  * bf16((x / 255) * 2 - 1): the normalisation above followed by the cast and the patch gather of the SigLIP patch

@@ -52,3 +52,22 @@ def test_frames_reject_bad_arguments(device):
     odd = torch.zeros((1, 3, 3, 3), device=device, dtype=torch.uint8)
     with pytest.raises(RuntimeError):                    # 3 * patch^2 must be a multiple of 4
         K.frames_to_patches(odd, torch.zeros((1, 27), device=device, dtype=torch.bfloat16), 3)
+
+
+@pytest.mark.parametrize("source", [(256, 256), (480, 640), (128, 96), (224, 300), (224, 224)])
+def test_frame_resize_matches_the_oracle(device, source):
+    """Same sources as the reference's own test (tests/test_fused_operators.py:525); the oracle is pinned on Pillow."""
+    from embodiinfer_b200.frames import FrameResize, pillow_bilinear_taps, resize_geometry
+    frames = torch.randint(0, 256, (2, *source, 3), dtype=torch.uint8, generator=torch.Generator().manual_seed(0))
+    resize = FrameResize(source, (224, 224), device)
+    images = torch.empty((2, 3, 224, 224), device=device)
+    resize(frames.to(device), resize.rows_buffer(2, device), images)
+    geometry = resize_geometry(source, (224, 224))
+    assert geometry == (resize.height, resize.width, resize.top, resize.left)
+    want = FO.resize_with_pad(frames.numpy(), (224, 224), geometry, pillow_bilinear_taps(source[1], geometry[1]),
+                              pillow_bilinear_taps(source[0], geometry[0]))
+    assert np.array_equal(images.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    resize(frames.to(device), None, images)          # the scratch of the reference's two-pass kernel is optional here
+    assert np.array_equal(images.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    with pytest.raises(ValueError):
+        resize(frames.to(device)[:, :-1].contiguous(), None, images)
