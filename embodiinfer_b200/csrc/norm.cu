@@ -80,22 +80,30 @@ __device__ __forceinline__ uint4 apply_update(const NormArgs& a, const uint4& in
     return pack_bf16x8(v);
 }
 
-// y = bf16((r * inverse) * (1 + scale))  or  bf16((r * inverse) * (1 + m_scale) + m_shift), in place.
-__device__ __forceinline__ void affine_vector(const NormArgs& a, int64_t modulation_base, int column, float inverse, float (&v)[8]) {
+// y = bf16((r * inverse) * (1 + scale))  or  bf16((r * inverse) * (1 + m_scale) + m_shift) for the 8 packed
+// values of `r`, returned packed.  Two columns per instruction on the packed fp32 pipe (`mul.rn.f32x2`,
+// `add.rn.f32x2`: each lane rounds like the scalar operation, and nothing is fused).
+__device__ __forceinline__ uint4 affine_vector(const NormArgs& a, int64_t modulation_base, int column, float inverse,
+                                               const uint4& r) {
     const float* multiplier = a.modulation != nullptr ? a.modulation + modulation_base + column : a.scale + column;
     const float4 m0 = *reinterpret_cast<const float4*>(multiplier), m1 = *reinterpret_cast<const float4*>(multiplier + 4);
-    const float m[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+    const float2 m[4] = {make_float2(m0.x, m0.y), make_float2(m0.z, m0.w), make_float2(m1.x, m1.y), make_float2(m1.z, m1.w)};
+    const float2 inverse2 = make_float2(inverse, inverse), one = make_float2(1.0f, 1.0f);
+    const uint32_t words[4] = {r.x, r.y, r.z, r.w};
+    uint32_t y[4];
     if (a.modulation != nullptr) {
         const float* shift = a.modulation + modulation_base + a.columns + column;
         const float4 s0 = *reinterpret_cast<const float4*>(shift), s1 = *reinterpret_cast<const float4*>(shift + 4);
-        const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const float2 s[4] = {make_float2(s0.x, s0.y), make_float2(s0.z, s0.w), make_float2(s1.x, s1.y), make_float2(s1.z, s1.w)};
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-            v[i] = round_to_bf16(__fadd_rn(__fmul_rn(__fmul_rn(v[i], inverse), __fadd_rn(1.0f, m[i])), s[i]));
+        for (int i = 0; i < 4; ++i)
+            y[i] = float2_to_bf16x2(__fadd2_rn(__fmul2_rn(__fmul2_rn(bf16x2_to_float2(words[i]), inverse2), __fadd2_rn(one, m[i])), s[i]));
     } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = round_to_bf16(__fmul_rn(__fmul_rn(v[i], inverse), __fadd_rn(1.0f, m[i])));
+        for (int i = 0; i < 4; ++i)
+            y[i] = float2_to_bf16x2(__fmul2_rn(__fmul2_rn(bf16x2_to_float2(words[i]), inverse2), __fadd2_rn(one, m[i])));
     }
+    return make_uint4(y[0], y[1], y[2], y[3]);
 }
 
 __device__ __forceinline__ void write_gate_vector(const NormArgs& a, int64_t modulation_base, int64_t gate_base, int column) {
@@ -121,36 +129,48 @@ struct Encoder {
     __device__ __forceinline__ Encoder(float global_scale, float multiplier)
         : global(global_scale), reciprocal(multiplier), divide(false), by_global(rounded_product(6.0f, global_scale)) {}
 
-    // Every lane of the warp calls this (the NVFP4 block maximum is exchanged with the neighbouring lane);
-    // lanes without a vector pass valid = false.
+    // `y`: eight bf16 values, packed.  Every lane of the warp calls this (the NVFP4 block maximum is exchanged
+    // with the neighbouring lane); lanes without a vector pass valid = false.
     template <class Args>
-    __device__ __forceinline__ void store(const Args& a, int row, int64_t base, int column, bool valid, const float (&y)[8]) const {
+    __device__ __forceinline__ void store(const Args& a, int row, int64_t base, int column, bool valid, const uint4& y) const {
         if (BITS == 16) {
-            if (valid) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.output) + base + column) = pack_bf16x8(y);
+            if (valid) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.output) + base + column) = y;
         } else if (BITS == 8) {
             if (!valid) return;
-            float q[8];
+            const uint32_t words[4] = {y.x, y.y, y.z, y.w};
+            uint32_t codes[4];
+            if (divide) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) q[i] = divide ? __fdiv_rn(y[i], global) : __fmul_rn(y[i], reciprocal);
+                for (int i = 0; i < 4; ++i) {
+                    const float2 v = bf16x2_to_float2(words[i]);
+                    codes[i] = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v.x, global), __fdiv_rn(v.y, global)), __NV_SATFINITE, __NV_E4M3);
+                }
+            } else {
+                const float2 factor = make_float2(reciprocal, reciprocal);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    codes[i] = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(words[i]), factor), __NV_SATFINITE, __NV_E4M3);
+            }
             uint2 packed;
-            packed.x = pack_fp8x4(q[0], q[1], q[2], q[3]);
-            packed.y = pack_fp8x4(q[4], q[5], q[6], q[7]);
+            packed.x = codes[0] | (codes[1] << 16);
+            packed.y = codes[2] | (codes[3] << 16);
             *reinterpret_cast<uint2*>(a.output + base + column) = packed;
         } else {
             // A 16-element block is shared by an even lane and its odd neighbour.
-            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
-            if (valid) packed = pack_bf16x8(y);
-            const uint32_t words[4] = {packed.x, packed.y, packed.z, packed.w};
+            const uint32_t words[4] = {valid ? y.x : 0u, valid ? y.y : 0u, valid ? y.z : 0u, valid ? y.w : 0u};
             float maximum = abs_max_bf16_words(words);
             maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
             if (!valid) return;
             const uint8_t code = nvfp4_block_scale<true>(maximum, by_global, 0);
             const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(code)));
             uint32_t codes;
-            if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f)
+            if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f) {
                 codes = nvfp4_encode_words_short<true>(words[0], words[1], words[2], words[3], denominator);
-            else
-                codes = nvfp4_encode_x8<true>(y, denominator, maximum);
+            } else {
+                float values[8];
+                unpack_bf16x8(y, values);
+                codes = nvfp4_encode_x8<true>(values, denominator, maximum);
+            }
             *reinterpret_cast<uint32_t*>(a.output + (base + column) / 2) = codes;
             if (((column >> 3) & 1) == 0) {
                 const int block = column >> 4, blocks_per_row = a.columns >> 4;
@@ -264,10 +284,9 @@ norm_encode_block_kernel(const NormArgs a) {
 #pragma unroll
     for (int i = 0; i < VECTORS; ++i) {
         const int column = (threadIdx.x + i * NORM_THREADS) * 8;
-        float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        uint4 y = make_uint4(0u, 0u, 0u, 0u);
         if (valid[i]) {
-            unpack_bf16x8(packed[i], y);
-            affine_vector(a, modulation_base, column, inverse, y);
+            y = affine_vector(a, modulation_base, column, inverse, packed[i]);
             if (write_gate) write_gate_vector(a, modulation_base, gate_base, column);
         }
         encoder.store(a, row, base, column, valid[i], y);
@@ -319,9 +338,7 @@ norm_encode_warp_kernel(const NormArgs a) {
 #pragma unroll
     for (int i = 0; i < VECTORS; ++i) {
         const int column = (lane + 32 * i) * 8;
-        float y[8];
-        unpack_bf16x8(packed[i], y);
-        affine_vector(a, modulation_base, column, inverse, y);
+        const uint4 y = affine_vector(a, modulation_base, column, inverse, packed[i]);
         if (write_gate) write_gate_vector(a, modulation_base, gate_base, column);
         encoder.store(a, row, base, column, true, y);
     }
@@ -477,7 +494,7 @@ layer_norm_encode_kernel(const LayerNormArgs a) {
             for (int j = 0; j < 8; ++j)
                 y[j] = round_to_bf16(__fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(y[j], mean), deviation), weight[j]), bias[j]));
         }
-        encoder.store(a, row, base, column, valid[i], y);
+        encoder.store(a, row, base, column, valid[i], pack_bf16x8(y));
     }
 }
 
@@ -545,11 +562,11 @@ bhsd_encode_kernel(const BhsdArgs a) {
         const bool valid = index < total;
         const int row = int(index / vectors_per_row);           // b * tokens + s
         const int column = int(index - int64_t(row) * vectors_per_row) * 8;
-        float y[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        uint4 y = make_uint4(0u, 0u, 0u, 0u);
         if (valid) {
             const int b = row / a.tokens, s = row - b * a.tokens;
             const int h = column / a.head_dim, d = column - h * a.head_dim;
-            unpack_bf16x8(ld_nc_u4(reinterpret_cast<const uint4*>(a.input + b * a.stride_b + h * a.stride_h + s * a.stride_s + d)), y);
+            y = ld_nc_u4(reinterpret_cast<const uint4*>(a.input + b * a.stride_b + h * a.stride_h + s * a.stride_s + d));
         }
         encoder.store(a, row, int64_t(row) * a.columns, column, valid, y);
     }

@@ -157,6 +157,28 @@ def norm_cases(device):
             yield f"norm/residual_layer_norm_bits{bits}/{rows}x{columns}", make, total, total, 0
 
 
+def layout_cases(device):
+    """The transposing encoder behind the attention and the frame-to-patch producer."""
+    heads, head_dim = 8, 256
+    for batch, tokens in ((1, 560), (32, 560)):
+        for bits, out_bytes in ((8, 1.0), (4, 0.5 + 1 / 16)):
+            def make(_i, batch=batch, tokens=tokens, bits=bits):
+                attended = torch.randn((batch, heads, tokens, head_dim), device=device).to(torch.bfloat16)
+                rows, columns = batch * tokens, heads * head_dim
+                out = torch.empty((rows, columns if bits == 8 else columns // 2), device=device, dtype=torch.uint8)
+                blocked = torch.zeros(_blocked_bytes(rows, columns // 16), device=device, dtype=torch.uint8) if bits == 4 else None
+                return lambda: K.bhsd_quant(attended, out, bits=bits, scale_value=40.0 if bits == 8 else 0.004, blocked=blocked)
+            total = int(batch * tokens * heads * head_dim * (2 + out_bytes))
+            yield f"layout/bhsd_bits{bits}/{batch}x{heads}x{tokens}x{head_dim}", make, total, total, 0
+    for cameras in (3, 96):
+        def make(_i, cameras=cameras):
+            frames = torch.randint(0, 256, (cameras, 224, 224, 3), device=device, dtype=torch.uint8)
+            patches = torch.empty((cameras * 256, 588), device=device, dtype=torch.bfloat16)
+            return lambda: K.frames_to_patches(frames, patches, 14)
+        total = cameras * 224 * 224 * 3 * 3
+        yield f"layout/frames_to_patches/{cameras}x224x224", make, total, total, 0
+
+
 LINEAR_SHAPES = [
     # name, kind, M, N (features; GEGLU: gate features), K, epilogue
     ("cfg1_fp8_560x16384x2048", "fp8", 560, 16384, 2048, "linear"),
@@ -279,7 +301,7 @@ def main() -> None:
     torch.cuda.set_device(device)
     peaks = {"hbm_gbs": 6541.5, "fp8_tflops": 4500.0, "nvfp4_tflops": 9000.0}
     options = {"flags": args.flags, "feature_tile": args.feature_tile, "unpaired": args.unpaired}
-    sources = (quantiser_cases, geglu_cases, norm_cases, lambda dev: linear_cases(dev, options))
+    sources = (quantiser_cases, geglu_cases, norm_cases, layout_cases, lambda dev: linear_cases(dev, options))
     for source in sources:
         for name, make, set_bytes, algorithmic_bytes, flops in source(device):
             if not pattern.search(name):
