@@ -93,6 +93,7 @@ struct KernelArgs {
     uint8_t* out_scales;
     uint8_t* out_blocked;
     unsigned int* status;
+    int reduce_rows;             // cluster split: token rows (a multiple of 32) of a partial-sum slot in the leader's shared memory
     unsigned int* tickets;       // split-K: one arrival counter per tile (zero between launches)
     float* partials;             // split-K: [tile][split][128][tile_n] fp32
 };
@@ -419,12 +420,25 @@ struct TileWalk {
 
 // ---- the kernel ---------------------------------------------------------------
 
-// SPLIT_K: the variant whose epilogue goes through the split-K fix-up (its extra registers stay out of the
-// unsplit kernels).
-template <int KIND, int EPI, bool SPLIT_K>
+// SPLIT selects how K is cut across CTAs (each variant is its own kernel, so the fix-up's registers stay out of
+// the unsplit kernels):
+//   SPLIT_NONE     one CTA computes all of K of its tiles;
+//   SPLIT_GLOBAL   partial sums go through a caller-provided workspace in global memory, the CTA that draws a
+//                  tile's last ticket adds them (any number of token tiles; opt-in);
+//   SPLIT_CLUSTER  the CTAs of a thread-block cluster each take a K range of ONE tile; ranks 1.. write their fp32
+//                  partial sums (valid token rows only) into the shared memory of rank 0 through the cluster's
+//                  distributed shared memory, a cluster barrier orders the writes, and rank 0 adds them to its
+//                  own accumulator in rank order and runs the epilogue.  No workspace, no atomics, one launch;
+//                  for the single-token-tile launches (M <= 128) whose few tiles leave most SMs idle (opt-in:
+//                  B2_LINEAR_CLUSTER_SPLIT).
+enum SplitMode { SPLIT_NONE = 0, SPLIT_GLOBAL = 1, SPLIT_CLUSTER = 2 };
+
+template <int KIND, int EPI, int SPLIT_MODE>
 __global__ void __launch_bounds__(gemm_threads(EPI), 1)
 linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
               const KernelArgs args) {
+    constexpr bool SPLIT_K = SPLIT_MODE == SPLIT_GLOBAL;
+    constexpr bool CLUSTER = SPLIT_MODE == SPLIT_CLUSTER;
     constexpr bool GEGLU = is_gated(EPI);
     constexpr bool USES_TABLE = EPI != EPI_LINEAR;
     extern __shared__ uint8_t shared_raw[];
@@ -452,6 +466,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     const uint32_t tmem_slot = panel_bar + 8 * MAX_RESIDENT_KB;
     const uint32_t split_flag = tmem_slot + 8;                    // split-K: "this CTA drew the last ticket"
     const uint32_t compact_table = tmem_slot + 16;                // 2 * (gelu_hi - gelu_lo) bf16 entries
+    const uint32_t reduce_base = compact_table;                   // cluster split (plain epilogue, no table): [rank - 1][reduce_rows][BN] fp32
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -629,6 +644,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         // (split K ranges are a few stages long: nothing to prefetch ahead of)
         if (resident) { if (args.splits == 1) producer_role(Yes{}, Yes{}); else producer_role(Yes{}, No{}); }
         else { if (args.splits == 1) producer_role(No{}, Yes{}); else producer_role(No{}, No{}); }
+        if (CLUSTER) { cluster_arrive(); cluster_wait(); }        // every thread of the cluster takes part, once
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
         // (all lanes run the loop; one elected lane issues the tcgen05 instructions)
@@ -775,6 +791,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         else if (split_halves) { if (resident) mma_role(Yes{}, Yes{}, Yes{}); else mma_role(No{}, Yes{}, Yes{}); }
         else if (two_blocks) { if (resident) mma_role(Yes{}, Yes{}, No{}); else mma_role(No{}, Yes{}, No{}); }
         else { if (resident) mma_role(Yes{}, No{}, No{}); else mma_role(No{}, No{}, No{}); }
+        if (CLUSTER) { cluster_arrive(); cluster_wait(); }
     } else {
         // ------------------------------------------------------------- epilogue
         const int quarter = warp & 3;                      // the TMEM lane partition this warp may read
@@ -813,6 +830,31 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             // the workspace and takes a ticket; the CTA that draws the last ticket adds the slots in split order
             // (so the result does not depend on which CTA that is) and runs the epilogue on the sums.  No CTA
             // waits for another.
+            // Cluster split: the host launches exactly one work item per CTA, so this loop body runs once in every
+            // CTA of the cluster and the barrier below is reached by all of its epilogue threads.
+            if (CLUSTER) {
+                const uint32_t rank = cluster_cta_rank();
+                if (rank != 0) {
+                    const uint32_t row = uint32_t(quarter * 32 + lane);
+                    for (int chunk = part; chunk < BN / 32 && warp_has_tokens; chunk += WARPS_PER_QUARTER) {
+                        uint32_t v[32];
+                        tmem_load_32x32(lane_address + chunk * 32, v);
+                        tmem_load_wait();
+                        const uint32_t local = reduce_base + (((rank - 1u) * uint32_t(args.reduce_rows) + row) * uint32_t(BN) + uint32_t(chunk) * 32u) * 4u;
+                        const uint32_t remote = cluster_map_shared(local, 0u);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) cluster_store_u4(remote + 16u * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    }
+                }
+                cluster_arrive();
+                cluster_wait();
+                if (rank != 0) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buffer);
+                    continue;
+                }
+            }
             const float* sums = nullptr;
             if (SPLIT_K) {
                 const int64_t slot_floats = int64_t(TILE_TOKENS) * BN;
@@ -928,6 +970,21 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     } else {
                         tmem_load_32x32(lane_address + chunk * 32, first);
                         tmem_load_wait();
+                        if (CLUSTER) {             // + the partial sums of ranks 1.., in rank order
+                            const uint32_t row = uint32_t(quarter * 32 + lane);
+                            for (int s = 1; s < args.splits; ++s) {
+                                const uint32_t slot = reduce_base + ((uint32_t(s - 1) * uint32_t(args.reduce_rows) + row) * uint32_t(BN) + uint32_t(chunk) * 32u) * 4u;
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) {
+                                    float4 p;
+                                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(p.x), "=f"(p.y), "=f"(p.z), "=f"(p.w) : "r"(slot + 16u * i) : "memory");
+                                    first[4 * i] = __float_as_uint(__fadd_rn(__uint_as_float(first[4 * i]), p.x));
+                                    first[4 * i + 1] = __float_as_uint(__fadd_rn(__uint_as_float(first[4 * i + 1]), p.y));
+                                    first[4 * i + 2] = __float_as_uint(__fadd_rn(__uint_as_float(first[4 * i + 2]), p.z));
+                                    first[4 * i + 3] = __float_as_uint(__fadd_rn(__uint_as_float(first[4 * i + 3]), p.w));
+                                }
+                            }
+                        }
                     }
                     epilogue_linear_chunk<GEGLU ? EPI_LINEAR : EPI>(first, args, scale, round_scale, token, f0 + chunk * 32, compact_table,
                                                                     out_scale, out_scale_rcp, true_div);
@@ -1053,7 +1110,37 @@ static void choose_tile_and_splits(int kind, bool geglu, int forced_tile, int fe
     }
 }
 
-template <int KIND, int EPI, bool SPLIT_K>
+// Single token tile, plain epilogue: tile width and cluster size (1, 2, 4 or 8 CTAs along K) from the same cycle
+// estimate.  A cluster launch runs one work item per CTA; the reduction costs a cluster barrier plus the leader's
+// pass over (splits - 1) slots of `rows` x tile fp32 in its shared memory.  Clusters are placed whole inside a GPC,
+// so the estimate stays below the SM count to keep the launch in one wave.
+constexpr int CLUSTER_CTA_BUDGET = 128;
+
+static void choose_cluster_split(int kind, int forced_tile, int features, int rows, int num_kb, bool nvfp4, int* tile_out,
+                                 int* splits_out) {
+    double best_cost = 0.0;
+    *tile_out = 0;
+    *splits_out = 1;
+    for (int tile = 256; tile >= 64; tile -= 64) {
+        if (!tile_allowed(false, tile) || (forced_tile > 0 && tile != forced_tile)) continue;
+        const int tiles = (features + tile - 1) / tile;
+        const double stage = 2.9 * (128.0 + tile);
+        const double fixed = 2500.0 + (can_double_buffer(kind, tile) ? 0.0 : 10.0 * tile);
+        const int stage_bytes = A_TILE_BYTES + tile * STAGE_K_BYTES + (nvfp4 ? 3 * SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES : 0);
+        for (int splits = 1; splits <= MAX_SPLITS; splits *= 2) {
+            const int64_t reduce_bytes = int64_t(splits - 1) * rows * tile * 4;
+            if (splits > 1 && (tiles * splits > CLUSTER_CTA_BUDGET || num_kb < 2 * splits ||
+                               reduce_bytes + 3 * stage_bytes + 4096 > SMEM_LIMIT))
+                break;
+            const int64_t waves = (int64_t(tiles) * splits + sm_count() - 1) / sm_count();
+            const int kb_item = (num_kb + splits - 1) / splits;
+            const double cost = double(waves) * (kb_item * stage + fixed) + (splits > 1 ? 1000.0 + double(reduce_bytes) / 64.0 : 0.0);
+            if (*tile_out == 0 || cost < best_cost) { *tile_out = tile; *splits_out = splits; best_cost = cost; }
+        }
+    }
+}
+
+template <int KIND, int EPI, int SPLIT_MODE>
 static int launch_linear_variant(const CUtensorMap& act_map, const CUtensorMap& weight_map, const KernelArgs& args,
                          int shared_bytes, cudaStream_t stream) {
     static bool configured[64] = {false};
@@ -1063,15 +1150,32 @@ static int launch_linear_variant(const CUtensorMap& act_map, const CUtensorMap& 
     if (device >= 0 && device < 64) {
         std::lock_guard<std::mutex> guard(lock);
         if (!configured[device]) {
-            const cudaError_t error = cudaFuncSetAttribute(linear_kernel<KIND, EPI, SPLIT_K>,
+            const cudaError_t error = cudaFuncSetAttribute(linear_kernel<KIND, EPI, SPLIT_MODE>,
                                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
             if (error != cudaSuccess) return int(error);
             configured[device] = true;
         }
     }
     const int items = args.total_tiles * args.splits;
+    if (SPLIT_MODE == SPLIT_CLUSTER) {
+        // one work item per CTA, the `splits` CTAs of a tile form one cluster (consecutive block indices)
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(unsigned(items));
+        config.blockDim = dim3(unsigned(gemm_threads(EPI)));
+        config.dynamicSmemBytes = size_t(shared_bytes);
+        config.stream = stream;
+        cudaLaunchAttribute attribute;
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = unsigned(args.splits);
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        const cudaError_t error = cudaLaunchKernelEx(&config, linear_kernel<KIND, EPI, SPLIT_MODE>, act_map, weight_map, args);
+        return error == cudaSuccess ? int(cudaGetLastError()) : int(error);
+    }
     const int grid = items < sm_count() ? items : sm_count();
-    linear_kernel<KIND, EPI, SPLIT_K><<<grid, gemm_threads(EPI), shared_bytes, stream>>>(act_map, weight_map, args);
+    linear_kernel<KIND, EPI, SPLIT_MODE><<<grid, gemm_threads(EPI), shared_bytes, stream>>>(act_map, weight_map, args);
     return int(cudaGetLastError());
 }
 
@@ -1081,9 +1185,11 @@ static int launch_linear(const CUtensorMap& act_map, const CUtensorMap& weight_m
     // only the plain epilogue has a split-K variant (the table epilogues would spill registers in the fix-up,
     // and `run_linear` never asks them to split)
     if constexpr (EPI == EPI_LINEAR) {
-        if (args.splits > 1) return launch_linear_variant<KIND, EPI, true>(act_map, weight_map, args, shared_bytes, stream);
+        if (args.splits > 1 && args.reduce_rows > 0)
+            return launch_linear_variant<KIND, EPI, SPLIT_CLUSTER>(act_map, weight_map, args, shared_bytes, stream);
+        if (args.splits > 1) return launch_linear_variant<KIND, EPI, SPLIT_GLOBAL>(act_map, weight_map, args, shared_bytes, stream);
     }
-    return launch_linear_variant<KIND, EPI, false>(act_map, weight_map, args, shared_bytes, stream);
+    return launch_linear_variant<KIND, EPI, SPLIT_NONE>(act_map, weight_map, args, shared_bytes, stream);
 }
 
 static bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointer) & 15u) == 0; }
@@ -1159,6 +1265,18 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         if (splits == 1 || d->workspace_bytes >= need) break;
         allow_split = false;
     }
+    // One token tile and the plain epilogue: on request K is cut across the CTAs of a cluster (no workspace needed).
+    args.reduce_rows = 0;
+    if (d->epilogue == B2_EPI_LINEAR && args.num_m_tiles == 1 && splits == 1 && (d->flags & B2_LINEAR_CLUSTER_SPLIT)) {
+        const int rows = (d->tokens + 31) / 32 * 32;
+        int cluster_tile = 0, cluster_splits = 1;
+        choose_cluster_split(d->kind, d->feature_tile, d->features, rows, args.num_kb, nvfp4, &cluster_tile, &cluster_splits);
+        if (cluster_tile != 0 && cluster_splits > 1) {
+            feature_tile = cluster_tile;
+            splits = cluster_splits;
+            args.reduce_rows = rows;
+        }
+    }
     args.tile_n = geglu ? 2 * feature_tile : feature_tile;
     args.num_n_tiles = (d->features + feature_tile - 1) / feature_tile;
     args.total_tiles = args.num_m_tiles * args.num_n_tiles;
@@ -1194,7 +1312,8 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         args.gelu_lo = d->gelu_lo;
         args.gelu_hi = d->gelu_hi;
     }
-    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 8 * MAX_RESIDENT_KB + 128 + 4 * (args.gelu_hi - args.gelu_lo);
+    const int reduce_bytes = args.reduce_rows > 0 ? (splits - 1) * args.reduce_rows * args.tile_n * 4 : 0;
+    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 8 * MAX_RESIDENT_KB + 128 + 4 * (args.gelu_hi - args.gelu_lo) + reduce_bytes;
     // Resident order (TileWalk): worth it when a CTA computes several feature tiles of its token tile and the
     // token tile of all K, the weight stages and (NVFP4) the token scales in TMEM all fit.
     int panel_bytes = 0;
@@ -1231,7 +1350,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     args.splits = splits;
     args.tickets = nullptr;
     args.partials = nullptr;
-    if (splits > 1) {
+    if (splits > 1 && args.reduce_rows == 0) {
         args.tickets = static_cast<unsigned int*>(d->workspace);
         args.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(d->workspace) + TICKET_BYTES);
     }

@@ -80,9 +80,23 @@ __device__ __forceinline__ uint4 apply_update(const NormArgs& a, const uint4& in
     return pack_bf16x8(v);
 }
 
+// Packed fp32 product and sum (`mul.rn.f32x2`, `add.rn.f32x2`).  Used where no product feeds a sum directly.
+__device__ __forceinline__ float2 mul2_rn(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ float2 add2_rn(float2 a, float2 b) {
+    float2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
 // y = bf16((r * inverse) * (1 + scale))  or  bf16((r * inverse) * (1 + m_scale) + m_shift) for the 8 packed
 // values of `r`, returned packed.  Two columns per instruction on the packed fp32 pipe (`mul.rn.f32x2`,
-// `add.rn.f32x2`: each lane rounds like the scalar operation, and nothing is fused).
+// `add.rn.f32x2`: each lane rounds like the scalar operation).
 __device__ __forceinline__ uint4 affine_vector(const NormArgs& a, int64_t modulation_base, int column, float inverse,
                                                const uint4& r) {
     const float* multiplier = a.modulation != nullptr ? a.modulation + modulation_base + column : a.scale + column;
@@ -96,12 +110,16 @@ __device__ __forceinline__ uint4 affine_vector(const NormArgs& a, int64_t modula
         const float4 s0 = *reinterpret_cast<const float4*>(shift), s1 = *reinterpret_cast<const float4*>(shift + 4);
         const float2 s[4] = {make_float2(s0.x, s0.y), make_float2(s0.z, s0.w), make_float2(s1.x, s1.y), make_float2(s1.z, s1.w)};
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-            y[i] = float2_to_bf16x2(__fadd2_rn(__fmul2_rn(__fmul2_rn(bf16x2_to_float2(words[i]), inverse2), __fadd2_rn(one, m[i])), s[i]));
+        for (int i = 0; i < 4; ++i) {
+            // the shift is added with the scalar intrinsic: a packed product followed by a packed sum came back
+            // fused (one rounding instead of two: 1 bf16 result in 30,000 differs), explicit `.rn` or not
+            const float2 scaled = mul2_rn(mul2_rn(bf16x2_to_float2(words[i]), inverse2), add2_rn(one, m[i]));
+            y[i] = float2_to_bf16x2(make_float2(__fadd_rn(scaled.x, s[i].x), __fadd_rn(scaled.y, s[i].y)));
+        }
     } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-            y[i] = float2_to_bf16x2(__fmul2_rn(__fmul2_rn(bf16x2_to_float2(words[i]), inverse2), __fadd2_rn(one, m[i])));
+            y[i] = float2_to_bf16x2(mul2_rn(mul2_rn(bf16x2_to_float2(words[i]), inverse2), add2_rn(one, m[i])));
     }
     return make_uint4(y[0], y[1], y[2], y[3]);
 }

@@ -277,4 +277,27 @@ __device__ __forceinline__ uint32_t idesc_nvf4(uint32_t m, uint32_t n) {
          | ((m >> 4) << 24);
 }
 
+// ---- thread-block clusters: rank, barrier, distributed shared memory ----------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+
+// Hardware barrier over every thread of every CTA of the cluster (release / acquire: shared-memory writes made
+// before the arrive, to any CTA of the cluster, are visible after the wait).  Each thread calls both, once per phase.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+
+// Address, in the cluster's shared window, of this CTA's shared address `local` in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+
+__device__ __forceinline__ void cluster_store_u4(uint32_t remote, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 }  // namespace b2

@@ -120,12 +120,19 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
 #define B2_LINEAR_STREAM_TOKENS 8 /* tuning aid: always load the token tile with every K stage.  By default a CTA keeps its
                                      128-token tile (all of K) and the token scales on chip whenever they fit and it computes
                                      several feature tiles of that token tile; results are identical either way. */
+#define B2_LINEAR_CLUSTER_SPLIT 16 /* opt-in: a plain-epilogue launch with one token tile (M <= 128) whose feature tiles leave most
+                                     SMs idle runs 2, 4 or 8 CTAs per tile as one thread-block cluster: each takes a K range, ranks 1..
+                                     write their fp32 partial sums into rank 0's shared memory (distributed shared memory), a
+                                     cluster barrier orders them, rank 0 adds them in rank order (deterministic) and runs the
+                                     epilogue.  No workspace.  Off by default: on B200 a cluster launch costs several microseconds
+                                     more than it saves at the shapes measured.  The fp32 summation order differs
+                                     from the unsplit launch. */
 
 typedef struct b2_linear_desc {
     int32_t kind;        /* B2_KIND_* */
     int32_t epilogue;    /* B2_EPI_* */
     int32_t out_format;  /* B2_OUT_* */
-    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_GEGLU_TRUE_DIV */
+    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_LINEAR_CLUSTER_SPLIT | B2_GEGLU_TRUE_DIV */
     int32_t tokens;      /* M: rows of the activation matrix */
     int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
     int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */

@@ -216,6 +216,37 @@ def test_split_k_is_deterministic_and_matches_oracle(device, kind, epilogue, tok
     assert_gemm_close(outputs[2], want)
 
 
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+@pytest.mark.parametrize("tokens,features,width", [(10, 2560, 1024), (10, 1024, 2048), (10, 1024, 4096), (80, 1024, 4096),
+                                                   (128, 2048, 2048), (1, 64, 1024), (33, 192, 8192)])
+def test_cluster_split_k(device, kind, tokens, features, width):
+    """One token tile, plain epilogue, few feature tiles, on request (B2_LINEAR_CLUSTER_SPLIT): K is cut across the
+    CTAs of a thread-block cluster and the partial sums meet in the leader's shared memory.  Same bits on every run
+    (fixed rank order), within the GEMM tolerance of the oracle; bias and residual are applied once, by the leader."""
+    host, dev = operands(kind, tokens, features, width, 7 + tokens + width, device)
+    bias = make_weight((1, features), 91, std=0.5).reshape(-1).to(torch.bfloat16).to(device)
+    residual = make_input((tokens, features), 92, outliers=False).to(device)
+
+    def run(flags, **extra):
+        out = torch.full((tokens + 1, features), float("nan"), device=device, dtype=torch.bfloat16)
+        status = torch.zeros(1, device=device, dtype=torch.int32)
+        K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out[:tokens],
+                 status=status, flags=flags, **extra, **dev)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.isnan(out[tokens]).all(), "wrote past the last token row"
+        return out[:tokens]
+
+    plain = run(N.LINEAR_CLUSTER_SPLIT)
+    assert torch.equal(plain, run(N.LINEAR_CLUSTER_SPLIT))
+    want = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+    assert_gemm_close(bits(plain), want)
+    assert_gemm_close(bits(run(0)), want)
+    # bias and residual in the leader's epilogue: exactly the separate bf16 adds on the launch's own plain result
+    full = run(N.LINEAR_CLUSTER_SPLIT, bias=bias, residual=residual)
+    assert torch.equal(full, (plain + bias) + residual)
+
+
 @pytest.mark.parametrize("kind,tokens,features,width", [("fp8", 256, 4304, 1152), ("fp8", 130, 384, 1024), ("nvfp4", 130, 384, 1024)])
 def test_bias_gelu_epilogue(device, kind, tokens, features, width):
     """out = gelu(x W^T + bias): bf16 against the oracle; e4m3 output identical to encoding the kernel's own

@@ -223,5 +223,9 @@ def test_calibrated_layer_record_with_smoothquant_scales(device, precision):
     plan = B200NormQuant(quantizer).plan(residual, bits=bits_, calibrated_scale=16.0 / (448 * (6 if bits_ == 4 else 1)), adaptive=False)
     encoded = plan.normalize(residual, scale=folded_scale)
     got = smoothed.project(residual.reshape(70, hidden_size), encoded)
-    error = (got.float() - expected.float()).norm() / expected.float().norm()
-    assert error < (0.06 if precision == "fp8" else 0.2), float(error)
+    # both plans carry their own quantisation noise: measure each against the unquantised MLP on the same input
+    n = normed.reshape(70, hidden_size).float()
+    hidden = torch.nn.functional.gelu(n @ gate_w.float().t(), approximate="tanh") * (n @ up_w.float().t())
+    exact = hidden @ down_w.float().t()
+    relative = lambda y: float((y.float() - exact).norm() / exact.norm())
+    assert relative(got) < max(2.0 * relative(expected), 0.05), (relative(got), relative(expected))
