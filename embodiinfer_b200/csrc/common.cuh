@@ -16,6 +16,39 @@ namespace b2 {
 
 int sm_count();
 
+// ---- programmatic dependent launch -----------------------------------------------------------------
+// Consecutive launches of this library on one stream may overlap head and tail: a kernel calls
+// `pdl_launch_dependents()` on entry (the next launch of the stream may then be scheduled as soon as every CTA of
+// this one has started) and `pdl_wait()` before it first touches memory that an earlier launch may have written
+// (it returns once all earlier launches have completed and their writes are visible).  What runs ahead of the wait
+// is each kernel's own set-up: barrier initialisation, tensor-memory allocation, descriptor prefetch, index
+// arithmetic.  Both calls are no-ops in a launch made without the attribute, and a launch that follows a kernel
+// which never triggers (any other library's) simply starts when that kernel has finished.  The reference uses the
+// same mechanism in its norm kernels (embodiinfer/backend/cuda/csrc/pdl.cuh).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Host: the launch attribute is set unless B2_PDL=0 is in the environment.
+constexpr bool PDL_DEFAULT = true;
+bool pdl_enabled();
+
+template <class... Parameters, class... Arguments>
+int launch_kernel(void (*kernel)(Parameters...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                  Arguments&&... arguments) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = pdl_enabled() ? 1 : 0;
+    const cudaError_t error = cudaLaunchKernelEx(&config, kernel, Parameters(arguments)...);
+    return error == cudaSuccess ? int(cudaGetLastError()) : int(error);
+}
+
 // ---- loads -----------------------------------------------------------------
 
 __device__ __forceinline__ uint4 ld_nc_u4(const uint4* pointer) {

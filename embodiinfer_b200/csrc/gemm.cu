@@ -26,6 +26,8 @@
 //
 // Every wait is bounded (ptx.cuh); an expired wait leaves a code in the status word.
 #include "common.cuh"
+
+#include <cstdlib>
 #include "ptx.cuh"
 
 #include <cuda.h>
@@ -441,6 +443,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     constexpr bool CLUSTER = SPLIT_MODE == SPLIT_CLUSTER;
     constexpr bool GEGLU = is_gated(EPI);
     constexpr bool USES_TABLE = EPI != EPI_LINEAR;
+    pdl_launch_dependents();
     extern __shared__ uint8_t shared_raw[];
     const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
     const int BN = args.tile_n;
@@ -501,6 +504,9 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     tc_fence_after_sync();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+    // Everything above is this launch's own set-up (the GELU table is a constant of the model); operands, scales,
+    // bias and residual may come from the launch before this one.
+    pdl_wait();
 
     bool failed = false;
     const int num_kb = args.num_kb;
@@ -1068,6 +1074,14 @@ int sm_count() {
     return counts[device];
 }
 
+bool pdl_enabled() {
+    static const bool enabled = [] {
+        const char* value = std::getenv("B2_PDL");
+        return value != nullptr ? (value[0] != '\0' && value[0] != '0') : PDL_DEFAULT;
+    }();
+    return enabled;
+}
+
 // Two accumulators fit (beside the NVFP4 scale columns)?
 static bool can_double_buffer(int kind, int tile_n, int scale_blocks = 2) {
     return 2 * tile_n <= (kind == B2_KIND_NVFP4 ? TMEM_COLUMNS - 2 * (TMEM_SFA_COLUMNS + 16 * scale_blocks) : TMEM_COLUMNS);
@@ -1175,8 +1189,8 @@ static int launch_linear_variant(const CUtensorMap& act_map, const CUtensorMap& 
         return error == cudaSuccess ? int(cudaGetLastError()) : int(error);
     }
     const int grid = items < sm_count() ? items : sm_count();
-    linear_kernel<KIND, EPI, SPLIT_MODE><<<grid, gemm_threads(EPI), shared_bytes, stream>>>(act_map, weight_map, args);
-    return int(cudaGetLastError());
+    return launch_kernel(linear_kernel<KIND, EPI, SPLIT_MODE>, dim3(unsigned(grid)), dim3(unsigned(gemm_threads(EPI))),
+                         size_t(shared_bytes), stream, act_map, weight_map, args);
 }
 
 template <int KIND, int EPI>

@@ -250,6 +250,8 @@ enum NormOrder { ORDER_LANES8 = 0, ORDER_STRIDED = 1 };
 template <int BITS, int ORDER>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_encode_block_kernel(const NormArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int VECTORS = ORDER == ORDER_LANES8 ? 1 : NORM_MAX_VECTORS;
     extern __shared__ __align__(16) uint8_t norm_shared[];
     __shared__ float partials[ORDER == ORDER_LANES8 ? 8 : NORM_THREADS];
@@ -321,6 +323,8 @@ constexpr int NORM_WARP_ROWS_THRESHOLD = 4096;     // below this a warp per row 
 template <int BITS, int VECTORS>
 __global__ void __launch_bounds__(NORM_ROWS_PER_BLOCK * 32)
 norm_encode_warp_kernel(const NormArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * NORM_ROWS_PER_BLOCK + (threadIdx.x >> 5);
     if (row >= a.rows) return;                                   // the whole warp leaves together
@@ -364,18 +368,19 @@ norm_encode_warp_kernel(const NormArgs a) {
 
 template <int BITS>
 static int launch_norm_bits(const NormArgs& a, cudaStream_t stream) {
+    int status;
     const bool lanes8 = a.columns == 1024 || a.columns == 2048;
     const int blocks = (a.rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK;
     if (lanes8 && a.rows >= NORM_WARP_ROWS_THRESHOLD && a.columns == 2048) {
-        norm_encode_warp_kernel<BITS, 8><<<blocks, NORM_ROWS_PER_BLOCK * 32, 0, stream>>>(a);
+        status = launch_kernel(norm_encode_warp_kernel<BITS, 8>, dim3(unsigned(blocks)), dim3(unsigned(NORM_ROWS_PER_BLOCK * 32)), size_t(0), stream, a);
     } else if (lanes8 && a.rows >= NORM_WARP_ROWS_THRESHOLD) {
-        norm_encode_warp_kernel<BITS, 4><<<blocks, NORM_ROWS_PER_BLOCK * 32, 0, stream>>>(a);
+        status = launch_kernel(norm_encode_warp_kernel<BITS, 4>, dim3(unsigned(blocks)), dim3(unsigned(NORM_ROWS_PER_BLOCK * 32)), size_t(0), stream, a);
     } else if (lanes8) {
-        norm_encode_block_kernel<BITS, ORDER_LANES8><<<a.rows, a.columns / 8, 0, stream>>>(a);
+        status = launch_kernel(norm_encode_block_kernel<BITS, ORDER_LANES8>, dim3(unsigned(a.rows)), dim3(unsigned(a.columns / 8)), size_t(0), stream, a);
     } else {
-        norm_encode_block_kernel<BITS, ORDER_STRIDED><<<a.rows, NORM_THREADS, size_t(a.columns) * 2, stream>>>(a);
+        status = launch_kernel(norm_encode_block_kernel<BITS, ORDER_STRIDED>, dim3(unsigned(a.rows)), dim3(unsigned(NORM_THREADS)), size_t(size_t(a.columns) * 2), stream, a);
     }
-    return cudaGetLastError() == cudaSuccess ? B2_OK : B2_E_DRIVER;
+    return status == 0 ? B2_OK : B2_E_DRIVER;
 }
 
 int launch_norm_quant(const b2_norm_desc* d, cudaStream_t stream) {
@@ -442,6 +447,8 @@ __device__ __forceinline__ void layer_sums_of_vector(const uint4& packed, float&
 template <int BITS, int WARPS, bool WARP_ROW>
 __global__ void __launch_bounds__(WARP_ROW ? NORM_ROWS_PER_BLOCK * 32 : WARPS * 32)
 layer_norm_encode_kernel(const LayerNormArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int VECTORS = WARP_ROW ? WARPS : 1;
     __shared__ float block_totals[2][8];
     const int lane = threadIdx.x & 31;
@@ -518,16 +525,17 @@ layer_norm_encode_kernel(const LayerNormArgs a) {
 
 template <int BITS>
 static int launch_layer_norm_bits(const LayerNormArgs& a, cudaStream_t stream) {
+    int status;
     const int blocks = (a.rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK;
     const bool narrow = a.columns <= 1152;                       // the reference's 160-thread block (norm_quant.cu:681)
     if (a.rows >= NORM_WARP_ROWS_THRESHOLD) {
-        if (narrow) layer_norm_encode_kernel<BITS, 5, true><<<blocks, NORM_ROWS_PER_BLOCK * 32, 0, stream>>>(a);
-        else layer_norm_encode_kernel<BITS, 8, true><<<blocks, NORM_ROWS_PER_BLOCK * 32, 0, stream>>>(a);
+        if (narrow) status = launch_kernel(layer_norm_encode_kernel<BITS, 5, true>, dim3(unsigned(blocks)), dim3(unsigned(NORM_ROWS_PER_BLOCK * 32)), size_t(0), stream, a);
+        else status = launch_kernel(layer_norm_encode_kernel<BITS, 8, true>, dim3(unsigned(blocks)), dim3(unsigned(NORM_ROWS_PER_BLOCK * 32)), size_t(0), stream, a);
     } else {
-        if (narrow) layer_norm_encode_kernel<BITS, 5, false><<<a.rows, 160, 0, stream>>>(a);
-        else layer_norm_encode_kernel<BITS, 8, false><<<a.rows, 256, 0, stream>>>(a);
+        if (narrow) status = launch_kernel(layer_norm_encode_kernel<BITS, 5, false>, dim3(unsigned(a.rows)), dim3(unsigned(160)), size_t(0), stream, a);
+        else status = launch_kernel(layer_norm_encode_kernel<BITS, 8, false>, dim3(unsigned(a.rows)), dim3(unsigned(256)), size_t(0), stream, a);
     }
-    return cudaGetLastError() == cudaSuccess ? B2_OK : B2_E_DRIVER;
+    return status == 0 ? B2_OK : B2_E_DRIVER;
 }
 
 int launch_layer_norm_quant(const void* input, const void* update, const void* weight, const void* bias, void* residual,
@@ -572,6 +580,8 @@ constexpr int BHSD_THREADS = 256;
 template <int BITS>
 __global__ void __launch_bounds__(BHSD_THREADS)
 bhsd_encode_kernel(const BhsdArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int vectors_per_row = a.columns >> 3;
     const int64_t total = int64_t(a.batch) * a.tokens * vectors_per_row;
     const int64_t rounded = (total + 31) & ~int64_t(31);        // whole warps enter the loop: NVFP4 pairs exchange maxima
@@ -610,10 +620,11 @@ int launch_bhsd_quant(const void* input, void* output, void* scales, void* block
     const int64_t total = int64_t(batch) * tokens * (a.columns >> 3);
     const int64_t wanted = (total + BHSD_THREADS - 1) / BHSD_THREADS;
     const int blocks = int(wanted < int64_t(sm_count()) * 16 ? wanted : int64_t(sm_count()) * 16);
-    if (bits == 16) bhsd_encode_kernel<16><<<blocks, BHSD_THREADS, 0, stream>>>(a);
-    else if (bits == 8) bhsd_encode_kernel<8><<<blocks, BHSD_THREADS, 0, stream>>>(a);
-    else bhsd_encode_kernel<4><<<blocks, BHSD_THREADS, 0, stream>>>(a);
-    return cudaGetLastError() == cudaSuccess ? B2_OK : B2_E_DRIVER;
+    int status;
+    if (bits == 16) status = launch_kernel(bhsd_encode_kernel<16>, dim3(unsigned(blocks)), dim3(unsigned(BHSD_THREADS)), size_t(0), stream, a);
+    else if (bits == 8) status = launch_kernel(bhsd_encode_kernel<8>, dim3(unsigned(blocks)), dim3(unsigned(BHSD_THREADS)), size_t(0), stream, a);
+    else status = launch_kernel(bhsd_encode_kernel<4>, dim3(unsigned(blocks)), dim3(unsigned(BHSD_THREADS)), size_t(0), stream, a);
+    return status == 0 ? B2_OK : B2_E_DRIVER;
 }
 
 }  // namespace b2

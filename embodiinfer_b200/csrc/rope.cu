@@ -19,6 +19,8 @@ rope_split_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict
                   __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out,
                   int batch, int tokens, int heads, int kv_heads, int head_dim, int64_t factor_batch_stride,
                   int kv_capacity, int kv_offset) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int half = head_dim >> 1;
     const int vectors_per_half = half >> 3;                       // 8 elements per thread
     const int total_heads = heads + 2 * kv_heads;                 // q heads, k heads, v heads of one token
@@ -78,11 +80,11 @@ int launch_rope_split(const void* qkv, const void* sine, const void* cosine, voi
     const int64_t wanted = (total + ROPE_THREADS - 1) / ROPE_THREADS;
     const int64_t cap = int64_t(sm_count()) * 8;
     const int grid = int(wanted < 1 ? 1 : (wanted < cap ? wanted : cap));
-    rope_split_kernel<<<grid, ROPE_THREADS, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(qkv), static_cast<const float*>(sine), static_cast<const float*>(cosine),
+    const int status = launch_kernel(rope_split_kernel, dim3(unsigned(grid)), dim3(unsigned(ROPE_THREADS)), size_t(0), stream,
+                                     static_cast<const __nv_bfloat16*>(qkv), static_cast<const float*>(sine), static_cast<const float*>(cosine),
         static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out), static_cast<__nv_bfloat16*>(v_out), batch, tokens,
         heads, kv_heads, head_dim, factor_batch_stride, kv_capacity, kv_offset);
-    return int(cudaGetLastError());
+    return status;
 }
 
 }  // namespace b2

@@ -120,7 +120,7 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
 #define B2_LINEAR_STREAM_TOKENS 8 /* tuning aid: always load the token tile with every K stage.  By default a CTA keeps its
                                      128-token tile (all of K) and the token scales on chip whenever they fit and it computes
                                      several feature tiles of that token tile; results are identical either way. */
-#define B2_LINEAR_CLUSTER_SPLIT 16 /* opt-in: a plain-epilogue launch with one token tile (M <= 128) whose feature tiles leave most
+#define B2_LINEAR_CLUSTER_SPLIT 32 /* opt-in: a plain-epilogue launch with one token tile (M <= 128) whose feature tiles leave most
                                      SMs idle runs 2, 4 or 8 CTAs per tile as one thread-block cluster: each takes a K range, ranks 1..
                                      write their fp32 partial sums into rank 0's shared memory (distributed shared memory), a
                                      cluster barrier orders them, rank 0 adds them in rank order (deterministic) and runs the
