@@ -29,6 +29,8 @@ constexpr int QUANT_THREADS = 256;
 __global__ void __launch_bounds__(QUANT_THREADS)
 tensor_scale_kernel(const uint4* __restrict__ input, int64_t vectors, const __nv_bfloat16* __restrict__ tail,
                     int tail_count, float bound, int flags, unsigned int* scratch, float* scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     float maximum = 0.0f;
     const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
     for (int64_t index = int64_t(blockIdx.x) * QUANT_THREADS + threadIdx.x; index < vectors; index += stride) {
@@ -68,6 +70,8 @@ __global__ void __launch_bounds__(QUANT_THREADS)
 fp8_encode_kernel(const uint4* __restrict__ input, uint2* __restrict__ output, int64_t vectors,
                   const __nv_bfloat16* __restrict__ tail_in, uint8_t* __restrict__ tail_out, int tail_count,
                   const float* __restrict__ scale_pointer, int flags) {
+    pdl_launch_dependents();
+    pdl_wait();
     float scale_value = __ldg(scale_pointer);
     if (!SPEC_C && (flags & B2_DIVISOR_BF16)) scale_value = __bfloat162float(__float2bfloat16(scale_value));
     const ExactDivider scale(scale_value);
@@ -93,6 +97,8 @@ template <bool SPEC_C>
 __global__ void __launch_bounds__(QUANT_THREADS)
 fp8_encode_wide_kernel(const uint8_t* __restrict__ input, uint4* __restrict__ output, int64_t vectors,
                        const float* __restrict__ scale_pointer, int flags) {
+    pdl_launch_dependents();
+    pdl_wait();
     float scale_value = __ldg(scale_pointer);
     if (!SPEC_C && (flags & B2_DIVISOR_BF16)) scale_value = __bfloat162float(__float2bfloat16(scale_value));
     const ExactDivider scale(scale_value);
@@ -125,6 +131,8 @@ __global__ void __launch_bounds__(QUANT_THREADS)
 nvfp4_encode_kernel(const uint4* __restrict__ input, uint32_t* __restrict__ output, uint8_t* __restrict__ scales,
                     uint8_t* __restrict__ blocked, const float* __restrict__ global_pointer, int rows, int columns,
                     int flags) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int vectors_per_row = columns >> 3;
     const int blocks_per_row = columns >> 4;
     const int column_tiles = (blocks_per_row + 3) >> 2;
@@ -185,6 +193,8 @@ __global__ void __launch_bounds__(QUANT_THREADS)
 nvfp4_encode_wide_kernel(const uint8_t* __restrict__ input, uint8_t* __restrict__ output, uint8_t* __restrict__ scales,
                          uint8_t* __restrict__ blocked, const float* __restrict__ global_pointer, int rows, int columns,
                          int flags) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int blocks_per_row = columns >> 4;
     const int column_tiles = (blocks_per_row + 3) >> 2;
     const int items_per_row = blocks_per_row / BLOCKS;                 // one item = BLOCKS adjacent blocks of one row
@@ -266,10 +276,10 @@ int launch_fp8_encode(const void* input, void* output, const void* scale, int64_
         const int64_t wide = count >> 4;
         const int grid = grid_for(wide, QUANT_THREADS * 2);
         if (flags & B2_SPEC_C)
-            fp8_encode_wide_kernel<true><<<grid, QUANT_THREADS, 0, stream>>>(
+            launch_kernel(fp8_encode_wide_kernel<true>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, 
                 static_cast<const uint8_t*>(input), static_cast<uint4*>(output), wide, static_cast<const float*>(scale), flags);
         else
-            fp8_encode_wide_kernel<false><<<grid, QUANT_THREADS, 0, stream>>>(
+            launch_kernel(fp8_encode_wide_kernel<false>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, 
                 static_cast<const uint8_t*>(input), static_cast<uint4*>(output), wide, static_cast<const float*>(scale), flags);
         const cudaError_t error = cudaGetLastError();
         if (error != cudaSuccess || (count & 15) == 0) return int(error);
@@ -283,11 +293,11 @@ int launch_fp8_encode(const void* input, void* output, const void* scale, int64_
     const int tail = int(count & 7);
     const int grid = grid_for(vectors, QUANT_THREADS * 2);
     if (flags & B2_SPEC_C)
-        fp8_encode_kernel<true><<<grid, QUANT_THREADS, 0, stream>>>(
+        launch_kernel(fp8_encode_kernel<true>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, 
             static_cast<const uint4*>(input), static_cast<uint2*>(output), vectors, base + vectors * 8,
             out_base + vectors * 8, tail, static_cast<const float*>(scale), flags);
     else
-        fp8_encode_kernel<false><<<grid, QUANT_THREADS, 0, stream>>>(
+        launch_kernel(fp8_encode_kernel<false>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, 
             static_cast<const uint4*>(input), static_cast<uint2*>(output), vectors, base + vectors * 8,
             out_base + vectors * 8, tail, static_cast<const float*>(scale), flags);
     return int(cudaGetLastError());
@@ -304,22 +314,22 @@ int launch_nvfp4_encode(const void* input, void* output, void* scales, void* blo
         uint8_t* tiled = static_cast<uint8_t*>(blocked);
         const float* g = static_cast<const float*>(global);
         if (flags & B2_SPEC_C) {
-            if (pairs) nvfp4_encode_wide_kernel<true, 2><<<grid, QUANT_THREADS, 0, stream>>>(in, out, row_major, tiled, g, rows, columns, flags);
-            else nvfp4_encode_wide_kernel<true, 1><<<grid, QUANT_THREADS, 0, stream>>>(in, out, row_major, tiled, g, rows, columns, flags);
+            if (pairs) launch_kernel(nvfp4_encode_wide_kernel<true, 2>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, in, out, row_major, tiled, g, rows, columns, flags);
+            else launch_kernel(nvfp4_encode_wide_kernel<true, 1>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, in, out, row_major, tiled, g, rows, columns, flags);
         } else {
-            if (pairs) nvfp4_encode_wide_kernel<false, 2><<<grid, QUANT_THREADS, 0, stream>>>(in, out, row_major, tiled, g, rows, columns, flags);
-            else nvfp4_encode_wide_kernel<false, 1><<<grid, QUANT_THREADS, 0, stream>>>(in, out, row_major, tiled, g, rows, columns, flags);
+            if (pairs) launch_kernel(nvfp4_encode_wide_kernel<false, 2>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, in, out, row_major, tiled, g, rows, columns, flags);
+            else launch_kernel(nvfp4_encode_wide_kernel<false, 1>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, in, out, row_major, tiled, g, rows, columns, flags);
         }
         return int(cudaGetLastError());
     }
     const int64_t total = int64_t(rows) * (columns >> 3);
     const int grid = grid_for(total, QUANT_THREADS * 2);
     if (flags & B2_SPEC_C)
-        nvfp4_encode_kernel<true><<<grid, QUANT_THREADS, 0, stream>>>(
+        launch_kernel(nvfp4_encode_kernel<true>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, 
             static_cast<const uint4*>(input), static_cast<uint32_t*>(output), static_cast<uint8_t*>(scales),
             static_cast<uint8_t*>(blocked), static_cast<const float*>(global), rows, columns, flags);
     else
-        nvfp4_encode_kernel<false><<<grid, QUANT_THREADS, 0, stream>>>(
+        launch_kernel(nvfp4_encode_kernel<false>, dim3(unsigned(grid)), dim3(unsigned(QUANT_THREADS)), size_t(0), stream, 
             static_cast<const uint4*>(input), static_cast<uint32_t*>(output), static_cast<uint8_t*>(scales),
             static_cast<uint8_t*>(blocked), static_cast<const float*>(global), rows, columns, flags);
     return int(cudaGetLastError());
