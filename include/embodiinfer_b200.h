@@ -125,7 +125,7 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
                                      write their fp32 partial sums into rank 0's shared memory (distributed shared memory), a
                                      cluster barrier orders them, rank 0 adds them in rank order (deterministic) and runs the
                                      epilogue.  No workspace.  Off by default: on B200 a cluster launch costs several microseconds
-                                     more than it saves at the shapes measured.  The fp32 summation order differs
+                                     more than it saves at the shapes measured (10x2560x1024 FP8: 9.2 vs 5.4 us).  The fp32 summation order differs
                                      from the unsplit launch. */
 
 typedef struct b2_linear_desc {
