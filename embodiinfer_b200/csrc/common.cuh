@@ -164,6 +164,10 @@ struct ExactDivider {
         fast = (bits >> 31) == 0 && exponent >= 67u && exponent <= 187u && (bits & 0x7fffffu) != 0x7fffffu;
         reciprocal = fast ? __frcp_rn(b) : 0.0f;
     }
+    // From a precomputed (divisor, reciprocal) pair as the constructor above would leave them: the reciprocal is
+    // 0.0 exactly when the divisor is outside the range of the short path.
+    __device__ __forceinline__ explicit ExactDivider(float2 entry) : divisor(entry.x), reciprocal(entry.y), fast(entry.y != 0.0f) {}
+    __device__ __forceinline__ float2 entry() const { return make_float2(divisor, reciprocal); }
     // The residual step alone, for callers that have already established: `fast`, |a * reciprocal| finite.
     // copysign restores the sign of a zero quotient (and changes nothing else: the divisor is positive).
     __device__ __forceinline__ float unchecked(float a) const {
@@ -342,13 +346,24 @@ __device__ __forceinline__ uint32_t nvfp4_encode_x8(const float (&v)[8], const E
     return word;
 }
 
+// The dividers by global * e4m3(code) for the 127 non-negative finite e4m3 codes (code 127 is NaN: its entry takes
+// the general path like the constructor would).  Called by the first 128 threads of a block; the caller
+// synchronises the block afterwards.
+__device__ __forceinline__ void fill_denominator_table(float2* table, float global) {
+    if (threadIdx.x < 128) table[threadIdx.x] = ExactDivider(__fmul_rn(global, e4m3_to_float(uint8_t(threadIdx.x)))).entry();
+}
+
 // One 16-element block held as eight bf16x2 words -> 16 nibbles (two words) and the block's e4m3 scale.
+// `denominators`: nullptr, or this launch's table (shared memory, 128 entries, see `fill_denominator_table`) of the
+// dividers by global * e4m3(code): the block's divider is then two loads instead of a conversion, a product and a
+// reciprocal.
 template <bool SPEC_C>
 __device__ __forceinline__ uint2 nvfp4_encode_block(const uint32_t (&w)[8], float global, const ExactDivider& by_global,
-                                                    int flags, uint8_t& scale_code) {
+                                                    int flags, uint8_t& scale_code, const float2* denominators = nullptr) {
     const float maximum = abs_max_bf16_words(w);
     scale_code = nvfp4_block_scale<SPEC_C>(maximum, by_global, flags);
-    const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
+    const ExactDivider denominator = denominators != nullptr ? ExactDivider(denominators[scale_code & 127u])
+                                                            : ExactDivider(__fmul_rn(global, e4m3_to_float(scale_code)));
     uint2 codes;
     if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f) {
         codes.x = nvfp4_encode_words_short<SPEC_C>(w[0], w[1], w[2], w[3], denominator);

@@ -140,12 +140,14 @@ struct Encoder {
     float global, reciprocal;
     bool divide;
     ExactDivider by_global;
-    __device__ __forceinline__ explicit Encoder(const NormArgs& a)
+    const float2* denominators = nullptr;    // NVFP4: the block's table of dividers by global * e4m3(code), in shared memory
+    __device__ __forceinline__ Encoder(const NormArgs& a, const float2* table)
         : global(BITS == 16 ? 1.0f : *a.global), reciprocal(rounded_reciprocal(global)), divide(a.mean != nullptr),
-          by_global(rounded_product(6.0f, global)) {}
+          by_global(rounded_product(6.0f, global)), denominators(BITS == 4 ? table : nullptr) {}
     // Scale (and, for e4m3, the multiplier) given by value, as the layer-norm entry points of the reference take them.
-    __device__ __forceinline__ Encoder(float global_scale, float multiplier)
-        : global(global_scale), reciprocal(multiplier), divide(false), by_global(rounded_product(6.0f, global_scale)) {}
+    __device__ __forceinline__ Encoder(float global_scale, float multiplier, const float2* table)
+        : global(global_scale), reciprocal(multiplier), divide(false), by_global(rounded_product(6.0f, global_scale)),
+          denominators(BITS == 4 ? table : nullptr) {}
 
     // `y`: eight bf16 values, packed.  Every lane of the warp calls this (the NVFP4 block maximum is exchanged
     // with the neighbouring lane); lanes without a vector pass valid = false.
@@ -180,7 +182,8 @@ struct Encoder {
             maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
             if (!valid) return;
             const uint8_t code = nvfp4_block_scale<true>(maximum, by_global, 0);
-            const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(code)));
+            const ExactDivider denominator = denominators != nullptr ? ExactDivider(denominators[code & 127u])
+                                                                    : ExactDivider(__fmul_rn(global, e4m3_to_float(code)));
             uint32_t codes;
             if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f) {
                 codes = nvfp4_encode_words_short<true>(words[0], words[1], words[2], words[3], denominator);
@@ -252,6 +255,11 @@ __global__ void __launch_bounds__(NORM_THREADS)
 norm_encode_block_kernel(const NormArgs a) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float2 denominator_table[BITS == 4 ? 128 : 1];
+    if (BITS == 4) {
+        fill_denominator_table(denominator_table, *a.global);
+        __syncthreads();
+    }
     constexpr int VECTORS = ORDER == ORDER_LANES8 ? 1 : NORM_MAX_VECTORS;
     extern __shared__ __align__(16) uint8_t norm_shared[];
     __shared__ float partials[ORDER == ORDER_LANES8 ? 8 : NORM_THREADS];
@@ -299,7 +307,7 @@ norm_encode_block_kernel(const NormArgs a) {
         inverse = rsqrtf(__fadd_rn(__fmul_rn(total, __fdiv_rn(1.0f, float(a.columns))), 1.0e-6f));
     }
     if (a.inverse != nullptr && threadIdx.x == 0) a.inverse[row] = inverse;
-    const Encoder<BITS> encoder(a);
+    const Encoder<BITS> encoder(a, denominator_table);
     const bool write_gate = a.gate != nullptr && row == batch * a.tokens;
 #pragma unroll
     for (int i = 0; i < VECTORS; ++i) {
@@ -325,6 +333,11 @@ __global__ void __launch_bounds__(NORM_ROWS_PER_BLOCK * 32)
 norm_encode_warp_kernel(const NormArgs a) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float2 denominator_table[BITS == 4 ? 128 : 1];
+    if (BITS == 4) {
+        fill_denominator_table(denominator_table, *a.global);
+        __syncthreads();
+    }
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * NORM_ROWS_PER_BLOCK + (threadIdx.x >> 5);
     if (row >= a.rows) return;                                   // the whole warp leaves together
@@ -355,7 +368,7 @@ norm_encode_warp_kernel(const NormArgs a) {
         inverse = rsqrtf(__fadd_rn(__fmul_rn(combine_warp_totals(totals), __fdiv_rn(1.0f, float(a.columns))), 1.0e-6f));
     }
     if (a.inverse != nullptr && lane == 0) a.inverse[row] = inverse;
-    const Encoder<BITS> encoder(a);
+    const Encoder<BITS> encoder(a, denominator_table);
     const bool write_gate = a.gate != nullptr && row == batch * a.tokens;
 #pragma unroll
     for (int i = 0; i < VECTORS; ++i) {
@@ -449,6 +462,11 @@ __global__ void __launch_bounds__(WARP_ROW ? NORM_ROWS_PER_BLOCK * 32 : WARPS * 
 layer_norm_encode_kernel(const LayerNormArgs a) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float2 denominator_table[BITS == 4 ? 128 : 1];
+    if (BITS == 4) {
+        fill_denominator_table(denominator_table, a.scale_value);
+        __syncthreads();
+    }
     constexpr int VECTORS = WARP_ROW ? WARPS : 1;
     __shared__ float block_totals[2][8];
     const int lane = threadIdx.x & 31;
@@ -505,7 +523,7 @@ layer_norm_encode_kernel(const LayerNormArgs a) {
         a.statistics[2 * row] = mean;
         a.statistics[2 * row + 1] = deviation;
     }
-    const Encoder<BITS> encoder(BITS == 4 ? a.scale_value : 1.0f, a.scale_value);
+    const Encoder<BITS> encoder(BITS == 4 ? a.scale_value : 1.0f, a.scale_value, denominator_table);
 #pragma unroll
     for (int i = 0; i < VECTORS; ++i) {
         const int column = (WARP_ROW ? lane + 32 * i : int(threadIdx.x)) * 8;
@@ -582,10 +600,15 @@ __global__ void __launch_bounds__(BHSD_THREADS)
 bhsd_encode_kernel(const BhsdArgs a) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float2 denominator_table[BITS == 4 ? 128 : 1];
+    if (BITS == 4) {
+        fill_denominator_table(denominator_table, a.scale_value);
+        __syncthreads();
+    }
     const int vectors_per_row = a.columns >> 3;
     const int64_t total = int64_t(a.batch) * a.tokens * vectors_per_row;
     const int64_t rounded = (total + 31) & ~int64_t(31);        // whole warps enter the loop: NVFP4 pairs exchange maxima
-    const Encoder<BITS> encoder(BITS == 4 ? a.scale_value : 1.0f, a.scale_value);
+    const Encoder<BITS> encoder(BITS == 4 ? a.scale_value : 1.0f, a.scale_value, denominator_table);
     for (int64_t index = int64_t(blockIdx.x) * BHSD_THREADS + threadIdx.x; index < rounded; index += int64_t(gridDim.x) * BHSD_THREADS) {
         const bool valid = index < total;
         const int row = int(index / vectors_per_row);           // b * tokens + s

@@ -201,29 +201,55 @@ nvfp4_encode_wide_kernel(const uint8_t* __restrict__ input, uint8_t* __restrict_
     const int64_t total = int64_t(rows) * items_per_row;
     const float global = __ldg(global_pointer);
     const ExactDivider by_global(SPEC_C ? __fmul_rn(6.0f, global) : global);
+    __shared__ float2 denominators[128];
+    fill_denominator_table(denominators, global);
+    __syncthreads();
     const bool whole_words = (blocks_per_row & 3) == 0;
     constexpr int LANES_PER_WORD = 4 / BLOCKS;
     const int64_t stride = int64_t(gridDim.x) * QUANT_THREADS;
     const int lane = threadIdx.x & 31;
     // warp-uniform loop: `total` is a multiple of LANES_PER_WORD whenever whole words are stored, so the
     // lanes of a scale word are active together
+    // (row, item in row) of this thread's item, advanced by the grid stride without a division per item
+    const int64_t first_index = int64_t(blockIdx.x) * QUANT_THREADS + threadIdx.x;
+    int row = int(first_index / items_per_row);
+    int item_in_row = int(first_index - int64_t(row) * items_per_row);
+    const int row_step = int(stride / items_per_row), item_step = int(stride - int64_t(row_step) * items_per_row);
+    // the loads of the next item are issued before the arithmetic of the current one (one item of look-ahead)
+    uint32_t ahead[BLOCKS][8];
+    {
+        const int64_t first = first_index;
+        if (first < total) {
+#pragma unroll
+            for (int b = 0; b < BLOCKS; ++b) ld_nc_u8(input + (first * BLOCKS + b) * 32, ahead[b]);
+        }
+    }
     for (int64_t warp_base = int64_t(blockIdx.x) * QUANT_THREADS + (threadIdx.x - lane); warp_base < total;
-         warp_base += stride) {
+         warp_base += stride, row += row_step, item_in_row += item_step) {
+        if (item_in_row >= items_per_row) {
+            item_in_row -= items_per_row;
+            ++row;
+        }
         const int64_t index = warp_base + lane;
         const bool active = index < total;
         const unsigned int mask = __ballot_sync(0xffffffffu, active);
         if (!active) continue;
         uint32_t w[BLOCKS][8];
 #pragma unroll
-        for (int b = 0; b < BLOCKS; ++b) ld_nc_u8(input + (index * BLOCKS + b) * 32, w[b]);
+        for (int b = 0; b < BLOCKS; ++b)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[b][i] = ahead[b][i];
+        if (index + stride < total) {
+#pragma unroll
+            for (int b = 0; b < BLOCKS; ++b) ld_nc_u8(input + ((index + stride) * BLOCKS + b) * 32, ahead[b]);
+        }
         uint8_t code[BLOCKS];
         uint2 codes[BLOCKS];
 #pragma unroll
-        for (int b = 0; b < BLOCKS; ++b) codes[b] = nvfp4_encode_block<SPEC_C>(w[b], global, by_global, flags, code[b]);
+        for (int b = 0; b < BLOCKS; ++b) codes[b] = nvfp4_encode_block<SPEC_C>(w[b], global, by_global, flags, code[b], denominators);
         if (BLOCKS == 2) *reinterpret_cast<uint4*>(output + index * 16) = make_uint4(codes[0].x, codes[0].y, codes[BLOCKS - 1].x, codes[BLOCKS - 1].y);
         else *reinterpret_cast<uint2*>(output + index * 8) = codes[0];
-        const int row = total <= 0x7fffffff ? int(uint32_t(index) / uint32_t(items_per_row)) : int(index / items_per_row);
-        const int block = int(index - int64_t(row) * items_per_row) * BLOCKS;
+        const int block = item_in_row * BLOCKS;
         if (whole_words) {
             const int base = lane & ~(LANES_PER_WORD - 1);
             unsigned int mine = code[0];
