@@ -53,7 +53,7 @@ constexpr int A_TILE_BYTES = TILE_TOKENS * STAGE_K_BYTES;
 constexpr int SCALE_ATOM_BYTES = 512;              // 128 rows x 4 blocks of 16
 constexpr int SCALE_ATOMS_PER_STAGE = 4;           // 4 x 64 elements = 256 e2m1 = 128 bytes of K
 
-constexpr int MAX_STAGES = 8;
+constexpr int MAX_STAGES = 16;
 constexpr int TMEM_COLUMNS = 512;
 // NVFP4 scale factors live in TMEM columns 384..479: two sets (alternating by K slice, so the copies for
 // one slice never overwrite columns an MMA of the previous slice may still be reading), each 16 columns
@@ -95,6 +95,9 @@ struct KernelArgs {
     uint8_t* out_scales;
     uint8_t* out_blocked;
     unsigned int* status;
+    int a_box_bytes;             // bytes of the token box of one K stage: 128 rows, or fewer (a multiple of 8) when the launch has
+                                 // one token tile with fewer tokens -- the rows beyond the box are whatever shared memory holds,
+                                 // they only feed accumulator rows that are never stored
     int reduce_rows;             // cluster split: token rows (a multiple of 32) of a partial-sum slot in the leader's shared memory
     unsigned int* tickets;       // split-K: one arrival counter per tile (zero between launches)
     float* partials;             // split-K: [tile][split][128][tile_n] fp32
@@ -451,7 +454,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     // shared memory: [resident token tile: num_kb x 16 KB][resident token scales: num_kb x 2 KB]
     //                [stages x (token tile unless resident | weight tile)][stages x scale atoms][barriers][GELU table]
     const bool resident = args.resident != 0;
-    const uint32_t a_stage_bytes = resident ? 0u : uint32_t(A_TILE_BYTES);
+    const uint32_t a_stage_bytes = resident ? 0u : uint32_t(args.a_box_bytes);
     const uint32_t stage_bytes = a_stage_bytes + uint32_t(BN) * STAGE_K_BYTES;
     constexpr uint32_t SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;     // one operand's atoms of a K stage
     const uint32_t token_part_bytes = resident ? 0u : SCALE_PART_BYTES;                 // offset of the feature atoms in a scale stage
@@ -512,11 +515,13 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     const int num_kb = args.num_kb;
     const int last_kb_mmas = ((args.k_bytes - (num_kb - 1) * STAGE_K_BYTES) + 31) / 32;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------- TMA producer
-        // (all lanes run the loop; one elected lane issues the copies; like the MMA role it is specialised
-        // on the launch-wide choices and entered once)
-        auto producer_role = [&](auto resident_tag, auto prefetch_tag) {
+    // ------------------------------------------------------------- TMA producer
+    // (all lanes run the loop; one elected lane issues the copies; like the MMA role it is specialised
+    // on the launch-wide choices and entered once)
+    // Launches whose CTAs have a single tile each are bound by how fast this one warp issues the copies of a stage
+    // (a few hundred cycles for the barrier handling and the copy instructions), so they skip the L2 prefetches.
+    const bool prefetch_ahead = args.splits == 1 && args.total_tiles > int(gridDim.x);
+    auto producer_role = [&](auto resident_tag, auto prefetch_tag) {
             constexpr bool RESIDENT = decltype(resident_tag)::value, PREFETCH = decltype(prefetch_tag)::value;
             int stage = 0;
             uint32_t phase = 0;
@@ -645,11 +650,14 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             if (panel_loaded)
                 for (int kb = 0; kb < num_kb; ++kb) mbar_wait(panel_bar + 8 * kb, 0u, drain_failed, args.status, STATUS_WAIT_DRAIN);
         };
-        using Yes = std::true_type;
-        using No = std::false_type;
-        // (split K ranges are a few stages long: nothing to prefetch ahead of)
-        if (resident) { if (args.splits == 1) producer_role(Yes{}, Yes{}); else producer_role(Yes{}, No{}); }
-        else { if (args.splits == 1) producer_role(No{}, Yes{}); else producer_role(No{}, No{}); }
+    using Yes = std::true_type;
+    using No = std::false_type;
+    if (warp == 0) {
+        // (split K ranges are a few stages long: nothing to prefetch ahead of; nor is there when every CTA has a
+        // single tile: its loads are all issued within a few stages anyway, and each prefetch is one more
+        // instruction on the warp whose issue rate bounds the small launches)
+        if (resident) { if (prefetch_ahead) producer_role(Yes{}, Yes{}); else producer_role(Yes{}, No{}); }
+        else { if (prefetch_ahead) producer_role(No{}, Yes{}); else producer_role(No{}, No{}); }
         if (CLUSTER) { cluster_arrive(); cluster_wait(); }        // every thread of the cluster takes part, once
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
@@ -1318,7 +1326,13 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     args.status = static_cast<unsigned int*>(d->status);
 
     constexpr int SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
-    int stage_bytes = A_TILE_BYTES + args.tile_n * STAGE_K_BYTES;
+    // A launch with one token tile loads only the token rows it has (rounded up to the 8-row swizzle atom): a K stage
+    // is then mostly weights, more stages fit, and more of a long K is in flight at once.  The MMA still reads 128
+    // rows, so the stage ring is followed by padding that keeps those reads inside the allocation.
+    const int box_rows = args.num_m_tiles == 1 ? (d->tokens + 7) / 8 * 8 : TILE_TOKENS;
+    args.a_box_bytes = box_rows * STAGE_K_BYTES;
+    const int ring_padding = A_TILE_BYTES - args.a_box_bytes;
+    int stage_bytes = args.a_box_bytes + args.tile_n * STAGE_K_BYTES;
     int scale_stage_bytes = nvfp4 ? (1 + args.scale_blocks) * SCALE_PART_BYTES : 0;
     args.gelu_lo = args.gelu_hi = 0;
     if (epilogue != EPI_LINEAR && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
@@ -1327,7 +1341,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         args.gelu_hi = d->gelu_hi;
     }
     const int reduce_bytes = args.reduce_rows > 0 ? (splits - 1) * args.reduce_rows * args.tile_n * 4 : 0;
-    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 8 * MAX_RESIDENT_KB + 128 + 4 * (args.gelu_hi - args.gelu_lo) + reduce_bytes;
+    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 8 * MAX_RESIDENT_KB + 128 + 4 * (args.gelu_hi - args.gelu_lo) + reduce_bytes + ring_padding;
     // Resident order (TileWalk): worth it when a CTA computes several feature tiles of its token tile and the
     // token tile of all K, the weight stages and (NVFP4) the token scales in TMEM all fit.
     int panel_bytes = 0;
@@ -1339,7 +1353,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         const int resident_stages = (SMEM_LIMIT - fixed_bytes - resident_panel) / resident_stage;
         const int free_columns = TMEM_COLUMNS - args.accumulators * args.accumulator_stride - (nvfp4 ? args.num_kb * TMEM_SFA_COLUMNS : 0);
         const bool columns_fit = !nvfp4 || free_columns >= 2 * 16 * args.scale_blocks;
-        if (splits == 1 && !(d->flags & B2_LINEAR_STREAM_TOKENS) && args.num_kb <= MAX_RESIDENT_KB && args.num_m_tiles <= grid &&
+        if (splits == 1 && box_rows == TILE_TOKENS && !(d->flags & B2_LINEAR_STREAM_TOKENS) && args.num_kb <= MAX_RESIDENT_KB && args.num_m_tiles <= grid &&
             int64_t(args.num_n_tiles) * args.num_m_tiles >= 2 * int64_t(grid) && resident_stages >= 3 && columns_fit) {
             args.resident = 1;
             panel_bytes = resident_panel;
@@ -1370,7 +1384,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     }
 
     CUtensorMap act_map, weight_map;
-    if (!make_operand_map(&act_map, d->act, d->tokens, args.k_bytes, TILE_TOKENS)) return B2_E_DRIVER;
+    if (!make_operand_map(&act_map, d->act, d->tokens, args.k_bytes, box_rows)) return B2_E_DRIVER;
     if (geglu ? !make_gated_map(&weight_map, d->weight, d->features, args.k_bytes, feature_tile)
               : !make_operand_map(&weight_map, d->weight, weight_rows, args.k_bytes, feature_tile))
         return B2_E_DRIVER;
