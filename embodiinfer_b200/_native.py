@@ -26,7 +26,7 @@ NORM_RESIDUAL_EVICT_LAST = 1
 SCALE_SCRATCH_BYTES = 8
 STATIC_SCRATCH_BYTES = 16640
 STATIC_SCALE_MAX_COUNT = 67108864
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 _ERRORS = {
     E_INVALID: "invalid argument (null, non-positive size or misaligned pointer)",

@@ -21,7 +21,9 @@
 extern "C" {
 #endif
 
-#define B2_ABI_VERSION 2
+/* 3: adds the producers in front of the GEMMs (b2_norm_quant, b2_layer_norm_quant, b2_bhsd_quant, b2_normalize_frames,
+ * b2_frames_to_patches, b2_resize_frames) and B2_LINEAR_CLUSTER_SPLIT; everything of version 2 is unchanged. */
+#define B2_ABI_VERSION 3
 
 /* ---- status codes ---------------------------------------------------------- */
 #define B2_OK 0
