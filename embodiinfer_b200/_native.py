@@ -21,12 +21,12 @@ OUT_BF16, OUT_FP8, OUT_NVFP4 = 0, 1, 2
 LINEAR_ROUND_SCALE_BF16 = 1
 LINEAR_PAIRED_GATE_UP_SCALES = 4
 LINEAR_STREAM_TOKENS = 8
-LINEAR_CLUSTER_SPLIT = 32
+LINEAR_SINGLE_CTA = 64
 NORM_RESIDUAL_EVICT_LAST = 1
 SCALE_SCRATCH_BYTES = 8
 STATIC_SCRATCH_BYTES = 16640
 STATIC_SCALE_MAX_COUNT = 67108864
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 _ERRORS = {
     E_INVALID: "invalid argument (null, non-positive size or misaligned pointer)",

@@ -26,9 +26,9 @@
 //
 // Every wait is bounded (ptx.cuh); an expired wait leaves a code in the status word.
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 
 #include <cstdlib>
-#include "ptx.cuh"
 
 #include <cuda.h>
 
@@ -37,339 +37,6 @@
 
 namespace b2 {
 
-// Two service warps (TMA, MMA) plus the epilogue warps.  The plain Linear epilogue is a handful of
-// instructions per element and runs on 8 warps; the epilogues that go through the GELU table (lookups, two
-// roundings, block scale, exact division, packing) are latency-bound, so they get 16 warps: four per TMEM
-// lane partition, each owning 16-feature units (or 32-column chunks) of the tile.
-#ifndef B2_GEGLU_EPILOGUE_WARPS
-#define B2_GEGLU_EPILOGUE_WARPS 16
-#endif
-__host__ __device__ constexpr int epilogue_warps(int epi) { return epi != 0 ? B2_GEGLU_EPILOGUE_WARPS : 8; }
-constexpr int FIRST_EPILOGUE_WARP = 2;
-__host__ __device__ constexpr int gemm_threads(int epi) { return 32 * (FIRST_EPILOGUE_WARP + epilogue_warps(epi)); }
-constexpr int TILE_TOKENS = 128;                   // MMA M
-constexpr int STAGE_K_BYTES = 128;                 // one swizzle row
-constexpr int A_TILE_BYTES = TILE_TOKENS * STAGE_K_BYTES;
-constexpr int SCALE_ATOM_BYTES = 512;              // 128 rows x 4 blocks of 16
-constexpr int SCALE_ATOMS_PER_STAGE = 4;           // 4 x 64 elements = 256 e2m1 = 128 bytes of K
-
-constexpr int MAX_STAGES = 16;
-constexpr int TMEM_COLUMNS = 512;
-// NVFP4 scale factors live in TMEM columns 384..479: two sets (alternating by K slice, so the copies for
-// one slice never overwrite columns an MMA of the previous slice may still be reading), each 16 columns
-// of token scales (4 per 64 elements of K) followed by 32 columns of feature scales (8 per 64 elements).
-constexpr int MAX_RESIDENT_KB = 8;                 // K stages of a token tile kept in shared memory (8 x 16 KB)
-constexpr int PREFETCH_DISTANCE = 12;              // K stages between an L2 prefetch and its load
-constexpr int TMEM_SFA_COLUMNS = 16;               // 4 atoms x 4 columns of token scales per K stage
-// A set of scale columns = 16 token-scale columns + 16 per 128-row block of feature scales; sets are
-// stacked downwards from column 512 and rotate with the K stages.
-constexpr int SMEM_LIMIT = 227 * 1024;
-constexpr int MAX_COMPACT_GELU = 4096;             // magnitude codes of the GELU table kept in shared memory
-constexpr int SMEM_MINIMUM = 120 * 1024;           // keeps a second CTA (and its TMEM request) off the SM
-
-enum { EPI_LINEAR = 0, EPI_GEGLU_BF16 = 1, EPI_GEGLU_FP8 = 2, EPI_GEGLU_NVFP4 = 3, EPI_GELU_BF16 = 4, EPI_GELU_FP8 = 5 };
-__host__ __device__ constexpr bool is_gated(int epi) { return epi >= EPI_GEGLU_BF16 && epi <= EPI_GEGLU_NVFP4; }
-
-struct KernelArgs {
-    int tokens, features, k_bytes, num_kb;
-    int tile_n;                  // TMEM columns per tile (GEGLU: gate half + up half)
-    int num_m_tiles, num_n_tiles, total_tiles;
-    int stages, accumulators, accumulator_stride, scale_sets, scale_blocks;
-    int splits;                  // > 1: K is cut into `splits` ranges computed by different CTAs, see the epilogue
-    int resident;                // 1: the CTA keeps its token tile (all of K) and its token scales on chip, see TileWalk
-    int up_row_offset;           // row of the first "up" feature in the packed weight
-    int scale_column_tiles;      // 512-byte scale atoms per 128-row block
-    int act_row_blocks, weight_row_blocks;
-    int flags;
-    int gelu_lo, gelu_hi;        // bf16 magnitude codes [lo, hi) whose GELU is kept in shared memory (0,0 = none)
-    const uint8_t* act_scales;
-    const uint8_t* weight_scales;
-    const float* act_scale;
-    const float* weight_scale;
-    const float* weight_scale_up;   // GEGLU: scale of the up rows (nullptr = same as the gate rows)
-    const __nv_bfloat16* bias;
-    const __nv_bfloat16* residual;
-    const uint16_t* gelu_table;
-    const float* out_scale;
-    void* out;
-    uint8_t* out_scales;
-    uint8_t* out_blocked;
-    unsigned int* status;
-    int a_box_bytes;             // bytes of the token box of one K stage: 128 rows, or fewer (a multiple of 8) when the launch has
-                                 // one token tile with fewer tokens -- the rows beyond the box are whatever shared memory holds,
-                                 // they only feed accumulator rows that are never stored
-    int reduce_rows;             // cluster split: token rows (a multiple of 32) of a partial-sum slot in the leader's shared memory
-    unsigned int* tickets;       // split-K: one arrival counter per tile (zero between launches)
-    float* partials;             // split-K: [tile][split][128][tile_n] fp32
-};
-
-// ---- epilogue helpers ---------------------------------------------------------
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float low, float high) {
-    const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
-    return *reinterpret_cast<const uint32_t*>(&pair);
-}
-
-// acc -> the bf16 value the reference's GEMM returns, widened to fp32.
-//   plain:        bf16(acc * s)
-//   round_scale:  bf16(bf16(acc) * s) with s already rounded to bf16 (nvfp4.py:120)
-__device__ __forceinline__ float gemm_value(uint32_t acc_bits, float scale, bool round_scale) {
-    float acc = __uint_as_float(acc_bits);
-    if (round_scale) acc = round_to_bf16(acc);
-    return round_to_bf16(__fmul_rn(acc, scale));
-}
-
-__device__ __forceinline__ void store_u4(void* pointer, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    *reinterpret_cast<uint4*>(pointer) = make_uint4(a, b, c, d);
-}
-
-// bf16 pair from two floats in one conversion: low half = `low`, high half = `high`.
-__device__ __forceinline__ uint32_t cvt_bf16x2(float high, float low) {
-    uint32_t packed;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(high), "f"(low));
-    return packed;
-}
-
-// GELU of one bf16 bit pattern (16 bits), as bf16 bits.  Magnitude codes [lo, lo + span) come from the
-// shared-memory copy of the table ([positive | negative] halves).  Below lo the table equals bf16(x/2);
-// from lo + span up to the largest finite value it equals x (positive) or -0 (negative): the host verified
-// both against the table before choosing the range.  Subnormals, infinities, NaNs (and every value when
-// no range was supplied, span == 0) read the full table in global memory.
-__device__ __forceinline__ uint32_t gelu_lookup_general(uint32_t code, const KernelArgs& args, uint32_t compact_table,
-                                                        uint32_t lo, uint32_t span) {
-    const uint32_t magnitude = code & 0x7fffu;
-    const uint32_t offset = magnitude - lo;
-    const uint32_t negative = code >> 15;
-    if (offset < span) {
-        uint32_t value;
-        asm("ld.shared.u16 %0, [%1];" : "=r"(value) : "r"(compact_table + 2u * (offset + negative * span)));
-        return value;
-    }
-    if (span != 0u && magnitude >= 0x80u && magnitude < 0x7f80u) {
-        const float x = __uint_as_float(code << 16);
-        return magnitude < lo ? uint32_t(bf16_bits(__fmul_rn(0.5f, x))) : (negative ? 0x8000u : code);
-    }
-    return uint32_t(__ldg(args.gelu_table + code));
-}
-
-// The sixteen gates of one unit as eight bf16x2 words -> their GELUs as eight bf16x2 words.  One test per
-// unit (two adds per word: a magnitude m is >= lo iff m + (0x8000 - lo) carries into bit 15, and < hi iff
-// m + (0x8000 - hi) does not) picks between straight-line shared-memory lookups and the general path.
-__device__ __forceinline__ void gelu_lookup_unit(const uint32_t (&gate)[8], uint32_t (&gelu)[8], const KernelArgs& args,
-                                                 uint32_t compact_table, uint32_t lo, uint32_t span) {
-    const uint32_t above_lo = (0x8000u - lo) * 0x10001u, above_hi = (0x8000u - (lo + span)) * 0x10001u;
-    uint32_t reach_lo = 0xffffffffu, reach_hi = 0u;
-#pragma unroll
-    for (int p = 0; p < 8; ++p) {
-        const uint32_t magnitudes = gate[p] & 0x7fff7fffu;
-        reach_lo &= magnitudes + above_lo;
-        reach_hi |= magnitudes + above_hi;
-    }
-    if (span != 0u && ((~reach_lo | reach_hi) & 0x80008000u) == 0u) {
-        // address of code c: table + 2*(c - lo) for positive c, table + 2*(c - 0x8000 - lo + span) for negative
-        const uint32_t origin = compact_table - 2u * lo;
-        const uint32_t fold = 0x10000u - 2u * span;
-#pragma unroll
-        for (int p = 0; p < 8; ++p) {
-            const uint32_t first = gate[p] & 0xffffu, second = gate[p] >> 16;
-            uint32_t low, high;
-            asm("ld.shared.u16 %0, [%1];" : "=r"(low) : "r"(origin + 2u * first - (first >> 15) * fold));
-            asm("ld.shared.u16 %0, [%1];" : "=r"(high) : "r"(origin + 2u * second - (second >> 15) * fold));
-            gelu[p] = low | (high << 16);
-        }
-    } else {
-#pragma unroll
-        for (int p = 0; p < 8; ++p)
-            gelu[p] = gelu_lookup_general(gate[p] & 0xffffu, args, compact_table, lo, span) |
-                      (gelu_lookup_general(gate[p] >> 16, args, compact_table, lo, span) << 16);
-    }
-}
-
-// 32 accumulator columns of one token -> 32 bf16 outputs (64 contiguous bytes): one packed multiply and
-// one two-value conversion per pair, 32-byte stores where the row allows them.
-// EPI_GELU_*: the bf16 result goes through the GELU table and is stored as bf16 or, divided by *out_scale,
-// as e4m3 (32 contiguous bytes) -- SigLIP's fc1 (bias + tanh GELU + the encoder of fc2's input in one launch).
-template <int EPI>
-__device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32], const KernelArgs& args, float scale,
-                                                      bool round_scale, int token, int feature0, uint32_t compact_table,
-                                                      const ExactDivider& out_scale, float out_scale_rcp, bool true_div) {
-    uint32_t y[16];                                   // bf16 pairs
-    const float2 scale2 = make_float2(scale, scale);
-#pragma unroll
-    for (int p = 0; p < 16; ++p) {
-        float2 value = make_float2(__uint_as_float(acc[2 * p]), __uint_as_float(acc[2 * p + 1]));
-        if (round_scale) value = bf16x2_to_float2(float2_to_bf16x2(value));     // nvfp4.py:120: the GEMM's own bf16 output
-        y[p] = float2_to_bf16x2(__fmul2_rn(value, scale2));
-    }
-    if (args.bias != nullptr) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            if (feature0 + 8 * v < args.features) {
-                const uint4 packed = __ldg(reinterpret_cast<const uint4*>(args.bias + feature0 + 8 * v));
-                const uint32_t b[4] = {packed.x, packed.y, packed.z, packed.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    y[4 * v + i] = float2_to_bf16x2(__fadd2_rn(bf16x2_to_float2(y[4 * v + i]), bf16x2_to_float2(b[i])));
-            }
-        }
-    }
-    if (EPI != EPI_LINEAR) {
-        const uint32_t lo = uint32_t(args.gelu_lo), span = uint32_t(args.gelu_hi - args.gelu_lo);
-        uint32_t in[8], out[8];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) in[i] = y[8 * half + i];
-            gelu_lookup_unit(in, out, args, compact_table, lo, span);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) y[8 * half + i] = out[i];
-        }
-    }
-    if (token >= args.tokens) return;
-    const int64_t row = int64_t(token) * args.features;
-    if (EPI == EPI_GELU_FP8) {
-        uint32_t codes[8];
-        if (true_div) {
-            const float bound = __fmul_rn(1024.0f, out_scale.divisor);
-            uint32_t in[8], part[4];
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) in[i] = y[8 * half + i];
-                encode_fp8_words<true, 8>(in, part, out_scale, bound);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) codes[4 * half + i] = part[i];
-            }
-        } else {
-            const float2 rcp2 = make_float2(out_scale_rcp, out_scale_rcp);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const uint32_t low = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(y[2 * i]), rcp2), __NV_SATFINITE, __NV_E4M3);
-                const uint32_t high = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(y[2 * i + 1]), rcp2), __NV_SATFINITE, __NV_E4M3);
-                codes[i] = low | (high << 16);
-            }
-        }
-        uint8_t* out8 = static_cast<uint8_t*>(args.out) + row + feature0;
-        if (feature0 + 32 <= args.features && aligned32(out8)) {
-            st_u8(out8, codes);
-        } else {
-#pragma unroll
-            for (int v = 0; v < 4; ++v)        // 8 features = 8 bytes per step
-                if (feature0 + 8 * v < args.features) *reinterpret_cast<uint2*>(out8 + 8 * v) = make_uint2(codes[2 * v], codes[2 * v + 1]);
-        }
-        return;
-    }
-    if (args.residual != nullptr) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            if (feature0 + 8 * v < args.features) {
-                const uint4 packed = ld_nc_u4(reinterpret_cast<const uint4*>(args.residual + row + feature0 + 8 * v));
-                const uint32_t r[4] = {packed.x, packed.y, packed.z, packed.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    y[4 * v + i] = float2_to_bf16x2(__fadd2_rn(bf16x2_to_float2(y[4 * v + i]), bf16x2_to_float2(r[i])));
-            }
-        }
-    }
-    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out) + row + feature0;
-    if (feature0 + 32 <= args.features && aligned32(out)) {
-        const uint32_t first[8] = {y[0], y[1], y[2], y[3], y[4], y[5], y[6], y[7]};
-        const uint32_t second[8] = {y[8], y[9], y[10], y[11], y[12], y[13], y[14], y[15]};
-        st_u8(out, first);
-        st_u8(out + 16, second);
-        return;
-    }
-#pragma unroll
-    for (int v = 0; v < 4; ++v)
-        if (feature0 + 8 * v < args.features) store_u4(out + 8 * v, y[4 * v], y[4 * v + 1], y[4 * v + 2], y[4 * v + 3]);
-}
-
-// One 16-feature unit of a token's row: 16 gate + 16 up accumulator columns -> 16 hidden values
-// h = bf16(bf16(gelu(gate)) * up), stored as bf16, e4m3 or NVFP4 (fusion.cu:5-10, 31-107).  For NVFP4
-// the unit is exactly one quantisation block of the next layer's input.  Values travel as bf16 pairs:
-// the product of two bf16 numbers is exact in fp32, so the packed bf16 multiply rounds once, like the
-// reference's float multiply followed by the bf16 store.
-template <int EPI>
-__device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[16], const uint32_t (&up_acc)[16],
-                                                    const KernelArgs& args, uint32_t compact_table, float scale,
-                                                    float scale_up, bool round_scale, const ExactDivider& out_scale,
-                                                    const ExactDivider& by_global, float out_scale_rcp, bool true_div,
-                                                    int token, int feature0) {
-    const uint32_t lo = uint32_t(args.gelu_lo);
-    const uint32_t span = uint32_t(args.gelu_hi - args.gelu_lo);     // 0: every lookup reads the full table
-    const float2 scale2 = make_float2(scale, scale), scale_up2 = make_float2(scale_up, scale_up);
-    uint32_t gate[8], up[8], gelu[8], h[8];
-#pragma unroll
-    for (int p = 0; p < 8; ++p) {
-        float2 g = make_float2(__uint_as_float(gate_acc[2 * p]), __uint_as_float(gate_acc[2 * p + 1]));
-        float2 u = make_float2(__uint_as_float(up_acc[2 * p]), __uint_as_float(up_acc[2 * p + 1]));
-        if (round_scale) {
-            g = bf16x2_to_float2(float2_to_bf16x2(g));
-            u = bf16x2_to_float2(float2_to_bf16x2(u));
-        }
-        gate[p] = float2_to_bf16x2(__fmul2_rn(g, scale2));
-        up[p] = float2_to_bf16x2(__fmul2_rn(u, scale_up2));
-    }
-    gelu_lookup_unit(gate, gelu, args, compact_table, lo, span);
-#pragma unroll
-    for (int p = 0; p < 8; ++p) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(h[p]) : "r"(gelu[p]), "r"(up[p]));
-    if (token >= args.tokens || feature0 >= args.features) return;
-    const int64_t element = int64_t(token) * args.features + feature0;
-    if (EPI == EPI_GEGLU_BF16) {
-        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out) + element;
-        if (aligned32(out)) {
-            st_u8(out, h);
-        } else {
-            store_u4(out, h[0], h[1], h[2], h[3]);
-            store_u4(out + 8, h[4], h[5], h[6], h[7]);
-        }
-    } else if (EPI == EPI_GEGLU_FP8) {
-        uint32_t codes[4];
-        if (true_div) {
-            encode_fp8_words<true, 8>(h, codes, out_scale, __fmul_rn(1024.0f, out_scale.divisor));
-        } else {
-            const float2 rcp2 = make_float2(out_scale_rcp, out_scale_rcp);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t low = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(h[2 * i]), rcp2), __NV_SATFINITE, __NV_E4M3);
-                const uint32_t high = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(h[2 * i + 1]), rcp2), __NV_SATFINITE, __NV_E4M3);
-                codes[i] = low | (high << 16);
-            }
-        }
-        store_u4(static_cast<uint8_t*>(args.out) + element, codes[0], codes[1], codes[2], codes[3]);
-    } else {
-        // quantize.cu:85-104 arithmetic on this block
-        const float block_max = abs_max_bf16_words(h);
-        const uint8_t code = nvfp4_block_scale<true>(block_max, by_global, 0);
-        const ExactDivider denominator(__fmul_rn(out_scale.divisor, e4m3_to_float(code)));
-        uint32_t word0, word1;
-        if (denominator.fast && __fmul_rn(block_max, denominator.reciprocal) < 1.0e30f) {
-            word0 = nvfp4_encode_words_short<true>(h[0], h[1], h[2], h[3], denominator);
-            word1 = nvfp4_encode_words_short<true>(h[4], h[5], h[6], h[7], denominator);
-        } else {
-            float low[8], high[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                low[2 * i] = bf16_lo(h[i]); low[2 * i + 1] = bf16_hi(h[i]);
-                high[2 * i] = bf16_lo(h[4 + i]); high[2 * i + 1] = bf16_hi(h[4 + i]);
-            }
-            word0 = nvfp4_encode_x8<true>(low, denominator, block_max);
-            word1 = nvfp4_encode_x8<true>(high, denominator, block_max);
-        }
-        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(args.out) + (element >> 1)) = make_uint2(word0, word1);
-        const int block = feature0 >> 4;
-        const int blocks_per_row = args.features >> 4;
-        if (args.out_scales != nullptr) args.out_scales[int64_t(token) * blocks_per_row + block] = code;
-        if (args.out_blocked != nullptr)
-            args.out_blocked[scale_tile_offset(token, block, (blocks_per_row + 3) >> 2)] = code;
-    }
-}
-
-#ifdef B2_TRACE
-#define TRACE(slot, index) do { if (blockIdx.x == 0 && (args.flags & 0x1000) && lane == 0 && (index) < 400) reinterpret_cast<long long*>(args.status)[(slot) * 400 + (index)] = clock64(); } while (0)
-#else
-#define TRACE(slot, index)
-#endif
 // Which tiles a CTA computes, in which order.
 //   streaming (default): tile = blockIdx.x + i * gridDim.x over the n-major tile list (token tile inner), so
 //       the CTAs running side by side share a weight slab and every K stage loads a token tile and a
@@ -430,20 +97,13 @@ struct TileWalk {
 //   SPLIT_NONE     one CTA computes all of K of its tiles;
 //   SPLIT_GLOBAL   partial sums go through a caller-provided workspace in global memory, the CTA that draws a
 //                  tile's last ticket adds them (any number of token tiles; opt-in);
-//   SPLIT_CLUSTER  the CTAs of a thread-block cluster each take a K range of ONE tile; ranks 1.. write their fp32
-//                  partial sums (valid token rows only) into the shared memory of rank 0 through the cluster's
-//                  distributed shared memory, a cluster barrier orders the writes, and rank 0 adds them to its
-//                  own accumulator in rank order and runs the epilogue.  No workspace, no atomics, one launch;
-//                  for the single-token-tile launches (M <= 128) whose few tiles leave most SMs idle (opt-in:
-//                  B2_LINEAR_CLUSTER_SPLIT).
-enum SplitMode { SPLIT_NONE = 0, SPLIT_GLOBAL = 1, SPLIT_CLUSTER = 2 };
+enum SplitMode { SPLIT_NONE = 0, SPLIT_GLOBAL = 1 };
 
 template <int KIND, int EPI, int SPLIT_MODE>
 __global__ void __launch_bounds__(gemm_threads(EPI), 1)
 linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
               const KernelArgs args) {
     constexpr bool SPLIT_K = SPLIT_MODE == SPLIT_GLOBAL;
-    constexpr bool CLUSTER = SPLIT_MODE == SPLIT_CLUSTER;
     constexpr bool GEGLU = is_gated(EPI);
     constexpr bool USES_TABLE = EPI != EPI_LINEAR;
     pdl_launch_dependents();
@@ -472,7 +132,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     const uint32_t tmem_slot = panel_bar + 8 * MAX_RESIDENT_KB;
     const uint32_t split_flag = tmem_slot + 8;                    // split-K: "this CTA drew the last ticket"
     const uint32_t compact_table = tmem_slot + 16;                // 2 * (gelu_hi - gelu_lo) bf16 entries
-    const uint32_t reduce_base = compact_table;                   // cluster split (plain epilogue, no table): [rank - 1][reduce_rows][BN] fp32
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -525,7 +184,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             constexpr bool RESIDENT = decltype(resident_tag)::value, PREFETCH = decltype(prefetch_tag)::value;
             int stage = 0;
             uint32_t phase = 0;
-            int trace_index = 0; (void)trace_index;
             uint32_t filled = 0, fill_parity = 0;     // per stage: ever filled / phase of the last fill
             // L2 prefetch cursor, PREFETCH_DISTANCE K stages ahead of the loads.  Shared memory holds about
             // 2500 cycles' worth of loads at the tensor pipe's rate while a first touch of HBM takes about as
@@ -595,7 +253,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
                     mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
                     __syncwarp();
-                    TRACE(0, trace_index);
                     filled |= 1u << stage;
                     fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
                     if (elect_one()) {
@@ -637,7 +294,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         if (++pf_kb == num_kb) { pf_kb = 0; pf.next(args); }
                     }
                     __syncwarp();
-                    TRACE(1, trace_index); ++trace_index;
                     if (++stage == args.stages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -658,7 +314,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         // instruction on the warp whose issue rate bounds the small launches)
         if (resident) { if (prefetch_ahead) producer_role(Yes{}, Yes{}); else producer_role(Yes{}, No{}); }
         else { if (prefetch_ahead) producer_role(No{}, Yes{}); else producer_role(No{}, No{}); }
-        if (CLUSTER) { cluster_arrive(); cluster_wait(); }        // every thread of the cluster takes part, once
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
         // (all lanes run the loop; one elected lane issues the tcgen05 instructions)
@@ -683,7 +338,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             // cycles per 512-byte atom, overlapping the MMAs already queued).  The reverse order is not
             // guaranteed: before a set of columns is overwritten, the MMAs that last read it (scale_sets
             // stages ago) must have completed, which their commit to that stage's `empty` barrier reports.
-            int trace_index = 0; (void)trace_index;
             int set = 0, lag_stage = 0, issued = 0;
             uint32_t lag_phase = 0;
             const uint32_t set_columns = uint32_t((RESIDENT ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
@@ -741,7 +395,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         ++issued;
                     }
                     __syncwarp();
-                    TRACE(2, trace_index);
                     if (elect_one()) {
                         // shared memory: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
                         const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes) >> 4;
@@ -789,7 +442,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     tc_commit(empty_bar + 8 * stage);
                     }
                     __syncwarp();
-                    TRACE(3, trace_index); ++trace_index;
                     if (KIND == B2_KIND_NVFP4 && ++set == args.scale_sets) set = 0;
                     if (++stage == args.stages) { stage = 0; phase ^= 1u; }
                 }
@@ -805,7 +457,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         else if (split_halves) { if (resident) mma_role(Yes{}, Yes{}, Yes{}); else mma_role(No{}, Yes{}, Yes{}); }
         else if (two_blocks) { if (resident) mma_role(Yes{}, Yes{}, No{}); else mma_role(No{}, Yes{}, No{}); }
         else { if (resident) mma_role(Yes{}, No{}, No{}); else mma_role(No{}, No{}, No{}); }
-        if (CLUSTER) { cluster_arrive(); cluster_wait(); }
     } else {
         // ------------------------------------------------------------- epilogue
         const int quarter = warp & 3;                      // the TMEM lane partition this warp may read
@@ -837,38 +488,12 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             const uint32_t use = uint32_t(local_tile / args.accumulators);
             mbar_wait(acc_full_bar + 8 * buffer, use & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
             tc_fence_after_sync();
-            if (warp == FIRST_EPILOGUE_WARP) TRACE(4, local_tile);
             const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer * args.accumulator_stride);
             const bool warp_has_tokens = m_tile * TILE_TOKENS + quarter * 32 < args.tokens;   // else: padding rows only
             // Split K: every CTA of a tile leaves its partial sums (fp32, valid token rows only) in its slot of
             // the workspace and takes a ticket; the CTA that draws the last ticket adds the slots in split order
             // (so the result does not depend on which CTA that is) and runs the epilogue on the sums.  No CTA
             // waits for another.
-            // Cluster split: the host launches exactly one work item per CTA, so this loop body runs once in every
-            // CTA of the cluster and the barrier below is reached by all of its epilogue threads.
-            if (CLUSTER) {
-                const uint32_t rank = cluster_cta_rank();
-                if (rank != 0) {
-                    const uint32_t row = uint32_t(quarter * 32 + lane);
-                    for (int chunk = part; chunk < BN / 32 && warp_has_tokens; chunk += WARPS_PER_QUARTER) {
-                        uint32_t v[32];
-                        tmem_load_32x32(lane_address + chunk * 32, v);
-                        tmem_load_wait();
-                        const uint32_t local = reduce_base + (((rank - 1u) * uint32_t(args.reduce_rows) + row) * uint32_t(BN) + uint32_t(chunk) * 32u) * 4u;
-                        const uint32_t remote = cluster_map_shared(local, 0u);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) cluster_store_u4(remote + 16u * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                    }
-                }
-                cluster_arrive();
-                cluster_wait();
-                if (rank != 0) {
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buffer);
-                    continue;
-                }
-            }
             const float* sums = nullptr;
             if (SPLIT_K) {
                 const int64_t slot_floats = int64_t(TILE_TOKENS) * BN;
@@ -952,23 +577,13 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                             for (int i = 0; i < 16; ++i) first[i] = second[i] = 0u;
                         }
                     } else {
-#ifdef B2_TRACE
-                        if (args.flags & 0x20000) continue;                    // debug: no TMEM loads, no math, no stores
-#endif
                         tmem_load_32x16(lane_address + unit * 16, first);
                         tmem_load_32x16(lane_address + BN / 2 + unit * 16, second);
                         tmem_load_wait();
-#ifdef B2_TRACE
-                        if (args.flags & 0x10000) continue;                    // debug: TMEM loads only
-#endif
                     }
-                    int store_token = token;
-#ifdef B2_TRACE
-                    if (args.flags & 0x40000) store_token = args.tokens + (first[0] == 0x12345678u);   // debug: math, no stores
-#endif
                     epilogue_geglu_unit<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, compact_table, scale, scale_up,
                                                                      round_scale, out_scale, by_global, out_scale_rcp,
-                                                                     true_div, store_token, f0 + unit * 16);
+                                                                     true_div, token, f0 + unit * 16);
                 }
             } else {
                 const int chunks = features_per_tile / 32;
@@ -984,21 +599,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     } else {
                         tmem_load_32x32(lane_address + chunk * 32, first);
                         tmem_load_wait();
-                        if (CLUSTER) {             // + the partial sums of ranks 1.., in rank order
-                            const uint32_t row = uint32_t(quarter * 32 + lane);
-                            for (int s = 1; s < args.splits; ++s) {
-                                const uint32_t slot = reduce_base + ((uint32_t(s - 1) * uint32_t(args.reduce_rows) + row) * uint32_t(BN) + uint32_t(chunk) * 32u) * 4u;
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) {
-                                    float4 p;
-                                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(p.x), "=f"(p.y), "=f"(p.z), "=f"(p.w) : "r"(slot + 16u * i) : "memory");
-                                    first[4 * i] = __float_as_uint(__fadd_rn(__uint_as_float(first[4 * i]), p.x));
-                                    first[4 * i + 1] = __float_as_uint(__fadd_rn(__uint_as_float(first[4 * i + 1]), p.y));
-                                    first[4 * i + 2] = __float_as_uint(__fadd_rn(__uint_as_float(first[4 * i + 2]), p.z));
-                                    first[4 * i + 3] = __float_as_uint(__fadd_rn(__uint_as_float(first[4 * i + 3]), p.w));
-                                }
-                            }
-                        }
                     }
                     epilogue_linear_chunk<GEGLU ? EPI_LINEAR : EPI>(first, args, scale, round_scale, token, f0 + chunk * 32, compact_table,
                                                                     out_scale, out_scale_rcp, true_div);
@@ -1009,7 +609,6 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty_bar + 8 * buffer);
             }
-            if (warp == FIRST_EPILOGUE_WARP) TRACE(5, local_tile);
         }
     }
 
@@ -1024,11 +623,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
 // ---------------------------------------------------------------------------
 // host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_entry() {
+EncodeTiledFn encode_tiled_entry() {
     static EncodeTiledFn entry = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
@@ -1043,7 +638,7 @@ static EncodeTiledFn encode_tiled_entry() {
 
 // Row-major byte matrix [rows, row_bytes] viewed as tiles of box_rows x 128 bytes, 128-byte swizzle.
 // Rows and bytes beyond the matrix read as zero.
-static bool make_operand_map(CUtensorMap* map, const void* pointer, int64_t rows, int64_t row_bytes, int box_rows) {
+bool make_operand_map(CUtensorMap* map, const void* pointer, int64_t rows, int64_t row_bytes, int box_rows) {
     EncodeTiledFn encode = encode_tiled_entry();
     if (encode == nullptr) return false;
     const cuuint64_t dims[2] = {cuuint64_t(row_bytes), cuuint64_t(rows)};
@@ -1132,36 +727,6 @@ static void choose_tile_and_splits(int kind, bool geglu, int forced_tile, int fe
     }
 }
 
-// Single token tile, plain epilogue: tile width and cluster size (1, 2, 4 or 8 CTAs along K) from the same cycle
-// estimate.  A cluster launch runs one work item per CTA; the reduction costs a cluster barrier plus the leader's
-// pass over (splits - 1) slots of `rows` x tile fp32 in its shared memory.  Clusters are placed whole inside a GPC,
-// so the estimate stays below the SM count to keep the launch in one wave.
-constexpr int CLUSTER_CTA_BUDGET = 128;
-
-static void choose_cluster_split(int kind, int forced_tile, int features, int rows, int num_kb, bool nvfp4, int* tile_out,
-                                 int* splits_out) {
-    double best_cost = 0.0;
-    *tile_out = 0;
-    *splits_out = 1;
-    for (int tile = 256; tile >= 64; tile -= 64) {
-        if (!tile_allowed(false, tile) || (forced_tile > 0 && tile != forced_tile)) continue;
-        const int tiles = (features + tile - 1) / tile;
-        const double stage = 2.9 * (128.0 + tile);
-        const double fixed = 2500.0 + (can_double_buffer(kind, tile) ? 0.0 : 10.0 * tile);
-        const int stage_bytes = A_TILE_BYTES + tile * STAGE_K_BYTES + (nvfp4 ? 3 * SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES : 0);
-        for (int splits = 1; splits <= MAX_SPLITS; splits *= 2) {
-            const int64_t reduce_bytes = int64_t(splits - 1) * rows * tile * 4;
-            if (splits > 1 && (tiles * splits > CLUSTER_CTA_BUDGET || num_kb < 2 * splits ||
-                               reduce_bytes + 3 * stage_bytes + 4096 > SMEM_LIMIT))
-                break;
-            const int64_t waves = (int64_t(tiles) * splits + sm_count() - 1) / sm_count();
-            const int kb_item = (num_kb + splits - 1) / splits;
-            const double cost = double(waves) * (kb_item * stage + fixed) + (splits > 1 ? 1000.0 + double(reduce_bytes) / 64.0 : 0.0);
-            if (*tile_out == 0 || cost < best_cost) { *tile_out = tile; *splits_out = splits; best_cost = cost; }
-        }
-    }
-}
-
 template <int KIND, int EPI, int SPLIT_MODE>
 static int launch_linear_variant(const CUtensorMap& act_map, const CUtensorMap& weight_map, const KernelArgs& args,
                          int shared_bytes, cudaStream_t stream) {
@@ -1179,23 +744,6 @@ static int launch_linear_variant(const CUtensorMap& act_map, const CUtensorMap& 
         }
     }
     const int items = args.total_tiles * args.splits;
-    if (SPLIT_MODE == SPLIT_CLUSTER) {
-        // one work item per CTA, the `splits` CTAs of a tile form one cluster (consecutive block indices)
-        cudaLaunchConfig_t config = {};
-        config.gridDim = dim3(unsigned(items));
-        config.blockDim = dim3(unsigned(gemm_threads(EPI)));
-        config.dynamicSmemBytes = size_t(shared_bytes);
-        config.stream = stream;
-        cudaLaunchAttribute attribute;
-        attribute.id = cudaLaunchAttributeClusterDimension;
-        attribute.val.clusterDim.x = unsigned(args.splits);
-        attribute.val.clusterDim.y = 1;
-        attribute.val.clusterDim.z = 1;
-        config.attrs = &attribute;
-        config.numAttrs = 1;
-        const cudaError_t error = cudaLaunchKernelEx(&config, linear_kernel<KIND, EPI, SPLIT_MODE>, act_map, weight_map, args);
-        return error == cudaSuccess ? int(cudaGetLastError()) : int(error);
-    }
     const int grid = items < sm_count() ? items : sm_count();
     return launch_kernel(linear_kernel<KIND, EPI, SPLIT_MODE>, dim3(unsigned(grid)), dim3(unsigned(gemm_threads(EPI))),
                          size_t(shared_bytes), stream, act_map, weight_map, args);
@@ -1207,8 +755,6 @@ static int launch_linear(const CUtensorMap& act_map, const CUtensorMap& weight_m
     // only the plain epilogue has a split-K variant (the table epilogues would spill registers in the fix-up,
     // and `run_linear` never asks them to split)
     if constexpr (EPI == EPI_LINEAR) {
-        if (args.splits > 1 && args.reduce_rows > 0)
-            return launch_linear_variant<KIND, EPI, SPLIT_CLUSTER>(act_map, weight_map, args, shared_bytes, stream);
         if (args.splits > 1) return launch_linear_variant<KIND, EPI, SPLIT_GLOBAL>(act_map, weight_map, args, shared_bytes, stream);
     }
     return launch_linear_variant<KIND, EPI, SPLIT_NONE>(act_map, weight_map, args, shared_bytes, stream);
@@ -1224,6 +770,9 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     if (d->kind != B2_KIND_FP8 && d->kind != B2_KIND_NVFP4) return B2_E_UNSUPPORTED;
     if (d->epilogue != B2_EPI_LINEAR && d->epilogue != B2_EPI_GEGLU && d->epilogue != B2_EPI_GELU) return B2_E_UNSUPPORTED;
     if (d->tokens <= 0 || d->features <= 0 || d->width <= 0) return B2_E_INVALID;
+    constexpr int KNOWN_FLAGS = B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS |
+                                B2_LINEAR_SINGLE_CTA | B2_GEGLU_TRUE_DIV;
+    if (d->flags & ~KNOWN_FLAGS) return B2_E_INVALID;
     if (!planning) {
         if (d->act == nullptr || d->weight == nullptr || d->act_scale == nullptr || d->weight_scale == nullptr ||
             d->out == nullptr)
@@ -1260,6 +809,16 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         if (d->features % 8 != 0) return B2_E_UNSUPPORTED;             // 16-byte output vectors
     }
 
+    // More than one 128-token tile: two CTAs share every weight tile (gemm_pair.cu), unless the caller asks for the
+    // single-CTA schedule or passes a scale layout only that schedule reads.
+    if (!planning) {
+        const int pair_columns = pair_tile_columns(d, geglu);
+        if (pair_columns != 0) return run_linear_pair(d, epilogue, pair_columns, stream);
+    } else if (pair_tile_columns(d, geglu) != 0) {
+        *workspace_need = 0;
+        return B2_OK;
+    }
+
     KernelArgs args{};
     args.tokens = d->tokens;
     args.features = d->features;
@@ -1286,18 +845,6 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         }
         if (splits == 1 || d->workspace_bytes >= need) break;
         allow_split = false;
-    }
-    // One token tile and the plain epilogue: on request K is cut across the CTAs of a cluster (no workspace needed).
-    args.reduce_rows = 0;
-    if (d->epilogue == B2_EPI_LINEAR && args.num_m_tiles == 1 && splits == 1 && (d->flags & B2_LINEAR_CLUSTER_SPLIT)) {
-        const int rows = (d->tokens + 31) / 32 * 32;
-        int cluster_tile = 0, cluster_splits = 1;
-        choose_cluster_split(d->kind, d->feature_tile, d->features, rows, args.num_kb, nvfp4, &cluster_tile, &cluster_splits);
-        if (cluster_tile != 0 && cluster_splits > 1) {
-            feature_tile = cluster_tile;
-            splits = cluster_splits;
-            args.reduce_rows = rows;
-        }
     }
     args.tile_n = geglu ? 2 * feature_tile : feature_tile;
     args.num_n_tiles = (d->features + feature_tile - 1) / feature_tile;
@@ -1340,8 +887,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
         args.gelu_lo = d->gelu_lo;
         args.gelu_hi = d->gelu_hi;
     }
-    const int reduce_bytes = args.reduce_rows > 0 ? (splits - 1) * args.reduce_rows * args.tile_n * 4 : 0;
-    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 8 * MAX_RESIDENT_KB + 128 + 4 * (args.gelu_hi - args.gelu_lo) + reduce_bytes + ring_padding;
+    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 8 * MAX_RESIDENT_KB + 128 + 4 * (args.gelu_hi - args.gelu_lo) + ring_padding;
     // Resident order (TileWalk): worth it when a CTA computes several feature tiles of its token tile and the
     // token tile of all K, the weight stages and (NVFP4) the token scales in TMEM all fit.
     int panel_bytes = 0;
@@ -1378,7 +924,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     args.splits = splits;
     args.tickets = nullptr;
     args.partials = nullptr;
-    if (splits > 1 && args.reduce_rows == 0) {
+    if (splits > 1) {
         args.tickets = static_cast<unsigned int*>(d->workspace);
         args.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(d->workspace) + TICKET_BYTES);
     }

@@ -1,0 +1,588 @@
+// Quantised Linear, paired schedule: two CTAs of a thread-block cluster (two SMs) compute one tile of
+// 256 tokens x BN features with `tcgen05.mma.cta_group::2`.
+//
+// Why pairs.  With one CTA per 128-token tile (gemm.cu) every K stage moves 128 token rows and BN weight
+// rows into shared memory for 128 x BN x 128 bytes of tensor work; the kernel is then bound by operand bytes
+// per MMA (L2 -> SM traffic several times the algorithmic bytes, tensor pipe under 20 % busy).  A pair shares
+// the weight tile: each CTA loads its own 128 token rows and only HALF of the weight rows (BN/2), the
+// hardware reads the other half from the peer's shared memory, and each SM accumulates its own 128 tokens x
+// BN features in its own tensor memory.  Operand bytes per MMA drop by a third at BN = 256, and a weight byte
+// crosses L2 -> SM once per 256 tokens instead of once per 128.
+//
+// Roles per CTA (same warp layout as the single-CTA kernel, so the epilogues are shared code):
+//   warp 0      TMA producer: this CTA's token rows, its half of the weight rows, (NVFP4) its scale atoms.
+//               Every copy completes on the LEADER's `full` barrier (`cp.async.bulk.tensor...cta_group::2`,
+//               no multicast anywhere: each CTA issues plain loads of its own operands).
+//   warp 1      allocates tensor memory (both CTAs, `cta_group::2`); in the leader (cluster rank 0) it issues
+//               the scale copies and the MMAs for both SMs and commits to barriers in both CTAs.
+//   warps 2..   epilogue of this CTA's 128 tokens; the accumulator is handed back to the leader's MMA warp
+//               through a barrier in the leader's shared memory (the peer arrives remotely).
+//
+// Every wait is bounded (ptx.cuh); an expired wait leaves a code in the status word and the kernel drains.
+// The cluster barriers at entry and exit are hardware barriers that every thread reaches after at most its
+// bounded waits.
+#include "gemm_epilogue.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+#include <type_traits>
+
+namespace b2 {
+
+constexpr int PAIR_TOKENS = 2 * TILE_TOKENS;
+
+// ---- cta_group::2 forms of the tcgen05 / TMA instructions -------------------------------------------------
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t address, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+
+// The barrier at the same shared-memory offset in every CTA of `mask` receives one arrival when all tcgen05
+// operations issued so far by this thread have completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+
+__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void mma_nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
+// Shared memory -> tensor memory in both CTAs of the pair: each reads its own shared memory at the descriptor's
+// offset and writes its own tensor memory.
+__device__ __forceinline__ void tc_copy_32x128b_x4_pair(uint32_t dst_tmem, uint64_t src_desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(src_desc) : "memory");
+}
+
+// Tiled load into THIS CTA's shared memory whose completion bytes are counted on a barrier that may live in the
+// peer CTA (`bar` is a shared::cluster address).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tensor_map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// Instruction descriptors for the pair: M = 256 (128 rows per CTA).
+__device__ __forceinline__ uint32_t idesc_f8_pair(uint32_t n) { return idesc_f8(PAIR_TOKENS, n); }
+__device__ __forceinline__ uint32_t idesc_nvf4_pair(uint32_t n) { return idesc_nvf4(PAIR_TOKENS, n); }
+
+// Work items of a cluster: item = cluster + i * clusters over the n-major list (token pair inner), so the
+// clusters that run side by side share a weight slab (it comes from HBM once and from the L2 afterwards).
+struct PairWalk {
+    int item, step, m_pair, n_tile;
+    __device__ __forceinline__ explicit PairWalk(const KernelArgs& args) : item(int(blockIdx.x) >> 1), step(int(gridDim.x) >> 1) {
+        decompose(args);
+    }
+    __device__ __forceinline__ void decompose(const KernelArgs& args) {
+        n_tile = item / args.num_m_tiles;
+        m_pair = item - n_tile * args.num_m_tiles;
+    }
+    __device__ __forceinline__ bool valid(const KernelArgs& args) const { return item < args.total_tiles; }
+    __device__ __forceinline__ void next(const KernelArgs& args) {
+        item += step;
+        decompose(args);
+    }
+};
+
+// KernelArgs as the pair kernel reads them: num_m_tiles = token PAIRS, tile_n = BN (columns of one CTA's
+// accumulator), scale_blocks = 128-row blocks of feature scales per tile (1 or 2), a_box_bytes unused.
+template <int KIND, int EPI>
+__global__ void __launch_bounds__(gemm_threads(EPI), 1)
+pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
+                   const __grid_constant__ CUtensorMap act_scale_map, const __grid_constant__ CUtensorMap weight_scale_map,
+                   const KernelArgs args) {
+    constexpr bool GEGLU = is_gated(EPI);
+    constexpr bool USES_TABLE = EPI != EPI_LINEAR;
+    constexpr bool NVFP4 = KIND == B2_KIND_NVFP4;
+    pdl_launch_dependents();
+    extern __shared__ uint8_t shared_raw[];
+    const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
+    const int BN = args.tile_n;
+    const int features_per_tile = GEGLU ? BN / 2 : BN;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+    // shared memory: [stages x (token tile 16 KB | half weight tile)][stages x (token atoms | feature atoms)][barriers][GELU table]
+    const uint32_t b_tile_bytes = uint32_t(BN / 2) * STAGE_K_BYTES;
+    const uint32_t stage_bytes = A_TILE_BYTES + b_tile_bytes;
+    constexpr uint32_t SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
+    const uint32_t scale_stage_bytes = NVFP4 ? (1u + uint32_t(args.scale_blocks)) * SCALE_PART_BYTES : 0u;
+    const uint32_t stage_base = base;
+    const uint32_t scale_base = stage_base + uint32_t(args.stages) * stage_bytes;
+    const uint32_t barrier_base = scale_base + uint32_t(args.stages) * scale_stage_bytes;
+    const uint32_t full_bar = barrier_base;                       // [stages]  used in the leader only
+    const uint32_t empty_bar = barrier_base + 8 * MAX_STAGES;     // [stages]  one per CTA
+    const uint32_t acc_full_bar = barrier_base + 16 * MAX_STAGES; // [2]       one per CTA
+    const uint32_t acc_empty_bar = acc_full_bar + 16;             // [2]       used in the leader only
+    const uint32_t tmem_slot = acc_empty_bar + 16;
+    const uint32_t compact_table = tmem_slot + 16;                // 2 * (gelu_hi - gelu_lo) bf16 entries
+    // the leader's barriers as the peer addresses them
+    const uint32_t full_bar_leader = cluster_map_shared(full_bar, 0u);
+    const uint32_t acc_empty_bar_leader = cluster_map_shared(acc_empty_bar, 0u);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&act_map);
+        tma_prefetch_descriptor(&weight_map);
+        if (NVFP4) {
+            tma_prefetch_descriptor(&act_scale_map);
+            tma_prefetch_descriptor(&weight_scale_map);
+        }
+        for (int s = 0; s < args.stages; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar + 8 * b, 1);
+            mbar_init(acc_empty_bar + 8 * b, 2 * epilogue_warps(EPI));     // the epilogue warps of both CTAs
+        }
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, TMEM_COLUMNS);
+        tmem_relinquish_pair();
+    }
+    if (USES_TABLE) {
+        const int span = args.gelu_hi - args.gelu_lo;
+        for (int i = threadIdx.x; i < 2 * span; i += gemm_threads(EPI)) {
+            const int code = i < span ? args.gelu_lo + i : 0x8000 + args.gelu_lo + (i - span);
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(compact_table + 2u * uint32_t(i)), "h"(__ldg(args.gelu_table + code)) : "memory");
+        }
+    }
+    // Both CTAs' barriers and tensor memory exist before either touches the other's.
+    tc_fence_before_sync();
+    cluster_arrive();
+    cluster_wait();
+    tc_fence_after_sync();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+    pdl_wait();
+
+    bool failed = false;
+    const int num_kb = args.num_kb;
+    const int last_kb_mmas = ((args.k_bytes - (num_kb - 1) * STAGE_K_BYTES) + 31) / 32;
+    // bytes one CTA brings per stage; boxes that reach beyond a matrix are filled with zeros and still count in full
+    const uint32_t stage_tx_bytes = stage_bytes + scale_stage_bytes;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer (both CTAs)
+        int stage = 0;
+        uint32_t phase = 0;
+        uint32_t filled = 0, fill_parity = 0;
+        for (PairWalk walk(args); walk.valid(args); walk.next(args)) {
+            const int m0 = walk.m_pair * PAIR_TOKENS + int(rank) * TILE_TOKENS;
+            const int f0 = walk.n_tile * features_per_tile;
+            // this CTA's half of the weight tile: plain -> rows [f0 + rank*BN/2, +BN/2); gated -> the gate rows (leader)
+            // or the up rows (peer) of features [f0, f0 + BN/2)
+            const int weight_row = GEGLU ? int(rank) * args.up_row_offset + f0 : f0 + int(rank) * (BN / 2);
+            // scale atoms: token rows of this CTA; feature rows of the WHOLE tile (every SM scales all BN columns)
+            const int token_atom_row = (2 * walk.m_pair + int(rank)) * args.scale_column_tiles;
+            int feature_atom_row[2];
+            feature_atom_row[0] = (f0 >> 7) * args.scale_column_tiles;
+            feature_atom_row[1] = (GEGLU ? ((args.up_row_offset + f0) >> 7) : (f0 >> 7) + 1) * args.scale_column_tiles;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
+                __syncwarp();
+                filled |= 1u << stage;
+                fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
+                if (elect_one()) {
+                    const uint32_t bar = full_bar_leader + 8 * stage;
+                    const uint32_t a_smem = stage_base + uint32_t(stage) * stage_bytes;
+                    const int k0 = kb * STAGE_K_BYTES;
+                    if (leader) mbar_expect_tx(full_bar + 8 * stage, 2u * stage_tx_bytes);
+                    tma_load_2d_pair(a_smem, &act_map, bar, k0, m0);
+                    tma_load_2d_pair(a_smem + A_TILE_BYTES, &weight_map, bar, k0, weight_row);
+                    if (NVFP4) {
+                        const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
+                        const int atom = kb * SCALE_ATOMS_PER_STAGE;
+                        tma_load_2d_pair(s_smem, &act_scale_map, bar, 0, token_atom_row + atom);
+                        tma_load_2d_pair(s_smem + SCALE_PART_BYTES, &weight_scale_map, bar, 0, feature_atom_row[0] + atom);
+                        if (args.scale_blocks == 2)
+                            tma_load_2d_pair(s_smem + 2 * SCALE_PART_BYTES, &weight_scale_map, bar, 0, feature_atom_row[1] + atom);
+                    }
+                }
+                __syncwarp();
+                if (++stage == args.stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+        // The leader does not leave while a copy of the pair is still in flight: wait (bounded) for the last fill of
+        // every stage.  On the normal path these have all completed already.
+        if (leader) {
+            bool drain_failed = false;
+            for (int s = 0; s < args.stages; ++s)
+                if (filled & (1u << s))
+                    mbar_wait(full_bar + 8 * s, (fill_parity >> s) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer (leader only)
+        if (leader) {
+            auto mma_role = [&](auto two_blocks_tag) {
+                constexpr bool TWO = decltype(two_blocks_tag)::value;
+                const uint32_t idesc = NVFP4 ? idesc_nvf4_pair(uint32_t(BN)) : idesc_f8_pair(uint32_t(BN));
+                const uint64_t operand_desc = smem_desc_sw128(0);
+                const uint32_t operand_low = uint32_t(operand_desc), operand_high = uint32_t(operand_desc >> 32);
+                const uint64_t scale_desc = smem_desc_scale_atom(0);
+                const uint32_t scale_desc_high = uint32_t(scale_desc >> 32);
+                const uint32_t set_columns = uint32_t(TMEM_SFA_COLUMNS + 16 * args.scale_blocks);
+                int stage = 0;
+                uint32_t phase = 0;
+                int local_tile = 0;
+                int set = 0, lag_stage = 0, issued = 0;
+                uint32_t lag_phase = 0;
+                for (PairWalk walk(args); walk.valid(args); walk.next(args), ++local_tile) {
+                    const int f0 = walk.n_tile * features_per_tile;
+                    // a 64- or 128-column tile that starts inside a 128-row scale block starts at that block's column
+                    const uint32_t scale_column = (GEGLU || BN == 256) ? 0u : uint32_t((f0 & 127) >> 5);
+                    const int buffer = local_tile % args.accumulators;
+                    const uint32_t use = uint32_t(local_tile / args.accumulators);
+                    mbar_wait(acc_empty_bar + 8 * buffer, (use & 1u) ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + uint32_t(buffer * args.accumulator_stride);
+                    for (int kb = 0; kb < num_kb; ++kb) {
+                        mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
+                        tc_fence_after_sync();
+                        const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
+                        const uint32_t stage_smem = stage_base + uint32_t(stage) * stage_bytes;
+                        const uint32_t a_low = operand_low + (stage_smem >> 4);
+                        const uint32_t b_low = operand_low + ((stage_smem + A_TILE_BYTES) >> 4);
+                        const uint32_t set_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t(set + 1);
+                        const uint32_t sfa_tmem = set_tmem;
+                        const uint32_t sfb_tmem = set_tmem + TMEM_SFA_COLUMNS;
+                        if (NVFP4) {
+                            // a set of scale columns is overwritten only after the MMAs that last read it have completed
+                            if (issued >= args.scale_sets) {
+                                mbar_wait(empty_bar + 8 * lag_stage, lag_phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
+                                tc_fence_after_sync();
+                                if (++lag_stage == args.stages) { lag_stage = 0; lag_phase ^= 1u; }
+                            }
+                            ++issued;
+                        }
+                        __syncwarp();
+                        if (elect_one()) {
+                            const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes) >> 4;
+                            constexpr uint32_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
+                            const uint32_t feature_low = atom_low + PART;
+                            const uint32_t first_accumulate = kb != 0;
+                            auto issue = [&](const int count) {
+                                if (NVFP4) {
+#pragma unroll
+                                    for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
+                                        if (j < count) {
+                                            tc_copy_32x128b_x4_pair(sfa_tmem + j * 4, desc_from_words(atom_low + j * ATOM, scale_desc_high));
+                                            tc_copy_32x128b_x4_pair(sfb_tmem + j * (TWO ? 8 : 4), desc_from_words(feature_low + j * ATOM, scale_desc_high));
+                                            if (TWO)
+                                                tc_copy_32x128b_x4_pair(sfb_tmem + j * 8 + 4, desc_from_words(feature_low + PART + j * ATOM, scale_desc_high));
+                                        }
+                                    }
+                                }
+#pragma unroll
+                                for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
+                                    if (j < count) {
+                                        const uint32_t accumulate = j == 0 ? first_accumulate : 1u;
+                                        const uint64_t a_desc = desc_from_words(a_low + 2 * j, operand_high);
+                                        const uint64_t b_desc = desc_from_words(b_low + 2 * j, operand_high);
+                                        if (NVFP4)
+                                            mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4,
+                                                          sfb_tmem + j * (TWO ? 8 : 4) + scale_column, accumulate);
+                                        else
+                                            mma_f8f6f4_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
+                                    }
+                                }
+                            };
+                            if (mmas == SCALE_ATOMS_PER_STAGE) issue(SCALE_ATOMS_PER_STAGE);
+                            else issue(mmas);
+                            tc_commit_pair(empty_bar + 8 * stage, 3);     // the stage is free again in both CTAs
+                        }
+                        __syncwarp();
+                        if (NVFP4 && ++set == args.scale_sets) set = 0;
+                        if (++stage == args.stages) { stage = 0; phase ^= 1u; }
+                    }
+                    if (elect_one()) tc_commit_pair(acc_full_bar + 8 * buffer, 3);
+                    __syncwarp();
+                }
+            };
+            if (NVFP4 && args.scale_blocks == 2) mma_role(std::true_type{});
+            else mma_role(std::false_type{});
+        }
+    } else {
+        // ------------------------------------------------------------- epilogue (both CTAs, own 128 tokens)
+        const int quarter = warp & 3;
+        const bool round_scale = (args.flags & B2_LINEAR_ROUND_SCALE_BF16) != 0;
+        float scale = __fmul_rn(__ldg(args.act_scale), __ldg(args.weight_scale));
+        if (round_scale) scale = round_to_bf16(scale);
+        float scale_up = scale;
+        if (GEGLU && args.weight_scale_up != nullptr) {
+            scale_up = __fmul_rn(__ldg(args.act_scale), __ldg(args.weight_scale_up));
+            if (round_scale) scale_up = round_to_bf16(scale_up);
+        }
+        float out_scale_value = 1.0f, out_scale_rcp = 1.0f;
+        if (EPI == EPI_GEGLU_FP8 || EPI == EPI_GEGLU_NVFP4 || EPI == EPI_GELU_FP8) {
+            out_scale_value = __ldg(args.out_scale);
+            out_scale_rcp = __fdiv_rn(1.0f, out_scale_value);
+        }
+        const ExactDivider out_scale(out_scale_value);
+        const ExactDivider by_global(__fmul_rn(6.0f, out_scale_value));
+        const bool true_div = (args.flags & B2_GEGLU_TRUE_DIV) != 0;
+        constexpr int WARPS_PER_QUARTER = epilogue_warps(EPI) / 4;
+        const int part = (warp - FIRST_EPILOGUE_WARP) >> 2;
+        int local_tile = 0;
+        for (PairWalk walk(args); walk.valid(args); walk.next(args), ++local_tile) {
+            const int token0 = walk.m_pair * PAIR_TOKENS + int(rank) * TILE_TOKENS + quarter * 32;
+            const int token = token0 + lane;
+            const int f0 = walk.n_tile * features_per_tile;
+            const int buffer = local_tile % args.accumulators;
+            const uint32_t use = uint32_t(local_tile / args.accumulators);
+            mbar_wait(acc_full_bar + 8 * buffer, use & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
+            tc_fence_after_sync();
+            const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer * args.accumulator_stride);
+            const bool warp_has_tokens = token0 < args.tokens;      // else: padding rows only
+            if (GEGLU) {
+                const int units = features_per_tile / 16;
+                for (int unit = part; unit < units && warp_has_tokens; unit += WARPS_PER_QUARTER) {
+                    uint32_t first[16], second[16];
+                    tmem_load_32x16(lane_address + unit * 16, first);
+                    tmem_load_32x16(lane_address + BN / 2 + unit * 16, second);
+                    tmem_load_wait();
+                    epilogue_geglu_unit<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, compact_table, scale, scale_up,
+                                                                     round_scale, out_scale, by_global, out_scale_rcp,
+                                                                     true_div, token, f0 + unit * 16);
+                }
+            } else {
+                const int chunks = features_per_tile / 32;
+                for (int chunk = part; chunk < chunks && warp_has_tokens; chunk += WARPS_PER_QUARTER) {
+                    uint32_t first[32];
+                    tmem_load_32x32(lane_address + chunk * 32, first);
+                    tmem_load_wait();
+                    epilogue_linear_chunk<GEGLU ? EPI_LINEAR : EPI>(first, args, scale, round_scale, token, f0 + chunk * 32, compact_table,
+                                                                    out_scale, out_scale_rcp, true_div);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(acc_empty_bar + 8 * buffer);
+                else mbar_arrive_cluster(acc_empty_bar_leader + 8 * buffer);
+            }
+        }
+    }
+
+    // Neither CTA leaves (or frees tensor memory) while the other may still read its shared memory, write its
+    // barriers or run MMAs into its tensor memory.
+    tc_fence_before_sync();
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+
+// Scale atoms ([row blocks][column tiles] x 512 bytes, the 128x4-tile layout) as a matrix of 512-byte rows: one box =
+// the four atoms of a K stage.  Rows beyond the array read as zero.
+static bool make_atom_map(CUtensorMap* map, const void* pointer, int64_t atoms) {
+    EncodeTiledFn encode = encode_tiled_entry();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[2] = {cuuint64_t(SCALE_ATOM_BYTES / 4), cuuint64_t(atoms)};
+    const cuuint64_t strides[1] = {cuuint64_t(SCALE_ATOM_BYTES)};
+    const cuuint32_t box[2] = {cuuint32_t(SCALE_ATOM_BYTES / 4), cuuint32_t(SCALE_ATOMS_PER_STAGE)};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(pointer), dims, strides, box, element_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int KIND, int EPI>
+static int launch_pair(const CUtensorMap& act_map, const CUtensorMap& weight_map, const CUtensorMap& act_scale_map,
+                       const CUtensorMap& weight_scale_map, const KernelArgs& args, int shared_bytes, cudaStream_t stream) {
+    static bool configured[64] = {false};
+    static std::mutex lock;
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 0 && device < 64) {
+        std::lock_guard<std::mutex> guard(lock);
+        if (!configured[device]) {
+            const cudaError_t error = cudaFuncSetAttribute(pair_linear_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+            if (error != cudaSuccess) return int(error);
+            configured[device] = true;
+        }
+    }
+    const int clusters = args.total_tiles < sm_count() / 2 ? args.total_tiles : sm_count() / 2;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(unsigned(2 * clusters));
+    config.blockDim = dim3(unsigned(gemm_threads(EPI)));
+    config.dynamicSmemBytes = size_t(shared_bytes);
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 2;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = pdl_enabled() ? 2 : 1;
+    const cudaError_t error = cudaLaunchKernelEx(&config, pair_linear_kernel<KIND, EPI>, act_map, weight_map, act_scale_map,
+                                                 weight_scale_map, args);
+    return error == cudaSuccess ? int(cudaGetLastError()) : int(error);
+}
+
+// Columns of one accumulator for a launch the paired schedule takes, or 0 when it does not apply:
+//   more than one 128-token tile; no split K; the bundle-order scale layout (a tile's feature scales are whole
+//   128-row blocks: plain 128 or 256 features per tile, gated 128 + 128).
+int pair_tile_columns(const b2_linear_desc* d, bool geglu) {
+    if (d->tokens <= TILE_TOKENS) return 0;
+    if (d->flags & (B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRED_GATE_UP_SCALES)) return 0;
+    const bool nvfp4 = d->kind == B2_KIND_NVFP4;
+    if (geglu) {
+        if (d->feature_tile != 0 && d->feature_tile != 128) return 0;
+        if (nvfp4 && d->features % 128 != 0) return 0;
+        return 256;
+    }
+    if (d->feature_tile == 128 || d->feature_tile == 256) return d->feature_tile;
+    if (d->feature_tile != 0) return 0;
+    // fill the machine: the wider tile moves fewer operand bytes per MMA, the narrower one gives more work items
+    const int pairs = (d->tokens + PAIR_TOKENS - 1) / PAIR_TOKENS;
+    const int64_t wide_items = int64_t(pairs) * ((d->features + 255) / 256);
+    return wide_items >= sm_count() / 2 ? 256 : 128;
+}
+
+int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, cudaStream_t stream) {
+    const bool nvfp4 = d->kind == B2_KIND_NVFP4;
+    const bool geglu = is_gated(epilogue);
+    KernelArgs args{};
+    args.tokens = d->tokens;
+    args.features = d->features;
+    args.k_bytes = nvfp4 ? d->width / 2 : d->width;
+    args.num_kb = (args.k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+    args.num_m_tiles = (d->tokens + PAIR_TOKENS - 1) / PAIR_TOKENS;
+    args.tile_n = tile_columns;
+    const int features_per_tile = geglu ? tile_columns / 2 : tile_columns;
+    args.num_n_tiles = (d->features + features_per_tile - 1) / features_per_tile;
+    args.total_tiles = args.num_m_tiles * args.num_n_tiles;
+    args.splits = 1;
+    args.scale_blocks = tile_columns > 128 ? 2 : 1;
+    args.up_row_offset = d->features;
+    args.scale_column_tiles = nvfp4 ? (d->width / 16 + 3) / 4 : 0;
+    args.act_row_blocks = (d->tokens + 127) / 128;
+    const int weight_rows = (geglu ? 2 : 1) * d->features;
+    args.weight_row_blocks = (weight_rows + 127) / 128;
+    args.flags = d->flags;
+    args.act_scales = static_cast<const uint8_t*>(d->act_scales);
+    args.weight_scales = static_cast<const uint8_t*>(d->weight_scales);
+    args.act_scale = static_cast<const float*>(d->act_scale);
+    args.weight_scale = static_cast<const float*>(d->weight_scale);
+    args.weight_scale_up = geglu ? static_cast<const float*>(d->weight_scale_up) : nullptr;
+    args.bias = static_cast<const __nv_bfloat16*>(d->bias);
+    args.residual = static_cast<const __nv_bfloat16*>(d->residual);
+    args.gelu_table = static_cast<const uint16_t*>(d->gelu_table);
+    args.out_scale = static_cast<const float*>(d->out_scale);
+    args.out = d->out;
+    args.out_scales = static_cast<uint8_t*>(d->out_scales);
+    args.out_blocked = static_cast<uint8_t*>(d->out_blocked);
+    args.status = static_cast<unsigned int*>(d->status);
+    args.gelu_lo = args.gelu_hi = 0;
+    if (epilogue != EPI_LINEAR && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
+        d->gelu_hi - d->gelu_lo <= MAX_COMPACT_GELU) {
+        args.gelu_lo = d->gelu_lo;
+        args.gelu_hi = d->gelu_hi;
+    }
+
+    // tensor memory: accumulators from column 0, (NVFP4) sets of scale columns stacked down from column 512
+    const int set_columns = TMEM_SFA_COLUMNS + 16 * args.scale_blocks;
+    if (nvfp4) {
+        args.accumulators = 2 * tile_columns + 2 * set_columns <= TMEM_COLUMNS ? 2 : 1;
+        args.accumulator_stride = tile_columns;
+    } else {
+        args.accumulators = 2;
+        args.accumulator_stride = 256;
+    }
+    constexpr int SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
+    const int stage_bytes = A_TILE_BYTES + (tile_columns / 2) * STAGE_K_BYTES + (nvfp4 ? (1 + args.scale_blocks) * SCALE_PART_BYTES : 0);
+    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 128 + 4 * (args.gelu_hi - args.gelu_lo);
+    int stages = (SMEM_LIMIT - fixed_bytes) / stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) return B2_E_UNSUPPORTED;
+    args.stages = stages;
+    args.scale_sets = 1;
+    if (nvfp4) {
+        args.scale_sets = (TMEM_COLUMNS - args.accumulators * args.accumulator_stride) / set_columns;
+        if (args.scale_sets > stages) args.scale_sets = stages;
+        if (args.scale_sets < 2) return B2_E_UNSUPPORTED;
+    }
+    int shared_bytes = fixed_bytes + stages * stage_bytes;
+    if (shared_bytes < SMEM_MINIMUM) shared_bytes = SMEM_MINIMUM;
+
+    CUtensorMap act_map, weight_map, act_scale_map, weight_scale_map;
+    if (!make_operand_map(&act_map, d->act, d->tokens, args.k_bytes, TILE_TOKENS)) return B2_E_DRIVER;
+    if (!make_operand_map(&weight_map, d->weight, weight_rows, args.k_bytes, tile_columns / 2)) return B2_E_DRIVER;
+    if (nvfp4) {
+        if (!make_atom_map(&act_scale_map, d->act_scales, int64_t(args.act_row_blocks) * args.scale_column_tiles)) return B2_E_DRIVER;
+        if (!make_atom_map(&weight_scale_map, d->weight_scales, int64_t(args.weight_row_blocks) * args.scale_column_tiles))
+            return B2_E_DRIVER;
+    } else {
+        act_scale_map = act_map;          // never dereferenced by the FP8 kernels
+        weight_scale_map = weight_map;
+    }
+
+#define B2_PAIR_CASE(kind, epi) \
+    case epi: return launch_pair<kind, epi>(act_map, weight_map, act_scale_map, weight_scale_map, args, shared_bytes, stream)
+    if (nvfp4) {
+        switch (epilogue) {
+            B2_PAIR_CASE(B2_KIND_NVFP4, EPI_LINEAR);
+            B2_PAIR_CASE(B2_KIND_NVFP4, EPI_GEGLU_BF16);
+            B2_PAIR_CASE(B2_KIND_NVFP4, EPI_GEGLU_FP8);
+            B2_PAIR_CASE(B2_KIND_NVFP4, EPI_GEGLU_NVFP4);
+            B2_PAIR_CASE(B2_KIND_NVFP4, EPI_GELU_BF16);
+            B2_PAIR_CASE(B2_KIND_NVFP4, EPI_GELU_FP8);
+            default: return B2_E_UNSUPPORTED;
+        }
+    }
+    switch (epilogue) {
+        B2_PAIR_CASE(B2_KIND_FP8, EPI_LINEAR);
+        B2_PAIR_CASE(B2_KIND_FP8, EPI_GEGLU_BF16);
+        B2_PAIR_CASE(B2_KIND_FP8, EPI_GEGLU_FP8);
+        B2_PAIR_CASE(B2_KIND_FP8, EPI_GEGLU_NVFP4);
+        B2_PAIR_CASE(B2_KIND_FP8, EPI_GELU_BF16);
+        B2_PAIR_CASE(B2_KIND_FP8, EPI_GELU_FP8);
+        default: return B2_E_UNSUPPORTED;
+    }
+#undef B2_PAIR_CASE
+}
+
+}  // namespace b2

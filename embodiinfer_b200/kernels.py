@@ -9,7 +9,6 @@ These are the calls the plan objects (``embodiinfer_b200.backend``) and the regi
 from __future__ import annotations
 
 import ctypes
-import os
 
 import torch
 
@@ -293,8 +292,6 @@ def frames_to_patches(frames: torch.Tensor, patches: torch.Tensor, patch: int) -
     N.check(status, "b2_frames_to_patches")
 
 
-# B2_CLUSTER_SPLIT=1 in the environment asks every eligible launch for the cluster split of K (measurement aid).
-_CLUSTER_SPLIT = os.environ.get("B2_CLUSTER_SPLIT", "") not in ("", "0")
 _WORKSPACE_BYTES = 32 << 20
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
@@ -346,8 +343,6 @@ def linear(
         act, act_scale, weight, weight_scale, out, act_scales, weight_scales, weight_scale_up, bias, residual, gelu_table, out_scale,
         out_scales, out_blocked, status,
     )
-    if _CLUSTER_SPLIT:
-        flags |= N.LINEAR_CLUSTER_SPLIT
     desc = N.LinearDesc(
         kind=kind,
         epilogue=epilogue,

@@ -21,9 +21,11 @@
 extern "C" {
 #endif
 
-/* 3: adds the producers in front of the GEMMs (b2_norm_quant, b2_layer_norm_quant, b2_bhsd_quant, b2_normalize_frames,
- * b2_frames_to_patches, b2_resize_frames) and B2_LINEAR_CLUSTER_SPLIT; everything of version 2 is unchanged. */
-#define B2_ABI_VERSION 3
+/* 4: launches with more than 128 tokens run on pairs of SMs (B2_LINEAR_SINGLE_CTA opts out); unknown flag bits in
+ * b2_linear_desc are rejected; the opt-in cluster split of K of version 3 (flag value 32) is gone.
+ * 3: added the producers in front of the GEMMs (b2_norm_quant, b2_layer_norm_quant, b2_bhsd_quant, b2_normalize_frames,
+ * b2_frames_to_patches, b2_resize_frames). */
+#define B2_ABI_VERSION 4
 
 /* ---- status codes ---------------------------------------------------------- */
 #define B2_OK 0
@@ -122,19 +124,16 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
 #define B2_LINEAR_STREAM_TOKENS 8 /* tuning aid: always load the token tile with every K stage.  By default a CTA keeps its
                                      128-token tile (all of K) and the token scales on chip whenever they fit and it computes
                                      several feature tiles of that token tile; results are identical either way. */
-#define B2_LINEAR_CLUSTER_SPLIT 32 /* opt-in: a plain-epilogue launch with one token tile (M <= 128) whose feature tiles leave most
-                                     SMs idle runs 2, 4 or 8 CTAs per tile as one thread-block cluster: each takes a K range, ranks 1..
-                                     write their fp32 partial sums into rank 0's shared memory (distributed shared memory), a
-                                     cluster barrier orders them, rank 0 adds them in rank order (deterministic) and runs the
-                                     epilogue.  No workspace.  Off by default: on B200 a cluster launch costs several microseconds
-                                     more than it saves at the shapes measured (10x2560x1024 FP8: 9.2 vs 5.4 us).  The fp32 summation order differs
-                                     from the unsplit launch. */
+#define B2_LINEAR_SINGLE_CTA 64 /* tuning / test aid: never use the paired schedule.  By default a launch with more than 128 tokens
+                                  runs 256-token tiles on pairs of SMs (two CTAs of a thread-block cluster, `tcgen05.mma.cta_group::2`):
+                                  each CTA loads its 128 token rows and half of the weight tile.  The accumulation order along K is
+                                  the same in both schedules, so results are identical either way. */
 
 typedef struct b2_linear_desc {
     int32_t kind;        /* B2_KIND_* */
     int32_t epilogue;    /* B2_EPI_* */
     int32_t out_format;  /* B2_OUT_* */
-    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_LINEAR_CLUSTER_SPLIT | B2_GEGLU_TRUE_DIV */
+    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_LINEAR_SINGLE_CTA | B2_GEGLU_TRUE_DIV; any other bit: B2_E_INVALID */
     int32_t tokens;      /* M: rows of the activation matrix */
     int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
     int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */

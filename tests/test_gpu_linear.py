@@ -216,35 +216,130 @@ def test_split_k_is_deterministic_and_matches_oracle(device, kind, epilogue, tok
     assert_gemm_close(outputs[2], want)
 
 
+def run_linear(device, dev, *, tokens, features, width, flags=0, tile=0, **extra):
+    """One plain launch with a guard row behind the output and the status word checked."""
+    out = torch.full((tokens + 1, features), float("nan"), device=device, dtype=torch.bfloat16)
+    status = torch.zeros(1, device=device, dtype=torch.int32)
+    K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out[:tokens],
+             status=status, flags=flags, feature_tile=tile, **extra, **dev)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.isnan(out[tokens]).all(), "wrote past the last token row"
+    return out[:tokens]
+
+
 @pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
-@pytest.mark.parametrize("tokens,features,width", [(10, 2560, 1024), (10, 1024, 2048), (10, 1024, 4096), (80, 1024, 4096),
-                                                   (128, 2048, 2048), (1, 64, 1024), (33, 192, 8192)])
-def test_cluster_split_k(device, kind, tokens, features, width):
-    """One token tile, plain epilogue, few feature tiles, on request (B2_LINEAR_CLUSTER_SPLIT): K is cut across the
-    CTAs of a thread-block cluster and the partial sums meet in the leader's shared memory.  Same bits on every run
-    (fixed rank order), within the GEMM tolerance of the oracle; bias and residual are applied once, by the leader."""
-    host, dev = operands(kind, tokens, features, width, 7 + tokens + width, device)
+@pytest.mark.parametrize("tokens,features,width,tile", [(129, 256, 256, 0), (256, 512, 1024, 256), (257, 384, 512, 128), (560, 2048, 2048, 0),
+                                                         (560, 2048, 2048, 256), (700, 1152, 1152, 128), (1024, 4096, 512, 0), (300, 200, 320, 0)])
+def test_paired_schedule_equals_single_cta(device, kind, tokens, features, width, tile):
+    """More than 128 tokens: pairs of SMs compute 256-token tiles (`tcgen05.mma.cta_group::2`), each CTA loading its
+    own token rows and half of the weight tile.  B2_LINEAR_SINGLE_CTA keeps one CTA per 128-token tile.  The two
+    schedules accumulate along K in the same order: identical bits, with bias and residual, and within the GEMM
+    tolerance of the oracle."""
+    host, dev = operands(kind, tokens, features, width, 3 + tokens + features, device)
     bias = make_weight((1, features), 91, std=0.5).reshape(-1).to(torch.bfloat16).to(device)
     residual = make_input((tokens, features), 92, outliers=False).to(device)
-
-    def run(flags, **extra):
-        out = torch.full((tokens + 1, features), float("nan"), device=device, dtype=torch.bfloat16)
-        status = torch.zeros(1, device=device, dtype=torch.int32)
-        K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out[:tokens],
-                 status=status, flags=flags, **extra, **dev)
-        torch.cuda.synchronize()
-        assert int(status.item()) == 0
-        assert torch.isnan(out[tokens]).all(), "wrote past the last token row"
-        return out[:tokens]
-
-    plain = run(N.LINEAR_CLUSTER_SPLIT)
-    assert torch.equal(plain, run(N.LINEAR_CLUSTER_SPLIT))
+    common = dict(tokens=tokens, features=features, width=width, tile=tile)
+    paired = run_linear(device, dev, **common)
+    single = run_linear(device, dev, flags=N.LINEAR_SINGLE_CTA, **common)
+    assert torch.equal(paired.view(torch.int16), single.view(torch.int16))
     want = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
-    assert_gemm_close(bits(plain), want)
-    assert_gemm_close(bits(run(0)), want)
-    # bias and residual in the leader's epilogue: exactly the separate bf16 adds on the launch's own plain result
-    full = run(N.LINEAR_CLUSTER_SPLIT, bias=bias, residual=residual)
-    assert torch.equal(full, (plain + bias) + residual)
+    assert_gemm_close(bits(paired), want)
+    full = run_linear(device, dev, bias=bias, residual=residual, **common)
+    assert torch.equal(full, (paired + bias) + residual)
+
+
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+@pytest.mark.parametrize("out_format", ("bf16", "fp8", "nvfp4"))
+def test_paired_schedule_gated_equals_single_cta(device, kind, out_format):
+    """The gated epilogue on pairs: the leader CTA loads the gate rows of a tile, its peer the up rows; every encoded
+    output (codes, row-major and tiled block scales) equals the single-CTA schedule's bit for bit."""
+    tokens, features, width = 330, 512, 1024
+    host, dev = operands(kind, tokens, 2 * features, width, 17, device)
+    table = torch.from_numpy(gelu_table_cpu("tanh").view(np.int16).copy()).view(torch.uint16).to(device)
+    common = dict(epilogue=N.EPI_GEGLU, tokens=tokens, features=features, width=width, gelu_table=table,
+                  gelu_range=K.gelu_table_range(table), **dev)
+    results = []
+    for flags in (0, N.LINEAR_SINGLE_CTA):
+        status = torch.zeros(1, device=device, dtype=torch.int32)
+        if out_format == "bf16":
+            out = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+            K.linear(out_format=N.OUT_BF16, out=out, flags=flags, status=status, **common)
+            results.append((bits(out),))
+        elif out_format == "fp8":
+            out = torch.empty((tokens, features), device=device, dtype=torch.uint8)
+            K.linear(out_format=N.OUT_FP8, out=out, out_scale=torch.tensor(0.01, device=device), flags=flags, status=status, **common)
+            results.append((u8(out),))
+        else:
+            out = torch.empty((tokens, features // 2), device=device, dtype=torch.uint8)
+            linear = torch.empty((tokens, features // 16), device=device, dtype=torch.uint8)
+            blocked = torch.zeros(blocked_scale_bytes(tokens, features), device=device, dtype=torch.uint8)
+            K.linear(out_format=N.OUT_NVFP4, out=out, out_scales=linear, out_blocked=blocked,
+                     out_scale=torch.tensor(0.002, device=device), flags=flags, status=status, **common)
+            results.append((u8(out), u8(linear), u8(blocked)))
+        assert int(status.item()) == 0
+    for got, want in zip(*results):
+        assert np.array_equal(got, want)
+
+
+TAIL_TOKENS = list(range(1, 18)) + [127, 128, 129, 255, 256, 257, 559, 560, 561]
+
+
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+def test_token_tail_sweep(device, kind):
+    """Every token count around the tile boundaries (1..17, 127..129, 255..257, 559..561) at one small shape: each
+    launch is the oracle's result on its own rows and writes nothing behind its last row."""
+    features, width = 192, 256
+    host, dev = operands(kind, max(TAIL_TOKENS), features, width, 41, device)
+    want = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+    for tokens in TAIL_TOKENS:
+        sliced = dict(dev)
+        sliced["act"] = dev["act"][:tokens].contiguous()
+        out = run_linear(device, sliced, tokens=tokens, features=features, width=width)
+        assert_gemm_close(bits(out), want[:tokens])
+
+
+def test_config1_full_size(device):
+    """Benchmark configuration 1 at full size: FP8 W8A8 560 x 16384 x 2048 (+ bias), every output element against
+    the oracle."""
+    tokens, features, width = 560, 16384, 2048
+    host, dev = operands("fp8", tokens, features, width, 1001, device)
+    bias = make_weight((1, features), 1001, std=0.1).to(torch.bfloat16).reshape(-1)
+    out = run_linear(device, dev, tokens=tokens, features=features, width=width, bias=bias.to(device))
+    assert_gemm_close(bits(out), O.fp8_linear(host["a"], host["a_s"], host["w"], host["w_s"], bits(bias)))
+
+
+def test_config2_full_size(device):
+    """Benchmark configuration 2 at full size, all 560 rows: the gated launch's bf16 hidden activation against the
+    oracle, its NVFP4 re-encoding bit for bit against the CUDA-route encoder on that hidden activation, and the down
+    projection of the re-encoded activation against the oracle."""
+    tokens, hidden_width, inter = 560, 2048, 16384
+    host, dev = operands("nvfp4", tokens, 2 * inter, hidden_width, 1002, device)
+    table_host = gelu_table_cpu("tanh")
+    table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+    common = dict(epilogue=N.EPI_GEGLU, tokens=tokens, features=inter, width=hidden_width, gelu_table=table,
+                  gelu_range=K.gelu_table_range(table), **dev)
+    hidden = torch.empty((tokens, inter), device=device, dtype=torch.bfloat16)
+    K.linear(out_format=N.OUT_BF16, out=hidden, **common)
+    y = O.f32_to_bf16((accumulate("nvfp4", host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+    assert_gemm_close(bits(hidden), O.gelu_mul(y[:, :inter], y[:, inter:], table_host))
+    got_hidden = bits(hidden)
+    scale4 = np.float32(float(np.abs(O.bf16_to_f32(got_hidden)).max()) / (448.0 * 6.0))
+    out4 = torch.empty((tokens, inter // 2), device=device, dtype=torch.uint8)
+    linear = torch.empty((tokens, inter // 16), device=device, dtype=torch.uint8)
+    blocked = torch.zeros(blocked_scale_bytes(tokens, inter), device=device, dtype=torch.uint8)
+    K.linear(out_format=N.OUT_NVFP4, out=out4, out_scales=linear, out_blocked=blocked,
+             out_scale=torch.tensor(float(scale4), device=device), **common)
+    want4 = O.nvfp4_quantize_C(got_hidden, scale4)
+    assert np.array_equal(u8(out4), want4[0]) and np.array_equal(u8(linear), want4[1]) and np.array_equal(u8(blocked), want4[2])
+    # down projection of the re-encoded activation (K = 16384)
+    w = bits(make_weight((hidden_width, inter), 1003).to(torch.bfloat16))
+    wp, wsl, wbl, w_s = O.nvfp4_quantize_C(w)
+    down = dict(kind=N.KIND_NVFP4, act=out4, act_scales=blocked, act_scale=torch.tensor(float(scale4), device=device),
+                weight=torch.from_numpy(wp).to(device), weight_scales=torch.from_numpy(wbl).to(device),
+                weight_scale=torch.tensor(float(w_s), device=device))
+    out = run_linear(device, down, tokens=tokens, features=hidden_width, width=inter)
+    assert_gemm_close(bits(out), O.nvfp4_linear_plan(want4[0], want4[1], scale4, wp, wsl, w_s))
 
 
 @pytest.mark.parametrize("kind,tokens,features,width", [("fp8", 256, 4304, 1152), ("fp8", 130, 384, 1024), ("nvfp4", 130, 384, 1024)])
@@ -314,6 +409,10 @@ def test_full_size_properties(device):
 
 def test_rejections(device):
     x = torch.zeros((8, 64), device=device, dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match="error -1"):     # a flag bit the library does not know
+        K.linear(kind=N.KIND_FP8, epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=8, features=16, width=64, act=x,
+                 act_scale=torch.ones((), device=device), weight=torch.zeros((16, 64), device=device, dtype=torch.uint8),
+                 weight_scale=torch.ones((), device=device), out=torch.zeros((8, 16), device=device, dtype=torch.bfloat16), flags=0x1000)
     w = torch.zeros((16, 64), device=device, dtype=torch.uint8)
     one = torch.ones((), device=device)
     out = torch.zeros((8, 16), device=device, dtype=torch.bfloat16)
