@@ -34,7 +34,9 @@ class B200NormQuant:
         minimum_sm=(10, 0),
     )
 
-    def __init__(self, quantizer: B200Quantizer) -> None:
+    def __init__(self, quantizer: B200Quantizer, norm: object | None = None) -> None:
+        """``norm`` is accepted because the reference's callers pass their normalisation backend
+        (operators.py:187-189); this kernel computes the statistics itself and does not use it."""
         if not isinstance(quantizer, B200Quantizer):
             raise ValueError("CUDA norm/encoding requires CUDA quantization and strict CUDA normalization")
         self.quantizer, self.device = quantizer, quantizer.device

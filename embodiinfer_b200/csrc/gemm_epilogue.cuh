@@ -71,6 +71,8 @@ struct KernelArgs {
     int a_box_bytes;             // bytes of the token box of one K stage: 128 rows, or fewer (a multiple of 8) when the launch has
                                  // one token tile with fewer tokens -- the rows beyond the box are whatever shared memory holds,
                                  // they only feed accumulator rows that are never stored
+    const uint8_t* weight;       // the weight matrix itself (operands travel by tensor map; this pointer feeds the L2 prefetches)
+    int weight_rows;
     unsigned int* tickets;       // split-K: one arrival counter per tile (zero between launches)
     float* partials;             // split-K: [tile][split][128][tile_n] fp32
 };

@@ -189,6 +189,40 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
     tc_fence_after_sync();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+
+    // L2 prefetch of a tile's weights.  A tile's weight rows are one contiguous range of memory (whole rows of the
+    // row-major matrix), while the K-stage loads of the main loop touch it as 128-byte pieces two kilobytes apart,
+    // which DRAM serves slowly and with a long tail (a stage lands when its slowest piece does).  So the producer asks
+    // for the whole range with bulk prefetches, one tile ahead: DRAM streams it, and the stage loads find it in the L2.
+    // The token pairs that share a feature tile run side by side and take one part of the range each.  A prefetch is
+    // only a hint to the L2, the coherence point of the device, so it may run ahead of the launches before this one.
+    auto prefetch_tile = [&](const PairWalk& walk) {
+        if (args.weight == nullptr || !elect_one()) return;
+        const int f0 = walk.n_tile * features_per_tile;
+        const int row = GEGLU ? int(rank) * args.up_row_offset + f0 : f0 + int(rank) * (BN / 2);
+        const int limit = GEGLU ? (int(rank) + 1) * args.up_row_offset : args.weight_rows;
+        const int rows = min(BN / 2, limit - row);
+        if (rows <= 0) return;
+        const int64_t bytes = int64_t(rows) * args.k_bytes;
+        const int64_t part = ((bytes + args.num_m_tiles - 1) / args.num_m_tiles + 127) & ~int64_t(127);
+        const int64_t begin = walk.m_pair * part;
+        const int64_t length = min(part, bytes - begin);
+        const uint8_t* source = args.weight + int64_t(row) * args.k_bytes + begin;
+        constexpr int64_t CHUNK = 32768;
+        for (int64_t offset = 0; offset < length; offset += CHUNK)
+            bulk_prefetch_l2(source + offset, uint32_t(min(CHUNK, length - offset)));
+        if (NVFP4 && walk.m_pair == 0 && int(rank) < args.scale_blocks) {
+            const int block = rank == 0 ? (f0 >> 7) : (GEGLU ? ((args.up_row_offset + f0) >> 7) : (f0 >> 7) + 1);
+            if (block < args.weight_row_blocks)
+                bulk_prefetch_l2(args.weight_scales + int64_t(block) * args.scale_column_tiles * SCALE_ATOM_BYTES,
+                                 uint32_t(args.scale_column_tiles * SCALE_ATOM_BYTES));
+        }
+    };
+    if (warp == 0) {
+        const PairWalk first(args);
+        if (first.valid(args)) prefetch_tile(first);
+        __syncwarp();
+    }
     pdl_wait();
 
     bool failed = false;
@@ -203,6 +237,12 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
         uint32_t phase = 0;
         uint32_t filled = 0, fill_parity = 0;
         for (PairWalk walk(args); walk.valid(args); walk.next(args)) {
+            {
+                PairWalk ahead = walk;
+                ahead.next(args);
+                if (ahead.valid(args)) prefetch_tile(ahead);
+                __syncwarp();
+            }
             const int m0 = walk.m_pair * PAIR_TOKENS + int(rank) * TILE_TOKENS;
             const int f0 = walk.n_tile * features_per_tile;
             // this CTA's half of the weight tile: plain -> rows [f0 + rank*BN/2, +BN/2); gated -> the gate rows (leader)
@@ -516,6 +556,8 @@ int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, cud
     args.out_scales = static_cast<uint8_t*>(d->out_scales);
     args.out_blocked = static_cast<uint8_t*>(d->out_blocked);
     args.status = static_cast<unsigned int*>(d->status);
+    args.weight = (d->flags & B2_LINEAR_NO_L2_PREFETCH) ? nullptr : static_cast<const uint8_t*>(d->weight);
+    args.weight_rows = weight_rows;
     args.gelu_lo = args.gelu_hi = 0;
     if (epilogue != EPI_LINEAR && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
         d->gelu_hi - d->gelu_lo <= MAX_COMPACT_GELU) {

@@ -4,6 +4,7 @@ Linear at the shapes of the pi0.5-style towers.  One JSON line per case.
     python -m embodiinfer_b200.kernel_bench                       # every case
     python -m embodiinfer_b200.kernel_bench --case 'linear/fp8'   # cases whose name matches the regex
     python -m embodiinfer_b200.kernel_bench --case cfg1 --library # also time torch's scaled_mm on the same shape
+    python -m embodiinfer_b200.kernel_bench --case cfg1 --eager 3 # three plain launches and no timing: the form to run under a profiler
 
 Method: each case is launched ``--launches`` times inside one CUDA graph, rotating over as many
 operand sets as it takes to exceed the L2 capacity (capped at 16 sets; ``"l2": "warm"`` marks the
@@ -42,9 +43,23 @@ def _blocked_bytes(rows: int, blocks: int) -> int:
     return -(-rows // 128) * 128 * (-(-blocks // 4) * 4)
 
 
+def run_eager(make, set_bytes: int, launches: int) -> int:
+    """``launches`` plain launches over rotating operand sets (no graph, no timing): what a profiler should see."""
+    sets = max(1, min(MAX_SETS, launches, -(-2 * L2_BYTES // max(set_bytes, 1))))
+    closures = [make(index) for index in range(sets)]
+    torch.cuda.synchronize()
+    for index in range(launches):
+        closures[index % sets]()
+    torch.cuda.synchronize()
+    return sets
+
+
+FORCED_SETS = 0       # --sets: 1 keeps every operand in the L2 between launches (warm), 0 = enough sets to exceed it
+
+
 def time_graph(make, set_bytes: int, launches: int, settle: float = 0.5) -> tuple[float, int]:
     """Average microseconds per launch; ``make(i)`` returns the launch closure of operand set ``i``."""
-    sets = max(1, min(MAX_SETS, -(-2 * L2_BYTES // max(set_bytes, 1))))
+    sets = FORCED_SETS or max(1, min(MAX_SETS, -(-2 * L2_BYTES // max(set_bytes, 1))))
     closures = [make(index) for index in range(sets)]
     for closure in closures[:2]:
         closure()
@@ -288,11 +303,15 @@ def main() -> None:
     parser.add_argument("--launches", type=int, default=32)
     parser.add_argument("--library", action="store_true", help="also time torch's scaled_mm at each linear shape")
     parser.add_argument("--list", action="store_true")
-    parser.add_argument("--flags", type=int, default=0, help="OR-ed into the b2_linear flags (8 = stream the token tile)")
+    parser.add_argument("--sets", type=int, default=0, help="operand sets in rotation (1 = warm L2; default: enough to exceed the L2)")
+    parser.add_argument("--eager", type=int, default=0, help="run this many plain launches per case and no timing (for profilers)")
+    parser.add_argument("--flags", type=int, default=0, help="OR-ed into the b2_linear flags (8 = stream the token tile, 64 = one CTA per tile)")
     parser.add_argument("--feature-tile", type=int, default=0, help="features per tile (0 = the library's choice)")
     parser.add_argument("--unpaired", action="store_true", help="gated NVFP4 cases without the paired gate/up scale layout")
     args = parser.parse_args()
     pattern = re.compile(args.case)
+    global FORCED_SETS
+    FORCED_SETS = max(0, args.sets)
     if args.list:
         for name, *_ in LINEAR_SHAPES:
             print("linear/" + name)
@@ -305,6 +324,9 @@ def main() -> None:
     for source in sources:
         for name, make, set_bytes, algorithmic_bytes, flops in source(device):
             if not pattern.search(name):
+                continue
+            if args.eager > 0:
+                print(json.dumps({"case": name, "eager_launches": args.eager, "sets": run_eager(make, set_bytes, args.eager)}), flush=True)
                 continue
             microseconds, sets = time_graph(make, set_bytes, args.launches)
             line = {"case": name, "us": round(microseconds, 2), "gbs": round(algorithmic_bytes / microseconds / 1e3, 1),

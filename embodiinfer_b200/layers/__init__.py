@@ -12,7 +12,7 @@ from .linear import (
     register_linear,
     resolve_linear_backend,
 )
-from .plans import gelu_mul_backends, projection_backends, quantization_backends
+from .plans import gelu_mul_backends, norm_quant_backends, projection_backends, quantization_backends
 from .registry import BackendRegistry, OperatorCapabilities, OperatorRequest
 
 __all__ = [
@@ -32,4 +32,5 @@ __all__ = [
     "quantization_backends",
     "projection_backends",
     "gelu_mul_backends",
+    "norm_quant_backends",
 ]

@@ -129,11 +129,13 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
                                   each CTA loads its 128 token rows and half of the weight tile.  The accumulation order along K is
                                   the same in both schedules, so results are identical either way. */
 
+#define B2_LINEAR_NO_L2_PREFETCH 128 /* tuning aid: the paired schedule does not prefetch the next tile's weight rows into the L2 */
+
 typedef struct b2_linear_desc {
     int32_t kind;        /* B2_KIND_* */
     int32_t epilogue;    /* B2_EPI_* */
     int32_t out_format;  /* B2_OUT_* */
-    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_LINEAR_SINGLE_CTA | B2_GEGLU_TRUE_DIV; any other bit: B2_E_INVALID */
+    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_LINEAR_SINGLE_CTA | B2_LINEAR_NO_L2_PREFETCH | B2_GEGLU_TRUE_DIV; any other bit: B2_E_INVALID */
     int32_t tokens;      /* M: rows of the activation matrix */
     int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
     int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */

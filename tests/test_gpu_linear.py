@@ -17,7 +17,7 @@ from embodiinfer_b200 import _native as N
 from embodiinfer_b200 import kernels as K
 from embodiinfer_b200.backend.quantization import blocked_scale_bytes
 from oracle import quant_oracle as O
-from tests.util import assert_gemm_close, bits, gelu_table_cpu, make_input, make_weight, u8
+from tests.util import assert_gated_close, assert_gemm_close, bits, gelu_table_cpu, make_input, make_weight, u8
 
 pytestmark = pytest.mark.gpu
 
@@ -300,13 +300,15 @@ def test_token_tail_sweep(device, kind):
 
 
 def test_config1_full_size(device):
-    """Benchmark configuration 1 at full size: FP8 W8A8 560 x 16384 x 2048 (+ bias), every output element against
-    the oracle."""
+    """Benchmark configuration 1 at full size: FP8 W8A8 560 x 16384 x 2048, every output element against the oracle;
+    then with a bias."""
     tokens, features, width = 560, 16384, 2048
     host, dev = operands("fp8", tokens, features, width, 1001, device)
-    bias = make_weight((1, features), 1001, std=0.1).to(torch.bfloat16).reshape(-1)
-    out = run_linear(device, dev, tokens=tokens, features=features, width=width, bias=bias.to(device))
-    assert_gemm_close(bits(out), O.fp8_linear(host["a"], host["a_s"], host["w"], host["w_s"], bits(bias)))
+    out = run_linear(device, dev, tokens=tokens, features=features, width=width)
+    assert_gemm_close(bits(out), O.fp8_linear(host["a"], host["a_s"], host["w"], host["w_s"]))
+    # the bias is a separate bf16 addition on that result (fp8.py:139-140)
+    bias = make_weight((1, features), 1001, std=0.1).to(torch.bfloat16).reshape(-1).to(device)
+    assert torch.equal(run_linear(device, dev, tokens=tokens, features=features, width=width, bias=bias), out + bias)
 
 
 def test_config2_full_size(device):
@@ -322,7 +324,7 @@ def test_config2_full_size(device):
     hidden = torch.empty((tokens, inter), device=device, dtype=torch.bfloat16)
     K.linear(out_format=N.OUT_BF16, out=hidden, **common)
     y = O.f32_to_bf16((accumulate("nvfp4", host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
-    assert_gemm_close(bits(hidden), O.gelu_mul(y[:, :inter], y[:, inter:], table_host))
+    assert_gated_close(bits(hidden), y[:, :inter], y[:, inter:], table_host)
     got_hidden = bits(hidden)
     scale4 = np.float32(float(np.abs(O.bf16_to_f32(got_hidden)).max()) / (448.0 * 6.0))
     out4 = torch.empty((tokens, inter // 2), device=device, dtype=torch.uint8)

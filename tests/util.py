@@ -61,6 +61,33 @@ def assert_gemm_close(got_bf16: np.ndarray, want_bf16: np.ndarray) -> None:
     assert worst.max() <= 0, f"max-abs violation {np.abs(got - want).max()}"
 
 
+def _bf16_neighbours(bits16: np.ndarray) -> list[np.ndarray]:
+    """The bf16 value itself and the two adjacent bf16 values (one unit in the last place either way)."""
+    b = bits16.astype(np.int32)
+    magnitude = b & 0x7FFF
+    up = np.where(magnitude < 0x7F7F, b + 1, b)
+    down = np.where(magnitude > 0, b - 1, (b ^ 0x8000) | 1)       # below +-0 lies the smallest value of the other sign
+    return [bits16, up.astype(np.uint16), down.astype(np.uint16)]
+
+
+def assert_gated_close(got_bf16: np.ndarray, gate_bf16: np.ndarray, up_bf16: np.ndarray, table_u16: np.ndarray) -> None:
+    """The fused gated epilogue against the oracle's gate and up projections.
+
+    h = bf16(bf16(gelu(gate)) * up) amplifies a one-ulp difference of gate or up (two correct fp32 accumulation orders
+    can round to adjacent bf16 values) by the other factor, so a bound on |h - h_oracle| alone says little.  Instead
+    every element must EQUAL the oracle's h for some gate and some up each within one bf16 ulp of the oracle's, at
+    least 99 % must be the oracle's own h, and the whole tensor must stay within the relative Frobenius bound."""
+    assert got_bf16.shape == gate_bf16.shape == up_bf16.shape
+    assert O.rel_frobenius(got_bf16, O.gelu_mul(gate_bf16, up_bf16, table_u16)) <= REL_FROBENIUS
+    central = got_bf16 == O.gelu_mul(gate_bf16, up_bf16, table_u16)
+    matched = central.copy()
+    for gate in _bf16_neighbours(gate_bf16):
+        for up in _bf16_neighbours(up_bf16):
+            matched |= got_bf16 == O.gelu_mul(gate, up, table_u16)
+    assert matched.all(), f"{(~matched).sum()} of {matched.size} elements are no neighbour's result"
+    assert central.mean() >= 0.99, f"only {central.mean():.4f} of the elements are the oracle's own result"
+
+
 def gelu_table_cpu(approximate="tanh") -> np.ndarray:
     codes = torch.arange(65536, dtype=torch.int32).to(torch.uint16).view(torch.bfloat16)
     return torch.nn.functional.gelu(codes, approximate=approximate).view(torch.uint16).numpy()
