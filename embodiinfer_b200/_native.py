@@ -22,7 +22,7 @@ LINEAR_ROUND_SCALE_BF16 = 1
 LINEAR_PAIRED_GATE_UP_SCALES = 4
 LINEAR_STREAM_TOKENS = 8
 LINEAR_SINGLE_CTA = 64
-LINEAR_NO_L2_PREFETCH = 128
+LINEAR_PAIRS = 128
 NORM_RESIDUAL_EVICT_LAST = 1
 SCALE_SCRATCH_BYTES = 8
 STATIC_SCRATCH_BYTES = 16640

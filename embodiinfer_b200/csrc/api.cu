@@ -102,6 +102,13 @@ int b2_gelu_table_range(const void* host_table, int32_t* lo, int32_t* hi) {
         if (table[high - 1] != high - 1 || table[0x8000 + high - 1] != 0x8000) break;
     if (high - low > 4096) return B2_E_UNSUPPORTED;
     if (high == low) high = low + 1 <= last ? low + 1 : low;   // keep a non-empty range so the closed forms stay enabled
+    // Any wider range is as valid (inside it the table itself is read).  Ten more binades below `low` cost 5 KB of
+    // shared memory and make a gate outside the range a one-in-a-million event, so that a warp's look-ups stay on the
+    // straight-line path: with the tight range a quarter of a percent of Gaussian gates fall below it, which sent
+    // three warps in four through the slow general path as well.
+    constexpr int MARGIN = 1280;
+    const int widened = low - MARGIN > first ? low - MARGIN : first;
+    if (high - widened <= 4096) low = widened;
     *lo = low;
     *hi = high;
     return B2_OK;

@@ -71,8 +71,6 @@ struct KernelArgs {
     int a_box_bytes;             // bytes of the token box of one K stage: 128 rows, or fewer (a multiple of 8) when the launch has
                                  // one token tile with fewer tokens -- the rows beyond the box are whatever shared memory holds,
                                  // they only feed accumulator rows that are never stored
-    const uint8_t* weight;       // the weight matrix itself (operands travel by tensor map; this pointer feeds the L2 prefetches)
-    int weight_rows;
     unsigned int* tickets;       // split-K: one arrival counter per tile (zero between launches)
     float* partials;             // split-K: [tile][split][128][tile_n] fp32
 };
@@ -159,15 +157,14 @@ __device__ __forceinline__ void gelu_lookup_unit(const uint32_t (&gate)[8], uint
     }
 }
 
-// 32 accumulator columns of one token -> 32 bf16 outputs (64 contiguous bytes): one packed multiply and
-// one two-value conversion per pair, 32-byte stores where the row allows them.
+// 32 accumulator columns of one token -> 32 bf16 outputs (64 contiguous bytes), in two steps so that a schedule may
+// free the accumulator between them: one packed multiply and one two-value conversion per pair, then bias / table /
+// residual and 32-byte stores where the row allows them.
 // EPI_GELU_*: the bf16 result goes through the GELU table and is stored as bf16 or, divided by *out_scale,
 // as e4m3 (32 contiguous bytes) -- SigLIP's fc1 (bias + tanh GELU + the encoder of fc2's input in one launch).
-template <int EPI>
-__device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32], const KernelArgs& args, float scale,
-                                                      bool round_scale, int token, int feature0, uint32_t compact_table,
-                                                      const ExactDivider& out_scale, float out_scale_rcp, bool true_div) {
-    uint32_t y[16];                                   // bf16 pairs
+//
+// 32 accumulator columns -> the GEMM's bf16 result as 16 bf16x2 words (scales applied, nothing else).
+__device__ __forceinline__ void linear_scale_chunk(const uint32_t (&acc)[32], float scale, bool round_scale, uint32_t (&y)[16]) {
     const float2 scale2 = make_float2(scale, scale);
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
@@ -175,6 +172,13 @@ __device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32],
         if (round_scale) value = bf16x2_to_float2(float2_to_bf16x2(value));     // nvfp4.py:120: the GEMM's own bf16 output
         y[p] = float2_to_bf16x2(__fmul2_rn(value, scale2));
     }
+}
+
+// The rest of the plain / GELU epilogue on those words: bias, table, residual, stores.
+template <int EPI>
+__device__ __forceinline__ void epilogue_linear_words(uint32_t (&y)[16], const KernelArgs& args, int token, int feature0,
+                                                      uint32_t compact_table, const ExactDivider& out_scale, float out_scale_rcp,
+                                                      bool true_div) {
     if (args.bias != nullptr) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
@@ -258,21 +262,24 @@ __device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32],
         if (feature0 + 8 * v < args.features) store_u4(out + 8 * v, y[4 * v], y[4 * v + 1], y[4 * v + 2], y[4 * v + 3]);
 }
 
+template <int EPI>
+__device__ __forceinline__ void epilogue_linear_chunk(const uint32_t (&acc)[32], const KernelArgs& args, float scale,
+                                                      bool round_scale, int token, int feature0, uint32_t compact_table,
+                                                      const ExactDivider& out_scale, float out_scale_rcp, bool true_div) {
+    uint32_t y[16];
+    linear_scale_chunk(acc, scale, round_scale, y);
+    epilogue_linear_words<EPI>(y, args, token, feature0, compact_table, out_scale, out_scale_rcp, true_div);
+}
+
 // One 16-feature unit of a token's row: 16 gate + 16 up accumulator columns -> 16 hidden values
 // h = bf16(bf16(gelu(gate)) * up), stored as bf16, e4m3 or NVFP4 (fusion.cu:5-10, 31-107).  For NVFP4
 // the unit is exactly one quantisation block of the next layer's input.  Values travel as bf16 pairs:
 // the product of two bf16 numbers is exact in fp32, so the packed bf16 multiply rounds once, like the
 // reference's float multiply followed by the bf16 store.
-template <int EPI>
-__device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[16], const uint32_t (&up_acc)[16],
-                                                    const KernelArgs& args, uint32_t compact_table, float scale,
-                                                    float scale_up, bool round_scale, const ExactDivider& out_scale,
-                                                    const ExactDivider& by_global, float out_scale_rcp, bool true_div,
-                                                    int token, int feature0) {
-    const uint32_t lo = uint32_t(args.gelu_lo);
-    const uint32_t span = uint32_t(args.gelu_hi - args.gelu_lo);     // 0: every lookup reads the full table
+// 16 gate + 16 up accumulator columns -> the two GEMMs' bf16 results as 8 + 8 bf16x2 words.
+__device__ __forceinline__ void geglu_scale_unit(const uint32_t (&gate_acc)[16], const uint32_t (&up_acc)[16], float scale,
+                                                 float scale_up, bool round_scale, uint32_t (&gate)[8], uint32_t (&up)[8]) {
     const float2 scale2 = make_float2(scale, scale), scale_up2 = make_float2(scale_up, scale_up);
-    uint32_t gate[8], up[8], gelu[8], h[8];
 #pragma unroll
     for (int p = 0; p < 8; ++p) {
         float2 g = make_float2(__uint_as_float(gate_acc[2 * p]), __uint_as_float(gate_acc[2 * p + 1]));
@@ -284,6 +291,17 @@ __device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[1
         gate[p] = float2_to_bf16x2(__fmul2_rn(g, scale2));
         up[p] = float2_to_bf16x2(__fmul2_rn(u, scale_up2));
     }
+}
+
+// The rest of the gated epilogue on those words: table, product, encoding, stores.
+template <int EPI>
+__device__ __forceinline__ void epilogue_geglu_words(const uint32_t (&gate)[8], const uint32_t (&up)[8], const KernelArgs& args,
+                                                     uint32_t compact_table, const ExactDivider& out_scale,
+                                                     const ExactDivider& by_global, float out_scale_rcp, bool true_div,
+                                                     int token, int feature0) {
+    const uint32_t lo = uint32_t(args.gelu_lo);
+    const uint32_t span = uint32_t(args.gelu_hi - args.gelu_lo);     // 0: every lookup reads the full table
+    uint32_t gelu[8], h[8];
     gelu_lookup_unit(gate, gelu, args, compact_table, lo, span);
 #pragma unroll
     for (int p = 0; p < 8; ++p) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(h[p]) : "r"(gelu[p]), "r"(up[p]));
@@ -337,6 +355,17 @@ __device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[1
         if (args.out_blocked != nullptr)
             args.out_blocked[scale_tile_offset(token, block, (blocks_per_row + 3) >> 2)] = code;
     }
+}
+
+template <int EPI>
+__device__ __forceinline__ void epilogue_geglu_unit(const uint32_t (&gate_acc)[16], const uint32_t (&up_acc)[16],
+                                                    const KernelArgs& args, uint32_t compact_table, float scale,
+                                                    float scale_up, bool round_scale, const ExactDivider& out_scale,
+                                                    const ExactDivider& by_global, float out_scale_rcp, bool true_div,
+                                                    int token, int feature0) {
+    uint32_t gate[8], up[8];
+    geglu_scale_unit(gate_acc, up_acc, scale, scale_up, round_scale, gate, up);
+    epilogue_geglu_words<EPI>(gate, up, args, compact_table, out_scale, by_global, out_scale_rcp, true_div, token, feature0);
 }
 
 // ---- host helpers shared by the two schedules ---------------------------------

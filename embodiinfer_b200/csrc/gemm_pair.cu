@@ -30,6 +30,7 @@
 
 namespace b2 {
 
+
 constexpr int PAIR_TOKENS = 2 * TILE_TOKENS;
 
 // ---- cta_group::2 forms of the tcgen05 / TMA instructions -------------------------------------------------
@@ -190,39 +191,6 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
 
-    // L2 prefetch of a tile's weights.  A tile's weight rows are one contiguous range of memory (whole rows of the
-    // row-major matrix), while the K-stage loads of the main loop touch it as 128-byte pieces two kilobytes apart,
-    // which DRAM serves slowly and with a long tail (a stage lands when its slowest piece does).  So the producer asks
-    // for the whole range with bulk prefetches, one tile ahead: DRAM streams it, and the stage loads find it in the L2.
-    // The token pairs that share a feature tile run side by side and take one part of the range each.  A prefetch is
-    // only a hint to the L2, the coherence point of the device, so it may run ahead of the launches before this one.
-    auto prefetch_tile = [&](const PairWalk& walk) {
-        if (args.weight == nullptr || !elect_one()) return;
-        const int f0 = walk.n_tile * features_per_tile;
-        const int row = GEGLU ? int(rank) * args.up_row_offset + f0 : f0 + int(rank) * (BN / 2);
-        const int limit = GEGLU ? (int(rank) + 1) * args.up_row_offset : args.weight_rows;
-        const int rows = min(BN / 2, limit - row);
-        if (rows <= 0) return;
-        const int64_t bytes = int64_t(rows) * args.k_bytes;
-        const int64_t part = ((bytes + args.num_m_tiles - 1) / args.num_m_tiles + 127) & ~int64_t(127);
-        const int64_t begin = walk.m_pair * part;
-        const int64_t length = min(part, bytes - begin);
-        const uint8_t* source = args.weight + int64_t(row) * args.k_bytes + begin;
-        constexpr int64_t CHUNK = 32768;
-        for (int64_t offset = 0; offset < length; offset += CHUNK)
-            bulk_prefetch_l2(source + offset, uint32_t(min(CHUNK, length - offset)));
-        if (NVFP4 && walk.m_pair == 0 && int(rank) < args.scale_blocks) {
-            const int block = rank == 0 ? (f0 >> 7) : (GEGLU ? ((args.up_row_offset + f0) >> 7) : (f0 >> 7) + 1);
-            if (block < args.weight_row_blocks)
-                bulk_prefetch_l2(args.weight_scales + int64_t(block) * args.scale_column_tiles * SCALE_ATOM_BYTES,
-                                 uint32_t(args.scale_column_tiles * SCALE_ATOM_BYTES));
-        }
-    };
-    if (warp == 0) {
-        const PairWalk first(args);
-        if (first.valid(args)) prefetch_tile(first);
-        __syncwarp();
-    }
     pdl_wait();
 
     bool failed = false;
@@ -237,12 +205,6 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
         uint32_t phase = 0;
         uint32_t filled = 0, fill_parity = 0;
         for (PairWalk walk(args); walk.valid(args); walk.next(args)) {
-            {
-                PairWalk ahead = walk;
-                ahead.next(args);
-                if (ahead.valid(args)) prefetch_tile(ahead);
-                __syncwarp();
-            }
             const int m0 = walk.m_pair * PAIR_TOKENS + int(rank) * TILE_TOKENS;
             const int f0 = walk.n_tile * features_per_tile;
             // this CTA's half of the weight tile: plain -> rows [f0 + rank*BN/2, +BN/2); gated -> the gate rows (leader)
@@ -409,32 +371,70 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
             tc_fence_after_sync();
             const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer * args.accumulator_stride);
             const bool warp_has_tokens = token0 < args.tokens;      // else: padding rows only
+            // The accumulator goes back to the MMA warp as soon as this warp's columns sit in registers as bf16
+            // words (scales applied): the table look-ups, the encoding and the stores then overlap the next tile's
+            // main loop even when only one accumulator fits in tensor memory.
+            auto release = [&]() {
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader) mbar_arrive(acc_empty_bar + 8 * buffer);
+                    else mbar_arrive_cluster(acc_empty_bar_leader + 8 * buffer);
+                }
+            };
             if (GEGLU) {
+                constexpr int UNITS_PER_WARP = (128 / 16 + WARPS_PER_QUARTER - 1) / WARPS_PER_QUARTER;   // at most 128 features per tile
                 const int units = features_per_tile / 16;
-                for (int unit = part; unit < units && warp_has_tokens; unit += WARPS_PER_QUARTER) {
-                    uint32_t first[16], second[16];
-                    tmem_load_32x16(lane_address + unit * 16, first);
-                    tmem_load_32x16(lane_address + BN / 2 + unit * 16, second);
-                    tmem_load_wait();
-                    epilogue_geglu_unit<GEGLU ? EPI : EPI_GEGLU_BF16>(first, second, args, compact_table, scale, scale_up,
-                                                                     round_scale, out_scale, by_global, out_scale_rcp,
-                                                                     true_div, token, f0 + unit * 16);
+                uint32_t gate[UNITS_PER_WARP][8], up[UNITS_PER_WARP][8];
+#pragma unroll
+                for (int u = 0; u < UNITS_PER_WARP; ++u) {       // one unit's 32 accumulator registers at a time (96-register budget)
+                    const int unit = part + u * WARPS_PER_QUARTER;
+                    if (unit < units && warp_has_tokens) {
+                        uint32_t first[16], second[16];
+                        tmem_load_32x16(lane_address + unit * 16, first);
+                        tmem_load_32x16(lane_address + BN / 2 + unit * 16, second);
+                        tmem_load_wait();
+                        geglu_scale_unit(first, second, scale, scale_up, round_scale, gate[u], up[u]);
+                    }
+                }
+                release();
+#pragma unroll
+                for (int u = 0; u < UNITS_PER_WARP; ++u) {
+                    const int unit = part + u * WARPS_PER_QUARTER;
+                    if (unit < units && warp_has_tokens)
+                        epilogue_geglu_words<GEGLU ? EPI : EPI_GEGLU_BF16>(gate[u], up[u], args, compact_table, out_scale, by_global,
+                                                                          out_scale_rcp, true_div, token, f0 + unit * 16);
                 }
             } else {
+                constexpr int CHUNKS_PER_WARP = (256 / 32 + WARPS_PER_QUARTER - 1) / WARPS_PER_QUARTER;  // at most 256 features per tile
                 const int chunks = features_per_tile / 32;
-                for (int chunk = part; chunk < chunks && warp_has_tokens; chunk += WARPS_PER_QUARTER) {
-                    uint32_t first[32];
-                    tmem_load_32x32(lane_address + chunk * 32, first);
+                uint32_t y[CHUNKS_PER_WARP][16];
+                // accumulator chunks in flight per thread: two (64 registers) with the eight-warp plain epilogue, one
+                // with the sixteen-warp table epilogues, whose threads have 96 registers
+                constexpr int IN_FLIGHT = WARPS_PER_QUARTER == 2 ? 2 : 1;
+#pragma unroll
+                for (int c = 0; c < CHUNKS_PER_WARP; c += IN_FLIGHT) {
+                    uint32_t first[IN_FLIGHT][32];
+#pragma unroll
+                    for (int i = 0; i < IN_FLIGHT; ++i) {
+                        const int chunk = part + (c + i) * WARPS_PER_QUARTER;
+                        if (c + i < CHUNKS_PER_WARP && chunk < chunks && warp_has_tokens) tmem_load_32x32(lane_address + chunk * 32, first[i]);
+                    }
                     tmem_load_wait();
-                    epilogue_linear_chunk<GEGLU ? EPI_LINEAR : EPI>(first, args, scale, round_scale, token, f0 + chunk * 32, compact_table,
-                                                                    out_scale, out_scale_rcp, true_div);
+#pragma unroll
+                    for (int i = 0; i < IN_FLIGHT; ++i) {
+                        const int chunk = part + (c + i) * WARPS_PER_QUARTER;
+                        if (c + i < CHUNKS_PER_WARP && chunk < chunks && warp_has_tokens) linear_scale_chunk(first[i], scale, round_scale, y[c + i]);
+                    }
                 }
-            }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                if (leader) mbar_arrive(acc_empty_bar + 8 * buffer);
-                else mbar_arrive_cluster(acc_empty_bar_leader + 8 * buffer);
+                release();
+#pragma unroll
+                for (int c = 0; c < CHUNKS_PER_WARP; ++c) {
+                    const int chunk = part + c * WARPS_PER_QUARTER;
+                    if (chunk < chunks && warp_has_tokens)
+                        epilogue_linear_words<GEGLU ? EPI_LINEAR : EPI>(y[c], args, token, f0 + chunk * 32, compact_table, out_scale,
+                                                                        out_scale_rcp, true_div);
+                }
             }
         }
     }
@@ -508,6 +508,14 @@ static int launch_pair(const CUtensorMap& act_map, const CUtensorMap& weight_map
 int pair_tile_columns(const b2_linear_desc* d, bool geglu) {
     if (d->tokens <= TILE_TOKENS) return 0;
     if (d->flags & (B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRED_GATE_UP_SCALES)) return 0;
+    // A pair computes 256 token rows whether they exist or not.  When the last pair would be mostly padding (560
+    // tokens: 768 rows of work on pairs against 640 on single CTAs) the single-CTA schedule is as fast or faster
+    // (measured: 560 x 16384 x 2048 FP8 28.0 vs 27.1 us); with equal padding, or enough tokens for it not to
+    // matter, pairs win by 6-20 % (8192 x 1152 x 4304 FP8 51.6 vs 64.4 us; 8960 x 32768 x 2048 gated FP8 480 vs 543 us).
+    // B2_LINEAR_PAIRS asks for pairs regardless.
+    const int64_t pair_rows = int64_t((d->tokens + PAIR_TOKENS - 1) / PAIR_TOKENS) * PAIR_TOKENS;
+    const int64_t single_rows = int64_t((d->tokens + TILE_TOKENS - 1) / TILE_TOKENS) * TILE_TOKENS;
+    if (!(d->flags & B2_LINEAR_PAIRS) && pair_rows != single_rows && d->tokens < 2048) return 0;
     const bool nvfp4 = d->kind == B2_KIND_NVFP4;
     if (geglu) {
         if (d->feature_tile != 0 && d->feature_tile != 128) return 0;
@@ -556,8 +564,6 @@ int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, cud
     args.out_scales = static_cast<uint8_t*>(d->out_scales);
     args.out_blocked = static_cast<uint8_t*>(d->out_blocked);
     args.status = static_cast<unsigned int*>(d->status);
-    args.weight = (d->flags & B2_LINEAR_NO_L2_PREFETCH) ? nullptr : static_cast<const uint8_t*>(d->weight);
-    args.weight_rows = weight_rows;
     args.gelu_lo = args.gelu_hi = 0;
     if (epilogue != EPI_LINEAR && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
         d->gelu_hi - d->gelu_lo <= MAX_COMPACT_GELU) {

@@ -124,18 +124,19 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
 #define B2_LINEAR_STREAM_TOKENS 8 /* tuning aid: always load the token tile with every K stage.  By default a CTA keeps its
                                      128-token tile (all of K) and the token scales on chip whenever they fit and it computes
                                      several feature tiles of that token tile; results are identical either way. */
-#define B2_LINEAR_SINGLE_CTA 64 /* tuning / test aid: never use the paired schedule.  By default a launch with more than 128 tokens
-                                  runs 256-token tiles on pairs of SMs (two CTAs of a thread-block cluster, `tcgen05.mma.cta_group::2`):
-                                  each CTA loads its 128 token rows and half of the weight tile.  The accumulation order along K is
-                                  the same in both schedules, so results are identical either way. */
-
-#define B2_LINEAR_NO_L2_PREFETCH 128 /* tuning aid: the paired schedule does not prefetch the next tile's weight rows into the L2 */
+#define B2_LINEAR_SINGLE_CTA 64 /* tuning / test aid: never use the paired schedule.  In the paired schedule 256-token tiles run on
+                                  pairs of SMs (two CTAs of a thread-block cluster, `tcgen05.mma.cta_group::2`): each CTA loads its
+                                  128 token rows and half of the weight tile.  The library picks it when there are more than 128
+                                  tokens and the 256-row tiles add no padding over 128-row tiles (or there are at least 2048 tokens).
+                                  The accumulation order along K is the same in both schedules: results are identical either way. */
+#define B2_LINEAR_PAIRS 128 /* tuning / test aid: use the paired schedule whenever it applies (more than 128 tokens, no split K,
+                               bundle-order scale layout), whatever the padding */
 
 typedef struct b2_linear_desc {
     int32_t kind;        /* B2_KIND_* */
     int32_t epilogue;    /* B2_EPI_* */
     int32_t out_format;  /* B2_OUT_* */
-    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_LINEAR_SINGLE_CTA | B2_LINEAR_NO_L2_PREFETCH | B2_GEGLU_TRUE_DIV; any other bit: B2_E_INVALID */
+    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRS | B2_GEGLU_TRUE_DIV; any other bit: B2_E_INVALID */
     int32_t tokens;      /* M: rows of the activation matrix */
     int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
     int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */
@@ -293,8 +294,9 @@ int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc);
  * (negative) from hi upward.  b2_linear then keeps only [lo, hi) of the table, for both signs, in shared
  * memory and evaluates the closed forms elsewhere, which is bit-identical to indexing the full table.
  * Returns B2_E_UNSUPPORTED (and 0, 0) when the table has no such structure or the range is wider than
- * 4096 codes; b2_linear then reads the full table from global memory.  The tanh-approximated GELU has
- * lo = 0x3b4b, hi = 0x40a2 (|x| in [3.1e-3, 5.06)).  Host-only; no reference counterpart (the reference
+ * 4096 codes; b2_linear then reads the full table from global memory.  The tanh-approximated GELU's closed forms
+ * hold outside [0x3b4b, 0x40a2) (|x| in [3.1e-3, 5.06)); the function returns lo lowered by ten binades (0x364b),
+ * which is as valid and keeps nearly every gate value inside the range (one straight-line path per warp).  Host-only; no reference counterpart (the reference
  * always gathers from the 128 KiB table, fusion.cu:5-10). */
 int b2_gelu_table_range(const void* host_table, int32_t* lo, int32_t* hi);
 

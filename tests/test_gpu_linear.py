@@ -240,12 +240,12 @@ def test_paired_schedule_equals_single_cta(device, kind, tokens, features, width
     bias = make_weight((1, features), 91, std=0.5).reshape(-1).to(torch.bfloat16).to(device)
     residual = make_input((tokens, features), 92, outliers=False).to(device)
     common = dict(tokens=tokens, features=features, width=width, tile=tile)
-    paired = run_linear(device, dev, **common)
+    paired = run_linear(device, dev, flags=N.LINEAR_PAIRS, **common)
     single = run_linear(device, dev, flags=N.LINEAR_SINGLE_CTA, **common)
     assert torch.equal(paired.view(torch.int16), single.view(torch.int16))
     want = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
     assert_gemm_close(bits(paired), want)
-    full = run_linear(device, dev, bias=bias, residual=residual, **common)
+    full = run_linear(device, dev, flags=N.LINEAR_PAIRS, bias=bias, residual=residual, **common)
     assert torch.equal(full, (paired + bias) + residual)
 
 
@@ -260,7 +260,7 @@ def test_paired_schedule_gated_equals_single_cta(device, kind, out_format):
     common = dict(epilogue=N.EPI_GEGLU, tokens=tokens, features=features, width=width, gelu_table=table,
                   gelu_range=K.gelu_table_range(table), **dev)
     results = []
-    for flags in (0, N.LINEAR_SINGLE_CTA):
+    for flags in (N.LINEAR_PAIRS, N.LINEAR_SINGLE_CTA):
         status = torch.zeros(1, device=device, dtype=torch.int32)
         if out_format == "bf16":
             out = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
@@ -297,6 +297,9 @@ def test_token_tail_sweep(device, kind):
         sliced["act"] = dev["act"][:tokens].contiguous()
         out = run_linear(device, sliced, tokens=tokens, features=features, width=width)
         assert_gemm_close(bits(out), want[:tokens])
+        if tokens > 128:        # and on pairs of SMs, whatever the padding
+            paired = run_linear(device, sliced, tokens=tokens, features=features, width=width, flags=N.LINEAR_PAIRS)
+            assert torch.equal(paired.view(torch.int16), out.view(torch.int16))
 
 
 def test_config1_full_size(device):
@@ -306,6 +309,8 @@ def test_config1_full_size(device):
     host, dev = operands("fp8", tokens, features, width, 1001, device)
     out = run_linear(device, dev, tokens=tokens, features=features, width=width)
     assert_gemm_close(bits(out), O.fp8_linear(host["a"], host["a_s"], host["w"], host["w_s"]))
+    paired = run_linear(device, dev, tokens=tokens, features=features, width=width, flags=N.LINEAR_PAIRS)
+    assert torch.equal(paired.view(torch.int16), out.view(torch.int16))
     # the bias is a separate bf16 addition on that result (fp8.py:139-140)
     bias = make_weight((1, features), 1001, std=0.1).to(torch.bfloat16).reshape(-1).to(device)
     assert torch.equal(run_linear(device, dev, tokens=tokens, features=features, width=width, bias=bias), out + bias)
@@ -432,7 +437,7 @@ def test_rejections(device):
                  act_scale=one, weight=w, weight_scale=one, out=out)
 
 
-@pytest.mark.parametrize("std", (1e-4, 0.02, 0.5))
+@pytest.mark.parametrize("std", (1e-7, 0.02, 0.5))
 def test_compact_gelu_table_matches_full_table(device, std):
     """Keeping only the non-trivial part of the GELU table in shared memory (b2_gelu_table_range)
     gives the same bits as gathering from the full table, for tiny, ordinary and huge gate values."""
@@ -444,7 +449,7 @@ def test_compact_gelu_table_matches_full_table(device, std):
     table_host = gelu_table_cpu("tanh")
     table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
     table_range = K.gelu_table_range(table)
-    assert table_range == (0x3B4B, 0x40A2)
+    assert table_range == (0x3B4B - 1280, 0x40A2)      # the closed forms hold outside [0x3B4B, 0x40A2); lo comes back ten binades lower
     scalar = lambda v: torch.tensor(float(v), device=device)
     common = dict(kind=N.KIND_FP8, epilogue=N.EPI_GEGLU, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width,
                   act=torch.from_numpy(aq).to(device), act_scale=scalar(a_s), weight=torch.from_numpy(wq).to(device),
@@ -456,8 +461,8 @@ def test_compact_gelu_table_matches_full_table(device, std):
     assert torch.equal(full.view(torch.int16), compact.view(torch.int16))
     gate = O.bf16_to_f32(O.fp8_linear(aq, a_s, wq[:features], w_s))
     magnitudes = (O.f32_to_bf16(gate) & 0x7FFF)
-    if std == 1e-4:
-        assert (magnitudes < 0x3B4B).mean() > 0.5       # the x/2 tail is exercised
+    if std == 1e-7:
+        assert (magnitudes < 0x3B4B - 1280).mean() > 0.3       # the x/2 tail is exercised
     if std == 0.5:
         assert (magnitudes >= 0x40A2).mean() > 0.2      # the identity / -0 tail is exercised
 
