@@ -79,6 +79,10 @@ class FusedMlpPlan:
         self.gate_up.release_scope(scope)
         self.down.release_scope(scope)
 
+    def refit_tensors(self, prefix: str = "") -> dict[str, torch.Tensor]:
+        """Packed operands of both launches, for an in-place weight refit (see ``B200Projection.refit_tensors``)."""
+        return {**self.gate_up.refit_tensors(prefix + "gate_up."), **self.down.refit_tensors(prefix + "down.")}
+
 
 class FusedGeluMlpPlan:
     """``fc2(gelu(fc1(x) + b1)) + b2`` with calibrated FP8 ranges in three launches: encode(x), fc1 + bias +
@@ -122,6 +126,13 @@ class FusedGeluMlpPlan:
     def release_scope(self, scope: WorkspaceKey) -> None:
         self.fc1.release_scope(scope)
         self.fc2.release_scope(scope)
+
+    def refit_tensors(self, prefix: str = "") -> dict[str, torch.Tensor]:
+        found = {**self.fc1.refit_tensors(prefix + "fc1."), **self.fc2.refit_tensors(prefix + "fc2.")}
+        for name in ("fc1_bias", "fc2_bias"):
+            if getattr(self, name) is not None:
+                found[prefix + name] = getattr(self, name)
+        return found
 
 
 class _ShapeOnly:

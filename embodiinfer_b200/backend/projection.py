@@ -23,6 +23,13 @@ from ..weights import blocked_scales
 from .quantization import blocked_scale_bytes
 
 
+def uses_sm_pairs(tokens: int) -> bool:
+    """Whether ``b2_linear`` runs this many token rows on pairs of SMs (256-row tiles) when the scale layout allows
+    it: more than 128 rows and no more padding than 128-row tiles would add, or at least 2048 rows (the library's
+    own rule; gated NVFP4 launches must pass the matching block-scale layout)."""
+    return tokens > 128 and (tokens >= 2048 or -(-tokens // 256) * 256 == -(-tokens // 128) * 128)
+
+
 class B200Projection:
     """One packed weight plus its execution-scoped activation encoders and output buffers."""
 
@@ -84,7 +91,10 @@ class B200Projection:
         return self.plans[key].quantize(matrix)
 
     def release_scope(self, scope: WorkspaceKey) -> None:
-        """Drop the workspaces of one finished execution scope (projection.py:88-93)."""
+        """Drop the workspaces of one finished execution scope (projection.py:88-93).  The scope's launches have
+        been waited for by then, so this is also where an expired bounded wait of one of them is reported."""
+        if self.precision != "bf16":
+            K.check_status(self.device)
         for key in tuple(self.plans):
             if key[-1] == scope:
                 del self.plans[key]
@@ -194,12 +204,15 @@ class B200Projection:
                     "gated4_blocked", (blocked_scale_bytes(rows, features),), torch.float8_e4m3fn, zero=True
                 )
                 out_format = N.OUT_NVFP4
+        operands, flags = self._operands(encoded), self.gated_flags
+        if flags & N.LINEAR_PAIRED_GATE_UP_SCALES and uses_sm_pairs(rows) and getattr(self, "weight_blocks_bundle", None) is not None:
+            operands["weight_scales"], flags = self.weight_blocks_bundle, flags & ~N.LINEAR_PAIRED_GATE_UP_SCALES
         K.linear(
             epilogue=N.EPI_GEGLU, out_format=out_format, tokens=rows, features=features, width=self.input_dim,
             out=result.output, gelu_table=table, out_scale=result.scale, out_scales=result.scales,
             out_blocked=result.blocked, weight_scale_up=self.weight_scale_up, gelu_range=table_range,
-            flags=self.gated_flags,
-            **self._operands(encoded),
+            flags=flags,
+            **operands,
         )
         return result
 
@@ -280,7 +293,26 @@ class B200Projection:
             ).reshape(2 * rows, blocks)
             pair.weight_blocks = blocked_scales(paired)
             pair.gated_flags = N.LINEAR_PAIRED_GATE_UP_SCALES
+            # ... and in bundle order (gate rows, then up rows) for the paired-SM schedule, whose 128 + 128 column
+            # tiles read whole 128-row scale blocks
+            pair.weight_blocks_bundle = blocked_scales(torch.cat(
+                (gate.weight_rowmajor_scales.view(torch.uint8), up.weight_rowmajor_scales.view(torch.uint8))))
+            pair.weight_rowmajor_scales = None
         return pair
+
+    def refit_tensors(self, prefix: str = "") -> dict[str, torch.Tensor]:
+        """The packed operands a weight refit has to refresh, by name: codes, block scales (every layout held) and
+        per-tensor / global scales.  A refit copies new values INTO these tensors, so device pointers recorded in
+        CUDA graphs and read by the launches stay valid (embodiinfer/engine/rollout/refit.py:122-137 runs its
+        ``on_refit`` hook for the same reason)."""
+        names = ("weight", "weight_scale", "weight_scale_up", "weight_blocks", "weight_blocks_bundle", "weight_rowmajor_scales",
+                 "bf16_weight")
+        found = {}
+        for name in names:
+            tensor = getattr(self, name, None)
+            if isinstance(tensor, torch.Tensor):
+                found[prefix + name] = tensor
+        return found
 
 
 class _GatedOutput:

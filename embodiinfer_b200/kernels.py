@@ -292,6 +292,44 @@ def frames_to_patches(frames: torch.Tensor, patches: torch.Tensor, patch: int) -
     N.check(status, "b2_frames_to_patches")
 
 
+# ---- the status word of the bounded waits -------------------------------------------------------------
+# Every wait inside the tensor-core kernels is bounded; a wait that runs out leaves a code in the launch's status
+# word and the kernel drains with a wrong result instead of hanging.  The plan objects and the registry kernels
+# pass ONE word per device to every launch (a launch only ever writes a non-zero code into a zero word), and the
+# host reads it where it synchronises anyway: at the end of a rollout step, when a workspace scope is released.
+STATUS_NAMES = {0x101: "the TMA producer waited for a free stage", 0x102: "the MMA issuer waited for a filled stage",
+                0x103: "the MMA issuer waited for a drained accumulator", 0x104: "the epilogue waited for a finished accumulator",
+                0x105: "the producer waited for its copies in flight"}
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The device's status word (int32, zero unless a bounded wait expired since the last check).  Created on first
+    use: touch it once before capturing a CUDA graph, as with every plan buffer."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(index)
+    if word is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("Warm tensor-core launches before graph capture")
+        word = _status_words[index] = torch.zeros(1, device=torch.device("cuda", index), dtype=torch.int32)
+    return word
+
+
+def check_status(device: torch.device) -> None:
+    """Read the device's status word (this synchronises with the device) and raise ``RuntimeError`` naming the wait
+    that expired; the word is cleared so that later launches are judged on their own."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    word = _status_words.get(index)
+    if word is None:
+        return
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        what = STATUS_NAMES.get(code, "an unknown wait")
+        raise RuntimeError(f"a tensor-core launch on cuda:{index} gave up a bounded wait (status {code:#x}: {what} for longer than "
+                           "its limit); its result and those of the launches after it are invalid")
+
+
 _WORKSPACE_BYTES = 32 << 20
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
@@ -335,7 +373,8 @@ def linear(
     gelu_range: tuple[int, int] = (0, 0),
     workspace: torch.Tensor | None | bool = None,
 ) -> None:
-    """One fused tensor-core launch, see ``b2_linear``.  ``workspace``: zeroed split-K scratch, e.g.
+    """One fused tensor-core launch, see ``b2_linear``.  ``status``: the word an expired bounded wait is reported in
+    (default: the device's word, read by :func:`check_status`).  ``workspace``: zeroed split-K scratch, e.g.
     :func:`linear_workspace`; without one (the default) K is never split.  The fix-up through the L2 costs
     more than the shorter K loop saves at every shape of the pi0.5 stacks measured so far (560x2048x16384:
     35 vs 28 us; 10x2560x1024: 12.5 vs 5.6 us), so the plans do not pass one."""
@@ -343,6 +382,8 @@ def linear(
         act, act_scale, weight, weight_scale, out, act_scales, weight_scales, weight_scale_up, bias, residual, gelu_table, out_scale,
         out_scales, out_blocked, status,
     )
+    if status is None:
+        status = status_word(device)
     desc = N.LinearDesc(
         kind=kind,
         epilogue=epilogue,

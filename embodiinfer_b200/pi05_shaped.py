@@ -352,6 +352,24 @@ class SiglipBlock(nn.Module):
         self.dense_mlp = None
 
 
+def plan_tensors(module: nn.Module) -> dict[str, torch.Tensor]:
+    """Every packed operand held by the calibrated plans below ``module`` (they are not module buffers), by a stable
+    name: what a weight refit must refresh besides the state dict once ``calibrate_fused_mlp`` has run."""
+    found: dict[str, torch.Tensor] = {}
+    for name, child in module.named_modules():
+        prefix = f"{name}." if name else ""
+        plan = getattr(child, "plan", None)
+        if isinstance(plan, B200Projection):
+            found.update(plan.refit_tensors(prefix + "plan."))
+        fused = getattr(child, "fused_mlp", None)
+        if fused is not None:
+            found.update(fused.refit_tensors(prefix + "fused_mlp."))
+        bias = getattr(child, "dense_bias", None)
+        if isinstance(bias, torch.Tensor) and plan is not None:
+            found[prefix + "dense_bias"] = bias
+    return found
+
+
 class Pi05ShapedPolicy(nn.Module):
     """uint8 camera frames + text tokens -> [B, 10, 32] action chunk.
 
@@ -467,6 +485,10 @@ class Pi05ShapedPolicy(nn.Module):
         for projection in projections:
             projection.recording = False
             projection.calibrate(self.quantizer, margin)
+
+    def refit_tensors(self) -> dict[str, torch.Tensor]:
+        """Picked up by ``BroadcastWeightSync``: the calibrated plans' packed operands (see ``plan_tensors``)."""
+        return plan_tensors(self)
 
     def flops_per_observation(self) -> float:
         """2*M*N*K over the quantised projections of one observation (attention and norms excluded)."""

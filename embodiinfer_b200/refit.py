@@ -7,11 +7,17 @@ state that moves is the *quantised* bundle state (packed codes, block scales, gl
 packed into buckets of ``bucket_bytes`` so that NVLink sees a few large broadcasts instead of hundreds of
 small ones, and the copy back is in place: device pointers held by captured CUDA graphs and by the plan
 objects stay valid.  Rank order, names and shapes must agree on all ranks (same model definition).
+
+Plan objects keep their packed operands outside the module's state dict.  A module (or any of its
+submodules) that defines ``refit_tensors() -> dict[name, tensor]`` has those tensors broadcast and refreshed
+in place as well, under the prefix ``plans.``; ``on_refit`` callbacks run after the copies and BEFORE the
+version advances, like the reference's hook (embodiinfer/engine/rollout/refit.py:122-137), so a reader that
+sees the new version never computes with stale derived state.
 """
 
 from __future__ import annotations
 
-from collections.abc import Iterable
+from collections.abc import Callable, Iterable
 
 import torch
 import torch.distributed as dist
@@ -20,10 +26,11 @@ from torch import nn
 
 class BroadcastWeightSync:
     def __init__(self, module: nn.Module, src_rank: int = 0, group: dist.ProcessGroup | None = None,
-                 bucket_bytes: int = 64 << 20) -> None:
+                 bucket_bytes: int = 64 << 20, on_refit: Iterable[Callable[[], None]] = ()) -> None:
         if bucket_bytes <= 0:
             raise ValueError("bucket_bytes must be positive")
         self.module, self.src_rank, self.group, self.bucket_bytes = module, src_rank, group, bucket_bytes
+        self.on_refit = list(on_refit)
         self.version = 0
 
     @property
@@ -33,6 +40,11 @@ class BroadcastWeightSync:
 
     def _tensors(self, names: Iterable[str] | None) -> list[tuple[str, torch.Tensor]]:
         state = {name: tensor for name, tensor in self.module.state_dict(keep_vars=True).items()}
+        owners = [self.module] if hasattr(self.module, "refit_tensors") else [
+            child for child in self.module.modules() if child is not self.module and hasattr(child, "refit_tensors")]
+        for owner in owners:
+            for name, tensor in owner.refit_tensors().items():
+                state.setdefault(f"plans.{name}", tensor)
         if names is None:
             selected = sorted(state)
         else:
@@ -70,5 +82,7 @@ class BroadcastWeightSync:
                 if tensor is not None:
                     bucket.append(tensor)
                     size += nbytes
+        for hook in self.on_refit:          # derived state is rebuilt before a reader can see the new version
+            hook()
         self.version += 1
         return broadcasts

@@ -229,3 +229,46 @@ def test_calibrated_layer_record_with_smoothquant_scales(device, precision):
     exact = hidden @ down_w.float().t()
     relative = lambda y: float((y.float() - exact).norm() / exact.norm())
     assert relative(got) < max(2.0 * relative(expected), 0.05), (relative(got), relative(expected))
+
+
+@pytest.mark.parametrize("precision", ("fp8", "nvfp4"))
+def test_refit_refreshes_the_plans_in_place(device, precision):
+    """After a weight refit the calibrated plans must compute with the new weights although their packed operands
+    are not module buffers: copying a fresh plan's ``refit_tensors`` into the live plan's (what the broadcast does)
+    leaves every device pointer unchanged, and both the eager call and a graph captured BEFORE the refit then give
+    the fresh plan's result bit for bit."""
+    hidden, inter, tokens = 256, 512, 300
+    quantizer = L.quantization_backends.get("cuda", request(device, bits_=4))
+    def weights(seed):
+        return tuple(make_weight(shape, seed + i, std=0.05).to(device=device, dtype=torch.bfloat16)
+                     for i, shape in enumerate(((inter, hidden), (inter, hidden), (hidden, inter))))
+    def build(seed):
+        gate, up, down = weights(seed)
+        return FusedMlpPlan(gate, up, down, gate_up_max=6.0, down_max=4.0, gate_up=precision, down=precision,
+                            quantizer=quantizer, approximate="tanh")
+    live, fresh = build(1), build(50)
+    x = make_input((tokens, hidden), 7).to(device)
+    before = live(x).clone()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            live(x)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            captured = live(x)
+    torch.cuda.current_stream(device).wait_stream(side)
+    torch.cuda.synchronize()
+    pointers = {name: tensor.data_ptr() for name, tensor in live.refit_tensors().items()}
+    assert pointers and set(pointers) == set(fresh.refit_tensors())
+    with torch.no_grad():
+        for name, tensor in live.refit_tensors().items():
+            tensor.copy_(fresh.refit_tensors()[name])
+    assert {name: tensor.data_ptr() for name, tensor in live.refit_tensors().items()} == pointers
+    want = fresh(x)
+    after = live(x)
+    assert torch.equal(after, want) and not torch.equal(after, before)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(captured, want)

@@ -26,6 +26,12 @@ class Bundle(nn.Module):
         self.inner = nn.Linear(8, 8)
         with torch.no_grad():
             self.inner.weight.copy_(torch.randn(8, 8, generator=generator))
+        # what a calibrated plan holds outside the state dict: packed codes (e4m3) and a derived copy
+        self.plan_codes = torch.randint(0, 120, (16, 8), dtype=torch.uint8, generator=generator).view(torch.float8_e4m3fn)
+        self.derived = self.plan_codes.view(torch.uint8).clone()
+
+    def refit_tensors(self):
+        return {"proj.weight": self.plan_codes}
 
 
 def _worker(rank: int, world: int, init_file: str, results) -> None:
@@ -34,9 +40,20 @@ def _worker(rank: int, world: int, init_file: str, results) -> None:
     try:
         module = Bundle(seed=100 + rank)                      # every rank starts from different weights
         pointers = {name: tensor.data_ptr() for name, tensor in module.state_dict(keep_vars=True).items()}
-        sync = BroadcastWeightSync(module, src_rank=0, bucket_bytes=1024)      # small buckets: several broadcasts per dtype
+        seen_versions = []
+
+        def rebuild_derived():                                 # runs after the copies, before the version advances
+            seen_versions.append(sync.policy_version)
+            module.derived.copy_(module.plan_codes.view(torch.uint8))
+
+        plan_pointer = module.plan_codes.data_ptr()
+        sync = BroadcastWeightSync(module, src_rank=0, bucket_bytes=1024, on_refit=[rebuild_derived])      # small buckets: several broadcasts per dtype
         count = sync.update()
-        assert sync.policy_version == 1 and count >= 4
+        assert sync.policy_version == 1 and count >= 4 and seen_versions == [0]
+        # the plan's packed operand (not in the state dict) was refreshed in place, and the derived state with it
+        assert module.plan_codes.data_ptr() == plan_pointer
+        assert torch.equal(module.plan_codes.view(torch.uint8), Bundle(seed=100).plan_codes.view(torch.uint8))
+        assert torch.equal(module.derived, Bundle(seed=100).plan_codes.view(torch.uint8))
         assert all(tensor.data_ptr() == pointers[name] for name, tensor in module.state_dict(keep_vars=True).items()), "in place"
         reference = Bundle(seed=100)
         for name, tensor in module.state_dict().items():

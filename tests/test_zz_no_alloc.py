@@ -67,3 +67,18 @@ def test_largest_supported_tensor(device):
     static, reference = call_both(x, 448.0, N.SCALAR_RCP)
     assert np.float32(static) == np.float32(reference)
     assert np.float32(static) == np.float32((x.float().abs().amax() * torch.tensor(1.0 / 448.0, device=device)).item())
+
+
+def test_documented_maximum_uses_every_slot(device):
+    """Exactly B2_STATIC_SCALE_MAX_COUNT elements (64 Mi bf16, 128 MB): the last of the 4096 slots of the static
+    array is in use, with the largest magnitude placed in the very last element, and a second call at the boundary
+    right behind it sees none of the first one's state."""
+    count = N.STATIC_SCALE_MAX_COUNT
+    x = torch.randn(count, device=device).to(torch.bfloat16)
+    x[-1] = 300.0
+    static, reference = call_both(x, 448.0, N.SCALAR_RCP)
+    assert np.float32(static) == np.float32(reference) == np.float32(np.float32(300.0) * np.float32(1.0 / 448.0))
+    x[-1] = 0.5
+    static, reference = call_both(x, 448.0, N.SCALAR_RCP)
+    assert np.float32(static) == np.float32(reference)
+    assert np.float32(static) == np.float32((x.float().abs().amax() * torch.tensor(1.0 / 448.0, device=device)).item())
