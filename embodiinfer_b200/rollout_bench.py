@@ -6,7 +6,8 @@
 
 Every rank builds the same random-init policy (weights replicated), takes its contiguous shard of the
 batch (pinned host uint8 frames -> device inside the timed region), runs SigLIP -> prefix -> 10 denoise
-steps and joins one NCCL gather of the [n, 10, 32] fp32 action chunks.  Prints one JSON line on rank 0.
+steps and joins one NCCL gather (the only collective of a call) of the fixed-size per-rank records that carry
+the [n, 10, 32] fp32 action chunks.  Prints one JSON line on rank 0.
 
 ``--fused-mlp`` calibrates the Gemma MLPs on the first micro-batch and runs them as the calibrated fused
 plan; ``--graphs`` replays one CUDA graph per micro-batch (host-to-device copy of the frames included)
@@ -18,8 +19,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import time
-
 import torch
 import torch.distributed as dist
 
@@ -64,6 +63,63 @@ class GraphedReplica:
         return self.output[:count].clone()
 
 
+def measure_rollout(device: torch.device, *, observations: int = 256, micro_batch: int = 32, quantization: str = "fp8",
+                    layer_scale: float = 1.0, repeats: int = 3, fused_mlp: bool = True, graphs: bool = True,
+                    policy: Pi05ShapedPolicy | None = None) -> tuple[dict, Pi05ShapedPolicy]:
+    """Observations per second of the 256-observation rollout on the ranks of the initialised process group (or one
+    GPU).  Device time: CUDA events around each pass on the launching stream, maximum over ranks, best of ``repeats``.
+    Returns the result record (meaningful on rank 0) and the policy, for further measurements on it."""
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    if policy is None:
+        policy = Pi05ShapedPolicy(quantization, device=device, layer_scale=layer_scale)
+    batch = synthetic_observations(observations)
+    batch = {key: value.pin_memory() for key, value in batch.items()}
+    first = {key: value[:micro_batch] for key, value in batch.items()}
+    if fused_mlp and not getattr(policy, "calibrated", False):
+        policy.calibrate_fused_mlp(first, margin=1.25)
+        policy.calibrated = True
+    step = GraphedReplica(policy, first, micro_batch) if graphs else policy
+
+    def replica(shard):
+        chunks = []
+        count = len(shard["tokens"])
+        for begin in range(0, count, micro_batch):
+            piece = {key: value[begin: begin + micro_batch] for key, value in shard.items()}
+            chunks.append(step(piece))
+        return torch.cat(chunks)
+
+    rollout = DataParallelRollout(replica, device=device)
+    rollout.run(batch)                             # warm-up: workspaces, library heuristics, NCCL
+    torch.cuda.synchronize(device)
+    milliseconds = []
+    result = None
+    for _ in range(repeats):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        result = rollout.run(batch)
+        stop.record()
+        torch.cuda.synchronize(device)
+        elapsed = torch.tensor(start.elapsed_time(stop), device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+        milliseconds.append(elapsed.item())
+    best = min(milliseconds) * 1e-3
+    flops = policy.flops_per_observation() * observations
+    record = {
+        "metric": "rollout_observations_per_s", "value": observations / best, "unit": "obs/s", "n_gpus": world,
+        "observations": observations, "ms": milliseconds, "quantization": quantization,
+        "layer_scale": layer_scale, "micro_batch": micro_batch, "scaling": "strong",
+        "fused_mlp": fused_mlp, "cuda_graphs": graphs, "collectives_per_call": 1 if world > 1 else 0,
+        "quantised_linear_tflops": flops / best / 1e12, "actions_checksum": float(result.actions.double().sum()),
+        "gathered_bytes": result.actions.numel() * 4,
+        "h2d_bytes_per_observation": sum(value[0].numel() * value.element_size() for value in batch.values()),
+    }
+    return record, policy
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--observations", type=int, default=256)
@@ -79,48 +135,10 @@ def main() -> None:
     device = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    policy = Pi05ShapedPolicy(args.quantization, device=device, layer_scale=args.layer_scale)
-    observations = synthetic_observations(args.observations)
-    observations = {key: value.pin_memory() for key, value in observations.items()}
-    first = {key: value[: args.micro_batch] for key, value in observations.items()}
-    if args.fused_mlp:
-        policy.calibrate_fused_mlp(first, margin=1.25)
-    step = GraphedReplica(policy, first, args.micro_batch) if args.graphs else policy
-
-    def replica(shard):
-        chunks = []
-        count = len(shard["tokens"])
-        for begin in range(0, count, args.micro_batch):
-            piece = {key: value[begin: begin + args.micro_batch] for key, value in shard.items()}
-            chunks.append(step(piece))
-        return torch.cat(chunks)
-
-    rollout = DataParallelRollout(replica, device=device)
-    rollout.run(observations)                      # warm-up: workspaces, cuDNN/SDPA heuristics, NCCL
-    torch.cuda.synchronize()
-    seconds = []
-    for _ in range(args.repeats):
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        start = time.perf_counter()
-        result = rollout.run(observations)
-        torch.cuda.synchronize()
-        elapsed = torch.tensor(time.perf_counter() - start, device=device, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-        seconds.append(elapsed.item())
+    record, _ = measure_rollout(device, observations=args.observations, micro_batch=args.micro_batch, quantization=args.quantization,
+                                layer_scale=args.layer_scale, repeats=args.repeats, fused_mlp=args.fused_mlp, graphs=args.graphs)
     if rank == 0:
-        best = min(seconds)
-        flops = policy.flops_per_observation() * args.observations
-        print(json.dumps({
-            "metric": "rollout_observations_per_s", "value": args.observations / best, "unit": "obs/s", "n_gpus": world,
-            "observations": args.observations, "seconds": seconds, "quantization": args.quantization,
-            "layer_scale": args.layer_scale, "micro_batch": args.micro_batch, "scaling": "strong",
-            "fused_mlp": args.fused_mlp, "cuda_graphs": args.graphs,
-            "quantised_linear_tflops": flops / best / 1e12, "actions_checksum": float(result.actions.double().sum()),
-            "gathered_bytes": result.actions.numel() * 4,
-        }))
+        print(json.dumps(record))
     if world > 1:
         dist.destroy_process_group()
 

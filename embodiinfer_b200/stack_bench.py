@@ -55,6 +55,21 @@ def linear_flops(shape, tokens: int, layers: int) -> float:
 
 
 @torch.no_grad()
+def measure_denoise(policy: Pi05ShapedPolicy, batches=(1, 8, 64), seed: int = 1004) -> dict[str, float]:
+    """Milliseconds of the 10-step action-expert denoise (18 layers, 10-token chunk) per batch size, on ``policy``'s
+    expert tower with random prefix keys/values: one CUDA graph per batch size, 20 replays between CUDA events."""
+    device = policy.device_
+    generator = torch.Generator(device=device).manual_seed(seed)
+    found = {}
+    for batch in batches:
+        cache = [tuple(torch.randn((batch, 1, PREFIX_TOKENS, GEMMA_300M.head_dim), device=device, generator=generator).to(torch.bfloat16)
+                       for _ in range(2)) for _ in policy.expert]
+        noise = torch.randn((batch, ACTION_HORIZON, ACTION_DIM), device=device, generator=generator)
+        found[f"B{batch}"] = graph_milliseconds(lambda: policy.denoise(cache, PREFIX_TOKENS, noise))
+    return found
+
+
+@torch.no_grad()
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--quantization", default="fp8")

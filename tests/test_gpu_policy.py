@@ -84,3 +84,54 @@ def test_graph_replay_of_the_policy_step_equals_eager(device):
     assert torch.equal(graphed(observations), eager)
     half = {key: value[:2] for key, value in observations.items()}
     assert torch.equal(graphed(half), eager[:2])
+
+
+def _linear_records(block):
+    """Forward hooks on every quantised Linear bundle of one block: (name, input, output) of the real forward pass."""
+    records, handles = [], []
+    bundles = {"qkv": block.qkv.bundle, "o_proj": block.o_proj.bundle, "gate_up": block.gate_up, "down": block.down}
+    for name, module in bundles.items():
+        handles.append(module.register_forward_hook(
+            lambda mod, args, output, name=name: records.append((name, mod, args[0].detach().clone(), output.detach().clone()))))
+    return records, handles
+
+
+@pytest.mark.parametrize("quantization", ("fp8", "nvfp4"))
+@pytest.mark.parametrize("tower,batch,tokens", [("prefix", 1, 560), ("expert", 8, 10)])
+def test_full_width_layer_linears_match_the_oracle(device, quantization, tower, batch, tokens):
+    """One layer at its real width (Gemma-2B-shaped prefix layer over 560 tokens; Gemma-300M-shaped expert layer over
+    a 10-token chunk at B = 8): every quantised Linear of the forward pass -- packed QKV, output projection, packed
+    gate/up, down -- is compared with the CPU oracle of the registry route ON THE ACTIVATIONS THE LAYER ACTUALLY
+    PRODUCED, whole output, relative Frobenius <= 1e-3 and the per-element bound of the GEMM tests.  Same idea as
+    the reference's operator-equality test (tests/pi05/test_graphs.py:238-313), with the oracle as the other side."""
+    import numpy as np
+
+    from embodiinfer_b200 import layers as L
+    from embodiinfer_b200.pi05_shaped import GEMMA_2B, GEMMA_300M, GemmaBlock, rope_tables
+    from oracle import quant_oracle as O
+    from tests.util import assert_gemm_close, bits, u8
+
+    shape = GEMMA_2B if tower == "prefix" else GEMMA_300M
+    config = L.FP8Config(backend="native") if quantization == "fp8" else L.NVFP4Config(backend="native")
+    generator = torch.Generator(device=device).manual_seed(1003 if tower == "prefix" else 1004)
+    block = GemmaBlock(shape, shape.heads * shape.head_dim, config, generator, device)
+    x = torch.randn((batch, tokens, shape.width), device=device, generator=generator).to(torch.bfloat16)
+    rope = rope_tables(torch.arange(tokens, device=device), shape.head_dim)
+    records, handles = _linear_records(block)
+    with torch.no_grad():
+        output, _ = block(x, rope)
+    for handle in handles:
+        handle.remove()
+    assert torch.isfinite(output).all() and [name for name, *_ in records] == ["qkv", "o_proj", "gate_up", "down"]
+    for name, bundle, inputs, result in records:
+        rows = bits(inputs.reshape(-1, inputs.shape[-1]))
+        got = bits(result.reshape(-1, result.shape[-1]))
+        if quantization == "fp8":
+            codes, scale = O.fp8_quantize_T(rows, scalar_div="rcp", divisor_bf16=True)
+            want = O.fp8_linear(codes, scale, u8(bundle.weight), np.float32(bundle.weight_scale.item()))
+        else:
+            packed, block_scales, global_scale = O.nvfp4_quantize_T(rows, "rcp")
+            want = O.nvfp4_linear_registry(packed, block_scales, global_scale, u8(bundle.weight), u8(bundle.weight_scale),
+                                           np.float32(bundle.weight_global_scale.item()))
+        assert got.shape == want.shape, name
+        assert_gemm_close(got, want)

@@ -133,8 +133,8 @@ def test_gelu_mul(device, reference, bits, rows, columns):
     if bits != 4:
         theirs_packed = fusion.plan(gate, bits, scale_value).encode_packed(packed)
         ours_packed = torch.empty_like(out)
-        K.geglu(packed, None, ours_packed, bits=bits, table=fusion.table, rows=rows, columns=columns, row_stride=2 * columns,
-                scale=scale)
+        K.geglu(packed, packed[:, columns:], ours_packed, bits=bits, table=fusion.table, rows=rows, columns=columns,
+                row_stride=2 * columns, scale=scale)
         torch.cuda.synchronize()
         same(ours_packed, theirs_packed.output, "hidden activation from the packed matrix")
 
@@ -186,7 +186,7 @@ def test_norm_quant_single_pass(device, reference, bits, batch, tokens, columns,
     scales = torch.empty((rows, columns // 16), device=device, dtype=torch.uint8) if bits == 4 else None
     blocked = torch.zeros(blocked_bytes(rows, columns // 16), device=device, dtype=torch.uint8) if bits == 4 else None
     gate = torch.empty((batch, columns), device=device, dtype=torch.bfloat16) if adaptive else None
-    residual = torch.empty((rows, columns), device=device, dtype=torch.bfloat16)
+    residual = torch.empty_like(x)
     K.norm_quant(x, out, bits=bits, tokens=tokens, scale=scale, modulation=modulation, update=update,
                  update_gate=None if update_gate is None else update_gate.reshape(batch, columns), global_scale=plan.scale,
                  residual=residual, scales=scales, blocked=blocked, gate=gate)
