@@ -157,10 +157,13 @@ class B200Projection:
         self._check(inputs, encoded)
         rows = encoded.output.shape[0]
         output = self._buffer("linear", (rows, self.output_dim), torch.bfloat16)
+        # More than one token tile: the library may cut a long K across SM pairs when few feature tiles exist
+        # (e.g. the down projection of one observation: 560 x 2048 x 16384); it needs scratch for the partial sums.
+        workspace = K.linear_workspace(self.device) if rows > 128 else None
         K.linear(
             epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=rows, features=self.output_dim, width=self.input_dim,
             out=output, bias=bias, residual=None if residual is None else residual.reshape(rows, self.output_dim),
-            **self._operands(encoded),
+            workspace=workspace, **self._operands(encoded),
         )
         return output.reshape(shape)
 

@@ -811,12 +811,20 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
 
     // More than one 128-token tile: two CTAs share every weight tile (gemm_pair.cu), unless the caller asks for the
     // single-CTA schedule or passes a scale layout only that schedule reads.
-    if (!planning) {
-        const int pair_columns = pair_tile_columns(d, geglu);
-        if (pair_columns != 0) return run_linear_pair(d, epilogue, pair_columns, stream);
-    } else if (pair_tile_columns(d, geglu) != 0) {
-        *workspace_need = 0;
-        return B2_OK;
+    {
+        int pair_columns = 0, pair_splits = 1;
+        int64_t pair_need = 0;
+        const bool workspace_given = d->workspace != nullptr && aligned16(d->workspace);
+        pair_plan(d, geglu, planning || workspace_given, &pair_columns, &pair_splits, &pair_need);
+        if (!planning && pair_splits > 1 && d->workspace_bytes < pair_need)       // too small: decide again without splitting
+            pair_plan(d, geglu, false, &pair_columns, &pair_splits, &pair_need);
+        if (pair_columns != 0) {
+            if (planning) {
+                *workspace_need = pair_need;
+                return B2_OK;
+            }
+            return run_linear_pair(d, epilogue, pair_columns, pair_splits, stream);
+        }
     }
 
     KernelArgs args{};

@@ -376,8 +376,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn encode_tiled_entry();
 bool make_operand_map(CUtensorMap* map, const void* pointer, int64_t rows, int64_t row_bytes, int box_rows);
 
-// Paired schedule (gemm_pair.cu): accumulator columns it would use for this launch (0 = it does not apply), and the launch.
-int pair_tile_columns(const b2_linear_desc* d, bool geglu);
-int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, cudaStream_t stream);
+// Paired schedule (gemm_pair.cu): what it would do with a launch (0 columns = it does not apply), and the launch.
+void pair_plan(const b2_linear_desc* d, bool geglu, bool split_allowed, int* columns, int* splits, int64_t* workspace_need);
+int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, int splits, cudaStream_t stream);
 
 }  // namespace b2

@@ -32,6 +32,7 @@ namespace b2 {
 
 
 constexpr int PAIR_TOKENS = 2 * TILE_TOKENS;
+constexpr int PAIR_MAX_SPLITS = 4;
 
 // ---- cta_group::2 forms of the tcgen05 / TMA instructions -------------------------------------------------
 
@@ -103,14 +104,25 @@ __device__ __forceinline__ uint32_t idesc_nvf4_pair(uint32_t n) { return idesc_n
 // clusters that run side by side share a weight slab (it comes from HBM once and from the L2 afterwards).
 struct PairWalk {
     int item, step, m_pair, n_tile;
+    int tile, split, kb_begin, kb_end;      // split K: the work item is (tile, split) and covers K stages [kb_begin, kb_end)
     __device__ __forceinline__ explicit PairWalk(const KernelArgs& args) : item(int(blockIdx.x) >> 1), step(int(gridDim.x) >> 1) {
         decompose(args);
     }
     __device__ __forceinline__ void decompose(const KernelArgs& args) {
-        n_tile = item / args.num_m_tiles;
-        m_pair = item - n_tile * args.num_m_tiles;
+        tile = item;
+        split = 0;
+        kb_begin = 0;
+        kb_end = args.num_kb;
+        if (args.splits > 1) {
+            tile = item / args.splits;
+            split = item - tile * args.splits;
+            kb_begin = split * args.num_kb / args.splits;
+            kb_end = (split + 1) * args.num_kb / args.splits;
+        }
+        n_tile = tile / args.num_m_tiles;
+        m_pair = tile - n_tile * args.num_m_tiles;
     }
-    __device__ __forceinline__ bool valid(const KernelArgs& args) const { return item < args.total_tiles; }
+    __device__ __forceinline__ bool valid(const KernelArgs& args) const { return item < args.total_tiles * args.splits; }
     __device__ __forceinline__ void next(const KernelArgs& args) {
         item += step;
         decompose(args);
@@ -119,7 +131,13 @@ struct PairWalk {
 
 // KernelArgs as the pair kernel reads them: num_m_tiles = token PAIRS, tile_n = BN (columns of one CTA's
 // accumulator), scale_blocks = 128-row blocks of feature scales per tile (1 or 2), a_box_bytes unused.
-template <int KIND, int EPI>
+//
+// SPLIT (plain epilogue only): K is cut into `splits` ranges computed by different clusters, one work item each (the
+// host launches exactly tiles x splits clusters, all resident at once).  Every CTA leaves its fp32 partial sums (its
+// 128 token rows x BN) in the workspace, the CTAs of a tile meet at a counter, and then EACH of them adds the
+// partial sums of its own share of the tile's columns in split order and runs the epilogue on that share: the
+// fix-up is as parallel as the main loop, and the result does not depend on timing.  The meeting is a bounded wait.
+template <int KIND, int EPI, bool SPLIT>
 __global__ void __launch_bounds__(gemm_threads(EPI), 1)
 pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
                    const __grid_constant__ CUtensorMap act_scale_map, const __grid_constant__ CUtensorMap weight_scale_map,
@@ -215,7 +233,7 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
             int feature_atom_row[2];
             feature_atom_row[0] = (f0 >> 7) * args.scale_column_tiles;
             feature_atom_row[1] = (GEGLU ? ((args.up_row_offset + f0) >> 7) : (f0 >> 7) + 1) * args.scale_column_tiles;
-            for (int kb = 0; kb < num_kb; ++kb) {
+            for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
                 mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
                 __syncwarp();
                 filled |= 1u << stage;
@@ -273,7 +291,7 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
                     mbar_wait(acc_empty_bar + 8 * buffer, (use & 1u) ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + uint32_t(buffer * args.accumulator_stride);
-                    for (int kb = 0; kb < num_kb; ++kb) {
+                    for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
                         mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
                         tc_fence_after_sync();
                         const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
@@ -297,7 +315,7 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
                             const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes) >> 4;
                             constexpr uint32_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
                             const uint32_t feature_low = atom_low + PART;
-                            const uint32_t first_accumulate = kb != 0;
+                            const uint32_t first_accumulate = kb != walk.kb_begin;
                             auto issue = [&](const int count) {
                                 if (NVFP4) {
 #pragma unroll
@@ -382,7 +400,102 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
                     else mbar_arrive_cluster(acc_empty_bar_leader + 8 * buffer);
                 }
             };
-            if (GEGLU) {
+            if constexpr (SPLIT) {
+                // (a) this CTA's partial sums (valid token rows) -> its slot of the workspace, the accumulator goes back
+                const int64_t slot_floats = int64_t(TILE_TOKENS) * BN;
+                float* slots = args.partials + (int64_t(walk.tile) * args.splits * 2 + rank) * slot_floats;   // [split][rank][128][BN], this rank
+                // A slot is laid out [BN / 4 column groups][128 rows][4 floats]: the 32 lanes of a warp (32 token rows)
+                // write, and later read, 512 contiguous bytes per instruction.
+                // This CTA's own share of the columns (chunks [c0, c1) of 32) never leaves tensor memory: only the other
+                // chunks are written, and the accumulator is kept until the sums are done (a cluster has one work item).
+                const int row = quarter * 32 + lane;
+                const int chunks = BN / 32;
+                const int c0 = walk.split * chunks / args.splits, c1 = (walk.split + 1) * chunks / args.splits;
+                uint4* mine = reinterpret_cast<uint4*>(slots + int64_t(walk.split) * 2 * slot_floats) + row;
+                for (int chunk = part; chunk < chunks && warp_has_tokens; chunk += WARPS_PER_QUARTER) {
+                    if (chunk >= c0 && chunk < c1) continue;
+                    uint32_t v[32];
+                    tmem_load_32x32(lane_address + chunk * 32, v);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        __stcg(mine + (chunk * 8 + i) * TILE_TOKENS, make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+                }
+                // (b) meet the other splits of this tile (same rank): one thread counts in and waits, bounded
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"r"(32 * epilogue_warps(EPI)) : "memory");
+                unsigned int* arrived = args.tickets + 4 * walk.tile + rank;          // per tile: arrived[2], departed[2]
+                unsigned int* departed = arrived + 2;
+                if (threadIdx.x == 32 * FIRST_EPILOGUE_WARP) {
+                    atomicAdd(arrived, 1u);
+                    const long long start = clock64();
+                    unsigned int seen = 0, ok = 1;
+                    while (true) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(arrived) : "memory");
+                        if (seen >= unsigned(args.splits)) break;
+                        if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                            ok = 0;
+                            if (args.status != nullptr) atomicCAS(args.status, 0u, unsigned(STATUS_WAIT_SPLIT));
+                            break;
+                        }
+                    }
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(tmem_slot + 8), "r"(ok) : "memory");
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(32 * epilogue_warps(EPI)) : "memory");
+                unsigned int met;
+                asm volatile("ld.shared.u32 %0, [%1];" : "=r"(met) : "r"(tmem_slot + 8) : "memory");
+                // (c) this split's share of the columns: the other splits' partial sums (up to three: every load of a
+                // 16-column group is issued before the first addition) and its own from tensor memory, added in split
+                // order whichever CTA does it; then the plain epilogue
+                const float4* row_sums = reinterpret_cast<const float4*>(slots) + row;
+                for (int chunk = c0 + part; chunk < c1 && warp_has_tokens && met; chunk += WARPS_PER_QUARTER) {
+                    uint32_t first[32];
+                    tmem_load_32x32(lane_address + chunk * 32, first);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        float4 piece[PAIR_MAX_SPLITS][4];
+#pragma unroll
+                        for (int q = 0; q < PAIR_MAX_SPLITS; ++q)
+                            if (q < args.splits && q != walk.split) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    piece[q][j] = __ldcg(row_sums + int64_t(q) * 2 * (slot_floats / 4) + (chunk * 8 + half * 4 + j) * TILE_TOKENS);
+                            }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                            for (int q = 0; q < PAIR_MAX_SPLITS; ++q)
+                                if (q < args.splits) {
+                                    float4 term = piece[q][j];
+                                    if (q == walk.split)
+                                        term = make_float4(__uint_as_float(first[half * 16 + 4 * j]), __uint_as_float(first[half * 16 + 4 * j + 1]),
+                                                           __uint_as_float(first[half * 16 + 4 * j + 2]), __uint_as_float(first[half * 16 + 4 * j + 3]));
+                                    if (q == 0) {
+                                        total = term;
+                                    } else {
+                                        total.x = __fadd_rn(total.x, term.x); total.y = __fadd_rn(total.y, term.y);
+                                        total.z = __fadd_rn(total.z, term.z); total.w = __fadd_rn(total.w, term.w);
+                                    }
+                                }
+                            first[half * 16 + 4 * j] = __float_as_uint(total.x); first[half * 16 + 4 * j + 1] = __float_as_uint(total.y);
+                            first[half * 16 + 4 * j + 2] = __float_as_uint(total.z); first[half * 16 + 4 * j + 3] = __float_as_uint(total.w);
+                        }
+                    }
+                    epilogue_linear_chunk<EPI_LINEAR>(first, args, scale, round_scale, token, f0 + chunk * 32, compact_table, out_scale,
+                                                      out_scale_rcp, true_div);
+                }
+                release();
+                // (d) the last CTA to leave puts both counters back to zero for the next launch
+                asm volatile("bar.sync 1, %0;" ::"r"(32 * epilogue_warps(EPI)) : "memory");
+                if (threadIdx.x == 32 * FIRST_EPILOGUE_WARP && met) {
+                    if (atomicAdd(departed, 1u) == unsigned(args.splits - 1)) {
+                        *arrived = 0u;
+                        *departed = 0u;
+                    }
+                }
+            } else if (GEGLU) {
                 constexpr int UNITS_PER_WARP = (128 / 16 + WARPS_PER_QUARTER - 1) / WARPS_PER_QUARTER;   // at most 128 features per tile
                 const int units = features_per_tile / 16;
                 uint32_t gate[UNITS_PER_WARP][8], up[UNITS_PER_WARP][8];
@@ -467,8 +580,8 @@ static bool make_atom_map(CUtensorMap* map, const void* pointer, int64_t atoms) 
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int KIND, int EPI>
-static int launch_pair(const CUtensorMap& act_map, const CUtensorMap& weight_map, const CUtensorMap& act_scale_map,
+template <int KIND, int EPI, bool SPLIT>
+static int launch_pair_variant(const CUtensorMap& act_map, const CUtensorMap& weight_map, const CUtensorMap& act_scale_map,
                        const CUtensorMap& weight_scale_map, const KernelArgs& args, int shared_bytes, cudaStream_t stream) {
     static bool configured[64] = {false};
     static std::mutex lock;
@@ -477,12 +590,13 @@ static int launch_pair(const CUtensorMap& act_map, const CUtensorMap& weight_map
     if (device >= 0 && device < 64) {
         std::lock_guard<std::mutex> guard(lock);
         if (!configured[device]) {
-            const cudaError_t error = cudaFuncSetAttribute(pair_linear_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+            const cudaError_t error = cudaFuncSetAttribute(pair_linear_kernel<KIND, EPI, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
             if (error != cudaSuccess) return int(error);
             configured[device] = true;
         }
     }
-    const int clusters = args.total_tiles < sm_count() / 2 ? args.total_tiles : sm_count() / 2;
+    const int items = args.total_tiles * args.splits;
+    const int clusters = items < sm_count() / 2 ? items : sm_count() / 2;
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(unsigned(2 * clusters));
     config.blockDim = dim3(unsigned(gemm_threads(EPI)));
@@ -497,40 +611,78 @@ static int launch_pair(const CUtensorMap& act_map, const CUtensorMap& weight_map
     attributes[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attributes;
     config.numAttrs = pdl_enabled() ? 2 : 1;
-    const cudaError_t error = cudaLaunchKernelEx(&config, pair_linear_kernel<KIND, EPI>, act_map, weight_map, act_scale_map,
+    const cudaError_t error = cudaLaunchKernelEx(&config, pair_linear_kernel<KIND, EPI, SPLIT>, act_map, weight_map, act_scale_map,
                                                  weight_scale_map, args);
     return error == cudaSuccess ? int(cudaGetLastError()) : int(error);
 }
 
-// Columns of one accumulator for a launch the paired schedule takes, or 0 when it does not apply:
-//   more than one 128-token tile; no split K; the bundle-order scale layout (a tile's feature scales are whole
-//   128-row blocks: plain 128 or 256 features per tile, gated 128 + 128).
-int pair_tile_columns(const b2_linear_desc* d, bool geglu) {
-    if (d->tokens <= TILE_TOKENS) return 0;
-    if (d->flags & (B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRED_GATE_UP_SCALES)) return 0;
-    // A pair computes 256 token rows whether they exist or not.  When the last pair would be mostly padding (560
-    // tokens: 768 rows of work on pairs against 640 on single CTAs) the single-CTA schedule is as fast or faster
-    // (measured: 560 x 16384 x 2048 FP8 28.0 vs 27.1 us); with equal padding, or enough tokens for it not to
-    // matter, pairs win by 6-20 % (8192 x 1152 x 4304 FP8 51.6 vs 64.4 us; 8960 x 32768 x 2048 gated FP8 480 vs 543 us).
-    // B2_LINEAR_PAIRS asks for pairs regardless.
-    const int64_t pair_rows = int64_t((d->tokens + PAIR_TOKENS - 1) / PAIR_TOKENS) * PAIR_TOKENS;
-    const int64_t single_rows = int64_t((d->tokens + TILE_TOKENS - 1) / TILE_TOKENS) * TILE_TOKENS;
-    if (!(d->flags & B2_LINEAR_PAIRS) && pair_rows != single_rows && d->tokens < 2048) return 0;
-    const bool nvfp4 = d->kind == B2_KIND_NVFP4;
-    if (geglu) {
-        if (d->feature_tile != 0 && d->feature_tile != 128) return 0;
-        if (nvfp4 && d->features % 128 != 0) return 0;
-        return 256;
+template <int KIND, int EPI>
+static int launch_pair(const CUtensorMap& act_map, const CUtensorMap& weight_map, const CUtensorMap& act_scale_map,
+                       const CUtensorMap& weight_scale_map, const KernelArgs& args, int shared_bytes, cudaStream_t stream) {
+    if constexpr (EPI == EPI_LINEAR) {
+        if (args.splits > 1)
+            return launch_pair_variant<KIND, EPI, true>(act_map, weight_map, act_scale_map, weight_scale_map, args, shared_bytes, stream);
     }
-    if (d->feature_tile == 128 || d->feature_tile == 256) return d->feature_tile;
-    if (d->feature_tile != 0) return 0;
-    // fill the machine: the wider tile moves fewer operand bytes per MMA, the narrower one gives more work items
-    const int pairs = (d->tokens + PAIR_TOKENS - 1) / PAIR_TOKENS;
-    const int64_t wide_items = int64_t(pairs) * ((d->features + 255) / 256);
-    return wide_items >= sm_count() / 2 ? 256 : 128;
+    return launch_pair_variant<KIND, EPI, false>(act_map, weight_map, act_scale_map, weight_scale_map, args, shared_bytes, stream);
 }
 
-int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, cudaStream_t stream) {
+constexpr int64_t PAIR_TICKET_BYTES = 1024;      // per tile: arrived[2], departed[2] (uint32); zero between launches
+
+// What the paired schedule would do with this launch: accumulator columns (0 = it does not apply), K splits, and the
+// workspace bytes the splits need.
+//   Pairs apply to more than one 128-token tile and the bundle-order scale layout (a tile's feature scales are whole
+//   128-row blocks: plain 128 or 256 features per tile, gated 128 + 128).
+//   A pair computes 256 token rows whether they exist or not.  When the last pair would be mostly padding (560 tokens:
+//   768 rows of work on pairs against 640 on single CTAs) the single-CTA schedule is as fast or faster (measured:
+//   560 x 16384 x 2048 FP8 28.0 vs 27.1 us); with equal padding, or enough tokens for it not to matter, pairs win by
+//   6-20 % (8192 x 1152 x 4304 FP8 51.6 vs 64.4 us; 8960 x 32768 x 2048 gated FP8 480 vs 543 us).  B2_LINEAR_PAIRS asks
+//   for pairs regardless.
+//   Split K (plain epilogue, caller-provided workspace): when 256-column tiles leave more than half of the SM pairs
+//   idle and K is long (560 x 2048 x 16384: 24 tiles for 74 pairs), K is cut so that tiles x splits fills one wave;
+//   that launch runs on pairs whatever the padding.
+void pair_plan(const b2_linear_desc* d, bool geglu, bool split_allowed, int* columns, int* splits, int64_t* workspace_need) {
+    *columns = 0;
+    *splits = 1;
+    *workspace_need = 0;
+    if (d->tokens <= TILE_TOKENS) return;
+    if (d->flags & (B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRED_GATE_UP_SCALES)) return;
+    const bool nvfp4 = d->kind == B2_KIND_NVFP4;
+    const int pairs = (d->tokens + PAIR_TOKENS - 1) / PAIR_TOKENS;
+    const int clusters = sm_count() / 2;
+    if (!geglu && d->epilogue == B2_EPI_LINEAR && split_allowed && (d->feature_tile == 0 || d->feature_tile == 256)) {
+        const int64_t tiles = int64_t(pairs) * ((d->features + 255) / 256);
+        const int k_bytes = nvfp4 ? d->width / 2 : d->width;
+        const int num_kb = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+        int count = int(clusters / (tiles > 0 ? tiles : 1));
+        if (count > PAIR_MAX_SPLITS) count = PAIR_MAX_SPLITS;
+        while (count > 1 && num_kb / count < 16) --count;        // the fix-up costs about as much as ten K stages
+        if (count > 1 && tiles * 16 <= PAIR_TICKET_BYTES) {
+            *columns = 256;
+            *splits = count;
+            *workspace_need = PAIR_TICKET_BYTES + tiles * count * 2 * TILE_TOKENS * 256 * 4;
+            return;
+        }
+    }
+    const int64_t pair_rows = int64_t(pairs) * PAIR_TOKENS;
+    const int64_t single_rows = int64_t((d->tokens + TILE_TOKENS - 1) / TILE_TOKENS) * TILE_TOKENS;
+    if (!(d->flags & B2_LINEAR_PAIRS) && pair_rows != single_rows && d->tokens < 2048) return;
+    if (geglu) {
+        if (d->feature_tile != 0 && d->feature_tile != 128) return;
+        if (nvfp4 && d->features % 128 != 0) return;
+        *columns = 256;
+        return;
+    }
+    if (d->feature_tile == 128 || d->feature_tile == 256) {
+        *columns = d->feature_tile;
+        return;
+    }
+    if (d->feature_tile != 0) return;
+    // fill the machine: the wider tile moves fewer operand bytes per MMA, the narrower one gives more work items
+    const int64_t wide_items = int64_t(pairs) * ((d->features + 255) / 256);
+    *columns = wide_items >= clusters ? 256 : 128;
+}
+
+int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, int splits, cudaStream_t stream) {
     const bool nvfp4 = d->kind == B2_KIND_NVFP4;
     const bool geglu = is_gated(epilogue);
     KernelArgs args{};
@@ -543,7 +695,13 @@ int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, cud
     const int features_per_tile = geglu ? tile_columns / 2 : tile_columns;
     args.num_n_tiles = (d->features + features_per_tile - 1) / features_per_tile;
     args.total_tiles = args.num_m_tiles * args.num_n_tiles;
-    args.splits = 1;
+    args.splits = splits;
+    args.tickets = nullptr;
+    args.partials = nullptr;
+    if (splits > 1) {
+        args.tickets = static_cast<unsigned int*>(d->workspace);
+        args.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(d->workspace) + PAIR_TICKET_BYTES);
+    }
     args.scale_blocks = tile_columns > 128 ? 2 : 1;
     args.up_row_offset = d->features;
     args.scale_column_tiles = nvfp4 ? (d->width / 16 + 3) / 4 : 0;

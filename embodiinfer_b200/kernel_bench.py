@@ -5,6 +5,7 @@ Linear at the shapes of the pi0.5-style towers.  One JSON line per case.
     python -m embodiinfer_b200.kernel_bench --case 'linear/fp8'   # cases whose name matches the regex
     python -m embodiinfer_b200.kernel_bench --case cfg1 --library # also time torch's scaled_mm on the same shape
     python -m embodiinfer_b200.kernel_bench --case cfg1 --eager 3 # three plain launches and no timing: the form to run under a profiler
+    python -m embodiinfer_b200.kernel_bench --case 'quant|geglu|norm' --reference   # the reference's own kernels beside each case
 
 Method: each case is launched ``--launches`` times inside one CUDA graph, rotating over as many
 operand sets as it takes to exceed the L2 capacity (capped at 16 sets; ``"l2": "warm"`` marks the
@@ -265,6 +266,8 @@ def linear_cases(device, options=None):
             else:
                 arguments.update(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16,
                                  out=torch.empty((tokens, features), device=device, dtype=torch.bfloat16))
+            if options.get("workspace") and not gated:
+                arguments["workspace"] = K.linear_workspace(device)
             arguments["flags"] = arguments.get("flags", 0) | options.get("flags", 0)
             arguments["feature_tile"] = options.get("feature_tile", 0)
             return lambda: K.linear(**arguments)
@@ -297,16 +300,93 @@ def library_time(kind: str, tokens: int, rows: int, width: int, device, launches
         return None
 
 
+# ---- the reference's own CUDA kernels, timed by the same harness ---------------------------------------
+
+def reference_cases(device):
+    """The reference's SIMT kernels for this path (its quantiser, GELU*up epilogue, norm + encoder, LayerNorm + encoder and
+    transposing encoder), imported unmodified from ``baseline/_ref`` and compiled by the reference's own loader, at the
+    shapes of the cases above.  Yields (name of the matching case here, make, set_bytes)."""
+    import ctypes
+    import os
+    import sys
+    import tempfile
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent / "baseline" / "_ref"
+    if not (root / "embodiinfer").exists():
+        raise SystemExit("--reference needs the reference under baseline/_ref (python baseline/install_reference.py <checkout>)")
+    os.environ.setdefault("EMBODIINFER_CUDA_CACHE_DIR", tempfile.mkdtemp(prefix="embodiinfer_ref_cache_"))
+    sys.path.insert(0, str(root))
+    from embodiinfer.backend.cuda.activation import GeluMulFusion
+    from embodiinfer.backend.cuda.norm_quant import NormQuantReduceFusion
+    from embodiinfer.backend.cuda.normalization import NormFusion
+    from embodiinfer.backend.cuda.quantization import CudaQuantizer
+
+    quantizer = CudaQuantizer()
+    fusion = GeluMulFusion(quantizer, approximate="tanh")
+    norm_quant = NormQuantReduceFusion(quantizer, NormFusion())
+    library = norm_quant.library
+    pointer = ctypes.c_void_p
+    library.cc_layer_norm_fp8.argtypes = [pointer] * 6 + [ctypes.c_float, ctypes.c_int, ctypes.c_int, pointer]
+    library.cc_layer_norm_fp4.argtypes = [pointer] * 7 + [ctypes.c_float, ctypes.c_int, ctypes.c_int, pointer]
+    stream = lambda: torch.cuda.current_stream(device).cuda_stream
+
+    for rows in (560, 17920):
+        columns = 2048
+        for bits, name, out_bytes in ((8, "fp8_C", 1.0), (4, "nvfp4_C", 0.5 + 1 / 16)):
+            def make(_i, rows=rows, bits=bits):
+                x = torch.randn((rows, columns), device=device).to(torch.bfloat16)
+                plan = quantizer.plan(x, bits, 0.01 if bits == 8 else 0.002)
+                return lambda: plan.quantize(x)
+            yield f"quant/{name}/{rows}x{columns}", make, int(rows * columns * (2 + out_bytes))
+        for bits, out_bytes in ((8, 1.0), (4, 0.5 + 1 / 16)):
+            def make(_i, rows=rows, bits=bits):
+                x = torch.randn((rows // 560, 560, columns), device=device).to(torch.bfloat16)
+                update = torch.randn_like(x)
+                weight = torch.randn(columns, device=device) * 0.1
+                plan = norm_quant.plan(x, bits=bits, calibrated_scale=0.01, adaptive=False)
+                return lambda: plan.residual_normalize(x, update, None, scale=weight)
+            yield f"norm/residual_rms_bits{bits}/{rows}x{columns}", make, int(rows * columns * (6 + out_bytes))
+    rows, features = 560, 16384
+    for bits, out_bytes in ((16, 2.0), (8, 1.0), (4, 0.5 + 1 / 16)):
+        def make(_i, bits=bits):
+            packed = torch.randn((rows, 2 * features), device=device).to(torch.bfloat16)
+            gate, up = packed[:, :features].contiguous(), packed[:, features:].contiguous()
+            plan = fusion.plan(gate, bits, None if bits == 16 else 0.01)
+            return lambda: plan.encode(gate, up)
+        yield f"geglu/standalone_bits{bits}/{rows}x{features}", make, int(rows * features * (4 + out_bytes))
+    columns = 1152
+    for rows in (768, 24576):
+        for bits, out_bytes in ((8, 1.0), (4, 0.5 + 1 / 16)):
+            def make(_i, rows=rows, bits=bits):
+                x = torch.randn((rows, columns), device=device).to(torch.bfloat16)
+                update = torch.randn_like(x)
+                residual = torch.empty_like(x)
+                weight = torch.randn(columns, device=device).to(torch.bfloat16)
+                bias = torch.randn(columns, device=device).to(torch.bfloat16)
+                out = torch.empty((rows, columns if bits == 8 else columns // 2), device=device, dtype=torch.uint8)
+                blocked = torch.zeros(_blocked_bytes(rows, columns // 16), device=device, dtype=torch.uint8)
+                if bits == 8:
+                    return lambda: library.cc_layer_norm_fp8(x.data_ptr(), update.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                                                             residual.data_ptr(), out.data_ptr(), 40.0, rows, columns, stream())
+                return lambda: library.cc_layer_norm_fp4(x.data_ptr(), update.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                                                         residual.data_ptr(), out.data_ptr(), blocked.data_ptr(), 0.004, rows, columns, stream())
+            yield f"norm/residual_layer_norm_bits{bits}/{rows}x{columns}", make, int(rows * columns * (6 + out_bytes))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--case", default=".", help="regex over case names")
     parser.add_argument("--launches", type=int, default=32)
     parser.add_argument("--library", action="store_true", help="also time torch's scaled_mm at each linear shape")
     parser.add_argument("--list", action="store_true")
+    parser.add_argument("--reference", action="store_true",
+                        help="also time the reference's own CUDA kernels (baseline/_ref) at the quantiser / epilogue / norm cases")
     parser.add_argument("--sets", type=int, default=0, help="operand sets in rotation (1 = warm L2; default: enough to exceed the L2)")
     parser.add_argument("--eager", type=int, default=0, help="run this many plain launches per case and no timing (for profilers)")
     parser.add_argument("--flags", type=int, default=0, help="OR-ed into the b2_linear flags (8 = stream the token tile, 64 = one CTA per tile)")
     parser.add_argument("--feature-tile", type=int, default=0, help="features per tile (0 = the library's choice)")
+    parser.add_argument("--workspace", action="store_true", help="give the plain launches split-K scratch (the library then decides)")
     parser.add_argument("--unpaired", action="store_true", help="gated NVFP4 cases without the paired gate/up scale layout")
     args = parser.parse_args()
     pattern = re.compile(args.case)
@@ -319,8 +399,13 @@ def main() -> None:
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     peaks = {"hbm_gbs": 6541.5, "fp8_tflops": 4500.0, "nvfp4_tflops": 9000.0}
-    options = {"flags": args.flags, "feature_tile": args.feature_tile, "unpaired": args.unpaired}
+    options = {"flags": args.flags, "feature_tile": args.feature_tile, "unpaired": args.unpaired, "workspace": args.workspace}
     sources = (quantiser_cases, geglu_cases, norm_cases, layout_cases, lambda dev: linear_cases(dev, options))
+    reference_us = {}
+    if args.reference:
+        for name, make, set_bytes in reference_cases(device):
+            if pattern.search(name):
+                reference_us[name] = round(time_graph(make, set_bytes, args.launches)[0], 2)
     for source in sources:
         for name, make, set_bytes, algorithmic_bytes, flops in source(device):
             if not pattern.search(name):
@@ -344,6 +429,9 @@ def main() -> None:
                         line["torch_scaled_mm_tflops"] = round(flops / library / 1e6, 1)
             else:
                 line["frac_of_measured_hbm"] = round(line["gbs"] / peaks["hbm_gbs"], 3)
+                if name in reference_us:
+                    line["reference_kernel_us"] = reference_us[name]
+                    line["reference_kernel_gbs"] = round(algorithmic_bytes / reference_us[name] / 1e3, 1)
             print(json.dumps(line), flush=True)
             torch.cuda.empty_cache()
 

@@ -195,7 +195,7 @@ def test_split_k_is_deterministic_and_matches_oracle(device, kind, epilogue, tok
     host, dev = operands(kind, tokens, (2 if gated else 1) * features, width, 11 + tokens, device)
     table_host = gelu_table_cpu("tanh")
     table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
-    workspace = torch.zeros(16 << 20, device=device, dtype=torch.uint8)
+    workspace = torch.zeros(32 << 20, device=device, dtype=torch.uint8)
     outputs = []
     for ws in (workspace, workspace, False):
         out = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
