@@ -228,8 +228,6 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "INFO")             # communicator lines (rank / nranks) on stderr
-        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
         dist.init_process_group("nccl", device_id=device)
 
     x, gate, up, down = synthetic_inputs(SEED + rank)       # every rank its own batch; same weights' distribution

@@ -9,7 +9,7 @@ Arithmetic (rounding points, encoders, scales) is that of the separate steps.
 
 from __future__ import annotations
 
-from collections.abc import Callable
+from collections.abc import Callable, Sequence
 from typing import Literal
 
 import torch
@@ -44,12 +44,31 @@ class FusedMlpPlan:
         approximate: Literal["none", "tanh"] = "tanh",
         workspace_key: Callable[[torch.device], WorkspaceKey] | None = None,
         table: torch.Tensor | None = None,
+        outliers: Sequence[int] | None = None,
     ) -> None:
         if gate_up == "bf16":
             raise ValueError("the fused MLP needs fp8 or nvfp4 gate/up projections")
         if gate_weight.shape != up_weight.shape or down_weight.shape != tuple(reversed(gate_weight.shape)):
             raise ValueError("Optimized MLP projection dimensions do not match")
         self.inter_size, self.hidden_size = gate_weight.shape
+        # BF16 outlier channels (policies/pi05/inference/mlp.py:119-131): hidden channels whose range would dominate
+        # their NVFP4 blocks are taken out of the quantised path (their gate/up rows and down columns are zeroed before
+        # packing, so the kept channels no longer share block scales with them) and computed beside it in bf16.
+        self.side_gate_up = self.side_down = None
+        self._side_buffers: dict = {}
+        self._workspace_key = workspace_key or (lambda device: ("stream", torch.cuda.current_stream(device).cuda_stream))
+        if outliers is not None:
+            if gate_up != "nvfp4":
+                raise ValueError("BF16 outlier channels require NVFP4 gate/up projections")
+            index = torch.tensor(tuple(outliers), dtype=torch.long, device=gate_weight.device)
+            if index.numel() == 0 or int(index.max()) >= self.inter_size or int(index.min()) < 0:
+                raise ValueError("Outlier channels exceed the MLP width")
+            self.side_gate_up = torch.cat((gate_weight[index], up_weight[index]), dim=0).t().contiguous()
+            self.side_down = down_weight[:, index].t().contiguous()
+            gate_weight, up_weight, down_weight = (weight.clone() for weight in (gate_weight, up_weight, down_weight))
+            gate_weight[index] = 0
+            up_weight[index] = 0
+            down_weight[:, index] = 0
         self.gate_up = B200Projection.gated_pair(gate_weight, up_weight, gate_up_max, gate_up, quantizer, workspace_key)
         self.down = B200Projection(down_weight, down_max, down, quantizer if down != "bf16" else None, workspace_key)
         self.table = gelu_table(gate_weight.device, approximate) if table is None else table
@@ -59,8 +78,11 @@ class FusedMlpPlan:
     def encode(self, inputs: torch.Tensor) -> EncodedActivation:
         return self.gate_up.encode(inputs)
 
-    def project(self, inputs: torch.Tensor, encoded: EncodedActivation, *, residual: torch.Tensor | None = None):
-        """``encoded`` is ``inputs`` at the gate/up scale (shared by both halves, mlp.py:222)."""
+    def project(self, inputs: torch.Tensor, encoded: EncodedActivation, *, residual: torch.Tensor | None = None,
+                normalized: torch.Tensor | None = None):
+        """``encoded`` is ``inputs`` at the gate/up scale (shared by both halves, mlp.py:222).  With outlier channels,
+        ``normalized`` is the bf16 MLP input (the norm's output) the side path multiplies; it defaults to ``inputs``,
+        which is right unless the caller passes the residual stream there (the fused norm + encoder route)."""
         bits = _BITS[self.down.precision]
         scale = None if bits == 16 else self.down.maximum / (448 * (6 if bits == 4 else 1))
         hidden = self.gate_up.apply_gated(
@@ -68,9 +90,32 @@ class FusedMlpPlan:
         )
         shape = (*inputs.shape[:-1], self.inter_size)
         if bits == 16:
-            return self.down.apply(hidden.output.reshape(shape), None)
-        # The encoded hidden activation is complete; `apply` only reads shape/dtype/device of its first argument.
-        return self.down.apply(_ShapeOnly(shape, inputs), hidden, residual=residual)
+            output = self.down.apply(hidden.output.reshape(shape), None)
+        else:
+            # The encoded hidden activation is complete; `apply` only reads shape/dtype/device of its first argument.
+            output = self.down.apply(_ShapeOnly(shape, inputs), hidden, residual=residual)
+        if self.side_down is not None:
+            source = inputs if normalized is None else normalized
+            if not isinstance(source, torch.Tensor):
+                raise RuntimeError("BF16 outlier channels need the residual and norm of the fused NVFP4 input")
+            self._add_outliers(source, output)
+        return output
+
+    def _add_outliers(self, normalized: torch.Tensor, output: torch.Tensor) -> None:
+        """Accumulate the outlier channels' bf16 GELU(gate) * up and down projection into ``output``
+        (mlp.py:242-260: two library GEMMs and one elementwise product, outside the quantised path)."""
+        rows_in = normalized.reshape(-1, normalized.shape[-1])
+        rows, width = rows_in.shape[0], self.side_down.shape[0]
+        key = (rows, normalized.device, self._workspace_key(normalized.device))
+        if key not in self._side_buffers:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("Warm the BF16 outlier channels before graph capture")
+            self._side_buffers[key] = (torch.empty((rows, 2 * width), device=normalized.device, dtype=torch.bfloat16),
+                                       torch.empty((rows, width), device=normalized.device, dtype=torch.bfloat16))
+        gate_up, hidden = self._side_buffers[key]
+        torch.matmul(rows_in, self.side_gate_up, out=gate_up)
+        torch.mul(torch.nn.functional.gelu(gate_up[:, :width], approximate=self.approximate), gate_up[:, width:], out=hidden)
+        output.view(-1, output.shape[-1]).addmm_(hidden, self.side_down)
 
     def __call__(self, inputs: torch.Tensor, *, residual: torch.Tensor | None = None) -> torch.Tensor:
         return self.project(inputs, self.encode(inputs), residual=residual)
@@ -78,10 +123,16 @@ class FusedMlpPlan:
     def release_scope(self, scope: WorkspaceKey) -> None:
         self.gate_up.release_scope(scope)
         self.down.release_scope(scope)
+        for key in tuple(self._side_buffers):
+            if key[-1] == scope:
+                del self._side_buffers[key]
 
     def refit_tensors(self, prefix: str = "") -> dict[str, torch.Tensor]:
         """Packed operands of both launches, for an in-place weight refit (see ``B200Projection.refit_tensors``)."""
-        return {**self.gate_up.refit_tensors(prefix + "gate_up."), **self.down.refit_tensors(prefix + "down.")}
+        found = {**self.gate_up.refit_tensors(prefix + "gate_up."), **self.down.refit_tensors(prefix + "down.")}
+        if self.side_down is not None:
+            found[prefix + "side_gate_up"], found[prefix + "side_down"] = self.side_gate_up, self.side_down
+        return found
 
 
 class FusedGeluMlpPlan:

@@ -9,8 +9,8 @@ tensor arithmetic only: nothing here launches a kernel of this package; ``fused_
 folded weights to ``FusedMlpPlan``.
 
 The reference ships ranges for its own devices ("thor", "spark", "4090"); a B200 deployment passes its own
-schema-2 file (or names one of those device keys explicitly).  The bf16 outlier side path is tied to the Thor
-prefix tower in the reference and is rejected here with the reference's own message.
+schema-2 file (or names one of those device keys explicitly).  The bf16 outlier side path, which the reference
+ties to its Thor prefix tower (mlp.py:119-121), is available for any NVFP4 gate/up layer here.
 """
 
 from __future__ import annotations
@@ -165,8 +165,68 @@ def fused_mlp_from_layer(gate_weight: torch.Tensor, up_weight: torch.Tensor, dow
         raise ValueError("Optimized Pi05 MLPs require bias-free BF16 projection weights")
     if gate_weight.shape != up_weight.shape or down_weight.shape != tuple(reversed(gate_weight.shape)):
         raise ValueError("Optimized Pi05 MLP projection dimensions do not match")
-    if layer.outliers is not None:
-        raise ValueError("BF16 outlier channels require a Thor prefix NVFP4 MLP")
     gate_weight, up_weight = smoothed_projection_weights(gate_weight.detach(), up_weight.detach(), layer)
+    if layer.outliers is not None and max(layer.outliers) >= gate_weight.shape[0]:
+        raise ValueError("Outlier channels exceed the MLP width")
     return FusedMlpPlan(gate_weight, up_weight, down_weight.detach(), gate_up_max=layer.gate_up_max, down_max=layer.down_max,
-                        gate_up=layer.gate_up, down=layer.down, quantizer=quantizer, **options)
+                        gate_up=layer.gate_up, down=layer.down, quantizer=quantizer, outliers=layer.outliers, **options)
+
+
+# ---- deployment recipes -------------------------------------------------------------------------------------
+# Counterpart of ``resolve_preset`` (embodiinfer/policies/pi05/inference/presets.py:27-112): one name selects the
+# formats of the prefix and action towers' MLPs, the calibration supplies the per-layer ranges, and the recipe names
+# the operator back ends a policy should ask the registries for.  The reference has launch profiles for "thor",
+# "spark", "orin" and "4090"; this package adds the one for "b200" and keeps the reference's preset names, checks
+# and messages.
+
+_FORMATS = ("bf16", "fp8", "nvfp4")
+_OPTIMIZED = {"bf16": ("bf16", "bf16"),
+              **{f"{prefix}-{action}": (prefix, action) for prefix in _FORMATS for action in _FORMATS if (prefix, action) != ("bf16", "bf16")}}
+DEVICES = ("b200",)
+
+
+@dataclass(frozen=True)
+class Recipe:
+    """What a preset resolves to: tower formats, per-layer calibrated ranges (``None`` for a bf16 tower) and the back-end
+    names to request from ``quantization_backends`` / ``projection_backends`` / ``gelu_mul_backends`` /
+    ``norm_quant_backends`` (the names ``embodiinfer_b200.integration.register_into_reference`` registers)."""
+
+    hardware: str
+    prefix: Precision = "bf16"
+    action: Precision = "bf16"
+    prefix_layers: tuple[MlpLayerPrecision, ...] | None = None
+    action_layers: tuple[MlpLayerPrecision, ...] | None = None
+    checkpoint_sha256: str | None = None
+    fused_mlp: bool = False
+    numerics: str = "openpi_rlinf"
+    activation: str = "gelu_pytorch_exact"
+    operators: Mapping[str, str] | None = None
+
+    @property
+    def has_quantized_mlp(self) -> bool:
+        return self.prefix != "bf16" or self.action != "bf16"
+
+
+def resolve_preset(device: str, preset: str, *, calibration: str | Path | Mapping | None) -> Recipe:
+    """Resolve one complete recipe; format names are ordered prefix then action (``"nvfp4-fp8"``)."""
+    if device not in DEVICES:
+        raise ValueError(f"Unknown Pi05 device {device!r}; choose from {DEVICES}")
+    if preset == "strict":
+        if calibration is not None:
+            raise ValueError("The strict BF16 preset does not use calibration")
+        return Recipe(hardware=device)
+    if preset in ("w4a16", "w8a8-w4a16"):
+        raise ValueError("Integer MLP presets require Orin and an offline calibrated weight manifest")
+    if preset not in _OPTIMIZED:
+        raise ValueError("Pi05 preset must be strict, bf16, w4a16, w8a8-w4a16 or a prefix-action format pair")
+    prefix, action = _OPTIMIZED[preset]
+    operators = {"quantization": "b200", "projection": "b200", "gelu_mul": "b200", "norm_quant": "b200", "attention_projection": "b200"}
+    recipe = Recipe(hardware=device, prefix=prefix, action=action, fused_mlp=True, operators=operators)
+    if not recipe.has_quantized_mlp:
+        return recipe
+    if calibration is None:
+        raise ValueError(f"Calibration has no ranges for {device}")      # the reference falls back to its bundled file, which has no B200 entry
+    found = load_calibration(calibration, hardware=device, formats={"prefix": prefix, "action": action},
+                             numerics=recipe.numerics, activation=recipe.activation)
+    return Recipe(hardware=device, prefix=prefix, action=action, prefix_layers=found.prefix_layers, action_layers=found.action_layers,
+                  checkpoint_sha256=found.checkpoint_sha256, fused_mlp=True, operators=operators)

@@ -194,13 +194,6 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
         tmem_alloc_pair(tmem_slot, TMEM_COLUMNS);
         tmem_relinquish_pair();
     }
-    if (USES_TABLE) {
-        const int span = args.gelu_hi - args.gelu_lo;
-        for (int i = threadIdx.x; i < 2 * span; i += gemm_threads(EPI)) {
-            const int code = i < span ? args.gelu_lo + i : 0x8000 + args.gelu_lo + (i - span);
-            asm volatile("st.shared.u16 [%0], %1;" ::"r"(compact_table + 2u * uint32_t(i)), "h"(__ldg(args.gelu_table + code)) : "memory");
-        }
-    }
     // Both CTAs' barriers and tensor memory exist before either touches the other's.
     tc_fence_before_sync();
     cluster_arrive();
@@ -208,6 +201,17 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
     tc_fence_after_sync();
     uint32_t tmem_base;
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+    // The shared-memory copy of the GELU table is the epilogue warps' business only: they fill it (the table is a
+    // constant of the model, so this may run ahead of the launches before this one) and meet at their own barrier,
+    // while the producer and the MMA warp are already at work.
+    if (USES_TABLE && warp >= FIRST_EPILOGUE_WARP) {
+        const int span = args.gelu_hi - args.gelu_lo;
+        for (int i = int(threadIdx.x) - 32 * FIRST_EPILOGUE_WARP; i < 2 * span; i += 32 * epilogue_warps(EPI)) {
+            const int code = i < span ? args.gelu_lo + i : 0x8000 + args.gelu_lo + (i - span);
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(compact_table + 2u * uint32_t(i)), "h"(__ldg(args.gelu_table + code)) : "memory");
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(32 * epilogue_warps(EPI)) : "memory");
+    }
 
     pdl_wait();
 

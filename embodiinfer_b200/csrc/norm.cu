@@ -18,8 +18,6 @@
 // columns (e4m3), 9/16*columns (NVFP4) or 2*columns (bf16) out for the result.
 #include "common.cuh"
 
-#include <cstdlib>
-
 namespace b2 {
 
 constexpr int NORM_THREADS = 256;       // strided order: the reference's reduction width
@@ -386,8 +384,10 @@ static int launch_norm_bits(const NormArgs& a, cudaStream_t stream) {
     int status;
     const bool lanes8 = a.columns == 1024 || a.columns == 2048;
     const int blocks = (a.rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK;
-    static const bool experiment_block4 = getenv("B2_NORM_BLOCK4") != nullptr;
-    if (BITS == 4 && experiment_block4 && lanes8) {
+    if (BITS == 4 && lanes8) {
+        // NVFP4: the row-per-block shape at every row count.  The encoder's arithmetic, not memory, bounds this kernel, and a
+        // thread that holds one 8-column vector leaves the scheduler more warps to hide it with than a lane that holds 64
+        // columns of a whole row (17920 x 2048 with update and residual: 69 us against 76 us; the reference's kernel: 64 us).
         status = launch_kernel(norm_encode_block_kernel<BITS, ORDER_LANES8>, dim3(unsigned(a.rows)), dim3(unsigned(a.columns / 8)), size_t(0), stream, a);
     } else if (lanes8 && a.rows >= NORM_WARP_ROWS_THRESHOLD && a.columns == 2048) {
         status = launch_kernel(norm_encode_warp_kernel<BITS, 8>, dim3(unsigned(blocks)), dim3(unsigned(NORM_ROWS_PER_BLOCK * 32)), size_t(0), stream, a);
@@ -551,8 +551,7 @@ static int launch_layer_norm_bits(const LayerNormArgs& a, cudaStream_t stream) {
     int status;
     const int blocks = (a.rows + NORM_ROWS_PER_BLOCK - 1) / NORM_ROWS_PER_BLOCK;
     const bool narrow = a.columns <= 1152;                       // the reference's 160-thread block (norm_quant.cu:681)
-    static const bool experiment_block4 = getenv("B2_NORM_BLOCK4") != nullptr;
-    if (a.rows >= NORM_WARP_ROWS_THRESHOLD && !(BITS == 4 && experiment_block4)) {
+    if (a.rows >= NORM_WARP_ROWS_THRESHOLD) {
         if (narrow) status = launch_kernel(layer_norm_encode_kernel<BITS, 5, true>, dim3(unsigned(blocks)), dim3(unsigned(NORM_ROWS_PER_BLOCK * 32)), size_t(0), stream, a);
         else status = launch_kernel(layer_norm_encode_kernel<BITS, 8, true>, dim3(unsigned(blocks)), dim3(unsigned(NORM_ROWS_PER_BLOCK * 32)), size_t(0), stream, a);
     } else {

@@ -111,10 +111,37 @@ def test_folding_leaves_the_mlp_input_product_unchanged():
 def test_plan_builder_rejects_layouts_without_a_gpu():
     gate = torch.zeros((96, 64), dtype=torch.bfloat16)
     down = torch.zeros((64, 96), dtype=torch.bfloat16)
-    layer = C.MlpLayerPrecision("nvfp4", "nvfp4", 1.0, 1.0, outliers=[3])
-    with pytest.raises(ValueError, match="Thor prefix"):
+    layer = C.MlpLayerPrecision("nvfp4", "nvfp4", 1.0, 1.0, outliers=[96])
+    with pytest.raises(ValueError, match="Outlier channels exceed the MLP width"):
         C.fused_mlp_from_layer(gate, gate, down, layer, quantizer=None)
     with pytest.raises(ValueError, match="dimensions do not match"):
         C.fused_mlp_from_layer(gate, gate, gate, C.MlpLayerPrecision("fp8", "fp8"), quantizer=None)
     with pytest.raises(ValueError, match="BF16 projection weights"):
         C.fused_mlp_from_layer(gate.float(), gate.float(), down.float(), C.MlpLayerPrecision("fp8", "fp8"), quantizer=None)
+
+
+def test_presets_resolve_like_the_reference():
+    """``resolve_preset`` for the B200 launch profile: the reference's preset names, checks and messages
+    (policies/pi05/inference/presets.py:27-112), ranges from a schema-2 document."""
+    row = dict(gate_up="nvfp4", down="nvfp4", gate_up_max=3.0, down_max=40.0)
+    document = {"schema_version": 2, "numerics": "openpi_rlinf", "activation": "gelu_pytorch_exact", "checkpoint_sha256": "ab" * 32,
+                "devices": {"b200": {"prefix": {"nvfp4": [dict(row, outliers=[7]) if i == 3 else row for i in range(18)]},
+                                     "action": {"fp8": [dict(gate_up="fp8", down="fp8", gate_up_max=2.0, down_max=9.0)] * 18}}}}
+    recipe = C.resolve_preset("b200", "nvfp4-fp8", calibration=document)
+    assert (recipe.prefix, recipe.action, recipe.fused_mlp, recipe.checkpoint_sha256) == ("nvfp4", "fp8", True, "ab" * 32)
+    assert len(recipe.prefix_layers) == len(recipe.action_layers) == 18 and recipe.prefix_layers[3].outliers == (7,)
+    assert recipe.operators["norm_quant"] == "b200" and recipe.has_quantized_mlp
+    assert C.resolve_preset("b200", "strict", calibration=None) == C.Recipe(hardware="b200")
+    assert not C.resolve_preset("b200", "bf16", calibration=None).has_quantized_mlp
+    with pytest.raises(ValueError, match="Unknown Pi05 device 'thor'"):
+        C.resolve_preset("thor", "fp8-fp8", calibration=document)
+    with pytest.raises(ValueError, match="strict BF16 preset does not use calibration"):
+        C.resolve_preset("b200", "strict", calibration=document)
+    with pytest.raises(ValueError, match="Integer MLP presets require Orin"):
+        C.resolve_preset("b200", "w4a16", calibration=document)
+    with pytest.raises(ValueError, match="prefix-action format pair"):
+        C.resolve_preset("b200", "int8-int8", calibration=document)
+    with pytest.raises(ValueError, match="requires 18 action MLP layer ranges for nvfp4"):
+        C.resolve_preset("b200", "nvfp4-nvfp4", calibration=document)
+    with pytest.raises(ValueError, match="no ranges for b200"):
+        C.resolve_preset("b200", "fp8-fp8", calibration=None)

@@ -272,3 +272,45 @@ def test_refit_refreshes_the_plans_in_place(device, precision):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(captured, want)
+
+
+def test_bf16_outlier_channels_beside_the_nvfp4_mlp(device):
+    """Hidden channels listed as outliers leave the NVFP4 path (their gate/up rows and down columns are packed as
+    zeros) and are computed in bf16 beside it, as in the reference's ``MlpPlan._add_outliers``
+    (policies/pi05/inference/mlp.py:119-131, 242-260).  The result is exactly the zeroed NVFP4 MLP plus the bf16 side
+    path, and it is closer to the unquantised MLP than the plain NVFP4 plan when those channels carry huge values."""
+    hidden, inter, tokens = 256, 512, 200
+    quantizer = L.quantization_backends.get("cuda", request(device, bits_=4))
+    gate = make_weight((inter, hidden), 1, std=0.05).to(device=device, dtype=torch.bfloat16)
+    up = make_weight((inter, hidden), 2, std=0.05).to(device=device, dtype=torch.bfloat16)
+    down = make_weight((hidden, inter), 3, std=0.05).to(device=device, dtype=torch.bfloat16)
+    outliers = (5, 130, 131, 400)
+    with torch.no_grad():
+        gate[list(outliers)] *= 30                   # these hidden channels dwarf their neighbours' block scales
+        up[list(outliers)] *= 30
+    x = make_input((tokens, hidden), 9, outliers=False).to(device)
+    exact = torch.nn.functional.gelu(x.float() @ gate.float().t(), approximate="tanh") * (x.float() @ up.float().t())
+    hidden_peak = float(exact.abs().max())
+    exact = exact @ down.float().t()
+    kept = [c for c in range(inter) if c not in outliers]
+    kept_peak = float((torch.nn.functional.gelu(x.float() @ gate.float()[kept].t(), approximate="tanh") * (x.float() @ up.float()[kept].t())).abs().max())
+    common = dict(gate_up_max=float(x.abs().max()), gate_up="nvfp4", down="nvfp4", quantizer=quantizer, approximate="tanh")
+    plain = FusedMlpPlan(gate, up, down, down_max=hidden_peak, **common)
+    protected = FusedMlpPlan(gate, up, down, down_max=kept_peak, outliers=outliers, **common)
+    got = protected(x).clone()
+    # composition: the same plan without the side path on zeroed weights, plus the side path by hand
+    index = torch.tensor(outliers, device=device)
+    gate0, up0, down0 = gate.clone(), up.clone(), down.clone()
+    gate0[index] = 0
+    up0[index] = 0
+    down0[:, index] = 0
+    zeroed = FusedMlpPlan(gate0, up0, down0, down_max=kept_peak, **common)(x).clone()
+    side = torch.nn.functional.gelu(x @ gate[index].t(), approximate="tanh") * (x @ up[index].t())
+    assert torch.equal(got, zeroed.addmm_(side, down[:, index].t().contiguous()))
+    error = lambda y: float((y.float() - exact).norm() / exact.norm())
+    assert error(got) < 0.5 * error(plain(x)), (error(got), error(plain(x)))
+    assert set(protected.refit_tensors()) >= {"side_gate_up", "side_down"}
+    with pytest.raises(ValueError, match="exceed the MLP width"):
+        FusedMlpPlan(gate, up, down, down_max=1.0, outliers=(inter,), **common)
+    with pytest.raises(ValueError, match="require NVFP4"):
+        FusedMlpPlan(gate, up, down, gate_up_max=1.0, down_max=1.0, gate_up="fp8", down="fp8", quantizer=quantizer, outliers=(1,))
