@@ -23,11 +23,21 @@ from ..weights import blocked_scales
 from .quantization import blocked_scale_bytes
 
 
-def uses_sm_pairs(tokens: int) -> bool:
-    """Whether ``b2_linear`` runs this many token rows on pairs of SMs (256-row tiles) when the scale layout allows
-    it: more than 128 rows and no more padding than 128-row tiles would add, or at least 2048 rows (the library's
-    own rule; gated NVFP4 launches must pass the matching block-scale layout)."""
-    return tokens > 128 and (tokens >= 2048 or -(-tokens // 256) * 256 == -(-tokens // 128) * 128)
+def gated_scale_layout(tokens: int, width: int) -> str:
+    """Which of the two block-scale layouts an NVFP4 gate/up launch over ``tokens`` rows passes to ``b2_linear``.
+
+    ``"paired"`` (64 gate rows + the 64 up rows of the same features per 128-row block) serves 64 + 64-column tiles:
+    the single-CTA schedule, and on SM pairs the order that keeps the token rows on chip with two accumulators in
+    tensor memory.  ``"bundle"`` (gate rows, then up rows) serves the 128 + 128-column tiles of SM pairs.  Measured
+    on a B200 (microseconds, paired / bundle): 560 x 2 x 16384 x 2048 38.9 / 36.0; 8960 rows 352 / 322;
+    640 x 2 x 4096 x 1024 11.0 / 12.1.  So: bundle for at least 2048 rows, and for prefill-sized launches (at least 512
+    rows of width 2048 or more) whose last 256-row tile is mostly padding; paired otherwise."""
+    if tokens >= 2048:
+        return "bundle"
+    padding = -(-tokens // 256) * 256 - tokens
+    if tokens >= 512 and width >= 2048 and padding >= 128:
+        return "bundle"
+    return "paired"
 
 
 class B200Projection:
@@ -208,7 +218,8 @@ class B200Projection:
                 )
                 out_format = N.OUT_NVFP4
         operands, flags = self._operands(encoded), self.gated_flags
-        if flags & N.LINEAR_PAIRED_GATE_UP_SCALES and uses_sm_pairs(rows) and getattr(self, "weight_blocks_bundle", None) is not None:
+        if (flags & N.LINEAR_PAIRED_GATE_UP_SCALES and getattr(self, "weight_blocks_bundle", None) is not None
+                and gated_scale_layout(rows, self.input_dim) == "bundle"):
             operands["weight_scales"], flags = self.weight_blocks_bundle, flags & ~N.LINEAR_PAIRED_GATE_UP_SCALES
         K.linear(
             epilogue=N.EPI_GEGLU, out_format=out_format, tokens=rows, features=features, width=self.input_dim,

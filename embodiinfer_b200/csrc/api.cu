@@ -109,6 +109,12 @@ int b2_gelu_table_range(const void* host_table, int32_t* lo, int32_t* hi) {
     constexpr int MARGIN = 1280;
     const int widened = low - MARGIN > first ? low - MARGIN : first;
     if (high - widened <= 4096) low = widened;
+    // And four binades above `high` (1 KB more): one gate in a hundred of a heavy-tailed activation lies beyond
+    // the point where GELU(x) = x in bf16 (about 5), and a single such value among the 512 of a warp's unit is enough
+    // to send the whole warp through the general path.
+    constexpr int MARGIN_ABOVE = 512;
+    const int raised = high + MARGIN_ABOVE < last ? high + MARGIN_ABOVE : last;
+    if (raised - low <= 4096) high = raised;
     *lo = low;
     *hi = high;
     return B2_OK;

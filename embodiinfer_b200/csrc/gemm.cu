@@ -338,6 +338,9 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             // cycles per 512-byte atom, overlapping the MMAs already queued).  The reverse order is not
             // guaranteed: before a set of columns is overwritten, the MMAs that last read it (scale_sets
             // stages ago) must have completed, which their commit to that stage's `empty` barrier reports.
+            // With one set per ring stage (the usual case) no such wait is needed: the stage's `full` barrier completed
+            // again only after the producer had seen the `empty` barrier of its last use.
+            const bool lag = args.scale_sets < args.stages;
             int set = 0, lag_stage = 0, issued = 0;
             uint32_t lag_phase = 0;
             const uint32_t set_columns = uint32_t((RESIDENT ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
@@ -383,10 +386,10 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     const uint32_t stage_smem = stage_base + uint32_t(stage) * stage_bytes;
                     const uint32_t a_low = operand_low + ((RESIDENT ? panel_base + uint32_t(kb) * A_TILE_BYTES : stage_smem) >> 4);
                     const uint32_t b_low = operand_low + ((stage_smem + a_stage_bytes) >> 4);
-                    const uint32_t set_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t(set + 1);
+                    const uint32_t set_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t((lag ? set : stage) + 1);
                     const uint32_t sfa_tmem = RESIDENT ? resident_sfa + uint32_t(kb * TMEM_SFA_COLUMNS) : set_tmem;
                     const uint32_t sfb_tmem = RESIDENT ? set_tmem : set_tmem + TMEM_SFA_COLUMNS;
-                    if (KIND == B2_KIND_NVFP4) {
+                    if (KIND == B2_KIND_NVFP4 && lag) {
                         if (issued >= args.scale_sets) {
                             mbar_wait(empty_bar + 8 * lag_stage, lag_phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
                             tc_fence_after_sync();
@@ -812,18 +815,16 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     // More than one 128-token tile: two CTAs share every weight tile (gemm_pair.cu), unless the caller asks for the
     // single-CTA schedule or passes a scale layout only that schedule reads.
     {
-        int pair_columns = 0, pair_splits = 1;
-        int64_t pair_need = 0;
         const bool workspace_given = d->workspace != nullptr && aligned16(d->workspace);
-        pair_plan(d, geglu, planning || workspace_given, &pair_columns, &pair_splits, &pair_need);
-        if (!planning && pair_splits > 1 && d->workspace_bytes < pair_need)       // too small: decide again without splitting
-            pair_plan(d, geglu, false, &pair_columns, &pair_splits, &pair_need);
-        if (pair_columns != 0) {
+        PairPlan plan = pair_plan(d, geglu, planning || workspace_given);
+        if (!planning && plan.splits > 1 && d->workspace_bytes < plan.workspace_need)   // too small: decide again without splitting
+            plan = pair_plan(d, geglu, false);
+        if (plan.columns != 0) {
             if (planning) {
-                *workspace_need = pair_need;
+                *workspace_need = plan.workspace_need;
                 return B2_OK;
             }
-            return run_linear_pair(d, epilogue, pair_columns, pair_splits, stream);
+            return run_linear_pair(d, epilogue, plan, stream);
         }
     }
 

@@ -50,6 +50,7 @@ struct KernelArgs {
     int stages, accumulators, accumulator_stride, scale_sets, scale_blocks;
     int splits;                  // > 1: K is cut into `splits` ranges computed by different CTAs, see the epilogue
     int resident;                // 1: the CTA keeps its token tile (all of K) and its token scales on chip, see TileWalk
+    int kps;                     // paired schedule: K atoms (128 bytes of K) per ring slot
     int up_row_offset;           // row of the first "up" feature in the packed weight
     int scale_column_tiles;      // 512-byte scale atoms per 128-row block
     int act_row_blocks, weight_row_blocks;
@@ -293,18 +294,47 @@ __device__ __forceinline__ void geglu_scale_unit(const uint32_t (&gate_acc)[16],
     }
 }
 
+// h = bf16(bf16(gelu(gate)) * up) for the 16 features of a unit, as eight bf16x2 words.
+__device__ __forceinline__ void geglu_hidden_words(const uint32_t (&gate)[8], const uint32_t (&up)[8], const KernelArgs& args,
+                                                   uint32_t compact_table, uint32_t (&h)[8]) {
+    uint32_t gelu[8];
+    gelu_lookup_unit(gate, gelu, args, compact_table, uint32_t(args.gelu_lo), uint32_t(args.gelu_hi - args.gelu_lo));
+#pragma unroll
+    for (int p = 0; p < 8; ++p) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(h[p]) : "r"(gelu[p]), "r"(up[p]));
+}
+
+// One 16-value block of the hidden activation -> its 16 e2m1 codes (two words) and its e4m3 block scale, with the
+// arithmetic of quantize.cu:85-104 (`out_scale` divides by the global scale g, `by_global` by 6 g).
+__device__ __forceinline__ uint2 hidden_block_nvfp4(const uint32_t (&h)[8], const ExactDivider& out_scale, const ExactDivider& by_global,
+                                                    uint8_t& code) {
+    const float block_max = abs_max_bf16_words(h);
+    code = nvfp4_block_scale<true>(block_max, by_global, 0);
+    const ExactDivider denominator(__fmul_rn(out_scale.divisor, e4m3_to_float(code)));
+    uint2 words;
+    if (denominator.fast && __fmul_rn(block_max, denominator.reciprocal) < 1.0e30f) {
+        words.x = nvfp4_encode_words_short<true>(h[0], h[1], h[2], h[3], denominator);
+        words.y = nvfp4_encode_words_short<true>(h[4], h[5], h[6], h[7], denominator);
+    } else {
+        float low[8], high[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            low[2 * i] = bf16_lo(h[i]); low[2 * i + 1] = bf16_hi(h[i]);
+            high[2 * i] = bf16_lo(h[4 + i]); high[2 * i + 1] = bf16_hi(h[4 + i]);
+        }
+        words.x = nvfp4_encode_x8<true>(low, denominator, block_max);
+        words.y = nvfp4_encode_x8<true>(high, denominator, block_max);
+    }
+    return words;
+}
+
 // The rest of the gated epilogue on those words: table, product, encoding, stores.
 template <int EPI>
 __device__ __forceinline__ void epilogue_geglu_words(const uint32_t (&gate)[8], const uint32_t (&up)[8], const KernelArgs& args,
                                                      uint32_t compact_table, const ExactDivider& out_scale,
                                                      const ExactDivider& by_global, float out_scale_rcp, bool true_div,
                                                      int token, int feature0) {
-    const uint32_t lo = uint32_t(args.gelu_lo);
-    const uint32_t span = uint32_t(args.gelu_hi - args.gelu_lo);     // 0: every lookup reads the full table
-    uint32_t gelu[8], h[8];
-    gelu_lookup_unit(gate, gelu, args, compact_table, lo, span);
-#pragma unroll
-    for (int p = 0; p < 8; ++p) asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(h[p]) : "r"(gelu[p]), "r"(up[p]));
+    uint32_t h[8];
+    geglu_hidden_words(gate, up, args, compact_table, h);
     if (token >= args.tokens || feature0 >= args.features) return;
     const int64_t element = int64_t(token) * args.features + feature0;
     if (EPI == EPI_GEGLU_BF16) {
@@ -330,25 +360,9 @@ __device__ __forceinline__ void epilogue_geglu_words(const uint32_t (&gate)[8], 
         }
         store_u4(static_cast<uint8_t*>(args.out) + element, codes[0], codes[1], codes[2], codes[3]);
     } else {
-        // quantize.cu:85-104 arithmetic on this block
-        const float block_max = abs_max_bf16_words(h);
-        const uint8_t code = nvfp4_block_scale<true>(block_max, by_global, 0);
-        const ExactDivider denominator(__fmul_rn(out_scale.divisor, e4m3_to_float(code)));
-        uint32_t word0, word1;
-        if (denominator.fast && __fmul_rn(block_max, denominator.reciprocal) < 1.0e30f) {
-            word0 = nvfp4_encode_words_short<true>(h[0], h[1], h[2], h[3], denominator);
-            word1 = nvfp4_encode_words_short<true>(h[4], h[5], h[6], h[7], denominator);
-        } else {
-            float low[8], high[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                low[2 * i] = bf16_lo(h[i]); low[2 * i + 1] = bf16_hi(h[i]);
-                high[2 * i] = bf16_lo(h[4 + i]); high[2 * i + 1] = bf16_hi(h[4 + i]);
-            }
-            word0 = nvfp4_encode_x8<true>(low, denominator, block_max);
-            word1 = nvfp4_encode_x8<true>(high, denominator, block_max);
-        }
-        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(args.out) + (element >> 1)) = make_uint2(word0, word1);
+        uint8_t code;
+        const uint2 words = hidden_block_nvfp4(h, out_scale, by_global, code);
+        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(args.out) + (element >> 1)) = words;
         const int block = feature0 >> 4;
         const int blocks_per_row = args.features >> 4;
         if (args.out_scales != nullptr) args.out_scales[int64_t(token) * blocks_per_row + block] = code;
@@ -377,7 +391,13 @@ EncodeTiledFn encode_tiled_entry();
 bool make_operand_map(CUtensorMap* map, const void* pointer, int64_t rows, int64_t row_bytes, int box_rows);
 
 // Paired schedule (gemm_pair.cu): what it would do with a launch (0 columns = it does not apply), and the launch.
-void pair_plan(const b2_linear_desc* d, bool geglu, bool split_allowed, int* columns, int* splits, int64_t* workspace_need);
-int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, int splits, cudaStream_t stream);
+struct PairPlan {
+    int columns = 0;             // accumulator columns of a tile; 0 = the paired schedule does not apply
+    int splits = 1;              // K ranges computed by different SM pairs
+    int resident = 0;            // 1: every pair keeps its 256 token rows on chip and streams weights only
+    int64_t workspace_need = 0;  // bytes the splits need
+};
+PairPlan pair_plan(const b2_linear_desc* d, bool geglu, bool split_allowed);
+int run_linear_pair(const b2_linear_desc* d, int epilogue, const PairPlan& plan, cudaStream_t stream);
 
 }  // namespace b2

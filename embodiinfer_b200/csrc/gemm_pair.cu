@@ -100,13 +100,30 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
 __device__ __forceinline__ uint32_t idesc_f8_pair(uint32_t n) { return idesc_f8(PAIR_TOKENS, n); }
 __device__ __forceinline__ uint32_t idesc_nvf4_pair(uint32_t n) { return idesc_nvf4(PAIR_TOKENS, n); }
 
-// Work items of a cluster: item = cluster + i * clusters over the n-major list (token pair inner), so the
-// clusters that run side by side share a weight slab (it comes from HBM once and from the L2 afterwards).
+// Work items of a cluster.
+//   streaming: item = cluster + i * clusters over the n-major list (token pair inner), so the clusters that run side
+//       by side share a weight slab (it comes from HBM once and from the L2 afterwards); every K stage loads token
+//       rows and weight rows.
+//   resident:  the cluster stays on one token pair (cluster % pairs) and walks the feature tiles r, r + G, r + 2G ...
+//       (r = cluster / pairs, G = clusters on that pair).  Each CTA loads its 128 token rows for all of K once
+//       (shared memory; NVFP4: their scales into tensor memory) and a K stage loads weights only.  Clusters c, c+1 ..
+//       of different token pairs start on the same feature tile, so the slab sharing through the L2 stays.
 struct PairWalk {
     int item, step, m_pair, n_tile;
     int tile, split, kb_begin, kb_end;      // split K: the work item is (tile, split) and covers K stages [kb_begin, kb_end)
-    __device__ __forceinline__ explicit PairWalk(const KernelArgs& args) : item(int(blockIdx.x) >> 1), step(int(gridDim.x) >> 1) {
-        decompose(args);
+    bool resident;
+    __device__ __forceinline__ explicit PairWalk(const KernelArgs& args)
+        : item(int(blockIdx.x) >> 1), step(int(gridDim.x) >> 1), resident(args.resident != 0) {
+        if (resident) {
+            const int cluster = item, clusters = step;
+            m_pair = cluster % args.num_m_tiles;
+            n_tile = cluster / args.num_m_tiles;
+            step = (clusters - m_pair + args.num_m_tiles - 1) / args.num_m_tiles;
+            tile = split = kb_begin = 0;
+            kb_end = args.num_kb;
+        } else {
+            decompose(args);
+        }
     }
     __device__ __forceinline__ void decompose(const KernelArgs& args) {
         tile = item;
@@ -122,10 +139,16 @@ struct PairWalk {
         n_tile = tile / args.num_m_tiles;
         m_pair = tile - n_tile * args.num_m_tiles;
     }
-    __device__ __forceinline__ bool valid(const KernelArgs& args) const { return item < args.total_tiles * args.splits; }
+    __device__ __forceinline__ bool valid(const KernelArgs& args) const {
+        return resident ? n_tile < args.num_n_tiles : item < args.total_tiles * args.splits;
+    }
     __device__ __forceinline__ void next(const KernelArgs& args) {
-        item += step;
-        decompose(args);
+        if (resident) {
+            n_tile += step;
+        } else {
+            item += step;
+            decompose(args);
+        }
     }
 };
 
@@ -152,23 +175,32 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
     const int features_per_tile = GEGLU ? BN / 2 : BN;
     const uint32_t rank = cluster_cta_rank();
     const bool leader = rank == 0;
-    // shared memory: [stages x (token tile 16 KB | half weight tile)][stages x (token atoms | feature atoms)][barriers][GELU table]
+    // shared memory: [resident token rows: num_kb x 16 KB][stages x (token tile 16 KB unless resident | half weight tile)]
+    //                [stages x (token atoms unless resident | feature atoms)][barriers][GELU table]
+    const bool resident = args.resident != 0;
+    const uint32_t kps = uint32_t(args.kps);                      // K atoms (128 bytes of K) per ring slot: 1, or 2 in the resident order
+    const uint32_t a_stage_bytes = resident ? 0u : uint32_t(A_TILE_BYTES);
     const uint32_t b_tile_bytes = uint32_t(BN / 2) * STAGE_K_BYTES;
-    const uint32_t stage_bytes = A_TILE_BYTES + b_tile_bytes;
+    const uint32_t stage_bytes = a_stage_bytes + kps * b_tile_bytes;
     constexpr uint32_t SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
-    const uint32_t scale_stage_bytes = NVFP4 ? (1u + uint32_t(args.scale_blocks)) * SCALE_PART_BYTES : 0u;
-    const uint32_t stage_base = base;
+    const uint32_t token_part_bytes = resident ? 0u : SCALE_PART_BYTES;
+    const uint32_t feature_part_bytes = uint32_t(args.scale_blocks) * SCALE_PART_BYTES;      // feature atoms of one K atom
+    const uint32_t scale_stage_bytes = NVFP4 ? token_part_bytes + kps * feature_part_bytes : 0u;
+    const uint32_t panel_base = base;
+    const uint32_t stage_base = panel_base + (resident ? uint32_t(args.num_kb) * A_TILE_BYTES : 0u);
     const uint32_t scale_base = stage_base + uint32_t(args.stages) * stage_bytes;
     const uint32_t barrier_base = scale_base + uint32_t(args.stages) * scale_stage_bytes;
     const uint32_t full_bar = barrier_base;                       // [stages]  used in the leader only
     const uint32_t empty_bar = barrier_base + 8 * MAX_STAGES;     // [stages]  one per CTA
     const uint32_t acc_full_bar = barrier_base + 16 * MAX_STAGES; // [2]       one per CTA
     const uint32_t acc_empty_bar = acc_full_bar + 16;             // [2]       used in the leader only
-    const uint32_t tmem_slot = acc_empty_bar + 16;
+    const uint32_t panel_bar = acc_empty_bar + 16;                // [MAX_RESIDENT_KB] leader only: both CTAs' token rows of K stage kb landed
+    const uint32_t tmem_slot = panel_bar + 8 * MAX_RESIDENT_KB;
     const uint32_t compact_table = tmem_slot + 16;                // 2 * (gelu_hi - gelu_lo) bf16 entries
     // the leader's barriers as the peer addresses them
     const uint32_t full_bar_leader = cluster_map_shared(full_bar, 0u);
     const uint32_t acc_empty_bar_leader = cluster_map_shared(acc_empty_bar, 0u);
+    const uint32_t panel_bar_leader = cluster_map_shared(panel_bar, 0u);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -188,6 +220,7 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
             mbar_init(acc_full_bar + 8 * b, 1);
             mbar_init(acc_empty_bar + 8 * b, 2 * epilogue_warps(EPI));     // the epilogue warps of both CTAs
         }
+        for (int kb = 0; kb < MAX_RESIDENT_KB; ++kb) mbar_init(panel_bar + 8 * kb, 1);
         fence_barrier_init();
     }
     if (warp == 1) {
@@ -219,147 +252,270 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
     const int num_kb = args.num_kb;
     const int last_kb_mmas = ((args.k_bytes - (num_kb - 1) * STAGE_K_BYTES) + 31) / 32;
     // bytes one CTA brings per stage; boxes that reach beyond a matrix are filled with zeros and still count in full
-    const uint32_t stage_tx_bytes = stage_bytes + scale_stage_bytes;
+    const uint32_t atom_tx_bytes = a_stage_bytes + b_tile_bytes + (NVFP4 ? token_part_bytes + feature_part_bytes : 0u);   // per K atom
 
+    using Yes = std::true_type;
+    using No = std::false_type;
+    const bool paired_scales = GEGLU && (args.flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
     if (warp == 0) {
         // ------------------------------------------------------------- TMA producer (both CTAs)
-        int stage = 0;
-        uint32_t phase = 0;
-        uint32_t filled = 0, fill_parity = 0;
-        for (PairWalk walk(args); walk.valid(args); walk.next(args)) {
-            const int m0 = walk.m_pair * PAIR_TOKENS + int(rank) * TILE_TOKENS;
-            const int f0 = walk.n_tile * features_per_tile;
-            // this CTA's half of the weight tile: plain -> rows [f0 + rank*BN/2, +BN/2); gated -> the gate rows (leader)
-            // or the up rows (peer) of features [f0, f0 + BN/2)
-            const int weight_row = GEGLU ? int(rank) * args.up_row_offset + f0 : f0 + int(rank) * (BN / 2);
-            // scale atoms: token rows of this CTA; feature rows of the WHOLE tile (every SM scales all BN columns)
-            const int token_atom_row = (2 * walk.m_pair + int(rank)) * args.scale_column_tiles;
-            int feature_atom_row[2];
-            feature_atom_row[0] = (f0 >> 7) * args.scale_column_tiles;
-            feature_atom_row[1] = (GEGLU ? ((args.up_row_offset + f0) >> 7) : (f0 >> 7) + 1) * args.scale_column_tiles;
-            for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
-                mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
-                __syncwarp();
-                filled |= 1u << stage;
-                fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
+        auto producer_role = [&](auto order_tag) {
+            constexpr int ORDER = decltype(order_tag)::value;      // 0 streaming, 1 resident, 2 resident with two K atoms per slot
+            constexpr bool RESIDENT = ORDER != 0;
+            constexpr int KPS = ORDER == 2 ? 2 : 1;
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t filled = 0, fill_parity = 0;
+            PairWalk walk(args);
+            const bool panel_loaded = RESIDENT && walk.valid(args);
+            if (panel_loaded) {
+                // this CTA's 128 token rows for all of K, once; (NVFP4) their scale atoms travel through the first slots of
+                // the stage ring, from where the MMA warp moves them into tensor memory for good
+                const int m0 = walk.m_pair * PAIR_TOKENS + int(rank) * TILE_TOKENS;
                 if (elect_one()) {
-                    const uint32_t bar = full_bar_leader + 8 * stage;
-                    const uint32_t a_smem = stage_base + uint32_t(stage) * stage_bytes;
-                    const int k0 = kb * STAGE_K_BYTES;
-                    if (leader) mbar_expect_tx(full_bar + 8 * stage, 2u * stage_tx_bytes);
-                    tma_load_2d_pair(a_smem, &act_map, bar, k0, m0);
-                    tma_load_2d_pair(a_smem + A_TILE_BYTES, &weight_map, bar, k0, weight_row);
-                    if (NVFP4) {
-                        const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
-                        const int atom = kb * SCALE_ATOMS_PER_STAGE;
-                        tma_load_2d_pair(s_smem, &act_scale_map, bar, 0, token_atom_row + atom);
-                        tma_load_2d_pair(s_smem + SCALE_PART_BYTES, &weight_scale_map, bar, 0, feature_atom_row[0] + atom);
-                        if (args.scale_blocks == 2)
-                            tma_load_2d_pair(s_smem + 2 * SCALE_PART_BYTES, &weight_scale_map, bar, 0, feature_atom_row[1] + atom);
+                    for (int kb = 0; kb < num_kb; ++kb) {
+                        if (leader) mbar_expect_tx(panel_bar + 8 * kb, 2u * A_TILE_BYTES);
+                        tma_load_2d_pair(panel_base + uint32_t(kb) * A_TILE_BYTES, &act_map, panel_bar_leader + 8 * kb, kb * STAGE_K_BYTES, m0);
                     }
                 }
                 __syncwarp();
-                if (++stage == args.stages) { stage = 0; phase ^= 1u; }
+                if (NVFP4) {
+                    const int token_atom_row = (2 * walk.m_pair + int(rank)) * args.scale_column_tiles;
+                    for (int kb = 0; kb < num_kb; kb += KPS) {
+                        mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
+                        __syncwarp();
+                        filled |= 1u << stage;
+                        fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
+                        if (elect_one()) {
+                            const int atoms = min(KPS, num_kb - kb);
+                            if (leader) mbar_expect_tx(full_bar + 8 * stage, 2u * uint32_t(atoms) * SCALE_PART_BYTES);
+#pragma unroll
+                            for (int k = 0; k < KPS; ++k)
+                                if (k < atoms)
+                                    tma_load_2d_pair(scale_base + uint32_t(stage) * scale_stage_bytes + uint32_t(k) * SCALE_PART_BYTES, &act_scale_map,
+                                                     full_bar_leader + 8 * stage, 0, token_atom_row + (kb + k) * SCALE_ATOMS_PER_STAGE);
+                        }
+                        __syncwarp();
+                        if (++stage == args.stages) { stage = 0; phase ^= 1u; }
+                    }
+                }
             }
-        }
-        // The leader does not leave while a copy of the pair is still in flight: wait (bounded) for the last fill of
-        // every stage.  On the normal path these have all completed already.
-        if (leader) {
-            bool drain_failed = false;
-            for (int s = 0; s < args.stages; ++s)
-                if (filled & (1u << s))
-                    mbar_wait(full_bar + 8 * s, (fill_parity >> s) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
-        }
+            for (; walk.valid(args); walk.next(args)) {
+                const int m0 = walk.m_pair * PAIR_TOKENS + int(rank) * TILE_TOKENS;
+                const int f0 = walk.n_tile * features_per_tile;
+                // this CTA's half of the weight tile: plain -> rows [f0 + rank*BN/2, +BN/2); gated -> the gate rows (leader)
+                // or the up rows (peer) of features [f0, f0 + BN/2)
+                const int weight_row = GEGLU ? int(rank) * args.up_row_offset + f0 : f0 + int(rank) * (BN / 2);
+                // scale atoms: token rows of this CTA; feature rows of the WHOLE tile (every SM scales all BN columns).
+                // With the paired gate/up layout the 64 gate + 64 up rows of feature tile n form the n-th 128-row block.
+                const int token_atom_row = (2 * walk.m_pair + int(rank)) * args.scale_column_tiles;
+                int feature_atom_row[2];
+                feature_atom_row[0] = (paired_scales ? walk.n_tile : (f0 >> 7)) * args.scale_column_tiles;
+                feature_atom_row[1] = (GEGLU ? ((args.up_row_offset + f0) >> 7) : (f0 >> 7) + 1) * args.scale_column_tiles;
+                for (int kb = walk.kb_begin; kb < walk.kb_end; kb += KPS) {
+                    mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
+                    __syncwarp();
+                    filled |= 1u << stage;
+                    fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
+                    if (elect_one()) {
+                        const uint32_t bar = full_bar_leader + 8 * stage;
+                        const uint32_t slot_smem = stage_base + uint32_t(stage) * stage_bytes;
+                        const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
+                        const int atoms = min(KPS, walk.kb_end - kb);
+                        if (leader) mbar_expect_tx(full_bar + 8 * stage, 2u * uint32_t(atoms) * atom_tx_bytes);
+#pragma unroll
+                        for (int k = 0; k < KPS; ++k) {
+                            if (k < atoms) {
+                                const int k0 = (kb + k) * STAGE_K_BYTES;
+                                const int atom = (kb + k) * SCALE_ATOMS_PER_STAGE;
+                                if (!RESIDENT) tma_load_2d_pair(slot_smem, &act_map, bar, k0, m0);
+                                tma_load_2d_pair(slot_smem + a_stage_bytes + uint32_t(k) * b_tile_bytes, &weight_map, bar, k0, weight_row);
+                                if (NVFP4) {
+                                    const uint32_t f_smem = s_smem + token_part_bytes + uint32_t(k) * feature_part_bytes;
+                                    if (!RESIDENT) tma_load_2d_pair(s_smem, &act_scale_map, bar, 0, token_atom_row + atom);
+                                    tma_load_2d_pair(f_smem, &weight_scale_map, bar, 0, feature_atom_row[0] + atom);
+                                    if (args.scale_blocks == 2)
+                                        tma_load_2d_pair(f_smem + SCALE_PART_BYTES, &weight_scale_map, bar, 0, feature_atom_row[1] + atom);
+                                }
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (++stage == args.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            // The leader does not leave while a copy of the pair is still in flight: wait (bounded) for the last fill of
+            // every stage.  On the normal path these have all completed already.
+            if (leader) {
+                bool drain_failed = false;
+                for (int s = 0; s < args.stages; ++s)
+                    if (filled & (1u << s))
+                        mbar_wait(full_bar + 8 * s, (fill_parity >> s) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
+                if (panel_loaded)
+                    for (int kb = 0; kb < num_kb; ++kb) mbar_wait(panel_bar + 8 * kb, 0u, drain_failed, args.status, STATUS_WAIT_DRAIN);
+            }
+        };
+        if (!resident) producer_role(std::integral_constant<int, 0>{});
+        else if (args.kps == 2) producer_role(std::integral_constant<int, 2>{});
+        else producer_role(std::integral_constant<int, 1>{});
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer (leader only)
+        // The tcgen05 instructions of a ring slot are few, but the barrier waits, the election and the operand
+        // arithmetic around them are a dependent chain of a hundred-odd instructions that this one warp works through
+        // slot after slot while sharing its scheduler with four epilogue warps: everything a slot needs is computed
+        // before the election, and the elected lane then issues the copies and MMAs back to back.
         if (leader) {
-            auto mma_role = [&](auto two_blocks_tag) {
+            auto mma_role = [&](auto order_tag, auto two_blocks_tag, auto lag_tag) {
+                constexpr int ORDER = decltype(order_tag)::value;      // 0 streaming, 1 resident, 2 resident with two K atoms per slot
+                constexpr bool RESIDENT = ORDER != 0;
+                constexpr int KPS = ORDER == 2 ? 2 : 1;
                 constexpr bool TWO = decltype(two_blocks_tag)::value;
+                // LAG: fewer sets of feature-scale columns than K atoms in the ring, so a set's reuse needs its own wait.
+                // With one set per atom of every slot (the usual case) the set is free whenever the slot's `full` barrier
+                // has completed again: the producer refilled the slot only after the MMAs that read it, and its scales,
+                // had completed.
+                constexpr bool LAG = decltype(lag_tag)::value;
+                static_assert(!(LAG && KPS == 2), "two atoms per slot need a scale set per atom");
                 const uint32_t idesc = NVFP4 ? idesc_nvf4_pair(uint32_t(BN)) : idesc_f8_pair(uint32_t(BN));
                 const uint64_t operand_desc = smem_desc_sw128(0);
                 const uint32_t operand_low = uint32_t(operand_desc), operand_high = uint32_t(operand_desc >> 32);
                 const uint64_t scale_desc = smem_desc_scale_atom(0);
                 const uint32_t scale_desc_high = uint32_t(scale_desc >> 32);
-                const uint32_t set_columns = uint32_t(TMEM_SFA_COLUMNS + 16 * args.scale_blocks);
+                const uint32_t set_columns = uint32_t((RESIDENT ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
+                // resident order: the token scales of all K stages sit in tensor memory right after the accumulators
+                const uint32_t resident_sfa = tmem_base + uint32_t(args.accumulators * args.accumulator_stride);
+                constexpr uint32_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
+                const bool two_accumulators = args.accumulators == 2;
                 int stage = 0;
                 uint32_t phase = 0;
                 int local_tile = 0;
-                int set = 0, lag_stage = 0, issued = 0;
-                uint32_t lag_phase = 0;
-                for (PairWalk walk(args); walk.valid(args); walk.next(args), ++local_tile) {
+                PairWalk walk(args);
+                if (RESIDENT && NVFP4 && walk.valid(args)) {
+                    // the first ring slots carry the token scale atoms of both CTAs: into tensor memory, slot freed
+                    for (int kb = 0; kb < num_kb; kb += KPS) {
+                        mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
+                        tc_fence_after_sync();
+                        __syncwarp();
+                        if (elect_one()) {
+                            const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes) >> 4;
+#pragma unroll
+                            for (int k = 0; k < KPS; ++k)
+                                if (kb + k < num_kb) {
+#pragma unroll
+                                    for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j)
+                                        tc_copy_32x128b_x4_pair(resident_sfa + uint32_t((kb + k) * TMEM_SFA_COLUMNS + j * 4),
+                                                                desc_from_words(atom_low + k * PART + j * ATOM, scale_desc_high));
+                                }
+                            tc_commit_pair(empty_bar + 8 * stage, 3);
+                        }
+                        __syncwarp();
+                        if (++stage == args.stages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+                int set = 0, lag_stage = stage, issued = 0;
+                uint32_t lag_phase = phase;
+                for (; walk.valid(args); walk.next(args), ++local_tile) {
                     const int f0 = walk.n_tile * features_per_tile;
                     // a 64- or 128-column tile that starts inside a 128-row scale block starts at that block's column
                     const uint32_t scale_column = (GEGLU || BN == 256) ? 0u : uint32_t((f0 & 127) >> 5);
-                    const int buffer = local_tile % args.accumulators;
-                    const uint32_t use = uint32_t(local_tile / args.accumulators);
+                    const int buffer = two_accumulators ? local_tile & 1 : 0;
+                    const uint32_t use = uint32_t(two_accumulators ? local_tile >> 1 : local_tile);
+                    const uint32_t d_tmem = tmem_base + uint32_t(buffer * args.accumulator_stride);
+                    // the epilogue has drained this accumulator's last use
                     mbar_wait(acc_empty_bar + 8 * buffer, (use & 1u) ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
                     tc_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + uint32_t(buffer * args.accumulator_stride);
-                    for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
+                    for (int kb = walk.kb_begin; kb < walk.kb_end; kb += KPS) {
                         mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
-                        tc_fence_after_sync();
-                        const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
-                        const uint32_t stage_smem = stage_base + uint32_t(stage) * stage_bytes;
-                        const uint32_t a_low = operand_low + (stage_smem >> 4);
-                        const uint32_t b_low = operand_low + ((stage_smem + A_TILE_BYTES) >> 4);
-                        const uint32_t set_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t(set + 1);
-                        const uint32_t sfa_tmem = set_tmem;
-                        const uint32_t sfb_tmem = set_tmem + TMEM_SFA_COLUMNS;
-                        if (NVFP4) {
+                        if (RESIDENT && local_tile == 0) {       // first pass over K: the token rows may still be landing
+                            mbar_wait(panel_bar + 8 * kb, 0u, failed, args.status, STATUS_WAIT_MMA_FULL);
+                            if (KPS == 2 && kb + 1 < num_kb) mbar_wait(panel_bar + 8 * (kb + 1), 0u, failed, args.status, STATUS_WAIT_MMA_FULL);
+                        }
+                        if (NVFP4 && LAG) {
                             // a set of scale columns is overwritten only after the MMAs that last read it have completed
                             if (issued >= args.scale_sets) {
                                 mbar_wait(empty_bar + 8 * lag_stage, lag_phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
-                                tc_fence_after_sync();
                                 if (++lag_stage == args.stages) { lag_stage = 0; lag_phase ^= 1u; }
                             }
                             ++issued;
                         }
+                        tc_fence_after_sync();
+                        // every operand of the slot's instructions, before the election
+                        const uint32_t slot_smem = stage_base + uint32_t(stage) * stage_bytes;
+                        const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes) >> 4;
+                        uint32_t a_low[KPS], b_low[KPS], sfa_tmem[KPS], sfb_tmem[KPS], feature_low[KPS];
+                        int count[KPS];
+#pragma unroll
+                        for (int k = 0; k < KPS; ++k) {
+                            const int atom_kb = kb + k;
+                            a_low[k] = operand_low + ((RESIDENT ? panel_base + uint32_t(atom_kb) * A_TILE_BYTES : slot_smem) >> 4);
+                            b_low[k] = operand_low + ((slot_smem + a_stage_bytes + uint32_t(k) * b_tile_bytes) >> 4);
+                            const uint32_t set_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t((LAG ? set : stage * KPS + k) + 1);
+                            sfa_tmem[k] = RESIDENT ? resident_sfa + uint32_t(atom_kb * TMEM_SFA_COLUMNS) : set_tmem;
+                            sfb_tmem[k] = RESIDENT ? set_tmem : set_tmem + TMEM_SFA_COLUMNS;
+                            feature_low[k] = atom_low + (RESIDENT ? uint32_t(k * args.scale_blocks) * PART : PART);
+                            count[k] = atom_kb >= walk.kb_end ? 0 : (atom_kb == num_kb - 1 ? last_kb_mmas : SCALE_ATOMS_PER_STAGE);
+                        }
+                        const bool full_slot = count[KPS - 1] == SCALE_ATOMS_PER_STAGE && (KPS == 1 || count[0] == SCALE_ATOMS_PER_STAGE);
+                        const bool last_slot = kb + KPS >= walk.kb_end;
                         __syncwarp();
                         if (elect_one()) {
-                            const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes) >> 4;
-                            constexpr uint32_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
-                            const uint32_t feature_low = atom_low + PART;
-                            const uint32_t first_accumulate = kb != walk.kb_begin;
-                            auto issue = [&](const int count) {
-                                if (NVFP4) {
+                            // `limit` is a literal except in a slot with a ragged or missing K atom
+                            auto issue = [&](auto full_tag) {
+                                constexpr bool FULL = decltype(full_tag)::value;
+#pragma unroll
+                                for (int k = 0; k < KPS; ++k) {
+                                    const int limit = FULL ? SCALE_ATOMS_PER_STAGE : count[k];
+                                    if (NVFP4) {
+#pragma unroll
+                                        for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
+                                            if (j < limit) {
+                                                if (!RESIDENT) tc_copy_32x128b_x4_pair(sfa_tmem[k] + j * 4, desc_from_words(atom_low + j * ATOM, scale_desc_high));
+                                                tc_copy_32x128b_x4_pair(sfb_tmem[k] + j * (TWO ? 8 : 4), desc_from_words(feature_low[k] + j * ATOM, scale_desc_high));
+                                                if (TWO)
+                                                    tc_copy_32x128b_x4_pair(sfb_tmem[k] + j * 8 + 4, desc_from_words(feature_low[k] + PART + j * ATOM, scale_desc_high));
+                                            }
+                                        }
+                                    }
 #pragma unroll
                                     for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
-                                        if (j < count) {
-                                            tc_copy_32x128b_x4_pair(sfa_tmem + j * 4, desc_from_words(atom_low + j * ATOM, scale_desc_high));
-                                            tc_copy_32x128b_x4_pair(sfb_tmem + j * (TWO ? 8 : 4), desc_from_words(feature_low + j * ATOM, scale_desc_high));
-                                            if (TWO)
-                                                tc_copy_32x128b_x4_pair(sfb_tmem + j * 8 + 4, desc_from_words(feature_low + PART + j * ATOM, scale_desc_high));
+                                        if (j < limit) {
+                                            const uint32_t accumulate = (j == 0 && k == 0) ? uint32_t(kb != walk.kb_begin) : 1u;
+                                            const uint64_t a_desc = desc_from_words(a_low[k] + 2 * j, operand_high);
+                                            const uint64_t b_desc = desc_from_words(b_low[k] + 2 * j, operand_high);
+                                            if (NVFP4)
+                                                mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem[k] + j * 4,
+                                                              sfb_tmem[k] + j * (TWO ? 8 : 4) + scale_column, accumulate);
+                                            else
+                                                mma_f8f6f4_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
                                         }
                                     }
                                 }
-#pragma unroll
-                                for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
-                                    if (j < count) {
-                                        const uint32_t accumulate = j == 0 ? first_accumulate : 1u;
-                                        const uint64_t a_desc = desc_from_words(a_low + 2 * j, operand_high);
-                                        const uint64_t b_desc = desc_from_words(b_low + 2 * j, operand_high);
-                                        if (NVFP4)
-                                            mma_nvf4_pair(d_tmem, a_desc, b_desc, idesc, sfa_tmem + j * 4,
-                                                          sfb_tmem + j * (TWO ? 8 : 4) + scale_column, accumulate);
-                                        else
-                                            mma_f8f6f4_pair(d_tmem, a_desc, b_desc, idesc, accumulate);
-                                    }
-                                }
                             };
-                            if (mmas == SCALE_ATOMS_PER_STAGE) issue(SCALE_ATOMS_PER_STAGE);
-                            else issue(mmas);
-                            tc_commit_pair(empty_bar + 8 * stage, 3);     // the stage is free again in both CTAs
+                            if (full_slot) issue(Yes{});
+                            else issue(No{});
+                            tc_commit_pair(empty_bar + 8 * stage, 3);     // the slot is free again in both CTAs
+                            if (last_slot) tc_commit_pair(acc_full_bar + 8 * buffer, 3);
                         }
                         __syncwarp();
-                        if (NVFP4 && ++set == args.scale_sets) set = 0;
+                        if (NVFP4 && LAG && ++set == args.scale_sets) set = 0;
                         if (++stage == args.stages) { stage = 0; phase ^= 1u; }
                     }
-                    if (elect_one()) tc_commit_pair(acc_full_bar + 8 * buffer, 3);
-                    __syncwarp();
                 }
             };
-            if (NVFP4 && args.scale_blocks == 2) mma_role(std::true_type{});
-            else mma_role(std::false_type{});
+            using Order0 = std::integral_constant<int, 0>;
+            using Order1 = std::integral_constant<int, 1>;
+            using Order2 = std::integral_constant<int, 2>;
+            const bool two_blocks = NVFP4 && args.scale_blocks == 2;
+            const bool lag = NVFP4 && args.scale_sets < args.stages * args.kps;
+            if (resident && args.kps == 2) {
+                if (two_blocks) mma_role(Order2{}, Yes{}, No{}); else mma_role(Order2{}, No{}, No{});
+            } else if (lag) {
+                if (resident) { if (two_blocks) mma_role(Order1{}, Yes{}, Yes{}); else mma_role(Order1{}, No{}, Yes{}); }
+                else { if (two_blocks) mma_role(Order0{}, Yes{}, Yes{}); else mma_role(Order0{}, No{}, Yes{}); }
+            } else {
+                if (resident) { if (two_blocks) mma_role(Order1{}, Yes{}, No{}); else mma_role(Order1{}, No{}, No{}); }
+                else { if (two_blocks) mma_role(Order0{}, Yes{}, No{}); else mma_role(Order0{}, No{}, No{}); }
+            }
         }
     } else {
         // ------------------------------------------------------------- epilogue (both CTAs, own 128 tokens)
@@ -382,13 +538,14 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
         const bool true_div = (args.flags & B2_GEGLU_TRUE_DIV) != 0;
         constexpr int WARPS_PER_QUARTER = epilogue_warps(EPI) / 4;
         const int part = (warp - FIRST_EPILOGUE_WARP) >> 2;
+        const bool two_accumulators = args.accumulators == 2;
         int local_tile = 0;
         for (PairWalk walk(args); walk.valid(args); walk.next(args), ++local_tile) {
             const int token0 = walk.m_pair * PAIR_TOKENS + int(rank) * TILE_TOKENS + quarter * 32;
             const int token = token0 + lane;
             const int f0 = walk.n_tile * features_per_tile;
-            const int buffer = local_tile % args.accumulators;
-            const uint32_t use = uint32_t(local_tile / args.accumulators);
+            const int buffer = two_accumulators ? local_tile & 1 : 0;
+            const uint32_t use = uint32_t(two_accumulators ? local_tile >> 1 : local_tile);
             mbar_wait(acc_full_bar + 8 * buffer, use & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
             tc_fence_after_sync();
             const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16) + uint32_t(buffer * args.accumulator_stride);
@@ -600,7 +757,7 @@ static int launch_pair_variant(const CUtensorMap& act_map, const CUtensorMap& we
         }
     }
     const int items = args.total_tiles * args.splits;
-    const int clusters = items < sm_count() / 2 ? items : sm_count() / 2;
+    const int clusters = items < sm_count() / 2 ? items : sm_count() / 2;      // resident: at least one cluster per token pair (pair_plan)
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(unsigned(2 * clusters));
     config.blockDim = dim3(unsigned(gemm_threads(EPI)));
@@ -632,63 +789,120 @@ static int launch_pair(const CUtensorMap& act_map, const CUtensorMap& weight_map
 
 constexpr int64_t PAIR_TICKET_BYTES = 1024;      // per tile: arrived[2], departed[2] (uint32); zero between launches
 
-// What the paired schedule would do with this launch: accumulator columns (0 = it does not apply), K splits, and the
-// workspace bytes the splits need.
-//   Pairs apply to more than one 128-token tile and the bundle-order scale layout (a tile's feature scales are whole
-//   128-row blocks: plain 128 or 256 features per tile, gated 128 + 128).
-//   A pair computes 256 token rows whether they exist or not.  When the last pair would be mostly padding (560 tokens:
-//   768 rows of work on pairs against 640 on single CTAs) the single-CTA schedule is as fast or faster (measured:
-//   560 x 16384 x 2048 FP8 28.0 vs 27.1 us); with equal padding, or enough tokens for it not to matter, pairs win by
-//   6-20 % (8192 x 1152 x 4304 FP8 51.6 vs 64.4 us; 8960 x 32768 x 2048 gated FP8 480 vs 543 us).  B2_LINEAR_PAIRS asks
-//   for pairs regardless.
+// Shared memory outside the stage ring and the resident token rows.
+static int pair_fixed_bytes(int gelu_span) {
+    return 1024 /* alignment slack */ + 16 * MAX_STAGES + 8 * MAX_RESIDENT_KB + 128 + 4 * gelu_span;
+}
+
+static int compact_gelu_span(const b2_linear_desc* d) {
+    if (d->epilogue != B2_EPI_LINEAR && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
+        d->gelu_hi - d->gelu_lo <= MAX_COMPACT_GELU)
+        return d->gelu_hi - d->gelu_lo;
+    return 0;
+}
+
+// The resident order for a tile of `columns` accumulator columns: does everything fit, and is it worth it?
+//   shared memory: the token rows of all of K (num_kb x 16 KB per CTA) beside at least four weight stages;
+//   tensor memory: the accumulators (two when they fit), the token scales of all of K, two or more feature-scale sets;
+//   work: at least two tiles per SM pair on average, so that loading the token rows once is amortised.
+static bool pair_resident_fits(const b2_linear_desc* d, int columns, int scale_blocks, int num_kb, int pairs, int64_t tiles) {
+    if (d->flags & B2_LINEAR_STREAM_TOKENS) return false;
+    const bool nvfp4 = d->kind == B2_KIND_NVFP4;
+    const int clusters = sm_count() / 2;
+    if (num_kb > MAX_RESIDENT_KB || pairs > clusters || tiles < 2 * int64_t(clusters)) return false;
+    constexpr int SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
+    const int stage_bytes = (columns / 2) * STAGE_K_BYTES + (nvfp4 ? scale_blocks * SCALE_PART_BYTES : 0);
+    const int stages = (SMEM_LIMIT - pair_fixed_bytes(compact_gelu_span(d)) - num_kb * A_TILE_BYTES) / stage_bytes;
+    if (stages < 4) return false;
+    if (nvfp4) {
+        const int free_columns = TMEM_COLUMNS - columns - num_kb * TMEM_SFA_COLUMNS;
+        if (free_columns < 2 * 16 * scale_blocks) return false;
+    }
+    return true;
+}
+
+// What the paired schedule would do with this launch: accumulator columns (0 = it does not apply), K splits, the
+// workspace bytes the splits need, and whether the token rows stay on chip.
+//   Pairs apply to more than one 128-token tile.  Feature scales are read as whole 128-row blocks: plain tiles of 128
+//   or 256 features, gated tiles of 128 + 128 in the bundle's order, or gated tiles of 64 + 64 in the paired gate/up
+//   layout (B2_LINEAR_PAIRED_GATE_UP_SCALES), which only the resident order reads.
+//   A pair computes 256 token rows whether they exist or not.  In the streaming order, when the last pair would be
+//   mostly padding (560 tokens: 768 rows of work on pairs against 640 on single CTAs) the single-CTA schedule is as
+//   fast or faster (measured: 560 x 16384 x 2048 FP8 28.0 vs 27.1 us); with equal padding, or enough tokens for it not
+//   to matter, pairs win by 6-20 % (8192 x 1152 x 4304 FP8 51.6 vs 64.4 us; 8960 x 32768 x 2048 gated FP8 480 vs 543
+//   us).  B2_LINEAR_PAIRS asks for pairs regardless.
+//   Resident order (K of at most eight stages, at least two tiles per SM pair): a K stage carries weights only, half
+//   the bytes of the streaming order and a third of the single-CTA schedule's, which is what bounds those; it is
+//   taken whatever the padding.
 //   Split K (plain epilogue, caller-provided workspace): when 256-column tiles leave more than half of the SM pairs
 //   idle and K is long (560 x 2048 x 16384: 24 tiles for 74 pairs), K is cut so that tiles x splits fills one wave;
 //   that launch runs on pairs whatever the padding.
-void pair_plan(const b2_linear_desc* d, bool geglu, bool split_allowed, int* columns, int* splits, int64_t* workspace_need) {
-    *columns = 0;
-    *splits = 1;
-    *workspace_need = 0;
-    if (d->tokens <= TILE_TOKENS) return;
-    if (d->flags & (B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRED_GATE_UP_SCALES)) return;
+PairPlan pair_plan(const b2_linear_desc* d, bool geglu, bool split_allowed) {
+    PairPlan plan;
+    if (d->tokens <= TILE_TOKENS) return plan;
+    if (d->flags & B2_LINEAR_SINGLE_CTA) return plan;
     const bool nvfp4 = d->kind == B2_KIND_NVFP4;
+    const bool paired_scales = (d->flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
     const int pairs = (d->tokens + PAIR_TOKENS - 1) / PAIR_TOKENS;
     const int clusters = sm_count() / 2;
+    const int k_bytes = nvfp4 ? d->width / 2 : d->width;
+    const int num_kb = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
+    if (paired_scales) {
+        // 64 gate + 64 up rows per scale block: tiles of 128 columns, resident order only
+        if (!(geglu && nvfp4) || (d->feature_tile != 0 && d->feature_tile != 64) || d->features % 64 != 0) return plan;
+        if (!pair_resident_fits(d, 128, 1, num_kb, pairs, int64_t(pairs) * (d->features / 64))) return plan;
+        plan.columns = 128;
+        plan.resident = 1;
+        return plan;
+    }
     if (!geglu && d->epilogue == B2_EPI_LINEAR && split_allowed && (d->feature_tile == 0 || d->feature_tile == 256)) {
         const int64_t tiles = int64_t(pairs) * ((d->features + 255) / 256);
-        const int k_bytes = nvfp4 ? d->width / 2 : d->width;
-        const int num_kb = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
         int count = int(clusters / (tiles > 0 ? tiles : 1));
         if (count > PAIR_MAX_SPLITS) count = PAIR_MAX_SPLITS;
-        while (count > 1 && num_kb / count < 16) --count;        // the fix-up costs about as much as ten K stages
+        while (count > 1 && num_kb / count < 20) --count;        // the fix-up costs about as much as a dozen K atoms
         if (count > 1 && tiles * 16 <= PAIR_TICKET_BYTES) {
-            *columns = 256;
-            *splits = count;
-            *workspace_need = PAIR_TICKET_BYTES + tiles * count * 2 * TILE_TOKENS * 256 * 4;
-            return;
+            plan.columns = 256;
+            plan.splits = count;
+            plan.workspace_need = PAIR_TICKET_BYTES + tiles * count * 2 * TILE_TOKENS * 256 * 4;
+            return plan;
         }
     }
+    int columns = 0;
+    if (geglu) {
+        if (d->feature_tile != 0 && d->feature_tile != 128) return plan;
+        if (nvfp4 && d->features % 128 != 0) return plan;
+        columns = 256;
+    } else if (d->feature_tile == 128 || d->feature_tile == 256) {
+        columns = d->feature_tile;
+    } else if (d->feature_tile != 0) {
+        return plan;
+    } else {
+        // fill the machine: the wider tile moves fewer operand bytes per MMA, the narrower one gives more work items
+        const int64_t wide_items = int64_t(pairs) * ((d->features + 255) / 256);
+        columns = wide_items >= clusters ? 256 : 128;
+    }
+    const int features_per_tile = geglu ? columns / 2 : columns;
+    const int64_t tiles = int64_t(pairs) * ((d->features + features_per_tile - 1) / features_per_tile);
     const int64_t pair_rows = int64_t(pairs) * PAIR_TOKENS;
     const int64_t single_rows = int64_t((d->tokens + TILE_TOKENS - 1) / TILE_TOKENS) * TILE_TOKENS;
-    if (!(d->flags & B2_LINEAR_PAIRS) && pair_rows != single_rows && d->tokens < 2048) return;
-    if (geglu) {
-        if (d->feature_tile != 0 && d->feature_tile != 128) return;
-        if (nvfp4 && d->features % 128 != 0) return;
-        *columns = 256;
-        return;
-    }
-    if (d->feature_tile == 128 || d->feature_tile == 256) {
-        *columns = d->feature_tile;
-        return;
-    }
-    if (d->feature_tile != 0) return;
-    // fill the machine: the wider tile moves fewer operand bytes per MMA, the narrower one gives more work items
-    const int64_t wide_items = int64_t(pairs) * ((d->features + 255) / 256);
-    *columns = wide_items >= clusters ? 256 : 128;
+    const bool little_padding = pair_rows == single_rows || d->tokens >= 2048;
+    // Gated 256-column tiles have one accumulator, so the main loop pauses while it is drained; with a token pair that
+    // is mostly padding the clusters of the resident order that sit on it finish early and the rest decide the time
+    // (560 x 2 x 16384 x 2048 NVFP4: resident 40.6 us, streaming 36.0 us; 8960 tokens: 322 against 335 us).
+    const bool resident = pair_resident_fits(d, columns, columns > 128 ? 2 : 1, num_kb, pairs, tiles) && (!geglu || little_padding);
+    const bool gated_nvfp4_prefill = geglu && nvfp4 && d->tokens >= 512;      // measured faster on pairs whatever the padding
+    if (!resident && !(d->flags & B2_LINEAR_PAIRS) && !little_padding && !gated_nvfp4_prefill) return plan;
+    plan.columns = columns;
+    plan.resident = resident ? 1 : 0;
+    return plan;
 }
 
-int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, int splits, cudaStream_t stream) {
+int run_linear_pair(const b2_linear_desc* d, int epilogue, const PairPlan& plan, cudaStream_t stream) {
     const bool nvfp4 = d->kind == B2_KIND_NVFP4;
     const bool geglu = is_gated(epilogue);
+    const int tile_columns = plan.columns;
+    const int splits = plan.splits;
+    const bool paired_scales = (d->flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
     KernelArgs args{};
     args.tokens = d->tokens;
     args.features = d->features;
@@ -700,6 +914,7 @@ int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, int
     args.num_n_tiles = (d->features + features_per_tile - 1) / features_per_tile;
     args.total_tiles = args.num_m_tiles * args.num_n_tiles;
     args.splits = splits;
+    args.resident = plan.resident;
     args.tickets = nullptr;
     args.partials = nullptr;
     if (splits > 1) {
@@ -711,7 +926,7 @@ int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, int
     args.scale_column_tiles = nvfp4 ? (d->width / 16 + 3) / 4 : 0;
     args.act_row_blocks = (d->tokens + 127) / 128;
     const int weight_rows = (geglu ? 2 : 1) * d->features;
-    args.weight_row_blocks = (weight_rows + 127) / 128;
+    args.weight_row_blocks = paired_scales ? args.num_n_tiles : (weight_rows + 127) / 128;
     args.flags = d->flags;
     args.act_scales = static_cast<const uint8_t*>(d->act_scales);
     args.weight_scales = static_cast<const uint8_t*>(d->weight_scales);
@@ -727,35 +942,49 @@ int run_linear_pair(const b2_linear_desc* d, int epilogue, int tile_columns, int
     args.out_blocked = static_cast<uint8_t*>(d->out_blocked);
     args.status = static_cast<unsigned int*>(d->status);
     args.gelu_lo = args.gelu_hi = 0;
-    if (epilogue != EPI_LINEAR && d->gelu_lo >= 0x80 && d->gelu_hi > d->gelu_lo && d->gelu_hi <= 0x7f80 &&
-        d->gelu_hi - d->gelu_lo <= MAX_COMPACT_GELU) {
+    if (compact_gelu_span(d) != 0) {
         args.gelu_lo = d->gelu_lo;
         args.gelu_hi = d->gelu_hi;
     }
 
-    // tensor memory: accumulators from column 0, (NVFP4) sets of scale columns stacked down from column 512
-    const int set_columns = TMEM_SFA_COLUMNS + 16 * args.scale_blocks;
+    // tensor memory: accumulators from column 0, (resident NVFP4) the token scales of all of K behind them, (NVFP4) sets
+    // of scale columns stacked down from column 512
+    const int resident_columns = plan.resident && nvfp4 ? args.num_kb * TMEM_SFA_COLUMNS : 0;
+    const int set_columns = (plan.resident ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks;
     if (nvfp4) {
-        args.accumulators = 2 * tile_columns + 2 * set_columns <= TMEM_COLUMNS ? 2 : 1;
+        args.accumulators = 2 * tile_columns + resident_columns + 2 * set_columns <= TMEM_COLUMNS ? 2 : 1;
         args.accumulator_stride = tile_columns;
     } else {
         args.accumulators = 2;
         args.accumulator_stride = 256;
     }
     constexpr int SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
-    const int stage_bytes = A_TILE_BYTES + (tile_columns / 2) * STAGE_K_BYTES + (nvfp4 ? (1 + args.scale_blocks) * SCALE_PART_BYTES : 0);
-    const int fixed_bytes = 1024 /* alignment slack */ + 16 * MAX_STAGES + 128 + 4 * (args.gelu_hi - args.gelu_lo);
-    int stages = (SMEM_LIMIT - fixed_bytes) / stage_bytes;
+    int stage_bytes = (plan.resident ? 0 : A_TILE_BYTES) + (tile_columns / 2) * STAGE_K_BYTES +
+                      (nvfp4 ? ((plan.resident ? 0 : 1) + args.scale_blocks) * SCALE_PART_BYTES : 0);
+    const int panel_bytes = plan.resident ? args.num_kb * A_TILE_BYTES : 0;
+    const int fixed_bytes = pair_fixed_bytes(args.gelu_hi - args.gelu_lo);
+    const int ring_bytes = SMEM_LIMIT - fixed_bytes - panel_bytes;
+    const int sets_available = nvfp4 ? (TMEM_COLUMNS - args.accumulators * args.accumulator_stride - resident_columns) / set_columns : 0;
+    // Resident order: two K atoms per ring slot when four such slots fit (and a scale set per atom): the MMA warp then
+    // passes its barrier waits, its election and its commit once per 256 bytes of K instead of once per 128, and that
+    // fixed part is most of what a K atom costs it at 128-column tiles.
+    args.kps = 1;
+    if (plan.resident && args.num_kb >= 2 && ring_bytes / (2 * stage_bytes) >= 4 && (!nvfp4 || sets_available >= 8)) {
+        args.kps = 2;
+        stage_bytes *= 2;
+    }
+    int stages = ring_bytes / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) return B2_E_UNSUPPORTED;
-    args.stages = stages;
     args.scale_sets = 1;
     if (nvfp4) {
-        args.scale_sets = (TMEM_COLUMNS - args.accumulators * args.accumulator_stride) / set_columns;
-        if (args.scale_sets > stages) args.scale_sets = stages;
+        args.scale_sets = sets_available;
+        if (args.kps == 2 && stages > sets_available / 2) stages = sets_available / 2;
+        if (args.scale_sets > stages * args.kps) args.scale_sets = stages * args.kps;
         if (args.scale_sets < 2) return B2_E_UNSUPPORTED;
     }
-    int shared_bytes = fixed_bytes + stages * stage_bytes;
+    args.stages = stages;
+    int shared_bytes = fixed_bytes + panel_bytes + stages * stage_bytes;
     if (shared_bytes < SMEM_MINIMUM) shared_bytes = SMEM_MINIMUM;
 
     CUtensorMap act_map, weight_map, act_scale_map, weight_scale_map;

@@ -211,6 +211,8 @@ LINEAR_SHAPES = [
     ("siglip_fc2_fp8_8192x1152x4304", "fp8", 8192, 1152, 4304, "linear"),
     ("prefix_mb16_gate_up_fp8_geglu_8960x2x16384x2048", "fp8", 8960, 16384, 2048, "geglu"),
     ("prefix_mb16_down_fp8_8960x2048x16384", "fp8", 8960, 2048, 16384, "linear"),
+    ("prefix_mb16_gate_up_nvfp4_geglu_8960x2x16384x2048", "nvfp4", 8960, 16384, 2048, "geglu"),
+    ("prefix_mb16_down_nvfp4_8960x2048x16384", "nvfp4", 8960, 2048, 16384, "linear"),
 ] + [
     (f"expert_B{batch}_{name}_{kind}_{10 * batch}x{n}x{k}", kind, 10 * batch, n, k, epilogue)
     for batch in (1, 8, 64) for kind in ("fp8", "nvfp4")
@@ -262,7 +264,8 @@ def linear_cases(device, options=None):
                 if kind == "nvfp4":
                     if not options.get("unpaired"):
                         arguments.update(flags=N.LINEAR_PAIRED_GATE_UP_SCALES)
-                    arguments.update(out_blocked=torch.zeros(_blocked_bytes(tokens, features // 16), device=device, dtype=torch.uint8))
+                    arguments.update(out_blocked=torch.zeros(_blocked_bytes(tokens, features // 16), device=device, dtype=torch.uint8),
+                                     out_scales=torch.empty((tokens, features // 16), device=device, dtype=torch.uint8))
             else:
                 arguments.update(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16,
                                  out=torch.empty((tokens, features), device=device, dtype=torch.bfloat16))

@@ -295,8 +295,9 @@ int64_t b2_linear_workspace_bytes(const b2_linear_desc* desc);
  * memory and evaluates the closed forms elsewhere, which is bit-identical to indexing the full table.
  * Returns B2_E_UNSUPPORTED (and 0, 0) when the table has no such structure or the range is wider than
  * 4096 codes; b2_linear then reads the full table from global memory.  The tanh-approximated GELU's closed forms
- * hold outside [0x3b4b, 0x40a2) (|x| in [3.1e-3, 5.06)); the function returns lo lowered by ten binades (0x364b),
- * which is as valid and keeps nearly every gate value inside the range (one straight-line path per warp).  Host-only; no reference counterpart (the reference
+ * hold outside [0x3b4b, 0x40a2) (|x| in [3.1e-3, 5.06)); the function returns lo lowered by ten binades (0x364b)
+ * and hi raised by four (0x42a2, |x| = 81), which is as valid and keeps nearly every gate value inside the range (one
+ * straight-line path per warp, also for heavy-tailed activations).  Host-only; no reference counterpart (the reference
  * always gathers from the 128 KiB table, fusion.cu:5-10). */
 int b2_gelu_table_range(const void* host_table, int32_t* lo, int32_t* hi);
 

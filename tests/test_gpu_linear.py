@@ -282,6 +282,66 @@ def test_paired_schedule_gated_equals_single_cta(device, kind, out_format):
         assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("kind,width", [("fp8", 1024), ("nvfp4", 2048), ("nvfp4", 320)])
+def test_resident_pair_order_equals_single_cta(device, kind, width):
+    """Short K and at least two tiles per SM pair: each pair keeps its 256 token rows (and their scales) on chip for
+    all of K and streams weights only.  Same accumulation order as the other schedules: identical bits, also with the
+    streaming order forced, with the ragged third token pair of 560 rows and a ragged last feature tile."""
+    tokens, features = 560, 12800 - 64
+    host, dev = operands(kind, tokens, features, width, 7 + width, device)
+    common = dict(tokens=tokens, features=features, width=width)
+    resident = run_linear(device, dev, **common)
+    single = run_linear(device, dev, flags=N.LINEAR_SINGLE_CTA, **common)
+    streaming = run_linear(device, dev, flags=N.LINEAR_PAIRS | N.LINEAR_STREAM_TOKENS, **common)
+    assert torch.equal(resident.view(torch.int16), single.view(torch.int16))
+    assert torch.equal(streaming.view(torch.int16), single.view(torch.int16))
+    rows = slice(500, 560)
+    want = O.f32_to_bf16((accumulate(kind, {**host, "a": host["a"][rows], **({"a_sl": host["a_sl"][rows]} if kind == "nvfp4" else {})})
+                          * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+    assert_gemm_close(bits(resident[rows]), want)
+
+
+@pytest.mark.parametrize("layout", ("paired", "bundle", "fp8"))
+@pytest.mark.parametrize("out_format", ("bf16", "nvfp4"))
+def test_resident_pair_order_gated(device, layout, out_format):
+    """The gated epilogue in the resident order: 64 + 64-feature tiles with the paired gate/up scale layout (two
+    accumulators in tensor memory), 128 + 128-feature tiles with the bundle's layout, and FP8; every output equals the
+    single-CTA schedule's bit for bit."""
+    kind = "fp8" if layout == "fp8" else "nvfp4"
+    tokens, features, width = 330, 4864 if layout == "paired" else 9600, 1024 if kind == "fp8" else 2048
+    host, dev = operands(kind, tokens, 2 * features, width, 23, device)
+    flags = 0
+    if layout == "paired":
+        scales = host["w_sl"]
+        blocks = scales.shape[1]
+        paired = np.stack((scales[:features].reshape(features // 64, 64, blocks),
+                           scales[features:].reshape(features // 64, 64, blocks)), axis=1).reshape(2 * features, blocks)
+        dev = {**dev, "weight_scales": torch.from_numpy(O.swizzle_scales(paired)).to(device)}
+        flags = N.LINEAR_PAIRED_GATE_UP_SCALES
+    table = torch.from_numpy(gelu_table_cpu("tanh").view(np.int16).copy()).view(torch.uint16).to(device)
+    common = dict(epilogue=N.EPI_GEGLU, tokens=tokens, features=features, width=width, gelu_table=table,
+                  gelu_range=K.gelu_table_range(table), **dev)
+    results = []
+    for extra in (0, N.LINEAR_SINGLE_CTA):
+        status = torch.zeros(1, device=device, dtype=torch.int32)
+        if out_format == "bf16":
+            out = torch.full((tokens + 1, features), float("nan"), device=device, dtype=torch.bfloat16)
+            K.linear(out_format=N.OUT_BF16, out=out[:tokens], flags=flags | extra, status=status, **common)
+            assert torch.isnan(out[tokens]).all()
+            results.append((bits(out[:tokens]),))
+        else:
+            out = torch.empty((tokens, features // 2), device=device, dtype=torch.uint8)
+            linear = torch.empty((tokens, features // 16), device=device, dtype=torch.uint8)
+            blocked = torch.zeros(blocked_scale_bytes(tokens, features), device=device, dtype=torch.uint8)
+            K.linear(out_format=N.OUT_NVFP4, out=out, out_scales=linear, out_blocked=blocked,
+                     out_scale=torch.tensor(0.002, device=device), flags=flags | extra, status=status, **common)
+            results.append((u8(out), u8(linear), u8(blocked)))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+    for got, want in zip(*results):
+        assert np.array_equal(got, want)
+
+
 TAIL_TOKENS = list(range(1, 18)) + [127, 128, 129, 255, 256, 257, 559, 560, 561]
 
 
@@ -437,7 +497,7 @@ def test_rejections(device):
                  act_scale=one, weight=w, weight_scale=one, out=out)
 
 
-@pytest.mark.parametrize("std", (1e-7, 0.02, 0.5))
+@pytest.mark.parametrize("std", (1e-7, 0.02, 0.5, 20.0))
 def test_compact_gelu_table_matches_full_table(device, std):
     """Keeping only the non-trivial part of the GELU table in shared memory (b2_gelu_table_range)
     gives the same bits as gathering from the full table, for tiny, ordinary and huge gate values."""
@@ -449,7 +509,8 @@ def test_compact_gelu_table_matches_full_table(device, std):
     table_host = gelu_table_cpu("tanh")
     table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
     table_range = K.gelu_table_range(table)
-    assert table_range == (0x3B4B - 1280, 0x40A2)      # the closed forms hold outside [0x3B4B, 0x40A2); lo comes back ten binades lower
+    # the closed forms hold outside [0x3B4B, 0x40A2); lo comes back ten binades lower, hi four binades higher
+    assert table_range == (0x3B4B - 1280, 0x40A2 + 512)
     scalar = lambda v: torch.tensor(float(v), device=device)
     common = dict(kind=N.KIND_FP8, epilogue=N.EPI_GEGLU, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width,
                   act=torch.from_numpy(aq).to(device), act_scale=scalar(a_s), weight=torch.from_numpy(wq).to(device),
@@ -464,7 +525,9 @@ def test_compact_gelu_table_matches_full_table(device, std):
     if std == 1e-7:
         assert (magnitudes < 0x3B4B - 1280).mean() > 0.3       # the x/2 tail is exercised
     if std == 0.5:
-        assert (magnitudes >= 0x40A2).mean() > 0.2      # the identity / -0 tail is exercised
+        assert (magnitudes >= 0x40A2).mean() > 0.2      # the identity / -0 values inside the widened range
+    if std == 20.0:
+        assert (magnitudes >= 0x40A2 + 512).mean() > 0.2      # the identity / -0 tail beyond it
 
 
 def test_gelu_table_range_rejects_unstructured_tables(device):
