@@ -1,0 +1,394 @@
+// Multi-query attention for the Gemma-shaped towers: head dimension 256, one key/value head shared by all query
+// heads, no mask (the prefix attends to itself; the action expert's ten-token chunk attends to prefix + chunk).
+//
+//   out[b, h, t, :] = softmax(q[b, h, t, :] . k[b, :, :]^T / sqrt(256)) v[b, :, :]
+//
+// It replaces the attention the reference computes between its QKV projection and its output projection
+// (embodiinfer/backend/torch/attention.py:97-106, `SDPAAttention`: torch's scaled_dot_product_attention on
+// [B, H, T, D] queries and [B, 1, S, D] keys / values, bf16) and, for the ten-query case, the job of
+// backend/cuda/csrc/mqa_decode_attention.cu:170-393 -- not that kernel's structure (it merges key splits behind a grid
+// barrier that spins without a bound).
+//
+// Because every query head reads the same keys and values, the H x T query rows of one batch element are one matrix:
+// a CTA takes 128 of those rows and walks the keys in tiles of 64.
+//   warp 0      TMA producer: the query tile once, then key and value tiles through two-stage rings
+//   warp 1      tensor-memory owner and MMA issuer: S = Q K^T (128 x 64, K = 256) and O += P V (128 x 256, K = 64),
+//               bf16 operands, fp32 accumulators in tensor memory; V is used as it lies in memory ([key][d], the MN-major
+//               operand form), no transpose anywhere
+//   warps 2-5   one thread per query row: scores from tensor memory, running maximum and sum (base-2 exponentials of
+//               scores pre-multiplied by log2(e)/16), probabilities as bf16 into shared memory in the operand layout the
+//               second MMA reads, rescaling of the output accumulator when the maximum moved, final 1/sum and store
+// S is double-buffered, so the scores of the next key tile are computed while this one's probabilities are formed.
+// Every wait is bounded and reports through the status word, as in the GEMM kernels.
+#include "gemm_epilogue.cuh"
+
+#include <cuda.h>
+
+namespace b2 {
+
+namespace {
+
+constexpr int ATT_D = 256;                       // head dimension
+constexpr int ATT_ROWS = 128;                    // query rows per CTA
+constexpr int ATT_KEYS = 64;                     // keys per tile
+constexpr int ATT_ATOM_BYTES = 128;              // bytes of one swizzled row: 64 bf16
+constexpr int ATT_D_ATOMS = ATT_D * 2 / ATT_ATOM_BYTES;      // 4 column groups of 64 elements
+constexpr uint32_t Q_ATOM_BYTES = ATT_ROWS * ATT_ATOM_BYTES;  // 16 KB
+constexpr uint32_t KV_ATOM_BYTES = ATT_KEYS * ATT_ATOM_BYTES; // 8 KB
+constexpr uint32_t Q_BYTES = ATT_D_ATOMS * Q_ATOM_BYTES;      // 64 KB
+constexpr uint32_t KV_STAGE_BYTES = ATT_D_ATOMS * KV_ATOM_BYTES;   // 32 KB
+constexpr uint32_t P_BYTES = ATT_ROWS * ATT_ATOM_BYTES;       // 16 KB: 128 rows x 64 keys of bf16
+constexpr int ATT_THREADS = 32 * 6;
+constexpr int ATT_SHARED_BYTES = 1024 + int(Q_BYTES + 4 * KV_STAGE_BYTES + 2 * P_BYTES) + 256;
+constexpr uint32_t TMEM_S = 0, TMEM_O = 128;     // two score buffers of 64 columns, then 256 output columns
+
+// Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, A K-major, B K-major or MN-major.
+__device__ __forceinline__ uint32_t idesc_bf16(uint32_t m, uint32_t n, bool b_mn_major) {
+    return (1u << 4)            // D format fp32
+         | (1u << 7)            // A = bf16
+         | (1u << 10)           // B = bf16
+         | (uint32_t(b_mn_major) << 16)
+         | ((n >> 3) << 17)
+         | ((m >> 4) << 24);
+}
+
+// Shared-memory descriptor of an MN-major operand written by TMA with the 128-byte swizzle as [k][64 elements]:
+// a 128-byte row holds 64 consecutive MN elements of one k; 8 consecutive k are 1024 bytes apart per group (stride
+// byte offset), the next 64 MN elements start `mn_group_bytes` further (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_address, uint32_t mn_group_bytes) {
+    uint64_t desc = 0;
+    desc |= static_cast<uint64_t>((smem_address & 0x3FFFF) >> 4);
+    desc |= static_cast<uint64_t>(mn_group_bytes >> 4) << 16;
+    desc |= static_cast<uint64_t>(1024 >> 4) << 32;
+    desc |= static_cast<uint64_t>(1) << 46;
+    desc |= static_cast<uint64_t>(2) << 61;
+    return desc;
+}
+
+__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_store_32x32(uint32_t address, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(address), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct AttentionArgs {
+    __nv_bfloat16* out;          // [batch, heads * queries, 256]
+    unsigned int* status;
+    int rows_per_batch;          // heads * queries
+    int keys;                    // keys (= values) per batch element
+    int tiles_per_batch;
+    float scale_log2;            // log2(e) / sqrt(256)
+};
+
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                 const __grid_constant__ CUtensorMap v_map, const AttentionArgs args) {
+    pdl_launch_dependents();
+    extern __shared__ uint8_t shared_raw[];
+    const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = base;
+    const uint32_t k_smem = q_smem + Q_BYTES;                 // [2 stages]
+    const uint32_t v_smem = k_smem + 2 * KV_STAGE_BYTES;      // [2 stages]
+    const uint32_t p_smem = v_smem + 2 * KV_STAGE_BYTES;      // [2 buffers]
+    const uint32_t bars = p_smem + 2 * P_BYTES;
+    const uint32_t q_full = bars;
+    const uint32_t k_full = bars + 8, k_empty = bars + 24, v_full = bars + 40, v_empty = bars + 56;      // [2] each
+    const uint32_t s_full = bars + 72, s_free = bars + 88, p_ready = bars + 104, p_free = bars + 120;    // [2] each
+    const uint32_t o_done = bars + 136;
+    const uint32_t tmem_slot = bars + 144;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int batch = int(blockIdx.x) / args.tiles_per_batch;
+    const int tile = int(blockIdx.x) - batch * args.tiles_per_batch;
+    const int row0 = tile * ATT_ROWS;                                   // within the batch element
+    const int num_key_tiles = (args.keys + ATT_KEYS - 1) / ATT_KEYS;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&q_map);
+        tma_prefetch_descriptor(&k_map);
+        tma_prefetch_descriptor(&v_map);
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_full + 8 * i, 1);
+            mbar_init(k_empty + 8 * i, 1);
+            mbar_init(v_full + 8 * i, 1);
+            mbar_init(v_empty + 8 * i, 1);
+            mbar_init(s_full + 8 * i, 1);
+            mbar_init(s_free + 8 * i, 4);        // the four softmax warps
+            mbar_init(p_ready + 8 * i, 4);
+            mbar_init(p_free + 8 * i, 1);
+        }
+        mbar_init(o_done, 1);
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLUMNS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot) : "memory");
+    pdl_wait();
+
+    bool failed = false;
+    if (warp == 0) {
+        // ------------------------------------------------------------- TMA producer
+        const int q_row = batch * args.rows_per_batch + row0;
+        const int kv_row = batch * args.keys;
+        if (elect_one()) {
+            mbar_expect_tx(q_full, Q_BYTES);
+            for (int a = 0; a < ATT_D_ATOMS; ++a) tma_load_2d(q_smem + a * Q_ATOM_BYTES, &q_map, q_full, a * ATT_ATOM_BYTES, q_row);
+        }
+        __syncwarp();
+        for (int j = 0; j < num_key_tiles; ++j) {
+            const int b = j & 1;
+            const uint32_t parity = uint32_t(j >> 1) & 1u;
+            mbar_wait(k_empty + 8 * b, parity ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
+            __syncwarp();
+            if (elect_one()) {
+                mbar_expect_tx(k_full + 8 * b, KV_STAGE_BYTES);
+                for (int a = 0; a < ATT_D_ATOMS; ++a)
+                    tma_load_2d(k_smem + b * KV_STAGE_BYTES + a * KV_ATOM_BYTES, &k_map, k_full + 8 * b, a * ATT_ATOM_BYTES, kv_row + j * ATT_KEYS);
+            }
+            __syncwarp();
+            mbar_wait(v_empty + 8 * b, parity ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
+            __syncwarp();
+            if (elect_one()) {
+                mbar_expect_tx(v_full + 8 * b, KV_STAGE_BYTES);
+                for (int a = 0; a < ATT_D_ATOMS; ++a)
+                    tma_load_2d(v_smem + b * KV_STAGE_BYTES + a * KV_ATOM_BYTES, &v_map, v_full + 8 * b, a * ATT_ATOM_BYTES, kv_row + j * ATT_KEYS);
+            }
+            __syncwarp();
+        }
+        // do not leave while a copy is in flight: the last fill of every stage has landed when the MMAs that read it were
+        // issued, and those complete before the row threads finish; the waits below only bound the abnormal path
+        bool drain_failed = false;
+        mbar_wait(q_full, 0u, drain_failed, args.status, STATUS_WAIT_DRAIN);
+        for (int b = 0; b < 2 && b < num_key_tiles; ++b) {
+            const int last = ((num_key_tiles - 1 - b) / 2) * 2 + b;      // last tile that used stage b
+            mbar_wait(k_full + 8 * b, uint32_t(last >> 1) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
+            mbar_wait(v_full + 8 * b, uint32_t(last >> 1) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer
+        const uint32_t idesc_scores = idesc_bf16(ATT_ROWS, ATT_KEYS, false);
+        const uint32_t idesc_output = idesc_bf16(ATT_ROWS, ATT_D, true);
+        const uint64_t k_major = smem_desc_sw128(0);
+        const uint32_t k_major_low = uint32_t(k_major), k_major_high = uint32_t(k_major >> 32);
+        const uint64_t mn_major = smem_desc_sw128_mn(0, KV_ATOM_BYTES);
+        const uint32_t mn_major_low = uint32_t(mn_major), mn_major_high = uint32_t(mn_major >> 32);
+        mbar_wait(q_full, 0u, failed, args.status, STATUS_WAIT_MMA_FULL);
+        tc_fence_after_sync();
+        auto scores = [&](int j) {          // S[j & 1] = Q K_j^T
+            const int b = j & 1;
+            const uint32_t parity = uint32_t(j >> 1) & 1u;
+            mbar_wait(k_full + 8 * b, parity, failed, args.status, STATUS_WAIT_MMA_FULL);
+            mbar_wait(s_free + 8 * b, parity ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
+            tc_fence_after_sync();
+            __syncwarp();
+            if (elect_one()) {
+                const uint32_t d_tmem = tmem_base + TMEM_S + uint32_t(b) * ATT_KEYS;
+#pragma unroll
+                for (int a = 0; a < ATT_D_ATOMS; ++a) {
+                    const uint32_t q_low = k_major_low + ((q_smem + a * Q_ATOM_BYTES) >> 4);
+                    const uint32_t k_low = k_major_low + ((k_smem + b * KV_STAGE_BYTES + a * KV_ATOM_BYTES) >> 4);
+#pragma unroll
+                    for (int s = 0; s < 4; ++s)          // 16 elements of D = 32 bytes per MMA
+                        mma_bf16(d_tmem, desc_from_words(q_low + 2 * s, k_major_high), desc_from_words(k_low + 2 * s, k_major_high),
+                                 idesc_scores, (a | s) != 0);
+                }
+                tc_commit(k_empty + 8 * b);
+                tc_commit(s_full + 8 * b);
+            }
+            __syncwarp();
+        };
+        auto output = [&](int j) {          // O += P[j & 1] V_j
+            const int b = j & 1;
+            const uint32_t parity = uint32_t(j >> 1) & 1u;
+            mbar_wait(v_full + 8 * b, parity, failed, args.status, STATUS_WAIT_MMA_FULL);
+            mbar_wait(p_ready + 8 * b, parity, failed, args.status, STATUS_WAIT_MMA_TMEM);
+            tc_fence_after_sync();
+            __syncwarp();
+            if (elect_one()) {
+                const uint32_t p_low = k_major_low + ((p_smem + b * P_BYTES) >> 4);
+                const uint32_t v_low = mn_major_low + ((v_smem + b * KV_STAGE_BYTES) >> 4);
+#pragma unroll
+                for (int s = 0; s < ATT_KEYS / 16; ++s)   // 16 keys per MMA: 32 bytes along a row of P, 16 rows (2048 bytes) of V
+                    mma_bf16(tmem_base + TMEM_O, desc_from_words(p_low + 2 * s, k_major_high),
+                             desc_from_words(v_low + s * (2048 >> 4), mn_major_high), idesc_output, (j | s) != 0);
+                tc_commit(v_empty + 8 * b);
+                tc_commit(p_free + 8 * b);
+                tc_commit(o_done);
+            }
+            __syncwarp();
+        };
+        scores(0);
+        for (int j = 0; j < num_key_tiles; ++j) {
+            if (j + 1 < num_key_tiles) scores(j + 1);
+            output(j);
+        }
+    } else {
+        // ------------------------------------------------------------- one thread per query row
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;                 // row of the tile = tensor-memory lane
+        const uint32_t lane_address = tmem_base + (uint32_t(quarter * 32) << 16);
+        float running_max = -INFINITY, running_sum = 0.0f;
+        for (int j = 0; j < num_key_tiles; ++j) {
+            const int b = j & 1;
+            const uint32_t parity = uint32_t(j >> 1) & 1u;
+            mbar_wait(s_full + 8 * b, parity, failed, args.status, STATUS_WAIT_EPILOGUE);
+            tc_fence_after_sync();
+            uint32_t raw[2][32];
+            tmem_load_32x32(lane_address + TMEM_S + uint32_t(b) * ATT_KEYS, raw[0]);
+            tmem_load_32x32(lane_address + TMEM_S + uint32_t(b) * ATT_KEYS + 32, raw[1]);
+            tmem_load_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free + 8 * b);      // the scores of key tile j + 2 may overwrite this buffer
+            const int valid = args.keys - j * ATT_KEYS;     // keys of this tile that exist
+            float tile_max = -INFINITY;
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float s = half * 32 + i < valid ? __uint_as_float(raw[half][i]) * args.scale_log2 : -INFINITY;
+                    raw[half][i] = __float_as_uint(s);
+                    tile_max = fmaxf(tile_max, s);
+                }
+            const float new_max = fmaxf(running_max, tile_max);
+            const float correction = exp2_approx(running_max - new_max);      // 0 on the first tile (running_max = -inf)
+            running_max = new_max;
+            float tile_sum = 0.0f;
+            uint32_t packed[2][16];
+#pragma unroll
+            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = exp2_approx(__uint_as_float(raw[half][2 * i]) - new_max);
+                    const float p1 = exp2_approx(__uint_as_float(raw[half][2 * i + 1]) - new_max);
+                    // the sum uses the probabilities as the second MMA will see them (rounded to bf16)
+                    const uint32_t pair = float2_to_bf16x2(make_float2(p0, p1));
+                    packed[half][i] = pair;
+                    tile_sum += bf16_lo(pair) + bf16_hi(pair);
+                }
+            running_sum = running_sum * correction + tile_sum;
+            // P[b]: row `row`, 64 keys = 128 bytes = 8 chunks of 16 bytes, chunk c stored at c ^ (row % 8) (128-byte swizzle)
+            mbar_wait(p_free + 8 * b, parity ^ 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
+            const uint32_t p_row = p_smem + b * P_BYTES + uint32_t(row >> 3) * 1024u + uint32_t(row & 7) * 128u;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t* w = &packed[c >> 2][(c & 3) * 4];
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + uint32_t((c ^ (row & 7)) * 16)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            }
+            // the accumulator holds the sum over the tiles before this one in units of the old maximum
+            if (j > 0) {
+                mbar_wait(o_done, uint32_t(j - 1) & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
+                tc_fence_after_sync();
+                if (__any_sync(0xffffffffu, correction != 1.0f)) {
+#pragma unroll 1
+                    for (int chunk = 0; chunk < ATT_D / 32; ++chunk) {
+                        uint32_t o[32];
+                        tmem_load_32x32(lane_address + TMEM_O + chunk * 32, o);
+                        tmem_load_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * correction);
+                        tmem_store_32x32(lane_address + TMEM_O + chunk * 32, o);
+                    }
+                    tmem_store_wait();
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P, written by these threads, is read by the tensor core
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready + 8 * b);
+        }
+        mbar_wait(o_done, uint32_t(num_key_tiles - 1) & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
+        tc_fence_after_sync();
+        const float inverse = 1.0f / running_sum;
+        const bool row_exists = row0 + row < args.rows_per_batch;
+        __nv_bfloat16* destination = args.out + (int64_t(batch) * args.rows_per_batch + row0 + row) * ATT_D;
+#pragma unroll 1
+        for (int chunk = 0; chunk < ATT_D / 32; ++chunk) {
+            uint32_t o[32];
+            tmem_load_32x32(lane_address + TMEM_O + chunk * 32, o);
+            tmem_load_wait();
+            if (row_exists) {
+                uint32_t words[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    words[i] = float2_to_bf16x2(make_float2(__uint_as_float(o[2 * i]) * inverse, __uint_as_float(o[2 * i + 1]) * inverse));
+                const uint32_t first[8] = {words[0], words[1], words[2], words[3], words[4], words[5], words[6], words[7]};
+                const uint32_t second[8] = {words[8], words[9], words[10], words[11], words[12], words[13], words[14], words[15]};
+                st_u8(destination + chunk * 32, first);
+                st_u8(destination + chunk * 32 + 16, second);
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLUMNS);
+    }
+}
+
+}  // namespace
+
+int launch_attention(const void* q, const void* k, const void* v, void* out, int batch, int heads, int queries, int keys,
+                     int head_dim, void* status, cudaStream_t stream) {
+    if (head_dim != ATT_D) return B2_E_UNSUPPORTED;
+    const int64_t rows_per_batch = int64_t(heads) * queries;
+    if (rows_per_batch * batch >= (int64_t(1) << 31) || int64_t(keys) * batch >= (int64_t(1) << 31)) return B2_E_TOO_LARGE;
+    static bool configured[64] = {false};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device >= 0 && device < 64 && !configured[device]) {
+        const cudaError_t error = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SHARED_BYTES);
+        if (error != cudaSuccess) return int(error);
+        configured[device] = true;
+    }
+    CUtensorMap q_map, k_map, v_map;
+    if (!make_operand_map(&q_map, q, rows_per_batch * batch, ATT_D * 2, ATT_ROWS)) return B2_E_DRIVER;
+    if (!make_operand_map(&k_map, k, int64_t(keys) * batch, ATT_D * 2, ATT_KEYS)) return B2_E_DRIVER;
+    if (!make_operand_map(&v_map, v, int64_t(keys) * batch, ATT_D * 2, ATT_KEYS)) return B2_E_DRIVER;
+    AttentionArgs args{};
+    args.out = static_cast<__nv_bfloat16*>(out);
+    args.status = static_cast<unsigned int*>(status);
+    args.rows_per_batch = int(rows_per_batch);
+    args.keys = keys;
+    args.tiles_per_batch = int((rows_per_batch + ATT_ROWS - 1) / ATT_ROWS);
+    args.scale_log2 = 1.4426950408889634f / 16.0f;
+    return launch_kernel(attention_kernel, dim3(unsigned(batch * args.tiles_per_batch)), dim3(ATT_THREADS), size_t(ATT_SHARED_BYTES), stream,
+                         q_map, k_map, v_map, args);
+}
+
+}  // namespace b2

@@ -162,6 +162,28 @@ def geglu(
     N.check(status, "b2_geglu")
 
 
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None, *, status: torch.Tensor | None = None) -> torch.Tensor:
+    """Unmasked multi-query attention, ``softmax(q k^T / sqrt(D)) v``: q [B, H, T, 256], k / v [B, 1, S, 256], all
+    contiguous bf16; returns [B, H, T, 256] (``b2_attention``; the reference's ``SDPAAttention``)."""
+    _require_cuda(q, k, v)
+    if q.dim() != 4 or k.shape != v.shape or k.dim() != 4 or k.shape[1] != 1 or k.shape[0] != q.shape[0] or k.shape[3] != q.shape[3]:
+        raise ValueError("attention requires q [B, H, T, D] and k, v [B, 1, S, D]")
+    if any(t.dtype != torch.bfloat16 or not t.is_contiguous() for t in (q, k, v)):
+        raise ValueError("attention requires contiguous bf16 tensors")
+    batch, heads, queries, head_dim = q.shape
+    if out is None:
+        out = torch.empty_like(q)
+    elif out.shape != q.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("attention output must be a contiguous bf16 tensor of the queries' shape")
+    if status is None:
+        status = status_word(q.device)
+    with torch.cuda.device(q.device):
+        code = N.load().b2_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), batch, heads, queries, k.shape[2],
+                                     head_dim, status.data_ptr(), _stream(q.device))
+    N.check(code, "b2_attention")
+    return out
+
+
 def rope_split(qkv: torch.Tensor, sine: torch.Tensor, cosine: torch.Tensor, q_out: torch.Tensor, k_out: torch.Tensor,
                v_out: torch.Tensor, *, batch: int, tokens: int, heads: int, kv_heads: int, head_dim: int, kv_offset: int = 0) -> None:
     """Split a packed QKV projection, rotate queries and keys, write ``q_out`` [B, heads, T, D] and the

@@ -25,7 +25,7 @@ extern "C" {
  * b2_linear_desc are rejected; the opt-in cluster split of K of version 3 (flag value 32) is gone.
  * 3: added the producers in front of the GEMMs (b2_norm_quant, b2_layer_norm_quant, b2_bhsd_quant, b2_normalize_frames,
  * b2_frames_to_patches, b2_resize_frames). */
-#define B2_ABI_VERSION 4
+#define B2_ABI_VERSION 5
 
 /* ---- status codes ---------------------------------------------------------- */
 #define B2_OK 0
@@ -178,6 +178,21 @@ typedef struct b2_linear_desc {
 int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q_out, void* k_out, void* v_out,
                   int32_t batch, int32_t tokens, int32_t heads, int32_t kv_heads, int32_t head_dim,
                   int64_t factor_batch_stride, int32_t kv_capacity, int32_t kv_offset, void* stream);
+
+/* Multi-query attention of the Gemma-shaped towers, unmasked:
+ *   out[b, h, t, :] = softmax(q[b, h, t, :] . k[b, :, :]^T / sqrt(head_dim)) v[b, :, :]
+ * It is the attention between the QKV projection and the output projection
+ * (embodiinfer/backend/torch/attention.py:97-106, SDPAAttention: scaled_dot_product_attention with one key/value head
+ * shared by all query heads), and for a ten-query chunk over prefix + chunk keys the job of
+ * embodiinfer/backend/cuda/csrc/mqa_decode_attention.cu:170-393.
+ *   q    bf16 [batch, heads, queries, head_dim]   (b2_rope_split's q_out)
+ *   k, v bf16 [batch, 1, keys, head_dim]           (b2_rope_split's k_out / v_out with kv_capacity == keys)
+ *   out  bf16 [batch, heads, queries, head_dim]   (what b2_bhsd_quant reads)
+ * head_dim must be 256 (B2_E_UNSUPPORTED otherwise); all pointers 16-byte aligned.  Scores and the output accumulate in
+ * fp32; probabilities enter the second product as bf16, as in torch's flash kernels.  `status` as in b2_linear_desc
+ * (NULL allowed). */
+int b2_attention(const void* q, const void* k, const void* v, void* out, int32_t batch, int32_t heads, int32_t queries,
+                 int32_t keys, int32_t head_dim, void* status, void* stream);
 
 /* RMSNorm (+ residual update, + adaptive modulation) fused with the activation encoder: the step in front of
  * every quantised projection.  Replaces cc_norm_quant and cc_norm_quant_reduce

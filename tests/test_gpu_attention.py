@@ -1,0 +1,62 @@
+"""b2_attention (tcgen05 multi-query attention, head dimension 256) against a float32 PyTorch attention on the same
+bf16 inputs.  Tolerance: the output is bf16 (relative rounding error up to 2^-9, about 1.1e-3 rms) and the probabilities
+enter the second product as bf16, as in torch's own flash kernels; the test asks for a relative Frobenius error of at
+most 3e-3 against the float32 result and for an error no larger than 1.5 times torch's bf16 scaled_dot_product_attention
+on the same inputs (reference semantics: embodiinfer/backend/torch/attention.py:97-106)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from embodiinfer_b200 import kernels as K
+
+pytestmark = pytest.mark.gpu
+
+
+def reference(q, k, v):
+    scores = torch.einsum("bhtd,bsd->bhts", q.float(), k[:, 0].float()) / 16.0
+    return torch.einsum("bhts,bsd->bhtd", scores.softmax(-1), v[:, 0].float())
+
+
+def relative(a, b):
+    return float((a.float() - b).norm() / b.norm())
+
+
+@pytest.mark.parametrize("batch,heads,queries,keys", [
+    (2, 8, 560, 560),       # prefix tower: 4480 query rows per batch element, 35 tiles, 9 key tiles (the last one ragged)
+    (3, 8, 10, 570),        # action expert: ten-token chunk over prefix + chunk
+    (1, 8, 10, 570),
+    (1, 1, 1, 1),           # a single key: softmax is 1
+    (2, 3, 77, 64),         # exactly one key tile, ragged rows
+    (2, 8, 16, 65),         # one key in the second tile
+    (1, 8, 128, 128),
+])
+@pytest.mark.parametrize("spread", (1.0, 6.0))
+def test_attention_matches_float32(device, batch, heads, queries, keys, spread):
+    generator = torch.Generator(device=device).manual_seed(7 * batch + heads + queries + keys)
+    q = (torch.randn((batch, heads, queries, 256), device=device, generator=generator) * spread).to(torch.bfloat16)
+    k = torch.randn((batch, 1, keys, 256), device=device, generator=generator).to(torch.bfloat16)
+    v = torch.randn((batch, 1, keys, 256), device=device, generator=generator).to(torch.bfloat16)
+    status = torch.zeros(1, device=device, dtype=torch.int32)
+    out = torch.full((batch * heads * queries + 1, 256), float("nan"), device=device, dtype=torch.bfloat16)
+    result = K.attention(q, k, v, out[:-1].view(batch, heads, queries, 256), status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.isnan(out[-1]).all(), "wrote past the last row"
+    want = reference(q, k, v)
+    error = relative(result, want)
+    library = relative(F.scaled_dot_product_attention(q, k, v, enable_gqa=heads > 1), want)
+    assert torch.isfinite(result.float()).all()
+    assert error <= 3e-3, (error, library)
+    assert error <= 1.5 * library + 1e-4, (error, library)
+
+
+def test_attention_rejects_other_shapes(device):
+    q = torch.zeros((1, 2, 4, 128), device=device, dtype=torch.bfloat16)
+    k = torch.zeros((1, 1, 4, 128), device=device, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="error -2"):
+        K.attention(q, k, k.clone())
+    with pytest.raises(ValueError):
+        K.attention(q, torch.zeros((1, 2, 4, 128), device=device, dtype=torch.bfloat16), k)
