@@ -15,9 +15,9 @@
 //   warp 1      tensor-memory owner and MMA issuer: S = Q K^T (128 x 64, K = 256) and O += P V (128 x 256, K = 64),
 //               bf16 operands, fp32 accumulators in tensor memory; V is used as it lies in memory ([key][d], the MN-major
 //               operand form), no transpose anywhere
-//   warps 2-5   one thread per query row: scores from tensor memory, running maximum and sum (base-2 exponentials of
+//   warps 2-5   one thread per query row: scores from tensor memory, running reference and sum (base-2 exponentials of
 //               scores pre-multiplied by log2(e)/16), probabilities as bf16 into shared memory in the operand layout the
-//               second MMA reads, rescaling of the output accumulator when the maximum moved, final 1/sum and store
+//               second MMA reads, rescaling of the output accumulator when the reference moved, final 1/sum and store
 // S is double-buffered, so the scores of the next key tile are computed while this one's probabilities are formed.
 // Every wait is bounded and reports through the status word, as in the GEMM kernels.
 #include "gemm_epilogue.cuh"
@@ -274,31 +274,41 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free + 8 * b);      // the scores of key tile j + 2 may overwrite this buffer
             const int valid = args.keys - j * ATT_KEYS;     // keys of this tile that exist
-            float tile_max = -INFINITY;
+            if (valid < ATT_KEYS) {                          // last tile: keys beyond the end never win the maximum and add nothing
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (half * 32 + i >= valid) raw[half][i] = __float_as_uint(-INFINITY);
+            }
+            // of the raw scores (the scale is positive); four independent chains, this thread is alone on its scheduler
+            float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int half = 0; half < 2; ++half)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float s = half * 32 + i < valid ? __uint_as_float(raw[half][i]) * args.scale_log2 : -INFINITY;
-                    raw[half][i] = __float_as_uint(s);
-                    tile_max = fmaxf(tile_max, s);
-                }
-            const float new_max = fmaxf(running_max, tile_max);
-            const float correction = exp2_approx(running_max - new_max);      // 0 on the first tile (running_max = -inf)
+                for (int i = 0; i < 32; ++i) partial_max[i & 3] = fmaxf(partial_max[i & 3], __uint_as_float(raw[half][i]));
+            const float tile_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3])) * args.scale_log2;
+            // The exponentials are taken relative to a reference that follows the row maximum lazily: it moves only when
+            // the maximum has grown by more than 2^8 since it was set (probabilities then stay below 256, far inside the
+            // range of bf16 and fp32, and the final division by the sum is exact whatever the reference), so the output
+            // accumulator in tensor memory is rescaled a few times per row instead of once per key tile.
+            const bool move = tile_max > running_max + 8.0f;                  // always on the first tile (running_max = -inf)
+            const float new_max = move ? tile_max : running_max;
+            const float correction = move ? exp2_approx(running_max - new_max) : 1.0f;      // 0 on the first tile
             running_max = new_max;
-            float tile_sum = 0.0f;
+            float partial_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t packed[2][16];
 #pragma unroll
             for (int half = 0; half < 2; ++half)
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    const float p0 = exp2_approx(__uint_as_float(raw[half][2 * i]) - new_max);
-                    const float p1 = exp2_approx(__uint_as_float(raw[half][2 * i + 1]) - new_max);
-                    // the sum uses the probabilities as the second MMA will see them (rounded to bf16)
-                    const uint32_t pair = float2_to_bf16x2(make_float2(p0, p1));
-                    packed[half][i] = pair;
-                    tile_sum += bf16_lo(pair) + bf16_hi(pair);
+                    // 2^(score * log2(e)/16 - reference) in one multiply-add per value
+                    const float p0 = exp2_approx(__fmaf_rn(__uint_as_float(raw[half][2 * i]), args.scale_log2, -new_max));
+                    const float p1 = exp2_approx(__fmaf_rn(__uint_as_float(raw[half][2 * i + 1]), args.scale_log2, -new_max));
+                    packed[half][i] = float2_to_bf16x2(make_float2(p0, p1));
+                    partial_sum[i & 3] += p0 + p1;
                 }
+            const float tile_sum = (partial_sum[0] + partial_sum[1]) + (partial_sum[2] + partial_sum[3]);
             running_sum = running_sum * correction + tile_sum;
             // P[b]: row `row`, 64 keys = 128 bytes = 8 chunks of 16 bytes, chunk c stored at c ^ (row % 8) (128-byte swizzle)
             mbar_wait(p_free + 8 * b, parity ^ 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
@@ -336,19 +346,23 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         const bool row_exists = row0 + row < args.rows_per_batch;
         __nv_bfloat16* destination = args.out + (int64_t(batch) * args.rows_per_batch + row0 + row) * ATT_D;
 #pragma unroll 1
-        for (int chunk = 0; chunk < ATT_D / 32; ++chunk) {
-            uint32_t o[32];
-            tmem_load_32x32(lane_address + TMEM_O + chunk * 32, o);
+        for (int group = 0; group < ATT_D / 128; ++group) {      // four 32-column loads in flight per wait
+            uint32_t o[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_load_32x32(lane_address + TMEM_O + group * 128 + c * 32, o[c]);
             tmem_load_wait();
             if (row_exists) {
-                uint32_t words[16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    words[i] = float2_to_bf16x2(make_float2(__uint_as_float(o[2 * i]) * inverse, __uint_as_float(o[2 * i + 1]) * inverse));
-                const uint32_t first[8] = {words[0], words[1], words[2], words[3], words[4], words[5], words[6], words[7]};
-                const uint32_t second[8] = {words[8], words[9], words[10], words[11], words[12], words[13], words[14], words[15]};
-                st_u8(destination + chunk * 32, first);
-                st_u8(destination + chunk * 32 + 16, second);
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t words[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        words[i] = float2_to_bf16x2(make_float2(__uint_as_float(o[c][2 * i]) * inverse, __uint_as_float(o[c][2 * i + 1]) * inverse));
+                    const uint32_t first[8] = {words[0], words[1], words[2], words[3], words[4], words[5], words[6], words[7]};
+                    const uint32_t second[8] = {words[8], words[9], words[10], words[11], words[12], words[13], words[14], words[15]};
+                    st_u8(destination + group * 128 + c * 32, first);
+                    st_u8(destination + group * 128 + c * 32 + 16, second);
+                }
             }
         }
     }

@@ -278,6 +278,36 @@ def linear_cases(device, options=None):
         yield f"linear/{name}", make, total, total, 2.0 * tokens * rows * width
 
 
+ATTENTION_SHAPES = [
+    # name, batch, query heads, queries, keys (head dimension 256, one key/value head)
+    ("prefix_B1_8x560x560", 1, 8, 560, 560),
+    ("prefix_B32_8x560x560", 32, 8, 560, 560),
+    ("expert_B1_8x10x570", 1, 8, 10, 570),
+    ("expert_B8_8x10x570", 8, 8, 10, 570),
+    ("expert_B32_8x10x570", 32, 8, 10, 570),
+    ("expert_B64_8x10x570", 64, 8, 10, 570),
+]
+
+
+def attention_cases(device, library: bool):
+    """b2_attention; with ``library`` torch's scaled_dot_product_attention on the same tensors instead (name suffix)."""
+    import torch.nn.functional as F
+    for name, batch, heads, queries, keys in ATTENTION_SHAPES:
+        total = 2 * (2 * batch * heads * queries * 256 + 2 * batch * keys * 256)
+        flops = 4.0 * batch * heads * queries * keys * 256
+
+        def make(_i, batch=batch, heads=heads, queries=queries, keys=keys, library=library):
+            q = torch.randn((batch, heads, queries, 256), device=device).to(torch.bfloat16)
+            k = torch.randn((batch, 1, keys, 256), device=device).to(torch.bfloat16)
+            v = torch.randn((batch, 1, keys, 256), device=device).to(torch.bfloat16)
+            out = torch.empty_like(q)
+            if library:
+                return lambda: F.scaled_dot_product_attention(q, k, v, enable_gqa=True)
+            return lambda: K.attention(q, k, v, out)
+
+        yield f"attention/{name}" + ("/torch_sdpa" if library else ""), make, total, total, flops
+
+
 def library_time(kind: str, tokens: int, rows: int, width: int, device, launches: int) -> float | None:
     """torch's scaled_mm (the GEMM the reference calls on this GPU) at the same shape; None when this
     torch build has no such kernel for the operand type."""
@@ -403,7 +433,8 @@ def main() -> None:
     torch.cuda.set_device(device)
     peaks = {"hbm_gbs": 6541.5, "fp8_tflops": 4500.0, "nvfp4_tflops": 9000.0}
     options = {"flags": args.flags, "feature_tile": args.feature_tile, "unpaired": args.unpaired, "workspace": args.workspace}
-    sources = (quantiser_cases, geglu_cases, norm_cases, layout_cases, lambda dev: linear_cases(dev, options))
+    sources = (quantiser_cases, geglu_cases, norm_cases, layout_cases, lambda dev: linear_cases(dev, options),
+               lambda dev: attention_cases(dev, False), lambda dev: attention_cases(dev, True) if args.library else iter(()))
     reference_us = {}
     if args.reference:
         for name, make, set_bytes in reference_cases(device):
@@ -419,7 +450,9 @@ def main() -> None:
             microseconds, sets = time_graph(make, set_bytes, args.launches)
             line = {"case": name, "us": round(microseconds, 2), "gbs": round(algorithmic_bytes / microseconds / 1e3, 1),
                     "sets": sets, "l2": "cold" if sets * set_bytes >= L2_BYTES else "warm"}
-            if flops:
+            if name.startswith("attention/"):
+                line["tflops"] = round(flops / microseconds / 1e6, 1)
+            elif flops:
                 line["tflops"] = round(flops / microseconds / 1e6, 1)
                 nominal = peaks["fp8_tflops"] if "fp8" in name else peaks["nvfp4_tflops"]
                 line["frac_of_nominal_tensor_peak"] = round(line["tflops"] / nominal, 3)
