@@ -83,15 +83,28 @@ class FusedNorm:
         self.scale = projection.maximum / (448 * (6 if self.bits == 4 else 1))
         self.plans: dict = {}
 
-    def __call__(self, x: torch.Tensor, weight: torch.Tensor):
-        """``x``: contiguous bf16 [B, T, D]; ``weight``: fp32 [D] RMSNorm weight (the scale is 1 + weight)."""
-        key = (tuple(x.shape), torch.cuda.current_stream(x.device).cuda_stream)
+    def _plan(self, x: torch.Tensor, adaptive: bool):
+        key = (tuple(x.shape), adaptive, torch.cuda.current_stream(x.device).cuda_stream)
         plan = self.plans.get(key)
         if plan is None:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("Warm the fused norm before graph capture")
-            plan = self.plans[key] = self.backend.plan(x, bits=self.bits, calibrated_scale=self.scale, adaptive=False)
-        return plan.normalize(x, scale=weight)
+            plan = self.plans[key] = self.backend.plan(x, bits=self.bits, calibrated_scale=self.scale, adaptive=adaptive)
+        return plan
+
+    def __call__(self, x: torch.Tensor, weight: torch.Tensor):
+        """``x``: contiguous bf16 [B, T, D]; ``weight``: fp32 [D] RMSNorm weight (the scale is 1 + weight)."""
+        return self._plan(x, False).normalize(x, scale=weight)
+
+    def modulated(self, x: torch.Tensor, modulation: torch.Tensor, pending=None):
+        """Adaptive RMSNorm (``NormQuantPlan`` with ``adaptive=True``): ``modulation`` fp32 [B, 3D] = scale | shift |
+        gate.  ``pending`` = (update, gate) of the sublayer before: the residual stream becomes
+        ``x + update * gate`` in the same launch.  Returns (residual stream, encoded activation, this norm's gate)."""
+        plan = self._plan(x, True)
+        if pending is None:
+            plan.normalize(x, modulation=modulation)
+            return x, plan, plan.gate
+        return plan.residual_normalize(x, pending[0].contiguous(), pending[1], modulation=modulation)
 
 
 class FusedLayerNorm:
@@ -160,12 +173,13 @@ class Projection(nn.Module):
         self.attention_output: FusedAttentionOutput | None = None
         self.maximum, self.recording = 0.0, False
 
-    def attended(self, attended: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    def attended(self, attended: torch.Tensor, residual: torch.Tensor, add_residual: bool = True) -> torch.Tensor:
         """``self(attended.transpose(1, 2).flatten(2), residual)`` for an attention output [B, H, T, D], the transpose
-        and the activation encoding in one launch (calibrated plans only)."""
+        and the activation encoding in one launch (calibrated plans only).  ``add_residual=False``: the projection
+        alone, shaped like ``residual`` (the adaptive blocks add it through the next norm's gate)."""
         rows = residual.reshape(-1, residual.shape[-1])
         like = _Shape((rows.shape[0], attended.shape[1] * attended.shape[3]), rows)
-        output = self.plan.apply(like, self.attention_output(attended), bias=self.dense_bias, residual=rows)
+        output = self.plan.apply(like, self.attention_output(attended), bias=self.dense_bias, residual=rows if add_residual else None)
         return output.reshape(residual.shape)
 
     def layer_normed(self, x: torch.Tensor, norm: nn.LayerNorm) -> torch.Tensor:
@@ -200,9 +214,35 @@ class Projection(nn.Module):
         self.dense_weight = None
 
 
+def _adarms_dense(width: int, generator, device) -> nn.Linear:
+    """The modulation projection of one AdaRMS norm: small random weights, bias 0 | 0 | 1 (scale, shift, gate), so that a
+    random-init stack keeps its sublayer outputs."""
+    dense = nn.Linear(width, 3 * width, bias=True, device=device, dtype=torch.bfloat16)
+    with torch.no_grad():
+        dense.weight.copy_((0.02 * torch.randn((3 * width, width), generator=generator, device=device)).to(torch.bfloat16))
+        dense.bias.zero_()
+        dense.bias[2 * width:] = 1.0
+    dense.requires_grad_(False)
+    return dense
+
+
 def _rms_norm(x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """Gemma RMSNorm, ``scale`` = 1 + weight (one fused kernel)."""
     return F.rms_norm(x, (x.shape[-1],), scale, 1e-6)
+
+
+def _ada_rms_norm(x: torch.Tensor, modulation: torch.Tensor):
+    """Adaptive RMSNorm as tensor operations (embodiinfer/policies/pi05/modeling_pi05.py:180-194): fp32 variance,
+    ``normed * (1 + scale) + shift`` with fp32 scale | shift | gate [B, 3D]; returns (bf16 output, bf16 gate [B, 1, D])."""
+    variance = x.float().square().mean(-1, keepdim=True)
+    normed = x * torch.rsqrt(variance + 1e-6)
+    scale, shift, gate = modulation.unsqueeze(1).chunk(3, dim=-1)
+    return (normed * (1 + scale) + shift).to(x.dtype), gate.to(x.dtype)
+
+
+def _gated_residual(x: torch.Tensor, pending) -> torch.Tensor:
+    """``x + update * gate`` with both products rounded to bf16, as the fused producer does."""
+    return x if pending is None else x + (pending[0] * pending[1])
 
 
 def rope_tables(positions: torch.Tensor, head_dim: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -224,9 +264,17 @@ def rope_reference(x: torch.Tensor, tables: tuple[torch.Tensor, torch.Tensor]) -
 class GemmaBlock(nn.Module):
     """Pre-norm block; ``prefix_kv`` lets the action expert attend to the prefix tower's keys/values."""
 
-    def __init__(self, shape: TowerShape, attention_width: int, config, generator, device) -> None:
+    def __init__(self, shape: TowerShape, attention_width: int, config, generator, device, adaptive: bool = False) -> None:
         super().__init__()
         self.shape = shape
+        # adaptive (the action expert): both norms are AdaRMS norms whose scale | shift | gate come from the flow time
+        # (a dense [width -> 3 width] per norm, evaluated once per schedule step outside the step's graph, as the
+        # reference's runtime does: policies/pi05/inference/runtime.py:366-401), and each sublayer's output enters the
+        # residual stream multiplied by its norm's gate
+        self.adaptive = adaptive
+        if adaptive:
+            self.input_dense = _adarms_dense(shape.width, generator, device)
+            self.post_dense = _adarms_dense(shape.width, generator, device)
         q_dim, kv_dim = shape.heads * shape.head_dim, shape.kv_heads * shape.head_dim
         make = lambda n, k: _random_linear(n, k, generator, device)
         self.qkv = Projection((make(q_dim, shape.width), make(kv_dim, shape.width), make(kv_dim, shape.width)), config)
@@ -273,12 +321,43 @@ class GemmaBlock(nn.Module):
         self.mlp_norm = FusedNorm(quantizer, self.fused_mlp.gate_up) if self.method is not None else None
         self.dense_mlp = None
 
-    def forward(self, x, rope, kv_buffers=None):
+    def adaptive_mlp(self, x: torch.Tensor, attention_output: torch.Tensor, attention_gate: torch.Tensor, modulation: torch.Tensor):
+        """The second half of an adaptive block: residual stream += attention output * gate, AdaRMS, gated MLP.  Returns
+        (residual stream, (MLP output, its gate)): the MLP output joins the stream in the next norm's launch."""
+        pending = (attention_output, attention_gate)
+        if self.fused_mlp is not None and self.mlp_norm is not None and self.fused_norm:
+            x, encoded, gate = self.mlp_norm.modulated(x.contiguous(), modulation, pending)
+            rows = x.reshape(-1, x.shape[-1])
+            return x, (self.fused_mlp.project(rows, encoded).reshape(x.shape), gate)
+        x = _gated_residual(x, pending)
+        normed, gate = _ada_rms_norm(x, modulation)
+        if self.fused_mlp is not None:
+            rows = normed.reshape(-1, normed.shape[-1])
+            return x, (self.fused_mlp(rows).reshape(x.shape), gate)
+        gate_half, up = self.gate_up(normed).chunk(2, dim=-1)
+        hidden = F.gelu(gate_half, approximate="tanh") * up
+        if self.recording:
+            self.mlp_ranges[0] = max(self.mlp_ranges[0], float(normed.abs().max()))
+            self.mlp_ranges[1] = max(self.mlp_ranges[1], float(hidden.abs().max()))
+        return x, (self.down(hidden), gate)
+
+    def forward(self, x, rope, kv_buffers=None, modulations=None, pending=None):
         """``kv_buffers`` (action expert): per-layer [B, 1, prefix + T, D] key/value buffers whose first
-        ``prefix`` rows hold the prefix tower's keys/values; this block writes its own rows behind them."""
+        ``prefix`` rows hold the prefix tower's keys/values; this block writes its own rows behind them.
+        Adaptive blocks take ``modulations`` = (input norm's, post-attention norm's) fp32 [B, 3 width] and ``pending`` =
+        (MLP output, gate) of the block before, and return (residual stream, own keys/values, pending)."""
         shape = self.shape
         batch, tokens, _ = x.shape
-        if self.qkv.norm is not None and self.fused_norm:
+        attention_gate = None
+        if self.adaptive:
+            if self.qkv.norm is not None and self.fused_norm:
+                x, encoded, attention_gate = self.qkv.norm.modulated(x.contiguous(), modulations[0], pending)
+                qkv = self.qkv.plan.apply(x.reshape(-1, x.shape[-1]), encoded, bias=self.qkv.dense_bias).reshape(batch, tokens, -1)
+            else:
+                x = _gated_residual(x, pending)
+                normed, attention_gate = _ada_rms_norm(x, modulations[0])
+                qkv = self.qkv(normed)
+        elif self.qkv.norm is not None and self.fused_norm:
             qkv = self.qkv.normed(x, self.input_weight)
         else:
             qkv = self.qkv(_rms_norm(x, self.input_scale))
@@ -301,6 +380,13 @@ class GemmaBlock(nn.Module):
             attended = K.attention(q, k, v)           # tcgen05 multi-query attention (b2_attention)
         else:
             attended = F.scaled_dot_product_attention(q, k, v, enable_gqa=shape.heads != shape.kv_heads)
+        if self.adaptive:
+            if self.o_proj.attention_output is not None and self.fused_norm:
+                projected = self.o_proj.attended(attended, x, add_residual=False)
+            else:
+                projected = self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim))
+            x, pending = self.adaptive_mlp(x, projected, attention_gate, modulations[1])
+            return x, own_kv, pending
         if self.o_proj.attention_output is not None and self.fused_norm:
             x = self.o_proj.attended(attended, x)
         else:
@@ -401,7 +487,7 @@ class Pi05ShapedPolicy(nn.Module):
             GemmaBlock(GEMMA_2B, GEMMA_2B.heads * GEMMA_2B.head_dim, config, generator, device) for _ in range(depth(GEMMA_2B))
         )
         self.expert = nn.ModuleList(
-            GemmaBlock(GEMMA_300M, GEMMA_300M.heads * GEMMA_300M.head_dim, config, generator, device)
+            GemmaBlock(GEMMA_300M, GEMMA_300M.heads * GEMMA_300M.head_dim, config, generator, device, adaptive=True)
             for _ in range(min(depth(GEMMA_300M), len(self.prefix)))
         )
         patches = (IMAGE_SIZE // PATCH) ** 2
@@ -413,7 +499,8 @@ class Pi05ShapedPolicy(nn.Module):
         self.token_embedding = rand(vocabulary, GEMMA_2B.width)
         self.action_in, self.action_out = rand(GEMMA_300M.width, ACTION_DIM), rand(ACTION_DIM, GEMMA_300M.width)
         self.time_mlp = rand(GEMMA_300M.width, GEMMA_300M.width)
-        self.final_scale = nn.Parameter(torch.ones(GEMMA_300M.width, device=device, dtype=torch.bfloat16), requires_grad=False)
+        self.final_dense = _adarms_dense(GEMMA_300M.width, generator, device)
+        self.schedules: dict = {}
         self.quantizer = B200Quantizer() if isinstance(config, (FP8Config, NVFP4Config)) and device.type == "cuda" else None
         self.device_ = device
         self.noise_seed = seed
@@ -443,26 +530,47 @@ class Pi05ShapedPolicy(nn.Module):
             cache.append(kv)
         return cache, x.shape[1]
 
+    def modulation_schedule(self, batch: int):
+        """Per Euler step, the fp32 [B, 3 width] scale | shift | gate of every AdaRMS norm of the expert (two per layer and
+        the final one), from the step's flow time: sine/cosine features -> time MLP -> SiLU -> each norm's dense.  The
+        times are fixed, so this is evaluated once per batch size and reused by every step's launches, like the
+        reference's cached schedule (policies/pi05/inference/runtime.py:366-401)."""
+        cached = self.schedules.get(batch)
+        if cached is None:
+            if torch.cuda.is_available() and self.device_.type == "cuda" and torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("Warm the modulation schedule before graph capture")
+            half = GEMMA_300M.width // 2
+            frequency = torch.exp(-math.log(10000.0) * torch.arange(half, device=self.device_) / half)
+            denses = [dense for block in self.expert for dense in (block.input_dense, block.post_dense)] + [self.final_dense]
+            rows = []
+            for step in range(DENOISE_STEPS):
+                angles = (1.0 - step / DENOISE_STEPS) * frequency
+                features = torch.cat((angles.sin(), angles.cos())).to(torch.bfloat16)
+                condition = F.silu(F.linear(features, self.time_mlp)).expand(batch, -1)
+                rows.append(tuple(dense(condition).float().contiguous() for dense in denses))
+            cached = self.schedules[batch] = tuple(rows)
+        return cached
+
     def denoise(self, cache, prefix_length: int, noise: torch.Tensor) -> torch.Tensor:
-        """``noise`` [B, 10, 32] fp32 ~ N(0, 1): ten Euler steps of the flow from t = 1 to t = 0."""
+        """``noise`` [B, 10, 32] fp32 ~ N(0, 1): ten Euler steps of the flow from t = 1 to t = 0.  The flow time reaches
+        the expert only through its AdaRMS norms."""
         actions = noise
         rope = rope_tables(prefix_length + torch.arange(ACTION_HORIZON, device=self.device_), GEMMA_300M.head_dim)
         dt = -1.0 / DENOISE_STEPS
-        half = GEMMA_300M.width // 2
-        frequency = torch.exp(-math.log(10000.0) * torch.arange(half, device=self.device_) / half)
+        schedule = self.modulation_schedule(noise.shape[0])
         # one key/value buffer per layer: the prefix rows are written once, the action rows every step
         buffers = []
         for keys, values in cache[: len(self.expert)]:
             pad = keys.new_zeros((*keys.shape[:2], ACTION_HORIZON, keys.shape[-1]))
             buffers.append((torch.cat((keys, pad), dim=2), torch.cat((values, pad), dim=2)))
         for step in range(DENOISE_STEPS):
-            time = 1.0 + step * dt
-            angles = time * frequency
-            time_embedding = F.linear(torch.cat((angles.sin(), angles.cos())).to(torch.bfloat16), self.time_mlp)
-            x = F.linear(actions.to(torch.bfloat16), self.action_in) + time_embedding
-            for block, kv in zip(self.expert, buffers):
-                x, _ = block(x, rope, kv_buffers=kv)
-            velocity = F.linear(_rms_norm(x, self.final_scale), self.action_out).float()
+            modulations = schedule[step]
+            x = F.linear(actions.to(torch.bfloat16), self.action_in)
+            pending = None
+            for index, (block, kv) in enumerate(zip(self.expert, buffers)):
+                x, _, pending = block(x, rope, kv_buffers=kv, modulations=modulations[2 * index: 2 * index + 2], pending=pending)
+            final, _ = _ada_rms_norm(_gated_residual(x, pending), modulations[-1])
+            velocity = F.linear(final, self.action_out).float()
             actions = actions + dt * velocity              # Euler step of the flow (flow.py:21-23)
         return actions
 

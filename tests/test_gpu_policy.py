@@ -135,3 +135,33 @@ def test_full_width_layer_linears_match_the_oracle(device, quantization, tower, 
                                            np.float32(bundle.weight_global_scale.item()))
         assert got.shape == want.shape, name
         assert_gemm_close(got, want)
+
+
+def test_expert_runs_on_adaptive_norms(device):
+    """The action expert's norms are AdaRMS norms: one modulation (scale | shift | gate, fp32 [B, 3 width]) per norm and
+    Euler step, from the flow time only (policies/pi05/inference/runtime.py:366-401); the calibrated route feeds them
+    to the fused norm + encoder launches (gated residual update, modulation, gate output) and stays close to the
+    tensor-operation route; the actions do depend on the modulation."""
+    from embodiinfer_b200.pi05_shaped import DENOISE_STEPS, GEMMA_300M
+    policy = Pi05ShapedPolicy("fp8", device=device, layer_scale=0.12, vocabulary=4096)
+    observations = synthetic_observations(4, vocabulary=4096)
+    schedule = policy.modulation_schedule(4)
+    assert len(schedule) == DENOISE_STEPS and len(schedule[0]) == 2 * len(policy.expert) + 1
+    assert all(m.shape == (4, 3 * GEMMA_300M.width) and m.dtype == torch.float32 for m in schedule[0])
+    assert not torch.equal(schedule[0][0], schedule[1][0]), "the modulation follows the flow time"
+    reference = policy(observations)
+    policy.calibrate_fused_mlp(observations)
+    assert all(block.adaptive and block.qkv.norm is not None for block in policy.expert)
+    fused = policy(observations)
+    assert torch.isfinite(fused).all() and torch.equal(fused, policy(observations))
+    assert float((fused - reference).norm() / reference.norm()) < 0.1
+    for block in policy.expert:
+        block.fused_norm = False
+    unfused = policy(observations)
+    assert float((fused - unfused).norm() / unfused.norm()) < 0.05
+    for block in policy.expert:
+        block.fused_norm = True
+    with torch.no_grad():
+        policy.final_dense.bias[: GEMMA_300M.width] += 0.5          # a different scale in the last norm
+    policy.schedules.clear()
+    assert float((policy(observations) - fused).norm() / fused.norm()) > 0.05
