@@ -114,11 +114,16 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
     // shared memory: [resident token tile: num_kb x 16 KB][resident token scales: num_kb x 2 KB]
     //                [stages x (token tile unless resident | weight tile)][stages x scale atoms][barriers][GELU table]
     const bool resident = args.resident != 0;
+    // A ring slot holds `kps` K atoms (128 bytes of K each): 1, or 2 / 4 for launches whose CTAs have a single tile and a
+    // long K, where the waits, the election and the commit of a slot (some 400 cycles of the MMA warp) dwarf the MMAs of one atom
+    const uint32_t kps = uint32_t(args.kps);
     const uint32_t a_stage_bytes = resident ? 0u : uint32_t(args.a_box_bytes);
-    const uint32_t stage_bytes = a_stage_bytes + uint32_t(BN) * STAGE_K_BYTES;
-    constexpr uint32_t SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;     // one operand's atoms of a K stage
-    const uint32_t token_part_bytes = resident ? 0u : SCALE_PART_BYTES;                 // offset of the feature atoms in a scale stage
-    const uint32_t scale_stage_bytes = KIND == B2_KIND_NVFP4 ? token_part_bytes + uint32_t(args.scale_blocks) * SCALE_PART_BYTES : 0;
+    const uint32_t atom_bytes = a_stage_bytes + uint32_t(BN) * STAGE_K_BYTES;            // operands of one K atom
+    const uint32_t stage_bytes = kps * atom_bytes;
+    constexpr uint32_t SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;     // one operand's atoms of a K atom
+    const uint32_t token_part_bytes = resident ? 0u : SCALE_PART_BYTES;                 // offset of the feature atoms behind the token atoms
+    const uint32_t scale_atom_bytes = KIND == B2_KIND_NVFP4 ? token_part_bytes + uint32_t(args.scale_blocks) * SCALE_PART_BYTES : 0;
+    const uint32_t scale_stage_bytes = kps * scale_atom_bytes;
     const uint32_t panel_base = base;
     const uint32_t panel_scale_base = panel_base + (resident ? uint32_t(args.num_kb) * A_TILE_BYTES : 0u);
     const uint32_t stage_base = panel_scale_base + (resident && KIND == B2_KIND_NVFP4 ? uint32_t(args.num_kb) * SCALE_PART_BYTES : 0u);
@@ -250,31 +255,39 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                         }
                 }
                 const int tail_atoms = args.scale_column_tiles - (num_kb - 1) * SCALE_ATOMS_PER_STAGE;
-                for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
+                for (int kb = walk.kb_begin; kb < walk.kb_end; kb += int(kps)) {
                     mbar_wait(empty_bar + 8 * stage, phase ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
                     __syncwarp();
                     filled |= 1u << stage;
                     fill_parity = (fill_parity & ~(1u << stage)) | (phase << stage);
                     if (elect_one()) {
                         const uint32_t bar = full_bar + 8 * stage;
-                        const uint32_t a_smem = stage_base + uint32_t(stage) * stage_bytes;
-                        const uint32_t b_smem = a_smem + a_stage_bytes;
-                        const int k0 = kb * STAGE_K_BYTES;
-                        const uint32_t copy_bytes = uint32_t(kb == num_kb - 1 ? tail_atoms : SCALE_ATOMS_PER_STAGE) * SCALE_ATOM_BYTES;
-                        mbar_expect_tx(bar, stage_bytes + (KIND == B2_KIND_NVFP4 ? uint32_t(live) * copy_bytes : 0u));
-                        if (!RESIDENT) tma_load_2d(a_smem, &act_map, bar, k0, m0);
-                        // gated: the map is three-dimensional (plane 0 = gate rows, plane 1 = up rows), one instruction
-                        // brings both halves of the tile ([gate | up] in shared memory)
-                        if (GEGLU) tma_load_3d(b_smem, &weight_map, bar, k0, f0, 0);
-                        else tma_load_2d(b_smem, &weight_map, bar, k0, f0);
-                        if (KIND == B2_KIND_NVFP4) {
-                            const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes;
-                            const int64_t offset = int64_t(kb) * (SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES);
-                            if (!RESIDENT) bulk_load(s_smem, token_scales + offset, copy_bytes, bar);
-                            if (feature_scales[0] != nullptr)
-                                bulk_load(s_smem + token_part_bytes, feature_scales[0] + offset, copy_bytes, bar);
-                            if (feature_scales[1] != nullptr)
-                                bulk_load(s_smem + token_part_bytes + SCALE_PART_BYTES, feature_scales[1] + offset, copy_bytes, bar);
+                        const int atoms = min(int(kps), walk.kb_end - kb);
+                        // bytes of the slot: full atoms, except that the last K atom of the matrix may have fewer scale atoms
+                        uint32_t bytes = uint32_t(atoms) * atom_bytes;
+                        if (KIND == B2_KIND_NVFP4)
+                            bytes += uint32_t(live) * SCALE_ATOM_BYTES *
+                                     uint32_t(atoms * SCALE_ATOMS_PER_STAGE - (kb + atoms == num_kb ? SCALE_ATOMS_PER_STAGE - tail_atoms : 0));
+                        mbar_expect_tx(bar, bytes);
+                        for (int k = 0; k < atoms; ++k) {
+                            const uint32_t a_smem = stage_base + uint32_t(stage) * stage_bytes + uint32_t(k) * atom_bytes;
+                            const uint32_t b_smem = a_smem + a_stage_bytes;
+                            const int k0 = (kb + k) * STAGE_K_BYTES;
+                            if (!RESIDENT) tma_load_2d(a_smem, &act_map, bar, k0, m0);
+                            // gated: the map is three-dimensional (plane 0 = gate rows, plane 1 = up rows), one instruction
+                            // brings both halves of the tile ([gate | up] in shared memory)
+                            if (GEGLU) tma_load_3d(b_smem, &weight_map, bar, k0, f0, 0);
+                            else tma_load_2d(b_smem, &weight_map, bar, k0, f0);
+                            if (KIND == B2_KIND_NVFP4) {
+                                const uint32_t copy_bytes = uint32_t(kb + k == num_kb - 1 ? tail_atoms : SCALE_ATOMS_PER_STAGE) * SCALE_ATOM_BYTES;
+                                const uint32_t s_smem = scale_base + uint32_t(stage) * scale_stage_bytes + uint32_t(k) * scale_atom_bytes;
+                                const int64_t offset = int64_t(kb + k) * (SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES);
+                                if (!RESIDENT) bulk_load(s_smem, token_scales + offset, copy_bytes, bar);
+                                if (feature_scales[0] != nullptr)
+                                    bulk_load(s_smem + token_part_bytes, feature_scales[0] + offset, copy_bytes, bar);
+                                if (feature_scales[1] != nullptr)
+                                    bulk_load(s_smem + token_part_bytes + SCALE_PART_BYTES, feature_scales[1] + offset, copy_bytes, bar);
+                            }
                         }
                     }
                     if (PREFETCH && pf.valid(args)) {
@@ -340,7 +353,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
             // stages ago) must have completed, which their commit to that stage's `empty` barrier reports.
             // With one set per ring stage (the usual case) no such wait is needed: the stage's `full` barrier completed
             // again only after the producer had seen the `empty` barrier of its last use.
-            const bool lag = args.scale_sets < args.stages;
+            const bool lag = args.scale_sets < args.stages * args.kps;     // the host keeps kps == 1 in that case
             int set = 0, lag_stage = 0, issued = 0;
             uint32_t lag_phase = 0;
             const uint32_t set_columns = uint32_t((RESIDENT ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
@@ -375,21 +388,15 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                 mbar_wait(acc_empty_bar + 8 * buffer, (use & 1u) ^ 1u, failed, args.status, STATUS_WAIT_MMA_TMEM);
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + uint32_t(buffer * args.accumulator_stride);
-                for (int kb = walk.kb_begin; kb < walk.kb_end; ++kb) {
+                for (int kb = walk.kb_begin; kb < walk.kb_end; kb += int(kps)) {
                     mbar_wait(full_bar + 8 * stage, phase, failed, args.status, STATUS_WAIT_MMA_FULL);
                     tc_fence_after_sync();
-                    const int mmas = kb == num_kb - 1 ? last_kb_mmas : STAGE_K_BYTES / 32;
-                    if (RESIDENT && local_tile == 0) {       // first pass over K: the token tile may still be landing
+                    if (RESIDENT && local_tile == 0) {       // first pass over K: the token tile may still be landing (one atom per slot)
                         mbar_wait(panel_bar + 8 * kb, 0u, failed, args.status, STATUS_WAIT_MMA_FULL);
                         tc_fence_after_sync();
                     }
                     const uint32_t stage_smem = stage_base + uint32_t(stage) * stage_bytes;
-                    const uint32_t a_low = operand_low + ((RESIDENT ? panel_base + uint32_t(kb) * A_TILE_BYTES : stage_smem) >> 4);
-                    const uint32_t b_low = operand_low + ((stage_smem + a_stage_bytes) >> 4);
-                    const uint32_t set_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t((lag ? set : stage) + 1);
-                    const uint32_t sfa_tmem = RESIDENT ? resident_sfa + uint32_t(kb * TMEM_SFA_COLUMNS) : set_tmem;
-                    const uint32_t sfb_tmem = RESIDENT ? set_tmem : set_tmem + TMEM_SFA_COLUMNS;
-                    if (KIND == B2_KIND_NVFP4 && lag) {
+                    if (KIND == B2_KIND_NVFP4 && lag) {      // (one atom per slot)
                         if (issued >= args.scale_sets) {
                             mbar_wait(empty_bar + 8 * lag_stage, lag_phase, failed, args.status, STATUS_WAIT_MMA_TMEM);
                             tc_fence_after_sync();
@@ -399,13 +406,22 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                     }
                     __syncwarp();
                     if (elect_one()) {
-                        // shared memory: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
-                        const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes) >> 4;
                         constexpr uint32_t ATOM = SCALE_ATOM_BYTES >> 4, PART = SCALE_ATOMS_PER_STAGE * ATOM;
-                        const uint32_t feature_low = atom_low + (RESIDENT ? 0u : PART);   // the stage holds no token atoms when they are resident
-                        const uint32_t first_accumulate = kb != walk.kb_begin;
-                        // `count` is a literal on the full-stage path; only a ragged last K stage takes the generic one.
-                        auto issue = [&](const int count) {
+                        const int atoms = min(int(kps), walk.kb_end - kb);
+                        // one K atom of the slot: `count` MMAs of 32 bytes of K each with their scale copies in front;
+                        // `count` is a literal on the full-atom path, only a ragged last K atom takes the generic one
+                        auto issue = [&](const int k, const int count) {
+                            const int atom_kb = kb + k;
+                            const uint32_t atom_smem = stage_smem + uint32_t(k) * atom_bytes;
+                            const uint32_t a_low = operand_low + ((RESIDENT ? panel_base + uint32_t(atom_kb) * A_TILE_BYTES : atom_smem) >> 4);
+                            const uint32_t b_low = operand_low + ((atom_smem + a_stage_bytes) >> 4);
+                            const uint32_t set_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - set_columns * uint32_t((lag ? set : stage * int(kps) + k) + 1);
+                            const uint32_t sfa_tmem = RESIDENT ? resident_sfa + uint32_t(atom_kb * TMEM_SFA_COLUMNS) : set_tmem;
+                            const uint32_t sfb_tmem = RESIDENT ? set_tmem : set_tmem + TMEM_SFA_COLUMNS;
+                            // shared memory per atom: [token atoms x4 | first feature block x4 | second feature block x4], 512 B each
+                            const uint32_t atom_low = (scale_base + uint32_t(stage) * scale_stage_bytes + uint32_t(k) * scale_atom_bytes) >> 4;
+                            const uint32_t feature_low = atom_low + (RESIDENT ? 0u : PART);   // no token atoms when they are resident
+                            const uint32_t first_accumulate = atom_kb != walk.kb_begin;
                             if (KIND == B2_KIND_NVFP4) {
 #pragma unroll
                                 for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {
@@ -440,9 +456,11 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
                                 }
                             }
                         };
-                        if (mmas == SCALE_ATOMS_PER_STAGE) issue(SCALE_ATOMS_PER_STAGE);
-                        else issue(mmas);
-                    tc_commit(empty_bar + 8 * stage);
+                        for (int k = 0; k < atoms; ++k) {
+                            if (kb + k == num_kb - 1 && last_kb_mmas != SCALE_ATOMS_PER_STAGE) issue(k, last_kb_mmas);
+                            else issue(k, SCALE_ATOMS_PER_STAGE);
+                        }
+                        tc_commit(empty_bar + 8 * stage);
                     }
                     __syncwarp();
                     if (KIND == B2_KIND_NVFP4 && ++set == args.scale_sets) set = 0;
@@ -693,9 +711,13 @@ static bool can_double_buffer(int kind, int tile_n, int scale_blocks = 2) {
     return 2 * tile_n <= (kind == B2_KIND_NVFP4 ? TMEM_COLUMNS - 2 * (TMEM_SFA_COLUMNS + 16 * scale_blocks) : TMEM_COLUMNS);
 }
 
-// LINEAR: 64, 128, 192 or 256 features per tile.  GEGLU: 64 or 128 features (128 or 256 columns).
-static bool tile_allowed(bool geglu, int features_per_tile) {
+// LINEAR: 64, 128, 192 or 256 features per tile, FP8 also 32.  GEGLU: 64 or 128 features (128 or 256 columns).
+// (NVFP4 stops at 64: the feature scales of a tile are read from the column of their 128-row block that the tile
+// starts in, and the block-scaled MMA takes that column only on a multiple of two -- an odd one is a misaligned
+// address.)
+static bool tile_allowed(int kind, bool geglu, int features_per_tile) {
     if (geglu) return features_per_tile == 64 || features_per_tile == 128;
+    if (features_per_tile == 32) return kind != B2_KIND_NVFP4;
     return features_per_tile == 64 || features_per_tile == 128 || features_per_tile == 192 || features_per_tile == 256;
 }
 
@@ -707,17 +729,26 @@ constexpr int MAX_SPLITS = 8;
 //   (~2.9 cycles per row, measured); a work item (tile x split) adds ~2,500 cycles of pipeline fill and epilogue,
 //   more when the accumulator is not double-buffered; a split launch adds the fix-up (partial sums through the
 //   L2, ticket, fixed-order sum).  Splits are considered only when the launch stays within one wave.
-static void choose_tile_and_splits(int kind, bool geglu, int forced_tile, int features, int m_tiles, int num_kb,
+//   A launch with a single token tile loads only the token rows it has, and with few CTAs each of them is bound by
+//   what one SM takes in (~32 bytes per cycle measured: 4 cycles per 128-byte row, not below ~130 cycles per K atom):
+//   1024 features at 64 per tile are 16 CTAs walking all of K, so such a launch may go down to 32 features per tile.
+static void choose_tile_and_splits(int kind, bool geglu, int forced_tile, int features, int tokens, int m_tiles, int num_kb,
                                    bool allow_split, int* tile_out, int* splits_out) {
     const int sms = sm_count();
     double best_cost = 0.0;
     *tile_out = 0;
     *splits_out = 1;
-    for (int tile = 256; tile >= 64; tile -= 64) {
-        if (!tile_allowed(geglu, tile) || (forced_tile > 0 && tile != forced_tile)) continue;
+    const int token_rows = (tokens + 7) / 8 * 8;
+    for (int tile = 256; tile >= 32; tile -= tile > 64 ? 64 : 32) {
+        if (!tile_allowed(kind, geglu, tile) || (forced_tile > 0 && tile != forced_tile)) continue;
+        if (tile == 32 && forced_tile != 32 && m_tiles != 1) continue;
         const int columns = geglu ? 2 * tile : tile;
         const int64_t tiles = int64_t((features + tile - 1) / tile) * m_tiles;
-        const double stage = 2.9 * (128.0 + columns);
+        double stage = 2.9 * (128.0 + columns);
+        if (m_tiles == 1) {
+            stage = 4.0 * (token_rows + columns);
+            if (stage < 130.0) stage = 130.0;
+        }
         const double fixed = 2500.0 + (can_double_buffer(kind, columns) ? 0.0 : 10.0 * columns);
         for (int splits = 1; splits <= MAX_SPLITS; ++splits) {
             if (splits > 1 && (!allow_split || tiles * splits > sms || num_kb / splits < 4 || tiles * 4 > TICKET_BYTES)) break;
@@ -837,13 +868,13 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     const bool paired = (d->flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) != 0;
     if (paired && !(geglu && nvfp4)) return B2_E_INVALID;
     if (paired && d->feature_tile != 0 && d->feature_tile != 64) return B2_E_UNSUPPORTED;
-    if (d->feature_tile > 0 && !tile_allowed(geglu, d->feature_tile)) return B2_E_UNSUPPORTED;
+    if (d->feature_tile > 0 && !tile_allowed(d->kind, geglu, d->feature_tile)) return B2_E_UNSUPPORTED;
     // K is split only into a caller-provided workspace; when the one given is too small the choice is repeated
     // without splitting
     bool allow_split = d->epilogue == B2_EPI_LINEAR && (planning || (d->workspace != nullptr && aligned16(d->workspace)));
     int feature_tile = 0, splits = 1;
     for (int attempt = 0; attempt < 2; ++attempt) {
-        choose_tile_and_splits(d->kind, geglu, paired ? 64 : d->feature_tile, d->features, args.num_m_tiles, args.num_kb,
+        choose_tile_and_splits(d->kind, geglu, paired ? 64 : d->feature_tile, d->features, d->tokens, args.num_m_tiles, args.num_kb,
                                allow_split, &feature_tile, &splits);
         if (feature_tile == 0) return B2_E_UNSUPPORTED;
         const int64_t tiles = int64_t((d->features + feature_tile - 1) / feature_tile) * args.num_m_tiles;
@@ -916,15 +947,38 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
             scale_stage_bytes = nvfp4 ? args.scale_blocks * SCALE_PART_BYTES : 0;
         }
     }
+    const int free_columns = TMEM_COLUMNS - args.accumulators * args.accumulator_stride - (args.resident ? args.num_kb * TMEM_SFA_COLUMNS : 0);
+    const int sets_available = nvfp4 ? free_columns / ((args.resident ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks) : 0;
+    // K atoms per ring slot.  A launch whose CTAs have one tile each and a long K (the expert's M = 10..80 projections:
+    // 16 CTAs walking 32 atoms) is bound by what the MMA warp spends per slot around the MMAs -- two barrier waits, the
+    // election, the commit, some 400 cycles against 70 of tensor work per atom at 64 columns -- so a slot carries four
+    // atoms (two when K is shorter), as long as three such slots fit and (NVFP4) tensor memory has a scale set per atom.
+    args.kps = 1;
+    {
+        const int grid = args.total_tiles < sm_count() ? args.total_tiles : sm_count();
+        const int ring_bytes = SMEM_LIMIT - fixed_bytes - panel_bytes;
+        if (!args.resident && splits == 1 && args.total_tiles <= grid && args.num_kb >= 8) {
+            for (int kps = args.num_kb >= 16 ? 4 : 2; kps > 1; kps /= 2) {
+                int slots = ring_bytes / (kps * (stage_bytes + scale_stage_bytes));
+                if (nvfp4 && slots > sets_available / kps) slots = sets_available / kps;
+                if (slots >= 3) {
+                    args.kps = kps;
+                    break;
+                }
+            }
+        }
+    }
+    stage_bytes *= args.kps;
+    scale_stage_bytes *= args.kps;
     int stages = (SMEM_LIMIT - fixed_bytes - panel_bytes) / (stage_bytes + scale_stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (args.kps > 1 && nvfp4 && stages > sets_available / args.kps) stages = sets_available / args.kps;
     if (stages < 2) return B2_E_UNSUPPORTED;
     args.stages = stages;
     args.scale_sets = 1;
     if (nvfp4) {
-        const int free_columns = TMEM_COLUMNS - args.accumulators * args.accumulator_stride - (args.resident ? args.num_kb * TMEM_SFA_COLUMNS : 0);
-        args.scale_sets = free_columns / ((args.resident ? 0 : TMEM_SFA_COLUMNS) + 16 * args.scale_blocks);
-        if (args.scale_sets > stages) args.scale_sets = stages;
+        args.scale_sets = sets_available;
+        if (args.scale_sets > stages * args.kps) args.scale_sets = stages * args.kps;
         if (args.scale_sets < 2) return B2_E_UNSUPPORTED;
     }
     int shared_bytes = fixed_bytes + panel_bytes + stages * (stage_bytes + scale_stage_bytes);

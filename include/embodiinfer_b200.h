@@ -140,7 +140,7 @@ typedef struct b2_linear_desc {
     int32_t tokens;      /* M: rows of the activation matrix */
     int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
     int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */
-    int32_t feature_tile; /* output features per tile: 0 = choose; LINEAR 64/128/192/256, GEGLU 64/128 */
+    int32_t feature_tile; /* output features per tile: 0 = choose; LINEAR 64/128/192/256 (FP8 also 32), GEGLU 64/128 */
     int32_t gelu_lo;      /* GEGLU: range of bf16 magnitude codes from b2_gelu_table_range, or 0, 0 */
     int32_t gelu_hi;
     const void* act;           /* e4m3 [M, K] or packed e2m1 [M, K/2] */

@@ -52,6 +52,10 @@ LINEAR_CASES = [
     (32, 128, 128, 64), (200, 256, 1024, 64), (10, 2560, 1024, 0), (80, 1024, 2048, 0), (640, 4096, 1024, 0),
     (560, 2048, 2048, 0), (560, 2048, 2048, 64), (560, 2048, 2048, 128), (560, 2048, 2048, 192), (560, 2048, 2048, 256),
     (1, 64, 64, 0), (17, 72, 192, 0), (129, 200, 320, 0), (559, 1152, 1152, 0), (561, 1024, 2048, 0),
+    # one tile per CTA and a long K: several K atoms per ring slot, with a short last slot and a ragged last atom
+    (10, 1024, 4096, 0), (100, 256, 1152, 0), (64, 128, 2304, 0), (50, 192, 2240, 0), (128, 64, 8192, 0),
+    # 32 features per tile: every 32-row quarter of a 128-row feature-scale block, a ragged last tile, two token tiles
+    (10, 160, 256, 32), (70, 96, 512, 32), (200, 256, 1024, 32), (24, 200, 2048, 32), (80, 1024, 4096, 0),
 ]
 
 
@@ -61,8 +65,13 @@ def test_linear_matches_oracle(device, kind, tokens, features, width, tile):
     host, dev = operands(kind, tokens, features, width, tokens + features, device)
     status = torch.zeros(1, device=device, dtype=torch.int32)
     out = torch.full((tokens + 1, features), float("nan"), device=device, dtype=torch.bfloat16)
-    K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out[:tokens],
-             status=status, feature_tile=tile, **dev)
+    call = dict(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width, out=out[:tokens],
+                status=status, feature_tile=tile, **dev)
+    if kind == "nvfp4" and tile == 32:        # 32-feature tiles are FP8 only
+        with pytest.raises(RuntimeError, match="error -2"):
+            K.linear(**call)
+        return
+    K.linear(**call)
     torch.cuda.synchronize()
     assert status.item() == 0
     assert torch.isnan(out[tokens]).all(), "wrote past the last token row"
