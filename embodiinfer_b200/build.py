@@ -15,7 +15,7 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 SOURCE_DIR = PACKAGE_DIR / "csrc"
 LIBRARY_PATH = PACKAGE_DIR / "libembodiinfer_b200.so"
-SOURCES = ("api.cu", "quantize.cu", "geglu.cu", "gemm.cu", "gemm_pair.cu", "static_scratch.cu", "rope.cu", "norm.cu", "frames.cu", "attention.cu")
+SOURCES = ("api.cu", "quantize.cu", "geglu.cu", "gemm.cu", "gemm_pair.cu", "gemm_skinny.cu", "static_scratch.cu", "rope.cu", "norm.cu", "frames.cu", "attention.cu")
 ARCH_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a")
 
 

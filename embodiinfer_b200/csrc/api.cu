@@ -117,6 +117,13 @@ int b2_gelu_table_range(const void* host_table, int32_t* lo, int32_t* hi) {
     constexpr int MARGIN_ABOVE = 512;
     const int raised = high + MARGIN_ABOVE < last ? high + MARGIN_ABOVE : last;
     if (raised - low <= 4096) high = raised;
+    // Both ends on a multiple of eight codes (16 bytes) when that still fits: a kernel can then bring each half of the
+    // range into shared memory with one bulk copy instead of a load per entry.
+    const int low8 = low & ~7, high8 = (high + 7) & ~7;
+    if (low8 >= first && high8 <= last && high8 - low8 <= 4096) {
+        low = low8;
+        high = high8;
+    }
     *lo = low;
     *hi = high;
     return B2_OK;

@@ -159,13 +159,7 @@ linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant
         tmem_alloc(tmem_slot, TMEM_COLUMNS);
         tmem_relinquish();
     }
-    if (USES_TABLE) {
-        const int span = args.gelu_hi - args.gelu_lo;
-        for (int i = threadIdx.x; i < 2 * span; i += gemm_threads(EPI)) {
-            const int code = i < span ? args.gelu_lo + i : 0x8000 + args.gelu_lo + (i - span);
-            asm volatile("st.shared.u16 [%0], %1;" ::"r"(compact_table + 2u * uint32_t(i)), "h"(__ldg(args.gelu_table + code)) : "memory");
-        }
-    }
+    if (USES_TABLE) fill_compact_gelu(args, compact_table, int(threadIdx.x), gemm_threads(EPI));
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -673,7 +667,7 @@ bool make_operand_map(CUtensorMap* map, const void* pointer, int64_t rows, int64
 
 // The packed [gate; up] weight ([2 * features, row_bytes]) as [2 planes][features][row_bytes]: one box of
 // box_rows x 128 bytes x 2 planes lands as [gate rows | up rows].
-static bool make_gated_map(CUtensorMap* map, const void* pointer, int64_t features, int64_t row_bytes, int box_rows) {
+bool make_gated_map(CUtensorMap* map, const void* pointer, int64_t features, int64_t row_bytes, int box_rows) {
     EncodeTiledFn encode = encode_tiled_entry();
     if (encode == nullptr) return false;
     const cuuint64_t dims[3] = {cuuint64_t(row_bytes), cuuint64_t(features), 2};
@@ -856,6 +850,18 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
                 return B2_OK;
             }
             return run_linear_pair(d, epilogue, plan, stream);
+        }
+    }
+
+    // At most 128 tokens: the weight becomes the "A" operand and a cluster shares the K of a feature tile (gemm_skinny.cu).
+    {
+        const SkinnyPlan plan = skinny_plan(d, geglu);
+        if (plan.splits != 0) {
+            if (planning) {
+                *workspace_need = 0;
+                return B2_OK;
+            }
+            return run_linear_skinny(d, epilogue, plan, stream);
         }
     }
 

@@ -125,6 +125,27 @@ __device__ __forceinline__ uint32_t gelu_lookup_general(uint32_t code, const Ker
     return uint32_t(__ldg(args.gelu_table + code));
 }
 
+// Fills the shared-memory copy of the GELU table ([positive | negative] halves of magnitude codes [lo, hi)) with `threads`
+// threads, this one being number `thread`.  Eight loads are issued before the first store: one load per store would
+// pay the L2 latency once per entry (the stores are volatile, nothing moves across them).
+__device__ __forceinline__ void fill_compact_gelu(const KernelArgs& args, uint32_t compact_table, int thread, int threads) {
+    const int span = args.gelu_hi - args.gelu_lo, total = 2 * span;
+    for (int first = thread; first < total; first += 8 * threads) {
+        uint16_t value[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = first + j * threads;
+            value[j] = 0;
+            if (i < total) value[j] = __ldg(args.gelu_table + (i < span ? args.gelu_lo + i : 0x8000 + args.gelu_lo + (i - span)));
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = first + j * threads;
+            if (i < total) asm volatile("st.shared.u16 [%0], %1;" ::"r"(compact_table + 2u * uint32_t(i)), "h"(value[j]) : "memory");
+        }
+    }
+}
+
 // The sixteen gates of one unit as eight bf16x2 words -> their GELUs as eight bf16x2 words.  One test per
 // unit (two adds per word: a magnitude m is >= lo iff m + (0x8000 - lo) carries into bit 15, and < hi iff
 // m + (0x8000 - hi) does not) picks between straight-line shared-memory lookups and the general path.
@@ -389,6 +410,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn encode_tiled_entry();
 bool make_operand_map(CUtensorMap* map, const void* pointer, int64_t rows, int64_t row_bytes, int box_rows);
+bool make_gated_map(CUtensorMap* map, const void* pointer, int64_t features, int64_t row_bytes, int box_rows);
 
 // Paired schedule (gemm_pair.cu): what it would do with a launch (0 columns = it does not apply), and the launch.
 struct PairPlan {
@@ -399,5 +421,17 @@ struct PairPlan {
 };
 PairPlan pair_plan(const b2_linear_desc* d, bool geglu, bool split_allowed);
 int run_linear_pair(const b2_linear_desc* d, int epilogue, const PairPlan& plan, cudaStream_t stream);
+
+// Cluster schedule for at most 128 tokens (gemm_skinny.cu): what it would do with a launch (0 splits = it does not apply).
+struct SkinnyPlan {
+    int splits = 0;              // CTAs of a cluster = K ranges of a feature tile; 0 = the schedule does not apply
+    int columns = 0;             // accumulator columns: tokens rounded up to 16
+    int atoms = 0;               // K atoms (128 bytes of K) of the longest K range
+    int tokens_per_rank = 0;     // tokens whose epilogue a CTA of the cluster runs
+    int shared_bytes = 0;
+    int gelu_span = 0;           // magnitude codes of the GELU table kept in shared memory
+};
+SkinnyPlan skinny_plan(const b2_linear_desc* d, bool geglu);
+int run_linear_skinny(const b2_linear_desc* d, int epilogue, const SkinnyPlan& plan, cudaStream_t stream);
 
 }  // namespace b2

@@ -238,11 +238,7 @@ pair_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_con
     // constant of the model, so this may run ahead of the launches before this one) and meet at their own barrier,
     // while the producer and the MMA warp are already at work.
     if (USES_TABLE && warp >= FIRST_EPILOGUE_WARP) {
-        const int span = args.gelu_hi - args.gelu_lo;
-        for (int i = int(threadIdx.x) - 32 * FIRST_EPILOGUE_WARP; i < 2 * span; i += 32 * epilogue_warps(EPI)) {
-            const int code = i < span ? args.gelu_lo + i : 0x8000 + args.gelu_lo + (i - span);
-            asm volatile("st.shared.u16 [%0], %1;" ::"r"(compact_table + 2u * uint32_t(i)), "h"(__ldg(args.gelu_table + code)) : "memory");
-        }
+        fill_compact_gelu(args, compact_table, int(threadIdx.x) - 32 * FIRST_EPILOGUE_WARP, 32 * epilogue_warps(EPI));
         asm volatile("bar.sync 1, %0;" ::"r"(32 * epilogue_warps(EPI)) : "memory");
     }
 

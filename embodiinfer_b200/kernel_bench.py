@@ -215,7 +215,7 @@ LINEAR_SHAPES = [
     ("prefix_mb16_down_nvfp4_8960x2048x16384", "nvfp4", 8960, 2048, 16384, "linear"),
 ] + [
     (f"expert_B{batch}_{name}_{kind}_{10 * batch}x{n}x{k}", kind, 10 * batch, n, k, epilogue)
-    for batch in (1, 8, 64) for kind in ("fp8", "nvfp4")
+    for batch in (1, 2, 4, 8, 12, 64) for kind in ("fp8", "nvfp4")
     for name, n, k, epilogue in (("qkv", 2560, 1024, "linear"), ("o", 1024, 2048, "linear"),
                                  ("gate_up_geglu", 4096, 1024, "geglu"), ("down", 1024, 4096, "linear"))
 ]

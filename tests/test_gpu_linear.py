@@ -56,6 +56,10 @@ LINEAR_CASES = [
     (10, 1024, 4096, 0), (100, 256, 1152, 0), (64, 128, 2304, 0), (50, 192, 2240, 0), (128, 64, 8192, 0),
     # 32 features per tile: every 32-row quarter of a 128-row feature-scale block, a ragged last tile, two token tiles
     (10, 160, 256, 32), (70, 96, 512, 32), (200, 256, 1024, 32), (24, 200, 2048, 32), (80, 1024, 4096, 0),
+    # cluster schedule: 1 .. 128 tokens, every cluster size (8 / 4 / 2 / 1 by the number of feature tiles and K atoms),
+    # K ranges of unequal length, a ragged last K atom, features that end inside a tile, more tiles than one wave
+    (5, 128, 128, 0), (16, 128, 256, 0), (33, 256, 640, 0), (128, 1024, 4096, 0), (127, 2176, 1024, 0), (9, 4352, 1152, 0),
+    (3, 9600, 512, 0), (48, 20480, 256, 0), (96, 1032, 3392, 0), (2, 136, 16384, 0),
 ]
 
 
@@ -71,15 +75,20 @@ def test_linear_matches_oracle(device, kind, tokens, features, width, tile):
         with pytest.raises(RuntimeError, match="error -2"):
             K.linear(**call)
         return
-    K.linear(**call)
-    torch.cuda.synchronize()
-    assert status.item() == 0
-    assert torch.isnan(out[tokens]).all(), "wrote past the last token row"
     if kind == "fp8":
         want = O.fp8_linear(host["a"], host["a_s"], host["w"], host["w_s"])
     else:
         want = O.nvfp4_linear_plan(host["a"], host["a_sl"], host["a_s"], host["w"], host["w_sl"], host["w_s"])
-    assert_gemm_close(bits(out[:tokens]), want)
+    # up to 128 tokens with no tile asked for: the cluster schedule (weights as the MMA's "A" operand); the flag keeps
+    # such a launch on the tile schedule, whose single-tile paths these cases also cover
+    schedules = (0, N.LINEAR_SINGLE_CTA) if tokens <= 128 and tile == 0 else (0,)
+    for flags in schedules:
+        out.fill_(float("nan"))
+        K.linear(flags=flags, **call)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        assert torch.isnan(out[tokens]).all(), "wrote past the last token row"
+        assert_gemm_close(bits(out[:tokens]), want)
 
 
 @pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
@@ -518,8 +527,9 @@ def test_compact_gelu_table_matches_full_table(device, std):
     table_host = gelu_table_cpu("tanh")
     table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
     table_range = K.gelu_table_range(table)
-    # the closed forms hold outside [0x3B4B, 0x40A2); lo comes back ten binades lower, hi four binades higher
-    assert table_range == (0x3B4B - 1280, 0x40A2 + 512)
+    # the closed forms hold outside [0x3B4B, 0x40A2); lo comes back ten binades lower, hi four binades higher, both on a
+    # multiple of eight codes
+    assert table_range == ((0x3B4B - 1280) & ~7, (0x40A2 + 512 + 7) & ~7)
     scalar = lambda v: torch.tensor(float(v), device=device)
     common = dict(kind=N.KIND_FP8, epilogue=N.EPI_GEGLU, out_format=N.OUT_BF16, tokens=tokens, features=features, width=width,
                   act=torch.from_numpy(aq).to(device), act_scale=scalar(a_s), weight=torch.from_numpy(wq).to(device),
