@@ -23,11 +23,12 @@ LINEAR_PAIRED_GATE_UP_SCALES = 4
 LINEAR_STREAM_TOKENS = 8
 LINEAR_SINGLE_CTA = 64
 LINEAR_PAIRS = 128
+LINEAR_CLUSTER = 256
 NORM_RESIDUAL_EVICT_LAST = 1
 SCALE_SCRATCH_BYTES = 8
 STATIC_SCRATCH_BYTES = 16640
 STATIC_SCALE_MAX_COUNT = 67108864
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 _ERRORS = {
     E_INVALID: "invalid argument (null, non-positive size or misaligned pointer)",

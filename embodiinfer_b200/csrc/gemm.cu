@@ -799,7 +799,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     if (d->epilogue != B2_EPI_LINEAR && d->epilogue != B2_EPI_GEGLU && d->epilogue != B2_EPI_GELU) return B2_E_UNSUPPORTED;
     if (d->tokens <= 0 || d->features <= 0 || d->width <= 0) return B2_E_INVALID;
     constexpr int KNOWN_FLAGS = B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS |
-                                B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRS | B2_GEGLU_TRUE_DIV;
+                                B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRS | B2_LINEAR_CLUSTER | B2_GEGLU_TRUE_DIV;
     if (d->flags & ~KNOWN_FLAGS) return B2_E_INVALID;
     if (!planning) {
         if (d->act == nullptr || d->weight == nullptr || d->act_scale == nullptr || d->weight_scale == nullptr ||

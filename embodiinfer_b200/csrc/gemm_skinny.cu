@@ -388,6 +388,13 @@ static int skinny_cluster(int tiles, int num_kb) {
     return 1;
 }
 
+// Whether this schedule applies to a launch, and whether it is the faster one.  Both times were measured on the action
+// expert's projections (FP8 and NVFP4; 10 .. 120 tokens; 1024 .. 4096 features; K = 1024 .. 4096) and follow
+//   tile schedule    ~ fixed + a per 128 elements of K  (one CTA walks all of K of its tile: a ~ 150 ns, gated ~ 270 ns)
+//   cluster schedule ~ fixed + 200 ns per K atom of a CTA + 26 ns per token (staging, exchange and epilogue grow with
+//                      the tokens; the K of a CTA shrinks with the cluster size)
+// with the cluster schedule's fixed part 140 ns (FP8) / 460 ns (NVFP4) below the tile schedule's.  B2_LINEAR_CLUSTER skips
+// the comparison.
 SkinnyPlan skinny_plan(const b2_linear_desc* d, bool geglu) {
     SkinnyPlan plan;
     if (d->tokens > SKINNY_MAX_TOKENS || d->feature_tile != 0) return plan;
@@ -410,6 +417,12 @@ SkinnyPlan skinny_plan(const b2_linear_desc* d, bool geglu) {
         const int64_t bytes = 1024 + (operand_bytes > staging_bytes ? operand_bytes : staging_bytes) +
                               int64_t(splits) * tokens_per_rank * SKINNY_ROW_FLOATS * 4 + 8 * MAX_STAGES + 64 + 4 * span;
         if (atoms <= MAX_STAGES && bytes <= SMEM_LIMIT && (!nvfp4 || columns + 32 * atoms <= TMEM_COLUMNS)) {
+            if (!(d->flags & B2_LINEAR_CLUSTER)) {
+                const int64_t waves = (int64_t(tiles) * splits + sm_count() - 1) / sm_count();
+                const int64_t tile_ns = (nvfp4 ? 460 : 140) + int64_t(geglu ? 270 : 150) * (d->width / 128);
+                const int64_t cluster_ns = waves * (200 * int64_t(atoms) + 26 * int64_t(d->tokens));
+                if (cluster_ns >= tile_ns) return plan;
+            }
             plan.splits = splits;
             plan.columns = columns;
             plan.atoms = atoms;

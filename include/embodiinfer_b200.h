@@ -21,11 +21,15 @@
 extern "C" {
 #endif
 
-/* 4: launches with more than 128 tokens run on pairs of SMs (B2_LINEAR_SINGLE_CTA opts out); unknown flag bits in
+/* 6: launches of at most 128 tokens may run on the cluster schedule (weights as the MMA's "A" operand, K split across a
+ * thread-block cluster; B2_LINEAR_CLUSTER asks for it whenever it applies, B2_LINEAR_SINGLE_CTA opts out);
+ * b2_gelu_table_range returns ranges on multiples of eight codes; FP8 launches accept 32 features per tile.
+ * 5: b2_attention.
+ * 4: launches with more than 128 tokens run on pairs of SMs (B2_LINEAR_SINGLE_CTA opts out); unknown flag bits in
  * b2_linear_desc are rejected; the opt-in cluster split of K of version 3 (flag value 32) is gone.
  * 3: added the producers in front of the GEMMs (b2_norm_quant, b2_layer_norm_quant, b2_bhsd_quant, b2_normalize_frames,
  * b2_frames_to_patches, b2_resize_frames). */
-#define B2_ABI_VERSION 5
+#define B2_ABI_VERSION 6
 
 /* ---- status codes ---------------------------------------------------------- */
 #define B2_OK 0
@@ -131,12 +135,19 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
                                   The accumulation order along K is the same in both schedules: results are identical either way. */
 #define B2_LINEAR_PAIRS 128 /* tuning / test aid: use the paired schedule whenever it applies (more than 128 tokens, no split K,
                                bundle-order scale layout), whatever the padding */
+#define B2_LINEAR_CLUSTER 256 /* tuning / test aid: use the cluster schedule whenever it applies (at most 128 tokens, no feature
+                                 tile asked for; gated NVFP4 only with B2_LINEAR_PAIRED_GATE_UP_SCALES).  There the 128 rows of the
+                                 MMA's "A" operand are 128 features (64 gate + 64 up), the tokens are its columns, and the K of a
+                                 feature tile is cut across the 1, 2, 4 or 8 CTAs of a thread-block cluster, which exchange fp32
+                                 partial sums through distributed shared memory and add them in a fixed order.  The library picks
+                                 it by an estimate of both schedules' times (few tokens, long K); B2_LINEAR_SINGLE_CTA opts out.
+                                 K is summed in a different order than in the tile schedules: results agree to fp32 rounding. */
 
 typedef struct b2_linear_desc {
     int32_t kind;        /* B2_KIND_* */
     int32_t epilogue;    /* B2_EPI_* */
     int32_t out_format;  /* B2_OUT_* */
-    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRS | B2_GEGLU_TRUE_DIV; any other bit: B2_E_INVALID */
+    int32_t flags;       /* B2_LINEAR_ROUND_SCALE_BF16 | B2_LINEAR_PAIRED_GATE_UP_SCALES | B2_LINEAR_STREAM_TOKENS | B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRS | B2_LINEAR_CLUSTER | B2_GEGLU_TRUE_DIV; any other bit: B2_E_INVALID */
     int32_t tokens;      /* M: rows of the activation matrix */
     int32_t features;    /* N: output width (GEGLU: the weight has 2*features rows, gate first) */
     int32_t width;       /* K: inner dimension; K % 16 == 0 (FP8), K % 64 == 0 (NVFP4) */

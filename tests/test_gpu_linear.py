@@ -79,9 +79,9 @@ def test_linear_matches_oracle(device, kind, tokens, features, width, tile):
         want = O.fp8_linear(host["a"], host["a_s"], host["w"], host["w_s"])
     else:
         want = O.nvfp4_linear_plan(host["a"], host["a_sl"], host["a_s"], host["w"], host["w_sl"], host["w_s"])
-    # up to 128 tokens with no tile asked for: the cluster schedule (weights as the MMA's "A" operand); the flag keeps
-    # such a launch on the tile schedule, whose single-tile paths these cases also cover
-    schedules = (0, N.LINEAR_SINGLE_CTA) if tokens <= 128 and tile == 0 else (0,)
+    # up to 128 tokens with no tile asked for: the library's own choice, the cluster schedule (weights as the MMA's "A"
+    # operand) and the tile schedule, whose single-tile paths these cases also cover
+    schedules = (0, N.LINEAR_CLUSTER, N.LINEAR_SINGLE_CTA) if tokens <= 128 and tile == 0 else (0,)
     for flags in schedules:
         out.fill_(float("nan"))
         K.linear(flags=flags, **call)
@@ -154,6 +154,73 @@ def test_gated_epilogues(device, kind, tokens, features, width, tile):
              out_scale=torch.tensor(float(scale4), device=device), **common)
     want4 = O.nvfp4_quantize_C(got_hidden, scale4)
     assert np.array_equal(u8(out4), want4[0]) and np.array_equal(u8(linear), want4[1]) and np.array_equal(u8(blocked), want4[2])
+
+
+@pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
+@pytest.mark.parametrize("tokens,features,width", [(10, 4096, 1024), (37, 384, 1536), (128, 256, 4096), (3, 128, 64)])
+def test_cluster_schedule_epilogues(device, kind, tokens, features, width):
+    """B2_LINEAR_CLUSTER: the weights are the MMA's "A" operand and a thread-block cluster shares the K of a feature tile.
+    Its partial sums meet in a fixed order, so a launch repeats its bits; against the oracle it is held to the GEMM
+    tolerance, and the encoded outputs must be exactly the encodings of its own bf16 hidden.  Gated NVFP4 takes the
+    paired gate / up scale layout there."""
+    host, dev = operands(kind, tokens, 2 * features, width, 31 + tokens, device)
+    table_host = gelu_table_cpu("tanh")
+    table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+    flags = N.LINEAR_CLUSTER
+    if kind == "nvfp4":
+        scales = host["w_sl"]
+        blocks = scales.shape[1]
+        paired = np.stack((scales[:features].reshape(features // 64, 64, blocks),
+                           scales[features:].reshape(features // 64, 64, blocks)), axis=1).reshape(2 * features, blocks)
+        dev = {**dev, "weight_scales": torch.from_numpy(O.swizzle_scales(paired)).to(device)}
+        flags |= N.LINEAR_PAIRED_GATE_UP_SCALES
+    status = torch.zeros(1, device=device, dtype=torch.int32)
+    for table_range in (K.gelu_table_range(table), (0x3B4B - 1277, 0x40A2 + 3), (0, 0)):     # bulk-copied, entry by entry, none
+        common = dict(epilogue=N.EPI_GEGLU, tokens=tokens, features=features, width=width, gelu_table=table, gelu_range=table_range,
+                      status=status, **dev)
+        hidden = torch.empty((tokens + 1, features), device=device, dtype=torch.bfloat16).fill_(float("nan"))
+        K.linear(out_format=N.OUT_BF16, out=hidden[:tokens], flags=flags, **common)
+        again = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+        K.linear(out_format=N.OUT_BF16, out=again, flags=flags, **common)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        assert torch.isnan(hidden[tokens]).all(), "wrote past the last token row"
+        assert np.array_equal(bits(hidden[:tokens]), bits(again))
+        y = O.f32_to_bf16((accumulate(kind, host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+        assert_gemm_close(bits(hidden[:tokens]), O.gelu_mul(y[:, :features], y[:, features:], table_host))
+    got_hidden = bits(hidden[:tokens])
+    peak = float(np.abs(O.bf16_to_f32(got_hidden)).max())
+    scale8 = np.float32(peak / 448.0)
+    out8 = torch.empty((tokens, features), device=device, dtype=torch.uint8)
+    K.linear(out_format=N.OUT_FP8, out=out8, out_scale=torch.tensor(float(scale8), device=device), flags=flags | N.GEGLU_TRUE_DIV, **common)
+    assert np.array_equal(u8(out8), O.fp8_quantize_C(got_hidden, scale8)[0])
+    scale4 = np.float32(peak / (448.0 * 6.0))
+    out4 = torch.empty((tokens, features // 2), device=device, dtype=torch.uint8)
+    linear = torch.empty((tokens, features // 16), device=device, dtype=torch.uint8)
+    blocked = torch.zeros(blocked_scale_bytes(tokens, features), device=device, dtype=torch.uint8)
+    K.linear(out_format=N.OUT_NVFP4, out=out4, out_scales=linear, out_blocked=blocked,
+             out_scale=torch.tensor(float(scale4), device=device), flags=flags, **common)
+    want4 = O.nvfp4_quantize_C(got_hidden, scale4)
+    assert np.array_equal(u8(out4), want4[0]) and np.array_equal(u8(linear), want4[1]) and np.array_equal(u8(blocked), want4[2])
+    assert status.item() == 0
+    # plain epilogue with bias and residual, and the GELU epilogue (bias + table), on the first `features` weight rows
+    bias = make_weight((1, features), 3, std=0.1).to(torch.bfloat16).reshape(-1)
+    residual = make_input((tokens, features), 4, outliers=False)
+    plain_dev = {**dev, "weight": dev["weight"][:features].contiguous()}
+    if kind == "nvfp4":
+        plain_dev["weight_scales"] = torch.from_numpy(O.swizzle_scales(host["w_sl"][:features])).to(device)
+    y = y[:, :features]
+    with_bias = O.f32_to_bf16(O.bf16_to_f32(y) + O.bf16_to_f32(bits(bias))[None, :])
+    out = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+    shape = dict(tokens=tokens, features=features, width=width, status=status)
+    K.linear(epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, out=out, bias=bias.to(device), residual=residual.to(device),
+             flags=N.LINEAR_CLUSTER, **shape, **plain_dev)
+    assert_gemm_close(bits(out), O.f32_to_bf16(O.bf16_to_f32(with_bias) + O.bf16_to_f32(bits(residual))))
+    K.linear(epilogue=N.EPI_GELU, out_format=N.OUT_BF16, out=out, bias=bias.to(device), gelu_table=table,
+             gelu_range=K.gelu_table_range(table), flags=N.LINEAR_CLUSTER, **shape, **plain_dev)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert_gemm_close(bits(out), table_host[with_bias])
 
 
 @pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
