@@ -20,6 +20,15 @@
 //               second MMA reads, rescaling of the output accumulator when the reference moved, final 1/sum and store
 // S is double-buffered, so the scores of the next key tile are computed while this one's probabilities are formed.
 // Every wait is bounded and reports through the status word, as in the GEMM kernels.
+//
+// Few rows (one observation's ten-token chunk is 80 rows: a single CTA walking all ten key tiles): the keys are cut
+// across the CTAs of a thread-block cluster instead (SPLIT).  Every CTA runs the loop above on its own key tiles and
+// ends with an unnormalised output, a reference m and a sum l per row; the rows are dealt to the CTAs in runs of T, each
+// CTA sends every other CTA the rows that one owns ([256 outputs | m | l] fp32, one bulk copy per owner through
+// distributed shared memory) and the owner combines them in rank order:
+//   out = sum_r 2^(m_r - M) O_r / sum_r 2^(m_r - M) l_r,   M = max_r m_r.
+// The exchange buffers lie over the query / key / value stages, which are dead by then in every CTA of the cluster: a
+// hardware cluster barrier separates the two uses.
 #include "gemm_epilogue.cuh"
 
 #include <cuda.h>
@@ -41,6 +50,29 @@ constexpr uint32_t P_BYTES = ATT_ROWS * ATT_ATOM_BYTES;       // 16 KB: 128 rows
 constexpr int ATT_THREADS = 32 * 6;
 constexpr int ATT_SHARED_BYTES = 1024 + int(Q_BYTES + 4 * KV_STAGE_BYTES + 2 * P_BYTES) + 256;
 constexpr uint32_t TMEM_S = 0, TMEM_O = 128;     // two score buffers of 64 columns, then 256 output columns
+constexpr uint32_t SPLIT_ROW_FLOATS = 260;       // 256 outputs, reference, sum, 2 of padding: rows start 4 banks apart
+constexpr uint32_t SPLIT_ROW_BYTES = SPLIT_ROW_FLOATS * 4;
+constexpr int SPLIT_MAX_CLUSTER = 8;
+constexpr unsigned int STATUS_WAIT_ATTENTION_EXCHANGE = 0x108;    // a CTA gave up waiting for the partial rows of its cluster
+
+__device__ __forceinline__ bool mbar_try_wait_cluster_scope(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+__device__ __forceinline__ void bulk_copy_rows_to_cluster(uint32_t dst, uint32_t src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "r"(src), "r"(bytes), "r"(bar) : "memory");
+}
 
 // Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, A K-major, B K-major or MN-major.
 __device__ __forceinline__ uint32_t idesc_bf16(uint32_t m, uint32_t n, bool b_mn_major) {
@@ -103,8 +135,11 @@ struct AttentionArgs {
     int keys;                    // keys (= values) per batch element
     int tiles_per_batch;
     float scale_log2;            // log2(e) / sqrt(256)
+    int splits;                  // SPLIT: CTAs of a cluster = key ranges of one 128-row tile
+    int rows_per_rank;           // SPLIT: rows whose partial results a CTA combines (T)
 };
 
+template <bool SPLIT>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                  const __grid_constant__ CUtensorMap v_map, const AttentionArgs args) {
@@ -121,13 +156,25 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     const uint32_t s_full = bars + 72, s_free = bars + 88, p_ready = bars + 104, p_free = bars + 120;    // [2] each
     const uint32_t o_done = bars + 136;
     const uint32_t tmem_slot = bars + 144;
+    const uint32_t receive_bar = bars + 152;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int batch = int(blockIdx.x) / args.tiles_per_batch;
-    const int tile = int(blockIdx.x) - batch * args.tiles_per_batch;
+    const uint32_t splits = SPLIT ? uint32_t(args.splits) : 1u;
+    const uint32_t rank = SPLIT ? cluster_cta_rank() : 0u;
+    const int work = SPLIT ? int(blockIdx.x) / args.splits : int(blockIdx.x);
+    const int batch = work / args.tiles_per_batch;
+    const int tile = work - batch * args.tiles_per_batch;
     const int row0 = tile * ATT_ROWS;                                   // within the batch element
-    const int num_key_tiles = (args.keys + ATT_KEYS - 1) / ATT_KEYS;
+    const int all_key_tiles = (args.keys + ATT_KEYS - 1) / ATT_KEYS;
+    const int first_key_tile = SPLIT ? int(rank) * all_key_tiles / args.splits : 0;
+    const int num_key_tiles = SPLIT ? (int(rank) + 1) * all_key_tiles / args.splits - first_key_tile : all_key_tiles;   // of this CTA (>= 1)
+    // SPLIT: rows of the tile that exist, and the exchange buffers over the dead operand stages
+    int tile_rows = args.rows_per_batch - row0;
+    if (tile_rows > ATT_ROWS) tile_rows = ATT_ROWS;
+    const uint32_t staging = base;
+    const uint32_t receive_base = staging + uint32_t(tile_rows) * SPLIT_ROW_BYTES;
+    const uint32_t weight_table = receive_base + splits * uint32_t(args.rows_per_rank) * SPLIT_ROW_BYTES;     // [T][S] floats
 
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&q_map);
@@ -145,7 +192,13 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             mbar_init(p_free + 8 * i, 1);
         }
         mbar_init(o_done, 1);
+        if (SPLIT) mbar_init(receive_bar, 1);
         fence_barrier_init();
+        if (SPLIT) {      // the bytes this CTA will receive: a partial row from every CTA for each row it owns
+            int owned = tile_rows - int(rank) * args.rows_per_rank;
+            owned = owned < 0 ? 0 : (owned > args.rows_per_rank ? args.rows_per_rank : owned);
+            mbar_expect_tx(receive_bar, splits * uint32_t(owned) * SPLIT_ROW_BYTES);
+        }
     }
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLUMNS);
@@ -176,7 +229,7 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             if (elect_one()) {
                 mbar_expect_tx(k_full + 8 * b, KV_STAGE_BYTES);
                 for (int a = 0; a < ATT_D_ATOMS; ++a)
-                    tma_load_2d(k_smem + b * KV_STAGE_BYTES + a * KV_ATOM_BYTES, &k_map, k_full + 8 * b, a * ATT_ATOM_BYTES, kv_row + j * ATT_KEYS);
+                    tma_load_2d(k_smem + b * KV_STAGE_BYTES + a * KV_ATOM_BYTES, &k_map, k_full + 8 * b, a * ATT_ATOM_BYTES, kv_row + (first_key_tile + j) * ATT_KEYS);
             }
             __syncwarp();
             mbar_wait(v_empty + 8 * b, parity ^ 1u, failed, args.status, STATUS_WAIT_PRODUCER);
@@ -184,7 +237,7 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             if (elect_one()) {
                 mbar_expect_tx(v_full + 8 * b, KV_STAGE_BYTES);
                 for (int a = 0; a < ATT_D_ATOMS; ++a)
-                    tma_load_2d(v_smem + b * KV_STAGE_BYTES + a * KV_ATOM_BYTES, &v_map, v_full + 8 * b, a * ATT_ATOM_BYTES, kv_row + j * ATT_KEYS);
+                    tma_load_2d(v_smem + b * KV_STAGE_BYTES + a * KV_ATOM_BYTES, &v_map, v_full + 8 * b, a * ATT_ATOM_BYTES, kv_row + (first_key_tile + j) * ATT_KEYS);
             }
             __syncwarp();
         }
@@ -197,6 +250,10 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             mbar_wait(k_full + 8 * b, uint32_t(last >> 1) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
             mbar_wait(v_full + 8 * b, uint32_t(last >> 1) & 1u, drain_failed, args.status, STATUS_WAIT_DRAIN);
         }
+        if (SPLIT) {
+            cluster_arrive();
+            cluster_wait();
+        }
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
         const uint32_t idesc_scores = idesc_bf16(ATT_ROWS, ATT_KEYS, false);
@@ -205,6 +262,10 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         const uint32_t k_major_low = uint32_t(k_major), k_major_high = uint32_t(k_major >> 32);
         const uint64_t mn_major = smem_desc_sw128_mn(0, KV_ATOM_BYTES);
         const uint32_t mn_major_low = uint32_t(mn_major), mn_major_high = uint32_t(mn_major >> 32);
+        // Descriptor address field: the low 18 bits of the shared address, in units of 16 bytes.  The mask matters: in a
+        // cluster launch the shared window of every CTA but rank 0 has bits above those, which would spill into the
+        // leading-byte-offset field next to it (the K-major operands ignore that field, the MN-major V operand does not).
+        auto field = [](uint32_t address) { return (address & 0x3FFFFu) >> 4; };
         mbar_wait(q_full, 0u, failed, args.status, STATUS_WAIT_MMA_FULL);
         tc_fence_after_sync();
         auto scores = [&](int j) {          // S[j & 1] = Q K_j^T
@@ -218,8 +279,8 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 const uint32_t d_tmem = tmem_base + TMEM_S + uint32_t(b) * ATT_KEYS;
 #pragma unroll
                 for (int a = 0; a < ATT_D_ATOMS; ++a) {
-                    const uint32_t q_low = k_major_low + ((q_smem + a * Q_ATOM_BYTES) >> 4);
-                    const uint32_t k_low = k_major_low + ((k_smem + b * KV_STAGE_BYTES + a * KV_ATOM_BYTES) >> 4);
+                    const uint32_t q_low = k_major_low + field(q_smem + a * Q_ATOM_BYTES);
+                    const uint32_t k_low = k_major_low + field(k_smem + b * KV_STAGE_BYTES + a * KV_ATOM_BYTES);
 #pragma unroll
                     for (int s = 0; s < 4; ++s)          // 16 elements of D = 32 bytes per MMA
                         mma_bf16(d_tmem, desc_from_words(q_low + 2 * s, k_major_high), desc_from_words(k_low + 2 * s, k_major_high),
@@ -238,8 +299,8 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             tc_fence_after_sync();
             __syncwarp();
             if (elect_one()) {
-                const uint32_t p_low = k_major_low + ((p_smem + b * P_BYTES) >> 4);
-                const uint32_t v_low = mn_major_low + ((v_smem + b * KV_STAGE_BYTES) >> 4);
+                const uint32_t p_low = k_major_low + field(p_smem + b * P_BYTES);
+                const uint32_t v_low = mn_major_low + field(v_smem + b * KV_STAGE_BYTES);
 #pragma unroll
                 for (int s = 0; s < ATT_KEYS / 16; ++s)   // 16 keys per MMA: 32 bytes along a row of P, 16 rows (2048 bytes) of V
                     mma_bf16(tmem_base + TMEM_O, desc_from_words(p_low + 2 * s, k_major_high),
@@ -254,6 +315,10 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         for (int j = 0; j < num_key_tiles; ++j) {
             if (j + 1 < num_key_tiles) scores(j + 1);
             output(j);
+        }
+        if (SPLIT) {
+            cluster_arrive();
+            cluster_wait();
         }
     } else {
         // ------------------------------------------------------------- one thread per query row
@@ -273,7 +338,7 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free + 8 * b);      // the scores of key tile j + 2 may overwrite this buffer
-            const int valid = args.keys - j * ATT_KEYS;     // keys of this tile that exist
+            const int valid = args.keys - (first_key_tile + j) * ATT_KEYS;     // keys of this tile that exist
             if (valid < ATT_KEYS) {                          // last tile: keys beyond the end never win the maximum and add nothing
 #pragma unroll
                 for (int half = 0; half < 2; ++half)
@@ -342,8 +407,115 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         }
         mbar_wait(o_done, uint32_t(num_key_tiles - 1) & 1u, failed, args.status, STATUS_WAIT_EPILOGUE);
         tc_fence_after_sync();
-        const float inverse = 1.0f / running_sum;
         const bool row_exists = row0 + row < args.rows_per_batch;
+        if (SPLIT) {
+            // (a) this CTA's partial rows [256 outputs | reference | sum] into its own shared memory (the operand stages
+            //     are dead: every MMA of this CTA has completed)
+            const int reader = (warp - 2) * 32 + lane;
+            const uint32_t my_row = staging + uint32_t(row) * SPLIT_ROW_BYTES;
+#pragma unroll 1
+            for (int chunk = 0; chunk < ATT_D / 32; ++chunk) {
+                uint32_t o[32];
+                tmem_load_32x32(lane_address + TMEM_O + chunk * 32, o);
+                tmem_load_wait();
+                if (row_exists) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + uint32_t(chunk * 128 + q * 16)),
+                                     "r"(o[4 * q]), "r"(o[4 * q + 1]), "r"(o[4 * q + 2]), "r"(o[4 * q + 3]) : "memory");
+                }
+            }
+            if (row_exists)
+                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(my_row + 1024u), "f"(running_max), "f"(running_sum) : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the copies below read these rows through the async proxy
+            // (b) first cluster barrier: every CTA of the cluster has finished with its operand stages, so partial rows may
+            //     land on them
+            cluster_arrive();
+            cluster_wait();
+            if (reader == 0) {
+                for (uint32_t step = 1; step <= splits; ++step) {       // starting with the next rank: no owner is everyone's first
+                    const uint32_t r = rank + step < splits ? rank + step : rank + step - splits;
+                    const int first = int(r) * args.rows_per_rank;
+                    int count = tile_rows - first;
+                    if (count > args.rows_per_rank) count = args.rows_per_rank;
+                    if (count > 0)
+                        bulk_copy_rows_to_cluster(cluster_map_shared(receive_base + rank * uint32_t(args.rows_per_rank) * SPLIT_ROW_BYTES, r),
+                                                  staging + uint32_t(first) * SPLIT_ROW_BYTES, uint32_t(count) * SPLIT_ROW_BYTES,
+                                                  cluster_map_shared(receive_bar, r));
+                }
+            }
+            // (c) the rows this CTA owns: weights 2^(m_r - M) / sum_r 2^(m_r - M) l_r per row, then the weighted sum in rank
+            //     order, 16 bytes of a row per thread and step
+            if (!failed) {
+                const long long start = clock64();
+                while (!mbar_try_wait_cluster_scope(receive_bar, 0u)) {
+                    if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                        failed = true;
+                        if (args.status != nullptr) atomicCAS(args.status, 0u, STATUS_WAIT_ATTENTION_EXCHANGE);
+                        break;
+                    }
+                }
+            }
+            const int first_row = int(rank) * args.rows_per_rank;
+            int owned = tile_rows - first_row;
+            if (owned > args.rows_per_rank) owned = args.rows_per_rank;
+            const uint32_t rank_stride = uint32_t(args.rows_per_rank) * SPLIT_ROW_BYTES;
+            if (reader < owned) {
+                float reference[SPLIT_MAX_CLUSTER], sum[SPLIT_MAX_CLUSTER];
+                float top = -INFINITY;
+#pragma unroll
+                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r) {
+                    if (r < splits) {
+                        float2 pair;
+                        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(pair.x), "=f"(pair.y)
+                                     : "r"(receive_base + r * rank_stride + uint32_t(reader) * SPLIT_ROW_BYTES + 1024u) : "memory");
+                        reference[r] = pair.x;
+                        sum[r] = pair.y;
+                        top = fmaxf(top, pair.x);
+                    }
+                }
+                float total = 0.0f;
+#pragma unroll
+                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r) {
+                    if (r < splits) {
+                        reference[r] = exp2_approx(reference[r] - top);
+                        total = __fmaf_rn(reference[r], sum[r], total);
+                    }
+                }
+                const float inverse = 1.0f / total;
+#pragma unroll
+                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r)
+                    if (r < splits)
+                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(weight_table + (uint32_t(reader) * SPLIT_MAX_CLUSTER + r) * 4u), "f"(reference[r] * inverse) : "memory");
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            __nv_bfloat16* tile_out = args.out + (int64_t(batch) * args.rows_per_batch + row0 + first_row) * ATT_D;
+            for (int slot = reader; slot < owned * 64; slot += 128) {
+                const uint32_t local = uint32_t(slot) >> 6, column = uint32_t(slot) & 63u;
+                const uint32_t address = receive_base + local * SPLIT_ROW_BYTES + column * 16u;
+                float4 part[SPLIT_MAX_CLUSTER];
+                float weight[SPLIT_MAX_CLUSTER];
+#pragma unroll
+                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r) {
+                    if (r < splits) {
+                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(part[r].x), "=f"(part[r].y), "=f"(part[r].z), "=f"(part[r].w)
+                                     : "r"(address + r * rank_stride) : "memory");
+                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(weight[r]) : "r"(weight_table + (local * SPLIT_MAX_CLUSTER + r) * 4u) : "memory");
+                    }
+                }
+                float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r) {
+                    if (r < splits) {
+                        total.x = __fmaf_rn(weight[r], part[r].x, total.x); total.y = __fmaf_rn(weight[r], part[r].y, total.y);
+                        total.z = __fmaf_rn(weight[r], part[r].z, total.z); total.w = __fmaf_rn(weight[r], part[r].w, total.w);
+                    }
+                }
+                const uint2 packed = make_uint2(float2_to_bf16x2(make_float2(total.x, total.y)), float2_to_bf16x2(make_float2(total.z, total.w)));
+                *reinterpret_cast<uint2*>(tile_out + local * ATT_D + column * 4u) = packed;
+            }
+        } else {
+        const float inverse = 1.0f / running_sum;
         __nv_bfloat16* destination = args.out + (int64_t(batch) * args.rows_per_batch + row0 + row) * ATT_D;
 #pragma unroll 1
         for (int group = 0; group < ATT_D / 128; ++group) {      // four 32-column loads in flight per wait
@@ -365,6 +537,7 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 }
             }
         }
+        }
     }
 
     tc_fence_before_sync();
@@ -372,6 +545,12 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLUMNS);
+    }
+    if (SPLIT) {
+        // second cluster barrier: no CTA leaves while a copy still reads its shared memory or writes another CTA's (every
+        // owner has seen all its bytes by the time it arrives here)
+        asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory");
+        cluster_wait();
     }
 }
 
@@ -386,7 +565,9 @@ int launch_attention(const void* q, const void* k, const void* v, void* out, int
     int device = 0;
     cudaGetDevice(&device);
     if (device >= 0 && device < 64 && !configured[device]) {
-        const cudaError_t error = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SHARED_BYTES);
+        cudaError_t error = cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SHARED_BYTES);
+        if (error == cudaSuccess)
+            error = cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SHARED_BYTES);
         if (error != cudaSuccess) return int(error);
         configured[device] = true;
     }
@@ -401,7 +582,43 @@ int launch_attention(const void* q, const void* k, const void* v, void* out, int
     args.keys = keys;
     args.tiles_per_batch = int((rows_per_batch + ATT_ROWS - 1) / ATT_ROWS);
     args.scale_log2 = 1.4426950408889634f / 16.0f;
-    return launch_kernel(attention_kernel, dim3(unsigned(batch * args.tiles_per_batch)), dim3(ATT_THREADS), size_t(ATT_SHARED_BYTES), stream,
+    args.splits = 1;
+    args.rows_per_rank = 0;
+    // Few CTAs and several key tiles: the keys of a tile are cut across a cluster of 2, 4 or 8 CTAs, as long as the launch
+    // stays well inside one wave and the partial rows of a tile (sent and received) fit over the operand stages.
+    const int key_tiles = (keys + ATT_KEYS - 1) / ATT_KEYS;
+    const int tiles = batch * args.tiles_per_batch;
+    int splits = key_tiles >= 8 ? 8 : key_tiles >= 4 ? 4 : key_tiles >= 2 ? 2 : 1;
+    while (splits > 1 && tiles * splits > sm_count() / 2) splits /= 2;
+    if (splits > 1 && args.tiles_per_batch == 1) {
+        const int rows = int(rows_per_batch);
+        const int rows_per_rank = (rows + splits - 1) / splits;
+        const int64_t exchange = int64_t(rows) * SPLIT_ROW_BYTES + int64_t(splits) * rows_per_rank * SPLIT_ROW_BYTES +
+                                 int64_t(rows_per_rank) * SPLIT_MAX_CLUSTER * 4;
+        if (exchange <= int64_t(Q_BYTES + 4 * KV_STAGE_BYTES + 2 * P_BYTES)) {
+            args.splits = splits;
+            args.rows_per_rank = rows_per_rank;
+        }
+    }
+    if (args.splits > 1) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(unsigned(tiles * args.splits));
+        config.blockDim = dim3(ATT_THREADS);
+        config.dynamicSmemBytes = size_t(ATT_SHARED_BYTES);
+        config.stream = stream;
+        cudaLaunchAttribute attributes[2];
+        attributes[0].id = cudaLaunchAttributeClusterDimension;
+        attributes[0].val.clusterDim.x = unsigned(args.splits);
+        attributes[0].val.clusterDim.y = 1;
+        attributes[0].val.clusterDim.z = 1;
+        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attributes;
+        config.numAttrs = pdl_enabled() ? 2 : 1;
+        const cudaError_t error = cudaLaunchKernelEx(&config, attention_kernel<true>, q_map, k_map, v_map, args);
+        return error == cudaSuccess ? int(cudaGetLastError()) : int(error);
+    }
+    return launch_kernel(attention_kernel<false>, dim3(unsigned(tiles)), dim3(ATT_THREADS), size_t(ATT_SHARED_BYTES), stream,
                          q_map, k_map, v_map, args);
 }
 

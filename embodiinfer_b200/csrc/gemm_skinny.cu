@@ -222,12 +222,13 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_c
             if (elect_one()) {
                 constexpr uint32_t ATOM = SCALE_ATOM_BYTES >> 4;
                 const uint32_t a_smem = base + uint32_t(i) * stage_bytes;
-                const uint32_t a_low = operand_low + (a_smem >> 4);
-                const uint32_t b_low = operand_low + ((a_smem + WEIGHT_BYTES) >> 4);
+                // (address field = low 18 bits: in a cluster every CTA but rank 0 has shared-window bits above them)
+                const uint32_t a_low = operand_low + ((a_smem & 0x3FFFFu) >> 4);
+                const uint32_t b_low = operand_low + (((a_smem + WEIGHT_BYTES) & 0x3FFFFu) >> 4);
                 // NVFP4: every atom has its own 32 columns of tensor memory (16 of weight scales, 16 of token scales)
                 const uint32_t sfa_tmem = tmem_base + uint32_t(TMEM_COLUMNS) - 32u * uint32_t(i + 1);
                 const uint32_t sfb_tmem = sfa_tmem + 16u;
-                const uint32_t scale_low = (scale_base + uint32_t(i) * 2u * SCALE_PART_BYTES) >> 4;
+                const uint32_t scale_low = ((scale_base + uint32_t(i) * 2u * SCALE_PART_BYTES) & 0x3FFFFu) >> 4;
                 const int count = kb_begin + i == num_kb - 1 ? last_kb_mmas : SCALE_ATOMS_PER_STAGE;
 #pragma unroll
                 for (int j = 0; j < SCALE_ATOMS_PER_STAGE; ++j) {

@@ -283,7 +283,10 @@ ATTENTION_SHAPES = [
     ("prefix_B1_8x560x560", 1, 8, 560, 560),
     ("prefix_B32_8x560x560", 32, 8, 560, 560),
     ("expert_B1_8x10x570", 1, 8, 10, 570),
+    ("expert_B2_8x10x570", 2, 8, 10, 570),
+    ("expert_B4_8x10x570", 4, 8, 10, 570),
     ("expert_B8_8x10x570", 8, 8, 10, 570),
+    ("expert_B16_8x10x570", 16, 8, 10, 570),
     ("expert_B32_8x10x570", 32, 8, 10, 570),
     ("expert_B64_8x10x570", 64, 8, 10, 570),
 ]

@@ -32,6 +32,13 @@ def relative(a, b):
     (2, 3, 77, 64),         # exactly one key tile, ragged rows
     (2, 8, 16, 65),         # one key in the second tile
     (1, 8, 128, 128),
+    # one tile per batch element and several key tiles: the keys are cut across a cluster of 8 / 4 / 2 CTAs
+    (1, 8, 10, 580),        # ten key tiles over eight CTAs (unequal key ranges), rows dealt 10 per CTA
+    (1, 8, 13, 130),        # 104 rows (the most the exchange buffers hold), three key tiles over two CTAs
+    (2, 4, 7, 300),         # 28 rows over four CTAs, a ragged last key tile
+    (1, 1, 3, 1030),        # fewer rows than CTAs: most CTAs own none
+    (9, 8, 10, 570),        # nine clusters of eight
+    (20, 8, 10, 570),       # clusters of two
 ])
 @pytest.mark.parametrize("spread", (1.0, 6.0))
 def test_attention_matches_float32(device, batch, heads, queries, keys, spread):
