@@ -24,14 +24,21 @@
 // Few rows (one observation's ten-token chunk is 80 rows: a single CTA walking all ten key tiles): the keys are cut
 // across the CTAs of a thread-block cluster instead (SPLIT).  Every CTA runs the loop above on its own key tiles and
 // ends with an unnormalised output, a reference m and a sum l per row; the rows are dealt to the CTAs in runs of T, each
-// CTA sends every other CTA the rows that one owns ([256 outputs | m | l] fp32, one bulk copy per owner through
-// distributed shared memory) and the owner combines them in rank order:
+// CTA sends every other CTA the rows that one owns (one bulk copy per owner through distributed shared memory) and the
+// owner combines them in rank order:
 //   out = sum_r 2^(m_r - M) O_r / sum_r 2^(m_r - M) l_r,   M = max_r m_r.
+// A partial row travels as 256 fp16 values c_r O_r with c_r the power of two that brings the row's largest magnitude
+// into [1, 2) (so no range of inputs overflows and the rounding, 2^-11 of the row's maximum, is a quarter of the
+// output's own bf16 rounding), followed by m_r, l_r and 1 / c_r in fp32: 528 bytes instead of 1040 -- the exchange moves
+// every row to its owner at some 18 bytes per cycle and SM, which is what bounds these launches.
 // The exchange buffers lie over the query / key / value stages, which are dead by then in every CTA of the cluster: a
 // hardware cluster barrier separates the two uses.
 #include "gemm_epilogue.cuh"
 
 #include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <type_traits>
 
 namespace b2 {
 
@@ -50,9 +57,8 @@ constexpr uint32_t P_BYTES = ATT_ROWS * ATT_ATOM_BYTES;       // 16 KB: 128 rows
 constexpr int ATT_THREADS = 32 * 6;
 constexpr int ATT_SHARED_BYTES = 1024 + int(Q_BYTES + 4 * KV_STAGE_BYTES + 2 * P_BYTES) + 256;
 constexpr uint32_t TMEM_S = 0, TMEM_O = 128;     // two score buffers of 64 columns, then 256 output columns
-constexpr uint32_t SPLIT_ROW_FLOATS = 260;       // 256 outputs, reference, sum, 2 of padding: rows start 4 banks apart
-constexpr uint32_t SPLIT_ROW_BYTES = SPLIT_ROW_FLOATS * 4;
-constexpr int SPLIT_MAX_CLUSTER = 8;
+constexpr uint32_t SPLIT_ROW_BYTES = 528;        // 256 outputs as fp16, then reference, sum and row scale as fp32, 4 bytes of padding:
+                                                 // rows start 4 banks apart
 constexpr unsigned int STATUS_WAIT_ATTENTION_EXCHANGE = 0x108;    // a CTA gave up waiting for the partial rows of its cluster
 
 __device__ __forceinline__ bool mbar_try_wait_cluster_scope(uint32_t bar, uint32_t parity) {
@@ -174,7 +180,6 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     if (tile_rows > ATT_ROWS) tile_rows = ATT_ROWS;
     const uint32_t staging = base;
     const uint32_t receive_base = staging + uint32_t(tile_rows) * SPLIT_ROW_BYTES;
-    const uint32_t weight_table = receive_base + splits * uint32_t(args.rows_per_rank) * SPLIT_ROW_BYTES;     // [T][S] floats
 
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&q_map);
@@ -409,24 +414,55 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         tc_fence_after_sync();
         const bool row_exists = row0 + row < args.rows_per_batch;
         if (SPLIT) {
-            // (a) this CTA's partial rows [256 outputs | reference | sum] into its own shared memory (the operand stages
-            //     are dead: every MMA of this CTA has completed)
+            // (a) this CTA's partial rows into its own shared memory (the operand stages are dead: every MMA of this CTA has
+            //     completed): the row's largest magnitude first, then the scaled values as fp16
             const int reader = (warp - 2) * 32 + lane;
             const uint32_t my_row = staging + uint32_t(row) * SPLIT_ROW_BYTES;
+            float largest = 0.0f;
 #pragma unroll 1
-            for (int chunk = 0; chunk < ATT_D / 32; ++chunk) {
-                uint32_t o[32];
-                tmem_load_32x32(lane_address + TMEM_O + chunk * 32, o);
+            for (int chunk = 0; chunk < ATT_D / 32; chunk += 2) {       // two loads in flight per wait
+                uint32_t o[2][32];
+                tmem_load_32x32(lane_address + TMEM_O + chunk * 32, o[0]);
+                tmem_load_32x32(lane_address + TMEM_O + chunk * 32 + 32, o[1]);
+                tmem_load_wait();
+                float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    part[i & 3] = fmaxf(part[i & 3], fabsf(__uint_as_float(o[0][i])));
+                    part[i & 3] = fmaxf(part[i & 3], fabsf(__uint_as_float(o[1][i])));
+                }
+                largest = fmaxf(fmaxf(largest, fmaxf(part[0], part[1])), fmaxf(part[2], part[3]));
+            }
+            // 2^-(exponent of the largest magnitude); 1 for an all-zero row and for infinities / NaNs (which then travel as they are)
+            uint32_t exponent = __float_as_uint(largest) & 0x7f800000u;
+            const bool unscaled = exponent == 0u || exponent == 0x7f800000u;
+            if (exponent > 0x7e000000u) exponent = 0x7e000000u;            // keeps the scale itself a normal number
+            const float row_scale = unscaled ? 1.0f : __uint_as_float(0x7f000000u - exponent);
+            const float row_unscale = unscaled ? 1.0f : __uint_as_float(exponent);          // 1 / row_scale, exactly
+#pragma unroll 1
+            for (int chunk = 0; chunk < ATT_D / 32; chunk += 2) {
+                uint32_t o[2][32];
+                tmem_load_32x32(lane_address + TMEM_O + chunk * 32, o[0]);
+                tmem_load_32x32(lane_address + TMEM_O + chunk * 32 + 32, o[1]);
                 tmem_load_wait();
                 if (row_exists) {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q)
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + uint32_t(chunk * 128 + q * 16)),
-                                     "r"(o[4 * q]), "r"(o[4 * q + 1]), "r"(o[4 * q + 2]), "r"(o[4 * q + 3]) : "memory");
+                    for (int half = 0; half < 2; ++half) {
+                        uint32_t h[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const __half2 pair = __floats2half2_rn(__uint_as_float(o[half][2 * i]) * row_scale, __uint_as_float(o[half][2 * i + 1]) * row_scale);
+                            h[i] = *reinterpret_cast<const uint32_t*>(&pair);
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + uint32_t((chunk + half) * 64 + q * 16)),
+                                         "r"(h[4 * q]), "r"(h[4 * q + 1]), "r"(h[4 * q + 2]), "r"(h[4 * q + 3]) : "memory");
+                    }
                 }
             }
             if (row_exists)
-                asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(my_row + 1024u), "f"(running_max), "f"(running_sum) : "memory");
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(my_row + 512u), "f"(running_max), "f"(running_sum), "f"(row_unscale), "f"(0.0f) : "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the copies below read these rows through the async proxy
             // (b) first cluster barrier: every CTA of the cluster has finished with its operand stages, so partial rows may
             //     land on them
@@ -460,59 +496,74 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             int owned = tile_rows - first_row;
             if (owned > args.rows_per_rank) owned = args.rows_per_rank;
             const uint32_t rank_stride = uint32_t(args.rows_per_rank) * SPLIT_ROW_BYTES;
-            if (reader < owned) {
-                float reference[SPLIT_MAX_CLUSTER], sum[SPLIT_MAX_CLUSTER];
-                float top = -INFINITY;
-#pragma unroll
-                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r) {
-                    if (r < splits) {
-                        float2 pair;
-                        asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(pair.x), "=f"(pair.y)
-                                     : "r"(receive_base + r * rank_stride + uint32_t(reader) * SPLIT_ROW_BYTES + 1024u) : "memory");
-                        reference[r] = pair.x;
-                        sum[r] = pair.y;
-                        top = fmaxf(top, pair.x);
-                    }
-                }
-                float total = 0.0f;
-#pragma unroll
-                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r) {
-                    if (r < splits) {
-                        reference[r] = exp2_approx(reference[r] - top);
-                        total = __fmaf_rn(reference[r], sum[r], total);
-                    }
-                }
-                const float inverse = 1.0f / total;
-#pragma unroll
-                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r)
-                    if (r < splits)
-                        asm volatile("st.shared.f32 [%0], %1;" ::"r"(weight_table + (uint32_t(reader) * SPLIT_MAX_CLUSTER + r) * 4u), "f"(reference[r] * inverse) : "memory");
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
             __nv_bfloat16* tile_out = args.out + (int64_t(batch) * args.rows_per_batch + row0 + first_row) * ATT_D;
-            for (int slot = reader; slot < owned * 64; slot += 128) {
-                const uint32_t local = uint32_t(slot) >> 6, column = uint32_t(slot) & 63u;
-                const uint32_t address = receive_base + local * SPLIT_ROW_BYTES + column * 16u;
-                float4 part[SPLIT_MAX_CLUSTER];
-                float weight[SPLIT_MAX_CLUSTER];
+            // The cluster size is a compile-time constant of the loop body (one copy per size, chosen below): with a run-time
+            // bound every partial row is its own basic block and the single warp of a scheduler crawls through them.
+            auto combine = [&](auto size_tag) {
+                constexpr uint32_t SIZE = decltype(size_tag)::value;
+                for (int slot = reader; slot < owned * 32; slot += 128) {
+                    const uint32_t local = uint32_t(slot) >> 5, column = uint32_t(slot) & 31u;      // 16 bytes = 8 values of a row
+                    const uint32_t row_address = receive_base + local * SPLIT_ROW_BYTES;
+                    // the row's weights 2^(m_r - M) / (c_r sum_r 2^(m_r - M) l_r): every thread works them out for its own slot
+                    // (the loads are the same address across a warp), which is cheaper than a table, a barrier and idle warps
+                    float weight[SIZE];
+                    {
+                        float4 tail[SIZE];
 #pragma unroll
-                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r) {
-                    if (r < splits) {
-                        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(part[r].x), "=f"(part[r].y), "=f"(part[r].z), "=f"(part[r].w)
-                                     : "r"(address + r * rank_stride) : "memory");
-                        asm volatile("ld.shared.f32 %0, [%1];" : "=f"(weight[r]) : "r"(weight_table + (local * SPLIT_MAX_CLUSTER + r) * 4u) : "memory");
-                    }
-                }
-                float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        for (uint32_t r = 0; r < SIZE; ++r)
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(tail[r].x), "=f"(tail[r].y), "=f"(tail[r].z), "=f"(tail[r].w)
+                                         : "r"(row_address + r * rank_stride + 512u) : "memory");
+                        float top = tail[0].x;
 #pragma unroll
-                for (uint32_t r = 0; r < SPLIT_MAX_CLUSTER; ++r) {
-                    if (r < splits) {
-                        total.x = __fmaf_rn(weight[r], part[r].x, total.x); total.y = __fmaf_rn(weight[r], part[r].y, total.y);
-                        total.z = __fmaf_rn(weight[r], part[r].z, total.z); total.w = __fmaf_rn(weight[r], part[r].w, total.w);
+                        for (uint32_t r = 1; r < SIZE; ++r) top = fmaxf(top, tail[r].x);
+                        float total = 0.0f;
+#pragma unroll
+                        for (uint32_t r = 0; r < SIZE; ++r) {
+                            const float w = exp2_approx(tail[r].x - top);
+                            total = __fmaf_rn(w, tail[r].y, total);
+                            weight[r] = w * tail[r].z;
+                        }
+                        const float inverse = __fdividef(1.0f, total);
+#pragma unroll
+                        for (uint32_t r = 0; r < SIZE; ++r) weight[r] *= inverse;
                     }
+                    uint4 part[SIZE];
+#pragma unroll
+                    for (uint32_t r = 0; r < SIZE; ++r)
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(part[r].x), "=r"(part[r].y), "=r"(part[r].z), "=r"(part[r].w)
+                                     : "r"(row_address + column * 16u + r * rank_stride) : "memory");
+                    float total[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (uint32_t r = 0; r < SIZE; ++r) {
+                        const uint32_t words[4] = {part[r].x, part[r].y, part[r].z, part[r].w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(&words[i]));
+                            total[2 * i] = __fmaf_rn(weight[r], pair.x, total[2 * i]);
+                            total[2 * i + 1] = __fmaf_rn(weight[r], pair.y, total[2 * i + 1]);
+                        }
+                    }
+                    const uint4 packed = make_uint4(float2_to_bf16x2(make_float2(total[0], total[1])), float2_to_bf16x2(make_float2(total[2], total[3])),
+                                                    float2_to_bf16x2(make_float2(total[4], total[5])), float2_to_bf16x2(make_float2(total[6], total[7])));
+                    *reinterpret_cast<uint4*>(tile_out + local * ATT_D + column * 8u) = packed;
                 }
-                const uint2 packed = make_uint2(float2_to_bf16x2(make_float2(total.x, total.y)), float2_to_bf16x2(make_float2(total.z, total.w)));
-                *reinterpret_cast<uint2*>(tile_out + local * ATT_D + column * 4u) = packed;
+            };
+            switch (splits) {
+                case 2: combine(std::integral_constant<uint32_t, 2>{}); break;
+                case 3: combine(std::integral_constant<uint32_t, 3>{}); break;
+                case 4: combine(std::integral_constant<uint32_t, 4>{}); break;
+                case 5: combine(std::integral_constant<uint32_t, 5>{}); break;
+                case 6: combine(std::integral_constant<uint32_t, 6>{}); break;
+                case 7: combine(std::integral_constant<uint32_t, 7>{}); break;
+                case 8: combine(std::integral_constant<uint32_t, 8>{}); break;
+                case 9: combine(std::integral_constant<uint32_t, 9>{}); break;
+                case 10: combine(std::integral_constant<uint32_t, 10>{}); break;
+                case 11: combine(std::integral_constant<uint32_t, 11>{}); break;
+                case 12: combine(std::integral_constant<uint32_t, 12>{}); break;
+                case 13: combine(std::integral_constant<uint32_t, 13>{}); break;
+                case 14: combine(std::integral_constant<uint32_t, 14>{}); break;
+                case 15: combine(std::integral_constant<uint32_t, 15>{}); break;
+                default: combine(std::integral_constant<uint32_t, 16>{}); break;
             }
         } else {
         const float inverse = 1.0f / running_sum;
@@ -584,17 +635,40 @@ int launch_attention(const void* q, const void* k, const void* v, void* out, int
     args.scale_log2 = 1.4426950408889634f / 16.0f;
     args.splits = 1;
     args.rows_per_rank = 0;
-    // Few CTAs and several key tiles: the keys of a tile are cut across a cluster of 2, 4 or 8 CTAs, as long as the launch
-    // stays well inside one wave and the partial rows of a tile (sent and received) fit over the operand stages.
+    // Few CTAs and several key tiles: the keys of a tile are cut across a cluster -- one CTA per key tile up to the largest
+    // cluster this device schedules (16 where the opt-in sizes are available, else 8) -- as long as the launch stays well
+    // inside one wave and the partial rows of a tile (sent and received) fit over the operand stages.
     const int key_tiles = (keys + ATT_KEYS - 1) / ATT_KEYS;
     const int tiles = batch * args.tiles_per_batch;
-    int splits = key_tiles >= 8 ? 8 : key_tiles >= 4 ? 4 : key_tiles >= 2 ? 2 : 1;
+    static int largest_cluster[64] = {0};
+    if (device >= 0 && device < 64 && largest_cluster[device] == 0) {
+        largest_cluster[device] = 8;
+        if (cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+            cudaLaunchConfig_t probe = {};
+            probe.gridDim = dim3(16);
+            probe.blockDim = dim3(ATT_THREADS);
+            probe.dynamicSmemBytes = size_t(ATT_SHARED_BYTES);
+            cudaLaunchAttribute cluster;
+            cluster.id = cudaLaunchAttributeClusterDimension;
+            cluster.val.clusterDim.x = 16;
+            cluster.val.clusterDim.y = 1;
+            cluster.val.clusterDim.z = 1;
+            probe.attrs = &cluster;
+            probe.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, attention_kernel<true>, &probe) == cudaSuccess && clusters >= 4)
+                largest_cluster[device] = 16;
+        }
+        cudaGetLastError();
+    }
+    const int cluster_limit = device >= 0 && device < 64 ? largest_cluster[device] : 8;
+    int splits = key_tiles < cluster_limit ? key_tiles : cluster_limit;
+    if (tiles * splits > sm_count() / 2) splits = key_tiles >= 8 ? 8 : key_tiles >= 4 ? 4 : key_tiles >= 2 ? 2 : 1;
     while (splits > 1 && tiles * splits > sm_count() / 2) splits /= 2;
     if (splits > 1 && args.tiles_per_batch == 1) {
         const int rows = int(rows_per_batch);
         const int rows_per_rank = (rows + splits - 1) / splits;
-        const int64_t exchange = int64_t(rows) * SPLIT_ROW_BYTES + int64_t(splits) * rows_per_rank * SPLIT_ROW_BYTES +
-                                 int64_t(rows_per_rank) * SPLIT_MAX_CLUSTER * 4;
+        const int64_t exchange = int64_t(rows) * SPLIT_ROW_BYTES + int64_t(splits) * rows_per_rank * SPLIT_ROW_BYTES;
         if (exchange <= int64_t(Q_BYTES + 4 * KV_STAGE_BYTES + 2 * P_BYTES)) {
             args.splits = splits;
             args.rows_per_rank = rows_per_rank;

@@ -372,11 +372,11 @@ class GemmaBlock(nn.Module):
         K.rope_split(qkv.reshape(batch * tokens, -1), rope[0], rope[1], q, k, v, batch=batch, tokens=tokens, heads=shape.heads,
                      kv_heads=shape.kv_heads, head_dim=shape.head_dim, kv_offset=k.shape[2] - tokens)
         own_kv = (k, v)
-        # b2_attention runs one CTA per 128 query rows of a batch element and walks the keys serially, so a launch of one
-        # or two CTAs (a single observation's ten-token chunk) is latency-bound at ~12 us, where torch's kernel takes 11;
-        # from four CTAs on it is 1.5-4x faster (measured: B = 8 / 32 / 64 chunks 13 / 14 / 15 us against 20 / 33 / 62).
-        tiles = batch * -(-(shape.heads * tokens) // 128)
-        if self.native_attention and shape.head_dim == 256 and shape.kv_heads == 1 and tiles >= 4:
+        # b2_attention: one CTA per 128 query rows of a batch element; launches of few such tiles (a handful of observations'
+        # ten-token chunks) cut the keys of a tile across a thread-block cluster instead of walking them serially
+        # (measured, 8 heads x 10 queries over 570 keys: B = 1 / 8 / 32 / 64 take 7.2 / 7.7 / 12.3 / 15.0 us against
+        # 11.3 / 20.7 / 33.1 / 63.0 for torch's kernel).
+        if self.native_attention and shape.head_dim == 256 and shape.kv_heads == 1:
             attended = K.attention(q, k, v)           # tcgen05 multi-query attention (b2_attention)
         else:
             attended = F.scaled_dot_product_attention(q, k, v, enable_gqa=shape.heads != shape.kv_heads)

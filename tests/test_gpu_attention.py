@@ -33,8 +33,10 @@ def relative(a, b):
     (2, 8, 16, 65),         # one key in the second tile
     (1, 8, 128, 128),
     # one tile per batch element and several key tiles: the keys are cut across a cluster of 8 / 4 / 2 CTAs
-    (1, 8, 10, 580),        # ten key tiles over eight CTAs (unequal key ranges), rows dealt 10 per CTA
-    (1, 8, 13, 130),        # 104 rows (the most the exchange buffers hold), three key tiles over two CTAs
+    (1, 8, 10, 580),        # ten key tiles, one per CTA where clusters of ten are available (else unequal key ranges over eight)
+    (1, 8, 13, 130),        # 104 rows, three key tiles over three CTAs
+    (1, 8, 16, 200),        # a full tile of 128 rows
+    (1, 2, 5, 1000),        # sixteen key tiles: the largest cluster
     (2, 4, 7, 300),         # 28 rows over four CTAs, a ragged last key tile
     (1, 1, 3, 1030),        # fewer rows than CTAs: most CTAs own none
     (9, 8, 10, 570),        # nine clusters of eight
