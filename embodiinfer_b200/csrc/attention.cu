@@ -59,7 +59,6 @@ constexpr int ATT_SHARED_BYTES = 1024 + int(Q_BYTES + 4 * KV_STAGE_BYTES + 2 * P
 constexpr uint32_t TMEM_S = 0, TMEM_O = 128;     // two score buffers of 64 columns, then 256 output columns
 constexpr uint32_t SPLIT_ROW_BYTES = 528;        // 256 outputs as fp16, then reference, sum and row scale as fp32, 4 bytes of padding:
                                                  // rows start 4 banks apart
-constexpr unsigned int STATUS_WAIT_ATTENTION_EXCHANGE = 0x108;    // a CTA gave up waiting for the partial rows of its cluster
 
 __device__ __forceinline__ bool mbar_try_wait_cluster_scope(uint32_t bar, uint32_t parity) {
     uint32_t done;

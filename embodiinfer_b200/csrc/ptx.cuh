@@ -18,6 +18,7 @@ enum : unsigned int {
     STATUS_WAIT_DRAIN = 0x105,      // producer gave up waiting for its copies in flight
     STATUS_WAIT_SPLIT = 0x106,      // split K: a CTA gave up waiting for the other K ranges of its tile
     STATUS_WAIT_EXCHANGE = 0x107,   // cluster split K: a CTA gave up waiting for the partial sums of its cluster
+    STATUS_WAIT_ATTENTION_EXCHANGE = 0x108,   // split attention: a CTA gave up waiting for the partial rows of its cluster
 };
 
 // Upper bound, in SM clock cycles, for any single wait (about a second).

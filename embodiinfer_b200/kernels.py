@@ -322,7 +322,8 @@ def frames_to_patches(frames: torch.Tensor, patches: torch.Tensor, patch: int) -
 STATUS_NAMES = {0x101: "the TMA producer waited for a free stage", 0x102: "the MMA issuer waited for a filled stage",
                 0x103: "the MMA issuer waited for a drained accumulator", 0x104: "the epilogue waited for a finished accumulator",
                 0x105: "the producer waited for its copies in flight", 0x106: "a CTA waited for the other K ranges of its tile",
-                0x107: "a CTA waited for the partial sums of its cluster"}
+                0x107: "a CTA waited for the partial sums of its cluster",
+                0x108: "a CTA waited for the partial attention rows of its cluster"}
 _status_words: dict[int, torch.Tensor] = {}
 
 

@@ -200,7 +200,9 @@ int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q
  *   k, v bf16 [batch, 1, keys, head_dim]           (b2_rope_split's k_out / v_out with kv_capacity == keys)
  *   out  bf16 [batch, heads, queries, head_dim]   (what b2_bhsd_quant reads)
  * head_dim must be 256 (B2_E_UNSUPPORTED otherwise); all pointers 16-byte aligned.  Scores and the output accumulate in
- * fp32; probabilities enter the second product as bf16, as in torch's flash kernels.  `status` as in b2_linear_desc
+ * fp32; probabilities enter the second product as bf16, as in torch's flash kernels.  A launch of few 128-row tiles (a handful
+ * of ten-query chunks) cuts the keys of a tile across a thread-block cluster of up to 16 CTAs and merges the partial rows
+ * (fp16 scaled per row by a power of two, with fp32 maxima and sums) in a fixed order.  `status` as in b2_linear_desc
  * (NULL allowed). */
 int b2_attention(const void* q, const void* k, const void* v, void* out, int32_t batch, int32_t heads, int32_t queries,
                  int32_t keys, int32_t head_dim, void* status, void* stream);
