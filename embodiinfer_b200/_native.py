@@ -101,6 +101,7 @@ SIGNATURES: dict[str, list] = {
     "b2_resize_frames": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "b2_rope_split": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I64, _I, _I, _P],
     "b2_attention": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "b2_attention_fp8": [_P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _P, _P],
 }
 RESULT_TYPES = {"b2_linear_workspace_bytes": ctypes.c_int64}
 

@@ -6,8 +6,8 @@
 
 namespace b2 {
 int run_linear(const b2_linear_desc* desc, cudaStream_t stream, int64_t* workspace_need = nullptr);
-int launch_attention(const void* q, const void* k, const void* v, void* out, int batch, int heads, int queries, int keys,
-                     int head_dim, void* status, cudaStream_t stream);
+int launch_attention(const void* q, const void* k, const void* v, void* out, void* codes, float multiplier, int batch, int heads,
+                     int queries, int keys, int head_dim, void* status, cudaStream_t stream);
 int launch_rope_split(const void* qkv, const void* sine, const void* cosine, void* q_out, void* k_out, void* v_out, int batch,
                       int tokens, int heads, int kv_heads, int head_dim, int64_t factor_batch_stride, int kv_capacity,
                       int kv_offset, cudaStream_t stream);
@@ -140,7 +140,18 @@ int b2_attention(const void* q, const void* k, const void* v, void* out, int32_t
     const uintptr_t alignment = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
                                 reinterpret_cast<uintptr_t>(out);
     if (alignment & 15u) return B2_E_INVALID;
-    return b2::launch_attention(q, k, v, out, batch, heads, queries, keys, head_dim, status, static_cast<cudaStream_t>(stream));
+    return b2::launch_attention(q, k, v, out, nullptr, 1.0f, batch, heads, queries, keys, head_dim, status, static_cast<cudaStream_t>(stream));
+}
+
+int b2_attention_fp8(const void* q, const void* k, const void* v, void* codes, float multiplier, int32_t batch, int32_t heads,
+                     int32_t queries, int32_t keys, int32_t head_dim, void* status, void* stream) {
+    if (q == nullptr || k == nullptr || v == nullptr || codes == nullptr) return B2_E_INVALID;
+    if (batch <= 0 || heads <= 0 || queries <= 0 || keys <= 0 || head_dim <= 0) return B2_E_INVALID;
+    if (!(multiplier > 0.0f) || multiplier > 3.0e38f) return B2_E_INVALID;
+    const uintptr_t alignment = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                                reinterpret_cast<uintptr_t>(codes);
+    if (alignment & 15u) return B2_E_INVALID;
+    return b2::launch_attention(q, k, v, nullptr, codes, multiplier, batch, heads, queries, keys, head_dim, status, static_cast<cudaStream_t>(stream));
 }
 
 int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q_out, void* k_out, void* v_out,

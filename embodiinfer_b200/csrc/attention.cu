@@ -133,8 +133,22 @@ __device__ __forceinline__ float exp2_approx(float x) {
     return y;
 }
 
+// Four bf16 pairs -> eight e4m3 codes at a static multiplier: the arithmetic of the stand-alone output encoder
+// (bhsd_encode_kernel, bits 8): e4m3(bf16 value * multiplier), saturating.
+__device__ __forceinline__ uint2 encode_row_words(const uint32_t (&words)[4], float multiplier) {
+    const float2 factor = make_float2(multiplier, multiplier);
+    uint32_t codes[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        codes[i] = __nv_cvt_float2_to_fp8x2(__fmul2_rn(bf16x2_to_float2(words[i]), factor), __NV_SATFINITE, __NV_E4M3);
+    return make_uint2(codes[0] | (codes[1] << 16), codes[2] | (codes[3] << 16));
+}
+
 struct AttentionArgs {
-    __nv_bfloat16* out;          // [batch, heads * queries, 256]
+    __nv_bfloat16* out;          // [batch, heads * queries, 256], or nullptr when `codes` is given
+    uint8_t* codes;              // e4m3 [batch * queries, heads * 256]: the encoded rows of the output projection, or nullptr
+    float multiplier;            // codes = e4m3(bf16(out) * multiplier)
+    int queries;                 // queries per head (row of a batch element = head * queries + query)
     unsigned int* status;
     int rows_per_batch;          // heads * queries
     int keys;                    // keys (= values) per batch element
@@ -542,9 +556,18 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                             total[2 * i + 1] = __fmaf_rn(weight[r], pair.y, total[2 * i + 1]);
                         }
                     }
-                    const uint4 packed = make_uint4(float2_to_bf16x2(make_float2(total[0], total[1])), float2_to_bf16x2(make_float2(total[2], total[3])),
-                                                    float2_to_bf16x2(make_float2(total[4], total[5])), float2_to_bf16x2(make_float2(total[6], total[7])));
-                    *reinterpret_cast<uint4*>(tile_out + local * ATT_D + column * 8u) = packed;
+                    const uint32_t words[4] = {float2_to_bf16x2(make_float2(total[0], total[1])), float2_to_bf16x2(make_float2(total[2], total[3])),
+                                               float2_to_bf16x2(make_float2(total[4], total[5])), float2_to_bf16x2(make_float2(total[6], total[7]))};
+                    if (args.codes != nullptr) {
+                        // row (head, query) of the batch element -> row batch * queries + query, columns of that head
+                        const int tile_row = row0 + first_row + int(local);
+                        const int head = tile_row / args.queries, query = tile_row - head * args.queries;
+                        const int64_t width = int64_t(args.rows_per_batch / args.queries) * ATT_D;
+                        uint8_t* destination = args.codes + (int64_t(batch) * args.queries + query) * width + head * ATT_D + column * 8u;
+                        *reinterpret_cast<uint2*>(destination) = encode_row_words(words, args.multiplier);
+                    } else {
+                        *reinterpret_cast<uint4*>(tile_out + local * ATT_D + column * 8u) = make_uint4(words[0], words[1], words[2], words[3]);
+                    }
                 }
             };
             switch (splits) {
@@ -580,10 +603,25 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
                         words[i] = float2_to_bf16x2(make_float2(__uint_as_float(o[c][2 * i]) * inverse, __uint_as_float(o[c][2 * i + 1]) * inverse));
+                    if (args.codes != nullptr) {
+                        const int tile_row = row0 + row;
+                        const int head = tile_row / args.queries, query = tile_row - head * args.queries;
+                        const int64_t width = int64_t(args.rows_per_batch / args.queries) * ATT_D;
+                        uint8_t* encoded = args.codes + (int64_t(batch) * args.queries + query) * width + head * ATT_D + group * 128 + c * 32;
+                        uint2 part[4];
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const uint32_t four[4] = {words[4 * v], words[4 * v + 1], words[4 * v + 2], words[4 * v + 3]};
+                            part[v] = encode_row_words(four, args.multiplier);
+                        }
+                        *reinterpret_cast<uint4*>(encoded) = make_uint4(part[0].x, part[0].y, part[1].x, part[1].y);
+                        *reinterpret_cast<uint4*>(encoded + 16) = make_uint4(part[2].x, part[2].y, part[3].x, part[3].y);
+                    } else {
                     const uint32_t first[8] = {words[0], words[1], words[2], words[3], words[4], words[5], words[6], words[7]};
                     const uint32_t second[8] = {words[8], words[9], words[10], words[11], words[12], words[13], words[14], words[15]};
                     st_u8(destination + group * 128 + c * 32, first);
                     st_u8(destination + group * 128 + c * 32 + 16, second);
+                    }
                 }
             }
         }
@@ -606,8 +644,9 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
 
 }  // namespace
 
-int launch_attention(const void* q, const void* k, const void* v, void* out, int batch, int heads, int queries, int keys,
-                     int head_dim, void* status, cudaStream_t stream) {
+// `out`: bf16 [batch, heads, queries, 256]; or, with `codes` given, e4m3 [batch * queries, heads * 256] at `multiplier` and no `out`.
+int launch_attention(const void* q, const void* k, const void* v, void* out, void* codes, float multiplier, int batch, int heads,
+                     int queries, int keys, int head_dim, void* status, cudaStream_t stream) {
     if (head_dim != ATT_D) return B2_E_UNSUPPORTED;
     const int64_t rows_per_batch = int64_t(heads) * queries;
     if (rows_per_batch * batch >= (int64_t(1) << 31) || int64_t(keys) * batch >= (int64_t(1) << 31)) return B2_E_TOO_LARGE;
@@ -627,6 +666,9 @@ int launch_attention(const void* q, const void* k, const void* v, void* out, int
     if (!make_operand_map(&v_map, v, int64_t(keys) * batch, ATT_D * 2, ATT_KEYS)) return B2_E_DRIVER;
     AttentionArgs args{};
     args.out = static_cast<__nv_bfloat16*>(out);
+    args.codes = static_cast<uint8_t*>(codes);
+    args.multiplier = multiplier;
+    args.queries = queries;
     args.status = static_cast<unsigned int*>(status);
     args.rows_per_batch = int(rows_per_batch);
     args.keys = keys;

@@ -162,21 +162,32 @@ def geglu(
     N.check(status, "b2_geglu")
 
 
-def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None, *, status: torch.Tensor | None = None) -> torch.Tensor:
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None, *, status: torch.Tensor | None = None,
+              codes: torch.Tensor | None = None, multiplier: float | None = None) -> torch.Tensor:
     """Unmasked multi-query attention, ``softmax(q k^T / sqrt(D)) v``: q [B, H, T, 256], k / v [B, 1, S, 256], all
-    contiguous bf16; returns [B, H, T, 256] (``b2_attention``; the reference's ``SDPAAttention``)."""
+    contiguous bf16; returns [B, H, T, 256] (``b2_attention``; the reference's ``SDPAAttention``).  With ``codes`` (a
+    contiguous 1-byte [B*T, H*256] tensor) and ``multiplier`` the output is written as the e4m3 rows of the output
+    projection instead (``b2_attention_fp8``) and ``codes`` is returned."""
     _require_cuda(q, k, v)
     if q.dim() != 4 or k.shape != v.shape or k.dim() != 4 or k.shape[1] != 1 or k.shape[0] != q.shape[0] or k.shape[3] != q.shape[3]:
         raise ValueError("attention requires q [B, H, T, D] and k, v [B, 1, S, D]")
     if any(t.dtype != torch.bfloat16 or not t.is_contiguous() for t in (q, k, v)):
         raise ValueError("attention requires contiguous bf16 tensors")
     batch, heads, queries, head_dim = q.shape
+    if status is None:
+        status = status_word(q.device)
+    if codes is not None:
+        if multiplier is None or codes.element_size() != 1 or not codes.is_contiguous() or codes.numel() != q.numel() or codes.device != q.device:
+            raise ValueError("encoded attention output must be a contiguous 1-byte [B*T, H*D] tensor with a multiplier")
+        with torch.cuda.device(q.device):
+            code = N.load().b2_attention_fp8(q.data_ptr(), k.data_ptr(), v.data_ptr(), codes.data_ptr(), float(multiplier), batch, heads,
+                                             queries, k.shape[2], head_dim, status.data_ptr(), _stream(q.device))
+        N.check(code, "b2_attention_fp8")
+        return codes
     if out is None:
         out = torch.empty_like(q)
     elif out.shape != q.shape or out.dtype != torch.bfloat16 or not out.is_contiguous():
         raise ValueError("attention output must be a contiguous bf16 tensor of the queries' shape")
-    if status is None:
-        status = status_word(q.device)
     with torch.cuda.device(q.device):
         code = N.load().b2_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), batch, heads, queries, k.shape[2],
                                      head_dim, status.data_ptr(), _stream(q.device))

@@ -142,7 +142,9 @@ class FusedAttentionOutput:
         self.scale_value = 448.0 / projection.maximum if self.bits == 8 else self.scale
         self.plans: dict = {}
 
-    def __call__(self, attended: torch.Tensor):
+    def plan_for(self, attended: torch.Tensor):
+        """The encoding workspace for an attention output shaped like ``attended`` [B, H, T, D] (only its shape and device
+        are read)."""
         batch, heads, tokens, head_dim = attended.shape
         key = (batch * tokens, heads * head_dim, torch.cuda.current_stream(attended.device).cuda_stream)
         plan = self.plans.get(key)
@@ -151,6 +153,10 @@ class FusedAttentionOutput:
                 raise RuntimeError("Warm the attention-output encoder before graph capture")
             like = torch.empty((batch * tokens, heads * head_dim), device=attended.device, dtype=torch.bfloat16)
             plan = self.plans[key] = self.quantizer.plan(like, self.bits, self.scale)
+        return plan
+
+    def __call__(self, attended: torch.Tensor):
+        plan = self.plan_for(attended)
         K.bhsd_quant(attended, plan.output, bits=self.bits, scale_value=self.scale_value,
                      scales=plan.scales if self.bits == 4 else None, blocked=plan.blocked if self.bits == 4 else None)
         return plan
@@ -173,13 +179,16 @@ class Projection(nn.Module):
         self.attention_output: FusedAttentionOutput | None = None
         self.maximum, self.recording = 0.0, False
 
-    def attended(self, attended: torch.Tensor, residual: torch.Tensor, add_residual: bool = True) -> torch.Tensor:
+    def attended(self, attended: torch.Tensor | None, residual: torch.Tensor, add_residual: bool = True, encoded=None) -> torch.Tensor:
         """``self(attended.transpose(1, 2).flatten(2), residual)`` for an attention output [B, H, T, D], the transpose
         and the activation encoding in one launch (calibrated plans only).  ``add_residual=False``: the projection
-        alone, shaped like ``residual`` (the adaptive blocks add it through the next norm's gate)."""
+        alone, shaped like ``residual`` (the adaptive blocks add it through the next norm's gate).  ``encoded``: the
+        attention kernel already wrote the encoded rows (``b2_attention_fp8``); ``attended`` is then not read."""
         rows = residual.reshape(-1, residual.shape[-1])
-        like = _Shape((rows.shape[0], attended.shape[1] * attended.shape[3]), rows)
-        output = self.plan.apply(like, self.attention_output(attended), bias=self.dense_bias, residual=rows if add_residual else None)
+        if encoded is None:
+            encoded = self.attention_output(attended)
+        like = _Shape((rows.shape[0], self.plan.input_dim), rows)
+        output = self.plan.apply(like, encoded, bias=self.dense_bias, residual=rows if add_residual else None)
         return output.reshape(residual.shape)
 
     def layer_normed(self, x: torch.Tensor, norm: nn.LayerNorm) -> torch.Tensor:
@@ -297,6 +306,7 @@ class GemmaBlock(nn.Module):
         self.mlp_norm: FusedNorm | None = None
         self.fused_norm = True
         self.native_attention = True        # b2_attention instead of torch's scaled_dot_product_attention (head dimension 256, one kv head)
+        self.encode_in_attention = True     # FP8 output projection: the attention kernel writes its encoded input rows
 
     def mlp(self, x: torch.Tensor) -> torch.Tensor:
         """x + down(gelu_tanh(gate(n)) * up(n)), n = RMSNorm(x)."""
@@ -376,19 +386,26 @@ class GemmaBlock(nn.Module):
         # ten-token chunks) cut the keys of a tile across a thread-block cluster instead of walking them serially
         # (measured, 8 heads x 10 queries over 570 keys: B = 1 / 8 / 32 / 64 take 7.2 / 7.7 / 12.3 / 15.0 us against
         # 11.3 / 20.7 / 33.1 / 63.0 for torch's kernel).
-        if self.native_attention and shape.head_dim == 256 and shape.kv_heads == 1:
+        native = self.native_attention and shape.head_dim == 256 and shape.kv_heads == 1
+        output_encoder = self.o_proj.attention_output if self.fused_norm else None
+        encoded = None
+        if native and output_encoder is not None and output_encoder.bits == 8 and self.encode_in_attention:
+            # the attention kernel writes the e4m3 rows of the output projection itself (b2_attention_fp8): one launch less
+            encoded, attended = output_encoder.plan_for(q), None
+            K.attention(q, k, v, codes=encoded.output, multiplier=output_encoder.scale_value)
+        elif native:
             attended = K.attention(q, k, v)           # tcgen05 multi-query attention (b2_attention)
         else:
             attended = F.scaled_dot_product_attention(q, k, v, enable_gqa=shape.heads != shape.kv_heads)
         if self.adaptive:
             if self.o_proj.attention_output is not None and self.fused_norm:
-                projected = self.o_proj.attended(attended, x, add_residual=False)
+                projected = self.o_proj.attended(attended, x, add_residual=False, encoded=encoded)
             else:
                 projected = self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim))
             x, pending = self.adaptive_mlp(x, projected, attention_gate, modulations[1])
             return x, own_kv, pending
         if self.o_proj.attention_output is not None and self.fused_norm:
-            x = self.o_proj.attended(attended, x)
+            x = self.o_proj.attended(attended, x, encoded=encoded)
         else:
             x = self.o_proj(attended.transpose(1, 2).reshape(batch, tokens, q_dim), residual=x)
         return self.mlp(x), own_kv

@@ -23,7 +23,8 @@ extern "C" {
 
 /* 6: launches of at most 128 tokens may run on the cluster schedule (weights as the MMA's "A" operand, K split across a
  * thread-block cluster; B2_LINEAR_CLUSTER asks for it whenever it applies, B2_LINEAR_SINGLE_CTA opts out);
- * b2_gelu_table_range returns ranges on multiples of eight codes; FP8 launches accept 32 features per tile.
+ * b2_gelu_table_range returns ranges on multiples of eight codes; FP8 launches accept 32 features per tile;
+ * b2_attention_fp8.
  * 5: b2_attention.
  * 4: launches with more than 128 tokens run on pairs of SMs (B2_LINEAR_SINGLE_CTA opts out); unknown flag bits in
  * b2_linear_desc are rejected; the opt-in cluster split of K of version 3 (flag value 32) is gone.
@@ -206,6 +207,13 @@ int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q
  * (NULL allowed). */
 int b2_attention(const void* q, const void* k, const void* v, void* out, int32_t batch, int32_t heads, int32_t queries,
                  int32_t keys, int32_t head_dim, void* status, void* stream);
+
+/* The same attention with the output written straight as the e4m3 rows of the output projection: `codes`
+ * [batch * queries, heads * head_dim] = e4m3(bf16(out[b, h, t, :]) * multiplier) at row b * queries + t, columns of head h --
+ * bit-identical to b2_attention followed by b2_bhsd_quant (bits 8, scale_value = multiplier), one launch less on the
+ * expert's chain of short kernels.  multiplier: 448 / calibrated maximum, finite and positive. */
+int b2_attention_fp8(const void* q, const void* k, const void* v, void* codes, float multiplier, int32_t batch, int32_t heads,
+                     int32_t queries, int32_t keys, int32_t head_dim, void* status, void* stream);
 
 /* RMSNorm (+ residual update, + adaptive modulation) fused with the activation encoder: the step in front of
  * every quantised projection.  Replaces cc_norm_quant and cc_norm_quant_reduce

@@ -62,6 +62,28 @@ def test_attention_matches_float32(device, batch, heads, queries, keys, spread):
     assert error <= 1.5 * library + 1e-4, (error, library)
 
 
+@pytest.mark.parametrize("batch,heads,queries,keys", [(1, 8, 10, 580), (3, 8, 10, 570), (2, 8, 560, 560), (40, 8, 10, 70), (2, 3, 77, 64)])
+def test_encoded_output_matches_attention_then_encoder(device, batch, heads, queries, keys):
+    """b2_attention_fp8 writes the e4m3 rows [B*T, H*256] of the output projection: the same bytes as b2_attention followed
+    by b2_bhsd_quant, on the split (clusters over the keys) and the one-CTA-per-tile paths."""
+    generator = torch.Generator(device=device).manual_seed(batch + heads + queries + keys)
+    q = torch.randn((batch, heads, queries, 256), device=device, generator=generator).to(torch.bfloat16)
+    k = torch.randn((batch, 1, keys, 256), device=device, generator=generator).to(torch.bfloat16)
+    v = (3.0 * torch.randn((batch, 1, keys, 256), device=device, generator=generator)).to(torch.bfloat16)
+    multiplier = 448.0 / 2.5                    # values beyond 2.5 saturate
+    status = torch.zeros(1, device=device, dtype=torch.int32)
+    out = K.attention(q, k, v, status=status)
+    want = torch.zeros((batch * queries, heads * 256), device=device, dtype=torch.uint8)
+    K.bhsd_quant(out, want, bits=8, scale_value=multiplier)
+    got = torch.full((batch * queries + 1, heads * 256), 0x7f, device=device, dtype=torch.uint8)
+    K.attention(q, k, v, codes=got[:-1], multiplier=multiplier, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(got[:-1], want)
+    assert (got[-1] == 0x7f).all(), "wrote past the last row"
+    assert want.any()
+
+
 def test_attention_rejects_other_shapes(device):
     q = torch.zeros((1, 2, 4, 128), device=device, dtype=torch.bfloat16)
     k = torch.zeros((1, 1, 4, 128), device=device, dtype=torch.bfloat16)
