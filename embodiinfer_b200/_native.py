@@ -69,7 +69,16 @@ class LinearDesc(ctypes.Structure):
         ("status", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_int64),
+        ("rope", ctypes.c_void_p),
     ]
+
+
+class RopeDesc(ctypes.Structure):
+    """``b2_rope_desc``."""
+
+    _fields_ = [(name, ctypes.c_void_p) for name in ("sine", "cosine", "q_out", "k_out", "v_out")] + \
+               [("factor_batch_stride", ctypes.c_int64)] + \
+               [(name, ctypes.c_int32) for name in ("batch", "tokens", "heads", "kv_heads", "head_dim", "kv_capacity", "kv_offset")]
 
 
 class NormDesc(ctypes.Structure):

@@ -154,9 +154,13 @@ class B200Projection:
         *,
         bias: torch.Tensor | None = None,
         residual: torch.Tensor | None = None,
+        rope: dict | None = None,
     ) -> torch.Tensor:
         """bf16 ``[..., N]``; optional bias and residual are added in the epilogue, each with its own
-        bf16 rounding, exactly like separate ``output + bias`` / ``output + residual`` tensor adds."""
+        bf16 rounding, exactly like separate ``output + bias`` / ``output + residual`` tensor adds.
+        ``rope`` (FP8 packed QKV projections of at most 128 rows): the arguments of ``kernels.rope_split`` without
+        ``qkv`` -- the launch writes rotated queries, keys and values to their buffers instead of returning the
+        projection (``b2_linear_desc.rope``); the returned tensor is then not written."""
         shape = (*inputs.shape[:-1], self.output_dim)
         if self.precision == "bf16":
             if inputs.shape[-1] != self.input_dim or inputs.device != self.device or inputs.dtype != torch.bfloat16:
@@ -173,7 +177,7 @@ class B200Projection:
         K.linear(
             epilogue=N.EPI_LINEAR, out_format=N.OUT_BF16, tokens=rows, features=self.output_dim, width=self.input_dim,
             out=output, bias=bias, residual=None if residual is None else residual.reshape(rows, self.output_dim),
-            workspace=workspace, **self._operands(encoded),
+            workspace=workspace, rope=rope, **self._operands(encoded),
         )
         return output.reshape(shape)
 

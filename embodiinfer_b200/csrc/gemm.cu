@@ -803,7 +803,7 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     if (d->flags & ~KNOWN_FLAGS) return B2_E_INVALID;
     if (!planning) {
         if (d->act == nullptr || d->weight == nullptr || d->act_scale == nullptr || d->weight_scale == nullptr ||
-            d->out == nullptr)
+            (d->out == nullptr && d->rope == nullptr))
             return B2_E_INVALID;
         if (!aligned16(d->act) || !aligned16(d->weight) || !aligned16(d->out)) return B2_E_INVALID;
     }
@@ -854,8 +854,14 @@ int run_linear(const b2_linear_desc* d, cudaStream_t stream, int64_t* workspace_
     }
 
     // At most 128 tokens: the weight becomes the "A" operand and a cluster shares the K of a feature tile (gemm_skinny.cu).
+    // Only that schedule has the attention preparation (d->rope) as an epilogue.
+    if (d->rope != nullptr) {
+        if (!skinny_rope_supported(d)) return B2_E_UNSUPPORTED;
+        epilogue = EPI_ROPE;
+    }
     {
         const SkinnyPlan plan = skinny_plan(d, geglu);
+        if (d->rope != nullptr && plan.splits == 0) return B2_E_UNSUPPORTED;
         if (plan.splits != 0) {
             if (planning) {
                 *workspace_need = 0;

@@ -40,7 +40,8 @@ constexpr int SMEM_LIMIT = 227 * 1024;
 constexpr int MAX_COMPACT_GELU = 4096;             // magnitude codes of the GELU table kept in shared memory
 constexpr int SMEM_MINIMUM = 120 * 1024;           // keeps a second CTA (and its TMEM request) off the SM
 
-enum { EPI_LINEAR = 0, EPI_GEGLU_BF16 = 1, EPI_GEGLU_FP8 = 2, EPI_GEGLU_NVFP4 = 3, EPI_GELU_BF16 = 4, EPI_GELU_FP8 = 5 };
+enum { EPI_LINEAR = 0, EPI_GEGLU_BF16 = 1, EPI_GEGLU_FP8 = 2, EPI_GEGLU_NVFP4 = 3, EPI_GELU_BF16 = 4, EPI_GELU_FP8 = 5,
+       EPI_ROPE = 6 };          // cluster schedule only: the packed QKV projection with the attention preparation as its epilogue
 __host__ __device__ constexpr bool is_gated(int epi) { return epi >= EPI_GEGLU_BF16 && epi <= EPI_GEGLU_NVFP4; }
 
 struct KernelArgs {
@@ -72,6 +73,14 @@ struct KernelArgs {
     int a_box_bytes;             // bytes of the token box of one K stage: 128 rows, or fewer (a multiple of 8) when the launch has
                                  // one token tile with fewer tokens -- the rows beyond the box are whatever shared memory holds,
                                  // they only feed accumulator rows that are never stored
+    // EPI_ROPE (b2_rope_desc): rotary factors, destinations and shapes of the attention preparation
+    const float* rope_sine;
+    const float* rope_cosine;
+    __nv_bfloat16* rope_q;
+    __nv_bfloat16* rope_k;
+    __nv_bfloat16* rope_v;
+    long long rope_batch_stride;
+    int rope_tokens, rope_heads, rope_kv_heads, rope_capacity, rope_offset;
     unsigned int* tickets;       // split-K: one arrival counter per tile (zero between launches)
     float* partials;             // split-K: [tile][split][128][tile_n] fp32
 };
@@ -432,6 +441,7 @@ struct SkinnyPlan {
     int gelu_span = 0;           // magnitude codes of the GELU table kept in shared memory
 };
 SkinnyPlan skinny_plan(const b2_linear_desc* d, bool geglu);
+bool skinny_rope_supported(const b2_linear_desc* d);
 int run_linear_skinny(const b2_linear_desc* d, int epilogue, const SkinnyPlan& plan, cudaStream_t stream);
 
 }  // namespace b2

@@ -89,7 +89,8 @@ __global__ void __launch_bounds__(SKINNY_THREADS, 1)
 skinny_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap weight_map,
                      const KernelArgs args) {
     constexpr bool GEGLU = is_gated(EPI);
-    constexpr bool USES_TABLE = EPI != EPI_LINEAR;
+    constexpr bool ROPE = EPI == EPI_ROPE;      // tile = 64 features of a head and their 64 rotation partners (two planes, like gate / up)
+    constexpr bool USES_TABLE = EPI != EPI_LINEAR && !ROPE;
     constexpr bool NVFP4 = KIND == B2_KIND_NVFP4;
     constexpr uint32_t WEIGHT_BYTES = 128 * STAGE_K_BYTES;
     constexpr uint32_t SCALE_PART_BYTES = SCALE_ATOMS_PER_STAGE * SCALE_ATOM_BYTES;
@@ -157,7 +158,8 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_c
         // prefetch: it only moves lines into the L2, the loads below still read them after the dependency wait
         if (elect_one()) {
             for (int i = 0; i < atoms; ++i) {
-                if (GEGLU) tma_prefetch_l2_3d(&weight_map, (kb_begin + i) * STAGE_K_BYTES, f0, 0);
+                if (ROPE) tma_prefetch_l2_3d(&weight_map, (kb_begin + i) * STAGE_K_BYTES, (tile & 1) * 64, 2 * (tile >> 1));
+                else if (GEGLU) tma_prefetch_l2_3d(&weight_map, (kb_begin + i) * STAGE_K_BYTES, f0, 0);
                 else tma_prefetch_l2_2d(&weight_map, (kb_begin + i) * STAGE_K_BYTES, f0);
             }
         }
@@ -192,7 +194,8 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_c
                 const uint32_t a_smem = base + uint32_t(i) * stage_bytes;
                 const uint32_t copy_bytes = uint32_t(kb == num_kb - 1 ? tail_atoms : SCALE_ATOMS_PER_STAGE) * SCALE_ATOM_BYTES;
                 mbar_expect_tx(bar, stage_bytes + (NVFP4 ? 2u * copy_bytes : 0u));
-                if (GEGLU) tma_load_3d(a_smem, &weight_map, bar, kb * STAGE_K_BYTES, f0, 0);
+                if (ROPE) tma_load_3d(a_smem, &weight_map, bar, kb * STAGE_K_BYTES, (tile & 1) * 64, 2 * (tile >> 1));
+                else if (GEGLU) tma_load_3d(a_smem, &weight_map, bar, kb * STAGE_K_BYTES, f0, 0);
                 else tma_load_2d(a_smem, &weight_map, bar, kb * STAGE_K_BYTES, f0);
                 tma_load_2d(a_smem + WEIGHT_BYTES, &act_map, bar, kb * STAGE_K_BYTES, 0);
                 if (NVFP4) {
@@ -336,7 +339,54 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_c
             const int local = item >> 2, part = item & 3;
             const int token = first_token + local;
             const uint32_t sums = receive_base + uint32_t(local) * ROW_BYTES;
-            if (GEGLU) {
+            if (ROPE) {
+                // 16 features of a half head (sums in floats [16 part, 16 part + 16)) and their partners 128 features on (64
+                // floats further): the projection's bf16 result, then b2_rope_split's rotation, queries / keys / values to
+                // their places
+                uint32_t acc[32];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 x = ld_shared_f4(sums + uint32_t(part) * 64u + 16u * q), y = ld_shared_f4(sums + 256u + uint32_t(part) * 64u + 16u * q);
+                    acc[4 * q] = __float_as_uint(x.x); acc[4 * q + 1] = __float_as_uint(x.y);
+                    acc[4 * q + 2] = __float_as_uint(x.z); acc[4 * q + 3] = __float_as_uint(x.w);
+                    acc[16 + 4 * q] = __float_as_uint(y.x); acc[16 + 4 * q + 1] = __float_as_uint(y.y);
+                    acc[16 + 4 * q + 2] = __float_as_uint(y.z); acc[16 + 4 * q + 3] = __float_as_uint(y.w);
+                }
+                uint32_t words[16];
+                linear_scale_chunk(acc, scale, round_scale, words);
+                const int head = tile >> 1, first_dim = (tile & 1) * 64 + part * 16;
+                const int b = token / args.rope_tokens, t = token - b * args.rope_tokens;
+                __nv_bfloat16* destination;
+                bool rotate = true;
+                if (head < args.rope_heads) {
+                    destination = args.rope_q + ((int64_t(b) * args.rope_heads + head) * args.rope_tokens + t) * 256;
+                } else if (head < args.rope_heads + args.rope_kv_heads) {
+                    destination = args.rope_k + ((int64_t(b) * args.rope_kv_heads + (head - args.rope_heads)) * args.rope_capacity + args.rope_offset + t) * 256;
+                } else {
+                    destination = args.rope_v + ((int64_t(b) * args.rope_kv_heads + (head - args.rope_heads - args.rope_kv_heads)) * args.rope_capacity + args.rope_offset + t) * 256;
+                    rotate = false;
+                }
+                destination += first_dim;
+                uint32_t low[8], high[8];
+                if (rotate) {
+                    const float* s = args.rope_sine + b * args.rope_batch_stride + int64_t(t) * 128 + first_dim;
+                    const float* c = args.rope_cosine + b * args.rope_batch_stride + int64_t(t) * 128 + first_dim;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float2 x = bf16x2_to_float2(words[i]), y = bf16x2_to_float2(words[8 + i]);
+                        const float c0 = __ldg(c + 2 * i), c1 = __ldg(c + 2 * i + 1), s0 = __ldg(s + 2 * i), s1 = __ldg(s + 2 * i + 1);
+                        low[i] = float2_to_bf16x2(make_float2(__fsub_rn(__fmul_rn(x.x, c0), __fmul_rn(y.x, s0)), __fsub_rn(__fmul_rn(x.y, c1), __fmul_rn(y.y, s1))));
+                        high[i] = float2_to_bf16x2(make_float2(__fadd_rn(__fmul_rn(y.x, c0), __fmul_rn(x.x, s0)), __fadd_rn(__fmul_rn(y.y, c1), __fmul_rn(x.y, s1))));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { low[i] = words[i]; high[i] = words[8 + i]; }
+                }
+                store_u4(destination, low[0], low[1], low[2], low[3]);
+                store_u4(destination + 8, low[4], low[5], low[6], low[7]);
+                store_u4(destination + 128, high[0], high[1], high[2], high[3]);
+                store_u4(destination + 136, high[4], high[5], high[6], high[7]);
+            } else if (GEGLU) {
                 // 16 features: gate sums in floats [16 part, 16 part + 16), up sums 64 floats further
                 uint32_t gate_acc[16], up_acc[16];
 #pragma unroll
@@ -357,7 +407,7 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_c
                     acc[4 * q] = __float_as_uint(v.x); acc[4 * q + 1] = __float_as_uint(v.y);
                     acc[4 * q + 2] = __float_as_uint(v.z); acc[4 * q + 3] = __float_as_uint(v.w);
                 }
-                epilogue_linear_chunk<GEGLU ? EPI_LINEAR : EPI>(acc, args, scale, round_scale, token, f0 + part * 32, compact_table,
+                epilogue_linear_chunk<(GEGLU || ROPE) ? EPI_LINEAR : EPI>(acc, args, scale, round_scale, token, f0 + part * 32, compact_table,
                                                                 out_scale, out_scale_rcp, true_div);
             }
         }
@@ -402,6 +452,7 @@ SkinnyPlan skinny_plan(const b2_linear_desc* d, bool geglu) {
     if (d->flags & (B2_LINEAR_SINGLE_CTA | B2_LINEAR_PAIRS | B2_LINEAR_STREAM_TOKENS)) return plan;
     const bool nvfp4 = d->kind == B2_KIND_NVFP4;
     if (geglu && nvfp4 && (!(d->flags & B2_LINEAR_PAIRED_GATE_UP_SCALES) || d->features % 64 != 0)) return plan;
+    const bool rope = d->rope != nullptr;                 // only this schedule has the attention preparation as an epilogue
     const int k_bytes = nvfp4 ? d->width / 2 : d->width;
     const int num_kb = (k_bytes + STAGE_K_BYTES - 1) / STAGE_K_BYTES;
     const int columns = (d->tokens + 15) / 16 * 16;
@@ -418,7 +469,7 @@ SkinnyPlan skinny_plan(const b2_linear_desc* d, bool geglu) {
         const int64_t bytes = 1024 + (operand_bytes > staging_bytes ? operand_bytes : staging_bytes) +
                               int64_t(splits) * tokens_per_rank * SKINNY_ROW_FLOATS * 4 + 8 * MAX_STAGES + 64 + 4 * span;
         if (atoms <= MAX_STAGES && bytes <= SMEM_LIMIT && (!nvfp4 || columns + 32 * atoms <= TMEM_COLUMNS)) {
-            if (!(d->flags & B2_LINEAR_CLUSTER)) {
+            if (!(d->flags & B2_LINEAR_CLUSTER) && !rope) {
                 const int64_t waves = (int64_t(tiles) * splits + sm_count() - 1) / sm_count();
                 const int64_t tile_ns = (nvfp4 ? 460 : 140) + int64_t(geglu ? 270 : 150) * (d->width / 128);
                 const int64_t cluster_ns = waves * (200 * int64_t(atoms) + 26 * int64_t(d->tokens));
@@ -434,6 +485,35 @@ SkinnyPlan skinny_plan(const b2_linear_desc* d, bool geglu) {
         }
     }
     return plan;
+}
+
+// A launch with `d->rope` set that the EPI_ROPE epilogue handles (run_linear returns B2_E_UNSUPPORTED otherwise).
+bool skinny_rope_supported(const b2_linear_desc* d) {
+    const b2_rope_desc* r = d->rope;
+    if (r == nullptr) return false;
+    if (d->kind != B2_KIND_FP8 || d->epilogue != B2_EPI_LINEAR || d->out_format != B2_OUT_BF16 || d->bias != nullptr || d->residual != nullptr)
+        return false;
+    if (r->head_dim != 256 || r->batch <= 0 || r->tokens <= 0 || r->heads <= 0 || r->kv_heads <= 0) return false;
+    if (d->tokens != r->batch * r->tokens || d->tokens > SKINNY_MAX_TOKENS || d->features != (r->heads + 2 * r->kv_heads) * 256) return false;
+    if (r->kv_offset < 0 || r->kv_offset + r->tokens > r->kv_capacity || r->factor_batch_stride < 0) return false;
+    if (r->sine == nullptr || r->cosine == nullptr || r->q_out == nullptr || r->k_out == nullptr || r->v_out == nullptr) return false;
+    const uintptr_t alignment = reinterpret_cast<uintptr_t>(r->sine) | reinterpret_cast<uintptr_t>(r->cosine) |
+                                reinterpret_cast<uintptr_t>(r->q_out) | reinterpret_cast<uintptr_t>(r->k_out) | reinterpret_cast<uintptr_t>(r->v_out);
+    return (alignment & 15u) == 0;
+}
+
+// The packed QKV weight [(heads + 2 kv heads) * 256, row_bytes] as [row_bytes][128 rows][2 halves per head ...]: one box of
+// 64 rows x 128 bytes x 2 halves lands as [64 features of a half head | their 64 rotation partners].
+static bool make_rope_map(CUtensorMap* map, const void* pointer, int64_t total_heads, int64_t row_bytes) {
+    EncodeTiledFn encode = encode_tiled_entry();
+    if (encode == nullptr) return false;
+    const cuuint64_t dims[3] = {cuuint64_t(row_bytes), 128, cuuint64_t(2 * total_heads)};
+    const cuuint64_t strides[2] = {cuuint64_t(row_bytes), cuuint64_t(row_bytes) * 128};
+    const cuuint32_t box[3] = {cuuint32_t(STAGE_K_BYTES), 64, 2};
+    const cuuint32_t element_strides[3] = {1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(pointer), dims, strides, box, element_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int KIND, int EPI>
@@ -512,6 +592,22 @@ int run_linear_skinny(const b2_linear_desc* d, int epilogue, const SkinnyPlan& p
 
     CUtensorMap act_map, weight_map;
     if (!make_operand_map(&act_map, d->act, d->tokens, args.k_bytes, plan.columns)) return B2_E_DRIVER;
+    if (epilogue == EPI_ROPE) {
+        const b2_rope_desc* r = d->rope;
+        args.rope_sine = static_cast<const float*>(r->sine);
+        args.rope_cosine = static_cast<const float*>(r->cosine);
+        args.rope_q = static_cast<__nv_bfloat16*>(r->q_out);
+        args.rope_k = static_cast<__nv_bfloat16*>(r->k_out);
+        args.rope_v = static_cast<__nv_bfloat16*>(r->v_out);
+        args.rope_batch_stride = r->factor_batch_stride;
+        args.rope_tokens = r->tokens;
+        args.rope_heads = r->heads;
+        args.rope_kv_heads = r->kv_heads;
+        args.rope_capacity = r->kv_capacity;
+        args.rope_offset = r->kv_offset;
+        if (!make_rope_map(&weight_map, d->weight, r->heads + 2 * r->kv_heads, args.k_bytes)) return B2_E_DRIVER;
+        return launch_skinny<B2_KIND_FP8, EPI_ROPE>(act_map, weight_map, args, plan.shared_bytes, stream);
+    }
     if (geglu ? !make_gated_map(&weight_map, d->weight, d->features, args.k_bytes, 64)
               : !make_operand_map(&weight_map, d->weight, d->features, args.k_bytes, 128))
         return B2_E_DRIVER;

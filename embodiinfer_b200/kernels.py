@@ -195,6 +195,25 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tens
     return out
 
 
+def _rope_desc(sine: torch.Tensor, cosine: torch.Tensor, q_out: torch.Tensor, k_out: torch.Tensor, v_out: torch.Tensor, *,
+               batch: int, tokens: int, heads: int, kv_heads: int, head_dim: int, kv_offset: int = 0) -> "N.RopeDesc":
+    """The ``b2_rope_desc`` of these arguments (checked like :func:`rope_split`'s)."""
+    _require_cuda(sine, cosine, q_out, k_out, v_out)
+    for factor in (sine, cosine):
+        if factor.dtype != torch.float32 or not factor.is_contiguous() or factor.shape[-2:] != (tokens, head_dim // 2):
+            raise ValueError("rope requires contiguous fp32 factors [tokens, head_dim/2] (optionally with a batch dimension)")
+    if q_out.shape != (batch, heads, tokens, head_dim) or not q_out.is_contiguous() or q_out.dtype != torch.bfloat16:
+        raise ValueError("q_out must be a contiguous bf16 [batch, heads, tokens, head_dim] tensor")
+    for cache in (k_out, v_out):
+        if cache.ndim != 4 or cache.shape[0] != batch or cache.shape[1] != kv_heads or cache.shape[3] != head_dim or \
+                not cache.is_contiguous() or cache.dtype != torch.bfloat16 or cache.shape != k_out.shape:
+            raise ValueError("key/value buffers must be contiguous bf16 [batch, kv_heads, capacity, head_dim] tensors")
+    return N.RopeDesc(sine=sine.data_ptr(), cosine=cosine.data_ptr(), q_out=q_out.data_ptr(), k_out=k_out.data_ptr(),
+                      v_out=v_out.data_ptr(), factor_batch_stride=tokens * (head_dim // 2) if sine.ndim == 3 else 0,
+                      batch=batch, tokens=tokens, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                      kv_capacity=k_out.shape[2], kv_offset=kv_offset)
+
+
 def rope_split(qkv: torch.Tensor, sine: torch.Tensor, cosine: torch.Tensor, q_out: torch.Tensor, k_out: torch.Tensor,
                v_out: torch.Tensor, *, batch: int, tokens: int, heads: int, kv_heads: int, head_dim: int, kv_offset: int = 0) -> None:
     """Split a packed QKV projection, rotate queries and keys, write ``q_out`` [B, heads, T, D] and the
@@ -407,6 +426,7 @@ def linear(
     feature_tile: int = 0,
     gelu_range: tuple[int, int] = (0, 0),
     workspace: torch.Tensor | None | bool = None,
+    rope: dict | None = None,
 ) -> None:
     """One fused tensor-core launch, see ``b2_linear``.  ``status``: the word an expired bounded wait is reported in
     (default: the device's word, read by :func:`check_status`).  ``workspace``: zeroed split-K scratch, e.g.
@@ -448,6 +468,11 @@ def linear(
     )
     if isinstance(workspace, torch.Tensor):
         desc.workspace, desc.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    preparation = None
+    if rope is not None:
+        # the attention preparation as this projection's epilogue (``b2_linear_desc.rope``); `out` is not written
+        preparation = _rope_desc(**rope)
+        desc.rope = ctypes.addressof(preparation)
     with torch.cuda.device(device):
         code = N.load().b2_linear(ctypes.byref(desc), _stream(device))
     N.check(code, "b2_linear")

@@ -307,6 +307,7 @@ class GemmaBlock(nn.Module):
         self.fused_norm = True
         self.native_attention = True        # b2_attention instead of torch's scaled_dot_product_attention (head dimension 256, one kv head)
         self.encode_in_attention = True     # FP8 output projection: the attention kernel writes its encoded input rows
+        self.rope_in_projection = True      # adaptive blocks, FP8: the QKV projection's launch does the attention preparation
 
     def mlp(self, x: torch.Tensor) -> torch.Tensor:
         """x + down(gelu_tanh(gate(n)) * up(n)), n = RMSNorm(x)."""
@@ -359,10 +360,25 @@ class GemmaBlock(nn.Module):
         shape = self.shape
         batch, tokens, _ = x.shape
         attention_gate = None
+        q = torch.empty((batch, shape.heads, tokens, shape.head_dim), device=x.device, dtype=x.dtype)
+        if kv_buffers is None:
+            k = torch.empty((batch, shape.kv_heads, tokens, shape.head_dim), device=x.device, dtype=x.dtype)
+            v = torch.empty_like(k)
+        else:
+            k, v = kv_buffers
+        preparation = dict(sine=rope[0], cosine=rope[1], q_out=q, k_out=k, v_out=v, batch=batch, tokens=tokens, heads=shape.heads,
+                           kv_heads=shape.kv_heads, head_dim=shape.head_dim, kv_offset=k.shape[2] - tokens)
+        qkv = None
         if self.adaptive:
             if self.qkv.norm is not None and self.fused_norm:
                 x, encoded, attention_gate = self.qkv.norm.modulated(x.contiguous(), modulations[0], pending)
-                qkv = self.qkv.plan.apply(x.reshape(-1, x.shape[-1]), encoded, bias=self.qkv.dense_bias).reshape(batch, tokens, -1)
+                # A packed FP8 QKV projection of a handful of rows: the attention preparation is the launch's epilogue
+                # (b2_linear_desc.rope) -- measured faster than projection + b2_rope_split up to ~96 rows.
+                if (self.rope_in_projection and self.qkv.plan.precision == "fp8" and self.qkv.dense_bias is None
+                        and shape.head_dim == 256 and batch * tokens <= 96):
+                    self.qkv.plan.apply(x.reshape(-1, x.shape[-1]), encoded, rope=preparation)
+                else:
+                    qkv = self.qkv.plan.apply(x.reshape(-1, x.shape[-1]), encoded, bias=self.qkv.dense_bias).reshape(batch, tokens, -1)
             else:
                 x = _gated_residual(x, pending)
                 normed, attention_gate = _ada_rms_norm(x, modulations[0])
@@ -372,15 +388,9 @@ class GemmaBlock(nn.Module):
         else:
             qkv = self.qkv(_rms_norm(x, self.input_scale))
         q_dim = shape.heads * shape.head_dim
-        # one launch: split, rotate q and k, [B, heads, T, D] queries, keys / values written into the buffers
-        q = torch.empty((batch, shape.heads, tokens, shape.head_dim), device=x.device, dtype=x.dtype)
-        if kv_buffers is None:
-            k = torch.empty((batch, shape.kv_heads, tokens, shape.head_dim), device=x.device, dtype=x.dtype)
-            v = torch.empty_like(k)
-        else:
-            k, v = kv_buffers
-        K.rope_split(qkv.reshape(batch * tokens, -1), rope[0], rope[1], q, k, v, batch=batch, tokens=tokens, heads=shape.heads,
-                     kv_heads=shape.kv_heads, head_dim=shape.head_dim, kv_offset=k.shape[2] - tokens)
+        if qkv is not None:
+            # one launch: split, rotate q and k, [B, heads, T, D] queries, keys / values written into the buffers
+            K.rope_split(qkv.reshape(batch * tokens, -1), **preparation)
         own_kv = (k, v)
         # b2_attention: one CTA per 128 query rows of a batch element; launches of few such tiles (a handful of observations'
         # ten-token chunks) cut the keys of a tile across a thread-block cluster instead of walking them serially

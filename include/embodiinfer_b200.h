@@ -24,7 +24,7 @@ extern "C" {
 /* 6: launches of at most 128 tokens may run on the cluster schedule (weights as the MMA's "A" operand, K split across a
  * thread-block cluster; B2_LINEAR_CLUSTER asks for it whenever it applies, B2_LINEAR_SINGLE_CTA opts out);
  * b2_gelu_table_range returns ranges on multiples of eight codes; FP8 launches accept 32 features per tile;
- * b2_attention_fp8.
+ * b2_attention_fp8; b2_linear_desc.rope (the attention preparation as the projection's epilogue).
  * 5: b2_attention.
  * 4: launches with more than 128 tokens run on pairs of SMs (B2_LINEAR_SINGLE_CTA opts out); unknown flag bits in
  * b2_linear_desc are rejected; the opt-in cluster split of K of version 3 (flag value 32) is gone.
@@ -144,6 +144,18 @@ int b2_geglu(const void* gate, const void* up, void* output, void* scales, void*
                                  it by an estimate of both schedules' times (few tokens, long K); B2_LINEAR_SINGLE_CTA opts out.
                                  K is summed in a different order than in the tile schedules: results agree to fp32 rounding. */
 
+/* The attention preparation of b2_rope_split as the epilogue of the packed QKV projection (b2_linear_desc.rope); fields as
+ * in b2_rope_split. */
+typedef struct b2_rope_desc {
+    const void* sine;
+    const void* cosine;
+    void* q_out;
+    void* k_out;
+    void* v_out;
+    int64_t factor_batch_stride;
+    int32_t batch, tokens, heads, kv_heads, head_dim, kv_capacity, kv_offset;
+} b2_rope_desc;
+
 typedef struct b2_linear_desc {
     int32_t kind;        /* B2_KIND_* */
     int32_t epilogue;    /* B2_EPI_* */
@@ -175,6 +187,12 @@ typedef struct b2_linear_desc {
                                   launch leaves its first 1024 bytes (the ticket words) zero again, so
                                   launches that follow one another on a stream may share it) */
     int64_t workspace_bytes;   /* size of `workspace`; split K is used only when b2_linear_workspace_bytes(desc) fits */
+    const b2_rope_desc* rope;  /* NULL, or: this launch is a packed QKV projection whose result goes through b2_rope_split's
+                                  arithmetic in the epilogue -- rotated queries to q_out, rotated keys and plain values into the
+                                  key/value buffers -- instead of being stored to `out` (ignored, may be NULL).  Same bits as
+                                  b2_linear followed by b2_rope_split, one launch less.  Cluster schedule only: B2_KIND_FP8,
+                                  B2_EPI_LINEAR, no bias, no residual, tokens == batch * rope->tokens <= 128, head_dim 256,
+                                  features == (heads + 2 kv_heads) * 256; anything else: B2_E_UNSUPPORTED. */
 } b2_linear_desc;
 
 /* Attention preparation after a packed QKV projection (the steps between the projection and the attention in

@@ -43,7 +43,7 @@ def test_linear_desc_layout_matches_header():
     text = HEADER.read_text()
     body = re.search(r"typedef struct b2_linear_desc \{(.*?)\} b2_linear_desc;", text, flags=re.S).group(1)
     body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
-    fields = re.findall(r"(?:const\s+)?(?:int32_t|int64_t|void\*)\s+(\w+);", body)
+    fields = re.findall(r"(?:const\s+)?(?:int32_t|int64_t|void\*|b2_rope_desc\*)\s+(\w+);", body)
     assert fields == [name for name, _ in N.LinearDesc._fields_]
 
 
