@@ -481,17 +481,16 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             //     land on them
             cluster_arrive();
             cluster_wait();
-            if (reader == 0) {
-                for (uint32_t step = 1; step <= splits; ++step) {       // starting with the next rank: no owner is everyone's first
-                    const uint32_t r = rank + step < splits ? rank + step : rank + step - splits;
-                    const int first = int(r) * args.rows_per_rank;
-                    int count = tile_rows - first;
-                    if (count > args.rows_per_rank) count = args.rows_per_rank;
-                    if (count > 0)
-                        bulk_copy_rows_to_cluster(cluster_map_shared(receive_base + rank * uint32_t(args.rows_per_rank) * SPLIT_ROW_BYTES, r),
-                                                  staging + uint32_t(first) * SPLIT_ROW_BYTES, uint32_t(count) * SPLIT_ROW_BYTES,
-                                                  cluster_map_shared(receive_bar, r));
-                }
+            if (uint32_t(reader) < splits) {      // one copy per thread, starting with the next rank: no owner is everyone's first
+                const uint32_t step = uint32_t(reader) + 1u;
+                const uint32_t r = rank + step < splits ? rank + step : rank + step - splits;
+                const int first = int(r) * args.rows_per_rank;
+                int count = tile_rows - first;
+                if (count > args.rows_per_rank) count = args.rows_per_rank;
+                if (count > 0)
+                    bulk_copy_rows_to_cluster(cluster_map_shared(receive_base + rank * uint32_t(args.rows_per_rank) * SPLIT_ROW_BYTES, r),
+                                              staging + uint32_t(first) * SPLIT_ROW_BYTES, uint32_t(count) * SPLIT_ROW_BYTES,
+                                              cluster_map_shared(receive_bar, r));
             }
             // (c) the rows this CTA owns: weights 2^(m_r - M) / sum_r 2^(m_r - M) l_r per row, then the weighted sum in rank
             //     order, 16 bytes of a row per thread and step

@@ -296,17 +296,16 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_c
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the copies below read these rows through the async proxy
         asm volatile("bar.sync 1, 128;" ::: "memory");
         cluster_wait();
-        if (reader == 0) {
-            for (uint32_t step = 1; step <= splits; ++step) {       // starting with the next rank: no owner is everyone's first
-                const uint32_t r = rank + step < splits ? rank + step : rank + step - splits;
-                const int first = int(r) * tokens_per_rank;
-                int count = args.tokens - first;
-                if (count > tokens_per_rank) count = tokens_per_rank;
-                if (count > 0)
-                    bulk_copy_to_cluster(cluster_map_shared(receive_base + rank * uint32_t(tokens_per_rank) * ROW_BYTES, r),
-                                         base + uint32_t(first) * ROW_BYTES, uint32_t(count) * ROW_BYTES,
-                                         cluster_map_shared(receive_bar, r));
-            }
+        if (uint32_t(reader) < splits) {      // one copy per thread, starting with the next rank: no owner is everyone's first
+            const uint32_t step = uint32_t(reader) + 1u;
+            const uint32_t r = rank + step < splits ? rank + step : rank + step - splits;
+            const int first = int(r) * tokens_per_rank;
+            int count = args.tokens - first;
+            if (count > tokens_per_rank) count = tokens_per_rank;
+            if (count > 0)
+                bulk_copy_to_cluster(cluster_map_shared(receive_base + rank * uint32_t(tokens_per_rank) * ROW_BYTES, r),
+                                     base + uint32_t(first) * ROW_BYTES, uint32_t(count) * ROW_BYTES,
+                                     cluster_map_shared(receive_bar, r));
         }
 
         // (b) the tokens this CTA owns: all 128 threads add the S partial rows in rank order, one 16-byte column each
