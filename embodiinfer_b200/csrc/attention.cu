@@ -675,36 +675,48 @@ int launch_attention(const void* q, const void* k, const void* v, void* out, voi
     args.scale_log2 = 1.4426950408889634f / 16.0f;
     args.splits = 1;
     args.rows_per_rank = 0;
-    // Few CTAs and several key tiles: the keys of a tile are cut across a cluster -- one CTA per key tile up to the largest
-    // cluster this device schedules (16 where the opt-in sizes are available, else 8) -- as long as the launch stays well
-    // inside one wave and the partial rows of a tile (sent and received) fit over the operand stages.
+    // Few CTAs and several key tiles: the keys of a tile are cut across a cluster, as long as all clusters of the launch run
+    // at once and the partial rows of a tile (sent and received) fit over the operand stages.
     const int key_tiles = (keys + ATT_KEYS - 1) / ATT_KEYS;
     const int tiles = batch * args.tiles_per_batch;
-    static int largest_cluster[64] = {0};
-    if (device >= 0 && device < 64 && largest_cluster[device] == 0) {
-        largest_cluster[device] = 8;
-        if (cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+    // How many clusters of each size the device runs at once is asked of the driver, once per device (sizes above 8 are the
+    // opt-in ones; a size the device does not schedule reports 0): a launch takes the largest cluster, up to one CTA per
+    // key tile, whose clusters are all resident together.
+    static int resident_clusters[64][17] = {};
+    static bool probed[64] = {false};
+    if (device >= 0 && device < 64 && !probed[device]) {
+        const bool wide = cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        for (int size = 2; size <= 16; ++size) {
+            resident_clusters[device][size] = 0;
+            if (size > 8 && !wide) continue;
             cudaLaunchConfig_t probe = {};
-            probe.gridDim = dim3(16);
+            probe.gridDim = dim3(unsigned(size));
             probe.blockDim = dim3(ATT_THREADS);
             probe.dynamicSmemBytes = size_t(ATT_SHARED_BYTES);
             cudaLaunchAttribute cluster;
             cluster.id = cudaLaunchAttributeClusterDimension;
-            cluster.val.clusterDim.x = 16;
+            cluster.val.clusterDim.x = unsigned(size);
             cluster.val.clusterDim.y = 1;
             cluster.val.clusterDim.z = 1;
             probe.attrs = &cluster;
             probe.numAttrs = 1;
             int clusters = 0;
-            if (cudaOccupancyMaxActiveClusters(&clusters, attention_kernel<true>, &probe) == cudaSuccess && clusters >= 4)
-                largest_cluster[device] = 16;
+            if (cudaOccupancyMaxActiveClusters(&clusters, attention_kernel<true>, &probe) == cudaSuccess) resident_clusters[device][size] = clusters;
         }
         cudaGetLastError();
+        probed[device] = true;
     }
-    const int cluster_limit = device >= 0 && device < 64 ? largest_cluster[device] : 8;
-    int splits = key_tiles < cluster_limit ? key_tiles : cluster_limit;
-    if (tiles * splits > sm_count() / 2) splits = key_tiles >= 8 ? 8 : key_tiles >= 4 ? 4 : key_tiles >= 2 ? 2 : 1;
-    while (splits > 1 && tiles * splits > sm_count() / 2) splits /= 2;
+    int splits = 1;
+    if (device >= 0 && device < 64) {
+        for (int size = key_tiles < 16 ? key_tiles : 16; size >= 2; --size) {
+            if (size > 8 && size != key_tiles) continue;                 // beyond 8 only for one CTA per key tile
+            if (size <= 8 && (size & (size - 1)) != 0 && size != key_tiles) continue;      // else powers of two
+            if (tiles <= resident_clusters[device][size]) {
+                splits = size;
+                break;
+            }
+        }
+    }
     if (splits > 1 && args.tiles_per_batch == 1) {
         const int rows = int(rows_per_batch);
         const int rows_per_rank = (rows + splits - 1) / splits;
