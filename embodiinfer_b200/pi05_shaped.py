@@ -394,7 +394,7 @@ class GemmaBlock(nn.Module):
         own_kv = (k, v)
         # b2_attention: one CTA per 128 query rows of a batch element; launches of few such tiles (a handful of observations'
         # ten-token chunks) cut the keys of a tile across a thread-block cluster instead of walking them serially
-        # (measured, 8 heads x 10 queries over 570 keys: B = 1 / 8 / 32 / 64 take 7.2 / 7.7 / 12.3 / 15.0 us against
+        # (measured, 8 heads x 10 queries over 570 keys: B = 1 / 8 / 32 / 64 take 7.2 / 7.8 / 11.4 / 14.5 us against
         # 11.3 / 20.7 / 33.1 / 63.0 for torch's kernel).
         native = self.native_attention and shape.head_dim == 256 and shape.kv_heads == 1
         output_encoder = self.o_proj.attention_output if self.fused_norm else None
