@@ -427,14 +427,47 @@ skinny_linear_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_c
 // ---------------------------------------------------------------------------
 // host side
 
-// Cluster size for `tiles` feature tiles and `num_kb` K atoms: the largest of 8, 4, 2 that keeps the launch in one wave
-// of clusters (an SM runs one CTA of this kernel; a cluster sits inside one GPC, which holds two clusters of 8, four of
-// 4 ...) and leaves every CTA at least one K atom.
+// Clusters of 2, 4 and 8 CTAs of this kernel that the device runs at once (one CTA per SM: 120 KB of shared memory at
+// least), asked of the driver once per device; a cluster sits inside one GPC, so the answer is not SMs / size.
+static int resident_clusters(int size) {
+    static int answers[64][9] = {};
+    static bool probed[64] = {false};
+    static std::mutex lock;
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64) return sm_count() / size - 2;
+    std::lock_guard<std::mutex> guard(lock);
+    if (!probed[device]) {
+        cudaFuncSetAttribute(skinny_linear_kernel<B2_KIND_FP8, EPI_LINEAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+        for (int candidate = 2; candidate <= 8; candidate *= 2) {
+            cudaLaunchConfig_t probe = {};
+            probe.gridDim = dim3(unsigned(candidate));
+            probe.blockDim = dim3(unsigned(SKINNY_THREADS));
+            probe.dynamicSmemBytes = size_t(SMEM_MINIMUM);
+            cudaLaunchAttribute cluster;
+            cluster.id = cudaLaunchAttributeClusterDimension;
+            cluster.val.clusterDim.x = unsigned(candidate);
+            cluster.val.clusterDim.y = 1;
+            cluster.val.clusterDim.z = 1;
+            probe.attrs = &cluster;
+            probe.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, skinny_linear_kernel<B2_KIND_FP8, EPI_LINEAR>, &probe) != cudaSuccess || clusters <= 0)
+                clusters = sm_count() / candidate - (candidate == 8 ? 4 : candidate == 4 ? 4 : 2);      // the guess used before the query
+            answers[device][candidate] = clusters;
+        }
+        cudaGetLastError();
+        probed[device] = true;
+    }
+    return answers[device][size];
+}
+
+// Cluster size for `tiles` feature tiles and `num_kb` K atoms: the largest of 8, 4, 2 whose clusters are all resident at
+// once and that leaves every CTA at least one K atom.
 static int skinny_cluster(int tiles, int num_kb) {
-    const int sms = sm_count();
-    if (tiles <= sms / 8 - 2 && num_kb >= 8) return 8;      // 148 SMs: up to 16 clusters of 8
-    if (tiles <= sms / 4 - 4 && num_kb >= 4) return 4;      // up to 33 clusters of 4
-    if (tiles <= sms / 2 - 2 && num_kb >= 2) return 2;
+    if (num_kb >= 8 && tiles <= resident_clusters(8)) return 8;
+    if (num_kb >= 4 && tiles <= resident_clusters(4)) return 4;
+    if (num_kb >= 2 && tiles <= resident_clusters(2)) return 2;
     return 1;
 }
 
