@@ -156,6 +156,46 @@ def test_gated_epilogues(device, kind, tokens, features, width, tile):
     assert np.array_equal(u8(out4), want4[0]) and np.array_equal(u8(linear), want4[1]) and np.array_equal(u8(blocked), want4[2])
 
 
+@pytest.mark.parametrize("tokens,features,width", [(513, 512, 256), (640, 384, 512), (1100, 256, 1024), (560, 16384, 2048)])
+def test_gated_nvfp4_ragged_last_token_pair(device, tokens, features, width):
+    """Gated NVFP4 launches whose last token pair is mostly padding (1, 128, 76 and 48 rows of its 256): every row
+    against the oracle, nothing past the last row, and codes, row-major and blocked scales exactly the encodings of the
+    launch's own bf16 hidden, with and without the row-major scale output."""
+    host, dev = operands("nvfp4", tokens, 2 * features, width, 77 + tokens, device)
+    table_host = gelu_table_cpu("tanh")
+    table = torch.from_numpy(table_host.view(np.int16).copy()).view(torch.uint16).to(device)
+    status = torch.zeros(1, device=device, dtype=torch.int32)
+    common = dict(epilogue=N.EPI_GEGLU, tokens=tokens, features=features, width=width, gelu_table=table,
+                  gelu_range=K.gelu_table_range(table), status=status, **dev)
+    hidden = torch.full((tokens + 1, features), float("nan"), device=device, dtype=torch.bfloat16)
+    K.linear(out_format=N.OUT_BF16, out=hidden[:tokens], **common)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert torch.isnan(hidden[tokens]).all(), "wrote past the last token row"
+    got_hidden = bits(hidden[:tokens])
+    if features <= 512:
+        y = O.f32_to_bf16((accumulate("nvfp4", host) * float(host["a_s"]) * float(host["w_s"])).astype(np.float32))
+        assert_gemm_close(got_hidden, O.gelu_mul(y[:, :features], y[:, features:], table_host))
+    else:       # the benchmark's size: a launch with the pair schedule forced must agree to the same tolerance
+        paired = torch.empty((tokens, features), device=device, dtype=torch.bfloat16)
+        K.linear(out_format=N.OUT_BF16, out=paired, flags=N.LINEAR_PAIRS, **common)
+        assert_gemm_close(got_hidden, bits(paired))
+    scale4 = np.float32(float(np.abs(O.bf16_to_f32(got_hidden)).max()) / (448.0 * 6.0))
+    want4 = O.nvfp4_quantize_C(got_hidden, scale4)
+    for with_rows in (True, False):
+        out4 = torch.full((tokens + 1, features // 2), 0xA5, device=device, dtype=torch.uint8)
+        linear = torch.empty((tokens, features // 16), device=device, dtype=torch.uint8) if with_rows else None
+        blocked = torch.zeros(blocked_scale_bytes(tokens, features), device=device, dtype=torch.uint8)
+        K.linear(out_format=N.OUT_NVFP4, out=out4[:tokens], out_scales=linear, out_blocked=blocked,
+                 out_scale=torch.tensor(float(scale4), device=device), **common)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        assert (out4[tokens] == 0xA5).all()
+        assert np.array_equal(u8(out4[:tokens]), want4[0]) and np.array_equal(u8(blocked), want4[2])
+        if with_rows:
+            assert np.array_equal(u8(linear), want4[1])
+
+
 @pytest.mark.parametrize("kind", ("fp8", "nvfp4"))
 @pytest.mark.parametrize("tokens,features,width", [(10, 4096, 1024), (37, 384, 1536), (128, 256, 4096), (3, 128, 64)])
 def test_cluster_schedule_epilogues(device, kind, tokens, features, width):
