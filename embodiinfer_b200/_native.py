@@ -28,7 +28,7 @@ NORM_RESIDUAL_EVICT_LAST = 1
 SCALE_SCRATCH_BYTES = 8
 STATIC_SCRATCH_BYTES = 16640
 STATIC_SCALE_MAX_COUNT = 67108864
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 _ERRORS = {
     E_INVALID: "invalid argument (null, non-positive size or misaligned pointer)",
@@ -111,6 +111,7 @@ SIGNATURES: dict[str, list] = {
     "b2_rope_split": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I64, _I, _I, _P],
     "b2_attention": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "b2_attention_fp8": [_P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _P, _P],
+    "b2_attention_nvfp4": [_P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _P, _P],
 }
 RESULT_TYPES = {"b2_linear_workspace_bytes": ctypes.c_int64}
 

@@ -6,8 +6,9 @@
 
 namespace b2 {
 int run_linear(const b2_linear_desc* desc, cudaStream_t stream, int64_t* workspace_need = nullptr);
-int launch_attention(const void* q, const void* k, const void* v, void* out, void* codes, float multiplier, int batch, int heads,
-                     int queries, int keys, int head_dim, void* status, cudaStream_t stream);
+int launch_attention(const void* q, const void* k, const void* v, void* out, void* codes, float multiplier, void* block_scales,
+                     void* blocked, float global_scale, int batch, int heads, int queries, int keys, int head_dim, void* status,
+                     cudaStream_t stream);
 int launch_rope_split(const void* qkv, const void* sine, const void* cosine, void* q_out, void* k_out, void* v_out, int batch,
                       int tokens, int heads, int kv_heads, int head_dim, int64_t factor_batch_stride, int kv_capacity,
                       int kv_offset, cudaStream_t stream);
@@ -140,7 +141,7 @@ int b2_attention(const void* q, const void* k, const void* v, void* out, int32_t
     const uintptr_t alignment = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
                                 reinterpret_cast<uintptr_t>(out);
     if (alignment & 15u) return B2_E_INVALID;
-    return b2::launch_attention(q, k, v, out, nullptr, 1.0f, batch, heads, queries, keys, head_dim, status, static_cast<cudaStream_t>(stream));
+    return b2::launch_attention(q, k, v, out, nullptr, 1.0f, nullptr, nullptr, 1.0f, batch, heads, queries, keys, head_dim, status, static_cast<cudaStream_t>(stream));
 }
 
 int b2_attention_fp8(const void* q, const void* k, const void* v, void* codes, float multiplier, int32_t batch, int32_t heads,
@@ -151,7 +152,19 @@ int b2_attention_fp8(const void* q, const void* k, const void* v, void* codes, f
     const uintptr_t alignment = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
                                 reinterpret_cast<uintptr_t>(codes);
     if (alignment & 15u) return B2_E_INVALID;
-    return b2::launch_attention(q, k, v, nullptr, codes, multiplier, batch, heads, queries, keys, head_dim, status, static_cast<cudaStream_t>(stream));
+    return b2::launch_attention(q, k, v, nullptr, codes, multiplier, nullptr, nullptr, 1.0f, batch, heads, queries, keys, head_dim, status, static_cast<cudaStream_t>(stream));
+}
+
+int b2_attention_nvfp4(const void* q, const void* k, const void* v, void* codes, void* scales, void* blocked, float global_scale,
+                       int32_t batch, int32_t heads, int32_t queries, int32_t keys, int32_t head_dim, void* status, void* stream) {
+    if (q == nullptr || k == nullptr || v == nullptr || codes == nullptr || blocked == nullptr) return B2_E_INVALID;
+    if (batch <= 0 || heads <= 0 || queries <= 0 || keys <= 0 || head_dim <= 0) return B2_E_INVALID;
+    if (!(global_scale > 0.0f) || global_scale > 3.0e38f) return B2_E_INVALID;
+    const uintptr_t alignment = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                                reinterpret_cast<uintptr_t>(codes);
+    if (alignment & 15u) return B2_E_INVALID;
+    return b2::launch_attention(q, k, v, nullptr, codes, 1.0f, scales, blocked, global_scale, batch, heads, queries, keys, head_dim, status,
+                                static_cast<cudaStream_t>(stream));
 }
 
 int b2_rope_split(const void* qkv, const void* sine, const void* cosine, void* q_out, void* k_out, void* v_out,

@@ -144,10 +144,34 @@ __device__ __forceinline__ uint2 encode_row_words(const uint32_t (&words)[4], fl
     return make_uint2(codes[0] | (codes[1] << 16), codes[2] | (codes[3] << 16));
 }
 
+// Eight values of an NVFP4 block whose other eight the neighbouring lane (lane ^ 1) holds -> eight e2m1 codes and the
+// block's e4m3 scale: the arithmetic of the stand-alone output encoder (bhsd_encode_kernel, bits 4; quantize.cu:85-104).
+// Every lane of the warp calls this.
+__device__ __forceinline__ uint32_t encode_half_block_nvfp4(const uint32_t (&words)[4], float global, const ExactDivider& by_global,
+                                                            uint8_t& scale_code) {
+    float maximum = abs_max_bf16_words(words);
+    maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
+    scale_code = nvfp4_block_scale<true>(maximum, by_global, 0);
+    const ExactDivider denominator(__fmul_rn(global, e4m3_to_float(scale_code)));
+    if (denominator.fast && __fmul_rn(maximum, denominator.reciprocal) < 1.0e30f)
+        return nvfp4_encode_words_short<true>(words[0], words[1], words[2], words[3], denominator);
+    float values[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        values[2 * i] = bf16_lo(words[i]);
+        values[2 * i + 1] = bf16_hi(words[i]);
+    }
+    return nvfp4_encode_x8<true>(values, denominator, maximum);
+}
+
 struct AttentionArgs {
     __nv_bfloat16* out;          // [batch, heads * queries, 256], or nullptr when `codes` is given
     uint8_t* codes;              // e4m3 [batch * queries, heads * 256]: the encoded rows of the output projection, or nullptr
     float multiplier;            // codes = e4m3(bf16(out) * multiplier)
+    uint8_t* blocked;            // given: `codes` are e2m1 pairs [batch * queries, heads * 128] instead, with their e4m3 block
+                                 // scales here in 128 x 4 tile order (the stand-alone output encoder's bits = 4 form)
+    uint8_t* block_scales;       // the same block scales row-major [batch * queries, heads * 16], or nullptr
+    float global_scale;          // NVFP4: the projection's static global scale
     int queries;                 // queries per head (row of a batch element = head * queries + query)
     unsigned int* status;
     int rows_per_batch;          // heads * queries
@@ -511,6 +535,7 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             __nv_bfloat16* tile_out = args.out + (int64_t(batch) * args.rows_per_batch + row0 + first_row) * ATT_D;
             // The cluster size is a compile-time constant of the loop body (one copy per size, chosen below): with a run-time
             // bound every partial row is its own basic block and the single warp of a scheduler crawls through them.
+            const ExactDivider by_global(__fmul_rn(6.0f, args.global_scale));
             auto combine = [&](auto size_tag) {
                 constexpr uint32_t SIZE = decltype(size_tag)::value;
                 for (int slot = reader; slot < owned * 32; slot += 128) {
@@ -562,8 +587,21 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                         const int tile_row = row0 + first_row + int(local);
                         const int head = tile_row / args.queries, query = tile_row - head * args.queries;
                         const int64_t width = int64_t(args.rows_per_batch / args.queries) * ATT_D;
-                        uint8_t* destination = args.codes + (int64_t(batch) * args.queries + query) * width + head * ATT_D + column * 8u;
-                        *reinterpret_cast<uint2*>(destination) = encode_row_words(words, args.multiplier);
+                        const int64_t out_row = int64_t(batch) * args.queries + query;
+                        const int64_t element = out_row * width + head * ATT_D + column * 8u;
+                        if (args.blocked != nullptr) {
+                            // a warp's 32 slots are the 32 column groups of one row: lanes 2j and 2j + 1 hold one block
+                            uint8_t scale_code;
+                            const uint32_t nibbles = encode_half_block_nvfp4(words, args.global_scale, by_global, scale_code);
+                            *reinterpret_cast<uint32_t*>(args.codes + (element >> 1)) = nibbles;
+                            if ((column & 1u) == 0u) {
+                                const int block = (head * ATT_D + int(column) * 8) >> 4, blocks_per_row = int(width >> 4);
+                                args.blocked[scale_tile_offset(int(out_row), block, (blocks_per_row + 3) >> 2)] = scale_code;
+                                if (args.block_scales != nullptr) args.block_scales[out_row * blocks_per_row + block] = scale_code;
+                            }
+                        } else {
+                            *reinterpret_cast<uint2*>(args.codes + element) = encode_row_words(words, args.multiplier);
+                        }
                     } else {
                         *reinterpret_cast<uint4*>(tile_out + local * ATT_D + column * 8u) = make_uint4(words[0], words[1], words[2], words[3]);
                     }
@@ -606,7 +644,24 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                         const int tile_row = row0 + row;
                         const int head = tile_row / args.queries, query = tile_row - head * args.queries;
                         const int64_t width = int64_t(args.rows_per_batch / args.queries) * ATT_D;
-                        uint8_t* encoded = args.codes + (int64_t(batch) * args.queries + query) * width + head * ATT_D + group * 128 + c * 32;
+                        const int64_t out_row = int64_t(batch) * args.queries + query;
+                        const int64_t element = out_row * width + head * ATT_D + group * 128 + c * 32;
+                        if (args.blocked != nullptr) {      // two whole blocks of this row
+                            const ExactDivider out_scale(args.global_scale), by_global(__fmul_rn(6.0f, args.global_scale));
+                            const uint32_t first[8] = {words[0], words[1], words[2], words[3], words[4], words[5], words[6], words[7]};
+                            const uint32_t second[8] = {words[8], words[9], words[10], words[11], words[12], words[13], words[14], words[15]};
+                            uint8_t code[2];
+                            const uint2 low = hidden_block_nvfp4(first, out_scale, by_global, code[0]);
+                            const uint2 high = hidden_block_nvfp4(second, out_scale, by_global, code[1]);
+                            *reinterpret_cast<uint4*>(args.codes + (element >> 1)) = make_uint4(low.x, low.y, high.x, high.y);
+                            const int block = (head * ATT_D + group * 128 + c * 32) >> 4, blocks_per_row = int(width >> 4);
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                args.blocked[scale_tile_offset(int(out_row), block + half, (blocks_per_row + 3) >> 2)] = code[half];
+                                if (args.block_scales != nullptr) args.block_scales[out_row * blocks_per_row + block + half] = code[half];
+                            }
+                        } else {
+                        uint8_t* encoded = args.codes + element;
                         uint2 part[4];
 #pragma unroll
                         for (int v = 0; v < 4; ++v) {
@@ -615,6 +670,7 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                         }
                         *reinterpret_cast<uint4*>(encoded) = make_uint4(part[0].x, part[0].y, part[1].x, part[1].y);
                         *reinterpret_cast<uint4*>(encoded + 16) = make_uint4(part[2].x, part[2].y, part[3].x, part[3].y);
+                        }
                     } else {
                     const uint32_t first[8] = {words[0], words[1], words[2], words[3], words[4], words[5], words[6], words[7]};
                     const uint32_t second[8] = {words[8], words[9], words[10], words[11], words[12], words[13], words[14], words[15]};
@@ -643,9 +699,12 @@ attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
 
 }  // namespace
 
-// `out`: bf16 [batch, heads, queries, 256]; or, with `codes` given, e4m3 [batch * queries, heads * 256] at `multiplier` and no `out`.
-int launch_attention(const void* q, const void* k, const void* v, void* out, void* codes, float multiplier, int batch, int heads,
-                     int queries, int keys, int head_dim, void* status, cudaStream_t stream) {
+// `out`: bf16 [batch, heads, queries, 256]; or, with `codes` given and no `out`, e4m3 [batch * queries, heads * 256] at
+// `multiplier`; or, with `blocked` given as well, e2m1 pairs [batch * queries, heads * 128] with their block scales at
+// `global_scale` (`block_scales`: the row-major copy, optional).
+int launch_attention(const void* q, const void* k, const void* v, void* out, void* codes, float multiplier, void* block_scales,
+                     void* blocked, float global_scale, int batch, int heads, int queries, int keys, int head_dim, void* status,
+                     cudaStream_t stream) {
     if (head_dim != ATT_D) return B2_E_UNSUPPORTED;
     const int64_t rows_per_batch = int64_t(heads) * queries;
     if (rows_per_batch * batch >= (int64_t(1) << 31) || int64_t(keys) * batch >= (int64_t(1) << 31)) return B2_E_TOO_LARGE;
@@ -667,6 +726,9 @@ int launch_attention(const void* q, const void* k, const void* v, void* out, voi
     args.out = static_cast<__nv_bfloat16*>(out);
     args.codes = static_cast<uint8_t*>(codes);
     args.multiplier = multiplier;
+    args.blocked = static_cast<uint8_t*>(blocked);
+    args.block_scales = static_cast<uint8_t*>(block_scales);
+    args.global_scale = global_scale;
     args.queries = queries;
     args.status = static_cast<unsigned int*>(status);
     args.rows_per_batch = int(rows_per_batch);

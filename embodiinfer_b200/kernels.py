@@ -163,11 +163,14 @@ def geglu(
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None, *, status: torch.Tensor | None = None,
-              codes: torch.Tensor | None = None, multiplier: float | None = None) -> torch.Tensor:
+              codes: torch.Tensor | None = None, multiplier: float | None = None, blocked: torch.Tensor | None = None,
+              scales: torch.Tensor | None = None, global_scale: float | None = None) -> torch.Tensor:
     """Unmasked multi-query attention, ``softmax(q k^T / sqrt(D)) v``: q [B, H, T, 256], k / v [B, 1, S, 256], all
     contiguous bf16; returns [B, H, T, 256] (``b2_attention``; the reference's ``SDPAAttention``).  With ``codes`` (a
     contiguous 1-byte [B*T, H*256] tensor) and ``multiplier`` the output is written as the e4m3 rows of the output
-    projection instead (``b2_attention_fp8``) and ``codes`` is returned."""
+    projection instead (``b2_attention_fp8``) and ``codes`` is returned.  With ``codes`` ([B*T, H*128] bytes), ``blocked``
+    (the tiled block scales, padding zeroed), ``global_scale`` and optionally ``scales`` (row-major [B*T, H*16]) it is
+    written as the projection's NVFP4 rows (``b2_attention_nvfp4``)."""
     _require_cuda(q, k, v)
     if q.dim() != 4 or k.shape != v.shape or k.dim() != 4 or k.shape[1] != 1 or k.shape[0] != q.shape[0] or k.shape[3] != q.shape[3]:
         raise ValueError("attention requires q [B, H, T, D] and k, v [B, 1, S, D]")
@@ -176,6 +179,21 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tens
     batch, heads, queries, head_dim = q.shape
     if status is None:
         status = status_word(q.device)
+    if codes is not None and blocked is not None:
+        rows, blocks = batch * queries, heads * head_dim // 16
+        if global_scale is None or codes.element_size() != 1 or not codes.is_contiguous() or codes.numel() * 2 != q.numel() or \
+                codes.device != q.device or blocked.element_size() != 1 or not blocked.is_contiguous() or blocked.device != q.device or \
+                blocked.numel() < (rows + 127) // 128 * ((blocks + 3) // 4) * 512:
+            raise ValueError("NVFP4 attention output needs contiguous codes [B*T, H*D/2], tiled block scales and a global scale")
+        if scales is not None and (scales.element_size() != 1 or not scales.is_contiguous() or scales.numel() != rows * blocks or
+                                   scales.device != q.device):
+            raise ValueError("row-major block scales must be a contiguous 1-byte [B*T, H*D/16] tensor")
+        with torch.cuda.device(q.device):
+            code = N.load().b2_attention_nvfp4(q.data_ptr(), k.data_ptr(), v.data_ptr(), codes.data_ptr(),
+                                               None if scales is None else scales.data_ptr(), blocked.data_ptr(), float(global_scale),
+                                               batch, heads, queries, k.shape[2], head_dim, status.data_ptr(), _stream(q.device))
+        N.check(code, "b2_attention_nvfp4")
+        return codes
     if codes is not None:
         if multiplier is None or codes.element_size() != 1 or not codes.is_contiguous() or codes.numel() != q.numel() or codes.device != q.device:
             raise ValueError("encoded attention output must be a contiguous 1-byte [B*T, H*D] tensor with a multiplier")

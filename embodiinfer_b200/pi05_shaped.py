@@ -306,7 +306,7 @@ class GemmaBlock(nn.Module):
         self.mlp_norm: FusedNorm | None = None
         self.fused_norm = True
         self.native_attention = True        # b2_attention instead of torch's scaled_dot_product_attention (head dimension 256, one kv head)
-        self.encode_in_attention = True     # FP8 output projection: the attention kernel writes its encoded input rows
+        self.encode_in_attention = True     # the attention kernel writes the output projection's encoded input rows
         self.rope_in_projection = True      # adaptive blocks, FP8: the QKV projection's launch does the attention preparation
 
     def mlp(self, x: torch.Tensor) -> torch.Tensor:
@@ -399,10 +399,15 @@ class GemmaBlock(nn.Module):
         native = self.native_attention and shape.head_dim == 256 and shape.kv_heads == 1
         output_encoder = self.o_proj.attention_output if self.fused_norm else None
         encoded = None
-        if native and output_encoder is not None and output_encoder.bits == 8 and self.encode_in_attention:
-            # the attention kernel writes the e4m3 rows of the output projection itself (b2_attention_fp8): one launch less
+        if native and output_encoder is not None and self.encode_in_attention:
+            # the attention kernel writes the encoded rows of the output projection itself (b2_attention_fp8 /
+            # b2_attention_nvfp4): one launch less
             encoded, attended = output_encoder.plan_for(q), None
-            K.attention(q, k, v, codes=encoded.output, multiplier=output_encoder.scale_value)
+            if output_encoder.bits == 8:
+                K.attention(q, k, v, codes=encoded.output, multiplier=output_encoder.scale_value)
+            else:
+                K.attention(q, k, v, codes=encoded.output, blocked=encoded.blocked, scales=encoded.scales,
+                            global_scale=output_encoder.scale_value)
         elif native:
             attended = K.attention(q, k, v)           # tcgen05 multi-query attention (b2_attention)
         else:

@@ -21,7 +21,8 @@
 extern "C" {
 #endif
 
-/* 6: launches of at most 128 tokens may run on the cluster schedule (weights as the MMA's "A" operand, K split across a
+/* 7: b2_attention_nvfp4.
+ * 6: launches of at most 128 tokens may run on the cluster schedule (weights as the MMA's "A" operand, K split across a
  * thread-block cluster; B2_LINEAR_CLUSTER asks for it whenever it applies, B2_LINEAR_SINGLE_CTA opts out);
  * b2_gelu_table_range returns ranges on multiples of eight codes; FP8 launches accept 32 features per tile;
  * b2_attention_fp8; b2_linear_desc.rope (the attention preparation as the projection's epilogue).
@@ -30,7 +31,7 @@ extern "C" {
  * b2_linear_desc are rejected; the opt-in cluster split of K of version 3 (flag value 32) is gone.
  * 3: added the producers in front of the GEMMs (b2_norm_quant, b2_layer_norm_quant, b2_bhsd_quant, b2_normalize_frames,
  * b2_frames_to_patches, b2_resize_frames). */
-#define B2_ABI_VERSION 6
+#define B2_ABI_VERSION 7
 
 /* ---- status codes ---------------------------------------------------------- */
 #define B2_OK 0
@@ -232,6 +233,14 @@ int b2_attention(const void* q, const void* k, const void* v, void* out, int32_t
  * expert's chain of short kernels.  multiplier: 448 / calibrated maximum, finite and positive. */
 int b2_attention_fp8(const void* q, const void* k, const void* v, void* codes, float multiplier, int32_t batch, int32_t heads,
                      int32_t queries, int32_t keys, int32_t head_dim, void* status, void* stream);
+
+/* The same attention with the output written as the NVFP4 rows of the output projection: `codes` packed e2m1
+ * [batch * queries, heads * head_dim / 2], `blocked` their e4m3 block scales in 128 x 4 tile order (padding zeroed by the
+ * caller), `scales` the same block scales row-major [batch * queries, heads * head_dim / 16] or NULL -- bit-identical to
+ * b2_attention followed by b2_bhsd_quant (bits 4, scale_value = global_scale).  global_scale: the projection's static
+ * global scale (calibrated maximum / (448 * 6)), finite and positive. */
+int b2_attention_nvfp4(const void* q, const void* k, const void* v, void* codes, void* scales, void* blocked, float global_scale,
+                       int32_t batch, int32_t heads, int32_t queries, int32_t keys, int32_t head_dim, void* status, void* stream);
 
 /* RMSNorm (+ residual update, + adaptive modulation) fused with the activation encoder: the step in front of
  * every quantised projection.  Replaces cc_norm_quant and cc_norm_quant_reduce

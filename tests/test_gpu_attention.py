@@ -84,6 +84,41 @@ def test_encoded_output_matches_attention_then_encoder(device, batch, heads, que
     assert want.any()
 
 
+@pytest.mark.parametrize("batch,heads,queries,keys", [(1, 8, 10, 580), (3, 8, 10, 570), (2, 8, 560, 560), (40, 8, 10, 70), (2, 3, 77, 64)])
+@pytest.mark.parametrize("with_rows", (True, False))
+def test_nvfp4_output_matches_attention_then_encoder(device, batch, heads, queries, keys, with_rows):
+    """b2_attention_nvfp4 writes the NVFP4 rows of the output projection (e2m1 pairs, tiled and row-major e4m3 block scales):
+    the same bytes as b2_attention followed by b2_bhsd_quant (bits 4), on the split and the one-CTA-per-tile paths.  The
+    global scale is small enough for some block scales to saturate at 448 and some rows are zero (block scale 0)."""
+    generator = torch.Generator(device=device).manual_seed(batch + heads + queries + keys)
+    q = torch.randn((batch, heads, queries, 256), device=device, generator=generator).to(torch.bfloat16)
+    k = torch.randn((batch, 1, keys, 256), device=device, generator=generator).to(torch.bfloat16)
+    v = (3.0 * torch.randn((batch, 1, keys, 256), device=device, generator=generator)).to(torch.bfloat16)
+    v[:, :, :, 32:48] = 0                        # a block of zeros in every row
+    v[:, :, :, 100] *= 64.0                      # a block whose scale saturates
+    global_scale = 2.5 / (448.0 * 6.0)
+    rows, blocks = batch * queries, heads * 16
+    tiled = (rows + 127) // 128 * ((blocks + 3) // 4) * 512
+    status = torch.zeros(1, device=device, dtype=torch.int32)
+    out = K.attention(q, k, v, status=status)
+    want = torch.zeros((rows, heads * 128), device=device, dtype=torch.uint8)
+    want_rows = torch.zeros((rows, blocks), device=device, dtype=torch.uint8)
+    want_tiled = torch.zeros(tiled, device=device, dtype=torch.uint8)
+    K.bhsd_quant(out, want, bits=4, scale_value=global_scale, scales=want_rows, blocked=want_tiled)
+    got = torch.full((rows + 1, heads * 128), 0x7f, device=device, dtype=torch.uint8)
+    got_rows = torch.full((rows + 1, blocks), 0x7f, device=device, dtype=torch.uint8) if with_rows else None
+    got_tiled = torch.zeros(tiled, device=device, dtype=torch.uint8)
+    K.attention(q, k, v, codes=got[:-1], blocked=got_tiled, scales=None if got_rows is None else got_rows[:-1],
+                global_scale=global_scale, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(got[:-1], want) and torch.equal(got_tiled, want_tiled)
+    assert (got[-1] == 0x7f).all(), "wrote past the last row"
+    if with_rows:
+        assert torch.equal(got_rows[:-1], want_rows) and (got_rows[-1] == 0x7f).all()
+    assert want.any() and (want_rows == 0).any() and (want_rows == 0x7e).any()
+
+
 def test_attention_rejects_other_shapes(device):
     q = torch.zeros((1, 2, 4, 128), device=device, dtype=torch.bfloat16)
     k = torch.zeros((1, 1, 4, 128), device=device, dtype=torch.bfloat16)

@@ -63,8 +63,15 @@ def test_calibrated_fused_mlp_route_stays_close_to_the_registry_route(device, qu
     assert torch.isfinite(fused).all() and torch.equal(fused, policy(observations))
     error = (fused - reference).norm() / reference.norm()
     assert error < 0.1, float(error)
-    # the norm + encoder launch in front of the calibrated plans against torch's rms_norm + the separate encoder
     gemma = [*policy.prefix, *policy.expert]
+    # the attention kernel writes the output projection's encoded rows (e4m3 or NVFP4): the same bits as attention and
+    # encoder in two launches
+    for block in gemma:
+        block.encode_in_attention = False
+    assert torch.equal(policy(observations), fused)
+    for block in gemma:
+        block.encode_in_attention = True
+    # the norm + encoder launch in front of the calibrated plans against torch's rms_norm + the separate encoder
     assert all(block.mlp_norm is not None and block.qkv.norm is not None for block in gemma)
     assert all(block.mlp_norm is not None and block.qkv.layer_norm is not None for block in policy.vision)
     for block in [*gemma, *policy.vision]:
