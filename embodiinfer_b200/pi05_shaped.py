@@ -399,9 +399,11 @@ class GemmaBlock(nn.Module):
         native = self.native_attention and shape.head_dim == 256 and shape.kv_heads == 1
         output_encoder = self.o_proj.attention_output if self.fused_norm else None
         encoded = None
-        if native and output_encoder is not None and self.encode_in_attention:
-            # the attention kernel writes the encoded rows of the output projection itself (b2_attention_fp8 /
-            # b2_attention_nvfp4): one launch less
+        # The attention kernel writes the encoded rows of the output projection itself (b2_attention_fp8 /
+        # b2_attention_nvfp4): one launch less.  The NVFP4 encoding is some 150 instructions per 16 values on the four
+        # epilogue warps of a CTA, which only pays on the latency chain of a small launch (B = 1 / 8: 7.27 -> 7.16 and
+        # 9.45 -> 9.28 ms per chunk); the 560-token prefix (2.20 -> 2.40 ms per stack) and B = 64 keep the encoder launch.
+        if native and output_encoder is not None and self.encode_in_attention and (output_encoder.bits == 8 or batch * tokens <= 128):
             encoded, attended = output_encoder.plan_for(q), None
             if output_encoder.bits == 8:
                 K.attention(q, k, v, codes=encoded.output, multiplier=output_encoder.scale_value)
