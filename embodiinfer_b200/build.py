@@ -60,7 +60,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         str(LIBRARY_PATH),
         *[str(path) for path in sources()],
     ]
-    command[1:1] = os.environ.get("B2_NVCC_FLAGS", "").split()      # e.g. -DB2_TRACE for the kernel's stage trace
+    command[1:1] = os.environ.get("B2_NVCC_FLAGS", "").split()      # e.g. -DB2_GEGLU_EPILOGUE_WARPS=8 to sweep the gated epilogue
     if verbose:
         command.insert(1, "-Xptxas=-v")
     result = subprocess.run(command, capture_output=True, text=True)
